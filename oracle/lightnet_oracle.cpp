@@ -1,0 +1,1258 @@
+// lightnet_oracle.cpp -- CPU restatement of the lightnet detector-inference path.
+//
+// THIS IS TEST INFRASTRUCTURE, NOT PRODUCT CODE.  It is the checker the parity
+// tests, the smoke entry and the bench's cpu_baseline leg compare the CUDA path
+// against.  Nothing in the shipped library links, imports or executes it.
+//
+// Parity status:
+//   * f32 path (cfg parse, shape rules, conv, BN, activations, maxpool, route,
+//     shortcut, upsample, yolo decode, NMS, FP8 E4M3 codec): PINNED against the
+//     known-answer tests the reference carries for this path (see
+//     tests/test_oracle_kats.py, which cites each one).
+//   * int8 quantiser / int8 network: the reference has no int8 path, so the
+//     quantisation scheme itself is "parity unpinned"; it is defined here and the
+//     CUDA path is held bit-exact to this definition.
+//
+// Every function cites the reference file:line (paths inside the lightnet
+// project) whose behaviour it restates.  Plain scalar C++17, built with
+// `g++ -O2 -ffp-contract=off` (no fast-math) so that no multiply-add is contracted:
+// the reference is Rust, which never contracts.
+//
+// The optional OpenMP parallelism is over (image, filter) / (image) only; the
+// accumulation order of every single output value is unchanged, so results are
+// identical for any thread count.
+
+#include <algorithm>
+#include <cctype>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+#include <map>
+#include <memory>
+#include <numeric>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace orc {
+
+// ---------------------------------------------------------------------------
+// Model vocabulary
+// ---------------------------------------------------------------------------
+
+enum Act { ACT_LINEAR = 0, ACT_LOGISTIC = 1, ACT_LEAKY = 2, ACT_MISH = 3, ACT_SWISH = 4, ACT_RELU = 5 };
+enum Kind { K_CONV = 0, K_MAXPOOL = 1, K_ROUTE = 2, K_SHORTCUT = 3, K_UPSAMPLE = 4, K_YOLO = 5 };
+
+// lightnet-model/src/model.rs:19 TensorShape{width,height,channels,batch}
+struct Shape {
+    int w = 0, h = 0, c = 0, b = 0;
+    size_t count() const { return (size_t)w * h * c * b; }
+};
+
+// lightnet-model/src/model.rs:48,98  planar NCHW f32, offset = ((b*C+c)*H+y)*W+x
+struct Tensor {
+    Shape s;
+    std::vector<float> d;
+    Tensor() {}
+    explicit Tensor(Shape sh) : s(sh), d(sh.count(), 0.0f) {}
+    size_t off(int b, int c, int y, int x) const { return (((size_t)b * s.c + c) * s.h + y) * s.w + x; }
+    float get(int b, int c, int y, int x) const { return d[off(b, c, y, x)]; }
+    void set(int b, int c, int y, int x, float v) { d[off(b, c, y, x)] = v; }
+};
+
+struct TensorI8 {
+    Shape s;
+    std::vector<int8_t> d;  // NCHW
+    TensorI8() {}
+    explicit TensorI8(Shape sh) : s(sh), d(sh.count(), 0) {}
+    size_t off(int b, int c, int y, int x) const { return (((size_t)b * s.c + c) * s.h + y) * s.w + x; }
+};
+
+struct Layer {
+    Kind kind = K_CONV;
+    Shape in, out;
+    // convolutional (model.rs:4088-4144)
+    int filters = 1, size = 1, stride_x = 1, stride_y = 1, dilation = 1, padding = 0, groups = 1;
+    bool bn = false;
+    Act act = ACT_LOGISTIC;
+    // route / shortcut: absolute source indices
+    std::vector<int> sources;
+    int route_groups = 1, route_group_id = 0;
+    // upsample
+    int up_stride = 2;
+    float up_scale = 1.0f;
+    bool up_reverse = false;
+    // yolo
+    int classes = 20, num = 1;
+    std::vector<int> mask;
+    std::vector<float> anchors;
+    float scale_x_y = 1.0f;
+    bool new_coords = false;
+    // parameters (lightnet-layers/src/params.rs:7-26)
+    std::vector<float> biases, scales, mean, var, weights;
+    // int8 model
+    std::vector<int8_t> wq;      // [filters][C/g][k][k]
+    std::vector<float> wscale;   // per filter
+    std::vector<float> fbias;    // folded bias
+};
+
+struct Net {
+    int width = 0, height = 0, channels = 0, batch = 1;
+    std::vector<Layer> layers;
+    // per-run state
+    std::vector<Tensor> out_f32;
+    std::vector<TensorI8> out_q8;
+    std::vector<Tensor> head_q8;          // f32 heads of the int8 run, indexed by layer
+    std::vector<float> amax;              // [0] = input, [1+i] = layer i output (f32 run)
+    std::vector<float> scale;             // same indexing; per-tensor activation scale
+    std::string error;
+};
+
+// ---------------------------------------------------------------------------
+// cfg parsing: lightnet-model/src/cfg.rs:109-171 (sections, comments, lower-case
+// keys, last value wins) and :183-195 (lists split on ',' or whitespace).
+// ---------------------------------------------------------------------------
+
+struct Section {
+    std::string name;
+    int line = 0;
+    std::map<std::string, std::string> kv;
+    bool has(const std::string& k) const { return kv.count(k) != 0; }
+    std::string str(const std::string& k, const std::string& d) const {
+        auto it = kv.find(k);
+        return it == kv.end() ? d : it->second;
+    }
+    long long i64(const std::string& k, long long d) const {
+        auto it = kv.find(k);
+        if (it == kv.end()) return d;
+        try {
+            size_t pos = 0;
+            long long v = std::stoll(it->second, &pos);
+            if (pos != it->second.size()) throw std::invalid_argument("x");
+            return v;
+        } catch (...) { throw std::runtime_error("invalid integer for key " + k + " in [" + name + "]"); }
+    }
+    int usz(const std::string& k, int d) const {
+        long long v = i64(k, d);
+        if (v < 0) throw std::runtime_error("negative value for key " + k + " in [" + name + "]");
+        return (int)v;
+    }
+    float f32(const std::string& k, float d) const {
+        auto it = kv.find(k);
+        if (it == kv.end()) return d;
+        try { return std::stof(it->second); } catch (...) { throw std::runtime_error("invalid float for key " + k); }
+    }
+    bool flag(const std::string& k, bool d) const { return i64(k, d ? 1 : 0) != 0; }  // cfg.rs:78
+};
+
+static std::string trim(const std::string& s) {
+    size_t a = 0, b = s.size();
+    while (a < b && std::isspace((unsigned char)s[a])) ++a;
+    while (b > a && std::isspace((unsigned char)s[b - 1])) --b;
+    return s.substr(a, b - a);
+}
+static std::string lower(std::string s) {
+    for (auto& ch : s) ch = (char)std::tolower((unsigned char)ch);
+    return s;
+}
+
+static std::vector<Section> parse_cfg(const std::string& text) {
+    std::vector<Section> secs;
+    std::istringstream in(text);
+    std::string raw;
+    int ln = 0;
+    bool have = false;
+    while (std::getline(in, raw)) {
+        ++ln;
+        std::string line = raw;
+        size_t p = line.find('#');
+        if (p != std::string::npos) line = line.substr(0, p);
+        p = line.find(';');
+        if (p != std::string::npos) line = line.substr(0, p);
+        line = trim(line);
+        if (line.empty()) continue;
+        if (line.front() == '[' && line.back() == ']') {
+            Section s;
+            s.name = lower(trim(line.substr(1, line.size() - 2)));
+            s.line = ln;
+            secs.push_back(s);
+            have = true;
+            continue;
+        }
+        size_t eq = line.find('=');
+        if (eq == std::string::npos) throw std::runtime_error("invalid config line " + std::to_string(ln) + ": expected key=value");
+        if (!have) throw std::runtime_error("key/value before any section at line " + std::to_string(ln));
+        secs.back().kv[lower(trim(line.substr(0, eq)))] = trim(line.substr(eq + 1));
+    }
+    if (secs.empty()) throw std::runtime_error("no Darknet sections found");
+    return secs;
+}
+
+template <class T>
+static std::vector<T> parse_list(const Section& s, const std::string& key) {
+    std::vector<T> out;
+    auto it = s.kv.find(key);
+    if (it == s.kv.end()) return out;
+    std::string item;
+    auto flush = [&]() {
+        if (item.empty()) return;
+        try {
+            if (std::is_floating_point<T>::value) out.push_back((T)std::stof(item));
+            else out.push_back((T)std::stoll(item));
+        } catch (...) { throw std::runtime_error("failed to parse list item \"" + item + "\" for key " + key); }
+        item.clear();
+    };
+    for (char ch : it->second) {
+        if (ch == ',' || std::isspace((unsigned char)ch)) flush();
+        else item.push_back(ch);
+    }
+    flush();
+    return out;
+}
+
+// model.rs:377 Activation::parse (subset reachable from the detector cfgs)
+static Act parse_act(const std::string& s) {
+    std::string a = lower(s);
+    if (a == "linear") return ACT_LINEAR;
+    if (a == "logistic") return ACT_LOGISTIC;
+    if (a == "leaky") return ACT_LEAKY;
+    if (a == "mish") return ACT_MISH;
+    if (a == "swish") return ACT_SWISH;
+    if (a == "relu") return ACT_RELU;
+    throw std::runtime_error("activation \"" + s + "\" is outside the oracle's scope");
+}
+
+// model.rs:6472 conv_dim, model.rs:8854 pool_dim
+static int conv_dim(int in, int pad, int size, int stride) {
+    int v = in + 2 * pad - size;
+    if (v < 0) v = 0;
+    return v / std::max(stride, 1) + 1;
+}
+static int pool_dim(int in, int pad, int size, int stride) {
+    int v = in + pad - size;
+    if (v < 0) v = 0;
+    return v / std::max(stride, 1) + 1;
+}
+
+// model.rs:6208 resolve_relative_layer
+static int resolve_rel(int layer_index, long long raw) {
+    long long a = raw < 0 ? layer_index + raw : raw;
+    if (a < 0 || a >= layer_index) throw std::runtime_error("invalid route reference at layer " + std::to_string(layer_index));
+    return (int)a;
+}
+
+// model.rs:3079 Network::from_config, restricted to the six layer kinds on the path.
+static std::unique_ptr<Net> build_net(const std::string& cfg, int batch_override) {
+    auto secs = parse_cfg(cfg);
+    auto net = std::make_unique<Net>();
+    const Section& n = secs[0];
+    if (n.name != "net" && n.name != "network") throw std::runtime_error("first section must be [net]");
+    net->width = n.usz("width", 0);
+    net->height = n.usz("height", 0);
+    net->channels = n.usz("channels", 0);
+    // model.rs:247-249: batch = batch / subdivisions * time_steps
+    int subdiv = std::max(n.usz("subdivisions", 1), 1);
+    int ts = std::max(n.usz("time_steps", 1), 1);
+    net->batch = n.usz("batch", 1) / subdiv * ts;
+    if (batch_override > 0) net->batch = batch_override;  // model.rs:3256 with_batch
+    Shape cur;
+    cur.w = net->width; cur.h = net->height; cur.c = net->channels; cur.b = net->batch;
+    for (size_t si = 1; si < secs.size(); ++si) {
+        const Section& s = secs[si];
+        int li = (int)net->layers.size();
+        Layer L;
+        L.in = cur;
+        if (s.name == "conv" || s.name == "convolutional") {
+            L.kind = K_CONV;
+            int stride = s.usz("stride", 1);
+            L.size = s.usz("size", 1);
+            bool pad = s.flag("pad", false);
+            L.padding = pad ? L.size / 2 : s.usz("padding", 0);
+            L.filters = s.usz("filters", 1);
+            L.groups = s.usz("groups", 1);
+            L.stride_x = s.usz("stride_x", stride);
+            L.stride_y = s.usz("stride_y", stride);
+            L.dilation = s.usz("dilation", 1);
+            L.bn = s.i64("batch_normalize", 0) != 0;
+            L.act = parse_act(s.str("activation", "logistic"));
+            L.out.w = conv_dim(cur.w, L.padding, L.size, L.stride_x);
+            L.out.h = conv_dim(cur.h, L.padding, L.size, L.stride_y);
+            L.out.c = L.filters;
+            L.out.b = cur.b;
+            int g = std::max(L.groups, 1);
+            if (L.filters % g || cur.c % g) throw std::runtime_error("conv groups do not divide channels");
+            size_t wn = (size_t)L.filters * (cur.c / g) * L.size * L.size;
+            L.biases.assign(L.filters, 0.0f);
+            L.weights.assign(wn, 0.0f);
+            if (L.bn) {
+                L.scales.assign(L.filters, 1.0f);
+                L.mean.assign(L.filters, 0.0f);
+                L.var.assign(L.filters, 1.0f);
+            }
+        } else if (s.name == "max" || s.name == "maxpool") {
+            L.kind = K_MAXPOOL;
+            int stride = s.usz("stride", 1);
+            L.size = s.usz("size", stride);
+            L.stride_x = s.usz("stride_x", stride);
+            L.stride_y = s.usz("stride_y", stride);
+            L.padding = s.usz("padding", L.size > 0 ? L.size - 1 : 0);
+            if (s.flag("maxpool_depth", false)) throw std::runtime_error("maxpool_depth is outside the oracle's scope");
+            L.out.w = pool_dim(cur.w, L.padding, L.size, L.stride_x);
+            L.out.h = pool_dim(cur.h, L.padding, L.size, L.stride_y);
+            L.out.c = cur.c;
+            L.out.b = cur.b;
+        } else if (s.name == "route") {
+            L.kind = K_ROUTE;
+            auto raw = parse_list<long long>(s, "layers");
+            if (raw.empty()) throw std::runtime_error("route must list at least one source layer");
+            L.route_groups = s.usz("groups", 1);
+            L.route_group_id = s.usz("group_id", 0);
+            int ch = 0;
+            Shape first;
+            for (size_t k = 0; k < raw.size(); ++k) {
+                int src = resolve_rel(li, raw[k]);
+                L.sources.push_back(src);
+                const Shape& sh = net->layers[src].out;
+                if (k == 0) first = sh;
+                else if (sh.w != first.w || sh.h != first.h) throw std::runtime_error("route mixes incompatible spatial shapes");
+                ch += sh.c;
+            }
+            // model.rs:6138 infer_route_shape
+            L.out.w = first.w; L.out.h = first.h; L.out.c = ch / std::max(L.route_groups, 1); L.out.b = cur.b;
+        } else if (s.name == "shortcut") {
+            L.kind = K_SHORTCUT;
+            auto raw = parse_list<long long>(s, "from");
+            for (auto r : raw) L.sources.push_back(resolve_rel(li, r));
+            L.act = parse_act(s.str("activation", "linear"));
+            L.out = cur;
+        } else if (s.name == "upsample") {
+            L.kind = K_UPSAMPLE;
+            long long st = s.i64("stride", 2);
+            L.up_reverse = st < 0;
+            L.up_stride = (int)std::llabs(st);
+            if (L.up_stride == 0) throw std::runtime_error("upsample cannot use stride=0");
+            L.up_scale = s.f32("scale", 1.0f);
+            L.out = cur;
+            if (L.up_reverse) { L.out.w = cur.w / L.up_stride; L.out.h = cur.h / L.up_stride; }
+            else { L.out.w = cur.w * L.up_stride; L.out.h = cur.h * L.up_stride; }
+        } else if (s.name == "yolo") {
+            L.kind = K_YOLO;
+            L.mask = parse_list<int>(s, "mask");
+            L.num = s.usz("num", L.mask.empty() ? 1 : (int)L.mask.size());
+            if (L.mask.empty()) for (int k = 0; k < L.num; ++k) L.mask.push_back(k);
+            L.classes = s.usz("classes", 20);
+            L.anchors = parse_list<float>(s, "anchors");
+            L.scale_x_y = s.f32("scale_x_y", 1.0f);
+            L.new_coords = s.i64("new_coords", 0) != 0;
+            L.out = cur;
+        } else {
+            throw std::runtime_error("layer [" + s.name + "] is outside the oracle's scope");
+        }
+        cur = L.out;
+        net->layers.push_back(std::move(L));
+    }
+    return net;
+}
+
+// ---------------------------------------------------------------------------
+// f32 layer math
+// ---------------------------------------------------------------------------
+
+static const float BN_EPS = 1e-5f;  // lightnet-layers/src/params.rs:4
+
+// runtime/layer_ops.rs:1682-1695 normalize_value
+static inline float normalize_value(float v, int idx, const Layer& L) {
+    if (L.bn) {
+        float normalized = (v - L.mean[idx]) / std::sqrt(L.var[idx] + BN_EPS);
+        return normalized * L.scales[idx] + L.biases[idx];
+    }
+    return v + L.biases[idx];
+}
+
+// runtime/layer_ops.rs:1697-1738 activate (libm f32)
+static inline float activate(Act a, float v) {
+    switch (a) {
+        case ACT_LINEAR: return v;
+        case ACT_LOGISTIC: return 1.0f / (1.0f + std::exp(-v));
+        case ACT_RELU: return std::max(v, 0.0f);
+        case ACT_LEAKY: return v > 0.0f ? v : 0.1f * v;
+        case ACT_MISH: return v * std::tanh(std::log(1.0f + std::exp(v)));
+        case ACT_SWISH: return v / (1.0f + std::exp(-v));
+    }
+    return v;
+}
+
+// runtime/forward_layers.rs:610-699 forward_convolutional_with_cache.
+// `folded` = use BN-folded weights/bias (runtime/weights_io.rs:32-92) instead of
+// the unfolded normalize_value; the GPU path of the reference folds, the CPU path
+// does not.
+static void conv_f32(const Layer& L, const Tensor& x, Tensor& y, bool folded, const std::vector<float>* fw,
+                     const std::vector<float>* fb) {
+    const int g = std::max(L.groups, 1);
+    const int fpg = L.filters / g, cpg = x.s.c / g;
+    const float* W = folded ? fw->data() : L.weights.data();
+#pragma omp parallel for collapse(2) schedule(dynamic)
+    for (int b = 0; b < x.s.b; ++b) {
+        for (int f = 0; f < L.filters; ++f) {
+            const int group = f / std::max(fpg, 1);
+            for (int oy = 0; oy < y.s.h; ++oy) {
+                for (int ox = 0; ox < y.s.w; ++ox) {
+                    float acc = 0.0f;
+                    for (int ic = 0; ic < cpg; ++ic) {
+                        for (int ky = 0; ky < L.size; ++ky) {
+                            for (int kx = 0; kx < L.size; ++kx) {
+                                int sy = oy * L.stride_y + ky * L.dilation - L.padding;
+                                int sx = ox * L.stride_x + kx * L.dilation - L.padding;
+                                if (sy < 0 || sy >= x.s.h || sx < 0 || sx >= x.s.w) continue;
+                                int ch = group * cpg + ic;
+                                float iv = x.d[x.off(b, ch, sy, sx)];
+                                size_t wi = (((size_t)f * cpg + ic) * L.size + ky) * L.size + kx;
+                                acc += iv * W[wi];
+                            }
+                        }
+                    }
+                    float biased = folded ? acc + (*fb)[f] : normalize_value(acc, f, L);
+                    y.d[y.off(b, f, oy, ox)] = activate(L.act, biased);
+                }
+            }
+        }
+    }
+}
+
+// runtime/weights_io.rs:32-92 fold_convolutional_params_for_inference
+static void fold_bn(const Layer& L, int in_c, std::vector<float>& fw, std::vector<float>& fb) {
+    fw = L.weights;
+    fb = L.biases;
+    if (!L.bn) return;
+    const int g = std::max(L.groups, 1);
+    size_t per = (size_t)(in_c / g) * L.size * L.size;
+    for (int f = 0; f < L.filters; ++f) {
+        float scale = L.scales[f] / std::sqrt(L.var[f] + BN_EPS);
+        fb[f] -= L.mean[f] * scale;
+        for (size_t k = 0; k < per; ++k) fw[f * per + k] *= scale;
+    }
+}
+
+// runtime/layer_ops.rs:1740-1799 forward_maxpool (average=false)
+static void maxpool_f32(const Layer& L, const Tensor& x, Tensor& y) {
+#pragma omp parallel for collapse(2)
+    for (int b = 0; b < x.s.b; ++b)
+        for (int c = 0; c < x.s.c; ++c)
+            for (int oy = 0; oy < y.s.h; ++oy)
+                for (int ox = 0; ox < y.s.w; ++ox) {
+                    float acc = -std::numeric_limits<float>::infinity();
+                    for (int ky = 0; ky < L.size; ++ky)
+                        for (int kx = 0; kx < L.size; ++kx) {
+                            int sy = oy * L.stride_y + ky - L.padding / 2;
+                            int sx = ox * L.stride_x + kx - L.padding / 2;
+                            if (sy < 0 || sy >= x.s.h || sx < 0 || sx >= x.s.w) continue;
+                            acc = std::max(acc, x.d[x.off(b, c, sy, sx)]);
+                        }
+                    y.d[y.off(b, c, oy, ox)] = acc;
+                }
+}
+
+// runtime/layer_ops.rs:1850-1883 forward_route
+template <class T>
+static void route_any(const Layer& L, const std::vector<T>& outs, T& y) {
+    int oc = 0;
+    for (int src : L.sources) {
+        const T& s = outs[src];
+        int chunk = s.s.c / std::max(L.route_groups, 1);
+        int start = chunk * L.route_group_id;
+        for (int b = 0; b < s.s.b; ++b)
+            for (int c = 0; c < chunk; ++c)
+                for (int yy = 0; yy < s.s.h; ++yy)
+                    for (int xx = 0; xx < s.s.w; ++xx)
+                        y.d[y.off(b, oc + c, yy, xx)] = s.d[s.off(b, start + c, yy, xx)];
+        oc += chunk;
+    }
+}
+
+// runtime/layer_ops.rs:2110-2145 forward_shortcut_with_cache: flat per-sample add of
+// min(len) elements, activation after the last add.
+static void shortcut_f32(const Layer& L, const Tensor& in, const std::vector<Tensor>& outs, Tensor& y) {
+    y.d = in.d;
+    for (int src : L.sources) {
+        const Tensor& s = outs[src];
+        if (s.s.b != y.s.b) throw std::runtime_error("shortcut mixes incompatible batch shapes");
+        size_t os = y.s.count() / y.s.b, ss = s.s.count() / s.s.b, n = std::min(os, ss);
+        for (int b = 0; b < y.s.b; ++b)
+            for (size_t i = 0; i < n; ++i) y.d[b * os + i] += s.d[b * ss + i];
+    }
+    for (auto& v : y.d) v = activate(L.act, v);
+}
+
+// runtime/layer_ops.rs:2208-2256 forward_upsample
+static void upsample_f32(const Layer& L, const Tensor& x, Tensor& y) {
+    int st = L.up_stride;
+    if (L.up_reverse) {
+        std::fill(y.d.begin(), y.d.end(), 0.0f);
+        int ch = y.s.h * st, cw = y.s.w * st;
+        for (int b = 0; b < y.s.b; ++b)
+            for (int c = 0; c < y.s.c; ++c)
+                for (int yy = 0; yy < ch; ++yy)
+                    for (int xx = 0; xx < cw; ++xx) y.d[y.off(b, c, yy / st, xx / st)] += L.up_scale * x.d[x.off(b, c, yy, xx)];
+    } else {
+        for (int b = 0; b < x.s.b; ++b)
+            for (int c = 0; c < x.s.c; ++c)
+                for (int yy = 0; yy < y.s.h; ++yy)
+                    for (int xx = 0; xx < y.s.w; ++xx) y.d[y.off(b, c, yy, xx)] = L.up_scale * x.d[x.off(b, c, yy / st, xx / st)];
+    }
+}
+
+static float amax_of(const std::vector<float>& v) {
+    float m = 0.0f;
+    for (float x : v) if (std::isfinite(x)) m = std::max(m, std::fabs(x));
+    return m;
+}
+
+// runtime/exec_forward.rs:223-1100 layer walk (forward), f32.
+// mode 0: faithful CPU path (unfolded BN); mode 1: BN folded first, like the GPU
+// executor (runtime/gpu_params.rs:559-687).
+static void forward_f32(Net& net, const float* input, int mode) {
+    Shape is; is.w = net.width; is.h = net.height; is.c = net.channels; is.b = net.batch;
+    Tensor cur(is);
+    std::memcpy(cur.d.data(), input, cur.d.size() * sizeof(float));
+    net.out_f32.assign(net.layers.size(), Tensor());
+    net.amax.assign(net.layers.size() + 1, 0.0f);
+    net.amax[0] = amax_of(cur.d);
+    for (size_t i = 0; i < net.layers.size(); ++i) {
+        Layer& L = net.layers[i];
+        const Tensor& x = i == 0 ? cur : net.out_f32[i - 1];
+        Tensor y(L.out);
+        switch (L.kind) {
+            case K_CONV: {
+                if (mode == 1) {
+                    std::vector<float> fw, fb;
+                    fold_bn(L, x.s.c, fw, fb);
+                    conv_f32(L, x, y, true, &fw, &fb);
+                } else conv_f32(L, x, y, false, nullptr, nullptr);
+                break;
+            }
+            case K_MAXPOOL: maxpool_f32(L, x, y); break;
+            case K_ROUTE: route_any(L, net.out_f32, y); break;
+            case K_SHORTCUT: shortcut_f32(L, x, net.out_f32, y); break;
+            case K_UPSAMPLE: upsample_f32(L, x, y); break;
+            case K_YOLO: y.d = x.d; break;  // exec_forward.rs:908-912 pass-through
+        }
+        net.amax[i + 1] = amax_of(y.d);
+        net.out_f32[i] = std::move(y);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Deterministic transcendental: the int8/FP8 epilogues and the device decode use
+// this exp instead of libm so that CPU and GPU agree bit for bit.  Every
+// operation is a single IEEE-754 binary32 operation (fma where written), so any
+// conforming implementation gives the same bits.  Accuracy: a few ulp of expf.
+// ---------------------------------------------------------------------------
+
+static inline float det_expf(float x) {
+    x = std::fmin(std::fmax(x, -87.0f), 88.0f);
+    const float LOG2E = 1.44269502e+00f;
+    const float LN2_HI = 6.93145752e-01f;   // upper bits of ln 2
+    const float LN2_LO = 1.42860677e-06f;   // ln 2 - LN2_HI
+    float n = std::nearbyint(x * LOG2E);
+    float r = std::fma(n, -LN2_HI, x);
+    r = std::fma(n, -LN2_LO, r);
+    float p = 1.98412698e-04f;               // 1/5040
+    p = std::fma(p, r, 1.38888889e-03f);     // 1/720
+    p = std::fma(p, r, 8.33333377e-03f);     // 1/120
+    p = std::fma(p, r, 4.16666679e-02f);     // 1/24
+    p = std::fma(p, r, 1.66666672e-01f);     // 1/6
+    p = std::fma(p, r, 5.00000000e-01f);
+    p = std::fma(p, r, 1.0f);
+    p = std::fma(p, r, 1.0f);
+    int32_t e = (int32_t)n;
+    // 2^e as two factors so that e in [-126,127] never leaves the normal range.
+    int32_t e1 = e / 2, e2 = e - e1;
+    uint32_t b1 = (uint32_t)(e1 + 127) << 23, b2 = (uint32_t)(e2 + 127) << 23;
+    float s1, s2;
+    std::memcpy(&s1, &b1, 4);
+    std::memcpy(&s2, &b2, 4);
+    return p * s1 * s2;
+}
+
+static inline float det_sigmoid(float v) { return 1.0f / (1.0f + det_expf(-v)); }
+
+// Activation of the quantised epilogue: same formulas as layer_ops.rs:1697-1738
+// with exp replaced by det_expf and mish's tanh(ln(1+e^v)) rewritten as the
+// algebraically equal w/(w+2), w = e^v(e^v+2).
+static inline float det_activate(Act a, float v) {
+    switch (a) {
+        case ACT_LINEAR: return v;
+        case ACT_LOGISTIC: return det_sigmoid(v);
+        case ACT_RELU: return v > 0.0f ? v : 0.0f;
+        case ACT_LEAKY: return v > 0.0f ? v : 0.1f * v;
+        case ACT_MISH: {
+            if (v > 20.0f) return v;
+            float e = det_expf(v);
+            float w = e * (e + 2.0f);
+            return v * (w / (w + 2.0f));
+        }
+        case ACT_SWISH: return v / (1.0f + det_expf(-v));
+    }
+    return v;
+}
+
+// ---------------------------------------------------------------------------
+// int8 model (defined by this build; the reference has none)
+//   weights : per-output-channel symmetric, s_k = max|w_k|/127, q = rne(w/s_k) clamp +-127
+//   tensors : per-tensor symmetric scale s = amax/127 from an f32 calibration run;
+//             tensors joined by route / maxpool / upsample share one scale
+//   conv    : acc = sum(xq*wq) int32;  v = fma(float(acc), s_x*s_k, b_k);  a = det_act(v)
+//             int8 out: q = clamp(rne(a * (1/s_y)), +-127);  head conv (feeds [yolo]): a kept f32
+// ---------------------------------------------------------------------------
+
+static inline int8_t quant_i8(float a, float inv_s) {
+    float r = std::nearbyint(a * inv_s);
+    if (!(r >= -127.0f)) r = -127.0f;  // also maps NaN to -127
+    if (r > 127.0f) r = 127.0f;
+    return (int8_t)(int)r;
+}
+
+static void quantize_weights(Net& net) {
+    for (size_t i = 0; i < net.layers.size(); ++i) {
+        Layer& L = net.layers[i];
+        if (L.kind != K_CONV) continue;
+        std::vector<float> fw;
+        fold_bn(L, L.in.c, fw, L.fbias);
+        size_t per = fw.size() / L.filters;
+        L.wq.assign(fw.size(), 0);
+        L.wscale.assign(L.filters, 1.0f);
+        for (int f = 0; f < L.filters; ++f) {
+            float m = 0.0f;
+            for (size_t k = 0; k < per; ++k) m = std::max(m, std::fabs(fw[f * per + k]));
+            float s = (m > 0.0f && std::isfinite(m)) ? m / 127.0f : 1.0f;
+            L.wscale[f] = s;
+            for (size_t k = 0; k < per; ++k) L.wq[f * per + k] = quant_i8(fw[f * per + k] / s, 1.0f);
+        }
+    }
+}
+
+struct UF {
+    std::vector<int> p;
+    explicit UF(int n) : p(n) { std::iota(p.begin(), p.end(), 0); }
+    int find(int a) { while (p[a] != a) a = p[a] = p[p[a]]; return a; }
+    void join(int a, int b) { a = find(a); b = find(b); if (a != b) p[std::max(a, b)] = std::min(a, b); }
+};
+
+// Scale groups: tensor index t = 0 is the network input, t = 1+i the output of layer i.
+static void calibrate(Net& net) {
+    int T = (int)net.layers.size() + 1;
+    UF uf(T);
+    for (int i = 0; i < (int)net.layers.size(); ++i) {
+        const Layer& L = net.layers[i];
+        if (L.kind == K_MAXPOOL || L.kind == K_UPSAMPLE || L.kind == K_YOLO) uf.join(i + 1, i);
+        if (L.kind == K_ROUTE) for (int s : L.sources) uf.join(i + 1, s + 1);
+    }
+    std::vector<float> gmax(T, 0.0f);
+    for (int t = 0; t < T; ++t) { int r = uf.find(t); gmax[r] = std::max(gmax[r], net.amax[t]); }
+    net.scale.assign(T, 1.0f);
+    for (int t = 0; t < T; ++t) {
+        float m = gmax[uf.find(t)];
+        net.scale[t] = (m > 0.0f && std::isfinite(m)) ? m / 127.0f : 1.0f;
+    }
+}
+
+static bool feeds_head(const Net& net, int i) {
+    // runtime/types.rs:146-170 conv_feeds_detection_head
+    return net.layers[i].kind == K_CONV && i + 1 < (int)net.layers.size() && net.layers[i + 1].kind == K_YOLO;
+}
+
+// int32 accumulators of one int8 conv; NCHW in, NCHW out.  Integer arithmetic is
+// order independent, so any loop order is exact.
+static void conv_q8_acc(const int8_t* x, int B, int C, int H, int W, const int8_t* wq, int F, int k, int sx, int sy,
+                        int pad, int OH, int OW, int32_t* acc) {
+#pragma omp parallel for collapse(2) schedule(dynamic)
+    for (int b = 0; b < B; ++b)
+        for (int f = 0; f < F; ++f) {
+            int32_t* out = acc + ((size_t)b * F + f) * OH * OW;
+            std::fill(out, out + (size_t)OH * OW, 0);
+            for (int ic = 0; ic < C; ++ic) {
+                const int8_t* xp = x + ((size_t)b * C + ic) * H * W;
+                for (int ky = 0; ky < k; ++ky)
+                    for (int kx = 0; kx < k; ++kx) {
+                        int32_t wv = wq[(((size_t)f * C + ic) * k + ky) * k + kx];
+                        if (wv == 0) continue;
+                        for (int oy = 0; oy < OH; ++oy) {
+                            int yy = oy * sy + ky - pad;
+                            if (yy < 0 || yy >= H) continue;
+                            const int8_t* row = xp + (size_t)yy * W;
+                            int32_t* orow = out + (size_t)oy * OW;
+                            for (int ox = 0; ox < OW; ++ox) {
+                                int xx = ox * sx + kx - pad;
+                                if (xx < 0 || xx >= W) continue;
+                                orow[ox] += wv * (int32_t)row[xx];
+                            }
+                        }
+                    }
+            }
+        }
+}
+
+static void forward_q8(Net& net, const float* input) {
+    const int NL = (int)net.layers.size();
+    net.out_q8.assign(NL, TensorI8());
+    net.head_q8.assign(NL, Tensor());
+    Shape is; is.w = net.width; is.h = net.height; is.c = net.channels; is.b = net.batch;
+    TensorI8 xin(is);
+    {
+        float inv = 1.0f / net.scale[0];
+        for (size_t i = 0; i < xin.d.size(); ++i) xin.d[i] = quant_i8(input[i], inv);
+    }
+    for (int i = 0; i < NL; ++i) {
+        Layer& L = net.layers[i];
+        const TensorI8& x = i == 0 ? xin : net.out_q8[i - 1];
+        const float sx = net.scale[i], sy = net.scale[i + 1];  // scale[i] = scale of layer i-1's output
+        TensorI8 y(L.out);
+        switch (L.kind) {
+            case K_CONV: {
+                if (L.groups != 1 || L.dilation != 1) throw std::runtime_error("int8 conv supports groups=1 dilation=1");
+                std::vector<int32_t> acc(L.out.count());
+                conv_q8_acc(x.d.data(), x.s.b, x.s.c, x.s.h, x.s.w, L.wq.data(), L.filters, L.size, L.stride_x, L.stride_y,
+                            L.padding, L.out.h, L.out.w, acc.data());
+                bool head = feeds_head(net, i);
+                if (head) net.head_q8[i] = Tensor(L.out);
+                float inv = 1.0f / sy;
+                size_t plane = (size_t)L.out.h * L.out.w;
+                for (int b = 0; b < L.out.b; ++b)
+                    for (int f = 0; f < L.filters; ++f) {
+                        float m = sx * L.wscale[f];
+                        float bias = L.fbias[f];
+                        size_t base = ((size_t)b * L.filters + f) * plane;
+                        for (size_t p = 0; p < plane; ++p) {
+                            float v = std::fma((float)acc[base + p], m, bias);
+                            float a = det_activate(L.act, v);
+                            if (head) net.head_q8[i].d[base + p] = a;
+                            else y.d[base + p] = quant_i8(a, inv);
+                        }
+                    }
+                break;
+            }
+            case K_MAXPOOL: {
+                for (int b = 0; b < x.s.b; ++b)
+                    for (int c = 0; c < x.s.c; ++c)
+                        for (int oy = 0; oy < y.s.h; ++oy)
+                            for (int ox = 0; ox < y.s.w; ++ox) {
+                                int m = -127;
+                                for (int ky = 0; ky < L.size; ++ky)
+                                    for (int kx = 0; kx < L.size; ++kx) {
+                                        int yy = oy * L.stride_y + ky - L.padding / 2;
+                                        int xx = ox * L.stride_x + kx - L.padding / 2;
+                                        if (yy < 0 || yy >= x.s.h || xx < 0 || xx >= x.s.w) continue;
+                                        m = std::max(m, (int)x.d[x.off(b, c, yy, xx)]);
+                                    }
+                                y.d[y.off(b, c, oy, ox)] = (int8_t)m;
+                            }
+                break;
+            }
+            case K_ROUTE: route_any(L, net.out_q8, y); break;
+            case K_SHORTCUT: {
+                float inv = 1.0f / sy;
+                for (int src : L.sources)
+                    if (net.out_q8[src].s.count() != y.s.count()) throw std::runtime_error("int8 shortcut needs same-shape sources");
+                for (size_t p = 0; p < y.d.size(); ++p) {
+                    float v = (float)x.d[p] * sx;
+                    for (int src : L.sources) v = std::fma((float)net.out_q8[src].d[p], net.scale[src + 1], v);
+                    y.d[p] = quant_i8(det_activate(L.act, v), inv);
+                }
+                break;
+            }
+            case K_UPSAMPLE: {
+                if (L.up_reverse || L.up_scale != 1.0f) throw std::runtime_error("int8 upsample supports scale=1, forward only");
+                for (int b = 0; b < y.s.b; ++b)
+                    for (int c = 0; c < y.s.c; ++c)
+                        for (int yy = 0; yy < y.s.h; ++yy)
+                            for (int xx = 0; xx < y.s.w; ++xx)
+                                y.d[y.off(b, c, yy, xx)] = x.d[x.off(b, c, yy / L.up_stride, xx / L.up_stride)];
+                break;
+            }
+            case K_YOLO: {
+                if (i == 0 || !feeds_head(net, i - 1)) throw std::runtime_error("int8 [yolo] must follow a convolution");
+                net.head_q8[i] = net.head_q8[i - 1];
+                break;
+            }
+        }
+        net.out_q8[i] = std::move(y);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Decode + NMS
+// ---------------------------------------------------------------------------
+
+struct Det {
+    int class_id;
+    float conf, obj, x, y, w, h;
+};
+
+// lightnet-model/src/detection_geometry.rs:80-102 (sigmoid/head_activation)
+static inline float head_act(float raw, bool new_coords, bool det) {
+    if (new_coords) return raw;
+    return det ? det_sigmoid(raw) : 1.0f / (1.0f + std::exp(-raw));
+}
+
+struct HeadSpec {
+    int gw, gh, classes, n_anchor;
+    const float* anchors_wh;  // n_anchor pairs, already selected through mask
+    float scale_x_y;
+    int new_coords;
+};
+
+// lightnet-train/src/detect.rs:934-1016 decode_yolo_head, :1288-1322 decode_bbox,
+// :1414-1447 correct_bbox.  `data` is one image's head, channel-major
+// [anchor*(5+classes)+entry][gh*gw].  det_exp selects det_expf instead of libm.
+static void decode_head(const float* data, const HeadSpec& hs, int net_w, int net_h, int img_w, int img_h, float thr,
+                        bool letterbox, bool det_exp, std::vector<Det>& out) {
+    const int stride = hs.gw * hs.gh, epa = hs.classes + 5;
+    const bool nc = hs.new_coords != 0;
+    const float iw = (float)img_w, ih = (float)img_h, nw = (float)net_w, nh = (float)net_h;
+    float new_w, new_h;
+    if (letterbox) {
+        if (nw / iw < nh / ih) { new_w = nw; new_h = ih * nw / iw; }
+        else { new_w = iw * nh / ih; new_h = nh; }
+    } else { new_w = nw; new_h = nh; }
+    const float delta_w = nw - new_w, delta_h = nh - new_h, ratio_w = new_w / nw, ratio_h = new_h / nh;
+    for (int a = 0; a < hs.n_anchor; ++a) {
+        const float aw = hs.anchors_wh[2 * a], ah = hs.anchors_wh[2 * a + 1];
+        const int ab = a * epa;
+        for (int idx = 0; idx < stride; ++idx) {
+            const int row = idx / hs.gw, col = idx % hs.gw;
+            float tx = data[(size_t)(ab + 0) * stride + idx];
+            float ty = data[(size_t)(ab + 1) * stride + idx];
+            float tw = data[(size_t)(ab + 2) * stride + idx];
+            float th = data[(size_t)(ab + 3) * stride + idx];
+            float obj = head_act(data[(size_t)(ab + 4) * stride + idx], nc, det_exp);
+            if (obj <= thr) continue;
+            float bx = ((float)col + hs.scale_x_y * head_act(tx, nc, det_exp) - 0.5f * (hs.scale_x_y - 1.0f)) / (float)hs.gw;
+            float by = ((float)row + hs.scale_x_y * head_act(ty, nc, det_exp) - 0.5f * (hs.scale_x_y - 1.0f)) / (float)hs.gh;
+            float bw, bh;
+            if (nc) { bw = tw * tw * 4.0f * aw / nw; bh = th * th * 4.0f * ah / nh; }
+            else {
+                bw = (det_exp ? det_expf(tw) : std::exp(tw)) * aw / nw;
+                bh = (det_exp ? det_expf(th) : std::exp(th)) * ah / nh;
+            }
+            bx = (bx - delta_w / 2.0f / nw) / ratio_w;
+            by = (by - delta_h / 2.0f / nh) / ratio_h;
+            bw /= ratio_w;
+            bh /= ratio_h;
+            bx *= iw; by *= ih; bw *= iw; bh *= ih;
+            for (int c = 0; c < hs.classes; ++c) {
+                float p = head_act(data[(size_t)(ab + 5 + c) * stride + idx], nc, det_exp);
+                float conf = obj * p;
+                if (conf > thr) out.push_back(Det{c, conf, obj, bx, by, bw, bh});
+            }
+        }
+    }
+}
+
+// lightnet-train/src/detect.rs:1486-1503 bbox_iou; detection_geometry.rs:14-30 edges
+static inline float bbox_iou(const Det& a, const Det& b) {
+    float al = a.x - a.w * 0.5f, at = a.y - a.h * 0.5f, ar = a.x + a.w * 0.5f, ab = a.y + a.h * 0.5f;
+    float bl = b.x - b.w * 0.5f, bt = b.y - b.h * 0.5f, br = b.x + b.w * 0.5f, bb = b.y + b.h * 0.5f;
+    float il = std::max(al, bl), it = std::max(at, bt), ir = std::min(ar, br), ib = std::min(ab, bb);
+    float iw = std::max(ir - il, 0.0f), ih = std::max(ib - it, 0.0f);
+    float inter = iw * ih;
+    if (inter <= 0.0f) return 0.0f;
+    float aa = std::max(a.w, 0.0f) * std::max(a.h, 0.0f), ba = std::max(b.w, 0.0f) * std::max(b.h, 0.0f);
+    return inter / (aa + ba - inter);
+}
+
+// lightnet-train/src/detect.rs:1449-1484 apply_nms.  The survivor compaction there
+// swaps survivors forward, which keeps survivors in their original relative order.
+static void apply_nms(std::vector<Det>& d, float thr) {
+    if (thr <= 0.0f) return;
+    const size_t n = d.size();
+    std::vector<char> sup(n, 0);
+    for (size_t i = 0; i < n; ++i) {
+        if (sup[i]) continue;
+        for (size_t j = i + 1; j < n; ++j) {
+            if (sup[j] || d[i].class_id != d[j].class_id) continue;
+            size_t keep, drop;
+            if (d[i].conf >= d[j].conf) { keep = i; drop = j; } else { keep = j; drop = i; }
+            if (bbox_iou(d[keep], d[drop]) > thr) sup[drop] = 1;
+        }
+    }
+    size_t k = 0;
+    for (size_t i = 0; i < n; ++i) if (!sup[i]) { if (k != i) d[k] = d[i]; ++k; }
+    d.resize(k);
+}
+
+// f32::total_cmp descending, stable (detect.rs:107, :242)
+static void sort_conf_desc(std::vector<Det>& d) {
+    auto key = [](float f) { int32_t b; std::memcpy(&b, &f, 4); return b < 0 ? (int32_t)(b ^ 0x7fffffff) : b; };
+    std::stable_sort(d.begin(), d.end(), [&](const Det& a, const Det& b) { return key(a.conf) > key(b.conf); });
+}
+
+// lightnet-train/src/detect.rs:113-244 decode_network_detections for one image:
+// all heads decoded (emission order head, anchor, cell, class); apply_nms(1.0) on the
+// unsorted list; stable sort; apply_nms(nms_thr); stable sort.  `skip_pass1` drops the
+// thr=1.0 pass (used by tests to show it is a no-op on a given input).  top_k > 0
+// truncates the final list (an extension; the reference has no top-k).
+static std::vector<Det> detect_image(const std::vector<const float*>& heads, const std::vector<HeadSpec>& specs, int net_w,
+                                     int net_h, int img_w, int img_h, float thr, float nms_thr, bool letterbox, int top_k,
+                                     bool det_exp, bool skip_pass1) {
+    std::vector<Det> d;
+    for (size_t h = 0; h < heads.size(); ++h) decode_head(heads[h], specs[h], net_w, net_h, img_w, img_h, thr, letterbox, det_exp, d);
+    if (!skip_pass1) apply_nms(d, 1.0f);
+    sort_conf_desc(d);
+    apply_nms(d, nms_thr);
+    sort_conf_desc(d);
+    if (top_k > 0 && (int)d.size() > top_k) d.resize(top_k);
+    return d;
+}
+
+// ---------------------------------------------------------------------------
+// FP8 E4M3 codec: lightnet-cuda-oxide/src/fp8.rs:153-181 (RNE, satfinite 448,
+// NaN -> 0x7F), decode :140-150.
+// ---------------------------------------------------------------------------
+
+static float e4m3_decode_mag(uint8_t m) {
+    int e = (m >> 3) & 0xF, f = m & 7;
+    if (e == 0) return std::ldexp((float)f, -9);
+    return std::ldexp(1.0f + (float)f / 8.0f, e - 7);
+}
+static float e4m3_to_f32(uint8_t bits) {
+    uint8_t m = bits & 0x7F;
+    if (m == 0x7F) return std::numeric_limits<float>::quiet_NaN();
+    float v = e4m3_decode_mag(m);
+    return (bits & 0x80) ? -v : v;
+}
+static uint8_t f32_to_e4m3(float v) {
+    if (std::isnan(v)) return 0x7F;
+    uint8_t sign = std::signbit(v) ? 0x80 : 0;
+    float mag = std::fabs(v);
+    const uint8_t maxc = 0x7E;
+    if (mag > e4m3_decode_mag(maxc)) return sign | maxc;
+    uint8_t best = 0;
+    float bd = std::numeric_limits<float>::infinity();
+    for (int c = 0; c <= maxc; ++c) {
+        float dist = std::fabs(mag - e4m3_decode_mag((uint8_t)c));
+        if (dist < bd || (dist == bd && (c & 1) == 0)) { best = (uint8_t)c; bd = dist; }
+    }
+    return sign | best;
+}
+
+}  // namespace orc
+
+// ---------------------------------------------------------------------------
+// C API (ctypes)
+// ---------------------------------------------------------------------------
+
+using namespace orc;
+
+static thread_local std::string g_err;
+
+#define ORC_TRY try {
+#define ORC_CATCH(ret) } catch (const std::exception& e) { g_err = e.what(); return ret; }
+
+extern "C" {
+
+const char* orc_last_error() { return g_err.c_str(); }
+
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+int orc_max_threads() {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+void* orc_net_create(const char* cfg_text, int batch) {
+    ORC_TRY
+    return build_net(cfg_text, batch).release();
+    ORC_CATCH(nullptr)
+}
+void orc_net_destroy(void* h) { delete (Net*)h; }
+int orc_net_num_layers(void* h) { return (int)((Net*)h)->layers.size(); }
+
+// info[16]: kind, in(w,h,c,b), out(w,h,c,b), filters,size,stride_x,stride_y,padding,bn,act
+int orc_net_layer_info(void* h, int i, int* info) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->layers.size()) return -1;
+    const Layer& L = n->layers[i];
+    int v[16] = {L.kind, L.in.w, L.in.h, L.in.c, L.in.b, L.out.w, L.out.h, L.out.c, L.out.b,
+                 L.filters, L.size, L.stride_x, L.stride_y, L.padding, L.bn ? 1 : 0, (int)L.act};
+    std::memcpy(info, v, sizeof v);
+    return 0;
+}
+void orc_net_dims(void* h, int* whcb) {
+    Net* n = (Net*)h;
+    whcb[0] = n->width; whcb[1] = n->height; whcb[2] = n->channels; whcb[3] = n->batch;
+}
+
+// Darknet .weights payload order (runtime/weights_io.rs:227-235): per conv biases,
+// [scales, rolling_mean, rolling_variance], weights.
+long long orc_net_weight_count(void* h) {
+    long long c = 0;
+    for (auto& L : ((Net*)h)->layers)
+        if (L.kind == K_CONV) c += (long long)L.biases.size() * (L.bn ? 4 : 1) + (long long)L.weights.size();
+    return c;
+}
+int orc_net_set_weights(void* h, const float* w, long long count) {
+    ORC_TRY
+    Net* n = (Net*)h;
+    if (count != orc_net_weight_count(h)) throw std::runtime_error("weight count mismatch");
+    for (auto& L : n->layers) {
+        if (L.kind != K_CONV) continue;
+        auto take = [&](std::vector<float>& v) { std::memcpy(v.data(), w, v.size() * 4); w += v.size(); };
+        take(L.biases);
+        if (L.bn) { take(L.scales); take(L.mean); take(L.var); }
+        take(L.weights);
+    }
+    quantize_weights(*n);
+    return 0;
+    ORC_CATCH(-1)
+}
+
+int orc_net_forward_f32(void* h, const float* input, int mode) {
+    ORC_TRY
+    forward_f32(*(Net*)h, input, mode);
+    return 0;
+    ORC_CATCH(-1)
+}
+int orc_net_layer_output_f32(void* h, int i, float* out) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->out_f32.size()) return -1;
+    std::memcpy(out, n->out_f32[i].d.data(), n->out_f32[i].d.size() * 4);
+    return 0;
+}
+int orc_net_calibrate(void* h) {
+    ORC_TRY
+    Net* n = (Net*)h;
+    if (n->amax.size() != n->layers.size() + 1) throw std::runtime_error("run forward_f32 before calibrate");
+    calibrate(*n);
+    return 0;
+    ORC_CATCH(-1)
+}
+// amax / scale arrays have num_layers+1 entries: [0] input, [1+i] layer i output.
+int orc_net_get_amax(void* h, float* out) {
+    Net* n = (Net*)h;
+    std::memcpy(out, n->amax.data(), n->amax.size() * 4);
+    return (int)n->amax.size();
+}
+int orc_net_get_scales(void* h, float* out) {
+    Net* n = (Net*)h;
+    std::memcpy(out, n->scale.data(), n->scale.size() * 4);
+    return (int)n->scale.size();
+}
+int orc_net_set_scales(void* h, const float* s, int count) {
+    Net* n = (Net*)h;
+    if (count != (int)n->layers.size() + 1) return -1;
+    n->scale.assign(s, s + count);
+    return 0;
+}
+int orc_net_forward_q8(void* h, const float* input) {
+    ORC_TRY
+    Net* n = (Net*)h;
+    if (n->scale.size() != n->layers.size() + 1) throw std::runtime_error("scales are not set");
+    forward_q8(*n, input);
+    return 0;
+    ORC_CATCH(-1)
+}
+int orc_net_layer_output_q8(void* h, int i, int8_t* out) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->out_q8.size()) return -1;
+    std::memcpy(out, n->out_q8[i].d.data(), n->out_q8[i].d.size());
+    return 0;
+}
+// f32 head of the int8 run; i = the [yolo] layer index (or its conv).
+int orc_net_head_q8(void* h, int i, float* out) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->head_q8.size() || n->head_q8[i].d.empty()) return -1;
+    std::memcpy(out, n->head_q8[i].d.data(), n->head_q8[i].d.size() * 4);
+    return 0;
+}
+// Per-filter weight scale and quantised weights of conv layer i.
+int orc_net_conv_quant(void* h, int i, int8_t* wq, float* wscale, float* fbias) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->layers.size() || n->layers[i].kind != K_CONV) return -1;
+    const Layer& L = n->layers[i];
+    if (wq) std::memcpy(wq, L.wq.data(), L.wq.size());
+    if (wscale) std::memcpy(wscale, L.wscale.data(), L.wscale.size() * 4);
+    if (fbias) std::memcpy(fbias, L.fbias.data(), L.fbias.size() * 4);
+    return 0;
+}
+
+// Detections of image `b` from the last run (source 0 = f32 run, 1 = int8 run).
+// out: records of 7 floats {class, conf, obj, x, y, w, h}; returns the count (may
+// exceed max_out; only max_out are written) or -1.
+int orc_net_detect(void* h, int source, int b, int img_w, int img_h, float thr, float nms_thr, int letterbox, int top_k,
+                   int det_exp, int skip_pass1, float* out, int max_out) {
+    ORC_TRY
+    Net* n = (Net*)h;
+    std::vector<const float*> heads;
+    std::vector<HeadSpec> specs;
+    std::vector<std::vector<float>> anch;
+    for (size_t i = 0; i < n->layers.size(); ++i) {
+        const Layer& L = n->layers[i];
+        if (L.kind != K_YOLO) continue;
+        const Tensor& t = source == 0 ? n->out_f32[i] : n->head_q8[i];
+        if (t.d.empty()) throw std::runtime_error("no head output; run forward first");
+        size_t sample = (size_t)t.s.w * t.s.h * L.mask.size() * (L.classes + 5);
+        if (sample * t.s.b != t.d.size()) throw std::runtime_error("YOLO head tensor length mismatch");
+        if (b < 0 || b >= t.s.b) throw std::runtime_error("batch index outside YOLO head batch");
+        heads.push_back(t.d.data() + sample * b);
+        std::vector<float> a;
+        for (int m : L.mask) {
+            if ((size_t)(2 * m + 1) >= L.anchors.size()) throw std::runtime_error("missing anchor for YOLO mask index");
+            a.push_back(L.anchors[2 * m]);
+            a.push_back(L.anchors[2 * m + 1]);
+        }
+        anch.push_back(a);
+        HeadSpec hs;
+        hs.gw = t.s.w; hs.gh = t.s.h; hs.classes = L.classes; hs.n_anchor = (int)L.mask.size();
+        hs.anchors_wh = nullptr; hs.scale_x_y = L.scale_x_y; hs.new_coords = L.new_coords;
+        specs.push_back(hs);
+    }
+    for (size_t k = 0; k < specs.size(); ++k) specs[k].anchors_wh = anch[k].data();
+    auto d = detect_image(heads, specs, n->width, n->height, img_w, img_h, thr, nms_thr, letterbox != 0, top_k, det_exp != 0,
+                          skip_pass1 != 0);
+    for (int i = 0; i < (int)d.size() && i < max_out; ++i) {
+        float* r = out + 7 * i;
+        r[0] = (float)d[i].class_id; r[1] = d[i].conf; r[2] = d[i].obj; r[3] = d[i].x; r[4] = d[i].y; r[5] = d[i].w; r[6] = d[i].h;
+    }
+    return (int)d.size();
+    ORC_CATCH(-1)
+}
+
+// Standalone decode+NMS of one image given raw head tensors.
+// meta per head (8 floats): gw, gh, classes, n_anchor, scale_x_y, new_coords, then
+// anchors are passed in `anchors` as consecutive (w,h) pairs per head.
+int orc_decode_nms(int n_heads, const float* const* heads, const float* meta, const float* anchors, int net_w, int net_h,
+                   int img_w, int img_h, float thr, float nms_thr, int letterbox, int top_k, int det_exp, int skip_pass1,
+                   float* out, int max_out) {
+    ORC_TRY
+    std::vector<const float*> hp(heads, heads + n_heads);
+    std::vector<HeadSpec> specs(n_heads);
+    const float* a = anchors;
+    for (int k = 0; k < n_heads; ++k) {
+        const float* m = meta + 8 * k;
+        specs[k].gw = (int)m[0]; specs[k].gh = (int)m[1]; specs[k].classes = (int)m[2]; specs[k].n_anchor = (int)m[3];
+        specs[k].scale_x_y = m[4]; specs[k].new_coords = (int)m[5];
+        specs[k].anchors_wh = a;
+        a += 2 * specs[k].n_anchor;
+    }
+    auto d = detect_image(hp, specs, net_w, net_h, img_w, img_h, thr, nms_thr, letterbox != 0, top_k, det_exp != 0, skip_pass1 != 0);
+    for (int i = 0; i < (int)d.size() && i < max_out; ++i) {
+        float* r = out + 7 * i;
+        r[0] = (float)d[i].class_id; r[1] = d[i].conf; r[2] = d[i].obj; r[3] = d[i].x; r[4] = d[i].y; r[5] = d[i].w; r[6] = d[i].h;
+    }
+    return (int)d.size();
+    ORC_CATCH(-1)
+}
+
+// Decode only (no NMS, no sort): candidates in emission order.
+int orc_decode_only(int n_heads, const float* const* heads, const float* meta, const float* anchors, int net_w, int net_h,
+                    int img_w, int img_h, float thr, int letterbox, int det_exp, float* out, int max_out) {
+    ORC_TRY
+    std::vector<Det> d;
+    const float* a = anchors;
+    for (int k = 0; k < n_heads; ++k) {
+        const float* m = meta + 8 * k;
+        HeadSpec hs;
+        hs.gw = (int)m[0]; hs.gh = (int)m[1]; hs.classes = (int)m[2]; hs.n_anchor = (int)m[3];
+        hs.scale_x_y = m[4]; hs.new_coords = (int)m[5]; hs.anchors_wh = a;
+        a += 2 * hs.n_anchor;
+        decode_head(heads[k], hs, net_w, net_h, img_w, img_h, thr, letterbox != 0, det_exp != 0, d);
+    }
+    for (int i = 0; i < (int)d.size() && i < max_out; ++i) {
+        float* r = out + 7 * i;
+        r[0] = (float)d[i].class_id; r[1] = d[i].conf; r[2] = d[i].obj; r[3] = d[i].x; r[4] = d[i].y; r[5] = d[i].w; r[6] = d[i].h;
+    }
+    return (int)d.size();
+    ORC_CATCH(-1)
+}
+
+// NMS passes on caller-supplied records (7 floats each, emission order): the
+// sequence of decode_network_detections after decoding.  Returns kept count.
+int orc_nms_records(float* recs, int n, float nms_thr, int top_k, int skip_pass1) {
+    std::vector<Det> d(n);
+    for (int i = 0; i < n; ++i) {
+        const float* r = recs + 7 * i;
+        d[i] = Det{(int)r[0], r[1], r[2], r[3], r[4], r[5], r[6]};
+    }
+    if (!skip_pass1) apply_nms(d, 1.0f);
+    sort_conf_desc(d);
+    apply_nms(d, nms_thr);
+    sort_conf_desc(d);
+    if (top_k > 0 && (int)d.size() > top_k) d.resize(top_k);
+    for (int i = 0; i < (int)d.size(); ++i) {
+        float* r = recs + 7 * i;
+        r[0] = (float)d[i].class_id; r[1] = d[i].conf; r[2] = d[i].obj; r[3] = d[i].x; r[4] = d[i].y; r[5] = d[i].w; r[6] = d[i].h;
+    }
+    return (int)d.size();
+}
+
+// Single-layer int8 conv: NCHW int8 in, [F][C][k][k] int8 weights, NCHW int32 accumulators out.
+void orc_conv_q8_acc(const int8_t* x, int B, int C, int H, int W, const int8_t* wq, int F, int k, int sx, int sy, int pad,
+                     int32_t* acc) {
+    int OH = conv_dim(H, pad, k, sy), OW = conv_dim(W, pad, k, sx);
+    conv_q8_acc(x, B, C, H, W, wq, F, k, sx, sy, pad, OH, OW, acc);
+}
+
+// Epilogue of the int8 conv on caller-supplied accumulators (NCHW): f32 activation value and int8.
+void orc_q8_epilogue(const int32_t* acc, int B, int F, int plane, const float* mult, const float* bias, int act, float inv_sy,
+                     float* out_f32, int8_t* out_q8) {
+    for (int b = 0; b < B; ++b)
+        for (int f = 0; f < F; ++f)
+            for (int p = 0; p < plane; ++p) {
+                size_t i = ((size_t)b * F + f) * plane + p;
+                float a = det_activate((Act)act, std::fma((float)acc[i], mult[f], bias[f]));
+                if (out_f32) out_f32[i] = a;
+                if (out_q8) out_q8[i] = quant_i8(a, inv_sy);
+            }
+}
+
+// Single f32 conv layer in the reference loop order (folded weights + bias), NCHW.
+void orc_conv_f32(const float* x, int B, int C, int H, int W, const float* w, const float* bias, int F, int k, int sx, int sy,
+                  int pad, int groups, int act, float* y) {
+    Layer L;
+    L.filters = F; L.size = k; L.stride_x = sx; L.stride_y = sy; L.padding = pad; L.groups = groups; L.act = (Act)act;
+    Shape is; is.w = W; is.h = H; is.c = C; is.b = B;
+    Shape os; os.w = conv_dim(W, pad, k, sx); os.h = conv_dim(H, pad, k, sy); os.c = F; os.b = B;
+    Tensor xt(is), yt(os);
+    std::memcpy(xt.d.data(), x, xt.d.size() * 4);
+    std::vector<float> fw(w, w + (size_t)F * (C / std::max(groups, 1)) * k * k), fb(bias, bias + F);
+    conv_f32(L, xt, yt, true, &fw, &fb);
+    std::memcpy(y, yt.d.data(), yt.d.size() * 4);
+}
+
+void orc_maxpool_f32(const float* x, int B, int C, int H, int W, int size, int sx, int sy, int padding, float* y) {
+    Layer L;
+    L.size = size; L.stride_x = sx; L.stride_y = sy; L.padding = padding;
+    Shape is; is.w = W; is.h = H; is.c = C; is.b = B;
+    Shape os; os.w = pool_dim(W, padding, size, sx); os.h = pool_dim(H, padding, size, sy); os.c = C; os.b = B;
+    Tensor xt(is), yt(os);
+    std::memcpy(xt.d.data(), x, xt.d.size() * 4);
+    maxpool_f32(L, xt, yt);
+    std::memcpy(y, yt.d.data(), yt.d.size() * 4);
+}
+
+float orc_activate(int act, float v) { return activate((Act)act, v); }
+float orc_det_activate(int act, float v) { return det_activate((Act)act, v); }
+float orc_det_expf(float v) { return det_expf(v); }
+float orc_bbox_iou(const float* a, const float* b) {
+    Det da{0, 0, 0, a[0], a[1], a[2], a[3]}, db{0, 0, 0, b[0], b[1], b[2], b[3]};
+    return bbox_iou(da, db);
+}
+unsigned char orc_f32_to_e4m3(float v) { return f32_to_e4m3(v); }
+float orc_e4m3_to_f32(unsigned char b) { return e4m3_to_f32(b); }
+int8_t orc_quant_i8(float a, float inv_s) { return quant_i8(a, inv_s); }
+
+}  // extern "C"

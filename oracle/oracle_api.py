@@ -1,0 +1,330 @@
+"""ctypes binding of the CPU oracle (oracle/lightnet_oracle.cpp).
+
+Test infrastructure only: imported by tests/, by the smoke entry and by the bench's
+cpu_baseline / reference legs as the checker.  The product package never imports it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "build", "liblightnet_oracle.so")
+
+ACT = {"linear": 0, "logistic": 1, "leaky": 2, "mish": 3, "swish": 4, "relu": 5}
+KIND = {0: "conv", 1: "maxpool", 2: "route", 3: "shortcut", 4: "upsample", 5: "yolo"}
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with its Makefile if the library is missing or stale."""
+    src = os.path.join(_HERE, "lightnet_oracle.cpp")
+    stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB_PATH)
+        L.orc_last_error.restype = C.c_char_p
+        L.orc_net_create.restype = C.c_void_p
+        L.orc_net_create.argtypes = [C.c_char_p, C.c_int]
+        L.orc_net_destroy.argtypes = [C.c_void_p]
+        L.orc_net_num_layers.argtypes = [C.c_void_p]
+        L.orc_net_layer_info.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.orc_net_dims.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_net_weight_count.restype = C.c_longlong
+        L.orc_net_weight_count.argtypes = [C.c_void_p]
+        L.orc_net_set_weights.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong]
+        L.orc_net_forward_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.orc_net_layer_output_f32.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.orc_net_calibrate.argtypes = [C.c_void_p]
+        L.orc_net_get_amax.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_net_get_scales.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_net_set_scales.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.orc_net_forward_q8.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_net_layer_output_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.orc_net_head_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.orc_net_conv_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.orc_net_detect.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_int,
+                                     C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        L.orc_decode_nms.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                     C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        L.orc_decode_only.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                      C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        L.orc_nms_records.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_int]
+        L.orc_conv_q8_acc.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
+        L.orc_q8_epilogue.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float,
+                                      C.c_void_p, C.c_void_p]
+        L.orc_conv_f32.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p, C.c_void_p] + [C.c_int] * 7 + [C.c_void_p]
+        L.orc_maxpool_f32.argtypes = [C.c_void_p] + [C.c_int] * 8 + [C.c_void_p]
+        for name in ("orc_activate", "orc_det_activate"):
+            getattr(L, name).restype = C.c_float
+            getattr(L, name).argtypes = [C.c_int, C.c_float]
+        L.orc_det_expf.restype = C.c_float
+        L.orc_det_expf.argtypes = [C.c_float]
+        L.orc_bbox_iou.restype = C.c_float
+        L.orc_bbox_iou.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_f32_to_e4m3.restype = C.c_ubyte
+        L.orc_f32_to_e4m3.argtypes = [C.c_float]
+        L.orc_e4m3_to_f32.restype = C.c_float
+        L.orc_e4m3_to_f32.argtypes = [C.c_ubyte]
+        L.orc_quant_i8.restype = C.c_int8
+        L.orc_quant_i8.argtypes = [C.c_float, C.c_float]
+        L.orc_set_threads.argtypes = [C.c_int]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _err():
+    return lib().orc_last_error().decode()
+
+
+class OracleError(RuntimeError):
+    pass
+
+
+class Net:
+    """The oracle's executable network: cfg text -> layers -> f32 / int8 forward -> detections."""
+
+    def __init__(self, cfg_text: str, batch: int = 0):
+        self.h = lib().orc_net_create(cfg_text.encode(), batch)
+        if not self.h:
+            raise OracleError(_err())
+        d = np.zeros(4, np.int32)
+        lib().orc_net_dims(self.h, _p(d))
+        self.width, self.height, self.channels, self.batch = (int(v) for v in d)
+        self.num_layers = lib().orc_net_num_layers(self.h)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().orc_net_destroy(self.h)
+            self.h = None
+
+    def layer_info(self, i):
+        v = np.zeros(16, np.int32)
+        if lib().orc_net_layer_info(self.h, i, _p(v)):
+            raise IndexError(i)
+        keys = ["kind", "in_w", "in_h", "in_c", "in_b", "out_w", "out_h", "out_c", "out_b", "filters", "size", "stride_x",
+                "stride_y", "padding", "bn", "act"]
+        d = dict(zip(keys, (int(x) for x in v)))
+        d["kind"] = KIND[d["kind"]]
+        return d
+
+    def layers(self):
+        return [self.layer_info(i) for i in range(self.num_layers)]
+
+    def weight_count(self) -> int:
+        return int(lib().orc_net_weight_count(self.h))
+
+    def set_weights(self, w: np.ndarray):
+        w = np.ascontiguousarray(w, np.float32)
+        if lib().orc_net_set_weights(self.h, _p(w), w.size):
+            raise OracleError(_err())
+
+    def forward_f32(self, x: np.ndarray, folded: bool = False):
+        x = np.ascontiguousarray(x, np.float32)
+        assert x.size == self.batch * self.channels * self.height * self.width
+        if lib().orc_net_forward_f32(self.h, _p(x), 1 if folded else 0):
+            raise OracleError(_err())
+
+    def out_shape(self, i):
+        d = self.layer_info(i)
+        return (d["out_b"], d["out_c"], d["out_h"], d["out_w"])
+
+    def layer_output_f32(self, i):
+        out = np.zeros(self.out_shape(i), np.float32)
+        if lib().orc_net_layer_output_f32(self.h, i, _p(out)):
+            raise OracleError("no f32 output for layer %d" % i)
+        return out
+
+    def calibrate(self):
+        if lib().orc_net_calibrate(self.h):
+            raise OracleError(_err())
+
+    def amax(self):
+        out = np.zeros(self.num_layers + 1, np.float32)
+        lib().orc_net_get_amax(self.h, _p(out))
+        return out
+
+    def scales(self):
+        out = np.zeros(self.num_layers + 1, np.float32)
+        lib().orc_net_get_scales(self.h, _p(out))
+        return out
+
+    def set_scales(self, s):
+        s = np.ascontiguousarray(s, np.float32)
+        if lib().orc_net_set_scales(self.h, _p(s), s.size):
+            raise OracleError("scale count mismatch")
+
+    def forward_q8(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        if lib().orc_net_forward_q8(self.h, _p(x)):
+            raise OracleError(_err())
+
+    def layer_output_q8(self, i):
+        out = np.zeros(self.out_shape(i), np.int8)
+        if lib().orc_net_layer_output_q8(self.h, i, _p(out)):
+            raise OracleError("no int8 output for layer %d" % i)
+        return out
+
+    def head_q8(self, i):
+        out = np.zeros(self.out_shape(i), np.float32)
+        if lib().orc_net_head_q8(self.h, i, _p(out)):
+            raise OracleError("layer %d is not a head of the int8 run" % i)
+        return out
+
+    def conv_quant(self, i):
+        d = self.layer_info(i)
+        n = d["filters"] * d["in_c"] * d["size"] * d["size"]
+        wq = np.zeros(n, np.int8)
+        ws = np.zeros(d["filters"], np.float32)
+        fb = np.zeros(d["filters"], np.float32)
+        if lib().orc_net_conv_quant(self.h, i, _p(wq), _p(ws), _p(fb)):
+            raise OracleError("layer %d is not a convolution" % i)
+        return wq.reshape(d["filters"], d["in_c"], d["size"], d["size"]), ws, fb
+
+    def detect(self, source, b, img_w, img_h, thr=0.25, nms=0.45, letterbox=True, top_k=0, det_exp=False,
+               skip_pass1=False, max_out=1 << 20):
+        """source: 'f32' or 'q8'.  Returns an (n,7) array {class, conf, obj, x, y, w, h}."""
+        out = np.zeros((max_out, 7), np.float32)
+        n = lib().orc_net_detect(self.h, 0 if source == "f32" else 1, b, img_w, img_h, thr, nms, int(letterbox), top_k,
+                                 int(det_exp), int(skip_pass1), _p(out), max_out)
+        if n < 0:
+            raise OracleError(_err())
+        return out[: min(n, max_out)].copy()
+
+
+def _head_args(heads, specs):
+    """heads: list of float32 arrays (one image each, [A*(5+cls), gh, gw]); specs: list of dicts
+    {gw, gh, classes, anchors:[(w,h),...], scale_x_y, new_coords}."""
+    arrs = [np.ascontiguousarray(h, np.float32) for h in heads]
+    ptrs = (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
+    meta = np.zeros((len(specs), 8), np.float32)
+    anchors = []
+    for k, s in enumerate(specs):
+        meta[k, :6] = [s["gw"], s["gh"], s["classes"], len(s["anchors"]), s.get("scale_x_y", 1.0), s.get("new_coords", 0)]
+        for a in s["anchors"]:
+            anchors += [a[0], a[1]]
+    return arrs, ptrs, meta, np.asarray(anchors, np.float32)
+
+
+def decode_nms(heads, specs, net_w, net_h, img_w, img_h, thr, nms, letterbox=False, top_k=0, det_exp=False,
+               skip_pass1=False, max_out=1 << 20):
+    arrs, ptrs, meta, anchors = _head_args(heads, specs)
+    out = np.zeros((max_out, 7), np.float32)
+    n = lib().orc_decode_nms(len(arrs), ptrs, _p(meta), _p(anchors), net_w, net_h, img_w, img_h, thr, nms, int(letterbox),
+                             top_k, int(det_exp), int(skip_pass1), _p(out), max_out)
+    if n < 0:
+        raise OracleError(_err())
+    return out[: min(n, max_out)].copy()
+
+
+def decode_only(heads, specs, net_w, net_h, img_w, img_h, thr, letterbox=False, det_exp=False, max_out=1 << 22):
+    arrs, ptrs, meta, anchors = _head_args(heads, specs)
+    out = np.zeros((max_out, 7), np.float32)
+    n = lib().orc_decode_only(len(arrs), ptrs, _p(meta), _p(anchors), net_w, net_h, img_w, img_h, thr, int(letterbox),
+                              int(det_exp), _p(out), max_out)
+    if n < 0:
+        raise OracleError(_err())
+    if n > max_out:
+        raise OracleError("decode_only: %d candidates exceed max_out" % n)
+    return out[:n].copy()
+
+
+def nms_records(recs, nms, top_k=0, skip_pass1=False):
+    r = np.ascontiguousarray(recs, np.float32).copy()
+    n = lib().orc_nms_records(_p(r), r.shape[0], nms, top_k, int(skip_pass1))
+    return r[:n].copy()
+
+
+def conv_q8_acc(x, wq, stride=1, pad=0):
+    """x int8 NCHW, wq int8 [F,C,k,k] -> int32 NCHW accumulators."""
+    x = np.ascontiguousarray(x, np.int8)
+    wq = np.ascontiguousarray(wq, np.int8)
+    B, Cc, H, W = x.shape
+    F, C2, k, _ = wq.shape
+    assert C2 == Cc
+    OH = (H + 2 * pad - k) // stride + 1
+    OW = (W + 2 * pad - k) // stride + 1
+    acc = np.zeros((B, F, OH, OW), np.int32)
+    lib().orc_conv_q8_acc(_p(x), B, Cc, H, W, _p(wq), F, k, stride, stride, pad, _p(acc))
+    return acc
+
+
+def q8_epilogue(acc, mult, bias, act, inv_sy):
+    acc = np.ascontiguousarray(acc, np.int32)
+    B, F, OH, OW = acc.shape
+    mult = np.ascontiguousarray(mult, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    of = np.zeros(acc.shape, np.float32)
+    oq = np.zeros(acc.shape, np.int8)
+    lib().orc_q8_epilogue(_p(acc), B, F, OH * OW, _p(mult), _p(bias), ACT[act] if isinstance(act, str) else act,
+                          float(inv_sy), _p(of), _p(oq))
+    return of, oq
+
+
+def conv_f32(x, w, bias, stride=1, pad=0, groups=1, act="linear"):
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    B, Cc, H, W = x.shape
+    F, _, k, _ = w.shape
+    OH = (H + 2 * pad - k) // stride + 1
+    OW = (W + 2 * pad - k) // stride + 1
+    y = np.zeros((B, F, OH, OW), np.float32)
+    lib().orc_conv_f32(_p(x), B, Cc, H, W, _p(w), _p(bias), F, k, stride, stride, pad, groups, ACT[act], _p(y))
+    return y
+
+
+def maxpool_f32(x, size, stride_x, stride_y, padding):
+    x = np.ascontiguousarray(x, np.float32)
+    B, Cc, H, W = x.shape
+    OH = max(H + padding - size, 0) // stride_y + 1
+    OW = max(W + padding - size, 0) // stride_x + 1
+    y = np.zeros((B, Cc, OH, OW), np.float32)
+    lib().orc_maxpool_f32(_p(x), B, Cc, H, W, size, stride_x, stride_y, padding, _p(y))
+    return y
+
+
+def activate(act, v):
+    return float(lib().orc_activate(ACT[act], float(v)))
+
+
+def det_activate(act, v):
+    return float(lib().orc_det_activate(ACT[act], float(v)))
+
+
+def det_expf(v):
+    return float(lib().orc_det_expf(float(v)))
+
+
+def bbox_iou(a, b):
+    a = np.asarray(a, np.float32)
+    b = np.asarray(b, np.float32)
+    return float(lib().orc_bbox_iou(_p(a), _p(b)))
+
+
+def f32_to_e4m3(v):
+    return int(lib().orc_f32_to_e4m3(float(v)))
+
+
+def e4m3_to_f32(b):
+    return float(lib().orc_e4m3_to_f32(int(b)))
+
+
+def set_threads(n):
+    lib().orc_set_threads(int(n))
