@@ -1,0 +1,244 @@
+/*
+ * lightnet_b200.h -- C ABI of the B200 (sm_100a) backend for lightnet's detector
+ * inference path: [convolutional] forward + route/shortcut/upsample/maxpool glue +
+ * [yolo] decode + per-class greedy NMS.
+ *
+ * The entry points map one to one onto the methods a Rust backend crate implements
+ * for the lightnet runtime (trait F32TensorOpsBackend, src/lightnet-cuda/src/lib.rs:460,
+ * and a reduced-precision trait shaped like F16TensorOpsBackend, lib.rs:6295).  Each
+ * declaration cites the trait method it stands behind.  All shapes are
+ * [batch, channels, height, width] as in runtime/weights_io.rs:758
+ * (tensor_backend_shape); host f32 data is planar NCHW (lightnet-model model.rs:98).
+ *
+ * Conventions
+ *   - every function returns an int32 status: LN_OK or an LN_ERR_* code; nothing aborts
+ *     or throws across the boundary; ln_last_error(ctx) gives the message
+ *     (maps to `Result<_, Self::Error>`, Error: Display)
+ *   - tensors are opaque ref-counted handles; every op returns a NEW tensor and never
+ *     mutates its inputs (maps to `type Tensor: Clone`; retain = Clone, release = Drop)
+ *   - one ctx = one device + one stream; all work is stream ordered; a ctx is
+ *     thread-compatible, not thread-safe (the runtime's executor is !Sync:
+ *     runtime/gpu_types.rs:227-244).  Multi-GPU = one ctx per device.
+ *   - there is no CPU fallback: without a usable CUDA device ln_ctx_create fails.
+ */
+#ifndef LIGHTNET_B200_H
+#define LIGHTNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ln_ctx ln_ctx;
+typedef struct ln_tensor ln_tensor;
+typedef struct ln_conv_weights ln_conv_weights;
+typedef struct ln_net ln_net;
+
+enum ln_status {
+    LN_OK = 0,
+    LN_ERR_SHAPE = 1,       /* OxideError::Shape analogue (lightnet-cuda-oxide/src/lib.rs:177-192) */
+    LN_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed */
+    LN_ERR_TIMEOUT = 3,     /* a bounded device-side wait gave up; the context stays usable */
+    LN_ERR_UNSUPPORTED = 4, /* OxideError::NotImplemented analogue */
+    LN_ERR_ARG = 5,
+    LN_ERR_PARSE = 6
+};
+
+/* F32ActivationKind (lightnet-cuda/src/lib.rs:23-55), hot-path subset. */
+enum ln_activation { LN_ACT_LINEAR = 0, LN_ACT_LOGISTIC = 1, LN_ACT_LEAKY = 2, LN_ACT_MISH = 3, LN_ACT_SWISH = 4, LN_ACT_RELU = 5 };
+
+enum ln_dtype { LN_F32 = 0, LN_Q8 = 1, LN_I32 = 2, LN_F8 = 3 };
+
+/* What a reduced-precision convolution writes. */
+enum ln_conv_out {
+    LN_OUT_Q = 0,   /* same 8-bit storage type as the input, requantised with y_scale */
+    LN_OUT_F32 = 1, /* f32 NCHW: the convolution feeding a detection head (ConvPrecision::NoLowPrecision policy,
+                       lightnet-cuda/src/lib.rs:161, runtime/types.rs:146-170) */
+    LN_OUT_ACC = 2  /* raw int32 accumulators, NCHW (parity checks only; int8 inputs only) */
+};
+
+/* ---- context ------------------------------------------------------------------- */
+/* OxideBackend::with_device (lightnet-cuda-oxide/src/lib.rs:643) */
+int32_t ln_ctx_create(int32_t device, ln_ctx** out);
+int32_t ln_ctx_destroy(ln_ctx* ctx);
+const char* ln_last_error(ln_ctx* ctx); /* ctx may be NULL: message of the last failed create */
+int32_t ln_sync(ln_ctx* ctx);
+/* The ctx's cudaStream_t, for callers that time with CUDA events. */
+void* ln_ctx_stream(ln_ctx* ctx);
+/* 1 = activation epilogues use only IEEE-exact operations (bit-reproducible on a CPU), 0 = fast hardware
+   approximations (default).  Affects mish / swish / logistic in reduced-precision convolutions. */
+int32_t ln_ctx_set_exact_epilogue(ln_ctx* ctx, int32_t on);
+/* Number of kernels this library has launched on the ctx since creation. */
+int64_t ln_ctx_launch_count(ln_ctx* ctx);
+
+/* ---- f32 tensors: F32TensorOpsBackend ---------------------------------------------- */
+/* upload_f32 / zeros_f32 / download_f32 / tensor_shape (lib.rs:464-469) */
+int32_t ln_tensor_upload_f32(ln_ctx* ctx, const int64_t shape[4], const float* host, ln_tensor** out);
+int32_t ln_tensor_zeros_f32(ln_ctx* ctx, const int64_t shape[4], ln_tensor** out);
+int32_t ln_tensor_download_f32(ln_ctx* ctx, const ln_tensor* t, float* host, int64_t count);
+int32_t ln_tensor_shape(const ln_tensor* t, int64_t shape[4]);
+int32_t ln_tensor_dtype(const ln_tensor* t);
+int32_t ln_tensor_retain(ln_tensor* t);
+int32_t ln_tensor_release(ln_tensor* t);
+
+/* conv2d_f32 (lib.rs:1776); weights are f32 [filters, C/groups, k, k] */
+int32_t ln_conv2d_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* weights, const int64_t output_shape[4],
+                      int64_t input_channels, int64_t input_height, int64_t input_width, int64_t filters,
+                      int64_t kernel_size, int64_t stride_x, int64_t stride_y, int64_t dilation, int64_t padding,
+                      int64_t groups, ln_tensor** out);
+/* bias_add_f32 (lib.rs:477), activation_f32 (lib.rs:500), bias_activation_f32 (lib.rs:546) */
+int32_t ln_bias_add_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* bias, int64_t channels, int64_t channel_stride,
+                        ln_tensor** out);
+int32_t ln_activation_f32(ln_ctx* ctx, const ln_tensor* x, int32_t activation, ln_tensor** out);
+int32_t ln_bias_activation_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* bias, int64_t channels,
+                               int64_t channel_stride, int32_t activation, ln_tensor** out);
+/* shortcut_add_f32 (lib.rs:803), shortcut_fit_f32 (lib.rs:4041) */
+int32_t ln_shortcut_add_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* y, ln_tensor** out);
+int32_t ln_shortcut_fit_f32(ln_ctx* ctx, const ln_tensor* x, int64_t batch, const int64_t output_shape[4], ln_tensor** out);
+/* route_concat_f32 (lib.rs:937) */
+int32_t ln_route_concat_f32(ln_ctx* ctx, const ln_tensor* const* inputs, int32_t n_inputs,
+                            const int64_t* input_channel_offsets, const int64_t* input_channels,
+                            const int64_t* input_total_channels, const int64_t output_shape[4], int64_t channel_stride,
+                            ln_tensor** out);
+/* maxpool_f32 (lib.rs:2036), upsample_f32 (lib.rs:3963) */
+int32_t ln_maxpool_f32(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels,
+                       int64_t input_height, int64_t input_width, int64_t size, int64_t stride_x, int64_t stride_y,
+                       int64_t padding, ln_tensor** out);
+int32_t ln_upsample_f32(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels,
+                        int64_t input_height, int64_t input_width, int64_t stride, float scale, int32_t reverse,
+                        ln_tensor** out);
+/* batchnorm_fold_f32 (lib.rs:6208): returns (scale, bias') */
+int32_t ln_batchnorm_fold_f32(ln_ctx* ctx, const ln_tensor* gamma, const ln_tensor* mean, const ln_tensor* variance,
+                              const ln_tensor* bias, float eps, ln_tensor** scale_out, ln_tensor** bias_out);
+
+/* ---- 8-bit tensors (int8 / FP8 E4M3): twins of F16TensorOpsBackend ------------------ */
+/* Storage is NHWC, channels padded to a multiple of 32, one f32 scale per tensor (value = q * scale).
+   upload_f16 (lib.rs:6300) analogue: quantise host f32 NCHW data with `scale` (int8: rne, clamp +-127;
+   FP8: cvt.rn.satfinite e4m3). */
+int32_t ln_tensor_upload_q(ln_ctx* ctx, const int64_t shape[4], const float* host, float scale, int32_t dtype, ln_tensor** out);
+/* Raw 8-bit codes of a Q8 / F8 tensor in NCHW order (parity checks), and its scale. */
+int32_t ln_tensor_download_q(ln_ctx* ctx, const ln_tensor* t, void* host_codes, int64_t count, float* scale);
+/* Raw 8-bit codes (NCHW order) -> device tensor with the given scale. */
+int32_t ln_tensor_upload_codes(ln_ctx* ctx, const int64_t shape[4], const void* host_codes, float scale, int32_t dtype,
+                               ln_tensor** out);
+/* int32 accumulators of an LN_OUT_ACC convolution, NCHW. */
+int32_t ln_tensor_download_i32(ln_ctx* ctx, const ln_tensor* t, int32_t* host, int64_t count);
+/* widen_f16 (lib.rs:6304) / narrow_f32 (lib.rs:6308) analogues, on device. */
+int32_t ln_tensor_widen_q(ln_ctx* ctx, const ln_tensor* t, ln_tensor** out_f32);
+int32_t ln_tensor_narrow_f32(ln_ctx* ctx, const ln_tensor* t, float scale, int32_t dtype, ln_tensor** out_q);
+float ln_tensor_scale(const ln_tensor* t);
+
+/* conv_weights_f16 (lib.rs:6311) analogue: f32 [filters, per_filter = C*k*k] BN-folded weights ->
+   the backend's GEMM operand ([filters][k][k][C] 8-bit, channels padded) plus per-filter scales
+   (int8: s = max|w|/127 per filter; FP8: s = max|w|/448 per filter). */
+int32_t ln_conv_weights_q(ln_ctx* ctx, const ln_tensor* weights_f32, int64_t filters, int64_t channels, int64_t kernel_size,
+                          int32_t dtype, ln_conv_weights** out);
+int32_t ln_conv_weights_release(ln_conv_weights* w);
+/* conv2d_bias_act_f16 (lib.rs:6342) analogue:
+     int8: acc = sum(xq*wq) (int32);  v = fma(float(acc), x.scale*w.scale[f], bias[f]);  a = act(v)
+     FP8 : acc = sum(xq*wq) (f32);    v = fma(acc,        x.scale*w.scale[f], bias[f]);  a = act(v)
+   LN_OUT_Q stores quantise(a / y_scale); LN_OUT_F32 stores a; LN_OUT_ACC stores acc.
+   groups must be 1 and dilation 1 (all detector cfgs on the path). */
+int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weights* weights, const ln_tensor* bias,
+                             const int64_t output_shape[4], int64_t channels, int64_t input_height, int64_t input_width,
+                             int64_t filters, int64_t kernel_size, int64_t stride_x, int64_t stride_y, int64_t dilation,
+                             int64_t padding, int64_t groups, int32_t activation, float y_scale, int32_t out_kind,
+                             ln_tensor** out);
+/* maxpool_f16 (lib.rs:6384), upsample_f16 (lib.rs:6405), route_concat_f16 (lib.rs:6417),
+   shortcut_add_act_f16 (lib.rs:6502) analogues.  Max-pool, up-sample and route keep the input scale
+   (route inputs must share one scale); shortcut requantises act(a*sa + b*sb) with y_scale. */
+int32_t ln_maxpool_q(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height,
+                     int64_t input_width, int64_t size, int64_t stride_x, int64_t stride_y, int64_t padding, ln_tensor** out);
+int32_t ln_upsample_q(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height,
+                      int64_t input_width, int64_t stride, float scale, int32_t reverse, ln_tensor** out);
+int32_t ln_route_concat_q(ln_ctx* ctx, const ln_tensor* const* inputs, int32_t n_inputs, const int64_t* input_channel_offsets,
+                          const int64_t* input_channels, const int64_t* input_total_channels, const int64_t output_shape[4],
+                          int64_t channel_stride, ln_tensor** out);
+int32_t ln_shortcut_add_act_q(ln_ctx* ctx, const ln_tensor* a, const ln_tensor* b, int32_t activation, float y_scale,
+                              ln_tensor** out);
+
+/* ---- [yolo] decode + NMS on the device ---------------------------------------------- */
+/* Optional device path for decode_network_detections (lightnet-train/src/detect.rs:113-244): the Rust shim
+   returns Ok(None) when this is absent (the idiom of yolo_loss_f32, lightnet-cuda/src/lib.rs:4918), so detect.rs
+   and the CLI stay unchanged.  Semantics: decode_yolo_head (detect.rs:934-1016) over every head in order,
+   stable sort by confidence (detect.rs:107), greedy per-class NMS (apply_nms, detect.rs:1449-1484, on the
+   sorted list), records in confidence-descending order; top_k > 0 truncates the result (extension).
+   The IoU>1.0 pre-pass of detect.rs:127-128 is not run (it can only fire for coincident boxes). */
+typedef struct ln_yolo_head {
+    const ln_tensor* raw;  /* f32 [batch, n_anchor*(5+classes), gh, gw] raw head (YoloHeadOutput, runtime/types.rs:107) */
+    int32_t classes;
+    int32_t n_anchor;
+    float anchors[2 * 8];  /* (w,h) per masked anchor, already selected through `mask` (detection_geometry.rs:100) */
+    float scale_x_y;
+    int32_t new_coords;
+} ln_yolo_head;
+
+typedef struct ln_detection { /* Detection (detect.rs:21-27): bbox centre/size in image pixels */
+    float class_id, confidence, objectness, x, y, w, h;
+} ln_detection;
+
+typedef struct ln_detect_options { /* DetectionOptions (detect.rs:47-61) + top_k */
+    float confidence_threshold;
+    float nms_threshold;
+    int32_t letterbox;
+    int32_t top_k;        /* 0 = unlimited */
+    int32_t max_per_image; /* capacity of the caller's record array per image */
+} ln_detect_options;
+
+/* records_host: [batch][max_per_image] ln_detection; counts_host: [batch] kept count (clamped to max_per_image).
+   image_w/image_h: per image original size (batch entries). */
+int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t net_w, int32_t net_h,
+                           const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
+                           ln_detection* records_host, int32_t* counts_host);
+/* Decode only: candidates of one image in emission order (parity with decode_yolo_head). */
+int32_t ln_yolo_decode_only(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t image_index, int32_t net_w,
+                            int32_t net_h, int32_t image_w, int32_t image_h, float confidence_threshold, int32_t letterbox,
+                            ln_detection* records_host, int64_t capacity, int64_t* count);
+
+/* ---- whole network: GpuExecutableNetwork<B> ------------------------------------------ */
+/* GpuExecutableNetwork::new (runtime/gpu_state.rs:8) from cfg text; `batch` > 0 overrides [net] batch
+   (Network::with_batch, model.rs:3256).  precision: LN_F32 (trait-faithful f32 NCHW path), LN_Q8 or LN_F8. */
+int32_t ln_net_create(ln_ctx* ctx, const char* cfg_text, int32_t batch, int32_t precision, ln_net** out);
+int32_t ln_net_destroy(ln_net* net);
+int32_t ln_net_num_layers(const ln_net* net);
+/* info[16]: kind(0 conv,1 maxpool,2 route,3 shortcut,4 upsample,5 yolo), in w,h,c,b, out w,h,c,b,
+   filters,size,stride_x,stride_y,padding,batch_normalize,activation */
+int32_t ln_net_layer_info(const ln_net* net, int32_t layer, int32_t info[16]);
+int64_t ln_net_weight_count(const ln_net* net);
+/* load_weights_file payload (runtime/weights_io.rs:227-235): per conv biases, [scales, mean, variance], weights. */
+int32_t ln_net_load_weights(ln_net* net, const float* blob, int64_t count);
+/* Darknet .weights file with header (runtime/weights_io.rs:911-928). */
+int32_t ln_net_load_weights_file(ln_net* net, const char* path);
+/* One f32 forward of `input` (host NCHW, net batch) recording amax of every layer output, then per-tensor
+   scales (amax/127 or amax/448; tensors joined by route/maxpool/upsample share one).  Needed before an
+   8-bit forward unless ln_net_set_scales is used. */
+int32_t ln_net_calibrate(ln_net* net, const float* input_host);
+/* scales[num_layers+1]: [0] network input, [1+i] output of layer i. */
+int32_t ln_net_get_scales(const ln_net* net, float* scales, int32_t count);
+int32_t ln_net_set_scales(ln_net* net, const float* scales, int32_t count);
+/* Layers of the batch run `micro_batch` images at a time so that activations stay in L2 (0 = whole batch). */
+int32_t ln_net_set_micro_batch(ln_net* net, int32_t micro_batch);
+/* forward_compact (runtime/gpu_forward_compact.rs:8): host f32 NCHW input -> heads resident on the device. */
+int32_t ln_net_forward(ln_net* net, const float* input_host);
+/* Same with the input already on the device (f32 NCHW tensor of the net's input shape). */
+int32_t ln_net_forward_device(ln_net* net, const ln_tensor* input);
+int32_t ln_net_num_heads(const ln_net* net);
+/* Head tensor (f32 NCHW raw logits) of the last forward; retained for the caller. */
+int32_t ln_net_head(ln_net* net, int32_t head_index, ln_tensor** out);
+/* Output of layer `layer` from the last forward (whole-batch forwards with micro_batch = 0 only). */
+int32_t ln_net_layer_output(ln_net* net, int32_t layer, ln_tensor** out);
+/* forward + device decode + NMS; what `lightnet-rs detect-image` does per batch (lightnet-cli/src/main.rs:249-459). */
+int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image_w, const int32_t* image_h,
+                      const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host);
+int32_t ln_net_detect_device(ln_net* net, const ln_tensor* input, const int32_t* image_w, const int32_t* image_h,
+                             const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host);
+/* Device time in ms of the most recent ln_net_forward* / ln_net_detect* call, by phase
+   (0 = layers, 1 = decode+NMS), measured with CUDA events on the ctx stream. */
+int32_t ln_net_last_times(const ln_net* net, float times_ms[2]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIGHTNET_B200_H */

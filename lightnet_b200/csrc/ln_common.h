@@ -1,0 +1,156 @@
+// Internal declarations shared by the translation units of liblightnet_b200.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/lightnet_b200.h"
+
+// cuTensorMapEncodeTiled is resolved at run time through cudaGetDriverEntryPoint so that the library
+// has no link-time dependency on the driver library (it must load on a machine without a GPU).
+typedef CUresult (*ln_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct ln_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::string err;
+    bool exact_epilogue = false;
+    int64_t launches = 0;
+    int sm_count = 0;
+    std::multimap<size_t, void*> free_blocks;  // size-keyed pool; reuse is stream ordered
+    size_t pool_bytes = 0;
+    int* d_status = nullptr;  // device status word written by kernels whose bounded waits give up
+    int* h_status = nullptr;  // pinned mirror
+    ln_encode_tiled_fn encode_tiled = nullptr;
+};
+
+struct ln_tensor {
+    ln_ctx* ctx = nullptr;
+    int refcount = 1;
+    int dtype = LN_F32;
+    int64_t n = 0, c = 0, h = 0, w = 0;  // logical shape [batch, channels, height, width]
+    void* ptr = nullptr;                 // first element of the view
+    void* base = nullptr;                // pool block (nullptr for a view onto `parent`)
+    size_t bytes = 0;
+    ln_tensor* parent = nullptr;         // keeps the owner of a view alive
+    int64_t cstride = 0;                 // 8-bit NHWC tensors: bytes between consecutive pixels
+    float scale = 1.0f;                  // 8-bit tensors: value = code * scale
+    int64_t count() const { return n * c * h * w; }
+};
+
+struct ln_conv_weights {
+    ln_ctx* ctx = nullptr;
+    int dtype = LN_Q8;
+    int64_t filters = 0, channels = 0, k = 0;
+    int64_t fpad = 0, cpad = 0;     // filters padded to a multiple of 16 (>= 64 multiple of 64), channels to 32
+    void* w = nullptr;              // [fpad][k][k][cpad] 8-bit codes
+    float* wscale = nullptr;        // [fpad] per-filter scale (device)
+    std::vector<float> h_wscale;    // host copy
+    void* w_oihw = nullptr;         // [filters][channels][k][k] codes in the reference's weight order (SIMT path)
+};
+
+int ln_fail(ln_ctx* ctx, int code, const char* fmt, ...);
+void* ln_pool_alloc(ln_ctx* ctx, size_t bytes);
+void ln_pool_free(ln_ctx* ctx, void* p, size_t bytes);
+ln_tensor* ln_tensor_new(ln_ctx* ctx, int dtype, int64_t n, int64_t c, int64_t h, int64_t w);  // allocates storage
+ln_tensor* ln_tensor_view_q(ln_tensor* parent, int64_t channel_offset, int64_t channels);      // channel slice of an NHWC tensor
+inline int64_t ln_round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+#define LN_CUDA(ctx, call)                                                                                   \
+    do {                                                                                                     \
+        cudaError_t e__ = (call);                                                                            \
+        if (e__ != cudaSuccess) return ln_fail((ctx), LN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
+    } while (0)
+
+#define LN_LAUNCHED(ctx)                                                                                             \
+    do {                                                                                                             \
+        (ctx)->launches++;                                                                                           \
+        cudaError_t e__ = cudaGetLastError();                                                                        \
+        if (e__ != cudaSuccess) return ln_fail((ctx), LN_ERR_CUDA, "kernel launch failed at %s:%d: %s", __FILE__, __LINE__, \
+                                               cudaGetErrorString(e__));                                             \
+    } while (0)
+
+// ---- device-side numerics shared by the kernels --------------------------------------------------
+
+#ifdef __CUDACC__
+// exp built only from IEEE-754 binary32 operations (fma where written): a CPU evaluating the same
+// sequence gets the same bits.  Accuracy: a few ulp.
+__device__ __forceinline__ float ln_det_expf(float x) {
+    x = fminf(fmaxf(x, -87.0f), 88.0f);
+    float n = rintf(__fmul_rn(x, 1.44269502e+00f));
+    float r = __fmaf_rn(n, -6.93145752e-01f, x);
+    r = __fmaf_rn(n, -1.42860677e-06f, r);
+    float p = 1.98412698e-04f;
+    p = __fmaf_rn(p, r, 1.38888889e-03f);
+    p = __fmaf_rn(p, r, 8.33333377e-03f);
+    p = __fmaf_rn(p, r, 4.16666679e-02f);
+    p = __fmaf_rn(p, r, 1.66666672e-01f);
+    p = __fmaf_rn(p, r, 5.00000000e-01f);
+    p = __fmaf_rn(p, r, 1.0f);
+    p = __fmaf_rn(p, r, 1.0f);
+    int e = (int)n;
+    int e1 = e / 2, e2 = e - e1;
+    float s1 = __int_as_float((e1 + 127) << 23), s2 = __int_as_float((e2 + 127) << 23);
+    return __fmul_rn(__fmul_rn(p, s1), s2);
+}
+__device__ __forceinline__ float ln_det_sigmoid(float v) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, ln_det_expf(-v))); }
+
+// Activation of the 8-bit epilogues.  EXACT: IEEE-only operations (bit-reproducible); otherwise the
+// hardware ex2/rcp approximations (about 2 ulp each).
+template <bool EXACT>
+__device__ __forceinline__ float ln_epilogue_act(int act, float v) {
+    switch (act) {
+        case LN_ACT_LINEAR: return v;
+        case LN_ACT_LEAKY: return fmaxf(v, __fmul_rn(0.1f, v));  // v>0 ? v : 0.1v
+        case LN_ACT_RELU: return fmaxf(v, 0.0f);
+        case LN_ACT_MISH: {
+            if (EXACT) {
+                if (v > 20.0f) return v;
+                float e = ln_det_expf(v);
+                float w = __fmul_rn(e, __fadd_rn(e, 2.0f));
+                return __fmul_rn(v, __fdiv_rn(w, __fadd_rn(w, 2.0f)));
+            } else {
+                float e = __expf(fminf(v, 20.0f));
+                float w = e * (e + 2.0f);
+                return v * __fdividef(w, w + 2.0f);
+            }
+        }
+        case LN_ACT_SWISH:
+            if (EXACT) return __fdiv_rn(v, __fadd_rn(1.0f, ln_det_expf(-v)));
+            return __fdividef(v, 1.0f + __expf(-v));
+        case LN_ACT_LOGISTIC:
+            if (EXACT) return ln_det_sigmoid(v);
+            return __fdividef(1.0f, 1.0f + __expf(-v));
+    }
+    return v;
+}
+
+// f32 path activations (libm-accurate device functions)
+__device__ __forceinline__ float ln_act_f32(int act, float v) {
+    switch (act) {
+        case LN_ACT_LINEAR: return v;
+        case LN_ACT_LOGISTIC: return 1.0f / (1.0f + expf(-v));
+        case LN_ACT_LEAKY: return v > 0.0f ? v : 0.1f * v;
+        case LN_ACT_MISH: return v * tanhf(logf(1.0f + expf(v)));
+        case LN_ACT_SWISH: return v / (1.0f + expf(-v));
+        case LN_ACT_RELU: return fmaxf(v, 0.0f);
+    }
+    return v;
+}
+
+// int8 quantiser of the epilogues: rne(a * inv_s), clamped to +-127.
+__device__ __forceinline__ int ln_quant_i8(float a, float inv_s) {
+    float t = __fmul_rn(a, inv_s);
+    t = fminf(fmaxf(t, -127.0f), 127.0f);  // NaN -> -127
+    return __float2int_rn(t);
+}
+#endif

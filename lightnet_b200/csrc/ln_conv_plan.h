@@ -1,0 +1,85 @@
+// Launch plan of one reduced-precision convolution (tensor-core path and CUDA-core path).
+#pragma once
+#include <cstring>
+
+#include "ln_common.h"
+
+enum { LN_KIND_I8 = 0, LN_KIND_F8 = 1 };
+
+// status word values written by kernels whose bounded waits gave up
+enum {
+    LN_STATUS_OK = 0,
+    LN_STATUS_PRODUCER_TIMEOUT = 101,
+    LN_STATUS_MMA_TIMEOUT = 102,
+    LN_STATUS_EPILOGUE_TIMEOUT = 103
+};
+
+struct ln_conv_umma_params {
+    CUtensorMap tmA[4];  // activations; stride-2 convolutions use one map per input parity class
+    CUtensorMap tmB;     // weights as a [fpad][k*k*cpad] matrix
+    int bk, bn, stages;
+    int R, S, stride, pad;
+    int cblocks, cpad;
+    int OW, OH, N, F, fpad_used;
+    int TW, TH, TN, log_tw, log_th;
+    int tiles_w, tiles_h, tiles_n, tiles_f, num_tiles;
+    int act, out_kind;
+    float inv_sy;
+    const float2* mb;  // [fpad] {x_scale * w_scale[f], bias[f]}
+    void* out;
+    long long out_pixel_stride;  // bytes between pixels of an 8-bit NHWC output
+    int* status;
+};
+
+struct ln_conv_umma_plan {
+    ln_conv_umma_params p;
+    float2* mb = nullptr;
+    size_t smem = 0;
+    int grid = 0;
+    int kind = LN_KIND_I8;
+};
+
+// Geometry of one convolution as the planners see it.
+struct ln_conv_geom {
+    int kind = LN_KIND_I8;
+    const void* x = nullptr;      // NHWC 8-bit input view
+    long long x_pixel_stride = 0; // bytes
+    int N = 0, H = 0, W = 0, C = 0, cpad = 0;
+    const void* w = nullptr;      // [fpad][k][k][cpad]
+    int F = 0, fpad = 0, k = 1, stride = 1, pad = 0;
+    int OH = 0, OW = 0;
+    int act = 0, out_kind = 0;
+    float inv_sy = 1.0f;
+    void* out = nullptr;
+    long long out_pixel_stride = 0;
+};
+
+inline int ln_conv_choose_bn(int64_t F) {
+    int bn = 32;
+    int64_t best = -1;
+    const int cand[4] = {32, 64, 128, 256};
+    for (int c : cand) {
+        int64_t fp = ln_round_up(F, c);
+        if (best < 0 || fp <= best) { best = fp; bn = c; }
+    }
+    return bn;
+}
+
+bool ln_conv_umma_supported(int64_t channels_padded, int64_t k, int64_t stride_x, int64_t stride_y, int64_t dilation, int64_t groups,
+                            int64_t in_w, int64_t in_h);
+// plan->mb must point at device storage for fpad float2 before the build.
+int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_geom& g);
+int ln_conv_umma_make_mb(ln_ctx* ctx, const float* wscale_dev, const float* bias_dev, float x_scale, int F, int fpad, float2* mb_dev);
+int ln_conv_umma_launch(ln_ctx* ctx, const ln_conv_umma_plan* plan);
+
+// CUDA-core int8 / FP8 convolution for shapes the tensor-core kernel does not take (any C, stride, padding).
+// Weights in the reference's [F][C][k][k] order.
+int ln_conv_simt_launch(ln_ctx* ctx, const ln_conv_geom& g, const void* w_oihw, const float2* mb);
+
+// First layer: f32 NCHW image in, quantise on the fly, 8-bit NHWC out (C <= 4).
+int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx, int N, int C, int H, int W, const void* w_oihw,
+                        const float2* mb, int F, int k, int stride, int pad, int OH, int OW, int act, float inv_sy, void* out,
+                        long long out_pixel_stride);
+
+// Reads the device status word; returns LN_OK or LN_ERR_TIMEOUT (and clears the word).
+int ln_check_status(ln_ctx* ctx, const char* where);

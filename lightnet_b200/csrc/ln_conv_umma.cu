@@ -1,0 +1,479 @@
+// Implicit-GEMM convolution on the Blackwell tensor cores (tcgen05.mma, accumulators in TMEM,
+// operands staged by TMA), int8 (s8 x s8 -> s32) and FP8 E4M3 (-> f32), with the
+// requantise / bias / activation epilogue fused.
+//
+// GEMM view of runtime/forward_layers.rs:646-695:
+//     D[pixel, filter] = sum over (ky, kx, c) of X[pixel shifted by tap (ky,kx), c] * Wt[filter, (ky,kx,c)]
+// Activations are NHWC 8-bit; weights are [filters][ky][kx][c].  One CTA tile is 128 output pixels
+// (a TW x TH x TN box of the output, TW*TH*TN = 128) by BN filters.  For every tap and every block of
+// BK channels the producer issues two TMA loads: the input box shifted by the tap (out-of-image taps
+// are zero-filled by the TMA unit, which is the reference's "skip taps outside the image") and the
+// matching weight slab.  Stride-2 convolutions use one tensor map per input parity class so that the
+// strided gather is again a dense box.  Every CTA fetches its own operands.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 = epilogue.
+// The accumulator is double buffered in TMEM so the epilogue of tile t overlaps the main loop of t+1.
+// Every mbarrier wait is bounded: when it gives up it raises a status word the host reads, and all
+// roles leave their loops, TMEM is released and the kernel returns.
+#include <cuda_fp8.h>
+
+#include "ln_conv_plan.h"
+
+namespace {
+
+constexpr int kMaxStages = 8;
+constexpr uint32_t kWaitLimit = 1u << 23;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the wait was abandoned (own limit reached, or another role
+// already raised the CTA's abort flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(status, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(bar), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if (KIND == LN_KIND_I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives the columns of TMEM lane (base lane + i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are BK bytes wide and swizzled
+// with a BK-byte pattern (BK in {32, 64, 128}); groups of 8 rows are 8*BK bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int bk) {
+    const uint64_t layout = bk == 128 ? 2ull : (bk == 64 ? 4ull : 6ull);
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address
+    d |= 1ull << 16;                                   // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)((8u * (uint32_t)bk) >> 4) << 32;   // stride byte offset between 8-row groups
+    d |= 1ull << 46;                                   // descriptor version
+    d |= layout << 61;
+    return d;
+}
+
+template <int KIND, int ACT, bool EXACT>
+__global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant__ ln_conv_umma_params p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int bk = p.bk, bn = p.bn, stages = p.stages;
+    const uint32_t a_bytes = 128u * bk, b_bytes = (uint32_t)bn * bk, stage_bytes = a_bytes + b_bytes;
+    const uint32_t bar_base = smem_base + (uint32_t)stages * stage_bytes;
+    // barrier block: full[8] empty[8] tfull[2] tempty[2] | tmem slot | abort flag
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
+    uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(generic_base + (bar_base - smem_base) + 8u * (2 * kMaxStages + 4));
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = 2u * bn;  // 64 .. 512, a power of two
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                     "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int kblocks = p.R * p.S * p.cblocks;
+    const int tiles_per_n = p.tiles_f * p.tiles_w * p.tiles_h;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                const int tf = tile % p.tiles_f;
+                const int tw = (tile / p.tiles_f) % p.tiles_w;
+                const int th = (tile / (p.tiles_f * p.tiles_w)) % p.tiles_h;
+                const int tn = tile / tiles_per_n;
+                const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
+                    const int r = tap / p.S, s = tap - r * p.S;
+                    int ty = r - p.pad, tx = s - p.pad, map = 0;
+                    if (p.stride == 2) {
+                        const int py = ty & 1, px = tx & 1;  // parity class of the tap (two's complement & 1 is non-negative)
+                        ty = (ty - py) >> 1;
+                        tx = (tx - px) >> 1;
+                        map = py * 2 + px;
+                    }
+                    if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT))) break;
+                    const uint32_t sa = smem_base + (uint32_t)stage * stage_bytes;
+                    mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+                    tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(stage));
+                    tma_load_2d(sa + a_bytes, &p.tmB, tap * p.cpad + c0, f0, full_bar(stage));
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((uint32_t)(bn >> 3) << 17) |
+                                   ((128u >> 4) << 24);
+            int stage = 0;
+            uint32_t phase = 0;
+            int t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
+                const int buf = t & 1;
+                const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+                if (!(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT))) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + (uint32_t)stage * stage_bytes;
+                    const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(sa + a_bytes, bk);
+                    for (int k = 0; k < bk / 32; ++k)  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
+                        tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
+                    tc_commit(empty_bar(stage));  // arrives when the MMAs above have finished reading this stage
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(tfull_bar(buf));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
+        const int row = quad * 32 + lane;
+        const int pw = row & (p.TW - 1), ph = (row >> p.log_tw) & (p.TH - 1), pn = row >> (p.log_tw + p.log_th);
+        int t = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
+            const int tf = tile % p.tiles_f;
+            const int tw = (tile / p.tiles_f) % p.tiles_w;
+            const int th = (tile / (p.tiles_f * p.tiles_w)) % p.tiles_h;
+            const int tn = tile / tiles_per_n;
+            const int ow = tw * p.TW + pw, oh = th * p.TH + ph, n = tn * p.TN + pn, f0 = tf * bn;
+            const bool valid = ow < p.OW && oh < p.OH && n < p.N;
+            const int buf = t & 1;
+            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            if (!(ok = mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT))) break;
+            tc_fence_after();
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * bn);
+            const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
+            for (int c0 = 0; c0 < bn; c0 += 32) {
+                uint32_t acc[32];
+                tmem_ld_32x32(taddr0 + (uint32_t)c0, acc);
+                if (!valid || f0 + c0 >= p.fpad_used) continue;
+                if (p.out_kind == LN_OUT_ACC) {
+                    int32_t* o = (int32_t*)p.out;  // NCHW, raw accumulator bits (int32 or f32)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int f = f0 + c0 + j;
+                        if (f < p.F) o[(((int64_t)n * p.F + f) * p.OH + oh) * p.OW + ow] = (int32_t)acc[j];
+                    }
+                    continue;
+                }
+                float a[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float2 mb = __ldg(&p.mb[f0 + c0 + j]);
+                    const float x = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[j]) : __uint_as_float(acc[j]);
+                    a[j] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x, mb.x, mb.y));
+                }
+                if (p.out_kind == LN_OUT_F32) {
+                    float* o = (float*)p.out;  // NCHW
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int f = f0 + c0 + j;
+                        if (f < p.F) o[(((int64_t)n * p.F + f) * p.OH + oh) * p.OW + ow] = a[j];
+                    }
+                } else {
+                    uint32_t packed[8];
+                    if (KIND == LN_KIND_I8) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            uint32_t v = 0;
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const int f = f0 + c0 + 4 * j + b;
+                                const int q = f < p.F ? ln_quant_i8(a[4 * j + b], p.inv_sy) : 0;
+                                v |= ((uint32_t)q & 0xFFu) << (8 * b);
+                            }
+                            packed[j] = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float v0 = a[4 * j] * p.inv_sy, v1 = a[4 * j + 1] * p.inv_sy, v2 = a[4 * j + 2] * p.inv_sy, v3 = a[4 * j + 3] * p.inv_sy;
+                            const int f = f0 + c0 + 4 * j;
+                            if (f >= p.F) v0 = 0.0f;
+                            if (f + 1 >= p.F) v1 = 0.0f;
+                            if (f + 2 >= p.F) v2 = 0.0f;
+                            if (f + 3 >= p.F) v3 = 0.0f;
+                            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v0, v1), __NV_SATFINITE, __NV_E4M3);
+                            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v2, v3), __NV_SATFINITE, __NV_E4M3);
+                            packed[j] = lo | (hi << 16);
+                        }
+                    }
+                    uint4* o = (uint4*)((uint8_t*)p.out + pix * p.out_pixel_stride + f0 + c0);
+                    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && warp == 0 && lane == 0) {
+        // a wait was abandoned: give copies that may still be in flight time to land before the CTA's
+        // shared memory is handed to another CTA
+        for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+template <int KIND, bool EXACT>
+cudaError_t launch_act(const ln_conv_umma_params& p, int grid, size_t smem, cudaStream_t stream) {
+#define LN_LAUNCH_ACT(A)                                                                                             \
+    case A: {                                                                                                        \
+        auto k = conv_umma_kernel<KIND, A, (A == LN_ACT_MISH || A == LN_ACT_SWISH || A == LN_ACT_LOGISTIC) && EXACT>; \
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+        if (e != cudaSuccess) return e;                                                                              \
+        k<<<grid, 192, smem, stream>>>(p);                                                                           \
+        return cudaGetLastError();                                                                                   \
+    }
+    switch (p.act) {
+        LN_LAUNCH_ACT(LN_ACT_LINEAR)
+        LN_LAUNCH_ACT(LN_ACT_LOGISTIC)
+        LN_LAUNCH_ACT(LN_ACT_LEAKY)
+        LN_LAUNCH_ACT(LN_ACT_MISH)
+        LN_LAUNCH_ACT(LN_ACT_SWISH)
+        LN_LAUNCH_ACT(LN_ACT_RELU)
+    }
+#undef LN_LAUNCH_ACT
+    return cudaErrorInvalidValue;
+}
+
+__global__ void make_mb_kernel(const float* __restrict__ wscale, const float* __restrict__ bias, float x_scale, int F, int fpad,
+                               float2* __restrict__ mb) {
+    int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= fpad) return;
+    mb[f] = f < F ? make_float2(__fmul_rn(x_scale, wscale[f]), bias[f]) : make_float2(0.0f, 0.0f);
+}
+
+int ilog2(int v) {
+    int l = 0;
+    while ((1 << l) < v) ++l;
+    return l;
+}
+
+}  // namespace
+
+bool ln_conv_umma_supported(int64_t channels_padded, int64_t k, int64_t stride_x, int64_t stride_y, int64_t dilation, int64_t groups,
+                            int64_t in_w, int64_t in_h) {
+    if (groups != 1 || dilation != 1) return false;
+    if (stride_x != stride_y || (stride_x != 1 && stride_x != 2)) return false;
+    if (channels_padded % 32 != 0 || k < 1 || k > 7) return false;
+    (void)in_w;
+    (void)in_h;
+    return true;
+}
+
+// Picks the output box: TW*TH*TN = 128, all powers of two, minimising the number of tiles (ties: wider in w).
+static void choose_box(int OW, int OH, int N, int* TW, int* TH, int* TN) {
+    int64_t best = -1;
+    for (int lw = 0; lw <= 7; ++lw)
+        for (int lh = 0; lw + lh <= 7; ++lh) {
+            int tw = 1 << lw, th = 1 << lh, tn = 128 >> (lw + lh);
+            int64_t tiles = (int64_t)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
+            if (best < 0 || tiles < best || (tiles == best && tw > *TW)) {
+                best = tiles;
+                *TW = tw; *TH = th; *TN = tn;
+            }
+        }
+}
+
+int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_geom& g) {
+    ln_conv_umma_params& p = plan->p;
+    memset(&p, 0, sizeof p);
+    if (!ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H))
+        return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported geometry (cpad %d k %d stride %d)", g.cpad, g.k, g.stride);
+    if (((uintptr_t)g.x & 15) || (g.x_pixel_stride & 15) || ((uintptr_t)g.w & 15))
+        return ln_fail(ctx, LN_ERR_ARG, "tensor-core convolution: operands must be 16-byte aligned with 16-byte pixel strides");
+    if (g.out_kind == LN_OUT_Q && ((((uintptr_t)g.out) & 15) || (g.out_pixel_stride & 15)))
+        return ln_fail(ctx, LN_ERR_ARG, "tensor-core convolution: 8-bit output must be 16-byte aligned");
+    const int bk = g.cpad % 128 == 0 ? 128 : (g.cpad % 64 == 0 ? 64 : 32);
+    const int bn = ln_conv_choose_bn(g.F);  // filter tile: least padding, ties to the larger tile
+    if (g.fpad % bn != 0) return ln_fail(ctx, LN_ERR_ARG, "tensor-core convolution: weights are padded to %d filters, tile needs a multiple of %d", g.fpad, bn);
+    p.bk = bk; p.bn = bn;
+    p.R = g.k; p.S = g.k; p.stride = g.stride; p.pad = g.pad;
+    p.cblocks = g.cpad / bk; p.cpad = g.cpad;
+    p.OW = g.OW; p.OH = g.OH; p.N = g.N; p.F = g.F;
+    p.fpad_used = (int)ln_round_up(g.F, 32);
+    choose_box(g.OW, g.OH, g.N, &p.TW, &p.TH, &p.TN);
+    p.log_tw = ilog2(p.TW); p.log_th = ilog2(p.TH);
+    p.tiles_w = (g.OW + p.TW - 1) / p.TW;
+    p.tiles_h = (g.OH + p.TH - 1) / p.TH;
+    p.tiles_n = (g.N + p.TN - 1) / p.TN;
+    p.tiles_f = (int)(ln_round_up(g.F, bn) / bn);
+    p.num_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_f;
+    p.act = g.act; p.inv_sy = g.inv_sy; p.out_kind = g.out_kind;
+    p.out = g.out; p.out_pixel_stride = g.out_pixel_stride;
+    p.status = ctx->d_status;
+    p.mb = plan->mb;
+
+    const uint32_t stage_bytes = (uint32_t)(128 + bn) * bk;
+    int stages = (int)((200 * 1024) / stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
+    p.stages = stages;
+    plan->smem = (size_t)stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
+    plan->kind = g.kind;
+
+    const CUtensorMapSwizzle swz = bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    const int nmaps = g.stride == 2 ? 4 : 1;
+    for (int m = 0; m < nmaps; ++m) {
+        const int py = m >> 1, px = m & 1;
+        // sub-lattice of input pixels (y, x) with y % stride == py, x % stride == px
+        int64_t Wm = (g.W - px + g.stride - 1) / g.stride, Hm = (g.H - py + g.stride - 1) / g.stride;
+        if (Wm < 1) Wm = 1;
+        if (Hm < 1) Hm = 1;
+        cuuint64_t dims[4] = {(cuuint64_t)g.cpad, (cuuint64_t)Wm, (cuuint64_t)Hm, (cuuint64_t)g.N};
+        cuuint64_t strides[3] = {(cuuint64_t)g.stride * g.x_pixel_stride, (cuuint64_t)g.stride * g.W * g.x_pixel_stride,
+                                 (cuuint64_t)g.H * g.W * g.x_pixel_stride};
+        cuuint32_t box[4] = {(cuuint32_t)bk, (cuuint32_t)p.TW, (cuuint32_t)p.TH, (cuuint32_t)p.TN};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        void* base = (uint8_t*)g.x + ((int64_t)py * g.W + px) * g.x_pixel_stride;
+        CUresult r = ctx->encode_tiled(&p.tmA[m], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base, dims, strides, box, estr,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return ln_fail(ctx, LN_ERR_CUDA, "cuTensorMapEncodeTiled(activations, map %d) failed with %d", m, (int)r);
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)g.k * g.k * g.cpad, (cuuint64_t)g.fpad};
+        cuuint64_t strides[1] = {(cuuint64_t)g.k * g.k * g.cpad};
+        cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)bn};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = ctx->encode_tiled(&p.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)g.w, dims, strides, box, estr,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return ln_fail(ctx, LN_ERR_CUDA, "cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
+    }
+    return LN_OK;
+}
+
+int ln_conv_umma_make_mb(ln_ctx* ctx, const float* wscale_dev, const float* bias_dev, float x_scale, int F, int fpad, float2* mb_dev) {
+    make_mb_kernel<<<(fpad + 127) / 128, 128, 0, ctx->stream>>>(wscale_dev, bias_dev, x_scale, F, fpad, mb_dev);
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+int ln_conv_umma_launch(ln_ctx* ctx, const ln_conv_umma_plan* plan) {
+    cudaError_t e;
+    const bool exact = ctx->exact_epilogue;
+    if (plan->kind == LN_KIND_I8)
+        e = exact ? launch_act<LN_KIND_I8, true>(plan->p, plan->grid, plan->smem, ctx->stream)
+                  : launch_act<LN_KIND_I8, false>(plan->p, plan->grid, plan->smem, ctx->stream);
+    else
+        e = exact ? launch_act<LN_KIND_F8, true>(plan->p, plan->grid, plan->smem, ctx->stream)
+                  : launch_act<LN_KIND_F8, false>(plan->p, plan->grid, plan->smem, ctx->stream);
+    ctx->launches++;
+    if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "tensor-core convolution launch: %s", cudaGetErrorString(e));
+    return LN_OK;
+}

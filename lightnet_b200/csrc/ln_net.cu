@@ -1,0 +1,1049 @@
+// Whole-network executor: the host side above the operators.  Mirrors the reference's
+// GpuExecutableNetwork (lightnet-runtime/src/runtime/gpu_types.rs:220): build from a Darknet cfg
+// (lightnet-model/src/cfg.rs:109, model.rs:3079), load Darknet weights (runtime/weights_io.rs:94),
+// fold batch norm (weights_io.rs:32-92), walk the layers (gpu_forward_compact.rs:8), keep the
+// convolution in front of a detection head at high precision (runtime/types.rs:146-170), and hand
+// the heads to the device decode + NMS.
+//
+// f32 precision issues exactly the operator sequence of forward_compact through the f32 C ABI.
+// 8-bit precisions run from a static plan: every layer output has a fixed home in device memory
+// (sized for one micro-batch), multi-source routes are zero-copy where the producer can write into
+// the concatenation buffer directly, and all tensor maps are built once.
+#include <algorithm>
+#include <cctype>
+#include <cmath>
+#include <fstream>
+#include <memory>
+#include <sstream>
+
+#include "ln_conv_plan.h"
+
+int ln_q_maxpool_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int OH, int OW,
+                        int size, int sx, int sy, int padding);
+int ln_q_upsample_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int stride);
+int ln_q_copy_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys, int64_t pixels, int C);
+int ln_q_shortcut_launch(ln_ctx* ctx, int kind, const void* a, int64_t as, float sa, const void* b, int64_t bs, float sb, void* y, int64_t ys,
+                         int64_t pixels, int C, int act, float inv_sy);
+int ln_q_quantize_launch(ln_ctx* ctx, int kind, const float* x, void* y, int64_t N, int C, int H, int W, int64_t cstride, float inv_s);
+
+namespace {
+
+enum Kind { K_CONV = 0, K_MAXPOOL = 1, K_ROUTE = 2, K_SHORTCUT = 3, K_UPSAMPLE = 4, K_YOLO = 5 };
+
+struct Shape4 { int w = 0, h = 0, c = 0, b = 0; };
+
+struct QView {  // where a layer output lives in the 8-bit plan
+    uint8_t* ptr = nullptr;
+    int64_t cstride = 0;
+    int c = 0, h = 0, w = 0;
+    int buffer = -1;  // owning buffer index
+};
+
+struct NLayer {
+    int kind = K_CONV;
+    Shape4 in, out;
+    int filters = 1, size = 1, stride_x = 1, stride_y = 1, dilation = 1, padding = 0, groups = 1;
+    bool bn = false;
+    int act = LN_ACT_LOGISTIC;
+    std::vector<int> sources;
+    int route_groups = 1, route_group_id = 0;
+    int up_stride = 2;
+    float up_scale = 1.0f;
+    bool up_reverse = false;
+    int classes = 20, num = 1;
+    std::vector<int> mask;
+    std::vector<float> anchors;
+    float scale_x_y = 1.0f;
+    bool new_coords = false;
+    // host parameters (lightnet-layers/src/params.rs:7-26)
+    std::vector<float> biases, scales, mean, var, weights;
+    // device parameters
+    ln_tensor* w_f32 = nullptr;  // BN-folded [F, C/g, k, k]
+    ln_tensor* b_f32 = nullptr;  // folded bias [F]
+    ln_conv_weights* wq = nullptr;
+};
+
+struct QStep {
+    int layer = -1;
+    int op = 0;  // 0 umma conv, 1 simt conv, 2 stem conv, 3 maxpool, 4 upsample, 5 copy, 6 shortcut, 7 quantize input
+    ln_conv_umma_plan umma;
+    ln_conv_geom geom;
+    float2* mb = nullptr;
+    bool head = false;          // output is an f32 head: pointer advances per micro-batch
+    int head_index = -1;
+    // glue
+    const uint8_t* x = nullptr; int64_t xs = 0;
+    const uint8_t* x2 = nullptr; int64_t xs2 = 0;
+    uint8_t* y = nullptr; int64_t ys = 0;
+    float sa = 1, sb = 1, inv_sy = 1;
+    int C = 0, H = 0, W = 0, OH = 0, OW = 0;
+};
+
+struct Section {
+    std::string name;
+    int line = 0;
+    std::vector<std::pair<std::string, std::string>> kv;
+    const std::string* find(const std::string& k) const {
+        const std::string* r = nullptr;
+        for (auto& e : kv) if (e.first == k) r = &e.second;  // last value wins (cfg.rs:155-157)
+        return r;
+    }
+};
+
+std::string trim(const std::string& s) {
+    size_t a = 0, b = s.size();
+    while (a < b && std::isspace((unsigned char)s[a])) ++a;
+    while (b > a && std::isspace((unsigned char)s[b - 1])) --b;
+    return s.substr(a, b - a);
+}
+std::string lower(std::string s) {
+    for (auto& c : s) c = (char)std::tolower((unsigned char)c);
+    return s;
+}
+
+struct ParseError { std::string msg; };
+
+long long get_i64(const Section& s, const char* k, long long d) {
+    const std::string* v = s.find(k);
+    if (!v) return d;
+    try {
+        size_t pos = 0;
+        long long r = std::stoll(*v, &pos);
+        if (pos != v->size()) throw 0;
+        return r;
+    } catch (...) { throw ParseError{"invalid integer \"" + *v + "\" for key " + k + " in [" + s.name + "] at line " + std::to_string(s.line)}; }
+}
+int get_usize(const Section& s, const char* k, int d) {
+    long long v = get_i64(s, k, d);
+    if (v < 0) throw ParseError{std::string("negative value for key ") + k + " in [" + s.name + "] at line " + std::to_string(s.line)};
+    return (int)v;
+}
+float get_f32(const Section& s, const char* k, float d) {
+    const std::string* v = s.find(k);
+    if (!v) return d;
+    try { return std::stof(*v); } catch (...) { throw ParseError{"invalid float \"" + *v + "\" for key " + k}; }
+}
+std::string get_str(const Section& s, const char* k, const char* d) {
+    const std::string* v = s.find(k);
+    return v ? *v : std::string(d);
+}
+template <class T>
+std::vector<T> get_list(const Section& s, const char* k) {
+    std::vector<T> out;
+    const std::string* v = s.find(k);
+    if (!v) return out;
+    std::string item;
+    auto flush = [&]() {
+        if (item.empty()) return;
+        try {
+            if (std::is_floating_point<T>::value) out.push_back((T)std::stof(item));
+            else out.push_back((T)std::stoll(item));
+        } catch (...) { throw ParseError{"failed to parse list item \"" + item + "\" for key \"" + k + "\" in [" + s.name + "] at line " + std::to_string(s.line)}; }
+        item.clear();
+    };
+    for (char ch : *v) {
+        if (ch == ',' || std::isspace((unsigned char)ch)) flush();
+        else item.push_back(ch);
+    }
+    flush();
+    return out;
+}
+
+// ConfigFile::parse_str (lightnet-model/src/cfg.rs:109-171)
+std::vector<Section> parse_sections(const std::string& text) {
+    std::vector<Section> secs;
+    std::istringstream in(text);
+    std::string raw;
+    int ln = 0;
+    while (std::getline(in, raw)) {
+        ++ln;
+        size_t p = raw.find('#');
+        if (p != std::string::npos) raw.resize(p);
+        p = raw.find(';');
+        if (p != std::string::npos) raw.resize(p);
+        std::string line = trim(raw);
+        if (line.empty()) continue;
+        if (line.front() == '[' && line.back() == ']') {
+            Section s;
+            s.name = lower(trim(line.substr(1, line.size() - 2)));
+            s.line = ln;
+            secs.push_back(std::move(s));
+            continue;
+        }
+        size_t eq = line.find('=');
+        if (eq == std::string::npos) throw ParseError{"invalid config line " + std::to_string(ln) + ": expected key=value"};
+        if (secs.empty()) throw ParseError{"encountered key/value before any section at line " + std::to_string(ln)};
+        secs.back().kv.emplace_back(lower(trim(line.substr(0, eq))), trim(line.substr(eq + 1)));
+    }
+    if (secs.empty()) throw ParseError{"no Darknet sections found"};
+    return secs;
+}
+
+int parse_activation(const std::string& s) {
+    std::string a = lower(s);
+    if (a == "linear") return LN_ACT_LINEAR;
+    if (a == "logistic") return LN_ACT_LOGISTIC;
+    if (a == "leaky") return LN_ACT_LEAKY;
+    if (a == "mish") return LN_ACT_MISH;
+    if (a == "swish") return LN_ACT_SWISH;
+    if (a == "relu") return LN_ACT_RELU;
+    throw ParseError{"activation \"" + s + "\" is not on the detector path"};
+}
+
+int conv_dim(int in, int pad, int size, int stride) {  // model.rs:6472
+    int v = in + 2 * pad - size;
+    if (v < 0) v = 0;
+    return v / std::max(stride, 1) + 1;
+}
+int pool_dim(int in, int pad, int size, int stride) {  // model.rs:8854
+    int v = in + pad - size;
+    if (v < 0) v = 0;
+    return v / std::max(stride, 1) + 1;
+}
+int resolve_relative(int layer_index, long long raw) {  // model.rs:6208
+    long long a = raw < 0 ? layer_index + raw : raw;
+    if (a < 0 || a >= layer_index) throw ParseError{"invalid route reference " + std::to_string(raw) + " at layer " + std::to_string(layer_index)};
+    return (int)a;
+}
+
+__global__ void amax_f32_kernel(const float* __restrict__ x, int64_t n, unsigned* __restrict__ out) {
+    float m = 0.0f;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float v = fabsf(x[i]);
+        if (isfinite(v)) m = fmaxf(m, v);
+    }
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(m));  // non-negative floats order like their bits
+}
+
+}  // namespace
+
+struct ln_net {
+    ln_ctx* ctx = nullptr;
+    int precision = LN_F32;
+    int width = 0, height = 0, channels = 0, batch = 1;
+    std::vector<NLayer> layers;
+    bool weights_loaded = false;
+    std::vector<float> scale;  // [0] input, [1+i] layer i output
+    bool scales_set = false;
+    int micro_batch = 0;
+    // results of the last forward
+    std::vector<ln_tensor*> out;       // f32 path: every layer output; 8-bit path: views (whole-batch runs only)
+    std::vector<int> head_layers;      // indices of [yolo] layers
+    std::vector<ln_tensor*> heads;     // f32 [batch, A*(5+classes), gh, gw]
+    // 8-bit plan
+    bool plan_valid = false;
+    int plan_mb = 0;
+    std::vector<QStep> steps;
+    std::vector<std::pair<void*, size_t>> buffers;
+    std::vector<QView> views;
+    ln_tensor* input_dev = nullptr;    // staging for host inputs
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    float times_ms[2] = {0, 0};
+};
+
+namespace {
+
+void build_layers(ln_net* net, const std::string& cfg, int batch_override) {
+    auto secs = parse_sections(cfg);
+    const Section& n = secs[0];
+    if (n.name != "net" && n.name != "network") throw ParseError{"the first section must be [net]"};
+    net->width = get_usize(n, "width", 0);
+    net->height = get_usize(n, "height", 0);
+    net->channels = get_usize(n, "channels", 0);
+    int subdiv = std::max(get_usize(n, "subdivisions", 1), 1), ts = std::max(get_usize(n, "time_steps", 1), 1);
+    net->batch = get_usize(n, "batch", 1) / subdiv * ts;  // model.rs:247-249
+    if (batch_override > 0) net->batch = batch_override;  // model.rs:3256
+    if (net->width < 1 || net->height < 1 || net->channels < 1 || net->batch < 1) throw ParseError{"[net] needs positive width, height, channels and batch"};
+    Shape4 cur;
+    cur.w = net->width; cur.h = net->height; cur.c = net->channels; cur.b = net->batch;
+    for (size_t si = 1; si < secs.size(); ++si) {
+        const Section& s = secs[si];
+        const int li = (int)net->layers.size();
+        NLayer L;
+        L.in = cur;
+        if (s.name == "conv" || s.name == "convolutional") {  // model.rs:4088-4144
+            L.kind = K_CONV;
+            int stride = get_usize(s, "stride", 1);
+            L.size = get_usize(s, "size", 1);
+            L.padding = get_i64(s, "pad", 0) != 0 ? L.size / 2 : get_usize(s, "padding", 0);
+            L.filters = get_usize(s, "filters", 1);
+            L.groups = get_usize(s, "groups", 1);
+            L.stride_x = get_usize(s, "stride_x", stride);
+            L.stride_y = get_usize(s, "stride_y", stride);
+            L.dilation = get_usize(s, "dilation", 1);
+            L.bn = get_i64(s, "batch_normalize", 0) != 0;
+            L.act = parse_activation(get_str(s, "activation", "logistic"));
+            if (L.groups < 1 || L.filters % L.groups || cur.c % L.groups) throw ParseError{"convolution groups do not divide filters / channels at layer " + std::to_string(li)};
+            L.out.w = conv_dim(cur.w, L.padding, L.size, L.stride_x);
+            L.out.h = conv_dim(cur.h, L.padding, L.size, L.stride_y);
+            L.out.c = L.filters;
+            L.out.b = cur.b;
+            L.biases.assign(L.filters, 0.0f);
+            L.weights.assign((size_t)L.filters * (cur.c / L.groups) * L.size * L.size, 0.0f);
+            if (L.bn) { L.scales.assign(L.filters, 1.0f); L.mean.assign(L.filters, 0.0f); L.var.assign(L.filters, 1.0f); }
+        } else if (s.name == "max" || s.name == "maxpool") {  // model.rs:4165-4183
+            L.kind = K_MAXPOOL;
+            int stride = get_usize(s, "stride", 1);
+            L.size = get_usize(s, "size", stride);
+            L.stride_x = get_usize(s, "stride_x", stride);
+            L.stride_y = get_usize(s, "stride_y", stride);
+            L.padding = get_usize(s, "padding", L.size > 0 ? L.size - 1 : 0);
+            if (get_i64(s, "maxpool_depth", 0) != 0) throw ParseError{"maxpool_depth is not on the detector path"};
+            L.out.w = pool_dim(cur.w, L.padding, L.size, L.stride_x);
+            L.out.h = pool_dim(cur.h, L.padding, L.size, L.stride_y);
+            L.out.c = cur.c; L.out.b = cur.b;
+        } else if (s.name == "route") {  // model.rs:4225-4229, :6138
+            L.kind = K_ROUTE;
+            auto raw = get_list<long long>(s, "layers");
+            if (raw.empty()) throw ParseError{"route layer #" + std::to_string(li) + " must list at least one source layer"};
+            L.route_groups = std::max(get_usize(s, "groups", 1), 1);
+            L.route_group_id = get_usize(s, "group_id", 0);
+            int ch = 0;
+            Shape4 first;
+            for (size_t k = 0; k < raw.size(); ++k) {
+                int src = resolve_relative(li, raw[k]);
+                L.sources.push_back(src);
+                const Shape4& sh = net->layers[src].out;
+                if (k == 0) first = sh;
+                else if (sh.w != first.w || sh.h != first.h) throw ParseError{"route layer #" + std::to_string(li) + " mixes incompatible spatial shapes"};
+                ch += sh.c;
+            }
+            L.out.w = first.w; L.out.h = first.h; L.out.c = ch / L.route_groups; L.out.b = cur.b;
+        } else if (s.name == "shortcut") {  // model.rs:4230-4237
+            L.kind = K_SHORTCUT;
+            for (auto r : get_list<long long>(s, "from")) L.sources.push_back(resolve_relative(li, r));
+            L.act = parse_activation(get_str(s, "activation", "linear"));
+            L.out = cur;
+        } else if (s.name == "upsample") {  // model.rs:4263-4270, :5711-5733
+            L.kind = K_UPSAMPLE;
+            long long st = get_i64(s, "stride", 2);
+            L.up_reverse = st < 0;
+            L.up_stride = (int)std::llabs(st);
+            if (L.up_stride == 0) throw ParseError{"upsample layer #" + std::to_string(li) + " cannot use stride=0"};
+            L.up_scale = get_f32(s, "scale", 1.0f);
+            L.out = cur;
+            if (L.up_reverse) { L.out.w = cur.w / L.up_stride; L.out.h = cur.h / L.up_stride; }
+            else { L.out.w = cur.w * L.up_stride; L.out.h = cur.h * L.up_stride; }
+        } else if (s.name == "yolo") {  // model.rs:4271-4344
+            L.kind = K_YOLO;
+            L.mask = get_list<int>(s, "mask");
+            L.num = get_usize(s, "num", L.mask.empty() ? 1 : (int)L.mask.size());
+            if (L.mask.empty()) for (int k = 0; k < L.num; ++k) L.mask.push_back(k);
+            L.classes = get_usize(s, "classes", 20);
+            L.anchors = get_list<float>(s, "anchors");
+            L.scale_x_y = get_f32(s, "scale_x_y", 1.0f);
+            L.new_coords = get_i64(s, "new_coords", 0) != 0;
+            for (int m : L.mask)  // detection_geometry.rs:80-95 anchor_pair
+                if ((size_t)(2 * m + 1) >= L.anchors.size()) throw ParseError{"missing anchor for YOLO mask index " + std::to_string(m)};
+            if (L.mask.size() > 8) throw ParseError{"more than 8 anchors per head"};
+            L.out = cur;
+            net->head_layers.push_back(li);
+        } else {
+            throw ParseError{"layer [" + s.name + "] at line " + std::to_string(s.line) + " is not on the detector path"};
+        }
+        cur = L.out;
+        net->layers.push_back(std::move(L));
+    }
+}
+
+bool feeds_head(const ln_net* net, int i) {  // runtime/types.rs:146-170
+    return net->layers[i].kind == K_CONV && i + 1 < (int)net->layers.size() && net->layers[i + 1].kind == K_YOLO;
+}
+
+void release_outputs(ln_net* net) {
+    for (auto*& t : net->out) { ln_tensor_release(t); t = nullptr; }
+    net->out.clear();
+}
+void release_heads(ln_net* net) {
+    for (auto*& t : net->heads) { ln_tensor_release(t); t = nullptr; }
+    net->heads.clear();
+}
+void release_plan(ln_net* net) {
+    ln_ctx* ctx = net->ctx;
+    for (auto& s : net->steps)
+        if (s.mb) ln_pool_free(ctx, s.mb, (size_t)net->layers[s.layer].wq->fpad * sizeof(float2));
+    net->steps.clear();
+    for (auto& b : net->buffers) ln_pool_free(ctx, b.first, b.second);
+    net->buffers.clear();
+    net->views.clear();
+    net->plan_valid = false;
+}
+
+// ---- f32 forward: the operator sequence of forward_compact (gpu_forward_compact.rs:8-540) --------
+int forward_f32(ln_net* net, const ln_tensor* input, unsigned* amax_dev) {
+    ln_ctx* ctx = net->ctx;
+    release_outputs(net);
+    release_heads(net);
+    const int NL = (int)net->layers.size();
+    net->out.assign(NL, nullptr);
+    auto record_amax = [&](const ln_tensor* t, int slot) {
+        if (!amax_dev) return;
+        int64_t n = t->count();
+        int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)ctx->sm_count * 8);
+        amax_f32_kernel<<<grid, 256, 0, ctx->stream>>>((const float*)t->ptr, n, amax_dev + slot);
+        ctx->launches++;
+    };
+    record_amax(input, 0);
+    for (int i = 0; i < NL; ++i) {
+        NLayer& L = net->layers[i];
+        const ln_tensor* x = i == 0 ? input : net->out[i - 1];
+        const int64_t oshape[4] = {L.out.b, L.out.c, L.out.h, L.out.w};
+        ln_tensor* y = nullptr;
+        int rc = LN_OK;
+        switch (L.kind) {
+            case K_CONV: {  // layers/convolutional/gpu.rs:138-209: conv2d_f32_with_precision + bias_activation_f32
+                ln_tensor* conv = nullptr;
+                rc = ln_conv2d_f32(ctx, x, L.w_f32, oshape, L.in.c, L.in.h, L.in.w, L.filters, L.size, L.stride_x, L.stride_y, L.dilation, L.padding,
+                                   L.groups, &conv);
+                if (rc == LN_OK) rc = ln_bias_activation_f32(ctx, conv, L.b_f32, L.filters, (int64_t)L.out.h * L.out.w, L.act, &y);
+                ln_tensor_release(conv);
+                break;
+            }
+            case K_MAXPOOL:  // layers/pool/gpu.rs:13-42
+                rc = ln_maxpool_f32(ctx, x, oshape, L.in.c, L.in.h, L.in.w, L.size, L.stride_x, L.stride_y, L.padding, &y);
+                break;
+            case K_ROUTE: {  // layers/route/gpu.rs:61-108
+                std::vector<const ln_tensor*> ins;
+                std::vector<int64_t> offs, chans, totals;
+                for (int src : L.sources) {
+                    const ln_tensor* t = net->out[src];
+                    int64_t chunk = t->c / L.route_groups;
+                    ins.push_back(t);
+                    offs.push_back(chunk * L.route_group_id);
+                    chans.push_back(chunk);
+                    totals.push_back(t->c);
+                }
+                rc = ln_route_concat_f32(ctx, ins.data(), (int)ins.size(), offs.data(), chans.data(), totals.data(), oshape, (int64_t)L.out.h * L.out.w, &y);
+                break;
+            }
+            case K_SHORTCUT: {  // layers/shortcut/gpu.rs:153-213: fit? + add per source, then activation
+                ln_tensor* acc = const_cast<ln_tensor*>(x);
+                ln_tensor_retain(acc);
+                for (int src : L.sources) {
+                    const ln_tensor* s = net->out[src];
+                    ln_tensor* fitted = nullptr;
+                    if (s->n != acc->n) { rc = ln_fail(ctx, LN_ERR_SHAPE, "shortcut layer #%d mixes incompatible batch shapes", i); break; }
+                    if (s->count() != acc->count()) {
+                        rc = ln_shortcut_fit_f32(ctx, s, L.out.b, oshape, &fitted);
+                        if (rc) break;
+                        s = fitted;
+                    }
+                    ln_tensor* sum = nullptr;
+                    rc = ln_shortcut_add_f32(ctx, acc, s, &sum);
+                    ln_tensor_release(fitted);
+                    if (rc) break;
+                    ln_tensor_release(acc);
+                    acc = sum;
+                }
+                if (rc == LN_OK) rc = ln_activation_f32(ctx, acc, L.act, &y);
+                ln_tensor_release(acc);
+                break;
+            }
+            case K_UPSAMPLE:  // layers/upsample/gpu.rs:12-33
+                rc = ln_upsample_f32(ctx, x, oshape, L.in.c, L.in.h, L.in.w, L.up_stride, L.up_scale, L.up_reverse ? 1 : 0, &y);
+                break;
+            case K_YOLO:  // gpu_forward_compact.rs:420-429: clone the handle, mark the head
+                y = const_cast<ln_tensor*>(x);
+                ln_tensor_retain(y);
+                net->heads.push_back(y);
+                ln_tensor_retain(y);
+                break;
+        }
+        if (rc) return rc;
+        net->out[i] = y;
+        record_amax(y, i + 1);
+    }
+    return LN_OK;
+}
+
+// ---- per-tensor scales from the calibration amax (tensors joined by route / maxpool / upsample share one)
+void scales_from_amax(ln_net* net, const std::vector<float>& amax, float qmax) {
+    const int T = (int)net->layers.size() + 1;
+    std::vector<int> parent(T);
+    for (int t = 0; t < T; ++t) parent[t] = t;
+    auto find = [&](int a) { while (parent[a] != a) a = parent[a] = parent[parent[a]]; return a; };
+    auto join = [&](int a, int b) { a = find(a); b = find(b); if (a != b) parent[std::max(a, b)] = std::min(a, b); };
+    for (int i = 0; i < T - 1; ++i) {
+        const NLayer& L = net->layers[i];
+        if (L.kind == K_MAXPOOL || L.kind == K_UPSAMPLE || L.kind == K_YOLO) join(i + 1, i);
+        if (L.kind == K_ROUTE) for (int s : L.sources) join(i + 1, s + 1);
+    }
+    std::vector<float> gmax(T, 0.0f);
+    for (int t = 0; t < T; ++t) { int r = find(t); gmax[r] = std::max(gmax[r], amax[t]); }
+    net->scale.assign(T, 1.0f);
+    for (int t = 0; t < T; ++t) {
+        float m = gmax[find(t)];
+        net->scale[t] = (m > 0.0f && std::isfinite(m)) ? m / qmax : 1.0f;
+    }
+    net->scales_set = true;
+}
+
+// ---- 8-bit plan ----------------------------------------------------------------------------------
+int build_plan(ln_net* net, int mb) {
+    ln_ctx* ctx = net->ctx;
+    release_plan(net);
+    const int NL = (int)net->layers.size();
+    const int kind = net->precision == LN_F8 ? LN_KIND_F8 : LN_KIND_I8;
+    if (!net->scales_set) return ln_fail(ctx, LN_ERR_ARG, "8-bit forward needs per-tensor scales: call ln_net_calibrate or ln_net_set_scales first");
+    // 1. support checks
+    for (int i = 0; i < NL; ++i) {
+        const NLayer& L = net->layers[i];
+        if (L.kind == K_CONV && (L.groups != 1 || L.dilation != 1 || L.stride_x != L.stride_y))
+            return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit convolution needs groups=1, dilation=1, stride_x=stride_y", i);
+        if (L.kind == K_UPSAMPLE && (L.up_reverse || L.up_scale != 1.0f)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit up-sample needs scale=1, forward", i);
+        if (L.kind == K_SHORTCUT) {
+            if (L.sources.size() != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit shortcut takes exactly one source", i);
+            const Shape4& s = net->layers[L.sources[0]].out;
+            if (s.w != L.out.w || s.h != L.out.h || s.c != L.out.c) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit shortcut needs same-shape sources", i);
+        }
+        if (L.kind == K_YOLO && (i == 0 || !feeds_head(net, i - 1))) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: [yolo] must follow a convolution", i);
+        if (L.kind == K_ROUTE && L.route_groups > 1 && (L.sources.size() != 1)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: grouped route with several sources", i);
+        if (L.kind != K_CONV && L.kind != K_YOLO && i > 0 && feeds_head(net, i - 1)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d reads a head convolution's f32 output", i);
+        if (L.kind == K_ROUTE || L.kind == K_SHORTCUT)
+            for (int s : L.sources)
+                if (feeds_head(net, s) || net->layers[s].kind == K_YOLO) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d reads a head's f32 output", i);
+    }
+    // 2. homes: alias chains and zero-copy concatenation
+    std::vector<int> alias(NL, -1);        // single-source ungrouped route -> its source
+    std::vector<int> home_buf(NL, -1);     // layer output placed inside another layer's (route) buffer
+    std::vector<int> home_off(NL, 0);
+    auto root_of = [&](int l) { while (alias[l] >= 0) l = alias[l]; return l; };
+    for (int i = 0; i < NL; ++i) {
+        const NLayer& L = net->layers[i];
+        if (L.kind == K_ROUTE && L.sources.size() == 1 && L.route_groups == 1) alias[i] = L.sources[0];
+    }
+    for (int i = 0; i < NL; ++i) {
+        const NLayer& L = net->layers[i];
+        if (L.kind != K_ROUTE || L.sources.size() < 2) continue;
+        int off = 0;
+        for (int s : L.sources) {
+            const int r = root_of(s);
+            const NLayer& P = net->layers[r];
+            const bool producer = (P.kind == K_CONV && !feeds_head(net, r)) || P.kind == K_SHORTCUT || P.kind == K_MAXPOOL || P.kind == K_UPSAMPLE;
+            if (producer && home_buf[r] < 0 && off % 32 == 0 && P.out.c % 32 == 0) { home_buf[r] = i; home_off[r] = off; }
+            off += net->layers[s].out.c;
+        }
+    }
+    // 3. buffers and views
+    net->views.assign(NL, QView());
+    std::vector<int> buffer_of(NL, -1);
+    auto alloc_buffer = [&](int64_t bytes) -> int {
+        void* p = ln_pool_alloc(ctx, (size_t)bytes);
+        if (!p) return -1;
+        cudaMemsetAsync(p, 0, (size_t)bytes, ctx->stream);
+        net->buffers.emplace_back(p, (size_t)bytes);
+        return (int)net->buffers.size() - 1;
+    };
+    for (int i = 0; i < NL; ++i) {  // routes with several sources own a concatenation buffer; allocate those first
+        const NLayer& L = net->layers[i];
+        if (L.kind == K_ROUTE && L.sources.size() >= 2) {
+            int64_t cs = ln_round_up(L.out.c, 32);
+            int b = alloc_buffer((int64_t)mb * L.out.h * L.out.w * cs);
+            if (b < 0) return LN_ERR_CUDA;
+            buffer_of[i] = b;
+            QView v;
+            v.ptr = (uint8_t*)net->buffers[b].first; v.cstride = cs; v.c = L.out.c; v.h = L.out.h; v.w = L.out.w; v.buffer = b;
+            net->views[i] = v;
+        }
+    }
+    for (int i = 0; i < NL; ++i) {
+        const NLayer& L = net->layers[i];
+        QView v;
+        v.c = L.out.c; v.h = L.out.h; v.w = L.out.w;
+        if (L.kind == K_YOLO || feeds_head(net, i)) { net->views[i] = v; continue; }  // f32 heads live elsewhere
+        if (L.kind == K_ROUTE) {
+            if (L.sources.size() >= 2) continue;  // done above
+            if (alias[i] >= 0) { net->views[i] = net->views[root_of(i)]; continue; }
+            // grouped single-source route: a channel slice of the source
+            const QView& sv = net->views[L.sources[0]];
+            const int chunk = net->layers[L.sources[0]].out.c / L.route_groups, start = chunk * L.route_group_id;
+            if (start % 16 == 0) {
+                v = sv; v.c = chunk; v.ptr = sv.ptr + start;
+                net->views[i] = v;
+                continue;
+            }
+            // unaligned slice: gets its own buffer and a copy step (below)
+        }
+        if (home_buf[i] >= 0) {
+            const QView& hv = net->views[home_buf[i]];
+            v.ptr = hv.ptr + home_off[i]; v.cstride = hv.cstride; v.buffer = hv.buffer;
+        } else {
+            int64_t cs = ln_round_up(L.out.c, 32);
+            int b = alloc_buffer((int64_t)mb * L.out.h * L.out.w * cs);
+            if (b < 0) return LN_ERR_CUDA;
+            v.ptr = (uint8_t*)net->buffers[b].first; v.cstride = cs; v.buffer = b;
+        }
+        net->views[i] = v;
+    }
+    // 4. heads
+    release_heads(net);
+    for (int hl : net->head_layers) {
+        const NLayer& L = net->layers[hl];
+        ln_tensor* t = ln_tensor_new(ctx, LN_F32, net->batch, L.out.c, L.out.h, L.out.w);
+        if (!t) return LN_ERR_CUDA;
+        net->heads.push_back(t);
+    }
+    // 5. steps
+    int head_counter = 0;
+    for (int i = 0; i < NL; ++i) {
+        NLayer& L = net->layers[i];
+        const float sx = net->scale[i], sy = net->scale[i + 1];
+        QStep st;
+        st.layer = i;
+        switch (L.kind) {
+            case K_CONV: {
+                const bool head = feeds_head(net, i);
+                st.head = head;
+                if (head) st.head_index = head_counter++;
+                st.mb = (float2*)ln_pool_alloc(ctx, (size_t)L.wq->fpad * sizeof(float2));
+                if (!st.mb) return LN_ERR_CUDA;
+                int rc = ln_conv_umma_make_mb(ctx, L.wq->wscale, (const float*)L.b_f32->ptr, sx, L.filters, (int)L.wq->fpad, st.mb);
+                if (rc) return rc;
+                ln_conv_geom& g = st.geom;
+                g.kind = kind;
+                g.N = mb; g.H = L.in.h; g.W = L.in.w; g.C = L.in.c; g.cpad = (int)L.wq->cpad;
+                g.w = L.wq->w; g.F = L.filters; g.fpad = (int)L.wq->fpad; g.k = L.size; g.stride = L.stride_x; g.pad = L.padding;
+                g.OH = L.out.h; g.OW = L.out.w; g.act = L.act;
+                g.out_kind = head ? LN_OUT_F32 : LN_OUT_Q;
+                g.inv_sy = head ? 1.0f : 1.0f / sy;
+                if (head) { g.out = net->heads[st.head_index]->ptr; g.out_pixel_stride = 0; }
+                else { g.out = net->views[i].ptr; g.out_pixel_stride = net->views[i].cstride; }
+                if (i == 0) {
+                    if (L.in.c > 4) {  // generic first layer: quantise the image, then a normal convolution
+                        QStep q;
+                        q.layer = i; q.op = 7;
+                        int64_t cs = ln_round_up(L.in.c, 32);
+                        int b = alloc_buffer((int64_t)mb * L.in.h * L.in.w * cs);
+                        if (b < 0) return LN_ERR_CUDA;
+                        q.y = (uint8_t*)net->buffers[b].first; q.ys = cs; q.C = L.in.c; q.H = L.in.h; q.W = L.in.w; q.inv_sy = 1.0f / sx;
+                        net->steps.push_back(q);
+                        g.x = q.y; g.x_pixel_stride = cs;
+                    } else {
+                        if (head) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #0 cannot be a head convolution in the 8-bit plan");
+                        st.op = 2;
+                        st.inv_sy = 1.0f / sx;  // input quantiser
+                        net->steps.push_back(st);
+                        break;
+                    }
+                } else {
+                    g.x = net->views[i - 1].ptr; g.x_pixel_stride = net->views[i - 1].cstride;
+                }
+                if (g.x_pixel_stride >= g.cpad && ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H)) {
+                    st.op = 0;
+                    st.umma.mb = st.mb;
+                    rc = ln_conv_umma_plan_build(ctx, &st.umma, g);
+                    if (rc) return rc;
+                } else st.op = 1;
+                net->steps.push_back(st);
+                break;
+            }
+            case K_MAXPOOL: {
+                st.op = 3;
+                st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride;
+                st.y = net->views[i].ptr; st.ys = net->views[i].cstride;
+                st.C = L.in.c; st.H = L.in.h; st.W = L.in.w; st.OH = L.out.h; st.OW = L.out.w;
+                net->steps.push_back(st);
+                break;
+            }
+            case K_UPSAMPLE: {
+                st.op = 4;
+                st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride;
+                st.y = net->views[i].ptr; st.ys = net->views[i].cstride;
+                st.C = L.in.c; st.H = L.in.h; st.W = L.in.w;
+                net->steps.push_back(st);
+                break;
+            }
+            case K_ROUTE: {
+                if (L.sources.size() >= 2) {
+                    int off = 0;
+                    for (int s : L.sources) {
+                        const int r = root_of(s);
+                        if (!(home_buf[r] == i && home_off[r] == off)) {  // not produced in place: copy
+                            QStep c;
+                            c.layer = i; c.op = 5;
+                            c.x = net->views[s].ptr; c.xs = net->views[s].cstride;
+                            c.y = net->views[i].ptr + off; c.ys = net->views[i].cstride;
+                            c.C = net->layers[s].out.c; c.H = L.out.h; c.W = L.out.w;
+                            net->steps.push_back(c);
+                        }
+                        off += net->layers[s].out.c;
+                    }
+                } else if (alias[i] < 0) {
+                    const int chunk = net->layers[L.sources[0]].out.c / L.route_groups, start = chunk * L.route_group_id;
+                    if (start % 16 != 0) {
+                        QStep c;
+                        c.layer = i; c.op = 5;
+                        c.x = net->views[L.sources[0]].ptr + start; c.xs = net->views[L.sources[0]].cstride;
+                        c.y = net->views[i].ptr; c.ys = net->views[i].cstride;
+                        c.C = chunk; c.H = L.out.h; c.W = L.out.w;
+                        net->steps.push_back(c);
+                    }
+                }
+                break;
+            }
+            case K_SHORTCUT: {
+                st.op = 6;
+                const int s = L.sources[0];
+                st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride; st.sa = sx;
+                st.x2 = net->views[s].ptr; st.xs2 = net->views[s].cstride; st.sb = net->scale[s + 1];
+                st.y = net->views[i].ptr; st.ys = net->views[i].cstride; st.inv_sy = 1.0f / sy;
+                st.C = L.out.c; st.H = L.out.h; st.W = L.out.w;
+                net->steps.push_back(st);
+                break;
+            }
+            case K_YOLO: break;
+        }
+    }
+    net->plan_valid = true;
+    net->plan_mb = mb;
+    return LN_OK;
+}
+
+int run_plan(ln_net* net, const float* input_dev_f32) {
+    ln_ctx* ctx = net->ctx;
+    const int mb = net->plan_mb;
+    const int kind = net->precision == LN_F8 ? LN_KIND_F8 : LN_KIND_I8;
+    const int64_t in_image = (int64_t)net->channels * net->height * net->width;
+    for (int b0 = 0; b0 < net->batch; b0 += mb) {
+        for (auto& st : net->steps) {
+            const NLayer& L = net->layers[st.layer];
+            int rc = LN_OK;
+            switch (st.op) {
+                case 0: {
+                    if (st.head) {
+                        ln_conv_umma_plan plan = st.umma;
+                        plan.p.out = (float*)st.geom.out + (int64_t)b0 * L.out.c * L.out.h * L.out.w;
+                        rc = ln_conv_umma_launch(ctx, &plan);
+                    } else rc = ln_conv_umma_launch(ctx, &st.umma);
+                    break;
+                }
+                case 1: {
+                    ln_conv_geom g = st.geom;
+                    if (st.head) g.out = (float*)st.geom.out + (int64_t)b0 * L.out.c * L.out.h * L.out.w;
+                    rc = ln_conv_simt_launch(ctx, g, nullptr, st.mb);
+                    break;
+                }
+                case 2:
+                    rc = ln_conv_stem_launch(ctx, kind, input_dev_f32 + b0 * in_image, st.inv_sy, mb, L.in.c, L.in.h, L.in.w, L.wq->w_oihw, st.mb, L.filters, L.size,
+                                             L.stride_x, L.padding, L.out.h, L.out.w, L.act, st.geom.inv_sy, st.geom.out, st.geom.out_pixel_stride);
+                    break;
+                case 3: rc = ln_q_maxpool_launch(ctx, kind, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, st.OH, st.OW, L.size, L.stride_x, L.stride_y, L.padding); break;
+                case 4: rc = ln_q_upsample_launch(ctx, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, L.up_stride); break;
+                case 5: rc = ln_q_copy_launch(ctx, st.x, st.xs, st.y, st.ys, (int64_t)mb * st.H * st.W, st.C); break;
+                case 6: rc = ln_q_shortcut_launch(ctx, kind, st.x, st.xs, st.sa, st.x2, st.xs2, st.sb, st.y, st.ys, (int64_t)mb * st.H * st.W, st.C, L.act, st.inv_sy); break;
+                case 7: rc = ln_q_quantize_launch(ctx, kind, input_dev_f32 + b0 * in_image, st.y, mb, st.C, st.H, st.W, st.ys, st.inv_sy); break;
+            }
+            if (rc) return rc;
+        }
+    }
+    return LN_OK;
+}
+
+int forward_any(ln_net* net, const ln_tensor* input) {
+    ln_ctx* ctx = net->ctx;
+    if (!net->weights_loaded) return ln_fail(ctx, LN_ERR_ARG, "weights are not loaded");
+    if (!input || input->dtype != LN_F32 || input->n != net->batch || input->c != net->channels || input->h != net->height || input->w != net->width)
+        return ln_fail(ctx, LN_ERR_SHAPE, "input tensor must be f32 [%d,%d,%d,%d]", net->batch, net->channels, net->height, net->width);
+    cudaSetDevice(ctx->device);
+    LN_CUDA(ctx, cudaEventRecord(net->ev[0], ctx->stream));
+    int rc;
+    if (net->precision == LN_F32) rc = forward_f32(net, input, nullptr);
+    else {
+        int mb = net->micro_batch > 0 && net->micro_batch < net->batch ? net->micro_batch : net->batch;
+        if (net->batch % mb != 0) return ln_fail(ctx, LN_ERR_ARG, "micro batch %d does not divide batch %d", mb, net->batch);
+        if (!net->plan_valid || net->plan_mb != mb) {
+            rc = build_plan(net, mb);
+            if (rc) { release_plan(net); return rc; }
+            LN_CUDA(ctx, cudaEventRecord(net->ev[0], ctx->stream));
+        }
+        rc = run_plan(net, (const float*)input->ptr);
+        if (rc == LN_OK) rc = ln_check_status(ctx, "ln_net_forward");
+    }
+    if (rc) return rc;
+    LN_CUDA(ctx, cudaEventRecord(net->ev[1], ctx->stream));
+    return LN_OK;
+}
+
+int fill_heads(ln_net* net, std::vector<ln_yolo_head>& hs) {
+    if (net->heads.size() != net->head_layers.size()) return ln_fail(net->ctx, LN_ERR_ARG, "no head output: run a forward first");
+    hs.resize(net->head_layers.size());
+    for (size_t k = 0; k < hs.size(); ++k) {
+        const NLayer& L = net->layers[net->head_layers[k]];
+        ln_yolo_head& h = hs[k];
+        memset(&h, 0, sizeof h);
+        h.raw = net->heads[k];
+        h.classes = L.classes;
+        h.n_anchor = (int)L.mask.size();
+        for (size_t m = 0; m < L.mask.size(); ++m) { h.anchors[2 * m] = L.anchors[2 * L.mask[m]]; h.anchors[2 * m + 1] = L.anchors[2 * L.mask[m] + 1]; }
+        h.scale_x_y = L.scale_x_y;
+        h.new_coords = L.new_coords ? 1 : 0;
+    }
+    return LN_OK;
+}
+
+int stage_input(ln_net* net, const float* host) {
+    ln_ctx* ctx = net->ctx;
+    cudaSetDevice(ctx->device);
+    if (!net->input_dev) {
+        net->input_dev = ln_tensor_new(ctx, LN_F32, net->batch, net->channels, net->height, net->width);
+        if (!net->input_dev) return LN_ERR_CUDA;
+    }
+    LN_CUDA(ctx, cudaMemcpyAsync(net->input_dev->ptr, host, (size_t)net->input_dev->count() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    return LN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ln_net_create(ln_ctx* ctx, const char* cfg_text, int32_t batch, int32_t precision, ln_net** out) {
+    if (!ctx || !cfg_text || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_net_create: NULL argument");
+    if (precision != LN_F32 && precision != LN_Q8 && precision != LN_F8) return ln_fail(ctx, LN_ERR_ARG, "ln_net_create: precision must be LN_F32, LN_Q8 or LN_F8");
+    std::unique_ptr<ln_net> net(new ln_net());
+    net->ctx = ctx;
+    net->precision = precision;
+    try {
+        build_layers(net.get(), cfg_text, batch);
+    } catch (const ParseError& e) {
+        return ln_fail(ctx, LN_ERR_PARSE, "%s", e.msg.c_str());
+    } catch (const std::exception& e) {
+        return ln_fail(ctx, LN_ERR_PARSE, "%s", e.what());
+    }
+    cudaSetDevice(ctx->device);
+    for (auto& e : net->ev)
+        if (cudaEventCreate(&e) != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "cudaEventCreate failed");
+    *out = net.release();
+    return LN_OK;
+}
+
+int32_t ln_net_destroy(ln_net* net) {
+    if (!net) return LN_OK;
+    cudaSetDevice(net->ctx->device);
+    cudaStreamSynchronize(net->ctx->stream);
+    release_plan(net);
+    release_outputs(net);
+    release_heads(net);
+    ln_tensor_release(net->input_dev);
+    for (auto& L : net->layers) {
+        ln_tensor_release(L.w_f32);
+        ln_tensor_release(L.b_f32);
+        ln_conv_weights_release(L.wq);
+    }
+    for (auto& e : net->ev) if (e) cudaEventDestroy(e);
+    delete net;
+    return LN_OK;
+}
+
+int32_t ln_net_num_layers(const ln_net* net) { return net ? (int)net->layers.size() : 0; }
+
+int32_t ln_net_layer_info(const ln_net* net, int32_t layer, int32_t info[16]) {
+    if (!net || !info || layer < 0 || layer >= (int)net->layers.size()) return LN_ERR_ARG;
+    const NLayer& L = net->layers[layer];
+    int v[16] = {L.kind, L.in.w, L.in.h, L.in.c, L.in.b, L.out.w, L.out.h, L.out.c, L.out.b, L.filters, L.size, L.stride_x, L.stride_y, L.padding, L.bn ? 1 : 0, L.act};
+    memcpy(info, v, sizeof v);
+    return LN_OK;
+}
+
+int64_t ln_net_weight_count(const ln_net* net) {
+    int64_t c = 0;
+    if (net)
+        for (auto& L : net->layers)
+            if (L.kind == K_CONV) c += (int64_t)L.biases.size() * (L.bn ? 4 : 1) + (int64_t)L.weights.size();
+    return c;
+}
+
+int32_t ln_net_load_weights(ln_net* net, const float* blob, int64_t count) {
+    if (!net || !blob) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_load_weights: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    if (count != ln_net_weight_count(net)) return ln_fail(ctx, LN_ERR_SHAPE, "weight blob has %lld values, the network needs %lld", (long long)count, (long long)ln_net_weight_count(net));
+    cudaSetDevice(ctx->device);
+    release_plan(net);
+    const float* w = blob;
+    for (auto& L : net->layers) {
+        if (L.kind != K_CONV) continue;
+        auto take = [&](std::vector<float>& v) { memcpy(v.data(), w, v.size() * 4); w += v.size(); };
+        take(L.biases);
+        if (L.bn) { take(L.scales); take(L.mean); take(L.var); }
+        take(L.weights);
+        // fold_convolutional_params_for_inference (runtime/weights_io.rs:32-92)
+        std::vector<float> fw = L.weights, fb = L.biases;
+        if (L.bn) {
+            const size_t per = fw.size() / L.filters;
+            for (int f = 0; f < L.filters; ++f) {
+                const float scale = L.scales[f] / std::sqrt(L.var[f] + 1e-5f);
+                const float shift = L.mean[f] * scale;
+                fb[f] = fb[f] - shift;
+                for (size_t k = 0; k < per; ++k) fw[f * per + k] = fw[f * per + k] * scale;
+            }
+        }
+        ln_tensor_release(L.w_f32); L.w_f32 = nullptr;
+        ln_tensor_release(L.b_f32); L.b_f32 = nullptr;
+        ln_conv_weights_release(L.wq); L.wq = nullptr;
+        const int64_t wshape[4] = {L.filters, L.in.c / L.groups, L.size, L.size}, bshape[4] = {1, L.filters, 1, 1};
+        int rc = ln_tensor_upload_f32(ctx, wshape, fw.data(), &L.w_f32);
+        if (rc == LN_OK) rc = ln_tensor_upload_f32(ctx, bshape, fb.data(), &L.b_f32);
+        if (rc == LN_OK) rc = ln_sync(ctx);  // the host vectors die at the end of this scope
+        if (rc == LN_OK && net->precision != LN_F32) {
+            if (L.groups != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "8-bit convolution needs groups=1");
+            rc = ln_conv_weights_q(ctx, L.w_f32, L.filters, L.in.c, L.size, net->precision, &L.wq);
+        }
+        if (rc) return rc;
+    }
+    net->weights_loaded = true;
+    return LN_OK;
+}
+
+int32_t ln_net_load_weights_file(ln_net* net, const char* path) {
+    if (!net || !path) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_load_weights_file: NULL argument");
+    std::ifstream f(path, std::ios::binary);
+    if (!f) return ln_fail(net->ctx, LN_ERR_ARG, "cannot open %s", path);
+    // read_header (runtime/weights_io.rs:911-928)
+    int32_t hdr[3];
+    f.read((char*)hdr, 12);
+    if (!f) return ln_fail(net->ctx, LN_ERR_PARSE, "%s: truncated header", path);
+    if (hdr[0] * 10 + hdr[1] >= 2) { uint64_t seen; f.read((char*)&seen, 8); } else { uint32_t seen; f.read((char*)&seen, 4); }
+    const int64_t n = ln_net_weight_count(net);
+    std::vector<float> blob((size_t)n);
+    f.read((char*)blob.data(), n * 4);
+    if (f.gcount() != n * 4) return ln_fail(net->ctx, LN_ERR_PARSE, "%s: expected %lld weight values after the header, file has %lld", path, (long long)n, (long long)(f.gcount() / 4));
+    return ln_net_load_weights(net, blob.data(), n);
+}
+
+int32_t ln_net_calibrate(ln_net* net, const float* input_host) {
+    if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_calibrate: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    if (!net->weights_loaded) return ln_fail(ctx, LN_ERR_ARG, "weights are not loaded");
+    int rc = stage_input(net, input_host);
+    if (rc) return rc;
+    const int T = (int)net->layers.size() + 1;
+    unsigned* amax_dev = (unsigned*)ln_pool_alloc(ctx, (size_t)T * 4);
+    if (!amax_dev) return LN_ERR_CUDA;
+    cudaMemsetAsync(amax_dev, 0, (size_t)T * 4, ctx->stream);
+    rc = forward_f32(net, net->input_dev, amax_dev);
+    std::vector<float> amax((size_t)T, 0.0f);
+    if (rc == LN_OK) {
+        cudaError_t e = cudaMemcpyAsync(amax.data(), amax_dev, (size_t)T * 4, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = ln_fail(ctx, LN_ERR_CUDA, "calibration download: %s", cudaGetErrorString(e));
+    }
+    ln_pool_free(ctx, amax_dev, (size_t)T * 4);
+    release_outputs(net);
+    release_heads(net);
+    if (rc) return rc;
+    scales_from_amax(net, amax, net->precision == LN_F8 ? 448.0f : 127.0f);
+    release_plan(net);
+    return LN_OK;
+}
+
+int32_t ln_net_get_scales(const ln_net* net, float* scales, int32_t count) {
+    if (!net || !scales || count != (int)net->layers.size() + 1 || !net->scales_set) return LN_ERR_ARG;
+    memcpy(scales, net->scale.data(), (size_t)count * 4);
+    return LN_OK;
+}
+
+int32_t ln_net_set_scales(ln_net* net, const float* scales, int32_t count) {
+    if (!net || !scales) return LN_ERR_ARG;
+    if (count != (int)net->layers.size() + 1) return ln_fail(net->ctx, LN_ERR_SHAPE, "expected %d scales, got %d", (int)net->layers.size() + 1, count);
+    for (int i = 0; i < count; ++i)
+        if (!(scales[i] > 0.0f)) return ln_fail(net->ctx, LN_ERR_ARG, "scale %d is not positive", i);
+    net->scale.assign(scales, scales + count);
+    net->scales_set = true;
+    release_plan(net);
+    return LN_OK;
+}
+
+int32_t ln_net_set_micro_batch(ln_net* net, int32_t micro_batch) {
+    if (!net || micro_batch < 0) return LN_ERR_ARG;
+    if (micro_batch > 0 && net->batch % micro_batch != 0) return ln_fail(net->ctx, LN_ERR_ARG, "micro batch %d does not divide batch %d", micro_batch, net->batch);
+    net->micro_batch = micro_batch;
+    return LN_OK;
+}
+
+int32_t ln_net_forward_device(ln_net* net, const ln_tensor* input) {
+    if (!net) return LN_ERR_ARG;
+    return forward_any(net, input);
+}
+
+int32_t ln_net_forward(ln_net* net, const float* input_host) {
+    if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_forward: NULL argument");
+    int rc = stage_input(net, input_host);
+    if (rc) return rc;
+    return forward_any(net, net->input_dev);
+}
+
+int32_t ln_net_num_heads(const ln_net* net) { return net ? (int)net->head_layers.size() : 0; }
+
+int32_t ln_net_head(ln_net* net, int32_t head_index, ln_tensor** out) {
+    if (!net || !out) return LN_ERR_ARG;
+    if (head_index < 0 || head_index >= (int)net->heads.size()) return ln_fail(net->ctx, LN_ERR_ARG, "head %d is not available (run a forward first)", head_index);
+    ln_tensor_retain(net->heads[head_index]);
+    *out = net->heads[head_index];
+    return LN_OK;
+}
+
+int32_t ln_net_layer_output(ln_net* net, int32_t layer, ln_tensor** out) {
+    if (!net || !out || layer < 0 || layer >= (int)net->layers.size()) return LN_ERR_ARG;
+    ln_ctx* ctx = net->ctx;
+    if (net->precision == LN_F32) {
+        if ((int)net->out.size() <= layer || !net->out[layer]) return ln_fail(ctx, LN_ERR_ARG, "layer %d has no output (run a forward first)", layer);
+        ln_tensor_retain(net->out[layer]);
+        *out = net->out[layer];
+        return LN_OK;
+    }
+    if (!net->plan_valid || net->plan_mb != net->batch) return ln_fail(ctx, LN_ERR_ARG, "8-bit layer outputs are kept for whole-batch forwards only (micro batch 0)");
+    const NLayer& L = net->layers[layer];
+    if (L.kind == K_YOLO || feeds_head(net, layer)) {
+        int k = 0;
+        for (size_t h = 0; h < net->head_layers.size(); ++h)
+            if (net->head_layers[h] == layer || net->head_layers[h] == layer + 1) k = (int)h;
+        ln_tensor_retain(net->heads[k]);
+        *out = net->heads[k];
+        return LN_OK;
+    }
+    const QView& v = net->views[layer];
+    // a copy, so that the handle stays valid after the plan is rebuilt
+    ln_tensor* t = ln_tensor_new(ctx, net->precision, net->batch, v.c, v.h, v.w);
+    if (!t) return LN_ERR_CUDA;
+    t->scale = net->scale[layer + 1];
+    cudaMemsetAsync(t->ptr, 0, t->bytes, ctx->stream);
+    int rc = ln_q_copy_launch(ctx, v.ptr, v.cstride, t->ptr, t->cstride, (int64_t)net->batch * v.h * v.w, v.c);
+    if (rc) { ln_tensor_release(t); return rc; }
+    *out = t;
+    return LN_OK;
+}
+
+int32_t ln_net_detect_device(ln_net* net, const ln_tensor* input, const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
+                             ln_detection* records_host, int32_t* counts_host) {
+    if (!net || !image_w || !image_h || !opts || !records_host || !counts_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_detect: NULL argument");
+    int rc = forward_any(net, input);
+    if (rc) return rc;
+    std::vector<ln_yolo_head> hs;
+    rc = fill_heads(net, hs);
+    if (rc) return rc;
+    rc = ln_yolo_decode_nms(net->ctx, hs.data(), (int)hs.size(), net->width, net->height, image_w, image_h, opts, records_host, counts_host);
+    if (rc) return rc;
+    ln_ctx* ctx = net->ctx;
+    LN_CUDA(ctx, cudaEventRecord(net->ev[2], ctx->stream));
+    LN_CUDA(ctx, cudaEventSynchronize(net->ev[2]));
+    cudaEventElapsedTime(&net->times_ms[0], net->ev[0], net->ev[1]);
+    cudaEventElapsedTime(&net->times_ms[1], net->ev[1], net->ev[2]);
+    return LN_OK;
+}
+
+int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
+                      ln_detection* records_host, int32_t* counts_host) {
+    if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_detect: NULL argument");
+    int rc = stage_input(net, input_host);
+    if (rc) return rc;
+    return ln_net_detect_device(net, net->input_dev, image_w, image_h, opts, records_host, counts_host);
+}
+
+int32_t ln_net_last_times(const ln_net* net, float times_ms[2]) {
+    if (!net || !times_ms) return LN_ERR_ARG;
+    times_ms[0] = net->times_ms[0];
+    times_ms[1] = net->times_ms[1];
+    return LN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,726 @@
+// 8-bit (int8 / FP8 E4M3) NHWC operators: quantise / dequantise / layout, weight packing, max-pool,
+// up-sample, route, shortcut, and the CUDA-core convolutions (first layer with C <= 4, and a general
+// fallback for geometries the tensor-core kernel does not take).  All of these are HBM-bound byte
+// work: one thread moves 16 bytes of channels of one pixel, loads and stores are 16-byte vectors,
+// grids are sized in multiples of the SM count.
+#include <cuda_fp8.h>
+
+#include "ln_conv_plan.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+int grid_for(ln_ctx* ctx, int64_t n) {
+    int64_t b = (n + kThreads - 1) / kThreads;
+    int64_t cap = (int64_t)ctx->sm_count * 16;
+    return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+    __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&hr));
+}
+__device__ __forceinline__ uint8_t float_to_e4m3(float v) { return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); }
+
+template <int KIND>
+__device__ __forceinline__ float code_to_float(uint8_t c) {
+    return KIND == LN_KIND_I8 ? (float)(int8_t)c : e4m3_to_float(c);
+}
+template <int KIND>
+__device__ __forceinline__ uint8_t quantize_code(float a, float inv_s) {
+    if (KIND == LN_KIND_I8) return (uint8_t)(ln_quant_i8(a, inv_s) & 0xFF);
+    return float_to_e4m3(__fmul_rn(a, inv_s));
+}
+
+// f32 NCHW -> 8-bit NHWC (pad channels written as zero)
+template <int KIND>
+__global__ void quantize_nchw_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, int64_t N, int C, int H, int W, int64_t cstride,
+                                     float inv_s) {
+    const int64_t total = N * H * W * cstride;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int c = (int)(i % cstride);
+        int64_t pix = i / cstride;
+        int64_t hw = pix % ((int64_t)H * W), n = pix / ((int64_t)H * W);
+        y[i] = c < C ? quantize_code<KIND>(x[(n * C + c) * H * W + hw], inv_s) : 0;
+    }
+}
+
+// 8-bit NHWC view -> f32 NCHW (value = code * scale)
+template <int KIND>
+__global__ void dequantize_nhwc_kernel(const uint8_t* __restrict__ x, float* __restrict__ y, int64_t N, int C, int H, int W, int64_t cstride,
+                                       float scale) {
+    const int64_t total = N * C * H * W;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t hw = i % ((int64_t)H * W);
+        int c = (int)((i / ((int64_t)H * W)) % C);
+        int64_t n = i / ((int64_t)H * W * C);
+        y[i] = code_to_float<KIND>(x[(n * H * W + hw) * cstride + c]) * scale;
+    }
+}
+
+// raw codes: NHWC view <-> NCHW dense
+__global__ void codes_nhwc_to_nchw_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, int64_t N, int C, int H, int W, int64_t cstride) {
+    const int64_t total = N * C * H * W;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t hw = i % ((int64_t)H * W);
+        int c = (int)((i / ((int64_t)H * W)) % C);
+        int64_t n = i / ((int64_t)H * W * C);
+        y[i] = x[(n * H * W + hw) * cstride + c];
+    }
+}
+__global__ void codes_nchw_to_nhwc_kernel(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, int64_t N, int C, int H, int W, int64_t cstride) {
+    const int64_t total = N * H * W * cstride;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int c = (int)(i % cstride);
+        int64_t pix = i / cstride;
+        int64_t hw = pix % ((int64_t)H * W), n = pix / ((int64_t)H * W);
+        y[i] = c < C ? x[(n * C + c) * H * W + hw] : 0;
+    }
+}
+
+// Weight packing: one block per (padded) filter.  s = max|w| / qmax, code = quantise(w / s);
+// layout [fpad][k][k][cpad] plus the reference's [F][C][k][k] order for the CUDA-core kernels.
+template <int KIND>
+__global__ void pack_weights_kernel(const float* __restrict__ w, int F, int C, int k, int cpad, uint8_t* __restrict__ packed,
+                                    uint8_t* __restrict__ oihw, float* __restrict__ wscale) {
+    const int f = blockIdx.x;
+    const int per = C * k * k;
+    __shared__ float red[32];
+    __shared__ float s_scale;
+    float m = 0.0f;
+    if (f < F)
+        for (int i = threadIdx.x; i < per; i += blockDim.x) m = fmaxf(m, fabsf(w[(int64_t)f * per + i]));
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float mm = 0.0f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) mm = fmaxf(mm, red[i]);
+        const float qmax = KIND == LN_KIND_I8 ? 127.0f : 448.0f;
+        float s = (mm > 0.0f && isfinite(mm)) ? __fdiv_rn(mm, qmax) : 1.0f;
+        s_scale = s;
+        wscale[f] = f < F ? s : 0.0f;
+    }
+    __syncthreads();
+    const float s = s_scale;
+    const int row = k * k * cpad;
+    for (int i = threadIdx.x; i < row; i += blockDim.x) {
+        int c = i % cpad, tap = i / cpad;
+        uint8_t code = 0;
+        if (f < F && c < C) {
+            float v = __fdiv_rn(w[((int64_t)f * C + c) * k * k + tap], s);
+            code = KIND == LN_KIND_I8 ? (uint8_t)(ln_quant_i8(v, 1.0f) & 0xFF) : float_to_e4m3(v);
+            oihw[((int64_t)f * C + c) * k * k + tap] = code;
+        }
+        packed[(int64_t)f * row + i] = code;
+    }
+}
+
+// ---- glue ------------------------------------------------------------------------------------
+
+// order-preserving key of an E4M3 byte under signed byte comparison (an involution)
+__device__ __forceinline__ uint32_t f8_key4(uint32_t v) {
+    uint32_t neg = (v >> 7) & 0x01010101u;  // 1 in each negative byte
+    return v ^ (neg * 0x7Fu);
+}
+
+template <int KIND>
+__device__ __forceinline__ uint4 max16(uint4 a, uint4 b) {
+    if (KIND == LN_KIND_I8) return make_uint4(__vmaxs4(a.x, b.x), __vmaxs4(a.y, b.y), __vmaxs4(a.z, b.z), __vmaxs4(a.w, b.w));
+    return make_uint4(f8_key4(__vmaxs4(f8_key4(a.x), f8_key4(b.x))), f8_key4(__vmaxs4(f8_key4(a.y), f8_key4(b.y))),
+                      f8_key4(__vmaxs4(f8_key4(a.z), f8_key4(b.z))), f8_key4(__vmaxs4(f8_key4(a.w), f8_key4(b.w))));
+}
+
+// Max-pool, NHWC, one thread per (output pixel, 16 channels).  Window origin o*stride - padding/2, taps outside the
+// image skipped (runtime/layer_ops.rs:1740-1799); a window with no tap inside gives the most negative code.
+template <int KIND>
+__global__ void maxpool_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N, int C16, int H,
+                                 int W, int OH, int OW, int size, int sx, int sy, int padding) {
+    const int64_t total = N * OH * OW * C16;
+    const int off = padding / 2;
+    const uint32_t lowest = KIND == LN_KIND_I8 ? 0x81818181u : 0xFEFEFEFEu;  // -127 / -448
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int cg = (int)(i % C16);
+        int64_t pix = i / C16;
+        int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
+        int64_t n = pix / ((int64_t)OW * OH);
+        uint4 m = make_uint4(lowest, lowest, lowest, lowest);
+        for (int ky = 0; ky < size; ++ky) {
+            int iy = oy * sy + ky - off;
+            if (iy < 0 || iy >= H) continue;
+            for (int kx = 0; kx < size; ++kx) {
+                int ix = ox * sx + kx - off;
+                if (ix < 0 || ix >= W) continue;
+                uint4 v = *reinterpret_cast<const uint4*>(x + ((n * H + iy) * W + ix) * xs + cg * 16);
+                m = max16<KIND>(m, v);
+            }
+        }
+        *reinterpret_cast<uint4*>(y + pix * ys + cg * 16) = m;
+    }
+}
+
+// nearest up-sample, NHWC (runtime/layer_ops.rs:2208-2256, scale folded into the tensor scale)
+__global__ void upsample_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N, int C16, int H, int W,
+                                  int s) {
+    const int OH = H * s, OW = W * s;
+    const int64_t total = N * OH * OW * C16;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int cg = (int)(i % C16);
+        int64_t pix = i / C16;
+        int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
+        int64_t n = pix / ((int64_t)OW * OH);
+        *reinterpret_cast<uint4*>(y + pix * ys + cg * 16) =
+            *reinterpret_cast<const uint4*>(x + ((n * H + oy / s) * W + ox / s) * xs + cg * 16);
+    }
+}
+
+// channel-slice copy between NHWC views (route); 16-byte and byte variants
+__global__ void copy_q16_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t pixels, int C16) {
+    const int64_t total = pixels * C16;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int cg = (int)(i % C16);
+        int64_t pix = i / C16;
+        *reinterpret_cast<uint4*>(y + pix * ys + cg * 16) = *reinterpret_cast<const uint4*>(x + pix * xs + cg * 16);
+    }
+}
+__global__ void copy_q1_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t pixels, int C) {
+    const int64_t total = pixels * C;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int c = (int)(i % C);
+        int64_t pix = i / C;
+        y[pix * ys + c] = x[pix * xs + c];
+    }
+}
+
+// shortcut: code = quantise(act(a*sa + b*sb) / sy); 4 channels per thread (pad channels stay zero)
+template <int KIND, bool EXACT>
+__global__ void shortcut_q_kernel(const uint8_t* __restrict__ a, int64_t as, float sa, const uint8_t* __restrict__ b, int64_t bs, float sb,
+                                  uint8_t* __restrict__ y, int64_t ys, int64_t pixels, int C4, int act, float inv_sy) {
+    const int64_t total = pixels * C4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int cg = (int)(i % C4);
+        int64_t pix = i / C4;
+        uint32_t va = *reinterpret_cast<const uint32_t*>(a + pix * as + cg * 4);
+        uint32_t vb = *reinterpret_cast<const uint32_t*>(b + pix * bs + cg * 4);
+        uint32_t out = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v = __fmul_rn(code_to_float<KIND>((uint8_t)(va >> (8 * j))), sa);
+            v = __fmaf_rn(code_to_float<KIND>((uint8_t)(vb >> (8 * j))), sb, v);
+            out |= (uint32_t)quantize_code<KIND>(ln_epilogue_act<EXACT>(act, v), inv_sy) << (8 * j);
+        }
+        *reinterpret_cast<uint32_t*>(y + pix * ys + cg * 4) = out;
+    }
+}
+
+// ---- CUDA-core convolutions ------------------------------------------------------------------
+
+// General fallback: one thread per (output pixel, filter); NHWC input, weights [fpad][k][k][cpad].
+template <int KIND, bool EXACT>
+__global__ void conv_simt_kernel(ln_conv_geom g, const float2* __restrict__ mb) {
+    const int64_t total = (int64_t)g.N * g.OH * g.OW * g.F;
+    const uint8_t* x = (const uint8_t*)g.x;
+    const uint8_t* w = (const uint8_t*)g.w;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int f = (int)(i % g.F);
+        int64_t pix = i / g.F;
+        int ox = (int)(pix % g.OW), oy = (int)((pix / g.OW) % g.OH);
+        int64_t n = pix / ((int64_t)g.OW * g.OH);
+        int iacc = 0;
+        float facc = 0.0f;
+        for (int ky = 0; ky < g.k; ++ky) {
+            int iy = oy * g.stride + ky - g.pad;
+            if (iy < 0 || iy >= g.H) continue;
+            for (int kx = 0; kx < g.k; ++kx) {
+                int ix = ox * g.stride + kx - g.pad;
+                if (ix < 0 || ix >= g.W) continue;
+                const uint8_t* xp = x + ((n * g.H + iy) * g.W + ix) * g.x_pixel_stride;
+                const uint8_t* wp = w + (((int64_t)f * g.k + ky) * g.k + kx) * g.cpad;
+                for (int c = 0; c < g.cpad; c += 4) {
+                    uint32_t xv = *reinterpret_cast<const uint32_t*>(xp + c), wv = *reinterpret_cast<const uint32_t*>(wp + c);
+                    if (KIND == LN_KIND_I8) iacc = __dp4a((int)xv, (int)wv, iacc);
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            facc = fmaf(e4m3_to_float((uint8_t)(xv >> (8 * j))), e4m3_to_float((uint8_t)(wv >> (8 * j))), facc);
+                    }
+                }
+            }
+        }
+        if (g.out_kind == LN_OUT_ACC) {
+            int32_t* o = (int32_t*)g.out;
+            o[(((int64_t)n * g.F + f) * g.OH + oy) * g.OW + ox] = KIND == LN_KIND_I8 ? iacc : __float_as_int(facc);
+            continue;
+        }
+        const float2 m = mb[f];
+        float a = ln_epilogue_act<EXACT>(g.act, __fmaf_rn(KIND == LN_KIND_I8 ? __int2float_rn(iacc) : facc, m.x, m.y));
+        if (g.out_kind == LN_OUT_F32) ((float*)g.out)[(((int64_t)n * g.F + f) * g.OH + oy) * g.OW + ox] = a;
+        else ((uint8_t*)g.out)[pix * g.out_pixel_stride + f] = quantize_code<KIND>(a, g.inv_sy);
+    }
+}
+
+// First layer (C <= 4): f32 NCHW image -> quantise -> k x k convolution -> epilogue -> 8-bit NHWC.
+// One thread per (output pixel, group of 16 filters); the quantised patch is packed 4 codes per word
+// (tap-major, channel-minor, zero padded) and each filter costs ceil(k*k*C/4) dp4a with its weights
+// read from shared memory.
+constexpr int kStemMaxWords = 13;  // k*k*C <= 52 (e.g. 3x3x3 = 27 -> 7 words; 7x7x1 = 49 -> 13 words)
+template <int KIND, bool EXACT>
+__global__ void conv_stem_kernel(const float* __restrict__ x, float inv_sx, int N, int C, int H, int W, const uint8_t* __restrict__ w_oihw,
+                                 const float2* __restrict__ mb, int F, int k, int stride, int pad, int OH, int OW, int act, float inv_sy,
+                                 uint8_t* __restrict__ out, int64_t out_pixel_stride) {
+    extern __shared__ uint32_t s_w[];  // [F16*16][words]
+    const int taps = k * k * C, words = (taps + 3) / 4;
+    const int F16 = (F + 15) / 16;
+    float2* s_mb = reinterpret_cast<float2*>(s_w + F16 * 16 * words);
+    for (int i = threadIdx.x; i < F16 * 16 * words; i += blockDim.x) {
+        int f = i / words, wd = i % words;
+        uint32_t v = 0;
+        for (int j = 0; j < 4; ++j) {
+            int t = wd * 4 + j;  // t = (ky*k + kx)*C + c
+            if (f < F && t < taps) {
+                int c = t % C, tap = t / C;
+                v |= (uint32_t)w_oihw[((int64_t)f * C + c) * k * k + tap] << (8 * j);
+            }
+        }
+        s_w[i] = v;
+    }
+    for (int i = threadIdx.x; i < F16 * 16; i += blockDim.x) s_mb[i] = i < F ? mb[i] : make_float2(0.0f, 0.0f);
+    __syncthreads();
+    const int64_t total = (int64_t)N * OH * OW * F16;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        // consecutive threads take consecutive pixels (coalesced NCHW reads); filter group is the slow index
+        int64_t pix = i % ((int64_t)N * OH * OW);
+        int fg = (int)(i / ((int64_t)N * OH * OW));
+        int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
+        int64_t n = pix / ((int64_t)OW * OH);
+        uint32_t patch[kStemMaxWords];
+#pragma unroll
+        for (int wd = 0; wd < kStemMaxWords; ++wd) patch[wd] = 0;
+        for (int t = 0; t < taps; ++t) {
+            int c = t % C, tap = t / C, ky = tap / k, kx = tap % k;
+            int iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
+            uint32_t code = 0;
+            if (iy >= 0 && iy < H && ix >= 0 && ix < W) code = quantize_code<KIND>(x[((n * C + c) * H + iy) * W + ix], inv_sx);
+            // static indexing keeps `patch` in registers
+#pragma unroll
+            for (int wd = 0; wd < kStemMaxWords; ++wd)
+                if (wd == (t >> 2)) patch[wd] |= code << (8 * (t & 3));
+        }
+        uint32_t packed[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t v = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int f = fg * 16 + q * 4 + b;
+                const uint32_t* wf = s_w + f * words;
+                int iacc = 0;
+                float facc = 0.0f;
+#pragma unroll
+                for (int wd = 0; wd < kStemMaxWords; ++wd) {
+                    if (wd < words) {
+                        if (KIND == LN_KIND_I8) iacc = __dp4a((int)patch[wd], (int)wf[wd], iacc);
+                        else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                facc = fmaf(e4m3_to_float((uint8_t)(patch[wd] >> (8 * j))), e4m3_to_float((uint8_t)(wf[wd] >> (8 * j))), facc);
+                        }
+                    }
+                }
+                const float2 m = s_mb[f];
+                float a = ln_epilogue_act<EXACT>(act, __fmaf_rn(KIND == LN_KIND_I8 ? __int2float_rn(iacc) : facc, m.x, m.y));
+                uint32_t code = f < F ? quantize_code<KIND>(a, inv_sy) : 0u;
+                v |= code << (8 * b);
+            }
+            packed[q] = v;
+        }
+        *reinterpret_cast<uint4*>(out + pix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+}
+
+bool is_q(const ln_tensor* t) { return t && (t->dtype == LN_Q8 || t->dtype == LN_F8); }
+int kind_of(int dtype) { return dtype == LN_F8 ? LN_KIND_F8 : LN_KIND_I8; }
+
+}  // namespace
+
+int ln_check_status(ln_ctx* ctx, const char* where) {
+    LN_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    LN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    int s = *ctx->h_status;
+    if (s == LN_STATUS_OK) return LN_OK;
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    return ln_fail(ctx, LN_ERR_TIMEOUT, "%s: a bounded device-side wait gave up (status %d: %s)", where, s,
+                   s == LN_STATUS_PRODUCER_TIMEOUT ? "TMA producer" : s == LN_STATUS_MMA_TIMEOUT ? "MMA issuer" : s == LN_STATUS_EPILOGUE_TIMEOUT ? "epilogue" : "unknown");
+}
+
+int ln_conv_simt_launch(ln_ctx* ctx, const ln_conv_geom& g, const void* w_unused, const float2* mb) {
+    (void)w_unused;
+    const int64_t total = (int64_t)g.N * g.OH * g.OW * g.F;
+    const int grid = grid_for(ctx, total);
+    const bool exact = ctx->exact_epilogue;
+    if (g.kind == LN_KIND_I8) {
+        if (exact) conv_simt_kernel<LN_KIND_I8, true><<<grid, kThreads, 0, ctx->stream>>>(g, mb);
+        else conv_simt_kernel<LN_KIND_I8, false><<<grid, kThreads, 0, ctx->stream>>>(g, mb);
+    } else {
+        if (exact) conv_simt_kernel<LN_KIND_F8, true><<<grid, kThreads, 0, ctx->stream>>>(g, mb);
+        else conv_simt_kernel<LN_KIND_F8, false><<<grid, kThreads, 0, ctx->stream>>>(g, mb);
+    }
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx, int N, int C, int H, int W, const void* w_oihw,
+                        const float2* mb, int F, int k, int stride, int pad, int OH, int OW, int act, float inv_sy, void* out,
+                        long long out_pixel_stride) {
+    const int taps = k * k * C, words = (taps + 3) / 4;
+    if (words > kStemMaxWords) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "first-layer convolution: k*k*C = %d exceeds %d", taps, kStemMaxWords * 4);
+    const int F16 = (F + 15) / 16;
+    const size_t smem = (size_t)F16 * 16 * words * 4 + (size_t)F16 * 16 * sizeof(float2);
+    if (smem > 48 * 1024) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "first-layer convolution: %d filters do not fit shared memory", F);
+    const int64_t total = (int64_t)N * OH * OW * F16;
+    const int grid = grid_for(ctx, total);
+    const bool exact = ctx->exact_epilogue;
+#define LN_STEM(K, E)                                                                                                                   \
+    conv_stem_kernel<K, E><<<grid, kThreads, smem, ctx->stream>>>(x_nchw, inv_sx, N, C, H, W, (const uint8_t*)w_oihw, mb, F, k, stride, pad, \
+                                                                 OH, OW, act, inv_sy, (uint8_t*)out, out_pixel_stride)
+    if (kind == LN_KIND_I8) { if (exact) LN_STEM(LN_KIND_I8, true); else LN_STEM(LN_KIND_I8, false); }
+    else { if (exact) LN_STEM(LN_KIND_F8, true); else LN_STEM(LN_KIND_F8, false); }
+#undef LN_STEM
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+// ---- internal helpers used by the network executor ------------------------------------------
+
+int ln_q_maxpool_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int OH, int OW,
+                        int size, int sx, int sy, int padding) {
+    const int C16 = (int)(ln_round_up(C, 16) / 16);
+    const int64_t total = N * OH * OW * C16;
+    if (kind == LN_KIND_I8)
+        maxpool_q_kernel<LN_KIND_I8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, OH, OW, size, sx, sy, padding);
+    else
+        maxpool_q_kernel<LN_KIND_F8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, OH, OW, size, sx, sy, padding);
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+int ln_q_upsample_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int stride) {
+    const int C16 = (int)(ln_round_up(C, 16) / 16);
+    const int64_t total = N * H * stride * W * stride * C16;
+    upsample_q_kernel<<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, stride);
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+int ln_q_copy_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys, int64_t pixels, int C) {
+    const bool vec = (C % 16 == 0) && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)xs | (uintptr_t)ys) % 16 == 0);
+    if (vec) copy_q16_kernel<<<grid_for(ctx, pixels * (C / 16)), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, pixels, C / 16);
+    else copy_q1_kernel<<<grid_for(ctx, pixels * C), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, pixels, C);
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+int ln_q_shortcut_launch(ln_ctx* ctx, int kind, const void* a, int64_t as, float sa, const void* b, int64_t bs, float sb, void* y, int64_t ys,
+                         int64_t pixels, int C, int act, float inv_sy) {
+    const int C4 = (int)(ln_round_up(C, 4) / 4);
+    const int64_t total = pixels * C4;
+    const int grid = grid_for(ctx, total);
+    const bool exact = ctx->exact_epilogue;
+#define LN_SC(K, E)                                                                                                                            \
+    shortcut_q_kernel<K, E><<<grid, kThreads, 0, ctx->stream>>>((const uint8_t*)a, as, sa, (const uint8_t*)b, bs, sb, (uint8_t*)y, ys, pixels, C4, \
+                                                               act, inv_sy)
+    if (kind == LN_KIND_I8) { if (exact) LN_SC(LN_KIND_I8, true); else LN_SC(LN_KIND_I8, false); }
+    else { if (exact) LN_SC(LN_KIND_F8, true); else LN_SC(LN_KIND_F8, false); }
+#undef LN_SC
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+int ln_q_quantize_launch(ln_ctx* ctx, int kind, const float* x, void* y, int64_t N, int C, int H, int W, int64_t cstride, float inv_s) {
+    const int64_t total = N * H * W * cstride;
+    if (kind == LN_KIND_I8) quantize_nchw_kernel<LN_KIND_I8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(x, (uint8_t*)y, N, C, H, W, cstride, inv_s);
+    else quantize_nchw_kernel<LN_KIND_F8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(x, (uint8_t*)y, N, C, H, W, cstride, inv_s);
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+// ---- C ABI -----------------------------------------------------------------------------------
+
+extern "C" {
+
+int32_t ln_tensor_upload_q(ln_ctx* ctx, const int64_t shape[4], const float* host, float scale, int32_t dtype, ln_tensor** out) {
+    if (!ctx || !shape || !host || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_upload_q: NULL argument");
+    if (dtype != LN_Q8 && dtype != LN_F8) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_upload_q: dtype must be LN_Q8 or LN_F8");
+    if (!(scale > 0.0f)) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_upload_q: scale must be positive");
+    ln_tensor* f = nullptr;
+    int rc = ln_tensor_upload_f32(ctx, shape, host, &f);
+    if (rc) return rc;
+    rc = ln_tensor_narrow_f32(ctx, f, scale, dtype, out);
+    ln_tensor_release(f);
+    return rc;
+}
+
+int32_t ln_tensor_narrow_f32(ln_ctx* ctx, const ln_tensor* t, float scale, int32_t dtype, ln_tensor** out_q) {
+    if (!ctx || !t || !out_q) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_narrow_f32: NULL argument");
+    if (t->dtype != LN_F32) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_narrow_f32: f32 tensor required");
+    if (dtype != LN_Q8 && dtype != LN_F8) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_narrow_f32: dtype must be LN_Q8 or LN_F8");
+    if (!(scale > 0.0f)) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_narrow_f32: scale must be positive");
+    cudaSetDevice(ctx->device);
+    ln_tensor* q = ln_tensor_new(ctx, dtype, t->n, t->c, t->h, t->w);
+    if (!q) return LN_ERR_CUDA;
+    q->scale = scale;
+    int rc = ln_q_quantize_launch(ctx, kind_of(dtype), (const float*)t->ptr, q->ptr, t->n, (int)t->c, (int)t->h, (int)t->w, q->cstride, 1.0f / scale);
+    if (rc) { ln_tensor_release(q); return rc; }
+    *out_q = q;
+    return LN_OK;
+}
+
+int32_t ln_tensor_widen_q(ln_ctx* ctx, const ln_tensor* t, ln_tensor** out_f32) {
+    if (!ctx || !out_f32) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_widen_q: NULL argument");
+    if (!is_q(t)) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_widen_q: 8-bit tensor required");
+    cudaSetDevice(ctx->device);
+    ln_tensor* f = ln_tensor_new(ctx, LN_F32, t->n, t->c, t->h, t->w);
+    if (!f) return LN_ERR_CUDA;
+    if (t->dtype == LN_Q8)
+        dequantize_nhwc_kernel<LN_KIND_I8><<<grid_for(ctx, f->count()), kThreads, 0, ctx->stream>>>((const uint8_t*)t->ptr, (float*)f->ptr, t->n, (int)t->c, (int)t->h, (int)t->w, t->cstride, t->scale);
+    else
+        dequantize_nhwc_kernel<LN_KIND_F8><<<grid_for(ctx, f->count()), kThreads, 0, ctx->stream>>>((const uint8_t*)t->ptr, (float*)f->ptr, t->n, (int)t->c, (int)t->h, (int)t->w, t->cstride, t->scale);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ln_tensor_release(f); return ln_fail(ctx, LN_ERR_CUDA, "widen launch: %s", cudaGetErrorString(e)); }
+    *out_f32 = f;
+    return LN_OK;
+}
+
+int32_t ln_tensor_download_q(ln_ctx* ctx, const ln_tensor* t, void* host_codes, int64_t count, float* scale) {
+    if (!ctx || !host_codes) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_download_q: NULL argument");
+    if (!is_q(t)) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_download_q: 8-bit tensor required");
+    if (count != t->count()) return ln_fail(ctx, LN_ERR_SHAPE, "download of %lld codes from a tensor of %lld", (long long)count, (long long)t->count());
+    cudaSetDevice(ctx->device);
+    void* tmp = ln_pool_alloc(ctx, (size_t)count);
+    if (!tmp) return LN_ERR_CUDA;
+    codes_nhwc_to_nchw_kernel<<<grid_for(ctx, count), kThreads, 0, ctx->stream>>>((const uint8_t*)t->ptr, (uint8_t*)tmp, t->n, (int)t->c, (int)t->h, (int)t->w, t->cstride);
+    ctx->launches++;
+    cudaError_t e = cudaMemcpyAsync(host_codes, tmp, (size_t)count, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    ln_pool_free(ctx, tmp, (size_t)count);
+    if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "download_q: %s", cudaGetErrorString(e));
+    if (scale) *scale = t->scale;
+    return LN_OK;
+}
+
+int32_t ln_tensor_upload_codes(ln_ctx* ctx, const int64_t shape[4], const void* host_codes, float scale, int32_t dtype, ln_tensor** out) {
+    if (!ctx || !shape || !host_codes || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_upload_codes: NULL argument");
+    if (dtype != LN_Q8 && dtype != LN_F8) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_upload_codes: dtype must be LN_Q8 or LN_F8");
+    cudaSetDevice(ctx->device);
+    ln_tensor* q = ln_tensor_new(ctx, dtype, shape[0], shape[1], shape[2], shape[3]);
+    if (!q) return LN_ERR_SHAPE;
+    q->scale = scale;
+    const int64_t count = q->count();
+    void* tmp = ln_pool_alloc(ctx, (size_t)count);
+    if (!tmp) { ln_tensor_release(q); return LN_ERR_CUDA; }
+    cudaError_t e = cudaMemcpyAsync(tmp, host_codes, (size_t)count, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) {
+        codes_nchw_to_nhwc_kernel<<<grid_for(ctx, q->n * q->h * q->w * q->cstride), kThreads, 0, ctx->stream>>>((const uint8_t*)tmp, (uint8_t*)q->ptr, q->n, (int)q->c, (int)q->h, (int)q->w, q->cstride);
+        ctx->launches++;
+        e = cudaGetLastError();
+    }
+    ln_pool_free(ctx, tmp, (size_t)count);
+    if (e != cudaSuccess) { ln_tensor_release(q); return ln_fail(ctx, LN_ERR_CUDA, "upload_codes: %s", cudaGetErrorString(e)); }
+    *out = q;
+    return LN_OK;
+}
+
+int32_t ln_conv_weights_q(ln_ctx* ctx, const ln_tensor* weights_f32, int64_t filters, int64_t channels, int64_t kernel_size, int32_t dtype,
+                          ln_conv_weights** out) {
+    if (!ctx || !weights_f32 || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_conv_weights_q: NULL argument");
+    if (weights_f32->dtype != LN_F32) return ln_fail(ctx, LN_ERR_ARG, "ln_conv_weights_q: f32 weights required");
+    if (dtype != LN_Q8 && dtype != LN_F8) return ln_fail(ctx, LN_ERR_ARG, "ln_conv_weights_q: dtype must be LN_Q8 or LN_F8");
+    if (filters < 1 || channels < 1 || kernel_size < 1 || weights_f32->count() != filters * channels * kernel_size * kernel_size)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_conv_weights_q: weight tensor has %lld elements, expected %lld", (long long)weights_f32->count(),
+                       (long long)(filters * channels * kernel_size * kernel_size));
+    cudaSetDevice(ctx->device);
+    ln_conv_weights* w = new ln_conv_weights();
+    w->ctx = ctx; w->dtype = dtype;
+    w->filters = filters; w->channels = channels; w->k = kernel_size;
+    w->cpad = ln_round_up(channels, 32);
+    w->fpad = ln_round_up(filters, ln_conv_choose_bn(filters));
+    const size_t packed_bytes = (size_t)(w->fpad * kernel_size * kernel_size * w->cpad);
+    const size_t oihw_bytes = (size_t)(filters * channels * kernel_size * kernel_size);
+    w->w = ln_pool_alloc(ctx, packed_bytes);
+    w->w_oihw = ln_pool_alloc(ctx, oihw_bytes);
+    w->wscale = (float*)ln_pool_alloc(ctx, (size_t)w->fpad * 4);
+    if (!w->w || !w->w_oihw || !w->wscale) { ln_conv_weights_release(w); return LN_ERR_CUDA; }
+    if (dtype == LN_Q8)
+        pack_weights_kernel<LN_KIND_I8><<<(int)w->fpad, 256, 0, ctx->stream>>>((const float*)weights_f32->ptr, (int)filters, (int)channels, (int)kernel_size, (int)w->cpad, (uint8_t*)w->w, (uint8_t*)w->w_oihw, w->wscale);
+    else
+        pack_weights_kernel<LN_KIND_F8><<<(int)w->fpad, 256, 0, ctx->stream>>>((const float*)weights_f32->ptr, (int)filters, (int)channels, (int)kernel_size, (int)w->cpad, (uint8_t*)w->w, (uint8_t*)w->w_oihw, w->wscale);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    w->h_wscale.resize((size_t)w->fpad);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->h_wscale.data(), w->wscale, (size_t)w->fpad * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { ln_conv_weights_release(w); return ln_fail(ctx, LN_ERR_CUDA, "weight packing: %s", cudaGetErrorString(e)); }
+    *out = w;
+    return LN_OK;
+}
+
+int32_t ln_conv_weights_release(ln_conv_weights* w) {
+    if (!w) return LN_OK;
+    ln_ctx* ctx = w->ctx;
+    if (w->w) ln_pool_free(ctx, w->w, (size_t)(w->fpad * w->k * w->k * w->cpad));
+    if (w->w_oihw) ln_pool_free(ctx, w->w_oihw, (size_t)(w->filters * w->channels * w->k * w->k));
+    if (w->wscale) ln_pool_free(ctx, w->wscale, (size_t)w->fpad * 4);
+    delete w;
+    return LN_OK;
+}
+
+int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weights* weights, const ln_tensor* bias, const int64_t output_shape[4],
+                             int64_t channels, int64_t input_height, int64_t input_width, int64_t filters, int64_t kernel_size, int64_t stride_x,
+                             int64_t stride_y, int64_t dilation, int64_t padding, int64_t groups, int32_t activation, float y_scale, int32_t out_kind,
+                             ln_tensor** out) {
+    if (!ctx || !weights || !bias || !output_shape || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: NULL argument");
+    if (!is_q(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: 8-bit input required");
+    if (x->dtype != weights->dtype) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: input and weights have different 8-bit types");
+    if (bias->dtype != LN_F32 || bias->count() != filters) return ln_fail(ctx, LN_ERR_SHAPE, "ln_conv2d_bias_act_q: bias must be f32 [filters]");
+    if (groups != 1 || dilation != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_conv2d_bias_act_q: groups and dilation must be 1");
+    if (stride_x != stride_y || stride_x < 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_conv2d_bias_act_q: stride_x must equal stride_y");
+    if (x->c != channels || x->h != input_height || x->w != input_width || weights->channels != channels || weights->filters != filters || weights->k != kernel_size)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_conv2d_bias_act_q: geometry does not match the tensors");
+    if (activation < LN_ACT_LINEAR || activation > LN_ACT_RELU) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_conv2d_bias_act_q: activation %d is not on the detector path", activation);
+    if (out_kind < LN_OUT_Q || out_kind > LN_OUT_ACC) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: bad out_kind");
+    if (out_kind == LN_OUT_Q && !(y_scale > 0.0f)) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: y_scale must be positive");
+    int64_t oh = (input_height + 2 * padding - kernel_size < 0 ? 0 : input_height + 2 * padding - kernel_size) / stride_y + 1;
+    int64_t ow = (input_width + 2 * padding - kernel_size < 0 ? 0 : input_width + 2 * padding - kernel_size) / stride_x + 1;
+    if (output_shape[0] != x->n || output_shape[1] != filters || output_shape[2] != oh || output_shape[3] != ow)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_conv2d_bias_act_q: output_shape does not match [%lld,%lld,%lld,%lld]", (long long)x->n, (long long)filters, (long long)oh, (long long)ow);
+    cudaSetDevice(ctx->device);
+    const int kind = kind_of(x->dtype);
+    int out_dtype = out_kind == LN_OUT_Q ? x->dtype : (out_kind == LN_OUT_F32 ? LN_F32 : (kind == LN_KIND_I8 ? LN_I32 : LN_F32));
+    ln_tensor* y = ln_tensor_new(ctx, out_dtype, x->n, filters, oh, ow);
+    if (!y) return LN_ERR_CUDA;
+    if (out_kind == LN_OUT_Q) {
+        y->scale = y_scale;
+        if (y->cstride != y->c) cudaMemsetAsync(y->ptr, 0, y->bytes, ctx->stream);
+    }
+    float2* mb = (float2*)ln_pool_alloc(ctx, (size_t)weights->fpad * sizeof(float2));
+    if (!mb) { ln_tensor_release(y); return LN_ERR_CUDA; }
+    int rc = ln_conv_umma_make_mb(ctx, weights->wscale, (const float*)bias->ptr, x->scale, (int)filters, (int)weights->fpad, mb);
+    ln_conv_geom g;
+    g.kind = kind;
+    g.x = x->ptr; g.x_pixel_stride = x->cstride;
+    g.N = (int)x->n; g.H = (int)x->h; g.W = (int)x->w; g.C = (int)x->c; g.cpad = (int)weights->cpad;
+    g.w = weights->w; g.F = (int)filters; g.fpad = (int)weights->fpad; g.k = (int)kernel_size; g.stride = (int)stride_x; g.pad = (int)padding;
+    g.OH = (int)oh; g.OW = (int)ow; g.act = activation; g.out_kind = out_kind;
+    g.inv_sy = out_kind == LN_OUT_Q ? 1.0f / y_scale : 1.0f;
+    g.out = y->ptr; g.out_pixel_stride = y->cstride;
+    if (rc == LN_OK) {
+        if (x->cstride >= weights->cpad && ln_conv_umma_supported(weights->cpad, kernel_size, stride_x, stride_y, dilation, groups, input_width, input_height)) {
+            ln_conv_umma_plan plan;
+            plan.mb = mb;
+            rc = ln_conv_umma_plan_build(ctx, &plan, g);
+            if (rc == LN_OK) rc = ln_conv_umma_launch(ctx, &plan);
+            if (rc == LN_OK) rc = ln_check_status(ctx, "ln_conv2d_bias_act_q");
+        } else {
+            rc = ln_conv_simt_launch(ctx, g, nullptr, mb);
+        }
+    }
+    ln_pool_free(ctx, mb, (size_t)weights->fpad * sizeof(float2));
+    if (rc) { ln_tensor_release(y); return rc; }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_maxpool_q(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height, int64_t input_width,
+                     int64_t size, int64_t stride_x, int64_t stride_y, int64_t padding, ln_tensor** out) {
+    if (!ctx || !output_shape || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_maxpool_q: NULL argument");
+    if (!is_q(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_maxpool_q: 8-bit tensor required");
+    if (x->c != channels || x->h != input_height || x->w != input_width || size < 1 || stride_x < 1 || stride_y < 1)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_maxpool_q: geometry does not match the input tensor");
+    int64_t oh = (input_height + padding - size < 0 ? 0 : input_height + padding - size) / stride_y + 1;
+    int64_t ow = (input_width + padding - size < 0 ? 0 : input_width + padding - size) / stride_x + 1;
+    if (output_shape[0] != x->n || output_shape[1] != channels || output_shape[2] != oh || output_shape[3] != ow)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_maxpool_q: output_shape does not match pool_dim (%lld x %lld)", (long long)oh, (long long)ow);
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, x->dtype, x->n, channels, oh, ow);
+    if (!y) return LN_ERR_CUDA;
+    y->scale = x->scale;
+    int rc = ln_q_maxpool_launch(ctx, kind_of(x->dtype), x->ptr, x->cstride, y->ptr, y->cstride, x->n, (int)channels, (int)input_height, (int)input_width,
+                                 (int)oh, (int)ow, (int)size, (int)stride_x, (int)stride_y, (int)padding);
+    if (rc) { ln_tensor_release(y); return rc; }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_upsample_q(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height, int64_t input_width,
+                      int64_t stride, float scale, int32_t reverse, ln_tensor** out) {
+    if (!ctx || !output_shape || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_upsample_q: NULL argument");
+    if (!is_q(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_upsample_q: 8-bit tensor required");
+    if (stride < 1) return ln_fail(ctx, LN_ERR_SHAPE, "ln_upsample_q: upsample stride cannot be zero");
+    if (reverse) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_upsample_q: reverse up-sampling is only available in f32");
+    if (!(scale > 0.0f)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_upsample_q: scale must be positive");
+    if (x->c != channels || x->h != input_height || x->w != input_width) return ln_fail(ctx, LN_ERR_SHAPE, "ln_upsample_q: geometry does not match the input tensor");
+    if (output_shape[0] != x->n || output_shape[1] != channels || output_shape[2] != input_height * stride || output_shape[3] != input_width * stride)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_upsample_q: output_shape does not match");
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, x->dtype, x->n, channels, input_height * stride, input_width * stride);
+    if (!y) return LN_ERR_CUDA;
+    y->scale = x->scale * scale;  // out = scale * in: the codes are unchanged, the tensor scale carries the factor
+    int rc = ln_q_upsample_launch(ctx, x->ptr, x->cstride, y->ptr, y->cstride, x->n, (int)channels, (int)input_height, (int)input_width, (int)stride);
+    if (rc) { ln_tensor_release(y); return rc; }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_route_concat_q(ln_ctx* ctx, const ln_tensor* const* inputs, int32_t n_inputs, const int64_t* input_channel_offsets,
+                          const int64_t* input_channels, const int64_t* input_total_channels, const int64_t output_shape[4], int64_t channel_stride,
+                          ln_tensor** out) {
+    if (!ctx || !out || !inputs || !input_channel_offsets || !input_channels || !input_total_channels || !output_shape || n_inputs < 1)
+        return ln_fail(ctx, LN_ERR_ARG, "ln_route_concat_q: NULL argument");
+    int64_t sum = 0;
+    for (int i = 0; i < n_inputs; ++i) {
+        if (!is_q(inputs[i]) || inputs[i]->dtype != inputs[0]->dtype) return ln_fail(ctx, LN_ERR_ARG, "ln_route_concat_q: input %d is not an 8-bit tensor of the common type", i);
+        if (inputs[i]->scale != inputs[0]->scale) return ln_fail(ctx, LN_ERR_ARG, "ln_route_concat_q: inputs must share one scale (input %d has %g, input 0 has %g)", i, inputs[i]->scale, inputs[0]->scale);
+        if (inputs[i]->c != input_total_channels[i] || input_channel_offsets[i] + input_channels[i] > input_total_channels[i] ||
+            inputs[i]->h * inputs[i]->w != channel_stride || inputs[i]->n != output_shape[0])
+            return ln_fail(ctx, LN_ERR_SHAPE, "ln_route_concat_q: input %d does not match its channel slice / plane size", i);
+        sum += input_channels[i];
+    }
+    if (sum != output_shape[1] || output_shape[2] * output_shape[3] != channel_stride)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_route_concat_q: slices sum to %lld channels, output has %lld", (long long)sum, (long long)output_shape[1]);
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, inputs[0]->dtype, output_shape[0], output_shape[1], output_shape[2], output_shape[3]);
+    if (!y) return LN_ERR_CUDA;
+    y->scale = inputs[0]->scale;
+    if (y->cstride != y->c) cudaMemsetAsync(y->ptr, 0, y->bytes, ctx->stream);
+    int64_t c0 = 0;
+    for (int i = 0; i < n_inputs; ++i) {
+        int rc = ln_q_copy_launch(ctx, (const uint8_t*)inputs[i]->ptr + input_channel_offsets[i], inputs[i]->cstride, (uint8_t*)y->ptr + c0, y->cstride,
+                                  y->n * channel_stride, (int)input_channels[i]);
+        if (rc) { ln_tensor_release(y); return rc; }
+        c0 += input_channels[i];
+    }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_shortcut_add_act_q(ln_ctx* ctx, const ln_tensor* a, const ln_tensor* b, int32_t activation, float y_scale, ln_tensor** out) {
+    if (!ctx || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_shortcut_add_act_q: NULL argument");
+    if (!is_q(a) || !is_q(b) || a->dtype != b->dtype) return ln_fail(ctx, LN_ERR_ARG, "ln_shortcut_add_act_q: two 8-bit tensors of one type required");
+    if (a->n != b->n || a->c != b->c || a->h != b->h || a->w != b->w) return ln_fail(ctx, LN_ERR_SHAPE, "ln_shortcut_add_act_q: shapes differ (use the f32 path to fit mismatched sources)");
+    if (!(y_scale > 0.0f)) return ln_fail(ctx, LN_ERR_ARG, "ln_shortcut_add_act_q: y_scale must be positive");
+    if (activation < LN_ACT_LINEAR || activation > LN_ACT_RELU) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_shortcut_add_act_q: activation %d is not on the detector path", activation);
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, a->dtype, a->n, a->c, a->h, a->w);
+    if (!y) return LN_ERR_CUDA;
+    y->scale = y_scale;
+    if (y->cstride != ln_round_up(y->c, 4)) cudaMemsetAsync(y->ptr, 0, y->bytes, ctx->stream);
+    int rc = ln_q_shortcut_launch(ctx, kind_of(a->dtype), a->ptr, a->cstride, a->scale, b->ptr, b->cstride, b->scale, y->ptr, y->cstride, a->n * a->h * a->w,
+                                  (int)a->c, activation, 1.0f / y_scale);
+    if (rc) { ln_tensor_release(y); return rc; }
+    *out = y;
+    return LN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,221 @@
+// Context, device-memory pool and tensor handles of liblightnet_b200.
+#include <cstring>
+
+#include "ln_common.h"
+
+static thread_local std::string g_create_error;
+
+int ln_fail(ln_ctx* ctx, int code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->err = buf;
+    else g_create_error = buf;
+    return code;
+}
+
+void* ln_pool_alloc(ln_ctx* ctx, size_t bytes) {
+    bytes = (size_t)ln_round_up((int64_t)(bytes ? bytes : 1), 512);
+    auto it = ctx->free_blocks.find(bytes);
+    if (it != ctx->free_blocks.end()) {
+        void* p = it->second;
+        ctx->free_blocks.erase(it);
+        return p;
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+        // release cached blocks once and retry
+        for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
+        ctx->free_blocks.clear();
+        (void)cudaGetLastError();
+        e = cudaMalloc(&p, bytes);
+        if (e != cudaSuccess) {
+            ln_fail(ctx, LN_ERR_CUDA, "cudaMalloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+    }
+    ctx->pool_bytes += bytes;
+    return p;
+}
+
+void ln_pool_free(ln_ctx* ctx, void* p, size_t bytes) {
+    if (!p) return;
+    bytes = (size_t)ln_round_up((int64_t)(bytes ? bytes : 1), 512);
+    ctx->free_blocks.emplace(bytes, p);
+}
+
+static size_t storage_bytes(int dtype, int64_t n, int64_t c, int64_t h, int64_t w, int64_t* cstride) {
+    if (dtype == LN_Q8 || dtype == LN_F8) {
+        *cstride = ln_round_up(c, 32);
+        return (size_t)(n * h * w * *cstride);
+    }
+    *cstride = 0;
+    return (size_t)(n * c * h * w) * 4;
+}
+
+ln_tensor* ln_tensor_new(ln_ctx* ctx, int dtype, int64_t n, int64_t c, int64_t h, int64_t w) {
+    if (n <= 0 || c <= 0 || h <= 0 || w <= 0) {
+        ln_fail(ctx, LN_ERR_SHAPE, "tensor shape [%lld,%lld,%lld,%lld] has a non-positive extent", (long long)n, (long long)c,
+                (long long)h, (long long)w);
+        return nullptr;
+    }
+    ln_tensor* t = new ln_tensor();
+    t->ctx = ctx;
+    t->dtype = dtype;
+    t->n = n; t->c = c; t->h = h; t->w = w;
+    t->bytes = storage_bytes(dtype, n, c, h, w, &t->cstride);
+    t->base = ln_pool_alloc(ctx, t->bytes);
+    if (!t->base) { delete t; return nullptr; }
+    t->ptr = t->base;
+    return t;
+}
+
+ln_tensor* ln_tensor_view_q(ln_tensor* parent, int64_t channel_offset, int64_t channels) {
+    ln_tensor* t = new ln_tensor(*parent);
+    t->refcount = 1;
+    t->base = nullptr;
+    t->bytes = 0;
+    t->parent = parent;
+    parent->refcount++;
+    t->c = channels;
+    t->ptr = (char*)parent->ptr + channel_offset;
+    return t;
+}
+
+extern "C" {
+
+int32_t ln_ctx_create(int32_t device, ln_ctx** out) {
+    if (!out) return ln_fail(nullptr, LN_ERR_ARG, "ln_ctx_create: out is NULL");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        (void)cudaGetLastError();
+        return ln_fail(nullptr, LN_ERR_CUDA, "no usable CUDA device (%s); this backend has no CPU fallback",
+                       e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+    }
+    if (device < 0 || device >= count) return ln_fail(nullptr, LN_ERR_ARG, "device %d out of range (%d devices)", device, count);
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess) return ln_fail(nullptr, LN_ERR_CUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return ln_fail(nullptr, LN_ERR_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    if (prop.major != 10) return ln_fail(nullptr, LN_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    ln_ctx* ctx = new ln_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete ctx; return ln_fail(nullptr, LN_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
+    e = cudaMalloc(&ctx->d_status, 64);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->d_status, 0, 64, ctx->stream);
+    if (e == cudaSuccess) e = cudaMallocHost(&ctx->h_status, 64);
+    if (e != cudaSuccess) { delete ctx; return ln_fail(nullptr, LN_ERR_CUDA, "status word allocation: %s", cudaGetErrorString(e)); }
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || !fn) { delete ctx; return ln_fail(nullptr, LN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
+    ctx->encode_tiled = (ln_encode_tiled_fn)fn;
+    *out = ctx;
+    return LN_OK;
+}
+
+int32_t ln_ctx_destroy(ln_ctx* ctx) {
+    if (!ctx) return LN_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return LN_OK;
+}
+
+const char* ln_last_error(ln_ctx* ctx) { return ctx ? ctx->err.c_str() : g_create_error.c_str(); }
+
+int32_t ln_sync(ln_ctx* ctx) {
+    if (!ctx) return LN_ERR_ARG;
+    LN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return LN_OK;
+}
+
+void* ln_ctx_stream(ln_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int32_t ln_ctx_set_exact_epilogue(ln_ctx* ctx, int32_t on) {
+    if (!ctx) return LN_ERR_ARG;
+    ctx->exact_epilogue = on != 0;
+    return LN_OK;
+}
+
+int64_t ln_ctx_launch_count(ln_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t ln_tensor_upload_f32(ln_ctx* ctx, const int64_t shape[4], const float* host, ln_tensor** out) {
+    if (!ctx || !shape || !host || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_upload_f32: NULL argument");
+    cudaSetDevice(ctx->device);
+    ln_tensor* t = ln_tensor_new(ctx, LN_F32, shape[0], shape[1], shape[2], shape[3]);
+    if (!t) return ctx->err.find("cudaMalloc") != std::string::npos ? LN_ERR_CUDA : LN_ERR_SHAPE;
+    cudaError_t e = cudaMemcpyAsync(t->ptr, host, (size_t)t->count() * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e != cudaSuccess) { ln_tensor_release(t); return ln_fail(ctx, LN_ERR_CUDA, "upload: %s", cudaGetErrorString(e)); }
+    *out = t;
+    return LN_OK;
+}
+
+int32_t ln_tensor_zeros_f32(ln_ctx* ctx, const int64_t shape[4], ln_tensor** out) {
+    if (!ctx || !shape || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_zeros_f32: NULL argument");
+    cudaSetDevice(ctx->device);
+    ln_tensor* t = ln_tensor_new(ctx, LN_F32, shape[0], shape[1], shape[2], shape[3]);
+    if (!t) return LN_ERR_SHAPE;
+    cudaError_t e = cudaMemsetAsync(t->ptr, 0, (size_t)t->count() * 4, ctx->stream);
+    if (e != cudaSuccess) { ln_tensor_release(t); return ln_fail(ctx, LN_ERR_CUDA, "memset: %s", cudaGetErrorString(e)); }
+    *out = t;
+    return LN_OK;
+}
+
+int32_t ln_tensor_download_f32(ln_ctx* ctx, const ln_tensor* t, float* host, int64_t count) {
+    if (!ctx || !t || !host) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_download_f32: NULL argument");
+    if (t->dtype != LN_F32) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_download_f32: tensor is not f32");
+    if (count != t->count()) return ln_fail(ctx, LN_ERR_SHAPE, "download of %lld elements from a tensor of %lld", (long long)count, (long long)t->count());
+    LN_CUDA(ctx, cudaMemcpyAsync(host, t->ptr, (size_t)count * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return LN_OK;
+}
+
+int32_t ln_tensor_download_i32(ln_ctx* ctx, const ln_tensor* t, int32_t* host, int64_t count) {
+    if (!ctx || !t || !host) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_download_i32: NULL argument");
+    if (t->dtype != LN_I32) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_download_i32: tensor is not int32");
+    if (count != t->count()) return ln_fail(ctx, LN_ERR_SHAPE, "download of %lld elements from a tensor of %lld", (long long)count, (long long)t->count());
+    LN_CUDA(ctx, cudaMemcpyAsync(host, t->ptr, (size_t)count * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return LN_OK;
+}
+
+int32_t ln_tensor_shape(const ln_tensor* t, int64_t shape[4]) {
+    if (!t || !shape) return LN_ERR_ARG;
+    shape[0] = t->n; shape[1] = t->c; shape[2] = t->h; shape[3] = t->w;
+    return LN_OK;
+}
+
+int32_t ln_tensor_dtype(const ln_tensor* t) { return t ? t->dtype : -1; }
+float ln_tensor_scale(const ln_tensor* t) { return t ? t->scale : 0.0f; }
+
+int32_t ln_tensor_retain(ln_tensor* t) {
+    if (!t) return LN_ERR_ARG;
+    t->refcount++;
+    return LN_OK;
+}
+
+int32_t ln_tensor_release(ln_tensor* t) {
+    if (!t) return LN_OK;
+    if (--t->refcount > 0) return LN_OK;
+    if (t->base) ln_pool_free(t->ctx, t->base, t->bytes);
+    ln_tensor* parent = t->parent;
+    delete t;
+    if (parent) ln_tensor_release(parent);
+    return LN_OK;
+}
+
+}  // extern "C"

@@ -991,6 +991,15 @@ int orc_net_layer_info(void* h, int i, int* info) {
     std::memcpy(info, v, sizeof v);
     return 0;
 }
+// Absolute source layers of a route / shortcut; yolo: mask entries.  Returns the count.
+int orc_net_layer_sources(void* h, int i, int* out, int max_out) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->layers.size()) return -1;
+    const Layer& L = n->layers[i];
+    const std::vector<int>& v = L.kind == K_YOLO ? L.mask : L.sources;
+    for (int k = 0; k < (int)v.size() && k < max_out; ++k) out[k] = v[k];
+    return (int)v.size();
+}
 void orc_net_dims(void* h, int* whcb) {
     Net* n = (Net*)h;
     whcb[0] = n->width; whcb[1] = n->height; whcb[2] = n->channels; whcb[3] = n->batch;

@@ -42,6 +42,7 @@ def lib():
         L.orc_net_num_layers.argtypes = [C.c_void_p]
         L.orc_net_layer_info.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
         L.orc_net_dims.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_net_layer_sources.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
         L.orc_net_weight_count.restype = C.c_longlong
         L.orc_net_weight_count.argtypes = [C.c_void_p]
         L.orc_net_set_weights.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong]
@@ -122,6 +123,9 @@ class Net:
                 "stride_y", "padding", "bn", "act"]
         d = dict(zip(keys, (int(x) for x in v)))
         d["kind"] = KIND[d["kind"]]
+        src = np.zeros(16, np.int32)
+        n = lib().orc_net_layer_sources(self.h, i, _p(src), 16)
+        d["sources"] = [int(x) for x in src[:n]]
         return d
 
     def layers(self):
