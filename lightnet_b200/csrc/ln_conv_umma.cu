@@ -22,7 +22,7 @@
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr uint32_t kWaitLimit = 1u << 23;
+constexpr uint32_t kWaitLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -1,0 +1,508 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.  Needs a B200: run with -m gpu.
+
+Bars: int32 accumulators of the int8 convolution bit-exact; int8 outputs bit-exact with the exact epilogue and
+within 1 code with the fast (hardware ex2/rcp) epilogue; f32 operators within the reference's own GPU tolerance
+1e-3 + 1e-3*|ref| (lightnet-cuda-oxide/tests/oxide_conv_parity.rs:12,38-47); decode bit-exact against the
+oracle's deterministic-exp decode; post-NMS records identical.
+"""
+import numpy as np
+import pytest
+
+import lightnet_b200 as ln
+from lightnet_b200 import synth, zoo
+from oracle import oracle_api as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be():
+    b = ln.B200Backend(0)
+    yield b
+    b.close()
+
+
+def conv_out(h, w, k, s, p):
+    return (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+
+
+# ---------------------------------------------------------------------------------------- f32 operators
+
+F32_CASES = [  # geometry cases of lightnet-cuda-oxide/tests/oxide_conv_parity.rs:106-121 (b,c,h,w,f,k,sx,sy,dil,pad,groups)
+    (2, 5, 7, 9, 6, 1, 1, 1, 1, 0, 1), (2, 3, 9, 11, 5, 3, 1, 1, 1, 1, 1), (1, 2, 8, 8, 3, 3, 1, 1, 1, 0, 1),
+    (1, 4, 13, 13, 6, 3, 2, 2, 1, 1, 1), (2, 3, 10, 12, 4, 3, 2, 1, 1, 1, 1), (3, 3, 15, 13, 5, 5, 2, 2, 1, 2, 1),
+    (2, 4, 9, 7, 6, 3, 1, 1, 1, 1, 2), (2, 6, 9, 9, 6, 3, 1, 1, 1, 1, 6), (2, 16, 10, 10, 70, 3, 1, 1, 1, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", F32_CASES)
+def test_conv2d_f32_matches_oracle(be, case):
+    b, c, h, w, f, k, sx, sy, dil, pad, g = case
+    if sx != sy:
+        pytest.skip("oracle helper takes one stride")
+    rng = np.random.default_rng(1)
+    x = rng.normal(0, 1, (b, c, h, w)).astype(np.float32)
+    wt = rng.normal(0, 0.3, (f, c // g, k, k)).astype(np.float32)
+    bias = rng.normal(0, 0.1, f).astype(np.float32)
+    oh, ow = conv_out(h, w, k, sx, pad)
+    tx, tw, tb = be.upload_f32(x.shape, x), be.upload_f32(wt.shape, wt), be.upload_f32((1, f, 1, 1), bias)
+    y = be.conv2d_f32(tx, tw, (b, f, oh, ow), c, h, w, f, k, sx, sy, dil, pad, g)
+    y = be.download_f32(be.bias_activation_f32(y, tb, f, oh * ow, "leaky"))
+    ref = orc.conv_f32(x, wt, bias, stride=sx, pad=pad, groups=g, act="leaky")
+    assert np.all(np.abs(y - ref) <= 1e-3 + 1e-3 * np.abs(ref))
+
+
+def test_f32_glue_matches_oracle(be):
+    rng = np.random.default_rng(2)
+    x = rng.normal(0, 1, (2, 6, 9, 11)).astype(np.float32)
+    tx = be.upload_f32(x.shape, x)
+    for size, sx, sy, padding in [(2, 2, 2, 1), (2, 1, 1, 1), (5, 1, 1, 4), (3, 2, 1, 1)]:
+        ref = orc.maxpool_f32(x, size, sx, sy, padding)
+        y = be.download_f32(be.maxpool_f32(tx, ref.shape, 6, 9, 11, size, sx, sy, padding))
+        assert np.array_equal(y, ref)
+    up = be.download_f32(be.upsample_f32(tx, (2, 6, 18, 22), 6, 9, 11, 2, 1.0, False))
+    assert np.array_equal(up, np.repeat(np.repeat(x, 2, 2), 2, 3))
+    x2 = rng.normal(0, 1, (2, 4, 9, 11)).astype(np.float32)
+    t2 = be.upload_f32(x2.shape, x2)
+    r = be.download_f32(be.route_concat_f32([tx, t2], [0, 0], [6, 4], [6, 4], (2, 10, 9, 11), 99))
+    assert np.array_equal(r, np.concatenate([x, x2], 1))
+    r = be.download_f32(be.route_concat_f32([tx], [3], [3], [6], (2, 3, 9, 11), 99))  # groups=2, group_id=1
+    assert np.array_equal(r, x[:, 3:])
+    s = be.download_f32(be.shortcut_add_f32(tx, tx))
+    assert np.array_equal(s, x + x)
+    fit = be.download_f32(be.shortcut_fit_f32(t2, 2, (2, 6, 9, 11)))
+    want = np.zeros((2, 6 * 99), np.float32)
+    want[:, : 4 * 99] = x2.reshape(2, -1)
+    assert np.array_equal(fit.reshape(2, -1), want)
+    for act in ("leaky", "mish", "swish", "logistic", "linear"):
+        a = be.download_f32(be.activation_f32(tx, act))
+        ref = np.array([orc.activate(act, v) for v in x.ravel()], np.float32).reshape(x.shape)
+        assert np.allclose(a, ref, rtol=2e-6, atol=2e-7), act
+
+
+def test_error_conventions(be):
+    x = be.upload_f32((1, 2, 4, 4), np.zeros(32, np.float32))
+    w = be.upload_f32((3, 2, 3, 3), np.zeros(54, np.float32))
+    with pytest.raises(ln.BackendError) as e:
+        be.conv2d_f32(x, w, (1, 3, 5, 5), 2, 4, 4, 3, 3, 1, 1, 1, 1, 1)  # wrong output shape
+    assert e.value.kind == "shape"
+    with pytest.raises(ln.BackendError) as e:
+        be.upsample_f32(x, (1, 2, 4, 4), 2, 4, 4, 0, 1.0, False)
+    assert "stride cannot be zero" in str(e.value)
+    with pytest.raises(ln.BackendError) as e:
+        ln.GpuExecutableNetwork(be, "[net]\nwidth=4\nheight=4\nchannels=1\n[route]\nlayers=0\n")
+    assert e.value.kind == "parse"
+    # the context stays usable after errors
+    assert be.download_f32(x).sum() == 0
+
+
+# ---------------------------------------------------------------------------------------- int8 convolution
+
+def quantized_conv_case(rng, n, c, h, w, f, k):
+    """Inputs of BASELINE config 2: weights N(0, 0.02) per-output-channel symmetric, activations leaky(N(0,1)) per tensor."""
+    wt = rng.normal(0, 0.02, (f, c, k, k)).astype(np.float32)
+    act = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    act = np.where(act > 0, act, np.float32(0.1) * act).astype(np.float32)
+    bias = rng.normal(0, 0.05, f).astype(np.float32)
+    sx = np.float32(np.abs(act).max() / 127.0)
+    return wt, act, bias, float(sx)
+
+
+Q8_CASES = [  # (n, c, h, w, f, k, stride, pad): BASELINE config-2 layer shapes at a batch the CPU oracle finishes quickly, plus edge shapes
+    (1, 256, 52, 52, 512, 3, 1, 1),
+    (2, 512, 52, 52, 256, 1, 1, 0),
+    (1, 128, 104, 104, 256, 3, 2, 1),
+    (3, 32, 19, 19, 64, 3, 1, 1),      # BK=32, ragged tiles
+    (2, 64, 38, 38, 255, 1, 1, 0),     # BK=64, filters not a multiple of the tile (head shape)
+    (1, 64, 13, 13, 32, 3, 2, 1),      # odd input, stride 2
+    (5, 128, 7, 5, 96, 3, 1, 1),       # tiny, batch-tiled
+    (1, 16, 20, 20, 32, 3, 1, 1),      # channels padded 16 -> 32
+]
+
+
+@pytest.mark.parametrize("case", Q8_CASES)
+def test_q8_conv_accumulators_bit_exact(be, case):
+    n, c, h, w, f, k, s, p = case
+    rng = np.random.default_rng(hash(case) & 0xFFFF)
+    wt, act, bias, sx = quantized_conv_case(rng, n, c, h, w, f, k)
+    oh, ow = conv_out(h, w, k, s, p)
+    tw = be.upload_f32(wt.shape, wt)
+    wq = be.conv_weights_q(tw, f, c, k, ln.LN_Q8)
+    tx = be.upload_q((n, c, h, w), act, sx, ln.LN_Q8)
+    tb = be.upload_f32((1, f, 1, 1), bias)
+    xq, sx_dev = be.download_q(tx)
+    assert sx_dev == np.float32(sx)
+    # the device quantiser is the oracle's
+    ref_xq = np.array([orc.lib().orc_quant_i8(float(v), float(np.float32(1.0) / np.float32(sx))) for v in act.ravel()[:4096]], np.int8)
+    assert np.array_equal(xq.ravel()[:4096], ref_xq)
+    # oracle weights: per-filter scale max|w|/127, code rne(w/s)
+    ws = (np.abs(wt.reshape(f, -1)).max(1) / np.float32(127.0)).astype(np.float32)
+    wq_ref = np.clip(np.rint(wt / ws[:, None, None, None]), -127, 127).astype(np.int8)
+    acc_ref = orc.conv_q8_acc(xq, wq_ref, s, p)
+    acc = be.download_i32(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, "linear", 1.0, ln.LN_OUT_ACC))
+    assert np.array_equal(acc, acc_ref)
+    # fused epilogue
+    mult = (np.float32(sx) * ws).astype(np.float32)
+    for act_name in ("leaky", "mish"):
+        a_ref, _ = orc.q8_epilogue(acc_ref, mult, bias, act_name, 1.0)
+        sy = np.float32(max(np.abs(a_ref).max(), 1e-6) / 127.0)
+        inv = float(np.float32(1.0) / sy)
+        a_ref, q_ref = orc.q8_epilogue(acc_ref, mult, bias, act_name, inv)
+        be.set_exact_epilogue(True)
+        q, _ = be.download_q(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, act_name, float(sy), ln.LN_OUT_Q))
+        assert np.array_equal(q, q_ref), act_name
+        head = be.download_f32(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, act_name, 1.0, ln.LN_OUT_F32))
+        assert np.array_equal(head, a_ref), act_name
+        be.set_exact_epilogue(False)
+        q, _ = be.download_q(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, act_name, float(sy), ln.LN_OUT_Q))
+        d = np.abs(q.astype(np.int32) - q_ref.astype(np.int32))
+        assert d.max() <= 1 and (d > 0).mean() < 1e-3, (act_name, d.max(), (d > 0).mean())
+
+
+def test_q8_glue_matches_oracle(be):
+    rng = np.random.default_rng(4)
+    codes = rng.integers(-127, 128, (3, 64, 19, 19), dtype=np.int8)
+    t = be.upload_codes(codes.shape, codes, 0.05, ln.LN_Q8)
+    back, s = be.download_q(t)
+    assert np.array_equal(back, codes) and s == np.float32(0.05)
+    for size, stride, padding in [(2, 2, 1), (2, 1, 1), (5, 1, 4), (9, 1, 8), (13, 1, 12)]:
+        ref = orc.maxpool_f32(codes.astype(np.float32), size, stride, stride, padding).astype(np.int8)
+        y, s = be.download_q(be.maxpool_q(t, ref.shape, 64, 19, 19, size, stride, stride, padding))
+        assert np.array_equal(y, ref) and s == np.float32(0.05)
+    up, _ = be.download_q(be.upsample_q(t, (3, 64, 38, 38), 64, 19, 19, 2, 1.0, False))
+    assert np.array_equal(up, np.repeat(np.repeat(codes, 2, 2), 2, 3))
+    c2 = rng.integers(-127, 128, (3, 32, 19, 19), dtype=np.int8)
+    t2 = be.upload_codes(c2.shape, c2, 0.05, ln.LN_Q8)
+    r, _ = be.download_q(be.route_concat_q([t2, t], [0, 0], [32, 64], [32, 64], (3, 96, 19, 19), 361))
+    assert np.array_equal(r, np.concatenate([c2, codes], 1))
+    r, _ = be.download_q(be.route_concat_q([t], [32], [32], [64], (3, 32, 19, 19), 361))
+    assert np.array_equal(r, codes[:, 32:])
+    with pytest.raises(ln.BackendError):
+        t3 = be.upload_codes(c2.shape, c2, 0.07, ln.LN_Q8)
+        be.route_concat_q([t3, t], [0, 0], [32, 64], [32, 64], (3, 96, 19, 19), 361)
+    # shortcut: quantise(act(a*sa + b*sb) / sy)
+    b2 = rng.integers(-127, 128, codes.shape, dtype=np.int8)
+    tb = be.upload_codes(codes.shape, b2, 0.03, ln.LN_Q8)
+    sy = np.float32(0.06)
+    y, _ = be.download_q(be.shortcut_add_act_q(t, tb, "linear", float(sy)))
+    v = codes.astype(np.float32) * np.float32(0.05)
+    v = (b2.astype(np.float32).astype(np.float64) * np.float64(np.float32(0.03)) + v.astype(np.float64)).astype(np.float32)  # fma
+    ref = np.clip(np.rint(v * (np.float32(1.0) / sy)), -127, 127).astype(np.int8)
+    assert np.array_equal(y, ref)
+
+
+# ---------------------------------------------------------------------------------------- decode + NMS
+
+def synth_heads(rng, batch, grids, classes, obj_mu=-4.0):
+    """Head tensors with the distributions of BASELINE config 5 (xy N(0,1), wh N(0,0.5), obj/class N(-4,2))."""
+    heads = []
+    for g in grids:
+        t = np.empty((batch, 3, 5 + classes, g, g), np.float32)
+        t[:, :, 0:2] = rng.normal(0, 1, (batch, 3, 2, g, g))
+        t[:, :, 2:4] = rng.normal(0, 0.5, (batch, 3, 2, g, g))
+        t[:, :, 4:] = rng.normal(obj_mu, 2, (batch, 3, 1 + classes, g, g))
+        heads.append(t.reshape(batch, 3 * (5 + classes), g, g))
+    return heads
+
+
+ANCH = [(10, 13), (16, 30), (33, 23), (30, 61), (62, 45), (59, 119), (116, 90), (156, 198), (373, 326)]
+
+
+@pytest.mark.parametrize("new_coords,letterbox", [(0, False), (0, True), (1, True)])
+def test_decode_bit_exact(be, new_coords, letterbox):
+    rng = np.random.default_rng(5)
+    grids, classes = [8, 4], 7
+    heads = synth_heads(rng, 2, grids, classes, obj_mu=-1.0)
+    if new_coords:
+        heads = [np.abs(np.tanh(h)).astype(np.float32) for h in heads]
+    specs = [dict(gw=g, gh=g, classes=classes, anchors=ANCH[3 * i:3 * i + 3], scale_x_y=1.1 + 0.1 * i, new_coords=new_coords) for i, g in enumerate(grids)]
+    dev = [dict(raw=be.upload_f32(h.shape, h), classes=classes, anchors=s["anchors"], scale_x_y=s["scale_x_y"], new_coords=new_coords)
+           for h, s in zip(heads, specs)]
+    for img in range(2):
+        ref = orc.decode_only([h[img] for h in heads], specs, 64, 64, 100, 75, 0.05, letterbox=letterbox, det_exp=True)
+        got = be.yolo_decode_only(dev, img, 64, 64, 100, 75, 0.05, letterbox)
+        assert got.shape == ref.shape and ref.shape[0] > 50
+        assert np.array_equal(got, ref)
+        # and the deterministic exp stays within a few ulp of the reference's libm decode
+        lib = orc.decode_only([h[img] for h in heads], specs, 64, 64, 100, 75, 0.05, letterbox=letterbox, det_exp=False)
+        if lib.shape == ref.shape:
+            assert np.allclose(lib, ref, rtol=3e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("thr,nms,top_k,maxper", [(0.25, 0.45, 0, 1024), (0.001, 0.65, 300, 300), (0.05, 0.3, 0, 4096), (0.3, 0.45, 5, 64)])
+def test_decode_nms_records_identical(be, thr, nms, top_k, maxper):
+    rng = np.random.default_rng(6)
+    grids, classes = [20, 10, 5], 12
+    batch = 3
+    heads = synth_heads(rng, batch, grids, classes, obj_mu=-2.0)
+    heads[0][1] = heads[0][0]  # image 1 repeats image 0 on one head: exercises ties across images of equal score
+    specs = [dict(gw=g, gh=g, classes=classes, anchors=ANCH[3 * i:3 * i + 3], scale_x_y=1.0, new_coords=0) for i, g in enumerate(grids)]
+    dev = [dict(raw=be.upload_f32(h.shape, h), classes=classes, anchors=s["anchors"], scale_x_y=1.0, new_coords=0) for h, s in zip(heads, specs)]
+    iw, ih = [320, 200, 640], [240, 200, 360]
+    got = be.yolo_decode_nms(dev, 160, 160, iw, ih, thr, nms, True, top_k, maxper)
+    for img in range(batch):
+        hs = [h[img] for h in heads]
+        ref = orc.decode_nms(hs, specs, 160, 160, iw[img], ih[img], thr, nms, letterbox=True, top_k=top_k, det_exp=True)
+        ref_skip = orc.decode_nms(hs, specs, 160, 160, iw[img], ih[img], thr, nms, letterbox=True, top_k=top_k, det_exp=True, skip_pass1=True)
+        assert np.array_equal(ref, ref_skip)  # the IoU > 1.0 pre-pass is a no-op on this input
+        ref = ref[:maxper]
+        assert got[img].shape == ref.shape, (img, got[img].shape, ref.shape)
+        assert np.array_equal(got[img], ref)
+
+
+def test_decode_nms_many_ties(be):
+    """Constant heads: every candidate has the same score, so ordering is decided purely by emission order and the
+    radix selection has to descend to the last digit."""
+    classes, g = 3, 16
+    h = np.zeros((1, 3 * (5 + classes), g, g), np.float32)
+    h[:, 4::8] = 2.0
+    h[:, 5::8] = 1.0
+    specs = [dict(gw=g, gh=g, classes=classes, anchors=ANCH[:3], scale_x_y=1.0, new_coords=0)]
+    dev = [dict(raw=be.upload_f32(h.shape, h), classes=classes, anchors=ANCH[:3], scale_x_y=1.0, new_coords=0)]
+    got = be.yolo_decode_nms(dev, 128, 128, 128, 128, 0.1, 0.45, False, 0, 2048)[0]
+    ref = orc.decode_nms([h[0]], specs, 128, 128, 128, 128, 0.1, 0.45, letterbox=False, det_exp=True)
+    assert ref.shape[0] > 10
+    assert np.array_equal(got, ref)
+
+
+def test_decode_nms_empty_and_errors(be):
+    h = np.full((2, 3 * 6, 4, 4), -20.0, np.float32)
+    dev = [dict(raw=be.upload_f32(h.shape, h), classes=1, anchors=ANCH[:3], scale_x_y=1.0, new_coords=0)]
+    got = be.yolo_decode_nms(dev, 32, 32, 32, 32)
+    assert [g.shape[0] for g in got] == [0, 0]
+    bad = [dict(raw=be.upload_f32(h.shape, h), classes=2, anchors=ANCH[:3], scale_x_y=1.0, new_coords=0)]
+    with pytest.raises(ln.BackendError) as e:
+        be.yolo_decode_nms(bad, 32, 32, 32, 32)
+    assert "length mismatch" in str(e.value)
+    with pytest.raises(ln.BackendError):
+        be.yolo_decode_nms(dev, 32, 32, 0, 32)
+
+
+# ---------------------------------------------------------------------------------------- whole networks
+
+MINI_CFG = """
+[net]
+batch=4
+width=64
+height=48
+channels=3
+[convolutional]
+batch_normalize=1
+filters=32
+size=3
+stride=1
+pad=1
+activation=mish
+[convolutional]
+batch_normalize=1
+filters=64
+size=3
+stride=2
+pad=1
+activation=mish
+[convolutional]
+batch_normalize=1
+filters=64
+size=1
+stride=1
+pad=1
+activation=mish
+[route]
+layers=-2
+[convolutional]
+batch_normalize=1
+filters=64
+size=1
+stride=1
+pad=1
+activation=mish
+[convolutional]
+batch_normalize=1
+filters=32
+size=1
+stride=1
+pad=1
+activation=leaky
+[convolutional]
+batch_normalize=1
+filters=64
+size=3
+stride=1
+pad=1
+activation=mish
+[shortcut]
+from=-3
+activation=linear
+[route]
+layers=-1,-6
+[convolutional]
+batch_normalize=1
+filters=128
+size=3
+stride=2
+pad=1
+activation=leaky
+[maxpool]
+size=5
+stride=1
+[route]
+layers=-2
+[maxpool]
+size=9
+stride=1
+[route]
+layers=-1,-3,-4
+[convolutional]
+batch_normalize=1
+filters=64
+size=1
+stride=1
+pad=1
+activation=swish
+[convolutional]
+filters=24
+size=1
+stride=1
+pad=1
+activation=linear
+[yolo]
+mask=0,1,2
+anchors=4,6, 8,10, 12,16, 20,24, 30,28, 40,44
+classes=3
+num=6
+scale_x_y=1.1
+[route]
+layers=-3
+[upsample]
+stride=2
+[route]
+layers=-1,8
+[convolutional]
+batch_normalize=1
+filters=64
+size=3
+stride=1
+pad=1
+activation=leaky
+[convolutional]
+filters=24
+size=1
+stride=1
+pad=1
+activation=logistic
+[yolo]
+mask=3,4,5
+anchors=4,6, 8,10, 12,16, 20,24, 30,28, 40,44
+classes=3
+num=6
+new_coords=1
+scale_x_y=2.0
+"""
+
+
+def check_f32_network(be, cfg, batch, seed):
+    o = orc.Net(cfg, batch)
+    blob = synth.he_weights(o.layers(), seed, bn_identity=False)
+    o.set_weights(blob)
+    x = synth.uniform_images(batch, o.channels, o.height, o.width, seed + 1)
+    o.forward_f32(x, folded=False)  # the reference's CPU path: unfolded batch norm
+    net = ln.GpuExecutableNetwork(be, cfg, batch, ln.LN_F32)
+    assert net.layers() == [{k: v for k, v in l.items() if k != "sources"} for l in o.layers()]
+    assert net.weight_count() == o.weight_count()
+    net.load_weights(blob)
+    net.forward(x)
+    for i in range(o.num_layers):
+        ref = o.layer_output_f32(i)
+        got = be.download_f32(net.layer_output(i))
+        # scale-normalised whole-network check of lightnet-cuda-oxide/tests/oxide_runtime_f16.rs:113-133, at f32 tolerance
+        assert np.abs(got - ref).max() <= 1e-4 * max(np.abs(ref).max(), 1e-6), i
+    return o, net, x
+
+
+def test_mini_network_f32(be):
+    o, net, x = check_f32_network(be, MINI_CFG, 4, 11)
+    dets = net.detect(x, 640, 480, 0.25, 0.45, True, 0, 512)
+    for b in range(4):
+        ref = o.detect("f32", b, 640, 480, 0.25, 0.45, True)
+        # identical detections up to float tolerance: same count unless a score sits on the threshold
+        assert abs(dets[b].shape[0] - ref.shape[0]) <= 2
+
+
+def test_yolov3_tiny_f32_config1(be):
+    """BASELINE config 1: yolov3-tiny 416, batch 1, He-normal weights, identity BN, uniform input."""
+    cfg = zoo.yolov3_tiny_cfg()
+    o = orc.Net(cfg, 1)
+    blob = synth.he_weights(o.layers(), 0)
+    o.set_weights(blob)
+    x = synth.uniform_images(1, 3, 416, 416, 1)
+    o.forward_f32(x)
+    net = ln.GpuExecutableNetwork(be, cfg, 1, ln.LN_F32)
+    net.load_weights(blob)
+    net.forward(x)
+    for k, layer in enumerate([16, 23]):
+        ref = o.layer_output_f32(layer)
+        got = be.download_f32(net.head(k))
+        assert np.abs(got - ref).max() <= 1e-4 * np.abs(ref).max()
+
+
+def check_q8_network(be, cfg, batch, seed, micro_batch=0):
+    o = orc.Net(cfg, batch)
+    blob = synth.he_weights(o.layers(), seed, bn_identity=False)
+    o.set_weights(blob)
+    x = synth.uniform_images(batch, o.channels, o.height, o.width, seed + 1)
+    net = ln.GpuExecutableNetwork(be, cfg, batch, ln.LN_Q8)
+    net.load_weights(blob)
+    net.calibrate(x)                       # f32 pass on the device
+    scales = net.scales()
+    o.forward_f32(x, folded=True)
+    o.calibrate()
+    assert np.allclose(scales, o.scales(), rtol=1e-4)   # the two calibrations agree to f32 rounding
+    o.set_scales(scales)                   # same quantised model on both sides
+    o.forward_q8(x)
+    # packed weights are the oracle's
+    be.set_exact_epilogue(True)
+    if micro_batch:
+        net.set_micro_batch(micro_batch)
+    net.forward(x)
+    return o, net, x
+
+
+def test_mini_network_q8_bit_exact(be):
+    o, net, x = check_q8_network(be, MINI_CFG, 4, 21)
+    for i, l in enumerate(o.layers()):
+        if l["kind"] == "yolo":
+            continue
+        if i + 1 < o.num_layers and o.layer_info(i + 1)["kind"] == "yolo":
+            assert np.array_equal(be.download_f32(net.layer_output(i)), o.head_q8(i)), i
+            continue
+        got, s = be.download_q(net.layer_output(i))
+        assert np.array_equal(got, o.layer_output_q8(i)), (i, l["kind"])
+    dets = net.detect(x, 640, 480, 0.2, 0.45, True, 0, 512)
+    for b in range(4):
+        ref = o.detect("q8", b, 640, 480, 0.2, 0.45, True, det_exp=True)
+        assert np.array_equal(dets[b], ref[:512])
+    be.set_exact_epilogue(False)
+
+
+def test_mini_network_q8_micro_batched_and_fast_epilogue(be):
+    o, net, x = check_q8_network(be, MINI_CFG, 4, 21, micro_batch=2)
+    heads_exact = [be.download_f32(net.head(k)) for k in range(net.num_heads())]
+    for k, layer in enumerate([16, 22]):
+        assert np.array_equal(heads_exact[k], o.head_q8(layer))
+    be.set_exact_epilogue(False)
+    net.forward(x)
+    for k in range(net.num_heads()):
+        got = be.download_f32(net.head(k))
+        assert np.abs(got - heads_exact[k]).max() <= 0.05 * np.abs(heads_exact[k]).max()
+
+
+def test_yolov3_tiny_q8_bit_exact(be):
+    o, net, x = check_q8_network(be, zoo.yolov3_tiny_cfg(), 1, 31)
+    for k, layer in enumerate([16, 23]):
+        assert np.array_equal(be.download_f32(net.head(k)), o.head_q8(layer))
+    # int8 heads track the f32 heads (scale-normalised, cf. oxide_runtime_f16.rs tolerance statement; int8 is coarser)
+    for k, layer in enumerate([16, 23]):
+        ref = o.layer_output_f32(layer)
+        got = be.download_f32(net.head(k))
+        assert np.abs(got - ref).max() <= 0.5 * np.abs(ref).max()
+    be.set_exact_epilogue(False)
