@@ -237,6 +237,12 @@ int32_t ln_net_detect_device(ln_net* net, const ln_tensor* input, const int32_t*
 /* Device time in ms of the most recent ln_net_forward* / ln_net_detect* call, by phase
    (0 = layers, 1 = decode+NMS), measured with CUDA events on the ctx stream. */
 int32_t ln_net_last_times(const ln_net* net, float times_ms[2]);
+/* Per-kernel timing of 8-bit forwards.  With profiling on, every launch of the plan is bracketed by CUDA events on
+   the ctx stream (the forward then synchronises).  ln_net_profile returns, for the last forward, device ms per layer
+   (per_layer_ms[num_layers]) and per kernel class (per_op_ms[8]: 0 tensor-core conv, 1 CUDA-core conv, 2 first-layer
+   conv, 3 max-pool, 4 up-sample, 5 route copy, 6 shortcut, 7 input quantise) and the launch count per class. */
+int32_t ln_net_set_profile(ln_net* net, int32_t on);
+int32_t ln_net_profile(const ln_net* net, float* per_layer_ms, int32_t num_layers, float per_op_ms[8], int32_t per_op_launches[8]);
 
 #ifdef __cplusplus
 }

@@ -109,6 +109,8 @@ SYMBOLS = {
     "ln_net_detect": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_detect_device": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_last_times": (C.c_int32, [_VP, _VP]),
+    "ln_net_set_profile": (C.c_int32, [_VP, C.c_int32]),
+    "ln_net_profile": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
 }
 
 
@@ -478,6 +480,19 @@ class GpuExecutableNetwork:
                       max_per_image=1024):
         return self._detect(self.lib.ln_net_detect_device, t.h, image_w, image_h, confidence_threshold, nms_threshold, letterbox,
                             top_k, max_per_image)
+
+    def set_profile(self, on: bool):
+        self.backend._check(self.lib.ln_net_set_profile(self.h, int(on)))
+
+    OP_CLASSES = ["conv_umma", "conv_simt", "conv_stem", "maxpool", "upsample", "route_copy", "shortcut", "quantize"]
+
+    def profile(self):
+        """(per-layer ms, {kernel class: (ms, launches)}) of the last profiled 8-bit forward."""
+        per_layer = np.zeros(self.num_layers, np.float32)
+        per_op = np.zeros(8, np.float32)
+        launches = np.zeros(8, np.int32)
+        self.backend._check(self.lib.ln_net_profile(self.h, _ptr(per_layer), self.num_layers, _ptr(per_op), _ptr(launches)))
+        return per_layer, {n: (float(per_op[i]), int(launches[i])) for i, n in enumerate(self.OP_CLASSES)}
 
     def last_times_ms(self):
         t = np.zeros(2, np.float32)

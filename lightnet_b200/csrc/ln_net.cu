@@ -240,6 +240,12 @@ struct ln_net {
     ln_tensor* input_dev = nullptr;    // staging for host inputs
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     float times_ms[2] = {0, 0};
+    // optional per-launch timing
+    bool profile = false;
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<float> prof_layer_ms;
+    float prof_op_ms[8] = {0};
+    int prof_op_launches[8] = {0};
 };
 
 namespace {
@@ -705,6 +711,16 @@ int run_plan(ln_net* net, const float* input_dev_f32) {
     const int mb = net->plan_mb;
     const int kind = net->precision == LN_F8 ? LN_KIND_F8 : LN_KIND_I8;
     const int64_t in_image = (int64_t)net->channels * net->height * net->width;
+    size_t ev_index = 0;
+    if (net->profile) {
+        const size_t need = net->steps.size() * (size_t)(net->batch / mb) + 1;
+        while (net->prof_events.size() < need) {
+            cudaEvent_t e;
+            LN_CUDA(ctx, cudaEventCreate(&e));
+            net->prof_events.push_back(e);
+        }
+        LN_CUDA(ctx, cudaEventRecord(net->prof_events[ev_index++], ctx->stream));
+    }
     for (int b0 = 0; b0 < net->batch; b0 += mb) {
         for (auto& st : net->steps) {
             const NLayer& L = net->layers[st.layer];
@@ -735,7 +751,23 @@ int run_plan(ln_net* net, const float* input_dev_f32) {
                 case 7: rc = ln_q_quantize_launch(ctx, kind, input_dev_f32 + b0 * in_image, st.y, mb, st.C, st.H, st.W, st.ys, st.inv_sy); break;
             }
             if (rc) return rc;
+            if (net->profile) LN_CUDA(ctx, cudaEventRecord(net->prof_events[ev_index++], ctx->stream));
         }
+    }
+    if (net->profile) {
+        LN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        net->prof_layer_ms.assign(net->layers.size(), 0.0f);
+        for (int i = 0; i < 8; ++i) { net->prof_op_ms[i] = 0; net->prof_op_launches[i] = 0; }
+        size_t e = 0;
+        for (int b0 = 0; b0 < net->batch; b0 += mb)
+            for (auto& st : net->steps) {
+                float ms = 0;
+                cudaEventElapsedTime(&ms, net->prof_events[e], net->prof_events[e + 1]);
+                ++e;
+                net->prof_layer_ms[st.layer] += ms;
+                net->prof_op_ms[st.op] += ms;
+                net->prof_op_launches[st.op] += 1;
+            }
     }
     return LN_OK;
 }
@@ -831,6 +863,7 @@ int32_t ln_net_destroy(ln_net* net) {
         ln_conv_weights_release(L.wq);
     }
     for (auto& e : net->ev) if (e) cudaEventDestroy(e);
+    for (auto& e : net->prof_events) cudaEventDestroy(e);
     delete net;
     return LN_OK;
 }
@@ -1037,6 +1070,22 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
     int rc = stage_input(net, input_host);
     if (rc) return rc;
     return ln_net_detect_device(net, net->input_dev, image_w, image_h, opts, records_host, counts_host);
+}
+
+int32_t ln_net_set_profile(ln_net* net, int32_t on) {
+    if (!net) return LN_ERR_ARG;
+    net->profile = on != 0;
+    return LN_OK;
+}
+
+int32_t ln_net_profile(const ln_net* net, float* per_layer_ms, int32_t num_layers, float per_op_ms[8], int32_t per_op_launches[8]) {
+    if (!net || !per_layer_ms || !per_op_ms || !per_op_launches) return LN_ERR_ARG;
+    if (num_layers != (int)net->layers.size() || net->prof_layer_ms.size() != net->layers.size())
+        return ln_fail(net->ctx, LN_ERR_ARG, "no profile: enable profiling and run an 8-bit forward first");
+    memcpy(per_layer_ms, net->prof_layer_ms.data(), (size_t)num_layers * 4);
+    memcpy(per_op_ms, net->prof_op_ms, sizeof net->prof_op_ms);
+    memcpy(per_op_launches, net->prof_op_launches, sizeof net->prof_op_launches);
+    return LN_OK;
 }
 
 int32_t ln_net_last_times(const ln_net* net, float times_ms[2]) {

@@ -183,77 +183,67 @@ __global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant_
     ImgState st = states[img];
     if (st.phase != PHASE_SELECT) return;
     __shared__ unsigned s_part[256];
-    __shared__ int s_bin;
-    __shared__ unsigned s_cum;
+    __shared__ unsigned s_h[kBins];
     unsigned* h = hist + (size_t)img * kBins;
     const int nb = 1 << level_bits(st.level);
-    const int per = kBins / 256;  // 16 bins per thread; thread t owns the bins from the top: [nb-1-16t-15, nb-1-16t]
-    unsigned mine[16];
+    const int per = kBins / 256;  // 16 bins per thread; thread t owns, from the top, bins nb-1-16t .. nb-1-16t-15
     unsigned sum = 0;
     for (int j = 0; j < per; ++j) {
-        const int bin = nb - 1 - (threadIdx.x * per + j);
-        mine[j] = bin >= 0 ? h[bin] : 0u;
-        sum += mine[j];
+        const int slot = threadIdx.x * per + j;  // slot 0 = top bin
+        const int bin = nb - 1 - slot;
+        const unsigned v = bin >= 0 ? h[bin] : 0u;
+        s_h[slot] = v;
+        sum += v;
         if (bin >= 0) h[bin] = 0u;
     }
     s_part[threadIdx.x] = sum;
-    if (threadIdx.x == 0) { s_bin = -1; s_cum = 0; }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        if (st.level == 0) {
-            int want = 4 * (p.k_eff - st.kept);
-            st.cap = want < 1024 ? 1024 : (want > kBandMax ? kBandMax : want);
-            st.above = 0;
-            st.prefix = 0;
-        }
-        const unsigned cap_left = (unsigned)(st.cap - st.above);
-        unsigned cum = 0;
-        int found = -1;
-        for (int t = 0; t < 256 && found < 0; ++t) {
-            if (cum + s_part[t] > cap_left) found = t;
-            else cum += s_part[t];
-        }
-        s_bin = found;
-        s_cum = cum;
+    if (threadIdx.x != 0) return;
+    // ---- one thread decides (a few hundred steps at most)
+    if (st.level == 0) {
+        int want = 4 * (p.k_eff - st.kept);
+        st.cap = want < 1024 ? 1024 : (want > kBandMax ? kBandMax : want);
+        st.above = 0;
+        st.prefix = 0;
     }
-    __syncthreads();
-    const int owner = s_bin;
+    const unsigned cap_left = (unsigned)(st.cap - st.above);
+    const int shift = level_shift(st.level), bits = level_bits(st.level);
+    unsigned cum = 0;
+    int owner = -1;
+    for (int t = 0; t < 256; ++t) {
+        if (cum + s_part[t] > cap_left) { owner = t; break; }
+        cum += s_part[t];
+    }
     if (owner < 0) {
-        if (threadIdx.x == 0) {
-            // everything that is left fits into one band
-            st.lo = st.level == 0 ? 0ull : (st.prefix << (level_shift(st.level) + level_bits(st.level)));
-            st.band_count = st.above + (int)s_cum;
-            st.exhausted = st.level == 0 ? 1 : 0;
-            st.phase = PHASE_BAND;
-            states[img] = st;
-        }
+        // everything that is left (under this prefix) fits into the band
+        st.lo = st.level == 0 ? 0ull : (st.prefix << (shift + bits));
+        st.band_count = st.above + (int)cum;
+        st.exhausted = st.level == 0 ? 1 : 0;
+        st.phase = PHASE_BAND;
+        states[img] = st;
         return;
     }
-    if ((int)threadIdx.x == owner) {
-        const unsigned cap_left = (unsigned)(st.cap - st.above);
-        unsigned cum = s_cum;
-        int b = -1;
-        for (int j = 0; j < per; ++j) {
-            if (cum + mine[j] > cap_left) { b = nb - 1 - (owner * per + j); break; }
-            cum += mine[j];
-        }
-        const int shift = level_shift(st.level), bits = level_bits(st.level);
-        const int total = st.above + (int)cum;
-        const bool last = st.level == kLevels - 1;
-        if (total >= st.cap / 4 || last) {
-            const unsigned long long base = st.level == 0 ? 0ull : (st.prefix << (shift + bits));
-            st.lo = base + ((unsigned long long)(b + 1) << shift);  // may carry into the prefix: that is the next digit up
-            st.band_count = total;
-            st.exhausted = 0;
-            st.phase = PHASE_BAND;
-        } else {
-            st.above = total;
-            st.prefix = (st.level == 0 ? 0ull : (st.prefix << bits)) | (unsigned long long)b;
-            st.level += 1;
-            atomicAdd(pending, 1);
-        }
-        states[img] = st;
+    int b = -1;
+    for (int j = 0; j < per; ++j) {
+        const int slot = owner * per + j;
+        if (cum + s_h[slot] > cap_left) { b = nb - 1 - slot; break; }
+        cum += s_h[slot];
     }
+    const int total = st.above + (int)cum;
+    const bool last = st.level == kLevels - 1;
+    if (total >= st.cap / 4 || last) {
+        const unsigned long long base = st.level == 0 ? 0ull : (st.prefix << (shift + bits));
+        st.lo = base + ((unsigned long long)(b + 1) << shift);  // b+1 == nb carries into the digit above: the band is `above` only
+        st.band_count = total;
+        st.exhausted = 0;
+        st.phase = PHASE_BAND;
+    } else {
+        st.above = total;
+        st.prefix = (st.level == 0 ? 0ull : (st.prefix << bits)) | (unsigned long long)b;
+        st.level += 1;
+        atomicAdd(pending, 1);
+    }
+    states[img] = st;
 }
 
 __device__ __forceinline__ void bitonic_sort_desc(unsigned long long* keys, int n_pow2) {

@@ -425,7 +425,7 @@ def test_mini_network_f32(be):
     for b in range(4):
         ref = o.detect("f32", b, 640, 480, 0.25, 0.45, True)
         # identical detections up to float tolerance: same count unless a score sits on the threshold
-        assert abs(dets[b].shape[0] - ref.shape[0]) <= 2
+        assert abs(dets[b].shape[0] - min(ref.shape[0], 512)) <= 2
 
 
 def test_yolov3_tiny_f32_config1(be):
