@@ -242,6 +242,8 @@ int32_t ln_net_last_times(const ln_net* net, float times_ms[2]);
    (per_layer_ms[num_layers]) and per kernel class (per_op_ms[8]: 0 tensor-core conv, 1 CUDA-core conv, 2 first-layer
    conv, 3 max-pool, 4 up-sample, 5 route copy, 6 shortcut, 7 input quantise) and the launch count per class. */
 int32_t ln_net_set_profile(ln_net* net, int32_t on);
+/* 8-bit forwards replay one captured CUDA graph of the whole batch (default on); 0 = launch kernel by kernel. */
+int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on);
 int32_t ln_net_profile(const ln_net* net, float* per_layer_ms, int32_t num_layers, float per_op_ms[8], int32_t per_op_launches[8]);
 
 #ifdef __cplusplus

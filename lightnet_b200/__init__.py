@@ -110,6 +110,7 @@ SYMBOLS = {
     "ln_net_detect_device": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_last_times": (C.c_int32, [_VP, _VP]),
     "ln_net_set_profile": (C.c_int32, [_VP, C.c_int32]),
+    "ln_net_set_cuda_graph": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_profile": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
 }
 
@@ -480,6 +481,9 @@ class GpuExecutableNetwork:
                       max_per_image=1024):
         return self._detect(self.lib.ln_net_detect_device, t.h, image_w, image_h, confidence_threshold, nms_threshold, letterbox,
                             top_k, max_per_image)
+
+    def set_cuda_graph(self, on: bool):
+        self.backend._check(self.lib.ln_net_set_cuda_graph(self.h, int(on)))
 
     def set_profile(self, on: bool):
         self.backend._check(self.lib.ln_net_set_profile(self.h, int(on)))

@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <map>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -31,6 +32,8 @@ struct ln_ctx {
     int* d_status = nullptr;  // device status word written by kernels whose bounded waits give up
     int* h_status = nullptr;  // pinned mirror
     ln_encode_tiled_fn encode_tiled = nullptr;
+    long long* debug_cycles = nullptr;  // when set (LN_DEBUG_CYCLES=1), the tensor-core convolution records role timings of CTA 0
+    std::set<const void*> configured_kernels;  // kernels whose dynamic shared memory limit has been raised
 };
 
 struct ln_tensor {
@@ -55,6 +58,7 @@ struct ln_conv_weights {
     void* w = nullptr;              // [fpad][k][k][cpad] 8-bit codes
     float* wscale = nullptr;        // [fpad] per-filter scale (device)
     std::vector<float> h_wscale;    // host copy
+    float max_l1 = 0.0f;            // max over filters of the sum of |code| (bounds the int8 accumulators)
     void* w_oihw = nullptr;         // [filters][channels][k][k] codes in the reference's weight order (SIMT path)
 };
 
@@ -104,6 +108,17 @@ __device__ __forceinline__ float ln_det_expf(float x) {
 }
 __device__ __forceinline__ float ln_det_sigmoid(float v) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, ln_det_expf(-v))); }
 
+__device__ __forceinline__ float ln_ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float ln_rcp_ftz(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Activation of the 8-bit epilogues.  EXACT: IEEE-only operations (bit-reproducible); otherwise the
 // hardware ex2/rcp approximations (about 2 ulp each).
 template <bool EXACT>
@@ -119,17 +134,17 @@ __device__ __forceinline__ float ln_epilogue_act(int act, float v) {
                 float w = __fmul_rn(e, __fadd_rn(e, 2.0f));
                 return __fmul_rn(v, __fdiv_rn(w, __fadd_rn(w, 2.0f)));
             } else {
-                float e = __expf(fminf(v, 20.0f));
-                float w = e * (e + 2.0f);
-                return v * __fdividef(w, w + 2.0f);
+                const float e = ln_ex2_ftz(fminf(v, 20.0f) * 1.44269504f);
+                const float w = e * (e + 2.0f);
+                return v * (w * ln_rcp_ftz(w + 2.0f));
             }
         }
         case LN_ACT_SWISH:
             if (EXACT) return __fdiv_rn(v, __fadd_rn(1.0f, ln_det_expf(-v)));
-            return __fdividef(v, 1.0f + __expf(-v));
+            return v * ln_rcp_ftz(1.0f + ln_ex2_ftz(fmaxf(v, -60.0f) * -1.44269504f));
         case LN_ACT_LOGISTIC:
             if (EXACT) return ln_det_sigmoid(v);
-            return __fdividef(1.0f, 1.0f + __expf(-v));
+            return ln_rcp_ftz(1.0f + ln_ex2_ftz(fmaxf(v, -60.0f) * -1.44269504f));
     }
     return v;
 }

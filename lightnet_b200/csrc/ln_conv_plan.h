@@ -17,7 +17,8 @@ enum {
 struct ln_conv_umma_params {
     CUtensorMap tmA[4];  // activations; stride-2 convolutions use one map per input parity class
     CUtensorMap tmB;     // weights as a [fpad][k*k*cpad] matrix
-    int bk, bn, stages;
+    int bk, bn, stages, nbuf;
+    int small_acc;  // every accumulator is known to stay below 2^22 in magnitude
     int R, S, stride, pad;
     int cblocks, cpad;
     int OW, OH, N, F, fpad_used;
@@ -29,6 +30,7 @@ struct ln_conv_umma_params {
     void* out;
     long long out_pixel_stride;  // bytes between pixels of an 8-bit NHWC output
     int* status;
+    long long* debug;  // optional: role timing of CTA 0 (32 counters), null = off
 };
 
 struct ln_conv_umma_plan {
@@ -50,6 +52,7 @@ struct ln_conv_geom {
     int OH = 0, OW = 0;
     int act = 0, out_kind = 0;
     float inv_sy = 1.0f;
+    bool small_acc = false;  // 127 * max over filters of sum|w code| < 2^22
     void* out = nullptr;
     long long out_pixel_stride = 0;
 };

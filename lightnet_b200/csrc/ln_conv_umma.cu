@@ -11,7 +11,8 @@
 // matching weight slab.  Stride-2 convolutions use one tensor map per input parity class so that the
 // strided gather is again a dense box.  Every CTA fetches its own operands.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 = epilogue.
+// Roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..9 = epilogue (two warps per
+// TMEM lane quadrant, alternating 32-column chunks, so every scheduler has two warps to hide latency with).
 // The accumulator is double buffered in TMEM so the epilogue of tile t overlaps the main loop of t+1.
 // Every mbarrier wait is bounded: when it gives up it raises a status word the host reads, and all
 // roles leave their loops, TMEM is released and the kernel returns.
@@ -22,6 +23,9 @@
 namespace {
 
 constexpr int kMaxStages = 8;
+constexpr int kThreads = 320;       // 2 + 8 warps
+constexpr int kEpilogueWarps = 8;    // two groups of four; a group takes every other tile
+constexpr int kMaxAccBufs = 8;       // accumulator tiles in TMEM: 512 columns / BN, at most 8
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -49,9 +53,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the wait was abandoned (own limit reached, or another role
 // already raised the CTA's abort flag).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          long long* waited = nullptr) {
+    const long long t0 = waited ? clock64() : 0;
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) {
+            if (waited) *waited += clock64() - t0;
+            return true;
+        }
+        if (it > 4u) __nanosleep(40);  // stop stealing issue slots from the epilogue warps of this scheduler
         if ((it & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1;
@@ -105,7 +115,31 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 16-byte read-only load that the compiler may not sink into the arithmetic that uses it
+__device__ __forceinline__ float4 ldg_f4_pinned(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+
+// int32 -> f32 (round to nearest even) on the FMA/ALU pipes only: the conversion unit shares its issue port with
+// ex2/rcp, which the transcendental epilogues need.  Exact: both halves convert exactly, the fma rounds once.
+__device__ __forceinline__ float i2f_alu(int v) {
+    const float lo = __fadd_rn(__uint_as_float(0x4B000000u | ((uint32_t)v & 0xFFFFu)), -8388608.0f);
+    const float hi = __fadd_rn(__uint_as_float(0x4B008000u ^ ((uint32_t)v >> 16)), -8421376.0f);  // (v >> 16) as a signed value
+    return __fmaf_rn(hi, 65536.0f, lo);
+}
+// rne(a * inv_s) clamped to +-127, returned in the low byte (two's complement) of the result; no conversion unit.
+__device__ __forceinline__ uint32_t quant_i8_magic(float a, float inv_s) {
+    float t = __fmul_rn(a, inv_s);
+    t = fminf(fmaxf(t, -127.0f), 127.0f);  // NaN -> -127
+    return __float_as_uint(__fadd_rn(t, 12582912.0f));
+}
+__device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are BK bytes wide and swizzled
@@ -122,32 +156,33 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int bk) {
 }
 
 template <int KIND, int ACT, bool EXACT>
-__global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant__ ln_conv_umma_params p) {
+__global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_constant__ ln_conv_umma_params p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int bk = p.bk, bn = p.bn, stages = p.stages;
     const uint32_t a_bytes = 128u * bk, b_bytes = (uint32_t)bn * bk, stage_bytes = a_bytes + b_bytes;
     const uint32_t bar_base = smem_base + (uint32_t)stages * stage_bytes;
-    // barrier block: full[8] empty[8] tfull[2] tempty[2] | tmem slot | abort flag
+    // barrier block: full[8] empty[8] tfull[8] tempty[8] | tmem slot | abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
-    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + 2 + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + kMaxAccBufs + b); };
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(generic_base + (bar_base - smem_base) + 8u * (2 * kMaxStages + 4));
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(generic_base + (bar_base - smem_base) + 8u * (2 * kMaxStages + 2 * kMaxAccBufs));
     volatile int* abort_flag = (volatile int*)(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tmem_cols = 2u * bn;  // 64 .. 512, a power of two
+    const uint32_t tmem_cols = 512u;  // the CTA owns the SM: take all of TMEM and keep 512/BN (at most 8) accumulator tiles in flight
+    const int nbuf = p.nbuf;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < nbuf; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 4);
+            mbar_init(tempty_bar(b), kEpilogueWarps / 2);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -172,6 +207,9 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            long long w_empty = 0;
+            long long* pw = p.debug ? &w_empty : nullptr;
+            const long long t_start = clock64();
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
                 const int tf = tile % p.tiles_f;
                 const int tw = (tile / p.tiles_f) % p.tiles_w;
@@ -188,7 +226,7 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
                         tx = (tx - px) >> 1;
                         map = py * 2 + px;
                     }
-                    if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT))) break;
+                    if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
                     const uint32_t sa = smem_base + (uint32_t)stage * stage_bytes;
                     mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
                     tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(stage));
@@ -196,6 +234,7 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
+            if (p.debug && blockIdx.x == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -206,14 +245,18 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
             uint32_t phase = 0;
             int t = 0;
             bool ok = true;
+            long long w_tempty = 0, w_full = 0;
+            long long* pw1 = p.debug ? &w_tempty : nullptr;
+            long long* pw2 = p.debug ? &w_full : nullptr;
+            const long long t_start = clock64();
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
-                const int buf = t & 1;
-                const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
-                if (!(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT))) break;
+                const int buf = t % nbuf;
+                const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
+                if (!(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw1))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT))) break;
+                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
                     tc_fence_after();
                     const uint32_t sa = smem_base + (uint32_t)stage * stage_bytes;
                     const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(sa + a_bytes, bk);
@@ -225,14 +268,20 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
                 if (!ok) break;
                 tc_commit(tfull_bar(buf));
             }
+            if (p.debug && blockIdx.x == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; }
         }
     } else {
         // ------------------------------------------------------------------ epilogue
-        const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
+        const int quad = warp & 3;          // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
+        const int group = (warp - 2) >> 2;  // which of the two warps of the quadrant: each group takes every other tile
         const int row = quad * 32 + lane;
         const int pw = row & (p.TW - 1), ph = (row >> p.log_tw) & (p.TH - 1), pn = row >> (p.log_tw + p.log_th);
+        constexpr bool kTranscendental = ACT == LN_ACT_MISH || ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC;
         int t = 0;
         bool ok = true;
+        long long w_tfull = 0;
+        long long* pwe = p.debug ? &w_tfull : nullptr;
+        const long long t_start = clock64();
         for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
             const int tf = tile % p.tiles_f;
             const int tw = (tile / p.tiles_f) % p.tiles_w;
@@ -240,15 +289,55 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
             const int tn = tile / tiles_per_n;
             const int ow = tw * p.TW + pw, oh = th * p.TH + ph, n = tn * p.TN + pn, f0 = tf * bn;
             const bool valid = ow < p.OW && oh < p.OH && n < p.N;
-            const int buf = t & 1;
-            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
-            if (!(ok = mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT))) break;
+            if ((t & 1) != group) continue;  // the other group of epilogue warps takes this tile
+            const int buf = t % nbuf;
+            const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
+            if (!(ok = mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT, pwe))) break;
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * bn);
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
             for (int c0 = 0; c0 < bn; c0 += 32) {
                 uint32_t acc[32];
                 tmem_ld_32x32(taddr0 + (uint32_t)c0, acc);
+                const bool fast = KIND == LN_KIND_I8 && p.out_kind == LN_OUT_Q && f0 + c0 + 32 <= p.F;
+                if (fast) {
+                    // ---- fast path: 32 valid filters, int8 out.  The {mult, bias} pairs (two per 16-byte load) are fetched
+                    // while the TMEM load is in flight, so the arithmetic below runs from registers only.
+                    const float4* mb4 = reinterpret_cast<const float4*>(p.mb + f0 + c0);
+                    float4 m[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) m[j] = ldg_f4_pinned(mb4 + j);
+                    tmem_ld_wait();
+                    if (!valid) continue;
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 m01 = m[2 * j], m23 = m[2 * j + 1];
+                        float x0, x1, x2, x3;
+                        if (p.small_acc) {  // |acc| < 2^22: adding it to the bits of 1.5*2^23 converts exactly, two FMA-pipe instructions
+                            x0 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j]), -12582912.0f);
+                            x1 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j + 1]), -12582912.0f);
+                            x2 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j + 2]), -12582912.0f);
+                            x3 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j + 3]), -12582912.0f);
+                        } else if (kTranscendental) {
+                            x0 = i2f_alu((int)acc[4 * j]); x1 = i2f_alu((int)acc[4 * j + 1]); x2 = i2f_alu((int)acc[4 * j + 2]); x3 = i2f_alu((int)acc[4 * j + 3]);
+                        } else {
+                            x0 = __int2float_rn((int)acc[4 * j]); x1 = __int2float_rn((int)acc[4 * j + 1]);
+                            x2 = __int2float_rn((int)acc[4 * j + 2]); x3 = __int2float_rn((int)acc[4 * j + 3]);
+                        }
+                        const float a0 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x0, m01.x, m01.y));
+                        const float a1 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x1, m01.z, m01.w));
+                        const float a2 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x2, m23.x, m23.y));
+                        const float a3 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x3, m23.z, m23.w));
+                        packed[j] = pack4_low_bytes(quant_i8_magic(a0, p.inv_sy), quant_i8_magic(a1, p.inv_sy), quant_i8_magic(a2, p.inv_sy),
+                                                    quant_i8_magic(a3, p.inv_sy));
+                    }
+                    uint4* o = (uint4*)((uint8_t*)p.out + pix * p.out_pixel_stride + f0 + c0);
+                    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    continue;
+                }
+                tmem_ld_wait();
                 if (!valid || f0 + c0 >= p.fpad_used) continue;
                 if (p.out_kind == LN_OUT_ACC) {
                     int32_t* o = (int32_t*)p.out;  // NCHW, raw accumulator bits (int32 or f32)
@@ -310,6 +399,7 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(buf));
         }
+        if (p.debug && blockIdx.x == 0 && lane == 0) { p.debug[6 + 2 * (warp - 2)] = clock64() - t_start; p.debug[7 + 2 * (warp - 2)] = w_tfull; }
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -327,14 +417,19 @@ __global__ void __launch_bounds__(192, 1) conv_umma_kernel(const __grid_constant
     }
 }
 
+constexpr int kMaxDynamicSmem = 227 * 1024;
+
 template <int KIND, bool EXACT>
-cudaError_t launch_act(const ln_conv_umma_params& p, int grid, size_t smem, cudaStream_t stream) {
+cudaError_t launch_act(ln_ctx* ctx, const ln_conv_umma_params& p, int grid, size_t smem, cudaStream_t stream) {
 #define LN_LAUNCH_ACT(A)                                                                                             \
     case A: {                                                                                                        \
         auto k = conv_umma_kernel<KIND, A, (A == LN_ACT_MISH || A == LN_ACT_SWISH || A == LN_ACT_LOGISTIC) && EXACT>; \
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
-        if (e != cudaSuccess) return e;                                                                              \
-        k<<<grid, 192, smem, stream>>>(p);                                                                           \
+        if (!ctx->configured_kernels.count((const void*)k)) { /* once per kernel per context */                      \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);   \
+            if (e != cudaSuccess) return e;                                                                          \
+            ctx->configured_kernels.insert((const void*)k);                                                          \
+        }                                                                                                            \
+        k<<<grid, kThreads, smem, stream>>>(p);                                                                           \
         return cudaGetLastError();                                                                                   \
     }
     switch (p.act) {
@@ -405,6 +500,8 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.cblocks = g.cpad / bk; p.cpad = g.cpad;
     p.OW = g.OW; p.OH = g.OH; p.N = g.N; p.F = g.F;
     p.fpad_used = (int)ln_round_up(g.F, 32);
+    p.nbuf = 512 / bn > kMaxAccBufs ? kMaxAccBufs : 512 / bn;
+    p.small_acc = g.small_acc ? 1 : 0;
     choose_box(g.OW, g.OH, g.N, &p.TW, &p.TH, &p.TN);
     p.log_tw = ilog2(p.TW); p.log_th = ilog2(p.TH);
     p.tiles_w = (g.OW + p.TW - 1) / p.TW;
@@ -415,6 +512,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.act = g.act; p.inv_sy = g.inv_sy; p.out_kind = g.out_kind;
     p.out = g.out; p.out_pixel_stride = g.out_pixel_stride;
     p.status = ctx->d_status;
+    p.debug = ctx->debug_cycles;
     p.mb = plan->mb;
 
     const uint32_t stage_bytes = (uint32_t)(128 + bn) * bk;
@@ -422,7 +520,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
     p.stages = stages;
-    plan->smem = (size_t)stages * stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    plan->smem = (size_t)stages * stage_bytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
     plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     plan->kind = g.kind;
 
@@ -468,11 +566,11 @@ int ln_conv_umma_launch(ln_ctx* ctx, const ln_conv_umma_plan* plan) {
     cudaError_t e;
     const bool exact = ctx->exact_epilogue;
     if (plan->kind == LN_KIND_I8)
-        e = exact ? launch_act<LN_KIND_I8, true>(plan->p, plan->grid, plan->smem, ctx->stream)
-                  : launch_act<LN_KIND_I8, false>(plan->p, plan->grid, plan->smem, ctx->stream);
+        e = exact ? launch_act<LN_KIND_I8, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
+                  : launch_act<LN_KIND_I8, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
     else
-        e = exact ? launch_act<LN_KIND_F8, true>(plan->p, plan->grid, plan->smem, ctx->stream)
-                  : launch_act<LN_KIND_F8, false>(plan->p, plan->grid, plan->smem, ctx->stream);
+        e = exact ? launch_act<LN_KIND_F8, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
+                  : launch_act<LN_KIND_F8, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
     ctx->launches++;
     if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "tensor-core convolution launch: %s", cudaGetErrorString(e));
     return LN_OK;

@@ -240,6 +240,12 @@ struct ln_net {
     ln_tensor* input_dev = nullptr;    // staging for host inputs
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     float times_ms[2] = {0, 0};
+    // CUDA graph of the 8-bit plan (one graph = the whole batch: every micro-batch, every layer)
+    bool use_graph = true;
+    cudaGraphExec_t graph_exec = nullptr;
+    const void* graph_input = nullptr;
+    bool graph_exact = false;
+    int graph_warm = 0;  // eager runs seen with the current key; the graph is captured on the second
     // optional per-launch timing
     bool profile = false;
     std::vector<cudaEvent_t> prof_events;
@@ -365,8 +371,15 @@ void release_heads(ln_net* net) {
     for (auto*& t : net->heads) { ln_tensor_release(t); t = nullptr; }
     net->heads.clear();
 }
+void release_graph(ln_net* net) {
+    if (net->graph_exec) { cudaGraphExecDestroy(net->graph_exec); net->graph_exec = nullptr; }
+    net->graph_input = nullptr;
+    net->graph_warm = 0;
+}
+
 void release_plan(ln_net* net) {
     ln_ctx* ctx = net->ctx;
+    release_graph(net);
     for (auto& s : net->steps)
         if (s.mb) ln_pool_free(ctx, s.mb, (size_t)net->layers[s.layer].wq->fpad * sizeof(float2));
     net->steps.clear();
@@ -613,6 +626,7 @@ int build_plan(ln_net* net, int mb) {
                 g.OH = L.out.h; g.OW = L.out.w; g.act = L.act;
                 g.out_kind = head ? LN_OUT_F32 : LN_OUT_Q;
                 g.inv_sy = head ? 1.0f : 1.0f / sy;
+                g.small_acc = kind == LN_KIND_I8 && 127.0f * L.wq->max_l1 < 4194304.0f;
                 if (head) { g.out = net->heads[st.head_index]->ptr; g.out_pixel_stride = 0; }
                 else { g.out = net->views[i].ptr; g.out_pixel_stride = net->views[i].cstride; }
                 if (i == 0) {
@@ -789,7 +803,35 @@ int forward_any(ln_net* net, const ln_tensor* input) {
             if (rc) { release_plan(net); return rc; }
             LN_CUDA(ctx, cudaEventRecord(net->ev[0], ctx->stream));
         }
-        rc = run_plan(net, (const float*)input->ptr);
+        if (!net->use_graph || net->profile) rc = run_plan(net, (const float*)input->ptr);
+        else {
+            // launch-bound otherwise (about a thousand launches per batch): replay one captured graph
+            if (net->graph_input != input->ptr || net->graph_exact != ctx->exact_epilogue) {
+                release_graph(net);
+                net->graph_input = input->ptr;
+                net->graph_exact = ctx->exact_epilogue;
+            }
+            if (net->graph_exec) {
+                LN_CUDA(ctx, cudaGraphLaunch(net->graph_exec, ctx->stream));
+                ctx->launches += (int64_t)net->steps.size() * (net->batch / mb);
+                rc = LN_OK;
+            } else if (net->graph_warm == 0) {
+                rc = run_plan(net, (const float*)input->ptr);  // first run is eager (kernel attributes get set here)
+                net->graph_warm = 1;
+            } else {
+                cudaGraph_t graph = nullptr;
+                LN_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+                rc = run_plan(net, (const float*)input->ptr);
+                cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+                if (rc == LN_OK && e != cudaSuccess) rc = ln_fail(ctx, LN_ERR_CUDA, "graph capture: %s", cudaGetErrorString(e));
+                if (rc == LN_OK) {
+                    e = cudaGraphInstantiate(&net->graph_exec, graph, 0);
+                    if (e != cudaSuccess) rc = ln_fail(ctx, LN_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+                }
+                if (graph) cudaGraphDestroy(graph);
+                if (rc == LN_OK) LN_CUDA(ctx, cudaGraphLaunch(net->graph_exec, ctx->stream));
+            }
+        }
         if (rc == LN_OK) rc = ln_check_status(ctx, "ln_net_forward");
     }
     if (rc) return rc;
@@ -1070,6 +1112,13 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
     int rc = stage_input(net, input_host);
     if (rc) return rc;
     return ln_net_detect_device(net, net->input_dev, image_w, image_h, opts, records_host, counts_host);
+}
+
+int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on) {
+    if (!net) return LN_ERR_ARG;
+    net->use_graph = on != 0;
+    if (!net->use_graph) release_graph(net);
+    return LN_OK;
 }
 
 int32_t ln_net_set_profile(ln_net* net, int32_t on) {

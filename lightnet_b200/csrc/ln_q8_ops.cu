@@ -105,6 +105,7 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, int F, int C, i
     __syncthreads();
     const float s = s_scale;
     const int row = k * k * cpad;
+    int l1 = 0;
     for (int i = threadIdx.x; i < row; i += blockDim.x) {
         int c = i % cpad, tap = i / cpad;
         uint8_t code = 0;
@@ -112,8 +113,19 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, int F, int C, i
             float v = __fdiv_rn(w[((int64_t)f * C + c) * k * k + tap], s);
             code = KIND == LN_KIND_I8 ? (uint8_t)(ln_quant_i8(v, 1.0f) & 0xFF) : float_to_e4m3(v);
             oihw[((int64_t)f * C + c) * k * k + tap] = code;
+            l1 += abs((int)(int8_t)code);
         }
         packed[(int64_t)f * row + i] = code;
+    }
+    // sum of |code| of the filter: 127 * this bounds the magnitude of any int8 accumulator
+    for (int o = 16; o > 0; o >>= 1) l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = (float)l1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+        wscale[gridDim.x + f] = t;
     }
 }
 
@@ -193,24 +205,30 @@ __global__ void copy_q1_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_
     }
 }
 
-// shortcut: code = quantise(act(a*sa + b*sb) / sy); 4 channels per thread (pad channels stay zero)
+// shortcut: code = quantise(act(a*sa + b*sb) / sy); 16 channels (one 16-byte vector) per thread
 template <int KIND, bool EXACT>
 __global__ void shortcut_q_kernel(const uint8_t* __restrict__ a, int64_t as, float sa, const uint8_t* __restrict__ b, int64_t bs, float sb,
-                                  uint8_t* __restrict__ y, int64_t ys, int64_t pixels, int C4, int act, float inv_sy) {
-    const int64_t total = pixels * C4;
+                                  uint8_t* __restrict__ y, int64_t ys, int64_t pixels, int C16, int act, float inv_sy) {
+    const int64_t total = pixels * C16;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        int cg = (int)(i % C4);
-        int64_t pix = i / C4;
-        uint32_t va = *reinterpret_cast<const uint32_t*>(a + pix * as + cg * 4);
-        uint32_t vb = *reinterpret_cast<const uint32_t*>(b + pix * bs + cg * 4);
-        uint32_t out = 0;
+        const int cg = (int)(i % C16);
+        const int64_t pix = i / C16;
+        const uint4 va = *reinterpret_cast<const uint4*>(a + pix * as + cg * 16);
+        const uint4 vb = *reinterpret_cast<const uint4*>(b + pix * bs + cg * 16);
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        uint32_t wo[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float v = __fmul_rn(code_to_float<KIND>((uint8_t)(va >> (8 * j))), sa);
-            v = __fmaf_rn(code_to_float<KIND>((uint8_t)(vb >> (8 * j))), sb, v);
-            out |= (uint32_t)quantize_code<KIND>(ln_epilogue_act<EXACT>(act, v), inv_sy) << (8 * j);
+        for (int w = 0; w < 4; ++w) {
+            uint32_t out = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float v = __fmul_rn(code_to_float<KIND>((uint8_t)(wa[w] >> (8 * j))), sa);
+                v = __fmaf_rn(code_to_float<KIND>((uint8_t)(wb[w] >> (8 * j))), sb, v);
+                out |= (uint32_t)quantize_code<KIND>(ln_epilogue_act<EXACT>(act, v), inv_sy) << (8 * j);
+            }
+            wo[w] = out;
         }
-        *reinterpret_cast<uint32_t*>(y + pix * ys + cg * 4) = out;
+        *reinterpret_cast<uint4*>(y + pix * ys + cg * 16) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
     }
 }
 
@@ -339,6 +357,81 @@ __global__ void conv_stem_kernel(const float* __restrict__ x, float inv_sx, int 
     }
 }
 
+// rne(a * inv_s) clamped to +-127 in the low byte of the result, on the FMA pipe only (no conversion unit).
+__device__ __forceinline__ uint32_t quant_i8_magic(float a, float inv_s) {
+    float t = __fmul_rn(a, inv_s);
+    t = fminf(fmaxf(t, -127.0f), 127.0f);  // NaN -> -127
+    return __float_as_uint(__fadd_rn(t, 12582912.0f));
+}
+__device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// The usual first layer: 3x3 convolution of a 3-channel f32 NCHW image, int8.  One thread per output pixel: the
+// 27 input values are quantised once into 7 packed words held in registers, then every filter costs 7 dp4a against
+// weights read (broadcast) from shared memory, and each group of 16 filters leaves as one 16-byte store.
+template <int ACT, bool EXACT>
+__global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
+                                                                const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
+                                                                int pad, int OH, int OW, float inv_sy, uint8_t* __restrict__ out,
+                                                                int64_t out_pixel_stride) {
+    extern __shared__ uint4 s_w4[];  // [F16*16][2]: 8 words per filter, 7 used; byte t of a filter = tap (t/3), channel (t%3)
+    const int F16 = (F + 15) / 16;
+    float2* s_mb = reinterpret_cast<float2*>(s_w4 + F16 * 16 * 2);
+    uint32_t* s_w = reinterpret_cast<uint32_t*>(s_w4);
+    for (int i = threadIdx.x; i < F16 * 16 * 8; i += blockDim.x) {
+        const int f = i >> 3, wd = i & 7;
+        uint32_t v = 0;
+        for (int j = 0; j < 4; ++j) {
+            const int t = wd * 4 + j;
+            if (f < F && t < 27) v |= (uint32_t)w_oihw[((int64_t)f * 3 + (t % 3)) * 9 + (t / 3)] << (8 * j);
+        }
+        s_w[i] = v;
+    }
+    for (int i = threadIdx.x; i < F16 * 16; i += blockDim.x) s_mb[i] = i < F ? mb[i] : make_float2(0.0f, 0.0f);
+    __syncthreads();
+    const int64_t total = (int64_t)N * OH * OW;
+    for (int64_t pix = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; pix < total; pix += (int64_t)gridDim.x * blockDim.x) {
+        const int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
+        const int64_t n = pix / ((int64_t)OW * OH);
+        uint32_t patch[7] = {0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int t = 0; t < 27; ++t) {
+            const int c = t % 3, ky = (t / 3) / 3, kx = (t / 3) % 3;
+            const int iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
+            uint32_t code = 0;
+            if (iy >= 0 && iy < H && ix >= 0 && ix < W) code = quant_i8_magic(__ldg(x + ((n * 3 + c) * H + iy) * W + ix), inv_sx) & 0xFFu;
+            patch[t >> 2] |= code << (8 * (t & 3));
+        }
+        for (int fg = 0; fg < F16; ++fg) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t u[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int f = fg * 16 + q * 4 + b;
+                    const uint4 w0 = s_w4[f * 2], w1 = s_w4[f * 2 + 1];
+                    int acc = __dp4a((int)patch[0], (int)w0.x, 0);
+                    acc = __dp4a((int)patch[1], (int)w0.y, acc);
+                    acc = __dp4a((int)patch[2], (int)w0.z, acc);
+                    acc = __dp4a((int)patch[3], (int)w0.w, acc);
+                    acc = __dp4a((int)patch[4], (int)w1.x, acc);
+                    acc = __dp4a((int)patch[5], (int)w1.y, acc);
+                    acc = __dp4a((int)patch[6], (int)w1.z, acc);
+                    const float2 m = s_mb[f];
+                    // |acc| <= 27*127*127 < 2^22: adding it to the bits of 1.5*2^23 converts exactly
+                    const float xf = __fadd_rn(__int_as_float(0x4B400000 + acc), -12582912.0f);
+                    const float a = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(xf, m.x, m.y));
+                    u[b] = f < F ? quant_i8_magic(a, inv_sy) : 0u;
+                }
+                packed[q] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
+            }
+            *reinterpret_cast<uint4*>(out + pix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+}
+
 bool is_q(const ln_tensor* t) { return t && (t->dtype == LN_Q8 || t->dtype == LN_F8); }
 int kind_of(int dtype) { return dtype == LN_F8 ? LN_KIND_F8 : LN_KIND_I8; }
 
@@ -381,6 +474,25 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
     const int64_t total = (int64_t)N * OH * OW * F16;
     const int grid = grid_for(ctx, total);
     const bool exact = ctx->exact_epilogue;
+    if (kind == LN_KIND_I8 && k == 3 && C == 3) {
+        const size_t smem3 = (size_t)F16 * 16 * 32 + (size_t)F16 * 16 * sizeof(float2);
+        const int grid3 = grid_for(ctx, (int64_t)N * OH * OW);
+#define LN_STEM3(A, E)                                                                                                                             \
+    conv_stem_k3c3_i8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, OW, \
+                                                                           inv_sy, (uint8_t*)out, out_pixel_stride)
+        switch (act) {
+            case LN_ACT_LINEAR: LN_STEM3(LN_ACT_LINEAR, false); break;
+            case LN_ACT_LEAKY: LN_STEM3(LN_ACT_LEAKY, false); break;
+            case LN_ACT_RELU: LN_STEM3(LN_ACT_RELU, false); break;
+            case LN_ACT_MISH: if (exact) LN_STEM3(LN_ACT_MISH, true); else LN_STEM3(LN_ACT_MISH, false); break;
+            case LN_ACT_SWISH: if (exact) LN_STEM3(LN_ACT_SWISH, true); else LN_STEM3(LN_ACT_SWISH, false); break;
+            case LN_ACT_LOGISTIC: if (exact) LN_STEM3(LN_ACT_LOGISTIC, true); else LN_STEM3(LN_ACT_LOGISTIC, false); break;
+            default: return ln_fail(ctx, LN_ERR_UNSUPPORTED, "first-layer convolution: activation %d", act);
+        }
+#undef LN_STEM3
+        LN_LAUNCHED(ctx);
+        return LN_OK;
+    }
 #define LN_STEM(K, E)                                                                                                                   \
     conv_stem_kernel<K, E><<<grid, kThreads, smem, ctx->stream>>>(x_nchw, inv_sx, N, C, H, W, (const uint8_t*)w_oihw, mb, F, k, stride, pad, \
                                                                  OH, OW, act, inv_sy, (uint8_t*)out, out_pixel_stride)
@@ -423,7 +535,7 @@ int ln_q_copy_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys
 
 int ln_q_shortcut_launch(ln_ctx* ctx, int kind, const void* a, int64_t as, float sa, const void* b, int64_t bs, float sb, void* y, int64_t ys,
                          int64_t pixels, int C, int act, float inv_sy) {
-    const int C4 = (int)(ln_round_up(C, 4) / 4);
+    const int C4 = (int)(ln_round_up(C, 16) / 16);  // 16-channel vectors (tensors are padded to 32 channels)
     const int64_t total = pixels * C4;
     const int grid = grid_for(ctx, total);
     const bool exact = ctx->exact_epilogue;
@@ -550,7 +662,7 @@ int32_t ln_conv_weights_q(ln_ctx* ctx, const ln_tensor* weights_f32, int64_t fil
     const size_t oihw_bytes = (size_t)(filters * channels * kernel_size * kernel_size);
     w->w = ln_pool_alloc(ctx, packed_bytes);
     w->w_oihw = ln_pool_alloc(ctx, oihw_bytes);
-    w->wscale = (float*)ln_pool_alloc(ctx, (size_t)w->fpad * 4);
+    w->wscale = (float*)ln_pool_alloc(ctx, (size_t)w->fpad * 8);  // [fpad] scales, then [fpad] sums of |code|
     if (!w->w || !w->w_oihw || !w->wscale) { ln_conv_weights_release(w); return LN_ERR_CUDA; }
     if (dtype == LN_Q8)
         pack_weights_kernel<LN_KIND_I8><<<(int)w->fpad, 256, 0, ctx->stream>>>((const float*)weights_f32->ptr, (int)filters, (int)channels, (int)kernel_size, (int)w->cpad, (uint8_t*)w->w, (uint8_t*)w->w_oihw, w->wscale);
@@ -558,9 +670,12 @@ int32_t ln_conv_weights_q(ln_ctx* ctx, const ln_tensor* weights_f32, int64_t fil
         pack_weights_kernel<LN_KIND_F8><<<(int)w->fpad, 256, 0, ctx->stream>>>((const float*)weights_f32->ptr, (int)filters, (int)channels, (int)kernel_size, (int)w->cpad, (uint8_t*)w->w, (uint8_t*)w->w_oihw, w->wscale);
     ctx->launches++;
     cudaError_t e = cudaGetLastError();
-    w->h_wscale.resize((size_t)w->fpad);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(w->h_wscale.data(), w->wscale, (size_t)w->fpad * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    w->h_wscale.resize((size_t)w->fpad * 2);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->h_wscale.data(), w->wscale, (size_t)w->fpad * 8, cudaMemcpyDeviceToHost, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    w->max_l1 = 0.0f;
+    for (int64_t f = 0; f < w->fpad; ++f) w->max_l1 = w->h_wscale[(size_t)(w->fpad + f)] > w->max_l1 ? w->h_wscale[(size_t)(w->fpad + f)] : w->max_l1;
+    w->h_wscale.resize((size_t)w->fpad);
     if (e != cudaSuccess) { ln_conv_weights_release(w); return ln_fail(ctx, LN_ERR_CUDA, "weight packing: %s", cudaGetErrorString(e)); }
     *out = w;
     return LN_OK;
@@ -571,7 +686,7 @@ int32_t ln_conv_weights_release(ln_conv_weights* w) {
     ln_ctx* ctx = w->ctx;
     if (w->w) ln_pool_free(ctx, w->w, (size_t)(w->fpad * w->k * w->k * w->cpad));
     if (w->w_oihw) ln_pool_free(ctx, w->w_oihw, (size_t)(w->filters * w->channels * w->k * w->k));
-    if (w->wscale) ln_pool_free(ctx, w->wscale, (size_t)w->fpad * 4);
+    if (w->wscale) ln_pool_free(ctx, w->wscale, (size_t)w->fpad * 8);
     delete w;
     return LN_OK;
 }
@@ -614,6 +729,7 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
     g.w = weights->w; g.F = (int)filters; g.fpad = (int)weights->fpad; g.k = (int)kernel_size; g.stride = (int)stride_x; g.pad = (int)padding;
     g.OH = (int)oh; g.OW = (int)ow; g.act = activation; g.out_kind = out_kind;
     g.inv_sy = out_kind == LN_OUT_Q ? 1.0f / y_scale : 1.0f;
+    g.small_acc = kind == LN_KIND_I8 && 127.0f * weights->max_l1 < 4194304.0f;
     g.out = y->ptr; g.out_pixel_stride = y->cstride;
     if (rc == LN_OK) {
         if (x->cstride >= weights->cpad && ln_conv_umma_supported(weights->cpad, kernel_size, stride_x, stride_y, dilation, groups, input_width, input_height)) {
@@ -715,7 +831,7 @@ int32_t ln_shortcut_add_act_q(ln_ctx* ctx, const ln_tensor* a, const ln_tensor* 
     ln_tensor* y = ln_tensor_new(ctx, a->dtype, a->n, a->c, a->h, a->w);
     if (!y) return LN_ERR_CUDA;
     y->scale = y_scale;
-    if (y->cstride != ln_round_up(y->c, 4)) cudaMemsetAsync(y->ptr, 0, y->bytes, ctx->stream);
+    if (y->cstride != ln_round_up(y->c, 16)) cudaMemsetAsync(y->ptr, 0, y->bytes, ctx->stream);
     int rc = ln_q_shortcut_launch(ctx, kind_of(a->dtype), a->ptr, a->cstride, a->scale, b->ptr, b->cstride, b->scale, y->ptr, y->cstride, a->n * a->h * a->w,
                                   (int)a->c, activation, 1.0f / y_scale);
     if (rc) { ln_tensor_release(y); return rc; }

@@ -1,4 +1,5 @@
 // Context, device-memory pool and tensor handles of liblightnet_b200.
+#include <cstdlib>
 #include <cstring>
 
 #include "ln_common.h"
@@ -119,6 +120,10 @@ int32_t ln_ctx_create(int32_t device, ln_ctx** out) {
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
     if (e != cudaSuccess || !fn) { delete ctx; return ln_fail(nullptr, LN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
     ctx->encode_tiled = (ln_encode_tiled_fn)fn;
+    if (getenv("LN_DEBUG_CYCLES")) {
+        if (cudaMallocManaged(&ctx->debug_cycles, 32 * sizeof(long long)) != cudaSuccess) ctx->debug_cycles = nullptr;
+        else memset(ctx->debug_cycles, 0, 32 * sizeof(long long));
+    }
     *out = ctx;
     return LN_OK;
 }
@@ -144,6 +149,9 @@ int32_t ln_sync(ln_ctx* ctx) {
 }
 
 void* ln_ctx_stream(ln_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+// Debug aid (LN_DEBUG_CYCLES=1): role timings of CTA 0 of the last tensor-core convolution; NULL when off.
+const long long* ln_ctx_debug_cycles(ln_ctx* ctx) { return ctx ? ctx->debug_cycles : nullptr; }
 
 int32_t ln_ctx_set_exact_epilogue(ln_ctx* ctx, int32_t on) {
     if (!ctx) return LN_ERR_ARG;
