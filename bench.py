@@ -138,7 +138,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
-    ap.add_argument("--micro-batch", type=int, default=8, help="images per pass through the layers (activations stay in L2)")
+    ap.add_argument("--micro-batch", type=int, default=0, help="images per pass through the layers (activations stay in L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--width", type=int, default=608)
     ap.add_argument("--height", type=int, default=608)

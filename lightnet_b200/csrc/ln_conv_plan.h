@@ -24,6 +24,7 @@ struct ln_conv_umma_params {
     int OW, OH, N, F, fpad_used;
     int TW, TH, TN, log_tw, log_th;
     int tiles_w, tiles_h, tiles_n, tiles_f, num_tiles;
+    unsigned long long magic_f, magic_w, magic_h;  // ceil(2^40 / tiles_*) for division-free tile decoding
     int act, out_kind;
     float inv_sy;
     const float2* mb;  // [fpad] {x_scale * w_scale[f], bias[f]}

@@ -116,6 +116,9 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
 }
+// n / d for n * d < 2^40 with the precomputed multiplier ceil(2^40 / d): one wide multiply and a shift
+__device__ __forceinline__ int fast_div(int n, unsigned long long magic) { return (int)(((unsigned long long)(unsigned)n * magic) >> 40); }
+
 // 16-byte read-only load that the compiler may not sink into the arithmetic that uses it
 __device__ __forceinline__ float4 ldg_f4_pinned(const float4* p) {
     float4 v;
@@ -199,7 +202,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     const int kblocks = p.R * p.S * p.cblocks;
-    const int tiles_per_n = p.tiles_f * p.tiles_w * p.tiles_h;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -211,10 +213,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             long long* pw = p.debug ? &w_empty : nullptr;
             const long long t_start = clock64();
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                const int tf = tile % p.tiles_f;
-                const int tw = (tile / p.tiles_f) % p.tiles_w;
-                const int th = (tile / (p.tiles_f * p.tiles_w)) % p.tiles_h;
-                const int tn = tile / tiles_per_n;
+                const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
+                const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
+                const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
                 const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
@@ -279,14 +280,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         constexpr bool kTranscendental = ACT == LN_ACT_MISH || ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC;
         int t = 0;
         bool ok = true;
-        long long w_tfull = 0;
+        long long w_tfull = 0, dbg_ld = 0, dbg_math = 0, dbg_st = 0;
         long long* pwe = p.debug ? &w_tfull : nullptr;
         const long long t_start = clock64();
         for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
-            const int tf = tile % p.tiles_f;
-            const int tw = (tile / p.tiles_f) % p.tiles_w;
-            const int th = (tile / (p.tiles_f * p.tiles_w)) % p.tiles_h;
-            const int tn = tile / tiles_per_n;
+            const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
+            const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
+            const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
             const int ow = tw * p.TW + pw, oh = th * p.TH + ph, n = tn * p.TN + pn, f0 = tf * bn;
             const bool valid = ow < p.OW && oh < p.OH && n < p.N;
             if ((t & 1) != group) continue;  // the other group of epilogue warps takes this tile
@@ -298,6 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
             for (int c0 = 0; c0 < bn; c0 += 32) {
                 uint32_t acc[32];
+                const long long tq0 = p.debug ? clock64() : 0;
                 tmem_ld_32x32(taddr0 + (uint32_t)c0, acc);
                 const bool fast = KIND == LN_KIND_I8 && p.out_kind == LN_OUT_Q && f0 + c0 + 32 <= p.F;
                 if (fast) {
@@ -308,33 +309,50 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
 #pragma unroll
                     for (int j = 0; j < 16; ++j) m[j] = ldg_f4_pinned(mb4 + j);
                     tmem_ld_wait();
+                    const long long tq1 = p.debug ? clock64() : 0;
+                    if (p.debug) dbg_ld += tq1 - tq0;
                     if (!valid) continue;
                     uint32_t packed[8];
+                    // int32 -> f32.  When every accumulator is known to stay below 2^22, adding it to the bits of 1.5*2^23
+                    // converts exactly in two FMA-pipe instructions; otherwise the conversion unit (or, for the
+                    // transcendental epilogues that need that unit for ex2/rcp, an exact ALU sequence).
+                    float x[32];
+                    if (p.small_acc) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 m01 = m[2 * j], m23 = m[2 * j + 1];
-                        float x0, x1, x2, x3;
-                        if (p.small_acc) {  // |acc| < 2^22: adding it to the bits of 1.5*2^23 converts exactly, two FMA-pipe instructions
-                            x0 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j]), -12582912.0f);
-                            x1 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j + 1]), -12582912.0f);
-                            x2 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j + 2]), -12582912.0f);
-                            x3 = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[4 * j + 3]), -12582912.0f);
-                        } else if (kTranscendental) {
-                            x0 = i2f_alu((int)acc[4 * j]); x1 = i2f_alu((int)acc[4 * j + 1]); x2 = i2f_alu((int)acc[4 * j + 2]); x3 = i2f_alu((int)acc[4 * j + 3]);
-                        } else {
-                            x0 = __int2float_rn((int)acc[4 * j]); x1 = __int2float_rn((int)acc[4 * j + 1]);
-                            x2 = __int2float_rn((int)acc[4 * j + 2]); x3 = __int2float_rn((int)acc[4 * j + 3]);
-                        }
-                        const float a0 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x0, m01.x, m01.y));
-                        const float a1 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x1, m01.z, m01.w));
-                        const float a2 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x2, m23.x, m23.y));
-                        const float a3 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x3, m23.z, m23.w));
-                        packed[j] = pack4_low_bytes(quant_i8_magic(a0, p.inv_sy), quant_i8_magic(a1, p.inv_sy), quant_i8_magic(a2, p.inv_sy),
-                                                    quant_i8_magic(a3, p.inv_sy));
+                        for (int j = 0; j < 32; ++j) x[j] = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[j]), -12582912.0f);
+                    } else if (kTranscendental) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = i2f_alu((int)acc[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = __int2float_rn((int)acc[j]);
                     }
+                    if (EXACT) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            x[2 * j] = ln_epilogue_act<true>(ACT, __fmaf_rn(x[2 * j], m[j].x, m[j].y));
+                            x[2 * j + 1] = ln_epilogue_act<true>(ACT, __fmaf_rn(x[2 * j + 1], m[j].z, m[j].w));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            packed[j] = pack4_low_bytes(quant_i8_magic(x[4 * j], p.inv_sy), quant_i8_magic(x[4 * j + 1], p.inv_sy),
+                                                        quant_i8_magic(x[4 * j + 2], p.inv_sy), quant_i8_magic(x[4 * j + 3], p.inv_sy));
+                    } else {
+                        // fast mode: the f32 scale-and-bias stays exact, activation and requantisation run two at a time in binary16
+                        const __half2 inv_h = __float2half2_rn(p.inv_sy);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t q01 = ln_h2_act_quant<ACT>(__fmaf_rn(x[4 * j], m[2 * j].x, m[2 * j].y), __fmaf_rn(x[4 * j + 1], m[2 * j].z, m[2 * j].w), inv_h);
+                            const uint32_t q23 = ln_h2_act_quant<ACT>(__fmaf_rn(x[4 * j + 2], m[2 * j + 1].x, m[2 * j + 1].y),
+                                                                      __fmaf_rn(x[4 * j + 3], m[2 * j + 1].z, m[2 * j + 1].w), inv_h);
+                            packed[j] = ln_h2_pack(q01, q23);
+                        }
+                    }
+                    const long long tq2 = p.debug ? clock64() : 0;
                     uint4* o = (uint4*)((uint8_t*)p.out + pix * p.out_pixel_stride + f0 + c0);
                     o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    if (p.debug) { dbg_math += tq2 - tq1; dbg_st += clock64() - tq2; }
                     continue;
                 }
                 tmem_ld_wait();
@@ -399,7 +417,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(buf));
         }
-        if (p.debug && blockIdx.x == 0 && lane == 0) { p.debug[6 + 2 * (warp - 2)] = clock64() - t_start; p.debug[7 + 2 * (warp - 2)] = w_tfull; }
+        if (p.debug && blockIdx.x == 0 && lane == 0) {
+            p.debug[6 + 2 * (warp - 2)] = clock64() - t_start;
+            p.debug[7 + 2 * (warp - 2)] = w_tfull;
+            if (warp == 2) { p.debug[22] = dbg_ld; p.debug[23] = dbg_math; p.debug[24] = dbg_st; }
+        }
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -423,7 +445,7 @@ template <int KIND, bool EXACT>
 cudaError_t launch_act(ln_ctx* ctx, const ln_conv_umma_params& p, int grid, size_t smem, cudaStream_t stream) {
 #define LN_LAUNCH_ACT(A)                                                                                             \
     case A: {                                                                                                        \
-        auto k = conv_umma_kernel<KIND, A, (A == LN_ACT_MISH || A == LN_ACT_SWISH || A == LN_ACT_LOGISTIC) && EXACT>; \
+        auto k = conv_umma_kernel<KIND, A, EXACT>;                                                                     \
         if (!ctx->configured_kernels.count((const void*)k)) { /* once per kernel per context */                      \
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);   \
             if (e != cudaSuccess) return e;                                                                          \
@@ -470,9 +492,11 @@ bool ln_conv_umma_supported(int64_t channels_padded, int64_t k, int64_t stride_x
 }
 
 // Picks the output box: TW*TH*TN = 128, all powers of two, minimising the number of tiles (ties: wider in w).
-static void choose_box(int OW, int OH, int N, int* TW, int* TH, int* TN) {
+// `wide`: planar (NCHW) outputs are written one filter plane at a time, 32 lanes = 32 consecutive pixels, so the box
+// must be at least 32 pixels wide for those stores to coalesce.
+static void choose_box(int OW, int OH, int N, bool wide, int* TW, int* TH, int* TN) {
     int64_t best = -1;
-    for (int lw = 0; lw <= 7; ++lw)
+    for (int lw = wide ? 5 : 0; lw <= 7; ++lw)
         for (int lh = 0; lw + lh <= 7; ++lh) {
             int tw = 1 << lw, th = 1 << lh, tn = 128 >> (lw + lh);
             int64_t tiles = (int64_t)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
@@ -502,13 +526,16 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.fpad_used = (int)ln_round_up(g.F, 32);
     p.nbuf = 512 / bn > kMaxAccBufs ? kMaxAccBufs : 512 / bn;
     p.small_acc = g.small_acc ? 1 : 0;
-    choose_box(g.OW, g.OH, g.N, &p.TW, &p.TH, &p.TN);
+    choose_box(g.OW, g.OH, g.N, g.out_kind != LN_OUT_Q, &p.TW, &p.TH, &p.TN);
     p.log_tw = ilog2(p.TW); p.log_th = ilog2(p.TH);
     p.tiles_w = (g.OW + p.TW - 1) / p.TW;
     p.tiles_h = (g.OH + p.TH - 1) / p.TH;
     p.tiles_n = (g.N + p.TN - 1) / p.TN;
     p.tiles_f = (int)(ln_round_up(g.F, bn) / bn);
     p.num_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_f;
+    auto magic = [](int d) { return ((1ull << 40) + (unsigned long long)d - 1) / (unsigned long long)d; };
+    p.magic_f = magic(p.tiles_f); p.magic_w = magic(p.tiles_w); p.magic_h = magic(p.tiles_h);
+    if ((long long)p.num_tiles * p.num_tiles >= (1ll << 40)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d tiles", p.num_tiles);
     p.act = g.act; p.inv_sy = g.inv_sy; p.out_kind = g.out_kind;
     p.out = g.out; p.out_pixel_stride = g.out_pixel_stride;
     p.status = ctx->d_status;

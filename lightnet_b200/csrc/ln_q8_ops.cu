@@ -405,9 +405,10 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
         }
         for (int fg = 0; fg < F16; ++fg) {
             uint32_t packed[4];
+            const __half2 inv_h = __float2half2_rn(inv_sy);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                uint32_t u[4];
+                float v[4];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                     const int f = fg * 16 + q * 4 + b;
@@ -422,10 +423,19 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
                     const float2 m = s_mb[f];
                     // |acc| <= 27*127*127 < 2^22: adding it to the bits of 1.5*2^23 converts exactly
                     const float xf = __fadd_rn(__int_as_float(0x4B400000 + acc), -12582912.0f);
-                    const float a = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(xf, m.x, m.y));
-                    u[b] = f < F ? quant_i8_magic(a, inv_sy) : 0u;
+                    v[b] = __fmaf_rn(xf, m.x, m.y);  // filters beyond F have m = {0, 0}: their code is act(0) and is masked below
                 }
-                packed[q] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
+                if (EXACT) {
+                    uint32_t u[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) u[b] = fg * 16 + q * 4 + b < F ? quant_i8_magic(ln_epilogue_act<true>(ACT, v[b]), inv_sy) : 0u;
+                    packed[q] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
+                } else {
+                    uint32_t w = ln_h2_pack(ln_h2_act_quant<ACT>(v[0], v[1], inv_h), ln_h2_act_quant<ACT>(v[2], v[3], inv_h));
+                    const int valid = F - (fg * 16 + q * 4);  // keep only the codes of real filters
+                    if (valid < 4) w = valid <= 0 ? 0u : (w & (0xFFFFFFFFu >> (8 * (4 - valid))));
+                    packed[q] = w;
+                }
             }
             *reinterpret_cast<uint4*>(out + pix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
@@ -481,9 +491,9 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
     conv_stem_k3c3_i8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, OW, \
                                                                            inv_sy, (uint8_t*)out, out_pixel_stride)
         switch (act) {
-            case LN_ACT_LINEAR: LN_STEM3(LN_ACT_LINEAR, false); break;
-            case LN_ACT_LEAKY: LN_STEM3(LN_ACT_LEAKY, false); break;
-            case LN_ACT_RELU: LN_STEM3(LN_ACT_RELU, false); break;
+            case LN_ACT_LINEAR: if (exact) LN_STEM3(LN_ACT_LINEAR, true); else LN_STEM3(LN_ACT_LINEAR, false); break;
+            case LN_ACT_LEAKY: if (exact) LN_STEM3(LN_ACT_LEAKY, true); else LN_STEM3(LN_ACT_LEAKY, false); break;
+            case LN_ACT_RELU: if (exact) LN_STEM3(LN_ACT_RELU, true); else LN_STEM3(LN_ACT_RELU, false); break;
             case LN_ACT_MISH: if (exact) LN_STEM3(LN_ACT_MISH, true); else LN_STEM3(LN_ACT_MISH, false); break;
             case LN_ACT_SWISH: if (exact) LN_STEM3(LN_ACT_SWISH, true); else LN_STEM3(LN_ACT_SWISH, false); break;
             case LN_ACT_LOGISTIC: if (exact) LN_STEM3(LN_ACT_LOGISTIC, true); else LN_STEM3(LN_ACT_LOGISTIC, false); break;

@@ -18,14 +18,19 @@
 //
 // All arithmetic that decides an ordering or a threshold (sigmoid, box decode, IoU) uses single IEEE-754
 // operations in the reference's evaluation order, so a CPU evaluating the same expressions gets the same bits.
+#include <cstdlib>
+#include <ctime>
+
 #include "ln_conv_plan.h"
 
 namespace {
 
 constexpr int kMaxHeads = 8;
-constexpr int kBandMax = 8192;   // candidates of one band (sorted in shared memory)
+constexpr int kBandMaxLarge = 16384;  // candidates of one band (sorted in shared memory) when at most 1024 survivors are wanted
+constexpr int kBandMaxSmall = 8192;   // ... when more are wanted (their boxes need the room)
 constexpr int kChunk = 512;      // candidates resolved per bitmask step
 constexpr int kBins = 4096;      // 12-bit radix digits
+constexpr unsigned kFlatChunk = 32768;  // cached score keys one block of the flat passes walks
 constexpr int kLevels = 6;       // 5 x 12 bits + 4 bits = 64
 
 enum { PHASE_SELECT = 0, PHASE_BAND = 1, PHASE_DONE = 2 };
@@ -45,13 +50,15 @@ struct YoloParams {
     float thr, nms_thr;
     int k_eff;          // survivors wanted per image
     int max_per_image;  // record capacity
+    int band_max;       // capacity of one band
+    unsigned cache_stride;  // cached score keys per image (total_ca * classes rounded up to 4)
 };
 
 struct ImgState {
     unsigned long long hi;      // keys >= hi have been consumed
     unsigned long long lo;      // current band is [lo, hi)
     unsigned long long prefix;  // digits fixed so far by the radix selection
-    int level, phase, cap, above, band_count, kept, exhausted, img_w, img_h, pad;
+    int level, phase, cap, above, band_count, kept, exhausted, img_w, img_h, last_gain;  // last_gain: survivors the previous band added
 };
 
 __device__ __forceinline__ int level_shift(int l) { return l < 5 ? 52 - 12 * l : 0; }
@@ -126,12 +133,86 @@ __device__ __forceinline__ int find_head(const YoloParams& p, int ca) {
     return h;
 }
 
-// One pass over the heads.  MODE 0: histogram of the current radix digit of the still unconsumed candidates.
+// One pass over the candidates.  MODE 0: histogram of the current radix digit of the still unconsumed candidates.
 // MODE 1: collect the keys of the band [lo, hi).  One thread per (anchor, cell); blockIdx.y = image.
-template <int MODE>
+// FIRST: read the head tensors, evaluate the scores and leave their 32-bit order-preserving keys (0 = not a
+// candidate) in `cache`, laid out [image][class][anchor-cell]; later passes read the cache instead and do
+// integer work only.
+template <int MODE, bool FIRST>
 __global__ void __launch_bounds__(256) yolo_scan_kernel(const __grid_constant__ YoloParams p, ImgState* __restrict__ states,
                                                         unsigned* __restrict__ hist, unsigned long long* __restrict__ band,
-                                                        int* __restrict__ band_fill) {
+                                                        int* __restrict__ band_fill, unsigned* __restrict__ cache) {
+    const int img = blockIdx.y;
+    const ImgState st = states[img];
+    if (!FIRST && (MODE == 0 ? st.phase != PHASE_SELECT : st.phase != PHASE_BAND)) return;
+    __shared__ unsigned s_hist[MODE == 0 ? kBins : 1];
+    if (MODE == 0) {
+        for (int i = threadIdx.x; i < kBins; i += blockDim.x) s_hist[i] = 0;
+        __syncthreads();
+    }
+    const int shift = level_shift(st.level), bits = level_bits(st.level);
+    const int ca = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ca < p.total_ca) {
+        unsigned* img_cache = cache + (size_t)img * p.cache_stride;
+        const float* img_raw = nullptr;
+        int stride = 0, a = 0, idx = 0, epa = 0, new_coords = 0;
+        float obj = 0.0f;
+        if (FIRST) {
+            const HeadDev& h = p.heads[find_head(p, ca)];
+            stride = h.gw * h.gh; epa = h.classes + 5; new_coords = h.new_coords;
+            const int local = ca - h.ca_base;
+            a = local / stride; idx = local - a * stride;
+            img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
+            obj = head_act(img_raw[(size_t)(a * epa + 4) * stride + idx], new_coords);
+        }
+        // consecutive classes often fall into the same bin (always, when scores saturate): count runs in registers
+        unsigned run_bin = 0xFFFFFFFFu, run_len = 0;
+        for (int c = 0; c < p.classes; ++c) {
+            unsigned ck;
+            if (FIRST) {
+                ck = 0;
+                if (obj > p.thr) {
+                    const float conf = __fmul_rn(obj, head_act(img_raw[(size_t)(a * epa + 5 + c) * stride + idx], new_coords));
+                    if (conf > p.thr) ck = conf_key(conf);
+                }
+                img_cache[(size_t)c * p.total_ca + ca] = ck;
+            } else {
+                ck = img_cache[(size_t)c * p.total_ca + ca];
+            }
+            if (ck == 0u) continue;
+            const unsigned eidx = (unsigned)ca * (unsigned)p.classes + (unsigned)c;
+            const unsigned long long key = ((unsigned long long)ck << 32) | (unsigned long long)(0xFFFFFFFFu - eidx);
+            if (key >= st.hi) continue;
+            if (MODE == 0) {
+                if (st.level > 0 && (key >> (shift + bits)) != st.prefix) continue;
+                const unsigned bin = (unsigned)(key >> shift) & ((1u << bits) - 1u);
+                if (bin == run_bin) ++run_len;
+                else {
+                    if (run_len) atomicAdd(&s_hist[run_bin], run_len);
+                    run_bin = bin;
+                    run_len = 1;
+                }
+            } else {
+                if (key < st.lo) continue;
+                const int slot = atomicAdd(&band_fill[img], 1);
+                if (slot < p.band_max) band[(size_t)img * p.band_max + slot] = key;
+            }
+        }
+        if (MODE == 0 && run_len) atomicAdd(&s_hist[run_bin], run_len);
+    }
+    if (MODE == 0) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < kBins; i += blockDim.x)
+            if (s_hist[i]) atomicAdd(&hist[(size_t)img * kBins + i], s_hist[i]);
+    }
+}
+
+// Later passes: one thread per cached score key (flat over [class][anchor-cell]); integer work only.  Lanes of a warp
+// that fall into the same histogram bin (all of them, when scores saturate) are merged into one shared-memory add.
+template <int MODE>
+__global__ void __launch_bounds__(256) yolo_scan_cached_kernel(const __grid_constant__ YoloParams p, const ImgState* __restrict__ states,
+                                                               unsigned* __restrict__ hist, unsigned long long* __restrict__ band,
+                                                               int* __restrict__ band_fill, const unsigned* __restrict__ cache) {
     const int img = blockIdx.y;
     const ImgState st = states[img];
     if (MODE == 0 ? st.phase != PHASE_SELECT : st.phase != PHASE_BAND) return;
@@ -141,37 +222,43 @@ __global__ void __launch_bounds__(256) yolo_scan_kernel(const __grid_constant__ 
         __syncthreads();
     }
     const int shift = level_shift(st.level), bits = level_bits(st.level);
-    const int ca = blockIdx.x * blockDim.x + threadIdx.x;
-    if (ca < p.total_ca) {
-        const int hd = find_head(p, ca);
-        const HeadDev& h = p.heads[hd];
-        const int stride = h.gw * h.gh, epa = h.classes + 5;
-        const int local = ca - h.ca_base, a = local / stride, idx = local - a * stride;
-        const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
-        const float obj = head_act(img_raw[(size_t)(a * epa + 4) * stride + idx], h.new_coords);
-        if (obj > p.thr) {
-            for (int c = 0; c < h.classes; ++c) {
-                const float prob = head_act(img_raw[(size_t)(a * epa + 5 + c) * stride + idx], h.new_coords);
-                const float conf = __fmul_rn(obj, prob);
-                if (!(conf > p.thr)) continue;
-                const unsigned eidx = (unsigned)ca * (unsigned)p.classes + (unsigned)c;
-                const unsigned long long key = ((unsigned long long)conf_key(conf) << 32) | (unsigned long long)(0xFFFFFFFFu - eidx);
-                if (key >= st.hi) continue;
-                if (MODE == 0) {
-                    if (st.level > 0 && (key >> (shift + bits)) != st.prefix) continue;
-                    atomicAdd(&s_hist[(unsigned)(key >> shift) & ((1u << bits) - 1u)], 1u);
-                } else {
-                    if (key < st.lo) continue;
-                    const int slot = atomicAdd(&band_fill[img], 1);
-                    if (slot < kBandMax) band[(size_t)img * kBandMax + slot] = key;
-                }
+    const unsigned per_image = (unsigned)p.total_ca * (unsigned)p.classes;
+    const unsigned chunk_begin = blockIdx.x * kFlatChunk;
+    const unsigned* img_cache = cache + (size_t)img * p.cache_stride;
+    // four keys per thread per step (one 16-byte load); the trip count is uniform over the block
+    for (unsigned base = chunk_begin; base < chunk_begin + kFlatChunk && base < per_image; base += 4u * blockDim.x) {
+        const unsigned i0 = base + 4u * threadIdx.x;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (i0 < per_image) v = *reinterpret_cast<const uint4*>(img_cache + i0);  // the padding of the last vector is zero
+        const unsigned cks[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const unsigned i = i0 + e, ck = cks[e];
+            bool valid = false;
+            unsigned bin = 0xFFFFFFFFu;
+            unsigned long long key = 0;
+            if (ck != 0u) {
+                const unsigned c = i / (unsigned)p.total_ca, ca = i - c * (unsigned)p.total_ca;
+                const unsigned eidx = ca * (unsigned)p.classes + c;
+                key = ((unsigned long long)ck << 32) | (unsigned long long)(0xFFFFFFFFu - eidx);
+                valid = key < st.hi;
+                if (MODE == 0) valid = valid && (st.level == 0 || (key >> (shift + bits)) == st.prefix);
+                else valid = valid && key >= st.lo;
+            }
+            if (MODE == 0) {
+                if (valid) bin = (unsigned)(key >> shift) & ((1u << bits) - 1u);
+                const unsigned same = __match_any_sync(0xffffffffu, bin);
+                if (valid && (threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&s_hist[bin], (unsigned)__popc(same));
+            } else if (valid) {
+                const int slot = atomicAdd(&band_fill[img], 1);
+                if (slot < p.band_max) band[(size_t)img * p.band_max + slot] = key;
             }
         }
     }
     if (MODE == 0) {
         __syncthreads();
-        for (int i = threadIdx.x; i < kBins; i += blockDim.x)
-            if (s_hist[i]) atomicAdd(&hist[(size_t)img * kBins + i], s_hist[i]);
+        for (int b = threadIdx.x; b < kBins; b += blockDim.x)
+            if (s_hist[b]) atomicAdd(&hist[(size_t)img * kBins + b], s_hist[b]);
     }
 }
 
@@ -201,8 +288,13 @@ __global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant_
     if (threadIdx.x != 0) return;
     // ---- one thread decides (a few hundred steps at most)
     if (st.level == 0) {
-        int want = 4 * (p.k_eff - st.kept);
-        st.cap = want < 1024 ? 1024 : (want > kBandMax ? kBandMax : want);
+        // band size: four candidates per survivor still wanted, or more when the previous band showed heavier suppression
+        long long want = 4ll * (p.k_eff - st.kept);
+        if (st.last_gain >= 0) {
+            const long long per = ((long long)st.band_count * 3 / 2) / (st.last_gain > 0 ? st.last_gain : 1) + 1;
+            if (per > 4) want = per * (p.k_eff - st.kept);
+        }
+        st.cap = want < 1024 ? 1024 : (want > p.band_max ? p.band_max : (int)want);
         st.above = 0;
         st.prefix = 0;
     }
@@ -271,8 +363,8 @@ __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant
     const int img = blockIdx.x;
     ImgState st = states[img];
     if (st.phase != PHASE_BAND) return;
-    unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem);             // kBandMax
-    float4* kbox = reinterpret_cast<float4*>(keys + kBandMax);                          // k_eff survivors
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem);             // band_max
+    float4* kbox = reinterpret_cast<float4*>(keys + p.band_max);                          // k_eff survivors
     float4* cbox = kbox + p.k_eff;                                                       // kChunk
     unsigned* mask = reinterpret_cast<unsigned*>(cbox + kChunk);                         // kChunk x 16 words
     int* kcls = reinterpret_cast<int*>(mask + kChunk * (kChunk / 32));                   // k_eff
@@ -283,10 +375,10 @@ __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant
     __shared__ int s_kept;
 
     int n = band_fill[img];
-    if (n > kBandMax) n = kBandMax;
+    if (n > p.band_max) n = p.band_max;
     int n2 = 1;
     while (n2 < n) n2 <<= 1;
-    for (int i = threadIdx.x; i < n2; i += blockDim.x) keys[i] = i < n ? band[(size_t)img * kBandMax + i] : 0ull;
+    for (int i = threadIdx.x; i < n2; i += blockDim.x) keys[i] = i < n ? band[(size_t)img * p.band_max + i] : 0ull;
     for (int i = threadIdx.x; i < st.kept; i += blockDim.x) {
         kbox[i] = kept_box[(size_t)img * p.k_eff + i];
         kcls[i] = kept_cls[(size_t)img * p.k_eff + i];
@@ -383,6 +475,8 @@ __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant
         if (s_kept >= p.k_eff) break;
     }
     if (threadIdx.x == 0) {
+        st.last_gain = s_kept - st.kept;
+        st.band_count = n;
         st.kept = s_kept;
         st.hi = st.lo;
         band_fill[img] = 0;
@@ -402,7 +496,7 @@ __global__ void yolo_init_states_kernel(ImgState* states, const int* img_w, cons
     ImgState s;
     s.hi = ~0ull; s.lo = 0; s.prefix = 0;
     s.level = 0; s.phase = PHASE_SELECT; s.cap = 0; s.above = 0; s.band_count = 0; s.kept = 0; s.exhausted = 0;
-    s.img_w = img_w[i]; s.img_h = img_h[i]; s.pad = 0;
+    s.img_w = img_w[i]; s.img_h = img_h[i]; s.last_gain = -1;
     states[i] = s;
 }
 
@@ -495,6 +589,7 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
     p.letterbox = opts->letterbox;
     p.max_per_image = opts->max_per_image;
     p.k_eff = opts->top_k > 0 && opts->top_k < opts->max_per_image ? opts->top_k : opts->max_per_image;
+    p.band_max = p.k_eff <= 1024 ? kBandMaxLarge : kBandMaxSmall;
     if (p.k_eff > 4096) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_yolo_decode_nms: at most 4096 detections per image (top_k / max_per_image)");
     for (int i = 0; i < p.batch; ++i)
         if (image_w[i] <= 0 || image_h[i] <= 0) return ln_fail(ctx, LN_ERR_ARG, "image dimensions must be positive for network detection decoding");
@@ -503,14 +598,16 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
     // scratch: states | hist | band | band_fill | kept | records | sizes | flags
     const size_t sz_states = (size_t)ln_round_up((int64_t)B * sizeof(ImgState), 256);
     const size_t sz_hist = (size_t)B * kBins * 4;
-    const size_t sz_band = (size_t)B * kBandMax * 8;
+    const size_t sz_band = (size_t)B * p.band_max * 8;
     const size_t sz_fill = (size_t)ln_round_up((int64_t)B * 4, 256);
     const size_t sz_kbox = (size_t)B * p.k_eff * sizeof(float4);
     const size_t sz_kcls = (size_t)ln_round_up((int64_t)B * p.k_eff * 4, 256);
     const size_t sz_rec = (size_t)ln_round_up((int64_t)B * p.max_per_image * sizeof(ln_detection), 256);
     const size_t sz_dims = (size_t)ln_round_up((int64_t)B * 8, 256);
     const size_t sz_cnt = (size_t)ln_round_up((int64_t)B * 4, 256);
-    const size_t total = sz_states + sz_hist + sz_band + sz_fill + sz_kbox + sz_kcls + sz_rec + sz_dims + sz_cnt + 256;
+    p.cache_stride = (unsigned)ln_round_up((int64_t)p.total_ca * p.classes, 4);
+    const size_t sz_cache = (size_t)ln_round_up((int64_t)B * p.cache_stride * 4, 256);  // score keys of every (cell, anchor, class)
+    const size_t total = sz_states + sz_hist + sz_band + sz_fill + sz_kbox + sz_kcls + sz_rec + sz_dims + sz_cnt + sz_cache + 256;
     unsigned char* scratch = (unsigned char*)ln_pool_alloc(ctx, total);
     if (!scratch) return LN_ERR_CUDA;
     unsigned char* q = scratch;
@@ -523,6 +620,7 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
     ln_detection* records = (ln_detection*)q; q += sz_rec;
     int* dims = (int*)q; q += sz_dims;
     int* counts = (int*)q; q += sz_cnt;
+    unsigned* cache = (unsigned*)q; q += sz_cache;
     int* flags = (int*)q;  // [0] pending selections, [1] images still active
 
     auto fail = [&](int code) { ln_pool_free(ctx, scratch, total); return code; };
@@ -531,7 +629,8 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
         cudaError_t e__ = (call);                                                                             \
         if (e__ != cudaSuccess) return fail(ln_fail(ctx, LN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e__))); \
     } while (0)
-    LN_Y(cudaMemsetAsync(hist, 0, sz_hist + sz_band * 0, ctx->stream));
+    LN_Y(cudaMemsetAsync(hist, 0, sz_hist, ctx->stream));
+    if (p.cache_stride != (unsigned)p.total_ca * (unsigned)p.classes) LN_Y(cudaMemsetAsync(cache, 0, sz_cache, ctx->stream));  // zero the per-image padding
     LN_Y(cudaMemsetAsync(band_fill, 0, sz_fill, ctx->stream));
     LN_Y(cudaMemsetAsync(flags, 0, 256, ctx->stream));
     LN_Y(cudaMemcpyAsync(dims, image_w, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -539,16 +638,24 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
     yolo_init_states_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, dims, dims + B, B);
     ctx->launches++;
 
-    const size_t nms_smem = (size_t)kBandMax * 8 + (size_t)(p.k_eff + kChunk) * sizeof(float4) + (size_t)kChunk * (kChunk / 32) * 4 +
+    const size_t nms_smem = (size_t)p.band_max * 8 + (size_t)(p.k_eff + kChunk) * sizeof(float4) + (size_t)kChunk * (kChunk / 32) * 4 +
                             (size_t)(p.k_eff + kChunk) * 4 + (size_t)kChunk * 8 + 64;
     LN_Y(cudaFuncSetAttribute(yolo_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nms_smem));
     const dim3 scan_grid((p.total_ca + 255) / 256, B);
+    const dim3 flat_grid((unsigned)(((int64_t)p.total_ca * p.classes + kFlatChunk - 1) / kFlatChunk), B);
     int* h_flags = ctx->h_status + 4;
     const int max_rounds = 4096;
     int round = 0;
+    const bool dbg = getenv("LN_DEBUG_NMS") != nullptr;
+    auto now = []() { timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6; };
+    double t_sel = 0, t_nms = 0;
+    int n_levels = 0;
     for (; round < max_rounds; ++round) {
+        const double ta = dbg ? now() : 0;
         for (int level = 0; level < kLevels; ++level) {
-            yolo_scan_kernel<0><<<scan_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill);
+            ++n_levels;
+            if (round == 0 && level == 0) yolo_scan_kernel<0, true><<<scan_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
+            else yolo_scan_cached_kernel<0><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
             yolo_select_kernel<<<B, 256, 0, ctx->stream>>>(p, states, hist, flags);
             ctx->launches += 2;
             LN_Y(cudaMemcpyAsync(h_flags, flags, 4, cudaMemcpyDeviceToHost, ctx->stream));
@@ -556,14 +663,20 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
             LN_Y(cudaStreamSynchronize(ctx->stream));
             if (h_flags[0] == 0) break;
         }
-        yolo_scan_kernel<1><<<scan_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill);
+        const double tb = dbg ? now() : 0;
+        t_sel += tb - ta;
+        yolo_scan_cached_kernel<1><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
+        if (dbg) { cudaStreamSynchronize(ctx->stream); const double tc = now(); fprintf(stderr, "[ln_yolo] collect %.3f ms\n", tc - tb); }
+        const double td = dbg ? now() : 0;
         yolo_nms_kernel<<<B, 1024, nms_smem, ctx->stream>>>(p, states, band, band_fill, kept_box, kept_cls, records, flags + 1);
         ctx->launches += 2;
         LN_Y(cudaMemcpyAsync(h_flags, flags + 1, 4, cudaMemcpyDeviceToHost, ctx->stream));
         LN_Y(cudaMemsetAsync(flags + 1, 0, 4, ctx->stream));
         LN_Y(cudaStreamSynchronize(ctx->stream));
+        if (dbg) t_nms += now() - td;
         if (h_flags[0] == 0) break;
     }
+    if (dbg) fprintf(stderr, "[ln_yolo] batch %d: %d rounds, %d selection passes (%.3f ms), nms kernels %.3f ms, band_max %d, k_eff %d\n", B, round + 1, n_levels, t_sel, t_nms, p.band_max, p.k_eff);
     if (round == max_rounds) return fail(ln_fail(ctx, LN_ERR_TIMEOUT, "ln_yolo_decode_nms: NMS did not finish in %d rounds", max_rounds));
     yolo_counts_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, counts, B, p.max_per_image);
     ctx->launches++;
