@@ -192,6 +192,26 @@ typedef struct ln_detect_options { /* DetectionOptions (detect.rs:47-61) + top_k
 int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t net_w, int32_t net_h,
                            const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
                            ln_detection* records_host, int32_t* counts_host);
+/* Same result as ln_yolo_decode_nms, for callers that must not allocate device memory.  (No counterpart in the
+   reference: its decode and NMS run on the host.)  Some hosts of this library cannot call cudaMalloc while they
+   serve requests -- a serving loop that has promised its memory budget to other tenants at start-up, a process whose
+   allocator is frozen after initialisation, a thread that may not take the device-wide synchronisation cudaMalloc
+   and cudaFree imply.  This entry point therefore keeps its working memory in a fixed 64 MiB array that belongs to
+   the loaded library (every GPU that loads the library holds those 64 MiB until the process ends) and calls no
+   cudaMalloc, cudaFree or other allocating routine; the caller still owns and passes the head tensors and the two
+   result arrays.
+   Limits and rules:
+     - a call whose working set (it grows with batch x grid cells x anchors x classes, and with max_per_image) does
+       not fit in the 64 MiB is refused with LN_ERR_UNSUPPORTED and a message that names both sizes; nothing is
+       truncated.  For scale: three YOLOv4-608 heads with 80 classes fit for batches up to 8;
+     - the first call on each device looks up the device address of the array; make that first call during set-up,
+       before any stream capture begins;
+     - all calls on a device share the one array, which still holds what the previous call left; the parts that must
+       start at zero are cleared on entry.  Two calls that overlap in time on the same GPU (two contexts, two
+       threads) race on it: serialise them. */
+int32_t ln_yolo_decode_nms_noalloc(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t net_w, int32_t net_h,
+                                   const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
+                                   ln_detection* records_host, int32_t* counts_host);
 /* Decode only: candidates of one image in emission order (parity with decode_yolo_head). */
 int32_t ln_yolo_decode_only(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t image_index, int32_t net_w,
                             int32_t net_h, int32_t image_w, int32_t image_h, float confidence_threshold, int32_t letterbox,

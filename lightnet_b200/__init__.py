@@ -88,6 +88,7 @@ SYMBOLS = {
     "ln_route_concat_q": (C.c_int32, [_VP, _PP, C.c_int32, _I64P, _I64P, _I64P, _I64P, C.c_int64, _PP]),
     "ln_shortcut_add_act_q": (C.c_int32, [_VP, _VP, _VP, C.c_int32, C.c_float, _PP]),
     "ln_yolo_decode_nms": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_int32, _VP, _VP, _VP, _VP, _VP]),
+    "ln_yolo_decode_nms_noalloc": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_int32, _VP, _VP, _VP, _VP, _VP]),
     "ln_yolo_decode_only": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                         C.c_int32, _VP, C.c_int64, C.POINTER(C.c_int64)]),
     "ln_net_create": (C.c_int32, [_VP, C.c_char_p, C.c_int32, C.c_int32, _PP]),
@@ -154,9 +155,10 @@ class Tensor:
         self.h = handle
 
     def __del__(self):
-        if getattr(self, "h", None) and _lib is not None:
+        # a handle that outlives its (closed) backend has nothing left to release: the context took its memory with it
+        if getattr(self, "h", None) and _lib is not None and getattr(self.backend, "ctx", None):
             _lib.ln_tensor_release(self.h)
-            self.h = None
+        self.h = None
 
     @property
     def shape(self):
@@ -174,13 +176,14 @@ class Tensor:
 
 
 class ConvWeights:
-    def __init__(self, handle):
+    def __init__(self, backend, handle):
+        self.backend = backend
         self.h = handle
 
     def __del__(self):
-        if getattr(self, "h", None) and _lib is not None:
+        if getattr(self, "h", None) and _lib is not None and getattr(self.backend, "ctx", None):
             _lib.ln_conv_weights_release(self.h)
-            self.h = None
+        self.h = None
 
 
 class B200Backend:
@@ -315,7 +318,7 @@ class B200Backend:
     def conv_weights_q(self, weights, filters, channels, kernel_size, dtype=LN_Q8):
         h = C.c_void_p()
         self._check(self.lib.ln_conv_weights_q(self.ctx, weights.h, filters, channels, kernel_size, dtype, C.byref(h)))
-        return ConvWeights(h)
+        return ConvWeights(self, h)
 
     def conv2d_bias_act_q(self, x, weights, bias, output_shape, channels, input_height, input_width, filters, kernel_size,
                           stride_x, stride_y, dilation, padding, groups, activation, y_scale=1.0, out_kind=LN_OUT_Q):
@@ -354,7 +357,7 @@ class B200Backend:
         return arr
 
     def yolo_decode_nms(self, heads, net_w, net_h, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45,
-                        letterbox=True, top_k=0, max_per_image=1024):
+                        letterbox=True, top_k=0, max_per_image=1024, noalloc=False):
         """heads: list of dicts {raw: Tensor f32 [B, A*(5+cls), gh, gw], classes, anchors [(w,h)...], scale_x_y, new_coords}.
         Returns a list (one per image) of (n,7) arrays {class, conf, obj, x, y, w, h}, confidence descending."""
         arr = self._heads(heads)
@@ -364,8 +367,10 @@ class B200Backend:
         opts = ln_detect_options(confidence_threshold, nms_threshold, int(letterbox), top_k, max_per_image)
         rec = np.zeros((batch, max_per_image, 7), np.float32)
         cnt = np.zeros(batch, np.int32)
-        self._check(self.lib.ln_yolo_decode_nms(self.ctx, arr, len(heads), net_w, net_h, _ptr(iw), _ptr(ih), C.byref(opts), _ptr(rec),
-                                                _ptr(cnt)))
+        # noalloc=True takes the entry point that keeps its working memory in a fixed array of the library (for hosts
+        # that may not allocate device memory while serving); same records, bounded problem size
+        fn = self.lib.ln_yolo_decode_nms_noalloc if noalloc else self.lib.ln_yolo_decode_nms
+        self._check(fn(self.ctx, arr, len(heads), net_w, net_h, _ptr(iw), _ptr(ih), C.byref(opts), _ptr(rec), _ptr(cnt)))
         return [rec[b, :cnt[b]].copy() for b in range(batch)]
 
     def yolo_decode_only(self, heads, image_index, net_w, net_h, image_w, image_h, confidence_threshold, letterbox, capacity=1 << 22):

@@ -689,6 +689,123 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
     return LN_OK;
 }
 
+// ---- decode + NMS without any allocation ------------------------------------------------------------
+// Working memory of ln_yolo_decode_nms_noalloc: a fixed array that is part of the loaded module.  Every GPU
+// that loads this library carries these 64 MiB until the process exits, whether or not the entry point is used.
+#define LN_NOALLOC_SCRATCH_BYTES (64u * 1024u * 1024u)
+static __device__ __align__(256) unsigned char ln_noalloc_scratch[LN_NOALLOC_SCRATCH_BYTES];
+// Device address of the array above, per device ordinal.  In host code the name `ln_noalloc_scratch` is only a
+// stand-in for the symbol, not a pointer a kernel could use; the address has to be asked for, once per device.
+static unsigned char* g_noalloc_ptr[64] = {nullptr};
+
+int32_t ln_yolo_decode_nms_noalloc(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t net_w, int32_t net_h, const int32_t* image_w,
+                                   const int32_t* image_h, const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host) {
+    const char* who = "ln_yolo_decode_nms_noalloc";
+    if (!ctx || !heads || !image_w || !image_h || !opts || !records_host || !counts_host) return ln_fail(ctx, LN_ERR_ARG, "%s: NULL argument", who);
+    if (opts->max_per_image < 1) return ln_fail(ctx, LN_ERR_ARG, "%s: max_per_image must be positive", who);
+    if (ctx->device < 0 || ctx->device >= 64) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "%s: device ordinal %d is outside the table of 64", who, ctx->device);
+    YoloParams p;
+    int rc = fill_params(ctx, &p, heads, n_heads, net_w, net_h, who);
+    if (rc) return rc;
+    p.thr = opts->confidence_threshold;
+    p.nms_thr = opts->nms_threshold;
+    p.letterbox = opts->letterbox;
+    p.max_per_image = opts->max_per_image;
+    p.k_eff = opts->top_k > 0 && opts->top_k < opts->max_per_image ? opts->top_k : opts->max_per_image;
+    p.band_max = kBandMaxSmall;
+    if (p.k_eff > 4096) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "%s: at most 4096 detections per image (top_k / max_per_image)", who);
+    for (int i = 0; i < p.batch; ++i)
+        if (image_w[i] <= 0 || image_h[i] <= 0) return ln_fail(ctx, LN_ERR_ARG, "image dimensions must be positive for network detection decoding");
+    const int B = p.batch;
+    const size_t sz_states = (size_t)ln_round_up((int64_t)B * sizeof(ImgState), 256);
+    const size_t sz_hist = (size_t)B * kBins * 4;
+    const size_t sz_band = (size_t)B * p.band_max * 8;
+    const size_t sz_fill = (size_t)ln_round_up((int64_t)B * 4, 256);
+    const size_t sz_kbox = (size_t)B * p.k_eff * sizeof(float4);
+    const size_t sz_kcls = (size_t)ln_round_up((int64_t)B * p.k_eff * 4, 256);
+    const size_t sz_rec = (size_t)ln_round_up((int64_t)B * p.max_per_image * sizeof(ln_detection), 256);
+    const size_t sz_dims = (size_t)ln_round_up((int64_t)B * 8, 256);
+    const size_t sz_cnt = (size_t)ln_round_up((int64_t)B * 4, 256);
+    p.cache_stride = (unsigned)ln_round_up((int64_t)p.total_ca * p.classes, 4);
+    const size_t sz_cache = (size_t)ln_round_up((int64_t)B * p.cache_stride * 4, 256);
+    const size_t total = sz_states + sz_hist + sz_band + sz_fill + sz_kbox + sz_kcls + sz_rec + sz_dims + sz_cnt + sz_cache + 256;
+    if (total > (size_t)LN_NOALLOC_SCRATCH_BYTES)
+        return ln_fail(ctx, LN_ERR_UNSUPPORTED,
+                       "%s: this call needs %zu bytes of working memory (batch %d, %d candidates per image, %d records per image) but the fixed "
+                       "array holds %u; use a smaller batch, fewer records, or ln_yolo_decode_nms",
+                       who, total, B, p.total_ca * p.classes, p.max_per_image, LN_NOALLOC_SCRATCH_BYTES);
+    cudaSetDevice(ctx->device);
+    if (!g_noalloc_ptr[ctx->device]) {
+        // once per device, with that device current: the address of the module's array on this device
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, ln_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) return ln_fail(ctx, LN_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
+        g_noalloc_ptr[ctx->device] = (unsigned char*)ptr;
+    }
+    unsigned char* q = g_noalloc_ptr[ctx->device];
+    ImgState* states = (ImgState*)q; q += sz_states;
+    unsigned* hist = (unsigned*)q; q += sz_hist;
+    unsigned long long* band = (unsigned long long*)q; q += sz_band;
+    int* band_fill = (int*)q; q += sz_fill;
+    float4* kept_box = (float4*)q; q += sz_kbox;
+    int* kept_cls = (int*)q; q += sz_kcls;
+    ln_detection* records = (ln_detection*)q; q += sz_rec;
+    int* dims = (int*)q; q += sz_dims;
+    int* counts = (int*)q; q += sz_cnt;
+    unsigned* cache = (unsigned*)q; q += sz_cache;
+    int* flags = (int*)q;
+#define LN_Z(call)                                                                                     \
+    do {                                                                                               \
+        cudaError_t e__ = (call);                                                                      \
+        if (e__ != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
+    } while (0)
+    // the array keeps whatever the previous call left: clear everything the kernels expect to start at zero
+    LN_Z(cudaMemsetAsync(hist, 0, sz_hist, ctx->stream));
+    LN_Z(cudaMemsetAsync(band_fill, 0, sz_fill, ctx->stream));
+    LN_Z(cudaMemsetAsync(flags, 0, 256, ctx->stream));
+    if (p.cache_stride != (unsigned)p.total_ca * (unsigned)p.classes) LN_Z(cudaMemsetAsync(cache, 0, sz_cache, ctx->stream));
+    LN_Z(cudaMemcpyAsync(dims, image_w, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    LN_Z(cudaMemcpyAsync(dims + B, image_h, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    yolo_init_states_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, dims, dims + B, B);
+    ctx->launches++;
+    const size_t nms_smem = (size_t)p.band_max * 8 + (size_t)(p.k_eff + kChunk) * sizeof(float4) + (size_t)kChunk * (kChunk / 32) * 4 +
+                            (size_t)(p.k_eff + kChunk) * 4 + (size_t)kChunk * 8 + 64;
+    LN_Z(cudaFuncSetAttribute(yolo_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nms_smem));
+    const dim3 scan_grid((p.total_ca + 255) / 256, B);
+    const dim3 flat_grid((unsigned)(((int64_t)p.total_ca * p.classes + kFlatChunk - 1) / kFlatChunk), B);
+    int* h_flags = ctx->h_status + 4;
+    const int max_rounds = 4096;
+    int round = 0;
+    for (; round < max_rounds; ++round) {
+        for (int level = 0; level < kLevels; ++level) {
+            if (round == 0 && level == 0) yolo_scan_kernel<0, true><<<scan_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
+            else yolo_scan_cached_kernel<0><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
+            yolo_select_kernel<<<B, 256, 0, ctx->stream>>>(p, states, hist, flags);
+            ctx->launches += 2;
+            LN_Z(cudaMemcpyAsync(h_flags, flags, 4, cudaMemcpyDeviceToHost, ctx->stream));
+            LN_Z(cudaMemsetAsync(flags, 0, 4, ctx->stream));
+            LN_Z(cudaStreamSynchronize(ctx->stream));
+            if (h_flags[0] == 0) break;
+        }
+        yolo_scan_cached_kernel<1><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
+        yolo_nms_kernel<<<B, 1024, nms_smem, ctx->stream>>>(p, states, band, band_fill, kept_box, kept_cls, records, flags + 1);
+        ctx->launches += 2;
+        LN_Z(cudaMemcpyAsync(h_flags, flags + 1, 4, cudaMemcpyDeviceToHost, ctx->stream));
+        LN_Z(cudaMemsetAsync(flags + 1, 0, 4, ctx->stream));
+        LN_Z(cudaStreamSynchronize(ctx->stream));
+        if (h_flags[0] == 0) break;
+    }
+    if (round == max_rounds) return ln_fail(ctx, LN_ERR_TIMEOUT, "%s: NMS did not finish in %d rounds", who, max_rounds);
+    yolo_counts_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, counts, B, p.max_per_image);
+    ctx->launches++;
+    LN_Z(cudaGetLastError());
+    LN_Z(cudaMemcpyAsync(counts_host, counts, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LN_Z(cudaMemcpyAsync(records_host, records, (size_t)B * p.max_per_image * sizeof(ln_detection), cudaMemcpyDeviceToHost, ctx->stream));
+    LN_Z(cudaStreamSynchronize(ctx->stream));
+#undef LN_Z
+    return LN_OK;
+}
+
 int32_t ln_yolo_decode_only(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t image_index, int32_t net_w, int32_t net_h,
                             int32_t image_w, int32_t image_h, float confidence_threshold, int32_t letterbox, ln_detection* records_host,
                             int64_t capacity, int64_t* count) {
