@@ -261,6 +261,9 @@ int32_t ln_net_last_times(const ln_net* net, float times_ms[2]);
    the ctx stream (the forward then synchronises).  ln_net_profile returns, for the last forward, device ms per layer
    (per_layer_ms[num_layers]) and per kernel class (per_op_ms[8]: 0 tensor-core conv, 1 CUDA-core conv, 2 first-layer
    conv, 3 max-pool, 4 up-sample, 5 route copy, 6 shortcut, 7 input quantise) and the launch count per class. */
+/* 8-bit plans run a linear [shortcut] in the epilogue of the convolution in front of it when nobody else reads that
+   convolution (same arithmetic on the same int8 codes, so results do not change); 0 = keep every layer separate. */
+int32_t ln_net_set_fusion(ln_net* net, int32_t on);
 int32_t ln_net_set_profile(ln_net* net, int32_t on);
 /* 8-bit forwards replay one captured CUDA graph of the whole batch (default on); 0 = launch kernel by kernel. */
 int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on);

@@ -111,6 +111,7 @@ SYMBOLS = {
     "ln_net_detect_device": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_last_times": (C.c_int32, [_VP, _VP]),
     "ln_net_set_profile": (C.c_int32, [_VP, C.c_int32]),
+    "ln_net_set_fusion": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_set_cuda_graph": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_profile": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
 }
@@ -489,6 +490,9 @@ class GpuExecutableNetwork:
 
     def set_cuda_graph(self, on: bool):
         self.backend._check(self.lib.ln_net_set_cuda_graph(self.h, int(on)))
+
+    def set_fusion(self, on: bool):
+        self.backend._check(self.lib.ln_net_set_fusion(self.h, int(on)))
 
     def set_profile(self, on: bool):
         self.backend._check(self.lib.ln_net_set_profile(self.h, int(on)))

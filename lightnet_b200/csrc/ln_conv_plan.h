@@ -30,6 +30,10 @@ struct ln_conv_umma_params {
     const float2* mb;  // [fpad] {x_scale * w_scale[f], bias[f]}
     void* out;
     long long out_pixel_stride;  // bytes between pixels of an 8-bit NHWC output
+    // fused shortcut (null = none): out = quant((code * s_c + residual_code * s_res) * inv_sy2), code = the convolution's own int8 output
+    const void* res;
+    long long res_pixel_stride;
+    float s_c, s_res, inv_sy2;
     int* status;
     long long* debug;  // optional: role timing of CTA 0 (32 counters), null = off
 };
@@ -56,6 +60,10 @@ struct ln_conv_geom {
     bool small_acc = false;  // 127 * max over filters of sum|w code| < 2^22
     void* out = nullptr;
     long long out_pixel_stride = 0;
+    // fused linear shortcut that follows the convolution (see ln_conv_umma_params)
+    const void* res = nullptr;
+    long long res_pixel_stride = 0;
+    float s_c = 1.0f, s_res = 1.0f, inv_sy2 = 1.0f;
 };
 
 inline int ln_conv_choose_bn(int64_t F) {

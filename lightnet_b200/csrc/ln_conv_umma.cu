@@ -53,6 +53,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the wait was abandoned (own limit reached, or another role
 // already raised the CTA's abort flag).
+template <bool BACKOFF = true>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                           long long* waited = nullptr) {
     const long long t0 = waited ? clock64() : 0;
@@ -61,7 +62,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (waited) *waited += clock64() - t0;
             return true;
         }
-        if (it > 4u) __nanosleep(40);  // stop stealing issue slots from the epilogue warps of this scheduler
+        if (BACKOFF && it > 4u) __nanosleep(40);  // single-lane roles: stop stealing issue slots from the epilogue warps of this scheduler
         if ((it & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1;
@@ -140,6 +141,11 @@ __device__ __forceinline__ uint32_t quant_i8_magic(float a, float inv_s) {
     float t = __fmul_rn(a, inv_s);
     t = fminf(fmaxf(t, -127.0f), 127.0f);  // NaN -> -127
     return __float_as_uint(__fadd_rn(t, 12582912.0f));
+}
+// signed byte `b` (0..3) of w as a float, FMA pipe only: (byte ^ 0x80) is byte + 128 as an unsigned number
+__device__ __forceinline__ float s8_to_float(uint32_t w, int b) {
+    const uint32_t u = (w >> (8 * b)) & 0xFFu;
+    return __fadd_rn(__uint_as_float(0x4B000000u | (u ^ 0x80u)), -8388736.0f);
 }
 __device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
@@ -292,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             if ((t & 1) != group) continue;  // the other group of epilogue warps takes this tile
             const int buf = t % nbuf;
             const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
-            if (!(ok = mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT, pwe))) break;
+            if (!(ok = mbar_wait<false>(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT, pwe))) break;
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * bn);
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
@@ -308,6 +314,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     float4 m[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) m[j] = ldg_f4_pinned(mb4 + j);
+                    uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
+                    if (p.res != nullptr && valid) {  // residual codes of the fused shortcut, fetched while TMEM is read
+                        const uint4* rp = (const uint4*)((const uint8_t*)p.res + pix * p.res_pixel_stride + f0 + c0);
+                        r0 = __ldg(rp);
+                        r1 = __ldg(rp + 1);
+                    }
                     tmem_ld_wait();
                     const long long tq1 = p.debug ? clock64() : 0;
                     if (p.debug) dbg_ld += tq1 - tq0;
@@ -346,6 +358,21 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                             const uint32_t q23 = ln_h2_act_quant<ACT>(__fmaf_rn(x[4 * j + 2], m[2 * j + 1].x, m[2 * j + 1].y),
                                                                       __fmaf_rn(x[4 * j + 3], m[2 * j + 1].z, m[2 * j + 1].w), inv_h);
                             packed[j] = ln_h2_pack(q01, q23);
+                        }
+                    }
+                    if (p.res != nullptr) {
+                        // fused shortcut, the arithmetic of the stand-alone shortcut kernel applied to the codes just produced
+                        const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            uint32_t u[4];
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                float v = __fmul_rn(s8_to_float(packed[j], b), p.s_c);
+                                v = __fmaf_rn(s8_to_float(rw[j], b), p.s_res, v);
+                                u[b] = quant_i8_magic(v, p.inv_sy2);
+                            }
+                            packed[j] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
                         }
                     }
                     const long long tq2 = p.debug ? clock64() : 0;
@@ -538,6 +565,9 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     if ((long long)p.num_tiles * p.num_tiles >= (1ll << 40)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d tiles", p.num_tiles);
     p.act = g.act; p.inv_sy = g.inv_sy; p.out_kind = g.out_kind;
     p.out = g.out; p.out_pixel_stride = g.out_pixel_stride;
+    p.res = g.res; p.res_pixel_stride = g.res_pixel_stride; p.s_c = g.s_c; p.s_res = g.s_res; p.inv_sy2 = g.inv_sy2;
+    if (g.res && (g.out_kind != LN_OUT_Q || g.kind != LN_KIND_I8 || g.F % 32 != 0 || (((uintptr_t)g.res) & 15) || (g.res_pixel_stride & 15)))
+        return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: a fused shortcut needs int8 output, filters a multiple of 32 and 16-byte aligned residuals");
     p.status = ctx->d_status;
     p.debug = ctx->debug_cycles;
     p.mb = plan->mb;

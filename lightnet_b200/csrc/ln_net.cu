@@ -241,6 +241,8 @@ struct ln_net {
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     float times_ms[2] = {0, 0};
     // CUDA graph of the 8-bit plan (one graph = the whole batch: every micro-batch, every layer)
+    bool fuse_shortcut = true;  // a linear [shortcut] whose input is a convolution nobody else reads runs in that convolution's epilogue
+    std::vector<char> fused_into_next;  // per layer: its output is not materialised (8-bit plan)
     bool use_graph = true;
     cudaGraphExec_t graph_exec = nullptr;
     const void* graph_input = nullptr;
@@ -544,6 +546,24 @@ int build_plan(ln_net* net, int mb) {
             off += net->layers[s].out.c;
         }
     }
+    // 2b. shortcut fusion: conv i -> shortcut i+1 (linear, one same-shape source), conv output read by nobody else
+    net->fused_into_next.assign(NL, 0);
+    if (net->fuse_shortcut && kind == LN_KIND_I8) {
+        std::vector<int> readers(NL, 0);
+        for (int i = 0; i < NL; ++i) {
+            if (i > 0 && net->layers[i].kind != K_ROUTE) readers[i - 1]++;  // sequential input (a route ignores it)
+            if (net->layers[i].kind == K_ROUTE || net->layers[i].kind == K_SHORTCUT)
+                for (int s : net->layers[i].sources) readers[s]++;
+        }
+        for (int i = 1; i + 1 < NL; ++i) {
+            const NLayer& C = net->layers[i];
+            const NLayer& S = net->layers[i + 1];
+            if (C.kind != K_CONV || S.kind != K_SHORTCUT || S.act != LN_ACT_LINEAR || S.sources.size() != 1) continue;
+            if (readers[i] != 1 || S.sources[0] == i || C.filters % 32 != 0 || feeds_head(net, i)) continue;
+            if (!ln_conv_umma_supported(ln_round_up(C.in.c, 32), C.size, C.stride_x, C.stride_y, C.dilation, C.groups, C.in.w, C.in.h)) continue;
+            net->fused_into_next[i] = 1;
+        }
+    }
     // 3. buffers and views
     net->views.assign(NL, QView());
     std::vector<int> buffer_of(NL, -1);
@@ -628,6 +648,12 @@ int build_plan(ln_net* net, int mb) {
                 g.inv_sy = head ? 1.0f : 1.0f / sy;
                 g.small_acc = kind == LN_KIND_I8 && 127.0f * L.wq->max_l1 < 4194304.0f;
                 if (head) { g.out = net->heads[st.head_index]->ptr; g.out_pixel_stride = 0; }
+                else if (net->fused_into_next[i]) {
+                    const int sl = i + 1, src = net->layers[sl].sources[0];
+                    g.out = net->views[sl].ptr; g.out_pixel_stride = net->views[sl].cstride;
+                    g.res = net->views[src].ptr; g.res_pixel_stride = net->views[src].cstride;
+                    g.s_c = sy; g.s_res = net->scale[src + 1]; g.inv_sy2 = 1.0f / net->scale[sl + 1];
+                }
                 else { g.out = net->views[i].ptr; g.out_pixel_stride = net->views[i].cstride; }
                 if (i == 0) {
                     if (L.in.c > 4) {  // generic first layer: quantise the image, then a normal convolution
@@ -655,6 +681,7 @@ int build_plan(ln_net* net, int mb) {
                     rc = ln_conv_umma_plan_build(ctx, &st.umma, g);
                     if (rc) return rc;
                 } else st.op = 1;
+                if (st.op != 0 && net->fused_into_next[i]) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: a fused shortcut needs the tensor-core convolution", i);
                 net->steps.push_back(st);
                 break;
             }
@@ -703,6 +730,7 @@ int build_plan(ln_net* net, int mb) {
                 break;
             }
             case K_SHORTCUT: {
+                if (net->fused_into_next[i - 1]) break;  // done in the epilogue of the convolution before it
                 st.op = 6;
                 const int s = L.sources[0];
                 st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride; st.sa = sx;
@@ -1076,6 +1104,7 @@ int32_t ln_net_layer_output(ln_net* net, int32_t layer, ln_tensor** out) {
         *out = net->heads[k];
         return LN_OK;
     }
+    if (net->fused_into_next[layer]) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer %d is fused into the shortcut after it and has no output of its own (ln_net_set_fusion(0) keeps it)", layer);
     const QView& v = net->views[layer];
     // a copy, so that the handle stays valid after the plan is rebuilt
     ln_tensor* t = ln_tensor_new(ctx, net->precision, net->batch, v.c, v.h, v.w);
@@ -1118,6 +1147,13 @@ int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on) {
     if (!net) return LN_ERR_ARG;
     net->use_graph = on != 0;
     if (!net->use_graph) release_graph(net);
+    return LN_OK;
+}
+
+int32_t ln_net_set_fusion(ln_net* net, int32_t on) {
+    if (!net) return LN_ERR_ARG;
+    net->fuse_shortcut = on != 0;
+    release_plan(net);
     return LN_OK;
 }
 

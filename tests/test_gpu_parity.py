@@ -469,6 +469,13 @@ def check_q8_network(be, cfg, batch, seed, micro_batch=0):
 
 def test_mini_network_q8_bit_exact(be):
     o, net, x = check_q8_network(be, MINI_CFG, 4, 21)
+    # with the shortcut fused into the convolution in front of it (the default) that convolution has no output of its own
+    with pytest.raises(ln.BackendError):
+        net.layer_output(6)
+    got, _ = be.download_q(net.layer_output(7))
+    assert np.array_equal(got, o.layer_output_q8(7))
+    net.set_fusion(False)
+    net.forward(x)
     for i, l in enumerate(o.layers()):
         if l["kind"] == "yolo":
             continue
@@ -477,6 +484,7 @@ def test_mini_network_q8_bit_exact(be):
             continue
         got, s = be.download_q(net.layer_output(i))
         assert np.array_equal(got, o.layer_output_q8(i)), (i, l["kind"])
+    net.set_fusion(True)
     dets = net.detect(x, 640, 480, 0.2, 0.45, True, 0, 512)
     for b in range(4):
         ref = o.detect("q8", b, 640, 480, 0.2, 0.45, True, det_exp=True)
