@@ -18,6 +18,7 @@ struct ln_conv_umma_params {
     CUtensorMap tmA[4];  // activations; stride-2 convolutions use one map per input parity class
     CUtensorMap tmB;     // weights as a [fpad][k*k*cpad] matrix
     int bk, bn, stages, nbuf;
+    int b_resident;  // the weights of the (single) filter tile stay in shared memory for the whole kernel
     int small_acc;  // every accumulator is known to stay below 2^22 in magnitude
     int R, S, stride, pad;
     int cblocks, cpad;

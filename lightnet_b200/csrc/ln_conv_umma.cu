@@ -53,7 +53,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the wait was abandoned (own limit reached, or another role
 // already raised the CTA's abort flag).
-template <bool BACKOFF = true>
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                           long long* waited = nullptr) {
     const long long t0 = waited ? clock64() : 0;
@@ -169,15 +169,22 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int bk = p.bk, bn = p.bn, stages = p.stages;
-    const uint32_t a_bytes = 128u * bk, b_bytes = (uint32_t)bn * bk, stage_bytes = a_bytes + b_bytes;
-    const uint32_t bar_base = smem_base + (uint32_t)stages * stage_bytes;
+    // Weight-stationary mode (one filter tile, all of its weights fit): the B operand of every k-block is loaded once and
+    // stays in shared memory; the ring then carries activations only.  TMA cost is per row, so this removes a third of the
+    // load work of the layers with few channels.
+    const bool b_res = p.b_resident != 0;
+    const uint32_t a_bytes = 128u * bk, b_bytes = (uint32_t)bn * bk, stage_bytes = b_res ? a_bytes : a_bytes + b_bytes;
+    const uint32_t bres_base = smem_base;  // resident weights first (kblocks * b_bytes), then the ring
+    const uint32_t ring_base = smem_base + (b_res ? (uint32_t)(p.R * p.S * p.cblocks) * b_bytes : 0u);
+    const uint32_t bar_base = ring_base + (uint32_t)stages * stage_bytes;
     // barrier block: full[8] empty[8] tfull[8] tempty[8] | tmem slot | abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + kMaxAccBufs + b); };
     uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(generic_base + (bar_base - smem_base) + 8u * (2 * kMaxStages + 2 * kMaxAccBufs));
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(generic_base + (bar_base - smem_base) + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 1));
+    const uint32_t bres_bar = bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -193,6 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             mbar_init(tfull_bar(b), 1);
             mbar_init(tempty_bar(b), kEpilogueWarps / 2);
         }
+        mbar_init(bres_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -218,6 +226,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             long long w_empty = 0;
             long long* pw = p.debug ? &w_empty : nullptr;
             const long long t_start = clock64();
+            if (b_res && (int)blockIdx.x < p.num_tiles) {
+                mbar_arrive_expect_tx(bres_bar, (uint32_t)kblocks * b_bytes);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
+                    tma_load_2d(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, 0, bres_bar);
+                }
+            }
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
                 const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
                 const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
@@ -234,10 +249,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                         map = py * 2 + px;
                     }
                     if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
-                    const uint32_t sa = smem_base + (uint32_t)stage * stage_bytes;
+                    const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
                     mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
                     tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(stage));
-                    tma_load_2d(sa + a_bytes, &p.tmB, tap * p.cpad + c0, f0, full_bar(stage));
+                    if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, tap * p.cpad + c0, f0, full_bar(stage));
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -256,6 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             long long* pw1 = p.debug ? &w_tempty : nullptr;
             long long* pw2 = p.debug ? &w_full : nullptr;
             const long long t_start = clock64();
+            if (b_res && (int)blockIdx.x < p.num_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT);
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
                 const int buf = t % nbuf;
                 const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
@@ -265,8 +281,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_base + (uint32_t)stage * stage_bytes;
-                    const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(sa + a_bytes, bk);
+                    const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
+                    const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + a_bytes, bk);
                     for (int k = 0; k < bk / 32; ++k)  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
                         tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
                     tc_commit(empty_bar(stage));  // arrives when the MMAs above have finished reading this stage
@@ -572,12 +588,14 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.debug = ctx->debug_cycles;
     p.mb = plan->mb;
 
-    const uint32_t stage_bytes = (uint32_t)(128 + bn) * bk;
-    int stages = (int)((200 * 1024) / stage_bytes);
+    const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)bn * bk;  // all weights of one filter tile
+    p.b_resident = (p.tiles_f == 1 && b_total <= 96u * 1024u) ? 1 : 0;
+    const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + bn) * bk;
+    int stages = (int)((200 * 1024 - (p.b_resident ? b_total : 0u)) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
     p.stages = stages;
-    plan->smem = (size_t)stages * stage_bytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    plan->smem = (size_t)stages * stage_bytes + (p.b_resident ? b_total : 0u) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     plan->kind = g.kind;
 

@@ -77,6 +77,7 @@ struct QStep {
     uint8_t* y = nullptr; int64_t ys = 0;
     float sa = 1, sb = 1, inv_sy = 1;
     int C = 0, H = 0, W = 0, OH = 0, OW = 0;
+    int pool_size = 0, pool_pad = 0;  // max-pool window actually run (a cascade shrinks it)
 };
 
 struct Section {
@@ -688,6 +689,23 @@ int build_plan(ln_net* net, int mb) {
             case K_MAXPOOL: {
                 st.op = 3;
                 st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride;
+                st.pool_size = L.size; st.pool_pad = L.padding;
+                // SPP cascade: a centred stride-1 max over s x s equals a centred max over (s - s' + 1) of an earlier
+                // centred s' x s' max of the same tensor (taps outside the image are skipped = -inf padding), e.g. 9 = 5 o 5
+                if (L.stride_x == 1 && L.stride_y == 1 && (L.size & 1) && L.padding == L.size - 1) {
+                    int best = -1;
+                    for (int j = 0; j < i; ++j) {
+                        const NLayer& P = net->layers[j];
+                        if (P.kind != K_MAXPOOL || P.stride_x != 1 || P.stride_y != 1 || !(P.size & 1) || P.padding != P.size - 1 || P.size >= L.size) continue;
+                        if (j == 0 || root_of(j - 1) != root_of(i - 1)) continue;
+                        if (best < 0 || P.size > net->layers[best].size) best = j;
+                    }
+                    if (best >= 0) {
+                        st.x = net->views[best].ptr; st.xs = net->views[best].cstride;
+                        st.pool_size = L.size - net->layers[best].size + 1;
+                        st.pool_pad = st.pool_size - 1;
+                    }
+                }
                 st.y = net->views[i].ptr; st.ys = net->views[i].cstride;
                 st.C = L.in.c; st.H = L.in.h; st.W = L.in.w; st.OH = L.out.h; st.OW = L.out.w;
                 net->steps.push_back(st);
@@ -786,7 +804,7 @@ int run_plan(ln_net* net, const float* input_dev_f32) {
                     rc = ln_conv_stem_launch(ctx, kind, input_dev_f32 + b0 * in_image, st.inv_sy, mb, L.in.c, L.in.h, L.in.w, L.wq->w_oihw, st.mb, L.filters, L.size,
                                              L.stride_x, L.padding, L.out.h, L.out.w, L.act, st.geom.inv_sy, st.geom.out, st.geom.out_pixel_stride);
                     break;
-                case 3: rc = ln_q_maxpool_launch(ctx, kind, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, st.OH, st.OW, L.size, L.stride_x, L.stride_y, L.padding); break;
+                case 3: rc = ln_q_maxpool_launch(ctx, kind, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, st.OH, st.OW, st.pool_size, L.stride_x, L.stride_y, st.pool_pad); break;
                 case 4: rc = ln_q_upsample_launch(ctx, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, L.up_stride); break;
                 case 5: rc = ln_q_copy_launch(ctx, st.x, st.xs, st.y, st.ys, (int64_t)mb * st.H * st.W, st.C); break;
                 case 6: rc = ln_q_shortcut_launch(ctx, kind, st.x, st.xs, st.sa, st.x2, st.xs2, st.sb, st.y, st.ys, (int64_t)mb * st.H * st.W, st.C, L.act, st.inv_sy); break;

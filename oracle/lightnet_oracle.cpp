@@ -100,6 +100,9 @@ struct Layer {
     std::vector<int8_t> wq;      // [filters][C/g][k][k]
     std::vector<float> wscale;   // per filter
     std::vector<float> fbias;    // folded bias
+    // FP8 E4M3 model: per-filter scale max|w|/448, codes
+    std::vector<uint8_t> w8;
+    std::vector<float> w8scale;
 };
 
 struct Net {
@@ -109,6 +112,8 @@ struct Net {
     std::vector<Tensor> out_f32;
     std::vector<TensorI8> out_q8;
     std::vector<Tensor> head_q8;          // f32 heads of the int8 run, indexed by layer
+    std::vector<std::vector<uint8_t>> out_f8;  // E4M3 codes, NCHW, per layer (FP8 run)
+    std::vector<Tensor> head_f8;
     std::vector<float> amax;              // [0] = input, [1+i] = layer i output (f32 run)
     std::vector<float> scale;             // same indexing; per-tensor activation scale
     std::string error;
@@ -610,6 +615,55 @@ static inline float det_activate(Act a, float v) {
 //   conv    : acc = sum(xq*wq) int32;  v = fma(float(acc), s_x*s_k, b_k);  a = det_act(v)
 //             int8 out: q = clamp(rne(a * (1/s_y)), +-127);  head conv (feeds [yolo]): a kept f32
 // ---------------------------------------------------------------------------
+// FP8 E4M3 codec: lightnet-cuda-oxide/src/fp8.rs:153-181 (RNE, satfinite 448,
+// NaN -> 0x7F), decode :140-150.
+// ---------------------------------------------------------------------------
+
+static float e4m3_decode_mag(uint8_t m) {
+    int e = (m >> 3) & 0xF, f = m & 7;
+    if (e == 0) return std::ldexp((float)f, -9);
+    return std::ldexp(1.0f + (float)f / 8.0f, e - 7);
+}
+static float e4m3_to_f32(uint8_t bits) {
+    uint8_t m = bits & 0x7F;
+    if (m == 0x7F) return std::numeric_limits<float>::quiet_NaN();
+    float v = e4m3_decode_mag(m);
+    return (bits & 0x80) ? -v : v;
+}
+static uint8_t f32_to_e4m3(float v) {
+    if (std::isnan(v)) return 0x7F;
+    uint8_t sign = std::signbit(v) ? 0x80 : 0;
+    float mag = std::fabs(v);
+    const uint8_t maxc = 0x7E;
+    if (mag > e4m3_decode_mag(maxc)) return sign | maxc;
+    uint8_t best = 0;
+    float bd = std::numeric_limits<float>::infinity();
+    for (int c = 0; c <= maxc; ++c) {
+        float dist = std::fabs(mag - e4m3_decode_mag((uint8_t)c));
+        if (dist < bd || (dist == bd && (c & 1) == 0)) { best = (uint8_t)c; bd = dist; }
+    }
+    return sign | best;
+}
+
+
+// Same mapping as f32_to_e4m3 (the reference's search), by binary search over the 127 finite magnitudes.
+static uint8_t f32_to_e4m3_fast(float v) {
+    static float mags[127];
+    static bool init = false;
+    if (!init) { for (int c = 0; c < 127; ++c) mags[c] = e4m3_decode_mag((uint8_t)c); init = true; }
+    if (std::isnan(v)) return 0x7F;
+    const uint8_t sign = std::signbit(v) ? 0x80 : 0;
+    const float mag = std::fabs(v);
+    if (mag > mags[126]) return sign | 0x7E;
+    int hi = (int)(std::lower_bound(mags, mags + 127, mag) - mags);  // first code with magnitude >= mag
+    if (hi == 0) return sign;
+    const int lo = hi - 1;
+    const float dl = mag - mags[lo], dh = mags[hi] - mag;
+    int best = dl < dh ? lo : (dh < dl ? hi : ((lo & 1) == 0 ? lo : hi));
+    return sign | (uint8_t)best;
+}
+
+// ---------------------------------------------------------------------------
 
 static inline int8_t quant_i8(float a, float inv_s) {
     float r = std::nearbyint(a * inv_s);
@@ -634,6 +688,15 @@ static void quantize_weights(Net& net) {
             L.wscale[f] = s;
             for (size_t k = 0; k < per; ++k) L.wq[f * per + k] = quant_i8(fw[f * per + k] / s, 1.0f);
         }
+        L.w8.assign(fw.size(), 0);
+        L.w8scale.assign(L.filters, 1.0f);
+        for (int f = 0; f < L.filters; ++f) {
+            float m = 0.0f;
+            for (size_t k = 0; k < per; ++k) m = std::max(m, std::fabs(fw[f * per + k]));
+            float s8 = (m > 0.0f && std::isfinite(m)) ? m / 448.0f : 1.0f;
+            L.w8scale[f] = s8;
+            for (size_t k = 0; k < per; ++k) L.w8[f * per + k] = f32_to_e4m3_fast(fw[f * per + k] / s8);
+        }
     }
 }
 
@@ -645,7 +708,7 @@ struct UF {
 };
 
 // Scale groups: tensor index t = 0 is the network input, t = 1+i the output of layer i.
-static void calibrate(Net& net) {
+static void calibrate(Net& net, float qmax = 127.0f) {
     int T = (int)net.layers.size() + 1;
     UF uf(T);
     for (int i = 0; i < (int)net.layers.size(); ++i) {
@@ -658,7 +721,7 @@ static void calibrate(Net& net) {
     net.scale.assign(T, 1.0f);
     for (int t = 0; t < T; ++t) {
         float m = gmax[uf.find(t)];
-        net.scale[t] = (m > 0.0f && std::isfinite(m)) ? m / 127.0f : 1.0f;
+        net.scale[t] = (m > 0.0f && std::isfinite(m)) ? m / qmax : 1.0f;
     }
 }
 
@@ -782,6 +845,118 @@ static void forward_q8(Net& net, const float* input) {
             }
         }
         net.out_q8[i] = std::move(y);
+    }
+}
+
+// FP8 E4M3 forward: the int8 model with E4M3 codes (scales amax/448, lightnet-cuda-oxide/src/fp8.rs:186) and
+// floating-point accumulation.  Accumulation is done in double here; a tensor core accumulates in f32 in its own
+// order, so comparisons against this are toleranced, never bit-exact.
+static inline int8_t f8_key(uint8_t c) { return (int8_t)((c & 0x80) ? (c ^ 0x7F) : c); }  // order of the values under signed compare
+
+static void forward_f8(Net& net, const float* input) {
+    const int NL = (int)net.layers.size();
+    net.out_f8.assign(NL, std::vector<uint8_t>());
+    net.head_f8.assign(NL, Tensor());
+    Shape is; is.w = net.width; is.h = net.height; is.c = net.channels; is.b = net.batch;
+    std::vector<uint8_t> xin(is.count());
+    {
+        float inv = 1.0f / net.scale[0];
+        for (size_t i = 0; i < xin.size(); ++i) xin[i] = f32_to_e4m3_fast(input[i] * inv);
+    }
+    auto off = [](const Shape& s, int b, int c, int y, int x) { return (((size_t)b * s.c + c) * s.h + y) * s.w + x; };
+    float dec[256];
+    for (int c = 0; c < 256; ++c) dec[c] = ((c & 0x7F) == 0x7F) ? 0.0f : e4m3_to_f32((uint8_t)c);
+    for (int i = 0; i < NL; ++i) {
+        Layer& L = net.layers[i];
+        const std::vector<uint8_t>& x = i == 0 ? xin : net.out_f8[i - 1];
+        const Shape xs = L.in;
+        const float sx = net.scale[i], sy = net.scale[i + 1];
+        std::vector<uint8_t> y(L.out.count(), 0);
+        switch (L.kind) {
+            case K_CONV: {
+                if (L.groups != 1 || L.dilation != 1) throw std::runtime_error("fp8 conv supports groups=1 dilation=1");
+                const bool head = feeds_head(net, i);
+                if (head) net.head_f8[i] = Tensor(L.out);
+                const float inv = 1.0f / sy;
+                const int C = xs.c, k = L.size;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+                for (int b = 0; b < L.out.b; ++b)
+                    for (int f = 0; f < L.filters; ++f) {
+                        const float m = sx * L.w8scale[f], bias = L.fbias[f];
+                        for (int oy = 0; oy < L.out.h; ++oy)
+                            for (int ox = 0; ox < L.out.w; ++ox) {
+                                double acc = 0.0;
+                                for (int ic = 0; ic < C; ++ic)
+                                    for (int ky = 0; ky < k; ++ky) {
+                                        const int yy = oy * L.stride_y + ky - L.padding;
+                                        if (yy < 0 || yy >= xs.h) continue;
+                                        for (int kx = 0; kx < k; ++kx) {
+                                            const int xx = ox * L.stride_x + kx - L.padding;
+                                            if (xx < 0 || xx >= xs.w) continue;
+                                            acc += (double)dec[x[off(xs, b, ic, yy, xx)]] * (double)dec[L.w8[(((size_t)f * C + ic) * k + ky) * k + kx]];
+                                        }
+                                    }
+                                const float a = det_activate(L.act, std::fma((float)acc, m, bias));
+                                const size_t o = off(L.out, b, f, oy, ox);
+                                if (head) net.head_f8[i].d[o] = a;
+                                else y[o] = f32_to_e4m3_fast(a * inv);
+                            }
+                    }
+                break;
+            }
+            case K_MAXPOOL:
+                for (int b = 0; b < xs.b; ++b)
+                    for (int c = 0; c < xs.c; ++c)
+                        for (int oy = 0; oy < L.out.h; ++oy)
+                            for (int ox = 0; ox < L.out.w; ++ox) {
+                                uint8_t best = 0xFE;
+                                for (int ky = 0; ky < L.size; ++ky)
+                                    for (int kx = 0; kx < L.size; ++kx) {
+                                        const int yy = oy * L.stride_y + ky - L.padding / 2, xx = ox * L.stride_x + kx - L.padding / 2;
+                                        if (yy < 0 || yy >= xs.h || xx < 0 || xx >= xs.w) continue;
+                                        const uint8_t v = x[off(xs, b, c, yy, xx)];
+                                        if (f8_key(v) > f8_key(best)) best = v;
+                                    }
+                                y[off(L.out, b, c, oy, ox)] = best;
+                            }
+                break;
+            case K_ROUTE: {
+                int oc = 0;
+                for (int src : L.sources) {
+                    const Shape ss = net.layers[src].out;
+                    const int chunk = ss.c / std::max(L.route_groups, 1), start = chunk * L.route_group_id;
+                    for (int b = 0; b < ss.b; ++b)
+                        for (int c = 0; c < chunk; ++c)
+                            for (int yy = 0; yy < ss.h; ++yy)
+                                for (int xx = 0; xx < ss.w; ++xx) y[off(L.out, b, oc + c, yy, xx)] = net.out_f8[src][off(ss, b, start + c, yy, xx)];
+                    oc += chunk;
+                }
+                break;
+            }
+            case K_SHORTCUT: {
+                const float inv = 1.0f / sy;
+                for (int src : L.sources)
+                    if (net.layers[src].out.count() != L.out.count()) throw std::runtime_error("fp8 shortcut needs same-shape sources");
+                for (size_t p = 0; p < y.size(); ++p) {
+                    float v = dec[x[p]] * sx;
+                    for (int src : L.sources) v = std::fma(dec[net.out_f8[src][p]], net.scale[src + 1], v);
+                    y[p] = f32_to_e4m3_fast(det_activate(L.act, v) * inv);
+                }
+                break;
+            }
+            case K_UPSAMPLE:
+                if (L.up_reverse || L.up_scale != 1.0f) throw std::runtime_error("fp8 upsample supports scale=1, forward only");
+                for (int b = 0; b < L.out.b; ++b)
+                    for (int c = 0; c < L.out.c; ++c)
+                        for (int yy = 0; yy < L.out.h; ++yy)
+                            for (int xx = 0; xx < L.out.w; ++xx) y[off(L.out, b, c, yy, xx)] = x[off(xs, b, c, yy / L.up_stride, xx / L.up_stride)];
+                break;
+            case K_YOLO:
+                if (i == 0 || !feeds_head(net, i - 1)) throw std::runtime_error("fp8 [yolo] must follow a convolution");
+                net.head_f8[i] = net.head_f8[i - 1];
+                break;
+        }
+        net.out_f8[i] = std::move(y);
     }
 }
 
@@ -910,37 +1085,6 @@ static std::vector<Det> detect_image(const std::vector<const float*>& heads, con
     return d;
 }
 
-// ---------------------------------------------------------------------------
-// FP8 E4M3 codec: lightnet-cuda-oxide/src/fp8.rs:153-181 (RNE, satfinite 448,
-// NaN -> 0x7F), decode :140-150.
-// ---------------------------------------------------------------------------
-
-static float e4m3_decode_mag(uint8_t m) {
-    int e = (m >> 3) & 0xF, f = m & 7;
-    if (e == 0) return std::ldexp((float)f, -9);
-    return std::ldexp(1.0f + (float)f / 8.0f, e - 7);
-}
-static float e4m3_to_f32(uint8_t bits) {
-    uint8_t m = bits & 0x7F;
-    if (m == 0x7F) return std::numeric_limits<float>::quiet_NaN();
-    float v = e4m3_decode_mag(m);
-    return (bits & 0x80) ? -v : v;
-}
-static uint8_t f32_to_e4m3(float v) {
-    if (std::isnan(v)) return 0x7F;
-    uint8_t sign = std::signbit(v) ? 0x80 : 0;
-    float mag = std::fabs(v);
-    const uint8_t maxc = 0x7E;
-    if (mag > e4m3_decode_mag(maxc)) return sign | maxc;
-    uint8_t best = 0;
-    float bd = std::numeric_limits<float>::infinity();
-    for (int c = 0; c <= maxc; ++c) {
-        float dist = std::fabs(mag - e4m3_decode_mag((uint8_t)c));
-        if (dist < bd || (dist == bd && (c & 1) == 0)) { best = (uint8_t)c; bd = dist; }
-    }
-    return sign | best;
-}
-
 }  // namespace orc
 
 // ---------------------------------------------------------------------------
@@ -1066,6 +1210,35 @@ int orc_net_set_scales(void* h, const float* s, int count) {
     n->scale.assign(s, s + count);
     return 0;
 }
+int orc_net_calibrate_qmax(void* h, float qmax) {
+    ORC_TRY
+    Net* n = (Net*)h;
+    if (n->amax.size() != n->layers.size() + 1) throw std::runtime_error("run forward_f32 before calibrate");
+    calibrate(*n, qmax);
+    return 0;
+    ORC_CATCH(-1)
+}
+int orc_net_forward_f8(void* h, const float* input) {
+    ORC_TRY
+    Net* n = (Net*)h;
+    if (n->scale.size() != n->layers.size() + 1) throw std::runtime_error("scales are not set");
+    forward_f8(*n, input);
+    return 0;
+    ORC_CATCH(-1)
+}
+int orc_net_layer_output_f8(void* h, int i, uint8_t* out) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->out_f8.size()) return -1;
+    std::memcpy(out, n->out_f8[i].data(), n->out_f8[i].size());
+    return 0;
+}
+int orc_net_head_f8(void* h, int i, float* out) {
+    Net* n = (Net*)h;
+    if (i < 0 || i >= (int)n->head_f8.size() || n->head_f8[i].d.empty()) return -1;
+    std::memcpy(out, n->head_f8[i].d.data(), n->head_f8[i].d.size() * 4);
+    return 0;
+}
+unsigned char orc_f32_to_e4m3_fast(float v) { return f32_to_e4m3_fast(v); }
 int orc_net_forward_q8(void* h, const float* input) {
     ORC_TRY
     Net* n = (Net*)h;

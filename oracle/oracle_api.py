@@ -53,6 +53,12 @@ def lib():
         L.orc_net_get_scales.argtypes = [C.c_void_p, C.c_void_p]
         L.orc_net_set_scales.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.orc_net_forward_q8.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_net_forward_f8.argtypes = [C.c_void_p, C.c_void_p]
+        L.orc_net_calibrate_qmax.argtypes = [C.c_void_p, C.c_float]
+        L.orc_net_layer_output_f8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.orc_net_head_f8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.orc_f32_to_e4m3_fast.restype = C.c_ubyte
+        L.orc_f32_to_e4m3_fast.argtypes = [C.c_float]
         L.orc_net_layer_output_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
         L.orc_net_head_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
         L.orc_net_conv_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -173,6 +179,27 @@ class Net:
         s = np.ascontiguousarray(s, np.float32)
         if lib().orc_net_set_scales(self.h, _p(s), s.size):
             raise OracleError("scale count mismatch")
+
+    def calibrate_f8(self):
+        if lib().orc_net_calibrate_qmax(self.h, 448.0):
+            raise OracleError(_err())
+
+    def forward_f8(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        if lib().orc_net_forward_f8(self.h, _p(x)):
+            raise OracleError(_err())
+
+    def layer_output_f8(self, i):
+        out = np.zeros(self.out_shape(i), np.uint8)
+        if lib().orc_net_layer_output_f8(self.h, i, _p(out)):
+            raise OracleError("no fp8 output for layer %d" % i)
+        return out
+
+    def head_f8(self, i):
+        out = np.zeros(self.out_shape(i), np.float32)
+        if lib().orc_net_head_f8(self.h, i, _p(out)):
+            raise OracleError("layer %d is not a head of the fp8 run" % i)
+        return out
 
     def forward_q8(self, x):
         x = np.ascontiguousarray(x, np.float32)
@@ -328,6 +355,15 @@ def f32_to_e4m3(v):
 
 def e4m3_to_f32(b):
     return float(lib().orc_e4m3_to_f32(int(b)))
+
+
+def f32_to_e4m3_fast(v):
+    return int(lib().orc_f32_to_e4m3_fast(float(v)))
+
+
+def e4m3_table():
+    """Value of every E4M3 code (NaN codes as nan)."""
+    return np.array([e4m3_to_f32(c) for c in range(256)], np.float32)
 
 
 def set_threads(n):
