@@ -3,6 +3,8 @@
     python bench.py --gpus N --steps K --warmup W            (this library, one process per GPU)
     python bench.py --impl reference --gpus N --steps K --warmup W   (the CPU restatement of the reference path)
 
+(`--workload` selects one of the baseline's other GPU configurations; the default is the headline one described here.)
+
 A step is one pass over one batch of `--batch` synthetic images per GPU (uniform [0,1) f32, 608x608x3, larger than
 L2) through the network built from the generated yolov4 cfg with He-normal random weights: forward, device decode
 (threshold 0.25) and per-class NMS (IoU 0.45); the detections land in host memory.  `value` times that with the
@@ -29,6 +31,17 @@ if ROOT not in sys.path:
 
 METRIC = "images/sec YOLOv4-608 int8 (conv stack + yolo decode + NMS)"
 CONF_THR, NMS_THR, MAX_PER_IMAGE = 0.25, 0.45, 1024
+
+# The default is the headline workload.  The other two are the remaining GPU configurations of the baseline, kept here so
+# that their numbers come from the same timing code: `--workload yolov7-640-fp8` (batch 32) and `--workload nms-stress`
+# (decode + NMS alone: 256 images x 25200 candidates x 80 classes, threshold 0.001, IoU 0.65, top-k 300).
+WORKLOADS = {
+    "yolov4-608-int8": dict(model="yolov4", size=608, batch=64, precision="int8", metric=METRIC),
+    "yolov7-640-fp8": dict(model="yolov7", size=640, batch=32, precision="fp8",
+                           metric="images/sec YOLOv7-640 FP8 E4M3 (conv stack + yolo decode + NMS)"),
+    "nms-stress": dict(model=None, size=640, batch=256, precision="f32", metric="decode + NMS GB/s (25200 candidates x 80 classes per image)"),
+}
+STRESS_THR, STRESS_NMS, STRESS_TOPK = 0.001, 0.65, 300
 
 
 def conv_ops_per_image(layers):
@@ -80,7 +93,7 @@ def measured_peaks():
     return 1400.0, 6650.0, "fallback"
 
 
-def cpu_reference_sample(batch, threads):
+def cpu_reference_sample(batch, threads, model="yolov4", size=608):
     """Times the reference's CPU path (oracle restatement: f32 direct convolution with unfolded batch norm, libm
     activations, decode, the two apply_nms passes) on ONE image of the workload and returns (seconds per image, note).
 
@@ -92,10 +105,10 @@ def cpu_reference_sample(batch, threads):
     from lightnet_b200 import synth, zoo
     from oracle import oracle_api as orc
 
-    cfg = zoo.yolov4_cfg(batch=1)
+    cfg = (zoo.yolov4_cfg if model == "yolov4" else zoo.yolov7_cfg)(size, size, batch=1)
     o = orc.Net(cfg, 1)
     o.set_weights(synth.he_weights(o.layers(), 0))
-    x = synth.uniform_images(1, 3, 608, 608, 1)
+    x = synth.uniform_images(1, 3, size, size, 1)
     orc.set_threads(threads)
     t0 = time.perf_counter()
     o.forward_f32(x)
@@ -110,7 +123,7 @@ def cpu_reference_sample(batch, threads):
         sub.append(dict(gw=hs.shape[2], gh=hs.shape[1], classes=sp["classes"], anchors=sp["anchors"], scale_x_y=sp["scale_x_y"],
                         new_coords=sp["new_coords"]))
     t0 = time.perf_counter()
-    d = orc.decode_nms(heads, sub, 608, 608, 608, 608, CONF_THR, NMS_THR, letterbox=True)
+    d = orc.decode_nms(heads, sub, size, size, size, size, CONF_THR, NMS_THR, letterbox=True)
     t_nms_sample = time.perf_counter() - t0
     t_nms = t_nms_sample * 256.0
     note = ("1 image of the batch of %d: f32 conv stack in full (%.1f s on %d threads, OpenMP over (image, filter)); decode + NMS timed on "
@@ -119,84 +132,78 @@ def cpu_reference_sample(batch, threads):
     return t_conv + t_nms, note
 
 
+def cpu_stress_sample(threads):
+    """decode + NMS of the reference (oracle restatement, one thread: the reference's decode and apply_nms are serial) on
+    ONE image of the stress workload, on 1/16 of its grid cells; returns (seconds per image, note).  Time is scaled by 16^2
+    because apply_nms visits every pair of candidates."""
+    from lightnet_b200 import synth
+    from oracle import oracle_api as orc
+
+    heads = [np.ascontiguousarray(h[0][:, ::4, ::4]) for h in synth.stress_heads(1)]
+    specs = synth.stress_head_specs()
+    for sp, h in zip(specs, heads):
+        sp["gw"], sp["gh"] = h.shape[2], h.shape[1]
+    t0 = time.perf_counter()
+    d = orc.decode_nms(heads, specs, 640, 640, 640, 640, STRESS_THR, STRESS_NMS, letterbox=True, top_k=STRESS_TOPK)
+    dt = time.perf_counter() - t0
+    note = ("1 image of 256, 1/16 of the grid cells (%.2f s, %d boxes kept), scaled by 16^2 for the quadratic pair loop of apply_nms"
+            % (dt, len(d)))
+    return dt * 256.0, note
+
+
 def run_reference(args, rank):
     """`--impl reference`: the reference's own CPU implementation of the path (restated in the oracle; the Rust crate cannot
     be built in this image), all host threads, a bounded sample per step."""
     if rank != 0:
         return
     cores = os.cpu_count() or 1
+    wl = WORKLOADS[args.workload]
     steps = max(1, min(args.steps, 2))
     total, note = 0.0, ""
     for _ in range(steps):
-        dt, note = cpu_reference_sample(args.batch, cores)
+        if wl["model"] is None:
+            dt, note = cpu_stress_sample(1)
+        else:
+            dt, note = cpu_reference_sample(args.batch, cores, wl["model"], wl["size"])
         total += dt
     dt = total / steps
-    v = 1.0 / dt
-    print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": "images/s", "n_gpus": args.gpus, "steps": steps,
+    if wl["model"] is None:
+        v, unit, cores = stress_bytes(1) / dt / 1e9, "GB/s", 1
+    else:
+        v, unit = 1.0 / dt, "images/s"
+    print(json.dumps({"impl": "reference", "metric": wl["metric"], "value": v, "unit": unit, "n_gpus": args.gpus, "steps": steps,
                       "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                       "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": "yolov4-608 conv stack + decode(0.25) + NMS(0.45), He-normal random weights, uniform[0,1) images",
-                                 "batch_per_gpu": args.batch},
-                      "cpu_baseline": {"value": v, "unit": "images/s", "cores": cores, "kind": "port", "sample": note},
-                      "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+                      "config": {"workload": workload_text(args.workload), "batch_per_gpu": args.batch},
+                      "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": note},
+                      "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
-def cpu_baseline(batch):
+def workload_text(name):
+    wl = WORKLOADS[name]
+    if wl["model"] is None:
+        return ("decode + NMS stress: 25200 candidates (3 anchors x (80^2+40^2+20^2)) x 80 classes per image, logits xy N(0,1), wh N(0,0.5), "
+                "obj/class N(-4,2); threshold %.3f, NMS IoU %.2f, top-k %d" % (STRESS_THR, STRESS_NMS, STRESS_TOPK))
+    return "%s-%d %s conv stack + decode(%.2f) + NMS(%.2f), He-normal random weights, uniform[0,1) images" % (
+        wl["model"], wl["size"], wl["precision"], CONF_THR, NMS_THR)
+
+
+def stress_bytes(batch):
+    """Algorithmic bytes of decode + NMS: every raw head value is read once (f32)."""
+    return batch * 25200 * 85 * 4
+
+
+def cpu_baseline(batch, model="yolov4", size=608):
     cores = os.cpu_count() or 1
-    dt, note = cpu_reference_sample(batch, cores)
+    dt, note = cpu_reference_sample(batch, cores, model, size)
     return {"value": 1.0 / dt, "unit": "images/s", "cores": cores, "kind": "port", "sample": note}
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
-    ap.add_argument("--micro-batch", type=int, default=0, help="images per pass through the layers (activations stay in L2)")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--width", type=int, default=608)
-    ap.add_argument("--height", type=int, default=608)
-    args = ap.parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        run_reference(args, rank)
-        return
-    args.warmup = max(args.warmup, 3)
-
+def make_timer(stream, world):
+    """timed(fn, steps): milliseconds of `steps` calls, CUDA events on the launching stream, barrier + device synchronize on
+    both sides, maximum over ranks."""
     import torch
     import torch.distributed as dist
-
-    import lightnet_b200 as ln
-    from lightnet_b200 import synth, zoo
-
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    B = args.batch
-    be = ln.B200Backend(local_rank)
-    cfg = zoo.yolov4_cfg(args.width, args.height, batch=B)
-    layers = ln.GpuExecutableNetwork(be, zoo.yolov4_cfg(args.width, args.height, batch=1), 1, ln.LN_F32).layers()
-    blob = synth.he_weights(layers, 0)
-    # calibration: a small f32 batch on the device gives the per-tensor scales
-    calib = ln.GpuExecutableNetwork(be, zoo.yolov4_cfg(args.width, args.height, batch=2), 2, ln.LN_Q8)
-    calib.load_weights(blob)
-    calib.calibrate(synth.uniform_images(2, 3, args.height, args.width, 7))
-    scales = calib.scales()
-    del calib
-    net = ln.GpuExecutableNetwork(be, cfg, B, ln.LN_Q8)
-    net.load_weights(blob)
-    net.set_scales(scales)
-    net.set_micro_batch(args.micro_batch if args.micro_batch < B else 0)
-
-    x_host = torch.from_numpy(synth.uniform_images(B, 3, args.height, args.width, 100 + rank)).pin_memory()
-    x_np = x_host.numpy()
-    x_dev = be.upload_f32(x_np.shape, x_np)
-    stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", local_rank))
-    det_args = (args.width, args.height, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE)
 
     def barrier():
         if world > 1:
@@ -216,6 +223,132 @@ def main():
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
+
+    return timed
+
+
+def run_nms_stress(args, be, rank, world, local_rank):
+    """decode + NMS alone on synthetic heads (resident in HBM for `value`; uploaded from pinned host memory inside the timed
+    region for `e2e`).  The heads of 256 images are 2.19 GB, far larger than L2."""
+    import torch
+
+    from lightnet_b200 import synth
+
+    B = args.batch
+    heads_np = synth.stress_heads(B, seed=2 + rank)
+    specs = synth.stress_head_specs()
+    pinned = [torch.from_numpy(h).pin_memory() for h in heads_np]
+    heads_np = [p.numpy() for p in pinned]
+    dev = [dict(raw=be.upload_f32(h.shape, h), classes=s["classes"], anchors=s["anchors"], scale_x_y=1.0, new_coords=0)
+           for h, s in zip(heads_np, specs)]
+    stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", local_rank))
+    timed = make_timer(stream, world)
+    call = lambda hs: be.yolo_decode_nms(hs, 640, 640, 640, 640, STRESS_THR, STRESS_NMS, True, STRESS_TOPK, STRESS_TOPK)
+
+    def e2e_call():
+        hs = [dict(d, raw=be.upload_f32(h.shape, h)) for d, h in zip(dev, heads_np)]
+        return call(hs)
+
+    dets = None
+    for _ in range(args.warmup):
+        dets = call(dev)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = be.launch_count
+    ms = timed(lambda: call(dev), args.steps)
+    launches = be.launch_count - launches0
+    e2e_call()
+    ms_e2e = timed(e2e_call, args.steps)
+    clocks = sampler.summary()
+    nbytes = stress_bytes(B)
+    _, hbm_gbs, basis = measured_peaks()
+    gbs = nbytes * args.steps / (ms * 1e-3) / 1e9
+    if rank == 0:
+        line = {
+            "metric": WORKLOADS["nms-stress"]["metric"], "value": gbs * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_text("nms-stress"), "batch_per_gpu": B, "l2": "inputs larger than L2 (%.2f GB of heads)" % (nbytes / 1e9),
+                       "parallelism": "batch-sharded, no collective"},
+            "images_per_s": B * world * args.steps / (ms * 1e-3),
+            "e2e": {"value": nbytes * world * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(nbytes),
+                    "d2h_bytes_per_step": int(B * STRESS_TOPK * 28 + B * 4), "api": "ln_tensor_upload_f32 x3 + ln_yolo_decode_nms"},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "whole decode + NMS call (scan, selection, sort, suppression kernels)", "achieved": gbs,
+                         "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs, "traffic": None, "peak_basis": "%s copy bandwidth" % basis},
+            "clocks": clocks,
+            "detections_first_image": int(len(dets[0])) if dets is not None else None,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            dt, note = cpu_stress_sample(1)
+            line["cpu_baseline"] = {"value": stress_bytes(1) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port", "sample": note}
+        print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="yolov4-608-int8", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="images per GPU per step (0 = the workload's own: 64 / 32 / 256)")
+    ap.add_argument("--micro-batch", type=int, default=0, help="images per pass through the layers; 0 (default, fastest) = the whole batch")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--width", type=int, default=0)
+    ap.add_argument("--height", type=int, default=0)
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    args.batch = args.batch or wl["batch"]
+    args.width = args.width or wl["size"]
+    args.height = args.height or wl["size"]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+
+    import lightnet_b200 as ln
+    from lightnet_b200 import synth, zoo
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    B = args.batch
+    be = ln.B200Backend(local_rank)
+    if wl["model"] is None:
+        run_nms_stress(args, be, rank, world, local_rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    make_cfg = zoo.yolov4_cfg if wl["model"] == "yolov4" else zoo.yolov7_cfg
+    prec = ln.LN_Q8 if wl["precision"] == "int8" else ln.LN_F8
+    cfg = make_cfg(args.width, args.height, batch=B)
+    layers = ln.GpuExecutableNetwork(be, make_cfg(args.width, args.height, batch=1), 1, ln.LN_F32).layers()
+    blob = synth.he_weights(layers, 0)
+    # calibration: a small f32 batch on the device gives the per-tensor scales
+    calib = ln.GpuExecutableNetwork(be, make_cfg(args.width, args.height, batch=2), 2, prec)
+    calib.load_weights(blob)
+    calib.calibrate(synth.uniform_images(2, 3, args.height, args.width, 7))
+    scales = calib.scales()
+    del calib
+    net = ln.GpuExecutableNetwork(be, cfg, B, prec)
+    net.load_weights(blob)
+    net.set_scales(scales)
+    net.set_micro_batch(args.micro_batch if args.micro_batch < B else 0)
+
+    x_host = torch.from_numpy(synth.uniform_images(B, 3, args.height, args.width, 100 + rank)).pin_memory()
+    x_np = x_host.numpy()
+    x_dev = be.upload_f32(x_np.shape, x_np)
+    stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", local_rank))
+    det_args = (args.width, args.height, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE)
+
+    timed = make_timer(stream, world)
 
     dets = None
     for _ in range(args.warmup):
@@ -237,22 +370,22 @@ def main():
     umma_ms, umma_launches = per_op["conv_umma"]
     ops_img = conv_ops_per_image(layers) - 2 * layers[0]["out_w"] * layers[0]["out_h"] * layers[0]["out_c"] * layers[0]["in_c"] * layers[0]["size"] ** 2
     bf16_tf, hbm_gbs, basis = measured_peaks()
-    peak = 2.0 * bf16_tf  # dense int8 tensor throughput is twice bf16 on this part
+    peak = 2.0 * bf16_tf  # dense int8 / FP8 tensor throughput is twice bf16 on this part
     achieved = ops_img * B / (umma_ms * 1e-3) / 1e12 if umma_ms > 0 else 0.0
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": B * world * args.steps / (ms * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "metric": wl["metric"], "value": B * world * args.steps / (ms * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "yolov4-%d conv stack + decode(%.2f) + NMS(%.2f), He-normal random weights, uniform[0,1) images" % (args.width, CONF_THR, NMS_THR),
+            "dtype": wl["precision"], "data": "synthetic",
+            "config": {"workload": workload_text(args.workload),
                        "batch_per_gpu": B, "micro_batch": args.micro_batch, "max_detections_per_image": MAX_PER_IMAGE,
                        "l2": "inputs larger than L2 (%.0f MB f32 batch)" % (x_np.nbytes / 1e6), "parallelism": "batch-sharded, no collective"},
             "e2e": {"value": B * world * args.steps / (ms_e2e * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(x_np.nbytes),
                     "d2h_bytes_per_step": int(B * MAX_PER_IMAGE * 28 + B * 4), "api": "ln_net_detect (host f32 NCHW batch -> detections)"},
             "gpu_launches": int(launches),
             "phases_ms": {"layers": fwd_ms, "decode_nms": nms_ms},
-            "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel (int8 implicit GEMM, all layers but the first)", "achieved": achieved,
+            "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel (%s implicit GEMM, all layers but the first)" % wl["precision"], "achieved": achieved,
                          "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": None,
                          "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf), "launches_per_step": umma_launches,
                          "ms_per_step": umma_ms},
@@ -261,7 +394,7 @@ def main():
             "detections_first_image": int(len(dets[0])) if dets is not None else None,
         }
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(B)
+            line["cpu_baseline"] = cpu_baseline(B, wl["model"], wl["size"])
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -70,6 +70,10 @@ void* ln_ctx_stream(ln_ctx* ctx);
 /* 1 = activation epilogues use only IEEE-exact operations (bit-reproducible on a CPU), 0 = fast hardware
    approximations (default).  Affects mish / swish / logistic in reduced-precision convolutions. */
 int32_t ln_ctx_set_exact_epilogue(ln_ctx* ctx, int32_t on);
+/* Tuning knob of ln_yolo_decode_nms (no counterpart in the reference): capacity, in candidates per image, of the
+   compact pool the NMS selection works in.  0 (default) = automatic.  A small pool costs extra passes over the head
+   tensors when very many candidates tie; the records do not depend on it. */
+int32_t ln_ctx_set_nms_pool_entries(ln_ctx* ctx, int64_t entries);
 /* Number of kernels this library has launched on the ctx since creation. */
 int64_t ln_ctx_launch_count(ln_ctx* ctx);
 

@@ -55,6 +55,7 @@ SYMBOLS = {
     "ln_sync": (C.c_int32, [_VP]),
     "ln_ctx_stream": (C.c_void_p, [_VP]),
     "ln_ctx_set_exact_epilogue": (C.c_int32, [_VP, C.c_int32]),
+    "ln_ctx_set_nms_pool_entries": (C.c_int32, [_VP, C.c_int64]),
     "ln_ctx_launch_count": (C.c_int64, [_VP]),
     "ln_tensor_upload_f32": (C.c_int32, [_VP, _I64P, _VP, _PP]),
     "ln_tensor_zeros_f32": (C.c_int32, [_VP, _I64P, _PP]),
@@ -226,6 +227,19 @@ class B200Backend:
 
     def set_exact_epilogue(self, on: bool):
         self._check(self.lib.ln_ctx_set_exact_epilogue(self.ctx, int(on)))
+
+    def set_nms_pool_entries(self, entries: int):
+        """Candidates per image the NMS selection pool holds (0 = automatic); results do not depend on it."""
+        self._check(self.lib.ln_ctx_set_nms_pool_entries(self.ctx, int(entries)))
+
+    def debug_score_key_error(self, obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x):
+        """Largest distance, in confidence-key units, between the approximate and the exact candidate score over a sweep."""
+        fn = self.lib.ln_debug_score_key_error
+        fn.restype = C.c_int32
+        fn.argtypes = [_VP, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32, C.POINTER(C.c_uint32)]
+        worst = C.c_uint32()
+        self._check(fn(self.ctx, obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x, C.byref(worst)))
+        return int(worst.value)
 
     # ---- F32TensorOpsBackend ------------------------------------------------------------------
     def upload_f32(self, shape, host):

@@ -26,6 +26,7 @@ struct ln_ctx {
     cudaStream_t stream = nullptr;
     std::string err;
     bool exact_epilogue = false;
+    int nms_pool_entries = 0;  // capacity of one NMS candidate pool, 0 = automatic
     int64_t launches = 0;
     int sm_count = 0;
     std::multimap<size_t, void*> free_blocks;  // size-keyed pool; reuse is stream ordered

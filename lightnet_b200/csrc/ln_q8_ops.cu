@@ -442,6 +442,66 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
     }
 }
 
+// The same first layer in FP8 E4M3: the 27 input values are rounded to E4M3 once and kept as floats (products of two
+// E4M3 values are exact in f32), every filter costs 27 FMAs against decoded weights read (broadcast) from shared memory.
+template <int ACT, bool EXACT>
+__global__ void __launch_bounds__(256) conv_stem_k3c3_f8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
+                                                                const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
+                                                                int pad, int OH, int OW, float inv_sy, uint8_t* __restrict__ out,
+                                                                int64_t out_pixel_stride) {
+    extern __shared__ uint4 s_w4[];  // [F16*16][7] float4: 28 floats per filter, 27 used; float t of a filter = tap (t/3), channel (t%3)
+    const int F16 = (F + 15) / 16;
+    float* s_w = reinterpret_cast<float*>(s_w4);
+    float2* s_mb = reinterpret_cast<float2*>(s_w + F16 * 16 * 28);
+    for (int i = threadIdx.x; i < F16 * 16 * 28; i += blockDim.x) {
+        const int f = i / 28, t = i % 28;
+        s_w[i] = (f < F && t < 27) ? e4m3_to_float(w_oihw[((int64_t)f * 3 + (t % 3)) * 9 + (t / 3)]) : 0.0f;
+    }
+    for (int i = threadIdx.x; i < F16 * 16; i += blockDim.x) s_mb[i] = i < F ? mb[i] : make_float2(0.0f, 0.0f);
+    __syncthreads();
+    const float4* s_wv = reinterpret_cast<const float4*>(s_w);
+    const int64_t total = (int64_t)N * OH * OW;
+    for (int64_t pix = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; pix < total; pix += (int64_t)gridDim.x * blockDim.x) {
+        const int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
+        const int64_t n = pix / ((int64_t)OW * OH);
+        float patch[28];
+        patch[27] = 0.0f;
+#pragma unroll
+        for (int t = 0; t < 27; ++t) {
+            const int c = t % 3, ky = (t / 3) / 3, kx = (t / 3) % 3;
+            const int iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
+            float v = 0.0f;
+            if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = e4m3_to_float(float_to_e4m3(__fmul_rn(__ldg(x + ((n * 3 + c) * H + iy) * W + ix), inv_sx)));
+            patch[t] = v;
+        }
+        for (int fg = 0; fg < F16; ++fg) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int f = fg * 16 + q * 4 + b;
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 7; ++j) {
+                        const float4 w = s_wv[f * 7 + j];
+                        acc = __fmaf_rn(patch[4 * j], w.x, acc);
+                        acc = __fmaf_rn(patch[4 * j + 1], w.y, acc);
+                        acc = __fmaf_rn(patch[4 * j + 2], w.z, acc);
+                        acc = __fmaf_rn(patch[4 * j + 3], w.w, acc);
+                    }
+                    const float2 m = s_mb[f];
+                    const float a = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(acc, m.x, m.y));
+                    if (f < F) word |= (uint32_t)float_to_e4m3(__fmul_rn(a, inv_sy)) << (8 * b);
+                }
+                packed[q] = word;
+            }
+            *reinterpret_cast<uint4*>(out + pix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+}
+
 bool is_q(const ln_tensor* t) { return t && (t->dtype == LN_Q8 || t->dtype == LN_F8); }
 int kind_of(int dtype) { return dtype == LN_F8 ? LN_KIND_F8 : LN_KIND_I8; }
 
@@ -484,12 +544,18 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
     const int64_t total = (int64_t)N * OH * OW * F16;
     const int grid = grid_for(ctx, total);
     const bool exact = ctx->exact_epilogue;
-    if (kind == LN_KIND_I8 && k == 3 && C == 3) {
-        const size_t smem3 = (size_t)F16 * 16 * 32 + (size_t)F16 * 16 * sizeof(float2);
+    if (k == 3 && C == 3 && (kind == LN_KIND_I8 || F16 * 16 * 28 * 4 <= 40 * 1024)) {
+        const size_t smem3 = (size_t)F16 * 16 * (kind == LN_KIND_I8 ? 32 : 28 * 4) + (size_t)F16 * 16 * sizeof(float2);
         const int grid3 = grid_for(ctx, (int64_t)N * OH * OW);
 #define LN_STEM3(A, E)                                                                                                                             \
-    conv_stem_k3c3_i8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, OW, \
-                                                                           inv_sy, (uint8_t*)out, out_pixel_stride)
+    do {                                                                                                                                           \
+        if (kind == LN_KIND_I8)                                                                                                                    \
+            conv_stem_k3c3_i8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, \
+                                                                                   OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride);              \
+        else                                                                                                                                       \
+            conv_stem_k3c3_f8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, \
+                                                                                   OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride);              \
+    } while (0)
         switch (act) {
             case LN_ACT_LINEAR: if (exact) LN_STEM3(LN_ACT_LINEAR, true); else LN_STEM3(LN_ACT_LINEAR, false); break;
             case LN_ACT_LEAKY: if (exact) LN_STEM3(LN_ACT_LEAKY, true); else LN_STEM3(LN_ACT_LEAKY, false); break;

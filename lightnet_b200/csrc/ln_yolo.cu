@@ -7,21 +7,37 @@
 //
 // Device formulation.  Every candidate gets the 64-bit key (order-preserving confidence bits << 32) |
 // ~emission_index; descending key order is exactly the reference's sorted order, ties included.  Greedy NMS
-// only ever needs candidates in that order, and only until top_k survivors exist, so the candidates are
-// consumed in bands from the top: a radix selection over the key (12-bit digits, histogram in shared memory,
-// descending only into a digit that holds too many candidates) finds a cut such that the band above it fits
-// in shared memory; the band is collected, sorted (bitonic) and resolved by one CTA per image: each 512-
-// candidate chunk is tested against the survivors so far, a 512 x 512 same-class IoU bitmask is built, and
-// one warp resolves it with ballot/shuffle.  Images stop as soon as they have top_k survivors or run out of
-// candidates.  The head tensors are the only large input; they are re-read once per selection / collection
-// pass and nothing of candidate size is ever written to HBM.
+// only ever needs candidates in that order, and only until top_k survivors exist, so they are consumed from
+// the top in two stages:
 //
-// All arithmetic that decides an ordering or a threshold (sigmoid, box decode, IoU) uses single IEEE-754
+//   pool  - two passes over the head tensors.  The first histograms the top 12 key bits of every candidate;
+//           a walk down the histogram fixes a key `pool_lo` such that the candidates at or above it are a few
+//           times what the survivors still wanted can need; the second pass writes exactly those keys to a
+//           compact per-image pool (or, when they fit, straight into the band).  Should one histogram bin hold
+//           more than a pool can (massive ties), the selection descends a digit with another pass.
+//   band  - inside the pool a radix selection over the compact keys (cheap: the pool sits in L2) cuts bands
+//           that fit in shared memory; each band is sorted (bitonic) and resolved by one CTA per image: every
+//           512-candidate chunk is tested against the survivors so far, a 512 x 512 same-class IoU bitmask is
+//           built, and one warp resolves it with shuffles.
+//
+// An image stops as soon as it has top_k survivors or runs out of candidates; a pool that is used up before
+// that is followed by the next one further down.  The head tensors are the only large input: they are read
+// twice per pool, and nothing of their size is written.
+//
+// Most of the candidates only need their histogram bin, not their exact bits.  The passes over the heads
+// therefore evaluate the class sigmoid with the hardware ex2 / rcp approximations first and fall back to the
+// exact evaluation only when the approximate key is within kKeySlack units of a boundary that matters (a bin
+// edge, the threshold, the ends of the range being collected).  Everything that is written anywhere -- pool
+// and band keys, records -- comes from the exact evaluation: sigmoid, box decode and IoU use single IEEE-754
 // operations in the reference's evaluation order, so a CPU evaluating the same expressions gets the same bits.
+#include <cooperative_groups.h>
+
 #include <cstdlib>
 #include <ctime>
 
 #include "ln_conv_plan.h"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -30,10 +46,15 @@ constexpr int kBandMaxLarge = 16384;  // candidates of one band (sorted in share
 constexpr int kBandMaxSmall = 8192;   // ... when more are wanted (their boxes need the room)
 constexpr int kChunk = 512;      // candidates resolved per bitmask step
 constexpr int kBins = 4096;      // 12-bit radix digits
-constexpr unsigned kFlatChunk = 32768;  // cached score keys one block of the flat passes walks
+constexpr unsigned kPoolChunk = 8192;  // pool keys one block of the pool passes walks
 constexpr int kLevels = 6;       // 5 x 12 bits + 4 bits = 64
+// Largest distance, in units of the 32-bit confidence key, assumed between the key of the approximate score and
+// the key of the exact one.  The approximations are good to a few units (measured by ln_debug_score_key_error).
+constexpr unsigned kKeySlack = 256;
+constexpr long long kPoolBytesTarget = 1ll << 30;  // pools of one call together, unless every candidate fits in less
 
-enum { PHASE_SELECT = 0, PHASE_BAND = 1, PHASE_DONE = 2 };
+enum { PHASE_POOL = 0, PHASE_FILL = 1, PHASE_SELECT = 2, PHASE_BAND = 3, PHASE_DONE = 4 };
+enum { FLAG_SELECT_PENDING = 0, FLAG_ACTIVE = 1, FLAG_POOL_PENDING = 2, FLAG_NEED_POOL = 3 };
 
 struct HeadDev {
     const float* raw;  // [batch][n_anchor*(5+classes)][gh*gw]
@@ -51,14 +72,18 @@ struct YoloParams {
     int k_eff;          // survivors wanted per image
     int max_per_image;  // record capacity
     int band_max;       // capacity of one band
-    unsigned cache_stride;  // cached score keys per image (total_ca * classes rounded up to 4)
+    int pool_max;       // capacity of one pool
 };
 
 struct ImgState {
-    unsigned long long hi;      // keys >= hi have been consumed
-    unsigned long long lo;      // current band is [lo, hi)
-    unsigned long long prefix;  // digits fixed so far by the radix selection
-    int level, phase, cap, above, band_count, kept, exhausted, img_w, img_h, last_gain;  // last_gain: survivors the previous band added
+    unsigned long long hi;       // keys >= hi have been consumed
+    unsigned long long lo;       // current band is [lo, hi)
+    unsigned long long prefix;   // digits fixed so far by the radix selection in progress (pool or band)
+    unsigned long long pool_lo;  // the pool holds every candidate in [pool_lo, hi at the time it was filled)
+    int level, phase, cap, above, band_count, kept, exhausted, img_w, img_h;
+    int last_gain;   // survivors the previous band added
+    int direct;      // the pool being filled is small enough to be the band itself
+    int pool_count;  // keys in the pool
 };
 
 __device__ __forceinline__ int level_shift(int l) { return l < 5 ? 52 - 12 * l : 0; }
@@ -133,150 +158,226 @@ __device__ __forceinline__ int find_head(const YoloParams& p, int ca) {
     return h;
 }
 
-// One pass over the candidates.  MODE 0: histogram of the current radix digit of the still unconsumed candidates.
-// MODE 1: collect the keys of the band [lo, hi).  One thread per (anchor, cell); blockIdx.y = image.
-// FIRST: read the head tensors, evaluate the scores and leave their 32-bit order-preserving keys (0 = not a
-// candidate) in `cache`, laid out [image][class][anchor-cell]; later passes read the cache instead and do
-// integer work only.
-template <int MODE, bool FIRST>
-__global__ void __launch_bounds__(256) yolo_scan_kernel(const __grid_constant__ YoloParams p, ImgState* __restrict__ states,
-                                                        unsigned* __restrict__ hist, unsigned long long* __restrict__ band,
-                                                        int* __restrict__ band_fill, unsigned* __restrict__ cache) {
+// Band size wanted next: four candidates per survivor still wanted, or more when the previous band showed heavier suppression.
+__device__ __forceinline__ int band_cap(const YoloParams& p, const ImgState& st) {
+    long long want = 4ll * (p.k_eff - st.kept);
+    if (st.last_gain >= 0) {
+        const long long per = ((long long)st.band_count * 3 / 2) / (st.last_gain > 0 ? st.last_gain : 1) + 1;
+        if (per > 4) want = per * (p.k_eff - st.kept);
+    }
+    return want < 1024 ? 1024 : (want > p.band_max ? p.band_max : (int)want);
+}
+
+// Confidence key of objectness * sigmoid(x) as an interval [klo, khi] that contains the exact key (valid for thresholds
+// >= 1e-30, see approx_ok below).  Branch-free on the common path:
+//   x >= 17   the exact sigmoid is 1, the score is the objectness itself: klo == khi
+//   x <= -80  ex2 overflows, the approximate score is 0; the exact one is below 2e-35: both far under the threshold
+//   NaN       not handled here: callers send NaN logits to the exact path
+__device__ __forceinline__ void approx_score_key(float obj, float x, unsigned& klo, unsigned& khi) {
+    const bool sat = x >= 17.0f;
+    const float s = sat ? obj : obj * ln_rcp_ftz(1.0f + ln_ex2_ftz(x * -1.44269504f));
+    const unsigned k = __float_as_uint(s) | 0x80000000u;  // s >= +0 (or NaN)
+    const unsigned d = sat ? 0u : kKeySlack;
+    klo = k - d;
+    khi = k + d;
+}
+
+constexpr int kWarpBuf = 512;  // keys one warp of the fill pass buffers in shared memory before it reserves space in the pool
+
+// Range of keys one pass over the heads is interested in, [rlo, rhi] inclusive, from the state of the image.
+struct ScanRange {
+    unsigned long long rlo, rhi;
+    unsigned rlo_ck, rhi_ck;
+};
+template <int MODE>
+__device__ __forceinline__ ScanRange scan_range(const ImgState& st) {
+    ScanRange r;
+    const int shift = level_shift(st.level), bits = level_bits(st.level);
+    r.rhi = st.hi - 1ull;  // hi >= 1 whenever an image is still active
+    if (MODE == 1) r.rlo = st.pool_lo;
+    else if (st.level == 0) r.rlo = 0ull;
+    else {
+        r.rlo = st.prefix << (shift + bits);
+        const unsigned long long pend = r.rlo | ((1ull << (shift + bits)) - 1ull);
+        if (pend < r.rhi) r.rhi = pend;
+    }
+    r.rlo_ck = (unsigned)(r.rlo >> 32);
+    r.rhi_ck = (unsigned)(r.rhi >> 32);
+    return r;
+}
+
+// Exact key of one candidate, or 0 when it is not a candidate inside [rlo, rhi].
+__device__ __forceinline__ unsigned long long exact_key_in_range(const YoloParams& p, const ScanRange& r, float obj, float x, int new_coords,
+                                                                 unsigned ca, unsigned c) {
+    const float conf = __fmul_rn(obj, head_act(x, new_coords));
+    if (!(conf > p.thr)) return 0ull;
+    const unsigned eidx = ca * (unsigned)p.classes + c;
+    const unsigned long long key = ((unsigned long long)conf_key(conf) << 32) | (unsigned long long)(0xFFFFFFFFu - eidx);
+    return (key < r.rlo || key > r.rhi) ? 0ull : key;  // a real key is never 0: its confidence bits are at least 0x80000000
+}
+
+// First pass over the head tensors for the images that need a pool: histogram of digit `level` (under `prefix`) of the
+// unconsumed candidates (keys < hi).  One thread per (anchor, cell), all classes; blockIdx.y = image.  The common path of
+// the class loop is branch-free: the flags of a score are computed unconditionally and only the rare score that needs the
+// exact evaluation leaves it.
+__global__ void __launch_bounds__(256) yolo_head_hist_kernel(const __grid_constant__ YoloParams p, const ImgState* __restrict__ states,
+                                                             unsigned* __restrict__ hist) {
     const int img = blockIdx.y;
     const ImgState st = states[img];
-    if (!FIRST && (MODE == 0 ? st.phase != PHASE_SELECT : st.phase != PHASE_BAND)) return;
-    __shared__ unsigned s_hist[MODE == 0 ? kBins : 1];
-    if (MODE == 0) {
-        for (int i = threadIdx.x; i < kBins; i += blockDim.x) s_hist[i] = 0;
-        __syncthreads();
-    }
+    if (st.phase != PHASE_POOL) return;
+    __shared__ unsigned s_hist[kBins + 1];  // slot kBins swallows the first, empty run of every thread
+    for (int i = threadIdx.x; i <= kBins; i += blockDim.x) s_hist[i] = 0;
+    __syncthreads();
     const int shift = level_shift(st.level), bits = level_bits(st.level);
+    const ScanRange r = scan_range<0>(st);
+    const unsigned kthr = conf_key(p.thr);
+    const bool approx_ok = p.thr >= 1e-30f;  // below that the exact exponential's clamp decides candidates
+    const bool level0 = st.level == 0;
     const int ca = blockIdx.x * blockDim.x + threadIdx.x;
     if (ca < p.total_ca) {
-        unsigned* img_cache = cache + (size_t)img * p.cache_stride;
-        const float* img_raw = nullptr;
-        int stride = 0, a = 0, idx = 0, epa = 0, new_coords = 0;
-        float obj = 0.0f;
-        if (FIRST) {
-            const HeadDev& h = p.heads[find_head(p, ca)];
-            stride = h.gw * h.gh; epa = h.classes + 5; new_coords = h.new_coords;
-            const int local = ca - h.ca_base;
-            a = local / stride; idx = local - a * stride;
-            img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
-            obj = head_act(img_raw[(size_t)(a * epa + 4) * stride + idx], new_coords);
-        }
-        // consecutive classes often fall into the same bin (always, when scores saturate): count runs in registers
-        unsigned run_bin = 0xFFFFFFFFu, run_len = 0;
-        for (int c = 0; c < p.classes; ++c) {
-            unsigned ck;
-            if (FIRST) {
-                ck = 0;
-                if (obj > p.thr) {
-                    const float conf = __fmul_rn(obj, head_act(img_raw[(size_t)(a * epa + 5 + c) * stride + idx], new_coords));
-                    if (conf > p.thr) ck = conf_key(conf);
+        const HeadDev& h = p.heads[find_head(p, ca)];
+        const int stride = h.gw * h.gh, new_coords = h.new_coords;
+        const int epa = h.classes + 5, local = ca - h.ca_base;
+        const int a = local / stride, idx = local - a * stride;
+        const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
+        const float obj = head_act(__ldg(img_raw + (size_t)(a * epa + 4) * stride + idx), new_coords);
+        const float* __restrict__ cls_raw = img_raw + (size_t)(a * epa + 5) * stride + idx;
+        const bool fast = approx_ok && !new_coords;
+        if (obj > p.thr) {
+            // consecutive classes often fall into the same bin (always, when scores saturate): runs are counted in registers
+            unsigned run_bin = kBins, run_len = 0;
+            // eight class logits are loaded before any of them is used: eight independent loads in flight per thread
+            for (int c0 = 0; c0 < p.classes; c0 += 8) {
+                float xs[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) xs[j] = c0 + j < p.classes ? __ldg(cls_raw + (size_t)j * stride) : 0.0f;
+                cls_raw += (size_t)8 * stride;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float x = xs[j];
+                    unsigned klo, khi;
+                    approx_score_key(obj, x, klo, khi);
+                    const bool usable = fast && x == x;  // a NaN logit goes to the exact evaluation, whose clamps decide what it means
+                    const bool out = khi <= kthr || klo > r.rhi_ck || khi < r.rlo_ck;  // certainly not a candidate of interest
+                    unsigned bin = klo >> 20;
+                    const bool certain = level0 && klo > kthr && khi < r.rhi_ck && bin == (khi >> 20);  // the bin is all this pass needs
+                    bool count = usable && !out && certain;
+                    if (c0 + j < p.classes && !(usable && (out || certain))) {  // rare
+                        const unsigned long long key = exact_key_in_range(p, r, obj, x, new_coords, (unsigned)ca, (unsigned)(c0 + j));
+                        count = key != 0ull;
+                        bin = (unsigned)(key >> shift) & ((1u << bits) - 1u);
+                    }
+                    count = count && c0 + j < p.classes;
+                    const bool same = bin == run_bin;
+                    if (count && !same) {
+                        atomicAdd(&s_hist[run_bin], run_len);
+                        run_bin = bin;
+                        run_len = 0;
+                    }
+                    run_len += count ? 1u : 0u;
                 }
-                img_cache[(size_t)c * p.total_ca + ca] = ck;
-            } else {
-                ck = img_cache[(size_t)c * p.total_ca + ca];
             }
-            if (ck == 0u) continue;
-            const unsigned eidx = (unsigned)ca * (unsigned)p.classes + (unsigned)c;
-            const unsigned long long key = ((unsigned long long)ck << 32) | (unsigned long long)(0xFFFFFFFFu - eidx);
-            if (key >= st.hi) continue;
-            if (MODE == 0) {
-                if (st.level > 0 && (key >> (shift + bits)) != st.prefix) continue;
-                const unsigned bin = (unsigned)(key >> shift) & ((1u << bits) - 1u);
-                if (bin == run_bin) ++run_len;
-                else {
-                    if (run_len) atomicAdd(&s_hist[run_bin], run_len);
-                    run_bin = bin;
-                    run_len = 1;
-                }
-            } else {
-                if (key < st.lo) continue;
-                const int slot = atomicAdd(&band_fill[img], 1);
-                if (slot < p.band_max) band[(size_t)img * p.band_max + slot] = key;
-            }
+            atomicAdd(&s_hist[run_bin], run_len);
         }
-        if (MODE == 0 && run_len) atomicAdd(&s_hist[run_bin], run_len);
     }
-    if (MODE == 0) {
-        __syncthreads();
-        for (int i = threadIdx.x; i < kBins; i += blockDim.x)
-            if (s_hist[i]) atomicAdd(&hist[(size_t)img * kBins + i], s_hist[i]);
-    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins; i += blockDim.x)
+        if (s_hist[i]) atomicAdd(&hist[(size_t)img * kBins + i], s_hist[i]);
 }
 
-// Later passes: one thread per cached score key (flat over [class][anchor-cell]); integer work only.  Lanes of a warp
-// that fall into the same histogram bin (all of them, when scores saturate) are merged into one shared-memory add.
-template <int MODE>
-__global__ void __launch_bounds__(256) yolo_scan_cached_kernel(const __grid_constant__ YoloParams p, const ImgState* __restrict__ states,
-                                                               unsigned* __restrict__ hist, unsigned long long* __restrict__ band,
-                                                               int* __restrict__ band_fill, const unsigned* __restrict__ cache) {
+// Second pass over the heads: write the exact keys of the candidates in [pool_lo, hi) to the pool, or to the band when
+// `direct`.  A block first lists the (anchor, cell) slots of its 256 whose objectness reaches the range at all (a class
+// probability never exceeds 1 where a sigmoid makes it), then walks (class, listed slot) pairs with all its threads, so
+// that a few qualifying cells do not leave most lanes idle.  Keys are buffered per warp in shared memory and written
+// out with one reservation per few hundred keys.
+__global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_constant__ YoloParams p, const ImgState* __restrict__ states,
+                                                             unsigned long long* __restrict__ band, int* __restrict__ band_fill,
+                                                             unsigned long long* __restrict__ pool, int* __restrict__ pool_fill) {
     const int img = blockIdx.y;
     const ImgState st = states[img];
-    if (MODE == 0 ? st.phase != PHASE_SELECT : st.phase != PHASE_BAND) return;
-    __shared__ unsigned s_hist[MODE == 0 ? kBins : 1];
-    if (MODE == 0) {
-        for (int i = threadIdx.x; i < kBins; i += blockDim.x) s_hist[i] = 0;
-        __syncthreads();
-    }
-    const int shift = level_shift(st.level), bits = level_bits(st.level);
-    const unsigned per_image = (unsigned)p.total_ca * (unsigned)p.classes;
-    const unsigned chunk_begin = blockIdx.x * kFlatChunk;
-    const unsigned* img_cache = cache + (size_t)img * p.cache_stride;
-    // four keys per thread per step (one 16-byte load); the trip count is uniform over the block
-    for (unsigned base = chunk_begin; base < chunk_begin + kFlatChunk && base < per_image; base += 4u * blockDim.x) {
-        const unsigned i0 = base + 4u * threadIdx.x;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (i0 < per_image) v = *reinterpret_cast<const uint4*>(img_cache + i0);  // the padding of the last vector is zero
-        const unsigned cks[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const unsigned i = i0 + e, ck = cks[e];
-            bool valid = false;
-            unsigned bin = 0xFFFFFFFFu;
-            unsigned long long key = 0;
-            if (ck != 0u) {
-                const unsigned c = i / (unsigned)p.total_ca, ca = i - c * (unsigned)p.total_ca;
-                const unsigned eidx = ca * (unsigned)p.classes + c;
-                key = ((unsigned long long)ck << 32) | (unsigned long long)(0xFFFFFFFFu - eidx);
-                valid = key < st.hi;
-                if (MODE == 0) valid = valid && (st.level == 0 || (key >> (shift + bits)) == st.prefix);
-                else valid = valid && key >= st.lo;
-            }
-            if (MODE == 0) {
-                if (valid) bin = (unsigned)(key >> shift) & ((1u << bits) - 1u);
-                const unsigned same = __match_any_sync(0xffffffffu, bin);
-                if (valid && (threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&s_hist[bin], (unsigned)__popc(same));
-            } else if (valid) {
-                const int slot = atomicAdd(&band_fill[img], 1);
-                if (slot < p.band_max) band[(size_t)img * p.band_max + slot] = key;
-            }
+    if (st.phase != PHASE_FILL) return;
+    __shared__ unsigned long long s_buf[8 * kWarpBuf];
+    __shared__ int s_cnt[8];
+    __shared__ const float* s_ptr[256];
+    __shared__ float s_obj[256];
+    __shared__ int s_stride[256];
+    __shared__ int s_ca[256];   // slot index, with the head's new_coords flag in bit 31
+    __shared__ int s_n;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) s_cnt[warp] = 0;
+    if (threadIdx.x == 0) s_n = 0;
+    __syncthreads();
+    const ScanRange r = scan_range<1>(st);
+    const unsigned kthr = conf_key(p.thr);
+    const bool approx_ok = p.thr >= 1e-30f;
+    unsigned long long* dst = st.direct ? band + (size_t)img * p.band_max : pool + (size_t)img * p.pool_max;
+    int* fill = st.direct ? band_fill + img : pool_fill + img;
+    const int dst_cap = st.direct ? p.band_max : p.pool_max;
+    const int ca = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ca < p.total_ca) {
+        const HeadDev& h = p.heads[find_head(p, ca)];
+        const int stride = h.gw * h.gh, new_coords = h.new_coords;
+        const int epa = h.classes + 5, local = ca - h.ca_base;
+        const int a = local / stride, idx = local - a * stride;
+        const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
+        const float obj = head_act(__ldg(img_raw + (size_t)(a * epa + 4) * stride + idx), new_coords);
+        if (obj > p.thr && (new_coords || conf_key(obj) >= r.rlo_ck)) {
+            const int slot = atomicAdd(&s_n, 1);
+            s_ptr[slot] = img_raw + (size_t)(a * epa + 5) * stride + idx;
+            s_obj[slot] = obj;
+            s_stride[slot] = stride;
+            s_ca[slot] = ca | (new_coords ? (int)0x80000000 : 0);
         }
     }
-    if (MODE == 0) {
-        __syncthreads();
-        for (int b = threadIdx.x; b < kBins; b += blockDim.x)
-            if (s_hist[b]) atomicAdd(&hist[(size_t)img * kBins + b], s_hist[b]);
+    __syncthreads();
+    const int n_listed = s_n;
+    if (n_listed == 0) return;
+    const int items = n_listed * p.classes;
+    for (int base = 0; base < items; base += 256) {  // uniform trip count
+        const int i = base + (int)threadIdx.x;
+        if (i < items) {
+            const int c = i / n_listed, j = i - c * n_listed;
+            const float obj = s_obj[j];
+            const int new_coords = s_ca[j] < 0 ? 1 : 0;
+            const unsigned cell = (unsigned)s_ca[j] & 0x7FFFFFFFu;
+            const float x = __ldg(s_ptr[j] + (size_t)c * s_stride[j]);
+            bool maybe = true;
+            if (approx_ok && !new_coords && x == x) {
+                unsigned klo, khi;
+                approx_score_key(obj, x, klo, khi);
+                maybe = !(khi <= kthr || khi < r.rlo_ck || klo > r.rhi_ck);
+            }
+            if (maybe) {
+                const unsigned long long key = exact_key_in_range(p, r, obj, x, new_coords, cell, (unsigned)c);
+                if (key != 0ull) {
+                    const int slot = atomicAdd(&s_cnt[warp], 1);  // < kWarpBuf: at most 32 new keys per step on top of at most kWarpBuf - 32 kept
+                    s_buf[warp * kWarpBuf + slot] = key;
+                }
+            }
+        }
+        // the warp writes its buffered keys out when the next step could overflow the buffer, and at the end
+        __syncwarp();
+        const int n = s_cnt[warp];
+        if (n > kWarpBuf - 32 || (n > 0 && base + 256 >= items)) {
+            int at = 0;
+            if (lane == 0) at = atomicAdd(fill, n);
+            at = __shfl_sync(0xffffffffu, at, 0);
+            for (int k = lane; k < n; k += 32)
+                if (at + k < dst_cap) dst[at + k] = s_buf[warp * kWarpBuf + k];
+            __syncwarp();
+            if (lane == 0) s_cnt[warp] = 0;
+        }
+        __syncwarp();
     }
 }
 
-// One block per image: walk the digit histogram from the top, either fix the band's lower bound or descend
-// into the digit that holds too many candidates.  Leaves the histogram zeroed.
-__global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant__ YoloParams p, ImgState* __restrict__ states,
-                                                          unsigned* __restrict__ hist, int* __restrict__ pending) {
-    const int img = blockIdx.x;
-    ImgState st = states[img];
-    if (st.phase != PHASE_SELECT) return;
-    __shared__ unsigned s_part[256];
-    __shared__ unsigned s_h[kBins];
-    unsigned* h = hist + (size_t)img * kBins;
-    const int nb = 1 << level_bits(st.level);
-    const int per = kBins / 256;  // 16 bins per thread; thread t owns, from the top, bins nb-1-16t .. nb-1-16t-15
+// Loads the histogram of one image top bin first into shared memory (and zeroes it in global memory);
+// s_part[t] = sum of the 16 slots thread t loaded.  Slot 0 is the top bin.
+__device__ __forceinline__ void load_hist_desc(unsigned* h, int nb, unsigned* s_h, unsigned* s_part) {
+    const int per = kBins / 256;
     unsigned sum = 0;
     for (int j = 0; j < per; ++j) {
-        const int slot = threadIdx.x * per + j;  // slot 0 = top bin
+        const int slot = threadIdx.x * per + j;
         const int bin = nb - 1 - slot;
         const unsigned v = bin >= 0 ? h[bin] : 0u;
         s_h[slot] = v;
@@ -285,30 +386,180 @@ __global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant_
     }
     s_part[threadIdx.x] = sum;
     __syncthreads();
+}
+
+// One block per image that needs a pool: walk the digit histogram from the top until the candidates counted reach the
+// band size wanted; everything from that bin up is the pool.  A bin too large for a pool is descended into.
+__global__ void __launch_bounds__(256) yolo_pool_select_kernel(const __grid_constant__ YoloParams p, ImgState* __restrict__ states,
+                                                               unsigned* __restrict__ hist, int* __restrict__ flags) {
+    const int img = blockIdx.x;
+    ImgState st = states[img];
+    if (st.phase != PHASE_POOL) return;
+    __shared__ unsigned s_part[256];
+    __shared__ unsigned s_h[kBins];
+    const int nb = 1 << level_bits(st.level);
+    load_hist_desc(hist + (size_t)img * kBins, nb, s_h, s_part);
     if (threadIdx.x != 0) return;
+    if (st.level == 0) {
+        st.cap = band_cap(p, st);
+        st.above = 0;
+        st.prefix = 0;
+    }
+    const int shift = level_shift(st.level), bits = level_bits(st.level);
+    const long long want = (long long)st.cap - st.above;  // > 0
+    long long cum = 0;
+    int b = -1;
+    for (int t = 0; t < 256 && b < 0; ++t) {
+        if (cum + s_part[t] < want) { cum += s_part[t]; continue; }
+        for (int j = 0; j < kBins / 256; ++j) {
+            const int slot = t * (kBins / 256) + j;
+            if (cum + s_h[slot] >= want) { b = nb - 1 - slot; break; }
+            cum += s_h[slot];
+        }
+    }
+    const unsigned long long base = st.level == 0 ? 0ull : (st.prefix << (shift + bits));
+    long long count;
+    if (b < 0) {
+        // everything that is left (under this prefix) is fewer than wanted: take all of it
+        st.pool_lo = base;
+        count = st.above + cum;
+    } else {
+        const long long incl = st.above + cum + s_h[nb - 1 - b];
+        if (incl <= p.pool_max || st.level == kLevels - 1) {
+            st.pool_lo = base + ((unsigned long long)b << shift);
+            count = incl;
+        } else {
+            st.above += (int)cum;
+            st.prefix = (st.level == 0 ? 0ull : (st.prefix << bits)) | (unsigned long long)b;
+            st.level += 1;
+            atomicAdd(&flags[FLAG_POOL_PENDING], 1);
+            states[img] = st;
+            return;
+        }
+    }
+    st.phase = PHASE_FILL;
+    st.direct = count <= p.band_max ? 1 : 0;
+    if (st.direct) {
+        st.lo = st.pool_lo;
+        st.band_count = (int)count;
+        st.exhausted = 1;
+    }
+    st.pool_count = 0;
+    states[img] = st;
+}
+
+// After the fill pass: a filled pool goes to band selection, a directly filled band to NMS.
+__global__ void yolo_after_fill_kernel(ImgState* __restrict__ states, const int* __restrict__ pool_fill, int batch, int pool_max) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= batch || states[i].phase != PHASE_FILL) return;
+    if (states[i].direct) states[i].phase = PHASE_BAND;
+    else {
+        const int n = pool_fill[i];
+        states[i].pool_count = n < pool_max ? n : pool_max;
+        states[i].phase = PHASE_SELECT;
+        states[i].level = 0;
+    }
+}
+
+// Passes over the pool: one thread per two keys; integer work only.
+// MODE 0: histogram of digit `level` under `prefix` of the unconsumed keys, plus the AND and OR of those keys (they tell
+// the selection which further digits all of them share).  Lanes of a warp that fall into the same bin are merged into one
+// shared-memory add.  MODE 1: collect the keys of the band [lo, hi).
+template <int MODE>
+__global__ void __launch_bounds__(256) yolo_pool_scan_kernel(const __grid_constant__ YoloParams p, const ImgState* __restrict__ states,
+                                                             unsigned* __restrict__ hist, unsigned long long* __restrict__ key_and_or,
+                                                             unsigned long long* __restrict__ band, int* __restrict__ band_fill,
+                                                             const unsigned long long* __restrict__ pool) {
+    const int img = blockIdx.y;
+    const ImgState st = states[img];
+    if (st.phase != (MODE == 0 ? PHASE_SELECT : PHASE_BAND) || (MODE == 1 && st.direct)) return;
+    const unsigned n = (unsigned)st.pool_count;
+    const unsigned chunk_begin = blockIdx.x * kPoolChunk;
+    if (chunk_begin >= n) return;
+    __shared__ unsigned s_hist[MODE == 0 ? kBins : 1];
+    __shared__ unsigned long long s_and, s_or;
+    if (MODE == 0) {
+        for (int i = threadIdx.x; i < kBins; i += blockDim.x) s_hist[i] = 0;
+        if (threadIdx.x == 0) { s_and = ~0ull; s_or = 0ull; }
+        __syncthreads();
+    }
+    const int shift = level_shift(st.level), bits = level_bits(st.level);
+    const unsigned long long* img_pool = pool + (size_t)img * p.pool_max;
+    unsigned long long t_and = ~0ull, t_or = 0ull;
+    for (unsigned base = chunk_begin; base < chunk_begin + kPoolChunk && base < n; base += 2u * blockDim.x) {  // uniform trip count
+        const unsigned i0 = base + 2u * threadIdx.x;
+        ulonglong2 v = make_ulonglong2(0ull, 0ull);
+        if (i0 + 1 < n) v = *reinterpret_cast<const ulonglong2*>(img_pool + i0);
+        else if (i0 < n) v.x = img_pool[i0];
+        const unsigned long long ks[2] = {v.x, v.y};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const unsigned long long key = ks[e];
+            bool valid = i0 + e < n && key < st.hi;
+            if (MODE == 0) {
+                valid = valid && (st.level == 0 || (key >> (shift + bits)) == st.prefix);
+                unsigned bin = 0xFFFFFFFFu;
+                if (valid) {
+                    bin = (unsigned)(key >> shift) & ((1u << bits) - 1u);
+                    t_and &= key;
+                    t_or |= key;
+                }
+                const unsigned same = __match_any_sync(0xffffffffu, bin);
+                if (valid && (threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&s_hist[bin], (unsigned)__popc(same));
+            } else if (valid && key >= st.lo) {
+                const int slot = atomicAdd(&band_fill[img], 1);
+                if (slot < p.band_max) band[(size_t)img * p.band_max + slot] = key;
+            }
+        }
+    }
+    if (MODE == 0) {
+        for (int o = 16; o > 0; o >>= 1) {
+            t_and &= __shfl_xor_sync(0xffffffffu, t_and, o);
+            t_or |= __shfl_xor_sync(0xffffffffu, t_or, o);
+        }
+        if ((threadIdx.x & 31) == 0) { atomicAnd(&s_and, t_and); atomicOr(&s_or, t_or); }
+        __syncthreads();
+        for (int b = threadIdx.x; b < kBins; b += blockDim.x)
+            if (s_hist[b]) atomicAdd(&hist[(size_t)img * kBins + b], s_hist[b]);
+        if (threadIdx.x == 0) { atomicAnd(&key_and_or[2 * img], s_and); atomicOr(&key_and_or[2 * img + 1], s_or); }
+    }
+}
+
+// One block per image: walk the digit histogram of the pool from the top, either fix the band's lower bound or descend
+// into the digit that holds too many candidates (skipping the digits all keys under it share).  Leaves the histogram zeroed.
+__global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant__ YoloParams p, ImgState* __restrict__ states,
+                                                          unsigned* __restrict__ hist, unsigned long long* __restrict__ key_and_or,
+                                                          int* __restrict__ flags) {
+    const int img = blockIdx.x;
+    ImgState st = states[img];
+    if (st.phase != PHASE_SELECT) return;
+    __shared__ unsigned s_part[256];
+    __shared__ unsigned s_h[kBins];
+    const int nb = 1 << level_bits(st.level);
+    const int per = kBins / 256;
+    load_hist_desc(hist + (size_t)img * kBins, nb, s_h, s_part);
+    if (threadIdx.x != 0) return;
+    const unsigned long long k_and = key_and_or[2 * img], k_or = key_and_or[2 * img + 1];
+    key_and_or[2 * img] = ~0ull;
+    key_and_or[2 * img + 1] = 0ull;
     // ---- one thread decides (a few hundred steps at most)
     if (st.level == 0) {
-        // band size: four candidates per survivor still wanted, or more when the previous band showed heavier suppression
-        long long want = 4ll * (p.k_eff - st.kept);
-        if (st.last_gain >= 0) {
-            const long long per = ((long long)st.band_count * 3 / 2) / (st.last_gain > 0 ? st.last_gain : 1) + 1;
-            if (per > 4) want = per * (p.k_eff - st.kept);
-        }
-        st.cap = want < 1024 ? 1024 : (want > p.band_max ? p.band_max : (int)want);
+        st.cap = band_cap(p, st);
         st.above = 0;
         st.prefix = 0;
     }
     const unsigned cap_left = (unsigned)(st.cap - st.above);
     const int shift = level_shift(st.level), bits = level_bits(st.level);
-    unsigned cum = 0;
+    unsigned cum = 0, everything = 0;
     int owner = -1;
+    for (int t = 0; t < 256; ++t) everything += s_part[t];
     for (int t = 0; t < 256; ++t) {
         if (cum + s_part[t] > cap_left) { owner = t; break; }
         cum += s_part[t];
     }
     if (owner < 0) {
-        // everything that is left (under this prefix) fits into the band
-        st.lo = st.level == 0 ? 0ull : (st.prefix << (shift + bits));
+        // everything that is left of the pool (under this prefix) fits into the band
+        st.lo = st.level == 0 ? st.pool_lo : (st.prefix << (shift + bits));
         st.band_count = st.above + (int)cum;
         st.exhausted = st.level == 0 ? 1 : 0;
         st.phase = PHASE_BAND;
@@ -333,10 +584,22 @@ __global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant_
         st.above = total;
         st.prefix = (st.level == 0 ? 0ull : (st.prefix << bits)) | (unsigned long long)b;
         st.level += 1;
-        atomicAdd(pending, 1);
+        if (s_h[nb - 1 - b] == everything) {
+            // every key of this pass sits in bin b: digits on which their AND and OR agree are shared by all of them
+            const unsigned long long diff = k_and ^ k_or;
+            while (st.level < kLevels - 1) {
+                const int sh = level_shift(st.level), bt = level_bits(st.level);
+                const unsigned long long m = ((1ull << bt) - 1ull) << sh;
+                if (diff & m) break;
+                st.prefix = (st.prefix << bt) | ((k_and & m) >> sh);
+                st.level += 1;
+            }
+        }
+        atomicAdd(&flags[FLAG_SELECT_PENDING], 1);
     }
     states[img] = st;
 }
+
 
 __device__ __forceinline__ void bitonic_sort_desc(unsigned long long* keys, int n_pow2) {
     for (int k = 2; k <= n_pow2; k <<= 1) {
@@ -358,7 +621,7 @@ __device__ __forceinline__ void bitonic_sort_desc(unsigned long long* keys, int 
 __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant__ YoloParams p, ImgState* __restrict__ states,
                                                            const unsigned long long* __restrict__ band, int* __restrict__ band_fill,
                                                            float4* __restrict__ kept_box, int* __restrict__ kept_cls,
-                                                           ln_detection* __restrict__ records, int* __restrict__ active) {
+                                                           ln_detection* __restrict__ records, int* __restrict__ flags) {
     extern __shared__ unsigned char smem[];
     const int img = blockIdx.x;
     ImgState st = states[img];
@@ -480,29 +743,53 @@ __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant
         st.kept = s_kept;
         st.hi = st.lo;
         band_fill[img] = 0;
-        if (st.exhausted || st.kept >= p.k_eff) st.phase = PHASE_DONE;
+        if (st.kept >= p.k_eff || (st.exhausted && st.pool_lo == 0ull)) st.phase = PHASE_DONE;
         else {
-            st.phase = PHASE_SELECT;
+            atomicAdd(&flags[FLAG_ACTIVE], 1);
             st.level = 0;
-            atomicAdd(active, 1);
+            if (st.exhausted) {  // the pool is used up: the next one starts below it
+                st.phase = PHASE_POOL;
+                st.prefix = 0;
+                st.above = 0;
+                atomicAdd(&flags[FLAG_NEED_POOL], 1);
+            } else st.phase = PHASE_SELECT;
         }
         states[img] = st;
     }
 }
 
-__global__ void yolo_init_states_kernel(ImgState* states, const int* img_w, const int* img_h, int batch) {
+__global__ void yolo_init_states_kernel(ImgState* states, unsigned long long* key_and_or, const int* img_w, const int* img_h, int batch) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= batch) return;
     ImgState s;
-    s.hi = ~0ull; s.lo = 0; s.prefix = 0;
-    s.level = 0; s.phase = PHASE_SELECT; s.cap = 0; s.above = 0; s.band_count = 0; s.kept = 0; s.exhausted = 0;
-    s.img_w = img_w[i]; s.img_h = img_h[i]; s.last_gain = -1;
+    s.hi = ~0ull; s.lo = 0; s.prefix = 0; s.pool_lo = 0;
+    s.level = 0; s.phase = PHASE_POOL; s.cap = 0; s.above = 0; s.band_count = 0; s.kept = 0; s.exhausted = 0;
+    s.img_w = img_w[i]; s.img_h = img_h[i]; s.last_gain = -1; s.direct = 0; s.pool_count = 0;
     states[i] = s;
+    key_and_or[2 * i] = ~0ull;
+    key_and_or[2 * i + 1] = 0ull;
 }
 
 __global__ void yolo_counts_kernel(const ImgState* states, int* counts, int batch, int max_per_image) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < batch) counts[i] = states[i].kept < max_per_image ? states[i].kept : max_per_image;
+}
+
+// Largest distance between the approximate and the exact confidence key over a sweep of logits (debug aid that
+// justifies kKeySlack): objectness sweeps [obj_lo, obj_hi], class logit sweeps [x_lo, x_hi].
+__global__ void yolo_key_error_kernel(float obj_lo, float obj_hi, float x_lo, float x_hi, int n_obj, int n_x, unsigned* __restrict__ worst) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_obj * n_x) return;
+    const int io = i / n_x, ix = i - io * n_x;
+    const float o = obj_lo + (obj_hi - obj_lo) * ((float)io / (float)(n_obj > 1 ? n_obj - 1 : 1));
+    const float x = x_lo + (x_hi - x_lo) * ((float)ix / (float)(n_x > 1 ? n_x - 1 : 1));
+    const float obj = ln_det_sigmoid(o);
+    unsigned klo, khi;
+    approx_score_key(obj, x, klo, khi);
+    const unsigned mid = klo + (khi - klo) / 2u;
+    const unsigned exact = conf_key(__fmul_rn(obj, ln_det_sigmoid(x)));
+    const unsigned d = mid > exact ? mid - exact : exact - mid;
+    atomicMax(worst, d);
 }
 
 // ---- decode only (parity helper): per (anchor, cell) counts, then ordered writes ---------------
@@ -573,111 +860,145 @@ int fill_params(ln_ctx* ctx, YoloParams* p, const ln_yolo_head* heads, int32_t n
     return LN_OK;
 }
 
-}  // namespace
+struct Scratch {
+    size_t sz_states, sz_hist, sz_band, sz_fill, sz_kbox, sz_kcls, sz_rec, sz_dims, sz_cnt, sz_andor, sz_flags, sz_pool, total;
+};
 
-extern "C" {
+// Sizes of the working arrays of one call.  pool_entries = 0 picks the pool size: every candidate of an image when that
+// keeps the pools of the call within kPoolBytesTarget, otherwise that budget split over the images (at least 65536 keys).
+void scratch_layout(YoloParams* p, int pool_entries, Scratch* s) {
+    const int64_t B = p->batch;
+    const int64_t per_image = (int64_t)p->total_ca * p->classes;
+    int64_t pm = pool_entries;
+    if (pm <= 0) {
+        pm = kPoolBytesTarget / 8 / B;
+        if (pm < 65536) pm = 65536;
+    }
+    if (pm > per_image) pm = per_image;
+    if (pm < p->band_max + 1) pm = p->band_max + 1;  // a pool is only used for more than a band holds
+    pm = ln_round_up(pm, 2);                         // 16-byte rows
+    p->pool_max = (int)pm;
+    s->sz_states = (size_t)ln_round_up(B * (int64_t)sizeof(ImgState), 256);
+    s->sz_hist = (size_t)B * kBins * 4;
+    s->sz_band = (size_t)B * p->band_max * 8;
+    s->sz_fill = (size_t)ln_round_up(B * 8, 256);  // band_fill, pool_fill
+    s->sz_kbox = (size_t)B * p->k_eff * sizeof(float4);
+    s->sz_kcls = (size_t)ln_round_up(B * p->k_eff * 4, 256);
+    s->sz_rec = (size_t)ln_round_up(B * p->max_per_image * (int64_t)sizeof(ln_detection), 256);
+    s->sz_dims = (size_t)ln_round_up(B * 8, 256);
+    s->sz_cnt = (size_t)ln_round_up(B * 4, 256);
+    s->sz_andor = (size_t)ln_round_up(B * 16, 256);
+    s->sz_flags = 256;
+    s->sz_pool = (size_t)B * (size_t)pm * 8;
+    s->total = s->sz_states + s->sz_hist + s->sz_band + s->sz_fill + s->sz_kbox + s->sz_kcls + s->sz_rec + s->sz_dims + s->sz_cnt + s->sz_andor +
+               s->sz_flags + s->sz_pool;
+}
 
-int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t net_w, int32_t net_h, const int32_t* image_w,
-                           const int32_t* image_h, const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host) {
-    if (!ctx || !heads || !image_w || !image_h || !opts || !records_host || !counts_host) return ln_fail(ctx, LN_ERR_ARG, "ln_yolo_decode_nms: NULL argument");
-    if (opts->max_per_image < 1) return ln_fail(ctx, LN_ERR_ARG, "ln_yolo_decode_nms: max_per_image must be positive");
-    YoloParams p;
-    int rc = fill_params(ctx, &p, heads, n_heads, net_w, net_h, "ln_yolo_decode_nms");
-    if (rc) return rc;
-    p.thr = opts->confidence_threshold;
-    p.nms_thr = opts->nms_threshold;
-    p.letterbox = opts->letterbox;
-    p.max_per_image = opts->max_per_image;
-    p.k_eff = opts->top_k > 0 && opts->top_k < opts->max_per_image ? opts->top_k : opts->max_per_image;
-    p.band_max = p.k_eff <= 1024 ? kBandMaxLarge : kBandMaxSmall;
-    if (p.k_eff > 4096) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_yolo_decode_nms: at most 4096 detections per image (top_k / max_per_image)");
-    for (int i = 0; i < p.batch; ++i)
+int check_options(ln_ctx* ctx, YoloParams* p, const ln_detect_options* opts, const int32_t* image_w, const int32_t* image_h, int band_max, const char* who) {
+    p->thr = opts->confidence_threshold;
+    p->nms_thr = opts->nms_threshold;
+    p->letterbox = opts->letterbox;
+    p->max_per_image = opts->max_per_image;
+    p->k_eff = opts->top_k > 0 && opts->top_k < opts->max_per_image ? opts->top_k : opts->max_per_image;
+    p->band_max = band_max ? band_max : (p->k_eff <= 1024 ? kBandMaxLarge : kBandMaxSmall);
+    if (p->k_eff > 4096) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "%s: at most 4096 detections per image (top_k / max_per_image)", who);
+    for (int i = 0; i < p->batch; ++i)
         if (image_w[i] <= 0 || image_h[i] <= 0) return ln_fail(ctx, LN_ERR_ARG, "image dimensions must be positive for network detection decoding");
-    cudaSetDevice(ctx->device);
-    const int B = p.batch;
-    // scratch: states | hist | band | band_fill | kept | records | sizes | flags
-    const size_t sz_states = (size_t)ln_round_up((int64_t)B * sizeof(ImgState), 256);
-    const size_t sz_hist = (size_t)B * kBins * 4;
-    const size_t sz_band = (size_t)B * p.band_max * 8;
-    const size_t sz_fill = (size_t)ln_round_up((int64_t)B * 4, 256);
-    const size_t sz_kbox = (size_t)B * p.k_eff * sizeof(float4);
-    const size_t sz_kcls = (size_t)ln_round_up((int64_t)B * p.k_eff * 4, 256);
-    const size_t sz_rec = (size_t)ln_round_up((int64_t)B * p.max_per_image * sizeof(ln_detection), 256);
-    const size_t sz_dims = (size_t)ln_round_up((int64_t)B * 8, 256);
-    const size_t sz_cnt = (size_t)ln_round_up((int64_t)B * 4, 256);
-    p.cache_stride = (unsigned)ln_round_up((int64_t)p.total_ca * p.classes, 4);
-    const size_t sz_cache = (size_t)ln_round_up((int64_t)B * p.cache_stride * 4, 256);  // score keys of every (cell, anchor, class)
-    const size_t total = sz_states + sz_hist + sz_band + sz_fill + sz_kbox + sz_kcls + sz_rec + sz_dims + sz_cnt + sz_cache + 256;
-    unsigned char* scratch = (unsigned char*)ln_pool_alloc(ctx, total);
-    if (!scratch) return LN_ERR_CUDA;
-    unsigned char* q = scratch;
-    ImgState* states = (ImgState*)q; q += sz_states;
-    unsigned* hist = (unsigned*)q; q += sz_hist;
-    unsigned long long* band = (unsigned long long*)q; q += sz_band;
-    int* band_fill = (int*)q; q += sz_fill;
-    float4* kept_box = (float4*)q; q += sz_kbox;
-    int* kept_cls = (int*)q; q += sz_kcls;
-    ln_detection* records = (ln_detection*)q; q += sz_rec;
-    int* dims = (int*)q; q += sz_dims;
-    int* counts = (int*)q; q += sz_cnt;
-    unsigned* cache = (unsigned*)q; q += sz_cache;
-    int* flags = (int*)q;  // [0] pending selections, [1] images still active
+    return LN_OK;
+}
 
-    auto fail = [&](int code) { ln_pool_free(ctx, scratch, total); return code; };
-#define LN_Y(call)                                                                                            \
-    do {                                                                                                      \
-        cudaError_t e__ = (call);                                                                             \
-        if (e__ != cudaSuccess) return fail(ln_fail(ctx, LN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e__))); \
+// The whole decode + NMS call over working memory that the caller provides (s.total bytes at `scratch`, 256-byte aligned).
+int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned char* scratch, const int32_t* image_w, const int32_t* image_h,
+                   ln_detection* records_host, int32_t* counts_host, const char* who) {
+    const int B = p.batch;
+    unsigned char* q = scratch;
+    ImgState* states = (ImgState*)q; q += s.sz_states;
+    unsigned* hist = (unsigned*)q; q += s.sz_hist;
+    unsigned long long* band = (unsigned long long*)q; q += s.sz_band;
+    int* band_fill = (int*)q; int* pool_fill = band_fill + B; q += s.sz_fill;
+    float4* kept_box = (float4*)q; q += s.sz_kbox;
+    int* kept_cls = (int*)q; q += s.sz_kcls;
+    ln_detection* records = (ln_detection*)q; q += s.sz_rec;
+    int* dims = (int*)q; q += s.sz_dims;
+    int* counts = (int*)q; q += s.sz_cnt;
+    unsigned long long* key_and_or = (unsigned long long*)q; q += s.sz_andor;
+    int* flags = (int*)q; q += s.sz_flags;
+    unsigned long long* pool = (unsigned long long*)q;
+#define LN_Y(call)                                                                                     \
+    do {                                                                                               \
+        cudaError_t e__ = (call);                                                                      \
+        if (e__ != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "%s: %s: %s", who, #call, cudaGetErrorString(e__)); \
     } while (0)
-    LN_Y(cudaMemsetAsync(hist, 0, sz_hist, ctx->stream));
-    if (p.cache_stride != (unsigned)p.total_ca * (unsigned)p.classes) LN_Y(cudaMemsetAsync(cache, 0, sz_cache, ctx->stream));  // zero the per-image padding
-    LN_Y(cudaMemsetAsync(band_fill, 0, sz_fill, ctx->stream));
-    LN_Y(cudaMemsetAsync(flags, 0, 256, ctx->stream));
+    // the working memory keeps whatever an earlier call left: clear everything the kernels expect to start at zero
+    LN_Y(cudaMemsetAsync(hist, 0, s.sz_hist, ctx->stream));
+    LN_Y(cudaMemsetAsync(band_fill, 0, s.sz_fill, ctx->stream));
+    LN_Y(cudaMemsetAsync(flags, 0, s.sz_flags, ctx->stream));
     LN_Y(cudaMemcpyAsync(dims, image_w, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
     LN_Y(cudaMemcpyAsync(dims + B, image_h, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
-    yolo_init_states_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, dims, dims + B, B);
+    yolo_init_states_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, key_and_or, dims, dims + B, B);
     ctx->launches++;
 
     const size_t nms_smem = (size_t)p.band_max * 8 + (size_t)(p.k_eff + kChunk) * sizeof(float4) + (size_t)kChunk * (kChunk / 32) * 4 +
                             (size_t)(p.k_eff + kChunk) * 4 + (size_t)kChunk * 8 + 64;
     LN_Y(cudaFuncSetAttribute(yolo_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nms_smem));
     const dim3 scan_grid((p.total_ca + 255) / 256, B);
-    const dim3 flat_grid((unsigned)(((int64_t)p.total_ca * p.classes + kFlatChunk - 1) / kFlatChunk), B);
-    int* h_flags = ctx->h_status + 4;
+    const dim3 pool_grid((unsigned)((p.pool_max + kPoolChunk - 1) / kPoolChunk), B);
+    int* h_flags = ctx->h_status + 4;  // 4 ints
     const int max_rounds = 4096;
-    int round = 0;
     const bool dbg = getenv("LN_DEBUG_NMS") != nullptr;
     auto now = []() { timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6; };
-    double t_sel = 0, t_nms = 0;
-    int n_levels = 0;
+    // with LN_DEBUG_NMS set, every kernel is followed by a synchronize and its wall time is added to its class
+    double t_k[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    double t_mark = 0;
+    auto tick = [&]() { if (dbg) { cudaStreamSynchronize(ctx->stream); t_mark = now(); } };
+    auto tock = [&](int k) { if (dbg) { cudaStreamSynchronize(ctx->stream); t_k[k] += now() - t_mark; } };
+    int n_full = 0, n_pool_passes = 0, round = 0;
+    bool need_pool = true;
     for (; round < max_rounds; ++round) {
-        const double ta = dbg ? now() : 0;
-        for (int level = 0; level < kLevels; ++level) {
-            ++n_levels;
-            if (round == 0 && level == 0) yolo_scan_kernel<0, true><<<scan_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
-            else yolo_scan_cached_kernel<0><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
-            yolo_select_kernel<<<B, 256, 0, ctx->stream>>>(p, states, hist, flags);
+        // selection: pools for the images that need one, then a band inside every pool; repeated while some image descends a digit
+        for (int step = 0; step < 2 * kLevels + 2; ++step) {
+            if (need_pool) {
+                tick();
+                yolo_head_hist_kernel<<<scan_grid, 256, 0, ctx->stream>>>(p, states, hist);
+                tock(0); tick();
+                yolo_pool_select_kernel<<<B, 256, 0, ctx->stream>>>(p, states, hist, flags);
+                tock(1); tick();
+                yolo_head_fill_kernel<<<scan_grid, 256, 0, ctx->stream>>>(p, states, band, band_fill, pool, pool_fill);
+                tock(2);
+                yolo_after_fill_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, pool_fill, B, p.pool_max);
+                ctx->launches += 4;
+                n_full += 2;
+            }
+            tick();
+            yolo_pool_scan_kernel<0><<<pool_grid, 256, 0, ctx->stream>>>(p, states, hist, key_and_or, band, band_fill, pool);
+            tock(3); tick();
+            yolo_select_kernel<<<B, 256, 0, ctx->stream>>>(p, states, hist, key_and_or, flags);
+            tock(4);
             ctx->launches += 2;
-            LN_Y(cudaMemcpyAsync(h_flags, flags, 4, cudaMemcpyDeviceToHost, ctx->stream));
-            LN_Y(cudaMemsetAsync(flags, 0, 4, ctx->stream));
+            ++n_pool_passes;
+            LN_Y(cudaMemcpyAsync(h_flags, flags, 16, cudaMemcpyDeviceToHost, ctx->stream));
+            LN_Y(cudaMemsetAsync(flags, 0, 16, ctx->stream));
             LN_Y(cudaStreamSynchronize(ctx->stream));
-            if (h_flags[0] == 0) break;
+            need_pool = h_flags[FLAG_POOL_PENDING] != 0;
+            if (!need_pool && h_flags[FLAG_SELECT_PENDING] == 0) break;
         }
-        const double tb = dbg ? now() : 0;
-        t_sel += tb - ta;
-        yolo_scan_cached_kernel<1><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
-        if (dbg) { cudaStreamSynchronize(ctx->stream); const double tc = now(); fprintf(stderr, "[ln_yolo] collect %.3f ms\n", tc - tb); }
-        const double td = dbg ? now() : 0;
-        yolo_nms_kernel<<<B, 1024, nms_smem, ctx->stream>>>(p, states, band, band_fill, kept_box, kept_cls, records, flags + 1);
+        tick();
+        yolo_pool_scan_kernel<1><<<pool_grid, 256, 0, ctx->stream>>>(p, states, hist, key_and_or, band, band_fill, pool);
+        tock(5); tick();
+        yolo_nms_kernel<<<B, 1024, nms_smem, ctx->stream>>>(p, states, band, band_fill, kept_box, kept_cls, records, flags);
+        tock(6);
         ctx->launches += 2;
-        LN_Y(cudaMemcpyAsync(h_flags, flags + 1, 4, cudaMemcpyDeviceToHost, ctx->stream));
-        LN_Y(cudaMemsetAsync(flags + 1, 0, 4, ctx->stream));
+        LN_Y(cudaMemcpyAsync(h_flags, flags, 16, cudaMemcpyDeviceToHost, ctx->stream));
+        LN_Y(cudaMemsetAsync(flags, 0, 16, ctx->stream));
+        LN_Y(cudaMemsetAsync(pool_fill, 0, (size_t)B * 4, ctx->stream));
         LN_Y(cudaStreamSynchronize(ctx->stream));
-        if (dbg) t_nms += now() - td;
-        if (h_flags[0] == 0) break;
+        if (h_flags[FLAG_ACTIVE] == 0) break;
+        need_pool = need_pool || h_flags[FLAG_NEED_POOL] != 0;
     }
-    if (dbg) fprintf(stderr, "[ln_yolo] batch %d: %d rounds, %d selection passes (%.3f ms), nms kernels %.3f ms, band_max %d, k_eff %d\n", B, round + 1, n_levels, t_sel, t_nms, p.band_max, p.k_eff);
-    if (round == max_rounds) return fail(ln_fail(ctx, LN_ERR_TIMEOUT, "ln_yolo_decode_nms: NMS did not finish in %d rounds", max_rounds));
+    if (dbg) fprintf(stderr, "[ln_yolo] batch %d: %d rounds, %d passes over the heads, %d pool passes; ms: head histogram %.3f, pool select %.3f, head fill %.3f, "
+                     "pool histogram %.3f, band select %.3f, band collect %.3f, sort + nms %.3f; band_max %d, pool_max %d, k_eff %d\n",
+                     B, round + 1, n_full, n_pool_passes, t_k[0], t_k[1], t_k[2], t_k[3], t_k[4], t_k[5], t_k[6], p.band_max, p.pool_max, p.k_eff);
+    if (round == max_rounds) return ln_fail(ctx, LN_ERR_TIMEOUT, "%s: NMS did not finish in %d rounds", who, max_rounds);
     yolo_counts_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, counts, B, p.max_per_image);
     ctx->launches++;
     LN_Y(cudaGetLastError());
@@ -685,8 +1006,31 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
     LN_Y(cudaMemcpyAsync(records_host, records, (size_t)B * p.max_per_image * sizeof(ln_detection), cudaMemcpyDeviceToHost, ctx->stream));
     LN_Y(cudaStreamSynchronize(ctx->stream));
 #undef LN_Y
-    ln_pool_free(ctx, scratch, total);
     return LN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_heads, int32_t net_w, int32_t net_h, const int32_t* image_w,
+                           const int32_t* image_h, const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host) {
+    const char* who = "ln_yolo_decode_nms";
+    if (!ctx || !heads || !image_w || !image_h || !opts || !records_host || !counts_host) return ln_fail(ctx, LN_ERR_ARG, "%s: NULL argument", who);
+    if (opts->max_per_image < 1) return ln_fail(ctx, LN_ERR_ARG, "%s: max_per_image must be positive", who);
+    YoloParams p;
+    int rc = fill_params(ctx, &p, heads, n_heads, net_w, net_h, who);
+    if (rc) return rc;
+    rc = check_options(ctx, &p, opts, image_w, image_h, 0, who);
+    if (rc) return rc;
+    Scratch s;
+    scratch_layout(&p, ctx->nms_pool_entries, &s);
+    cudaSetDevice(ctx->device);
+    unsigned char* scratch = (unsigned char*)ln_pool_alloc(ctx, s.total);
+    if (!scratch) return LN_ERR_CUDA;
+    rc = run_decode_nms(ctx, p, s, scratch, image_w, image_h, records_host, counts_host, who);
+    ln_pool_free(ctx, scratch, s.total);
+    return rc;
 }
 
 // ---- decode + NMS without any allocation ------------------------------------------------------------
@@ -707,33 +1051,19 @@ int32_t ln_yolo_decode_nms_noalloc(ln_ctx* ctx, const ln_yolo_head* heads, int32
     YoloParams p;
     int rc = fill_params(ctx, &p, heads, n_heads, net_w, net_h, who);
     if (rc) return rc;
-    p.thr = opts->confidence_threshold;
-    p.nms_thr = opts->nms_threshold;
-    p.letterbox = opts->letterbox;
-    p.max_per_image = opts->max_per_image;
-    p.k_eff = opts->top_k > 0 && opts->top_k < opts->max_per_image ? opts->top_k : opts->max_per_image;
-    p.band_max = kBandMaxSmall;
-    if (p.k_eff > 4096) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "%s: at most 4096 detections per image (top_k / max_per_image)", who);
-    for (int i = 0; i < p.batch; ++i)
-        if (image_w[i] <= 0 || image_h[i] <= 0) return ln_fail(ctx, LN_ERR_ARG, "image dimensions must be positive for network detection decoding");
-    const int B = p.batch;
-    const size_t sz_states = (size_t)ln_round_up((int64_t)B * sizeof(ImgState), 256);
-    const size_t sz_hist = (size_t)B * kBins * 4;
-    const size_t sz_band = (size_t)B * p.band_max * 8;
-    const size_t sz_fill = (size_t)ln_round_up((int64_t)B * 4, 256);
-    const size_t sz_kbox = (size_t)B * p.k_eff * sizeof(float4);
-    const size_t sz_kcls = (size_t)ln_round_up((int64_t)B * p.k_eff * 4, 256);
-    const size_t sz_rec = (size_t)ln_round_up((int64_t)B * p.max_per_image * sizeof(ln_detection), 256);
-    const size_t sz_dims = (size_t)ln_round_up((int64_t)B * 8, 256);
-    const size_t sz_cnt = (size_t)ln_round_up((int64_t)B * 4, 256);
-    p.cache_stride = (unsigned)ln_round_up((int64_t)p.total_ca * p.classes, 4);
-    const size_t sz_cache = (size_t)ln_round_up((int64_t)B * p.cache_stride * 4, 256);
-    const size_t total = sz_states + sz_hist + sz_band + sz_fill + sz_kbox + sz_kcls + sz_rec + sz_dims + sz_cnt + sz_cache + 256;
-    if (total > (size_t)LN_NOALLOC_SCRATCH_BYTES)
+    rc = check_options(ctx, &p, opts, image_w, image_h, kBandMaxSmall, who);
+    if (rc) return rc;
+    // the pool gets what the fixed array has left after the other working arrays, and must hold every candidate of an
+    // image: this entry point never takes the extra passes a smaller pool can need
+    Scratch s;
+    scratch_layout(&p, 0, &s);
+    const int64_t per_image = (int64_t)p.total_ca * p.classes;
+    if (p.pool_max < per_image || s.total > (size_t)LN_NOALLOC_SCRATCH_BYTES)
         return ln_fail(ctx, LN_ERR_UNSUPPORTED,
-                       "%s: this call needs %zu bytes of working memory (batch %d, %d candidates per image, %d records per image) but the fixed "
+                       "%s: this call needs %zu bytes of working memory (batch %d, %lld candidates per image, %d records per image) but the fixed "
                        "array holds %u; use a smaller batch, fewer records, or ln_yolo_decode_nms",
-                       who, total, B, p.total_ca * p.classes, p.max_per_image, LN_NOALLOC_SCRATCH_BYTES);
+                       who, s.total - s.sz_pool + (size_t)p.batch * (size_t)ln_round_up(per_image, 2) * 8, p.batch, (long long)per_image, p.max_per_image,
+                       LN_NOALLOC_SCRATCH_BYTES);
     cudaSetDevice(ctx->device);
     if (!g_noalloc_ptr[ctx->device]) {
         // once per device, with that device current: the address of the module's array on this device
@@ -742,67 +1072,29 @@ int32_t ln_yolo_decode_nms_noalloc(ln_ctx* ctx, const ln_yolo_head* heads, int32
         if (e != cudaSuccess || !ptr) return ln_fail(ctx, LN_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
         g_noalloc_ptr[ctx->device] = (unsigned char*)ptr;
     }
-    unsigned char* q = g_noalloc_ptr[ctx->device];
-    ImgState* states = (ImgState*)q; q += sz_states;
-    unsigned* hist = (unsigned*)q; q += sz_hist;
-    unsigned long long* band = (unsigned long long*)q; q += sz_band;
-    int* band_fill = (int*)q; q += sz_fill;
-    float4* kept_box = (float4*)q; q += sz_kbox;
-    int* kept_cls = (int*)q; q += sz_kcls;
-    ln_detection* records = (ln_detection*)q; q += sz_rec;
-    int* dims = (int*)q; q += sz_dims;
-    int* counts = (int*)q; q += sz_cnt;
-    unsigned* cache = (unsigned*)q; q += sz_cache;
-    int* flags = (int*)q;
-#define LN_Z(call)                                                                                     \
-    do {                                                                                               \
-        cudaError_t e__ = (call);                                                                      \
-        if (e__ != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
-    } while (0)
-    // the array keeps whatever the previous call left: clear everything the kernels expect to start at zero
-    LN_Z(cudaMemsetAsync(hist, 0, sz_hist, ctx->stream));
-    LN_Z(cudaMemsetAsync(band_fill, 0, sz_fill, ctx->stream));
-    LN_Z(cudaMemsetAsync(flags, 0, 256, ctx->stream));
-    if (p.cache_stride != (unsigned)p.total_ca * (unsigned)p.classes) LN_Z(cudaMemsetAsync(cache, 0, sz_cache, ctx->stream));
-    LN_Z(cudaMemcpyAsync(dims, image_w, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
-    LN_Z(cudaMemcpyAsync(dims + B, image_h, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
-    yolo_init_states_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, dims, dims + B, B);
+    return run_decode_nms(ctx, p, s, g_noalloc_ptr[ctx->device], image_w, image_h, records_host, counts_host, who);
+}
+
+// Debug aid: largest distance (in confidence-key units) between the approximate and the exact score over a sweep.
+int32_t ln_debug_score_key_error(ln_ctx* ctx, float obj_lo, float obj_hi, float x_lo, float x_hi, int32_t n_obj, int32_t n_x, uint32_t* worst) {
+    if (!ctx || !worst || n_obj < 1 || n_x < 1) return ln_fail(ctx, LN_ERR_ARG, "ln_debug_score_key_error: bad argument");
+    cudaSetDevice(ctx->device);
+    unsigned* d = (unsigned*)ln_pool_alloc(ctx, 256);
+    if (!d) return LN_ERR_CUDA;
+    cudaMemsetAsync(d, 0, 4, ctx->stream);
+    const long long total = (long long)n_obj * n_x;
+    yolo_key_error_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x, d);
     ctx->launches++;
-    const size_t nms_smem = (size_t)p.band_max * 8 + (size_t)(p.k_eff + kChunk) * sizeof(float4) + (size_t)kChunk * (kChunk / 32) * 4 +
-                            (size_t)(p.k_eff + kChunk) * 4 + (size_t)kChunk * 8 + 64;
-    LN_Z(cudaFuncSetAttribute(yolo_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nms_smem));
-    const dim3 scan_grid((p.total_ca + 255) / 256, B);
-    const dim3 flat_grid((unsigned)(((int64_t)p.total_ca * p.classes + kFlatChunk - 1) / kFlatChunk), B);
-    int* h_flags = ctx->h_status + 4;
-    const int max_rounds = 4096;
-    int round = 0;
-    for (; round < max_rounds; ++round) {
-        for (int level = 0; level < kLevels; ++level) {
-            if (round == 0 && level == 0) yolo_scan_kernel<0, true><<<scan_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
-            else yolo_scan_cached_kernel<0><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
-            yolo_select_kernel<<<B, 256, 0, ctx->stream>>>(p, states, hist, flags);
-            ctx->launches += 2;
-            LN_Z(cudaMemcpyAsync(h_flags, flags, 4, cudaMemcpyDeviceToHost, ctx->stream));
-            LN_Z(cudaMemsetAsync(flags, 0, 4, ctx->stream));
-            LN_Z(cudaStreamSynchronize(ctx->stream));
-            if (h_flags[0] == 0) break;
-        }
-        yolo_scan_cached_kernel<1><<<flat_grid, 256, 0, ctx->stream>>>(p, states, hist, band, band_fill, cache);
-        yolo_nms_kernel<<<B, 1024, nms_smem, ctx->stream>>>(p, states, band, band_fill, kept_box, kept_cls, records, flags + 1);
-        ctx->launches += 2;
-        LN_Z(cudaMemcpyAsync(h_flags, flags + 1, 4, cudaMemcpyDeviceToHost, ctx->stream));
-        LN_Z(cudaMemsetAsync(flags + 1, 0, 4, ctx->stream));
-        LN_Z(cudaStreamSynchronize(ctx->stream));
-        if (h_flags[0] == 0) break;
-    }
-    if (round == max_rounds) return ln_fail(ctx, LN_ERR_TIMEOUT, "%s: NMS did not finish in %d rounds", who, max_rounds);
-    yolo_counts_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, counts, B, p.max_per_image);
-    ctx->launches++;
-    LN_Z(cudaGetLastError());
-    LN_Z(cudaMemcpyAsync(counts_host, counts, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    LN_Z(cudaMemcpyAsync(records_host, records, (size_t)B * p.max_per_image * sizeof(ln_detection), cudaMemcpyDeviceToHost, ctx->stream));
-    LN_Z(cudaStreamSynchronize(ctx->stream));
-#undef LN_Z
+    cudaError_t e = cudaMemcpyAsync(worst, d, 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    ln_pool_free(ctx, d, 256);
+    if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "ln_debug_score_key_error: %s", cudaGetErrorString(e));
+    return LN_OK;
+}
+
+int32_t ln_ctx_set_nms_pool_entries(ln_ctx* ctx, int64_t entries) {
+    if (!ctx || entries < 0 || entries > (1ll << 30)) return ln_fail(ctx, LN_ERR_ARG, "ln_ctx_set_nms_pool_entries: entries must be in [0, 2^30]");
+    ctx->nms_pool_entries = (int)entries;
     return LN_OK;
 }
 

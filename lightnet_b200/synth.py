@@ -32,3 +32,28 @@ def he_weights(layers, seed: int = 0, bn_identity: bool = True) -> np.ndarray:
 
 def uniform_images(batch, channels, height, width, seed: int = 1) -> np.ndarray:
     return np.random.default_rng(seed).random((batch, channels, height, width), dtype=np.float32)
+
+
+COCO_ANCHORS = [(10, 13), (16, 30), (33, 23), (30, 61), (62, 45), (59, 119), (116, 90), (156, 198), (373, 326)]
+
+
+def stress_heads(batch, grids=(80, 40, 20), classes=80, seed: int = 2, obj_mu: float = -4.0, chunk: int = 16):
+    """Raw [yolo] head tensors of the decode + NMS stress workload: 3 anchors per cell, xy logits N(0,1), wh logits
+    N(0,0.5) (the decode multiplies exp(wh) by the anchors), objectness and class logits N(obj_mu, 2).
+    Returns one f32 array [batch, 3*(5+classes), g, g] per grid, generated `chunk` images at a time."""
+    rng = np.random.default_rng(seed)
+    heads = []
+    for g in grids:
+        t = np.empty((batch, 3, 5 + classes, g, g), np.float32)
+        for b0 in range(0, batch, chunk):
+            b1 = min(batch, b0 + chunk)
+            n = b1 - b0
+            t[b0:b1, :, 0:2] = rng.standard_normal((n, 3, 2, g, g), dtype=np.float32)
+            t[b0:b1, :, 2:4] = rng.standard_normal((n, 3, 2, g, g), dtype=np.float32) * np.float32(0.5)
+            t[b0:b1, :, 4:] = rng.standard_normal((n, 3, 1 + classes, g, g), dtype=np.float32) * np.float32(2.0) + np.float32(obj_mu)
+        heads.append(t.reshape(batch, 3 * (5 + classes), g, g))
+    return heads
+
+
+def stress_head_specs(grids=(80, 40, 20), classes=80):
+    return [dict(gw=g, gh=g, classes=classes, anchors=COCO_ANCHORS[3 * i:3 * i + 3], scale_x_y=1.0, new_coords=0) for i, g in enumerate(grids)]

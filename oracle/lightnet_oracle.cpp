@@ -1401,6 +1401,49 @@ void orc_q8_epilogue(const int32_t* acc, int B, int F, int plane, const float* m
             }
 }
 
+// The same epilogue over floating-point accumulators with an E4M3 output code.
+void orc_f8_epilogue(const float* acc, int B, int F, int plane, const float* mult, const float* bias, int act, float inv_sy,
+                     float* out_f32, uint8_t* out_f8) {
+    for (int b = 0; b < B; ++b)
+        for (int f = 0; f < F; ++f)
+            for (int p = 0; p < plane; ++p) {
+                size_t i = ((size_t)b * F + f) * plane + p;
+                float a = det_activate((Act)act, std::fma(acc[i], mult[f], bias[f]));
+                if (out_f32) out_f32[i] = a;
+                if (out_f8) out_f8[i] = f32_to_e4m3_fast(a * inv_sy);
+            }
+}
+
+// Convolution of E4M3 codes accumulated in double (NCHW codes, [F][C][k][k] weight codes); taps outside the image are skipped.
+// l1 (optional) receives sum |x||w| per output, the yardstick for accumulation-order tolerances.
+void orc_conv_f8_acc(const uint8_t* x, int B, int C, int H, int W, const uint8_t* w, int F, int k, int stride, int pad, double* acc, double* l1) {
+    const int OH = conv_dim(H, pad, k, stride), OW = conv_dim(W, pad, k, stride);
+    float dec[256];
+    for (int c = 0; c < 256; ++c) dec[c] = ((c & 0x7F) == 0x7F) ? 0.0f : e4m3_to_f32((uint8_t)c);
+#pragma omp parallel for collapse(2) schedule(dynamic)
+    for (int b = 0; b < B; ++b)
+        for (int f = 0; f < F; ++f)
+            for (int oy = 0; oy < OH; ++oy)
+                for (int ox = 0; ox < OW; ++ox) {
+                    double a = 0.0, l = 0.0;
+                    for (int ic = 0; ic < C; ++ic)
+                        for (int ky = 0; ky < k; ++ky) {
+                            const int yy = oy * stride + ky - pad;
+                            if (yy < 0 || yy >= H) continue;
+                            for (int kx = 0; kx < k; ++kx) {
+                                const int xx = ox * stride + kx - pad;
+                                if (xx < 0 || xx >= W) continue;
+                                const double p = (double)dec[x[(((size_t)b * C + ic) * H + yy) * W + xx]] * (double)dec[w[(((size_t)f * C + ic) * k + ky) * k + kx]];
+                                a += p;
+                                l += std::fabs(p);
+                            }
+                        }
+                    const size_t o = (((size_t)b * F + f) * OH + oy) * OW + ox;
+                    acc[o] = a;
+                    if (l1) l1[o] = l;
+                }
+}
+
 // Single f32 conv layer in the reference loop order (folded weights + bias), NCHW.
 void orc_conv_f32(const float* x, int B, int C, int H, int W, const float* w, const float* bias, int F, int k, int sx, int sy,
                   int pad, int groups, int act, float* y) {

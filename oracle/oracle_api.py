@@ -70,6 +70,8 @@ def lib():
                                       C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_int]
         L.orc_nms_records.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_int]
         L.orc_conv_q8_acc.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
+        L.orc_f8_epilogue.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
+        L.orc_conv_f8_acc.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p, C.c_void_p]
         L.orc_q8_epilogue.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float,
                                       C.c_void_p, C.c_void_p]
         L.orc_conv_f32.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p, C.c_void_p] + [C.c_int] * 7 + [C.c_void_p]
@@ -306,6 +308,37 @@ def q8_epilogue(acc, mult, bias, act, inv_sy):
     lib().orc_q8_epilogue(_p(acc), B, F, OH * OW, _p(mult), _p(bias), ACT[act] if isinstance(act, str) else act,
                           float(inv_sy), _p(of), _p(oq))
     return of, oq
+
+
+def f8_epilogue(acc, mult, bias, act, inv_sy):
+    acc = np.ascontiguousarray(acc, np.float32)
+    B, F, OH, OW = acc.shape
+    mult = np.ascontiguousarray(mult, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    of = np.zeros(acc.shape, np.float32)
+    oq = np.zeros(acc.shape, np.uint8)
+    lib().orc_f8_epilogue(_p(acc), B, F, OH * OW, _p(mult), _p(bias), ACT[act] if isinstance(act, str) else act,
+                          float(inv_sy), _p(of), _p(oq))
+    return of, oq
+
+
+def conv_f8_acc(x, w, stride, pad):
+    """E4M3 code convolution in double: returns (acc, l1), both float64 NCHW."""
+    x = np.ascontiguousarray(x, np.uint8)
+    w = np.ascontiguousarray(w, np.uint8)
+    B, Cc, H, W = x.shape
+    F, _, k, _ = w.shape
+    OH = (H + 2 * pad - k) // stride + 1
+    OW = (W + 2 * pad - k) // stride + 1
+    acc = np.zeros((B, F, OH, OW), np.float64)
+    l1 = np.zeros((B, F, OH, OW), np.float64)
+    lib().orc_conv_f8_acc(_p(x), B, Cc, H, W, _p(w), F, k, stride, pad, _p(acc), _p(l1))
+    return acc, l1
+
+
+def f32_to_e4m3_array(v):
+    v = np.ascontiguousarray(v, np.float32)
+    return np.array([f32_to_e4m3_fast(t) for t in v.ravel()], np.uint8).reshape(v.shape)
 
 
 def conv_f32(x, w, bias, stride=1, pad=0, groups=1, act="linear"):
