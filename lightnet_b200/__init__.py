@@ -380,7 +380,7 @@ class B200Backend:
         iw = np.ascontiguousarray(np.broadcast_to(np.asarray(image_w, np.int32), (batch,)))
         ih = np.ascontiguousarray(np.broadcast_to(np.asarray(image_h, np.int32), (batch,)))
         opts = ln_detect_options(confidence_threshold, nms_threshold, int(letterbox), top_k, max_per_image)
-        rec = np.zeros((batch, max_per_image, 7), np.float32)
+        rec = np.empty((batch, max_per_image, 7), np.float32)
         cnt = np.zeros(batch, np.int32)
         # noalloc=True takes the entry point that keeps its working memory in a fixed array of the library (for hosts
         # that may not allocate device memory while serving); same records, bounded problem size

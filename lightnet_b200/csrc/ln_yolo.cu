@@ -73,6 +73,7 @@ struct YoloParams {
     int max_per_image;  // record capacity
     int band_max;       // capacity of one band
     int pool_max;       // capacity of one pool
+    int hist_stride;    // the first histogram of a pool looks at every hist_stride-th block of 256 (anchor, cell) slots
 };
 
 struct ImgState {
@@ -84,6 +85,7 @@ struct ImgState {
     int last_gain;   // survivors the previous band added
     int direct;      // the pool being filled is small enough to be the band itself
     int pool_count;  // keys in the pool
+    int sampled;     // the histogram in progress is an estimate from a sample of the slots
 };
 
 __device__ __forceinline__ int level_shift(int l) { return l < 5 ? 52 - 12 * l : 0; }
@@ -225,6 +227,9 @@ __global__ void __launch_bounds__(256) yolo_head_hist_kernel(const __grid_consta
     const int img = blockIdx.y;
     const ImgState st = states[img];
     if (st.phase != PHASE_POOL) return;
+    // an estimate is enough to place the pool's lower bound (the fill pass is exact whatever the bound): sampled images
+    // histogram one block in hist_stride, offset by the image index
+    if (st.sampled && (int)(blockIdx.x % p.hist_stride) != img % p.hist_stride) return;
     __shared__ unsigned s_hist[kBins + 1];  // slot kBins swallows the first, empty run of every thread
     for (int i = threadIdx.x; i <= kBins; i += blockDim.x) s_hist[i] = 0;
     __syncthreads();
@@ -332,6 +337,58 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
     __syncthreads();
     const int n_listed = s_n;
     if (n_listed == 0) return;
+    auto emit = [&](unsigned long long key) {
+        const int slot = atomicAdd(&s_cnt[warp], 1);  // stays below kWarpBuf, see the flush conditions
+        s_buf[warp * kWarpBuf + slot] = key;
+    };
+    auto flush_if = [&](int limit, bool last) {
+        // the warp writes its buffered keys out when the next step could overflow the buffer, and at the end
+        __syncwarp();
+        const int n = s_cnt[warp];
+        if (n > limit || (n > 0 && last)) {
+            int at = 0;
+            if (lane == 0) at = atomicAdd(fill, n);
+            at = __shfl_sync(0xffffffffu, at, 0);
+            for (int k = lane; k < n; k += 32)
+                if (at + k < dst_cap) dst[at + k] = s_buf[warp * kWarpBuf + k];
+            __syncwarp();
+            if (lane == 0) s_cnt[warp] = 0;
+        }
+        __syncwarp();
+    };
+    if (n_listed >= 64) {
+        // many listed slots: thread t takes listed slot t and walks its classes, eight loads in flight
+        if (warp * 32 >= n_listed) return;
+        const bool have = (int)threadIdx.x < n_listed;
+        const int j = have ? (int)threadIdx.x : 0;
+        const float obj = s_obj[j];
+        const int new_coords = s_ca[j] < 0 ? 1 : 0, stride = s_stride[j];
+        const unsigned cell = (unsigned)s_ca[j] & 0x7FFFFFFFu;
+        const float* __restrict__ cls_raw = s_ptr[j];
+        const bool fast = approx_ok && !new_coords;
+        for (int c0 = 0; c0 < p.classes; c0 += 8) {
+            if (have) {
+                float xs[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) xs[q] = c0 + q < p.classes ? __ldg(cls_raw + (size_t)q * stride) : 0.0f;
+                cls_raw += (size_t)8 * stride;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const float x = xs[q];
+                    unsigned klo, khi;
+                    approx_score_key(obj, x, klo, khi);
+                    const bool out = fast && x == x && (khi <= kthr || khi < r.rlo_ck || klo > r.rhi_ck);
+                    if (!out && c0 + q < p.classes) {
+                        const unsigned long long key = exact_key_in_range(p, r, obj, x, new_coords, cell, (unsigned)(c0 + q));
+                        if (key != 0ull) emit(key);
+                    }
+                }
+            }
+            flush_if(kWarpBuf - 256, c0 + 8 >= p.classes);  // a step adds at most 8 x 32 keys
+        }
+        return;
+    }
+    // few listed slots: all threads share the (class, listed slot) pairs
     const int items = n_listed * p.classes;
     for (int base = 0; base < items; base += 256) {  // uniform trip count
         const int i = base + (int)threadIdx.x;
@@ -349,25 +406,10 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
             }
             if (maybe) {
                 const unsigned long long key = exact_key_in_range(p, r, obj, x, new_coords, cell, (unsigned)c);
-                if (key != 0ull) {
-                    const int slot = atomicAdd(&s_cnt[warp], 1);  // < kWarpBuf: at most 32 new keys per step on top of at most kWarpBuf - 32 kept
-                    s_buf[warp * kWarpBuf + slot] = key;
-                }
+                if (key != 0ull) emit(key);
             }
         }
-        // the warp writes its buffered keys out when the next step could overflow the buffer, and at the end
-        __syncwarp();
-        const int n = s_cnt[warp];
-        if (n > kWarpBuf - 32 || (n > 0 && base + 256 >= items)) {
-            int at = 0;
-            if (lane == 0) at = atomicAdd(fill, n);
-            at = __shfl_sync(0xffffffffu, at, 0);
-            for (int k = lane; k < n; k += 32)
-                if (at + k < dst_cap) dst[at + k] = s_buf[warp * kWarpBuf + k];
-            __syncwarp();
-            if (lane == 0) s_cnt[warp] = 0;
-        }
-        __syncwarp();
+        flush_if(kWarpBuf - 32, base + 256 >= items);  // a step adds at most 32 keys
     }
 }
 
@@ -390,6 +432,9 @@ __device__ __forceinline__ void load_hist_desc(unsigned* h, int nb, unsigned* s_
 
 // One block per image that needs a pool: walk the digit histogram from the top until the candidates counted reach the
 // band size wanted; everything from that bin up is the pool.  A bin too large for a pool is descended into.
+// With a sampled histogram the counts are estimates (scaled by the sampling stride): the target is doubled, sizes are
+// compared with a margin of one half, and an image whose boundary bin looks too large for a pool starts over with the
+// full histogram.  The fill pass counts exactly; should it overflow all the same, the image starts over as well.
 __global__ void __launch_bounds__(256) yolo_pool_select_kernel(const __grid_constant__ YoloParams p, ImgState* __restrict__ states,
                                                                unsigned* __restrict__ hist, int* __restrict__ flags) {
     const int img = blockIdx.x;
@@ -405,15 +450,16 @@ __global__ void __launch_bounds__(256) yolo_pool_select_kernel(const __grid_cons
         st.above = 0;
         st.prefix = 0;
     }
+    const long long scale = st.sampled ? p.hist_stride : 1;
     const int shift = level_shift(st.level), bits = level_bits(st.level);
-    const long long want = (long long)st.cap - st.above;  // > 0
+    const long long want = st.sampled ? 2ll * st.cap : (long long)st.cap - st.above;  // > 0
     long long cum = 0;
     int b = -1;
     for (int t = 0; t < 256 && b < 0; ++t) {
-        if (cum + s_part[t] < want) { cum += s_part[t]; continue; }
+        if ((cum + s_part[t]) * scale < want) { cum += s_part[t]; continue; }
         for (int j = 0; j < kBins / 256; ++j) {
             const int slot = t * (kBins / 256) + j;
-            if (cum + s_h[slot] >= want) { b = nb - 1 - slot; break; }
+            if ((cum + s_h[slot]) * scale >= want) { b = nb - 1 - slot; break; }
             cum += s_h[slot];
         }
     }
@@ -422,23 +468,27 @@ __global__ void __launch_bounds__(256) yolo_pool_select_kernel(const __grid_cons
     if (b < 0) {
         // everything that is left (under this prefix) is fewer than wanted: take all of it
         st.pool_lo = base;
-        count = st.above + cum;
+        count = st.above + cum * scale;
     } else {
-        const long long incl = st.above + cum + s_h[nb - 1 - b];
-        if (incl <= p.pool_max || st.level == kLevels - 1) {
+        const long long incl = st.above + (cum + s_h[nb - 1 - b]) * scale;
+        const long long fits = st.sampled ? incl + incl / 2 : incl;
+        if (fits <= p.pool_max || (!st.sampled && st.level == kLevels - 1)) {
             st.pool_lo = base + ((unsigned long long)b << shift);
             count = incl;
         } else {
-            st.above += (int)cum;
-            st.prefix = (st.level == 0 ? 0ull : (st.prefix << bits)) | (unsigned long long)b;
-            st.level += 1;
+            if (st.sampled) st.sampled = 0;  // same level again, every block this time
+            else {
+                st.above += (int)cum;
+                st.prefix = (st.level == 0 ? 0ull : (st.prefix << bits)) | (unsigned long long)b;
+                st.level += 1;
+            }
             atomicAdd(&flags[FLAG_POOL_PENDING], 1);
             states[img] = st;
             return;
         }
     }
     st.phase = PHASE_FILL;
-    st.direct = count <= p.band_max ? 1 : 0;
+    st.direct = (st.sampled ? count + count / 2 : count) <= p.band_max ? 1 : 0;
     if (st.direct) {
         st.lo = st.pool_lo;
         st.band_count = (int)count;
@@ -448,14 +498,29 @@ __global__ void __launch_bounds__(256) yolo_pool_select_kernel(const __grid_cons
     states[img] = st;
 }
 
-// After the fill pass: a filled pool goes to band selection, a directly filled band to NMS.
-__global__ void yolo_after_fill_kernel(ImgState* __restrict__ states, const int* __restrict__ pool_fill, int batch, int pool_max) {
+// After the fill pass: a filled pool goes to band selection, a directly filled band to NMS.  A fill that found more
+// keys than its destination holds (possible only after a sampled histogram) is thrown away and the image starts over
+// with the full histogram.
+__global__ void yolo_after_fill_kernel(ImgState* __restrict__ states, int* __restrict__ band_fill, int* __restrict__ pool_fill, int batch,
+                                       int band_max, int pool_max, int hist_stride, int* __restrict__ flags) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= batch || states[i].phase != PHASE_FILL) return;
-    if (states[i].direct) states[i].phase = PHASE_BAND;
-    else {
-        const int n = pool_fill[i];
-        states[i].pool_count = n < pool_max ? n : pool_max;
+    int* fill = states[i].direct ? band_fill + i : pool_fill + i;
+    const int n = *fill;
+    if (n > (states[i].direct ? band_max : pool_max)) {
+        *fill = 0;
+        states[i].phase = PHASE_POOL;
+        states[i].sampled = 0;
+        states[i].level = 0;
+        atomicAdd(&flags[FLAG_POOL_PENDING], 1);
+        return;
+    }
+    states[i].sampled = hist_stride > 1 ? 1 : 0;  // for the next pool of this image
+    if (states[i].direct) {
+        states[i].band_count = n;
+        states[i].phase = PHASE_BAND;
+    } else {
+        states[i].pool_count = n;
         states[i].phase = PHASE_SELECT;
         states[i].level = 0;
     }
@@ -758,13 +823,13 @@ __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant
     }
 }
 
-__global__ void yolo_init_states_kernel(ImgState* states, unsigned long long* key_and_or, const int* img_w, const int* img_h, int batch) {
+__global__ void yolo_init_states_kernel(ImgState* states, unsigned long long* key_and_or, const int* img_w, const int* img_h, int batch, int hist_stride) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= batch) return;
     ImgState s;
     s.hi = ~0ull; s.lo = 0; s.prefix = 0; s.pool_lo = 0;
     s.level = 0; s.phase = PHASE_POOL; s.cap = 0; s.above = 0; s.band_count = 0; s.kept = 0; s.exhausted = 0;
-    s.img_w = img_w[i]; s.img_h = img_h[i]; s.last_gain = -1; s.direct = 0; s.pool_count = 0;
+    s.img_w = img_w[i]; s.img_h = img_h[i]; s.last_gain = -1; s.direct = 0; s.pool_count = 0; s.sampled = hist_stride > 1 ? 1 : 0;
     states[i] = s;
     key_and_or[2 * i] = ~0ull;
     key_and_or[2 * i + 1] = 0ull;
@@ -878,6 +943,8 @@ void scratch_layout(YoloParams* p, int pool_entries, Scratch* s) {
     if (pm < p->band_max + 1) pm = p->band_max + 1;  // a pool is only used for more than a band holds
     pm = ln_round_up(pm, 2);                         // 16-byte rows
     p->pool_max = (int)pm;
+    // sampling pays once an image has many blocks of slots; small images are histogrammed in full
+    p->hist_stride = (p->total_ca + 255) / 256 >= 64 ? 8 : 1;
     s->sz_states = (size_t)ln_round_up(B * (int64_t)sizeof(ImgState), 256);
     s->sz_hist = (size_t)B * kBins * 4;
     s->sz_band = (size_t)B * p->band_max * 8;
@@ -929,13 +996,16 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
         cudaError_t e__ = (call);                                                                      \
         if (e__ != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "%s: %s: %s", who, #call, cudaGetErrorString(e__)); \
     } while (0)
+    const bool dbg = getenv("LN_DEBUG_NMS") != nullptr;
+    auto now = []() { timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6; };
+    const double t_begin = dbg ? now() : 0;
     // the working memory keeps whatever an earlier call left: clear everything the kernels expect to start at zero
     LN_Y(cudaMemsetAsync(hist, 0, s.sz_hist, ctx->stream));
     LN_Y(cudaMemsetAsync(band_fill, 0, s.sz_fill, ctx->stream));
     LN_Y(cudaMemsetAsync(flags, 0, s.sz_flags, ctx->stream));
     LN_Y(cudaMemcpyAsync(dims, image_w, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
     LN_Y(cudaMemcpyAsync(dims + B, image_h, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
-    yolo_init_states_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, key_and_or, dims, dims + B, B);
+    yolo_init_states_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, key_and_or, dims, dims + B, B, p.hist_stride);
     ctx->launches++;
 
     const size_t nms_smem = (size_t)p.band_max * 8 + (size_t)(p.k_eff + kChunk) * sizeof(float4) + (size_t)kChunk * (kChunk / 32) * 4 +
@@ -945,8 +1015,6 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
     const dim3 pool_grid((unsigned)((p.pool_max + kPoolChunk - 1) / kPoolChunk), B);
     int* h_flags = ctx->h_status + 4;  // 4 ints
     const int max_rounds = 4096;
-    const bool dbg = getenv("LN_DEBUG_NMS") != nullptr;
-    auto now = []() { timespec ts; clock_gettime(CLOCK_MONOTONIC, &ts); return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6; };
     // with LN_DEBUG_NMS set, every kernel is followed by a synchronize and its wall time is added to its class
     double t_k[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     double t_mark = 0;
@@ -965,7 +1033,7 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
                 tock(1); tick();
                 yolo_head_fill_kernel<<<scan_grid, 256, 0, ctx->stream>>>(p, states, band, band_fill, pool, pool_fill);
                 tock(2);
-                yolo_after_fill_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, pool_fill, B, p.pool_max);
+                yolo_after_fill_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, band_fill, pool_fill, B, p.band_max, p.pool_max, p.hist_stride, flags);
                 ctx->launches += 4;
                 n_full += 2;
             }
@@ -995,6 +1063,7 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
         if (h_flags[FLAG_ACTIVE] == 0) break;
         need_pool = need_pool || h_flags[FLAG_NEED_POOL] != 0;
     }
+    const double t_loop = dbg ? now() : 0;
     if (dbg) fprintf(stderr, "[ln_yolo] batch %d: %d rounds, %d passes over the heads, %d pool passes; ms: head histogram %.3f, pool select %.3f, head fill %.3f, "
                      "pool histogram %.3f, band select %.3f, band collect %.3f, sort + nms %.3f; band_max %d, pool_max %d, k_eff %d\n",
                      B, round + 1, n_full, n_pool_passes, t_k[0], t_k[1], t_k[2], t_k[3], t_k[4], t_k[5], t_k[6], p.band_max, p.pool_max, p.k_eff);
@@ -1005,6 +1074,7 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
     LN_Y(cudaMemcpyAsync(counts_host, counts, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
     LN_Y(cudaMemcpyAsync(records_host, records, (size_t)B * p.max_per_image * sizeof(ln_detection), cudaMemcpyDeviceToHost, ctx->stream));
     LN_Y(cudaStreamSynchronize(ctx->stream));
+    if (dbg) fprintf(stderr, "[ln_yolo] whole call %.3f ms, of which the read-back of counts and records %.3f ms\n", now() - t_begin, now() - t_loop);
 #undef LN_Y
     return LN_OK;
 }

@@ -319,6 +319,30 @@ def test_approximate_score_keys_stay_within_the_slack(be):
     assert worst <= 64, worst
 
 
+def test_decode_nms_sampled_histogram_misjudges(be):
+    """Large heads get their first histogram from one block of 256 (anchor, cell) slots in eight.  Here image 0 has candidates
+    only in blocks the sample does not look at, more of them than a band holds: the fill overflows the band the estimate chose
+    and the image has to start over with the full histogram.  Image 1 is ordinary."""
+    classes, g = 2, 128
+    rng = np.random.default_rng(13)
+    h = np.full((2, 3 * (5 + classes), g, g), -9.0, np.float32)
+    v = h.reshape(2, 3, 5 + classes, g * g)
+    v[:, :, 0:4] = rng.normal(0, 0.5, (2, 3, 4, g * g))
+    slot = np.arange(3 * g * g).reshape(3, g * g)          # (anchor, cell) slot index
+    chosen = (slot // 256) % 8 == 1                         # image 0 samples blocks with index % 8 == 0
+    v[0, :, 4][chosen] = 3.0
+    v[0, :, 5][chosen] = rng.normal(2.0, 0.3, chosen.sum())
+    v[0, :, 6][chosen] = 1.0
+    v[1, :, 4:] = rng.normal(-3, 2, (3, 1 + classes, g * g))
+    specs = [dict(gw=g, gh=g, classes=classes, anchors=ANCH[:3], scale_x_y=1.0, new_coords=0)]
+    dev = [dict(raw=be.upload_f32(h.shape, h), classes=classes, anchors=ANCH[:3], scale_x_y=1.0, new_coords=0)]
+    got = be.yolo_decode_nms(dev, 512, 512, 512, 512, 0.1, 0.45, False, 0, 2048)
+    for i in range(2):
+        ref = orc.decode_nms([h[i]], specs, 512, 512, 512, 512, 0.1, 0.45, letterbox=False, det_exp=True)[:2048]
+        assert ref.shape[0] > 100
+        assert np.array_equal(got[i], ref), i
+
+
 def test_decode_nms_nan_and_infinite_logits(be):
     """NaN and infinite objectness / class logits go through the same clamps as on the CPU (a NaN class logit comes out of the
     exact sigmoid as 1, a NaN objectness fails the threshold test)."""
