@@ -194,8 +194,10 @@ __device__ __forceinline__ __half2 ln_h2_act(__half2 v) {
 }
 template <int ACT>
 __device__ __forceinline__ uint32_t ln_h2_act_quant(float v0, float v1, __half2 inv_s) {
-    // pre-activations beyond the binary16 range saturate (their codes saturate anyway)
-    const __half2 v = __floats2half2_rn(fminf(fmaxf(v0, -60000.0f), 60000.0f), fminf(fmaxf(v1, -60000.0f), 60000.0f));
+    // pre-activations beyond the binary16 range saturate to its largest finite value in the conversion itself (their codes saturate anyway)
+    uint32_t vb;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(vb) : "f"(v1), "f"(v0));  // first source -> upper half
+    const __half2 v = *reinterpret_cast<const __half2*>(&vb);
     __half2 t = __hmul2(ln_h2_act<ACT>(v), inv_s);
     t = __hmin2(__hmax2(t, __float2half2_rn(-127.0f)), __float2half2_rn(127.0f));
     t = __hadd2(t, __float2half2_rn(1536.0f));  // ulp is 1 in [1024, 2048): the low mantissa bits are rne(t)

@@ -117,6 +117,8 @@ Q8_CASES = [  # (n, c, h, w, f, k, stride, pad): BASELINE config-2 layer shapes 
     (1, 64, 13, 13, 32, 3, 2, 1),      # odd input, stride 2
     (5, 128, 7, 5, 96, 3, 1, 1),       # tiny, batch-tiled
     (1, 16, 20, 20, 32, 3, 1, 1),      # channels padded 16 -> 32
+    (4, 64, 96, 96, 512, 1, 1, 0),     # several tiles per CTA with two accumulator buffers (256-filter tiles)
+    (6, 32, 120, 120, 64, 3, 1, 1),    # several tiles per CTA with eight accumulator buffers, weights resident
 ]
 
 
