@@ -207,7 +207,8 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
    Limits and rules:
      - a call whose working set (it grows with batch x grid cells x anchors x classes, and with max_per_image) does
        not fit in the 64 MiB is refused with LN_ERR_UNSUPPORTED and a message that names both sizes; nothing is
-       truncated.  For scale: three YOLOv4-608 heads with 80 classes fit for batches up to 8;
+       truncated.  For scale: three YOLOv4-608 heads with 80 classes fit for batches up to 4 (8 bytes for every
+       (cell, anchor, class) slot of an image, 1.82 million of them at that size);
      - the first call on each device looks up the device address of the array; make that first call during set-up,
        before any stream capture begins;
      - all calls on a device share the one array, which still holds what the previous call left; the parts that must
