@@ -35,6 +35,9 @@ struct ln_conv_umma_params {
     const void* res;
     long long res_pixel_stride;
     float s_c, s_res, inv_sy2;
+    // Pixel-group packing of 1x1 convolutions with few channels (pack > 1): an accumulator row is `pack` consecutive pixels,
+    // its column j * f_real + f is filter f of the j-th of them (see ln_conv_umma_plan_build).
+    int pack, f_real;
     int* status;
     long long* debug;  // optional: role timing of CTA 0 (32 counters), null = off
 };
@@ -42,6 +45,10 @@ struct ln_conv_umma_params {
 struct ln_conv_umma_plan {
     ln_conv_umma_params p;
     float2* mb = nullptr;
+    // device storage the plan owns when it packs pixel groups: the block-diagonal weight matrix and its {mult, bias} pairs
+    void* aux_w = nullptr;
+    float2* aux_mb = nullptr;
+    size_t aux_w_bytes = 0, aux_mb_bytes = 0;
     size_t smem = 0;
     int grid = 0;
     int kind = LN_KIND_I8;
@@ -84,6 +91,8 @@ bool ln_conv_umma_supported(int64_t channels_padded, int64_t k, int64_t stride_x
 int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_geom& g);
 int ln_conv_umma_make_mb(ln_ctx* ctx, const float* wscale_dev, const float* bias_dev, float x_scale, int F, int fpad, float2* mb_dev);
 int ln_conv_umma_launch(ln_ctx* ctx, const ln_conv_umma_plan* plan);
+// Returns the storage a plan owns (aux_w / aux_mb) to the ctx pool.
+void ln_conv_umma_plan_release(ln_ctx* ctx, ln_conv_umma_plan* plan);
 
 // CUDA-core int8 / FP8 convolution for shapes the tensor-core kernel does not take (any C, stride, padding).
 // Weights in the reference's [F][C][k][k] order.

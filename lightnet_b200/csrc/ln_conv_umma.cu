@@ -11,8 +11,8 @@
 // matching weight slab.  Stride-2 convolutions use one tensor map per input parity class so that the
 // strided gather is again a dense box.  Every CTA fetches its own operands.
 //
-// Roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..9 = epilogue (two warps per
-// TMEM lane quadrant, alternating 32-column chunks, so every scheduler has two warps to hide latency with).
+// Roles (448 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..13 = epilogue (three warps per
+// TMEM lane quadrant, each group of four warps taking every third tile, so every scheduler has three warps to hide latency with).
 // The accumulator is double buffered in TMEM so the epilogue of tile t overlaps the main loop of t+1.
 // Every mbarrier wait is bounded: when it gives up it raises a status word the host reads, and all
 // roles leave their loops, TMEM is released and the kernel returns.
@@ -23,10 +23,18 @@
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr int kThreads = 320;       // 2 + 8 warps
-constexpr int kEpilogueWarps = 8;    // two groups of four; a group takes every other tile
+constexpr int kEpilogueGroups = 3;   // groups of four epilogue warps (one warp per TMEM lane quadrant); group g takes the tiles t with t % groups == g
+constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
+constexpr int kThreads = 32 * (2 + kEpilogueWarps);  // producer warp, MMA warp, epilogue warps
 constexpr int kMaxAccBufs = 8;       // accumulator tiles in TMEM: 512 columns / BN, at most 8
 constexpr uint32_t kWaitLimit = 1u << 20;
+// Role timing of CTA 0 (clock reads in the hot loops) is compiled in only with -DLN_CONV_ROLE_TIMING.
+#ifdef LN_CONV_ROLE_TIMING
+constexpr bool kRoleTiming = true;
+#else
+constexpr bool kRoleTiming = false;
+#endif
+constexpr uint32_t kWaitHintNs = 2000;  // how long one try_wait may sleep in hardware before it reports "not yet"
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -43,10 +51,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     return ok != 0;
 }
@@ -56,10 +64,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 template <bool BACKOFF = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                           long long* waited = nullptr) {
-    const long long t0 = waited ? clock64() : 0;
+    const long long t0 = kRoleTiming && waited ? clock64() : 0;
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) {
-            if (waited) *waited += clock64() - t0;
+            if (kRoleTiming && waited) *waited += clock64() - t0;
             return true;
         }
         if (BACKOFF && it > 4u) __nanosleep(40);  // single-lane roles: stop stealing issue slots from the epilogue warps of this scheduler
@@ -198,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         }
         for (int b = 0; b < nbuf; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), kEpilogueWarps / 2);
+            mbar_init(tempty_bar(b), 4);  // the four warps of the group that drained the buffer
         }
         mbar_init(bres_bar, 1);
         *abort_flag = 0;
@@ -225,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             bool ok = true;
             long long w_empty = 0;
             long long* pw = p.debug ? &w_empty : nullptr;
-            const long long t_start = clock64();
+            const long long t_start = kRoleTiming ? clock64() : 0;
             if (b_res && (int)blockIdx.x < p.num_tiles) {
                 mbar_arrive_expect_tx(bres_bar, (uint32_t)kblocks * b_bytes);
                 for (int kb = 0; kb < kblocks; ++kb) {
@@ -256,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (p.debug && blockIdx.x == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
+            if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -270,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             long long w_tempty = 0, w_full = 0;
             long long* pw1 = p.debug ? &w_tempty : nullptr;
             long long* pw2 = p.debug ? &w_full : nullptr;
-            const long long t_start = clock64();
+            const long long t_start = kRoleTiming ? clock64() : 0;
             if (b_res && (int)blockIdx.x < p.num_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT);
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
                 const int buf = t % nbuf;
@@ -291,12 +299,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                 if (!ok) break;
                 tc_commit(tfull_bar(buf));
             }
-            if (p.debug && blockIdx.x == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; }
+            if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; }
         }
     } else {
         // ------------------------------------------------------------------ epilogue
         const int quad = warp & 3;          // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
-        const int group = (warp - 2) >> 2;  // which of the two warps of the quadrant: each group takes every other tile
+        // Which of the warps of the quadrant: group g takes the tiles with t % groups == g.  Never more groups than accumulator
+        // buffers: a group that starts waiting for tile t has finished tile t - groups, so every earlier tile's accumulation is
+        // complete, in particular the previous use of this buffer (tile t - nbuf <= t - groups); a parity wait needs that.
+        const int group = (warp - 2) >> 2;
+        const int groups = nbuf < kEpilogueGroups ? nbuf : kEpilogueGroups;
         const int row = quad * 32 + lane;
         const int pw = row & (p.TW - 1), ph = (row >> p.log_tw) & (p.TH - 1), pn = row >> (p.log_tw + p.log_th);
         constexpr bool kTranscendental = ACT == LN_ACT_MISH || ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC;
@@ -304,14 +316,15 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         bool ok = true;
         long long w_tfull = 0, dbg_ld = 0, dbg_math = 0, dbg_st = 0;
         long long* pwe = p.debug ? &w_tfull : nullptr;
-        const long long t_start = clock64();
-        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
+        const long long t_start = kRoleTiming ? clock64() : 0;
+        int turn = 0;  // t % groups
+        for (int tile = blockIdx.x; ok && group < groups && tile < p.num_tiles; tile += gridDim.x, ++t, turn = turn + 1 == groups ? 0 : turn + 1) {
+            if (turn != group) continue;  // another group of epilogue warps takes this tile
             const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
             const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
             const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
             const int ow = tw * p.TW + pw, oh = th * p.TH + ph, n = tn * p.TN + pn, f0 = tf * bn;
             const bool valid = ow < p.OW && oh < p.OH && n < p.N;
-            if ((t & 1) != group) continue;  // the other group of epilogue warps takes this tile
             const int buf = t % nbuf;
             const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
             if (!(ok = mbar_wait<false>(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT, pwe))) break;
@@ -320,9 +333,18 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
             for (int c0 = 0; c0 < bn; c0 += 32) {
                 uint32_t acc[32];
-                const long long tq0 = p.debug ? clock64() : 0;
+                const long long tq0 = kRoleTiming && p.debug ? clock64() : 0;
                 tmem_ld_32x32(taddr0 + (uint32_t)c0, acc);
                 const bool fast = KIND == LN_KIND_I8 && p.out_kind == LN_OUT_Q && f0 + c0 + 32 <= p.F;
+                // where this chunk goes: with pixel-group packing the columns [j * f_real, (j + 1) * f_real) are the filters of the
+                // j-th pixel of the row's group (f_real is a multiple of 32 then, so a chunk never straddles two pixels)
+                int64_t opix = pix;
+                int fo = f0 + c0;
+                if (p.pack > 1) {
+                    int j = 0;
+                    while (fo >= p.f_real) { fo -= p.f_real; ++j; }
+                    opix = pix * p.pack + j;
+                }
                 if (fast) {
                     // ---- fast path: 32 valid filters, int8 out.  The {mult, bias} pairs (two per 16-byte load) are fetched
                     // while the TMEM load is in flight, so the arithmetic below runs from registers only.
@@ -337,8 +359,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                         r1 = __ldg(rp + 1);
                     }
                     tmem_ld_wait();
-                    const long long tq1 = p.debug ? clock64() : 0;
-                    if (p.debug) dbg_ld += tq1 - tq0;
+                    const long long tq1 = kRoleTiming && p.debug ? clock64() : 0;
+                    if (kRoleTiming && p.debug) dbg_ld += tq1 - tq0;
                     if (!valid) continue;
                     uint32_t packed[8];
                     // int32 -> f32.  When every accumulator is known to stay below 2^22, adding it to the bits of 1.5*2^23
@@ -391,11 +413,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                             packed[j] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
                         }
                     }
-                    const long long tq2 = p.debug ? clock64() : 0;
-                    uint4* o = (uint4*)((uint8_t*)p.out + pix * p.out_pixel_stride + f0 + c0);
+                    const long long tq2 = kRoleTiming && p.debug ? clock64() : 0;
+                    uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
                     o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    if (p.debug) { dbg_math += tq2 - tq1; dbg_st += clock64() - tq2; }
+                    if (kRoleTiming && p.debug) { dbg_math += tq2 - tq1; dbg_st += clock64() - tq2; }
                     continue;
                 }
                 tmem_ld_wait();
@@ -451,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                             packed[j] = lo | (hi << 16);
                         }
                     }
-                    uint4* o = (uint4*)((uint8_t*)p.out + pix * p.out_pixel_stride + f0 + c0);
+                    uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
                     o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 }
@@ -516,6 +538,21 @@ __global__ void make_mb_kernel(const float* __restrict__ wscale, const float* __
     mb[f] = f < F ? make_float2(__fmul_rn(x_scale, wscale[f]), bias[f]) : make_float2(0.0f, 0.0f);
 }
 
+// Block-diagonal weights of a pixel-group-packed 1x1 convolution: row j * F + f holds filter f in bytes [j * cpad, (j + 1) * cpad)
+// of a 128-byte row and zeros elsewhere, so that one 128-byte activation row (pack = 128 / cpad consecutive pixels)
+// yields the outputs of all its pixels.  mb2[j * F + f] = mb[f].
+__global__ void pack_group_weights_kernel(const uint8_t* __restrict__ w, int cpad, int F, int pack, int fpad2, uint8_t* __restrict__ w2,
+                                          const float2* __restrict__ mb, float2* __restrict__ mb2) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 4 bytes of w2
+    if (i >= fpad2 * 32) return;
+    const int row = i >> 5, b = (i & 31) * 4;
+    const int j = row / F, f = row - j * F;
+    uint32_t v = 0;
+    if (j < pack && b >= j * cpad && b < (j + 1) * cpad) v = *reinterpret_cast<const uint32_t*>(w + (size_t)f * cpad + (b - j * cpad));
+    *reinterpret_cast<uint32_t*>(w2 + (size_t)row * 128 + b) = v;
+    if ((i & 31) == 0) mb2[row] = j < pack ? mb[f] : make_float2(0.0f, 0.0f);
+}
+
 int ilog2(int v) {
     int l = 0;
     while ((1 << l) < v) ++l;
@@ -550,9 +587,44 @@ static void choose_box(int OW, int OH, int N, bool wide, int* TW, int* TH, int* 
         }
 }
 
-int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_geom& g) {
+void ln_conv_umma_plan_release(ln_ctx* ctx, ln_conv_umma_plan* plan) {
+    if (plan->aux_w) ln_pool_free(ctx, plan->aux_w, plan->aux_w_bytes);
+    if (plan->aux_mb) ln_pool_free(ctx, plan->aux_mb, plan->aux_mb_bytes);
+    plan->aux_w = nullptr;
+    plan->aux_mb = nullptr;
+}
+
+int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_geom& g_in) {
     ln_conv_umma_params& p = plan->p;
     memset(&p, 0, sizeof p);
+    ln_conv_geom g = g_in;
+    float2* mb = plan->mb;
+    int pack = 1;
+    // Pixel-group packing.  The TMA unit spends about as long on a 32- or 64-byte row as on a 128-byte one, and a 1x1
+    // convolution over a dense NHWC tensor is a plain GEMM over pixels: read `pack` = 128 / C consecutive pixels as one
+    // 128-byte row and multiply by block-diagonal weights (pack x F virtual filters).  The tensor core does `pack` times the
+    // arithmetic, which it has to spare at these sizes; the loads are `pack` times fewer rows.
+    {
+        const int64_t P = (int64_t)g.N * g.H * g.W;
+        const int pk = g.cpad < 128 ? 128 / g.cpad : 1;
+        if (pk > 1 && g.k == 1 && g.stride == 1 && g.pad == 0 && g.x_pixel_stride == g.cpad && P % pk == 0 && g.out_kind == LN_OUT_Q &&
+            g.res == nullptr && g.F % 32 == 0 && pk * g.F <= 256 && (((uintptr_t)g.x) & 127) == 0 && P / pk < (1ll << 30)) {
+            const int F2 = pk * g.F, bn2 = ln_conv_choose_bn(F2), fpad2 = (int)ln_round_up(F2, bn2);
+            plan->aux_w_bytes = (size_t)fpad2 * 128;
+            plan->aux_mb_bytes = (size_t)fpad2 * sizeof(float2);
+            plan->aux_w = ln_pool_alloc(ctx, plan->aux_w_bytes);
+            plan->aux_mb = (float2*)ln_pool_alloc(ctx, plan->aux_mb_bytes);
+            if (!plan->aux_w || !plan->aux_mb) return LN_ERR_CUDA;
+            pack_group_weights_kernel<<<(fpad2 * 32 + 255) / 256, 256, 0, ctx->stream>>>((const uint8_t*)g.w, g.cpad, g.F, pk, fpad2, (uint8_t*)plan->aux_w,
+                                                                                     plan->mb, plan->aux_mb);
+            LN_LAUNCHED(ctx);
+            pack = pk;
+            g.w = plan->aux_w; g.fpad = fpad2; g.F = F2;
+            g.cpad = 128; g.C = 128; g.x_pixel_stride = 128;
+            g.W = (int)(P / pk); g.H = 1; g.N = 1; g.OW = g.W; g.OH = 1;
+            mb = plan->aux_mb;
+        }
+    }
     if (!ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H))
         return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported geometry (cpad %d k %d stride %d)", g.cpad, g.k, g.stride);
     if (((uintptr_t)g.x & 15) || (g.x_pixel_stride & 15) || ((uintptr_t)g.w & 15))
@@ -569,6 +641,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.fpad_used = (int)ln_round_up(g.F, 32);
     p.nbuf = 512 / bn > kMaxAccBufs ? kMaxAccBufs : 512 / bn;
     p.small_acc = g.small_acc ? 1 : 0;
+    p.pack = pack; p.f_real = g_in.F;
     choose_box(g.OW, g.OH, g.N, g.out_kind != LN_OUT_Q, &p.TW, &p.TH, &p.TN);
     p.log_tw = ilog2(p.TW); p.log_th = ilog2(p.TH);
     p.tiles_w = (g.OW + p.TW - 1) / p.TW;
@@ -586,7 +659,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: a fused shortcut needs int8 output, filters a multiple of 32 and 16-byte aligned residuals");
     p.status = ctx->d_status;
     p.debug = ctx->debug_cycles;
-    p.mb = plan->mb;
+    p.mb = mb;
 
     const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)bn * bk;  // all weights of one filter tile
     p.b_resident = (p.tiles_f == 1 && b_total <= 96u * 1024u) ? 1 : 0;

@@ -383,8 +383,10 @@ void release_graph(ln_net* net) {
 void release_plan(ln_net* net) {
     ln_ctx* ctx = net->ctx;
     release_graph(net);
-    for (auto& s : net->steps)
+    for (auto& s : net->steps) {
         if (s.mb) ln_pool_free(ctx, s.mb, (size_t)net->layers[s.layer].wq->fpad * sizeof(float2));
+        ln_conv_umma_plan_release(ctx, &s.umma);
+    }
     net->steps.clear();
     for (auto& b : net->buffers) ln_pool_free(ctx, b.first, b.second);
     net->buffers.clear();

@@ -814,6 +814,7 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
             rc = ln_conv_umma_plan_build(ctx, &plan, g);
             if (rc == LN_OK) rc = ln_conv_umma_launch(ctx, &plan);
             if (rc == LN_OK) rc = ln_check_status(ctx, "ln_conv2d_bias_act_q");
+            ln_conv_umma_plan_release(ctx, &plan);
         } else {
             rc = ln_conv_simt_launch(ctx, g, nullptr, mb);
         }

@@ -119,6 +119,10 @@ Q8_CASES = [  # (n, c, h, w, f, k, stride, pad): BASELINE config-2 layer shapes 
     (1, 16, 20, 20, 32, 3, 1, 1),      # channels padded 16 -> 32
     (4, 64, 96, 96, 512, 1, 1, 0),     # several tiles per CTA with two accumulator buffers (256-filter tiles)
     (6, 32, 120, 120, 64, 3, 1, 1),    # several tiles per CTA with eight accumulator buffers, weights resident
+    (3, 64, 40, 40, 64, 1, 1, 0),      # 1x1 over 64 channels: two pixels per 128-byte row
+    (2, 32, 36, 36, 64, 1, 1, 0),      # 1x1 over 32 channels: four pixels per row, 256 virtual filters
+    (1, 64, 7, 5, 64, 1, 1, 0),        # odd pixel count: not packed
+    (5, 64, 152, 152, 128, 1, 1, 0),   # packed, many tiles per CTA
 ]
 
 
