@@ -24,6 +24,11 @@ NVCC_FLAGS = [
 ]
 
 
+# extra compiler flags from the environment, e.g. LN_NVCC_EXTRA=-DLN_CONV_ROLE_TIMING to compile the role clocks of the
+# tensor-core convolution in (read back with ln_ctx_debug_cycles when LN_DEBUG_CYCLES is set)
+NVCC_FLAGS += os.environ.get("LN_NVCC_EXTRA", "").split()
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):

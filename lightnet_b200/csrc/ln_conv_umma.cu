@@ -246,22 +246,26 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                 const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
                 const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
                 const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn;
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
-                    const int r = tap / p.S, s = tap - r * p.S;
-                    int ty = r - p.pad, tx = s - p.pad, map = 0;
-                    if (p.stride == 2) {
-                        const int py = ty & 1, px = tx & 1;  // parity class of the tap (two's complement & 1 is non-negative)
-                        ty = (ty - py) >> 1;
-                        tx = (tx - px) >> 1;
-                        map = py * 2 + px;
+                // taps and channel blocks in nested loops: no division on this single thread's critical path
+                int wcol = 0;  // first column of the k-block in the weight matrix: tap * cpad + c0
+                for (int r = 0; ok && r < p.R; ++r) {
+                    for (int s = 0; ok && s < p.S; ++s) {
+                        int ty = r - p.pad, tx = s - p.pad, map = 0;
+                        if (p.stride == 2) {
+                            const int py = ty & 1, px = tx & 1;  // parity class of the tap (two's complement & 1 is non-negative)
+                            ty = (ty - py) >> 1;
+                            tx = (tx - px) >> 1;
+                            map = py * 2 + px;
+                        }
+                        for (int c0 = 0; c0 < p.cpad; c0 += bk, wcol += bk) {
+                            if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
+                            const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
+                            mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
+                            tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(stage));
+                            if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, wcol, f0, full_bar(stage));
+                            if (++stage == stages) { stage = 0; phase ^= 1u; }
+                        }
                     }
-                    if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
-                    const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
-                    mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
-                    tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(stage));
-                    if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, tap * p.cpad + c0, f0, full_bar(stage));
-                    if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
@@ -662,9 +666,11 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.mb = mb;
 
     const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)bn * bk;  // all weights of one filter tile
-    p.b_resident = (p.tiles_f == 1 && b_total <= 96u * 1024u) ? 1 : 0;
+    // weights stay in shared memory when there is a single filter tile and they leave room for at least four activation stages
+    const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u;
+    p.b_resident = (p.tiles_f == 1 && b_total + 4u * 128u * bk <= smem_budget) ? 1 : 0;
     const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + bn) * bk;
-    int stages = (int)((200 * 1024 - (p.b_resident ? b_total : 0u)) / stage_bytes);
+    int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u) - (p.b_resident ? b_total : 0u)) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
     p.stages = stages;
