@@ -38,6 +38,10 @@ struct ln_conv_umma_params {
     // Pixel-group packing of 1x1 convolutions with few channels (pack > 1): an accumulator row is `pack` consecutive pixels,
     // its column j * f_real + f is filter f of the j-th of them (see ln_conv_umma_plan_build).
     int pack, f_real;
+    // Row-shifted boxes for 3x3 stride-1 convolutions (halo = 1): per channel block the producer loads three boxes of
+    // TW x (TH + 2) pixels, shifted by 0, 1, 2 pixels in x; the tap (r, s) reads box s from row r on.  a_stages such sets
+    // are in flight; the weight tiles have their own ring (`stages`) unless they are resident.
+    int halo, a_stages, box_bytes;
     int* status;
     long long* debug;  // optional: role timing of CTA 0 (32 counters), null = off
 };

@@ -18,6 +18,9 @@
 // roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "ln_conv_plan.h"
 
 namespace {
@@ -184,8 +187,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     const uint32_t a_bytes = 128u * bk, b_bytes = (uint32_t)bn * bk, stage_bytes = b_res ? a_bytes : a_bytes + b_bytes;
     const uint32_t bres_base = smem_base;  // resident weights first (kblocks * b_bytes), then the ring
     const uint32_t ring_base = smem_base + (b_res ? (uint32_t)(p.R * p.S * p.cblocks) * b_bytes : 0u);
-    const uint32_t bar_base = ring_base + (uint32_t)stages * stage_bytes;
-    // barrier block: full[8] empty[8] tfull[8] tempty[8] | tmem slot | abort flag
+    // Row-shifted-box mode (3x3, stride 1): the activation ring holds a_stages sets of three boxes, the weight tiles follow in
+    // a ring of their own (none when they are resident).
+    const bool halo = p.halo != 0;
+    const uint32_t box_bytes = (uint32_t)p.box_bytes;
+    const uint32_t bring_base = ring_base + (uint32_t)p.a_stages * box_bytes;
+    const uint32_t bar_base = halo ? bring_base + (b_res ? 0u : (uint32_t)stages * b_bytes) : ring_base + (uint32_t)stages * stage_bytes;
+    // barrier block: full[8] empty[8] tfull[8] tempty[8] | resident weights | tmem slot | abort flag | afull[8] aempty[8]
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
@@ -194,6 +202,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(generic_base + (bar_base - smem_base) + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 1));
     const uint32_t bres_bar = bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 2);
+    auto afull_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 4 + s); };
+    auto aempty_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 4 + kMaxStages + s); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t tmem_cols = 512u;  // the CTA owns the SM: take all of TMEM and keep 512/BN (at most 8) accumulator tiles in flight
@@ -209,6 +219,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             mbar_init(tempty_bar(b), 4);  // the four warps of the group that drained the buffer
         }
         mbar_init(bres_bar, 1);
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(afull_bar(s), 1);
+            mbar_init(aempty_bar(s), 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -241,11 +255,31 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     tma_load_2d(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, 0, bres_bar);
                 }
             }
+            int astage = 0;
+            uint32_t aphase = 0;
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
                 const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
                 const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
                 const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
                 const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn;
+                if (halo) {
+                    // per channel block: box s, then (unless the weights are resident) the weight tiles of the taps that read it
+                    for (int c0 = 0; ok && c0 < p.cpad; c0 += bk)
+                        for (int s = 0; ok && s < 3; ++s) {
+                            if (!(ok = mbar_wait(aempty_bar(astage), aphase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
+                            mbar_arrive_expect_tx(afull_bar(astage), box_bytes);
+                            tma_load_4d(ring_base + (uint32_t)astage * box_bytes, &p.tmA[0], c0, ow0 - p.pad + s, oh0 - p.pad, n0, afull_bar(astage));
+                            if (++astage == p.a_stages) { astage = 0; aphase ^= 1u; }
+                            if (b_res) continue;
+                            for (int r = 0; r < 3; ++r) {
+                                if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
+                                mbar_arrive_expect_tx(full_bar(stage), b_bytes);
+                                tma_load_2d(bring_base + (uint32_t)stage * b_bytes, &p.tmB, (r * 3 + s) * p.cpad + c0, f0, full_bar(stage));
+                                if (++stage == stages) { stage = 0; phase ^= 1u; }
+                            }
+                        }
+                    continue;
+                }
                 // taps and channel blocks in nested loops: no division on this single thread's critical path
                 int wcol = 0;  // first column of the k-block in the weight matrix: tap * cpad + c0
                 for (int r = 0; ok && r < p.R; ++r) {
@@ -275,8 +309,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         if (lane == 0) {
             const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((uint32_t)(bn >> 3) << 17) |
                                    ((128u >> 4) << 24);
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, astage = 0;
+            uint32_t phase = 0, aphase = 0;
             int t = 0;
             bool ok = true;
             long long w_tempty = 0, w_full = 0;
@@ -290,6 +324,40 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                 if (!(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw1))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
+                if (halo) {
+                    uint32_t accumulate = 0;
+                    for (int cb = 0; ok && cb < p.cblocks; ++cb)
+                        for (int s = 0; ok && s < 3; ++s) {
+                            if (!(ok = mbar_wait(afull_bar(astage), aphase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                            tc_fence_after();
+                            const uint32_t sa = ring_base + (uint32_t)astage * box_bytes;
+                            for (int r = 0; r < 3; ++r) {
+                                uint32_t sb;
+                                if (b_res) sb = bres_base + (uint32_t)((r * 3 + s) * p.cblocks + cb) * b_bytes;
+                                else {
+                                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                                    tc_fence_after();
+                                    sb = bring_base + (uint32_t)stage * b_bytes;
+                                }
+                                // the box from its row r on: 128 consecutive rows of bk bytes, aligned to the 8-row swizzle pattern
+                                const uint64_t a_desc = make_smem_desc(sa + (uint32_t)(r * p.TW * bk), bk), b_desc = make_smem_desc(sb, bk);
+                                for (int k = 0; k < bk / 32; ++k) {
+                                    tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accumulate);
+                                    accumulate = 1u;
+                                }
+                                if (!b_res) {
+                                    tc_commit(empty_bar(stage));
+                                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                                }
+                            }
+                            if (!ok) break;
+                            tc_commit(aempty_bar(astage));  // arrives when the MMAs above have finished reading the box
+                            if (++astage == p.a_stages) { astage = 0; aphase ^= 1u; }
+                        }
+                    if (!ok) break;
+                    tc_commit(tfull_bar(buf));
+                    continue;
+                }
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
                     tc_fence_after();
@@ -604,6 +672,9 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     ln_conv_geom g = g_in;
     float2* mb = plan->mb;
     int pack = 1;
+    // LN_CONV_DISABLE=pack,halo switches the two layout modes off (for A/B measurements)
+    const char* disable = getenv("LN_CONV_DISABLE");
+    const bool allow_pack = !(disable && strstr(disable, "pack")), allow_halo = !(disable && strstr(disable, "halo"));
     // Pixel-group packing.  The TMA unit spends about as long on a 32- or 64-byte row as on a 128-byte one, and a 1x1
     // convolution over a dense NHWC tensor is a plain GEMM over pixels: read `pack` = 128 / C consecutive pixels as one
     // 128-byte row and multiply by block-diagonal weights (pack x F virtual filters).  The tensor core does `pack` times the
@@ -611,7 +682,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     {
         const int64_t P = (int64_t)g.N * g.H * g.W;
         const int pk = g.cpad < 128 ? 128 / g.cpad : 1;
-        if (pk > 1 && g.k == 1 && g.stride == 1 && g.pad == 0 && g.x_pixel_stride == g.cpad && P % pk == 0 && g.out_kind == LN_OUT_Q &&
+        if (allow_pack && pk > 1 && g.k == 1 && g.stride == 1 && g.pad == 0 && g.x_pixel_stride == g.cpad && P % pk == 0 && g.out_kind == LN_OUT_Q &&
             g.res == nullptr && g.F % 32 == 0 && pk * g.F <= 256 && (((uintptr_t)g.x) & 127) == 0 && P / pk < (1ll << 30)) {
             const int F2 = pk * g.F, bn2 = ln_conv_choose_bn(F2), fpad2 = (int)ln_round_up(F2, bn2);
             plan->aux_w_bytes = (size_t)fpad2 * 128;
@@ -647,6 +718,32 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.small_acc = g.small_acc ? 1 : 0;
     p.pack = pack; p.f_real = g_in.F;
     choose_box(g.OW, g.OH, g.N, g.out_kind != LN_OUT_Q, &p.TW, &p.TH, &p.TN);
+    // Row-shifted boxes for 3x3 stride-1 layers.  The nine taps of a tile read overlapping windows of the same input patch; one
+    // box per tap re-reads that patch nine times from L2, which is what bounds these layers (the TMA unit's row rate for few
+    // channels, L2 bandwidth for many).  Three boxes of TW x (TH + 2) pixels, shifted by 0 / 1 / 2 pixels in x, hold every
+    // tap's operand as 128 consecutive rows starting at row r of box s -- still aligned to the 8-row swizzle pattern because TW
+    // is a multiple of 8 -- so a tile and channel block costs 3 loads instead of 9.  The tile has to be TW x TH pixels of one
+    // image; the mode is used when that shape wastes at most 15 % of the rows, and only for layers of at most 64 channels:
+    // measured, it gains 10 % there and loses with 128 and more (the larger boxes complete later than per-tap boxes do).
+    const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u;
+    if (allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
+        int best_tw = 0, best_th = 0;
+        int64_t best_tiles = -1;
+        for (int lw = 3; lw <= 7; ++lw) {
+            const int tw = 1 << lw, th = 128 >> lw;
+            const int64_t tiles = (int64_t)((g.OW + tw - 1) / tw) * ((g.OH + th - 1) / th);
+            if (best_tiles < 0 || tiles < best_tiles) { best_tiles = tiles; best_tw = tw; best_th = th; }
+        }
+        const uint32_t box_bytes = (uint32_t)(best_th + 2) * best_tw * bk;
+        const uint32_t b_all = (uint32_t)(9 * (g.cpad / bk)) * (uint32_t)bn * bk;
+        const bool one_ftile = ln_round_up(g.F, bn) / bn == 1;
+        const bool resident = one_ftile && b_all + 4u * box_bytes <= smem_budget;      // resident weights + at least four boxes
+        const bool ring_fits = 4u * box_bytes + 4u * (uint32_t)bn * bk <= smem_budget;  // four boxes + four weight tiles
+        if (best_tiles * 128 * 100 <= (int64_t)g.OW * g.OH * 115 && (resident || ring_fits)) {
+            p.halo = 1; p.box_bytes = (int)box_bytes;
+            p.TW = best_tw; p.TH = best_th; p.TN = 1;
+        }
+    }
     p.log_tw = ilog2(p.TW); p.log_th = ilog2(p.TH);
     p.tiles_w = (g.OW + p.TW - 1) / p.TW;
     p.tiles_h = (g.OH + p.TH - 1) / p.TH;
@@ -667,7 +764,26 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
 
     const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)bn * bk;  // all weights of one filter tile
     // weights stay in shared memory when there is a single filter tile and they leave room for at least four activation stages
-    const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u;
+    if (p.halo) {
+        const uint32_t box = (uint32_t)p.box_bytes, b_bytes = (uint32_t)bn * bk;
+        p.b_resident = (p.tiles_f == 1 && b_total + 4u * box <= smem_budget) ? 1 : 0;
+        int a_stages, stages;
+        if (p.b_resident) {
+            a_stages = (int)((smem_budget - b_total) / box);
+            stages = 1;
+        } else {
+            // split what is left between boxes and weight tiles, three weight tiles per box (one box serves three taps)
+            a_stages = (int)(smem_budget / (box + 3u * b_bytes));
+            if (a_stages < 4) a_stages = 4;
+            if (a_stages > kMaxStages) a_stages = kMaxStages;
+            stages = (int)((smem_budget - (uint32_t)a_stages * box) / b_bytes);
+        }
+        if (a_stages > kMaxStages) a_stages = kMaxStages;
+        if (stages > kMaxStages) stages = kMaxStages;
+        p.a_stages = a_stages;
+        p.stages = stages;
+        plan->smem = (size_t)a_stages * box + (p.b_resident ? b_total : (size_t)stages * b_bytes) + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    } else {
     p.b_resident = (p.tiles_f == 1 && b_total + 4u * 128u * bk <= smem_budget) ? 1 : 0;
     const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + bn) * bk;
     int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u) - (p.b_resident ? b_total : 0u)) / stage_bytes);
@@ -675,6 +791,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
     p.stages = stages;
     plan->smem = (size_t)stages * stage_bytes + (p.b_resident ? b_total : 0u) + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    }
     plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     plan->kind = g.kind;
 
@@ -689,7 +806,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         cuuint64_t dims[4] = {(cuuint64_t)g.cpad, (cuuint64_t)Wm, (cuuint64_t)Hm, (cuuint64_t)g.N};
         cuuint64_t strides[3] = {(cuuint64_t)g.stride * g.x_pixel_stride, (cuuint64_t)g.stride * g.W * g.x_pixel_stride,
                                  (cuuint64_t)g.H * g.W * g.x_pixel_stride};
-        cuuint32_t box[4] = {(cuuint32_t)bk, (cuuint32_t)p.TW, (cuuint32_t)p.TH, (cuuint32_t)p.TN};
+        cuuint32_t box[4] = {(cuuint32_t)bk, (cuuint32_t)p.TW, (cuuint32_t)(p.halo ? p.TH + 2 : p.TH), (cuuint32_t)p.TN};
         cuuint32_t estr[4] = {1, 1, 1, 1};
         void* base = (uint8_t*)g.x + ((int64_t)py * g.W + px) * g.x_pixel_stride;
         CUresult r = ctx->encode_tiled(&p.tmA[m], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base, dims, strides, box, estr,

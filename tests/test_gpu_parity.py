@@ -123,6 +123,9 @@ Q8_CASES = [  # (n, c, h, w, f, k, stride, pad): BASELINE config-2 layer shapes 
     (2, 32, 36, 36, 64, 1, 1, 0),      # 1x1 over 32 channels: four pixels per row, 256 virtual filters
     (1, 64, 7, 5, 64, 1, 1, 0),        # odd pixel count: not packed
     (5, 64, 152, 152, 128, 1, 1, 0),   # packed, many tiles per CTA
+    (2, 128, 76, 76, 128, 3, 1, 1),    # 128-byte rows, resident weights of 147 KB
+    (2, 64, 152, 152, 64, 3, 1, 1),    # row-shifted boxes, 64-byte rows, weights resident
+    (1, 64, 80, 72, 512, 3, 1, 1),     # row-shifted boxes, weight tiles in their own ring
 ]
 
 
@@ -632,6 +635,8 @@ F8_CASES = [  # (n, c, h, w, f, k, stride, pad)
     (3, 32, 19, 19, 64, 3, 1, 1),
     (2, 64, 20, 20, 255, 1, 1, 0),
     (1, 16, 20, 20, 32, 3, 1, 1),
+    (1, 64, 64, 64, 64, 3, 1, 1),      # row-shifted boxes
+    (1, 64, 48, 80, 512, 3, 1, 1),     # row-shifted boxes, weight ring
 ]
 
 # Accumulation-order tolerance of an f32 tensor-core accumulator against the oracle's double sum:
@@ -670,8 +675,9 @@ def test_f8_conv_matches_oracle(be, case):
         be.set_exact_epilogue(True)
         q, _ = be.download_q(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, act_name, float(sy), ln.LN_OUT_Q))
         assert np.array_equal(q, q_ref), act_name
+        # the f32 (head) output may tile the layer differently and so accumulate in another order: a few ulp of the accumulator
         head = be.download_f32(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, act_name, 1.0, ln.LN_OUT_F32))
-        assert np.array_equal(head, a_ref), act_name
+        assert np.abs(head - a_ref).max() <= 1e-5 * np.abs(a_ref).max(), act_name
         be.set_exact_epilogue(False)
         q, _ = be.download_q(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, act_name, float(sy), ln.LN_OUT_Q))
         # fast epilogue: at most one E4M3 step away (codes of one sign are ordered like their values)
