@@ -40,7 +40,10 @@ WORKLOADS = {
     "yolov7-640-fp8": dict(model="yolov7", size=640, batch=32, precision="fp8",
                            metric="images/sec YOLOv7-640 FP8 E4M3 (conv stack + yolo decode + NMS)"),
     "nms-stress": dict(model=None, size=640, batch=256, precision="f32", metric="decode + NMS GB/s (25200 candidates x 80 classes per image)"),
+    "conv-sweep": dict(model=None, size=0, batch=16, precision="int8+fp8", metric="TOP/s single-layer implicit-GEMM convolution (bias + leaky epilogue)"),
 }
+# (channels, height, width, filters, kernel, stride, pad) of the single-layer sweep
+SWEEP_LAYERS = [(256, 52, 52, 512, 3, 1, 1), (512, 52, 52, 256, 1, 1, 0), (128, 104, 104, 256, 3, 2, 1)]
 STRESS_THR, STRESS_NMS, STRESS_TOPK = 0.001, 0.65, 300
 
 
@@ -160,6 +163,9 @@ def run_reference(args, rank):
     wl = WORKLOADS[args.workload]
     steps = max(1, min(args.steps, 2))
     total, note = 0.0, ""
+    if args.workload == "conv-sweep":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference has no int8 / FP8 convolution; the sweep has no CPU arm"}))
+        return
     for _ in range(steps):
         if wl["model"] is None:
             dt, note = cpu_stress_sample(1)
@@ -225,6 +231,66 @@ def make_timer(stream, world):
         return float(ms.item())
 
     return timed
+
+
+def run_conv_sweep(args, be, rank, world, local_rank):
+    """Single layers through the operator-level entry point (ln_conv2d_bias_act_q): weights N(0, 0.02), activations
+    leaky(N(0, 1)), bias + leaky epilogue, int8 and FP8.  The operands of one layer fit in L2, so a 512 MB buffer is
+    rewritten between timed launches; each launch is timed on its own with CUDA events on the ctx stream."""
+    import torch
+
+    import lightnet_b200 as ln
+
+    N = args.batch
+    flush = be.zeros_f32((1, 1, 8192, 16384))     # 512 MB
+    rng = np.random.default_rng(3)
+    bf16_tf, _, basis = measured_peaks()
+    peak = 2.0 * bf16_tf
+    rows = []
+    layers = SWEEP_LAYERS if args.layer < 0 else [SWEEP_LAYERS[args.layer]]
+    if args.shape:
+        layers = [tuple(int(v) for v in args.shape.split(","))]
+    kinds = [("int8", ln.LN_Q8, 127.0), ("fp8", ln.LN_F8, 448.0)]
+    if args.precision:
+        kinds = [k for k in kinds if k[0] == args.precision]
+    launches0 = be.launch_count
+    for (c, h, w, f, k, st, p) in layers:
+        wt = rng.normal(0, 0.02, (f, c, k, k)).astype(np.float32)
+        act = rng.normal(0, 1, (N, c, h, w)).astype(np.float32)
+        act = np.where(act > 0, act, np.float32(0.1) * act).astype(np.float32)
+        bias = rng.normal(0, 0.05, f).astype(np.float32)
+        oh, ow = (h + 2 * p - k) // st + 1, (w + 2 * p - k) // st + 1
+        for name, dt, qmax in kinds:
+            tw = be.upload_f32(wt.shape, wt)
+            wq = be.conv_weights_q(tw, f, c, k, dt)
+            tx = be.upload_q(act.shape, act, float(np.abs(act).max() / qmax), dt)
+            tb = be.upload_f32((1, f, 1, 1), bias)
+            run = lambda: be.conv2d_bias_act_q(tx, wq, tb, (N, f, oh, ow), c, h, w, f, k, st, st, 1, p, 1, args.activation, 4.0 / qmax, ln.LN_OUT_Q)
+            for _ in range(max(args.warmup, 3)):
+                run()
+            ms = []
+            be.set_kernel_timing(True)
+            for _ in range(args.steps):
+                be.activation_f32(flush, "linear")      # rewrites 512 MB: nothing of the layer is left in L2
+                run()
+                ms.append(be.last_kernel_ms())           # CUDA events around the convolution kernel, on the ctx stream
+            be.set_kernel_timing(False)
+            t = float(np.median(ms))
+            ops = 2.0 * N * oh * ow * f * c * k * k
+            rows.append({"layer": "%dx%d s%d C%d->K%d at %dx%d" % (k, k, st, c, f, h, w), "precision": name, "ms": t,
+                         "tops": ops / t / 1e9, "frac_of_peak": ops / t / 1e9 / peak})
+    launches = be.launch_count - launches0
+    if rank == 0:
+        best = max(rows, key=lambda r: r["tops"])
+        print(json.dumps({
+            "metric": WORKLOADS["conv-sweep"]["metric"], "value": best["tops"], "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8+fp8", "data": "synthetic",
+            "config": {"workload": "single-layer conv sweep, N=%d, weights N(0,0.02), activations leaky(N(0,1)), bias + %s epilogue" % (N, args.activation),
+                       "l2": "512 MB rewritten between timed launches", "timing": "median of per-launch CUDA-event times of the convolution kernel (ln_ctx_set_kernel_timing)"},
+            "layers": rows, "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel", "achieved": best["tops"], "peak": peak, "unit": "TOP/s",
+                         "frac": best["tops"] / peak, "traffic": None, "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf)}}))
 
 
 def run_nms_stress(args, be, rank, world, local_rank):
@@ -295,6 +361,10 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="images per GPU per step (0 = the workload's own: 64 / 32 / 256)")
     ap.add_argument("--micro-batch", type=int, default=0, help="images per pass through the layers; 0 (default, fastest) = the whole batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer", type=int, default=-1, help="conv-sweep: index of the one layer to run (default all)")
+    ap.add_argument("--precision", default="", choices=["", "int8", "fp8"], help="conv-sweep: one precision only")
+    ap.add_argument("--shape", default="", help="conv-sweep: one layer C,H,W,K,k,stride,pad instead of the three of the sweep")
+    ap.add_argument("--activation", default="leaky", help="conv-sweep: epilogue activation (leaky, mish, swish, relu, linear, logistic)")
     ap.add_argument("--width", type=int, default=0)
     ap.add_argument("--height", type=int, default=0)
     args = ap.parse_args()
@@ -322,7 +392,7 @@ def main():
     B = args.batch
     be = ln.B200Backend(local_rank)
     if wl["model"] is None:
-        run_nms_stress(args, be, rank, world, local_rank)
+        (run_conv_sweep if args.workload == "conv-sweep" else run_nms_stress)(args, be, rank, world, local_rank)
         if world > 1:
             dist.destroy_process_group()
         return

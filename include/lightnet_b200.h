@@ -74,6 +74,10 @@ int32_t ln_ctx_set_exact_epilogue(ln_ctx* ctx, int32_t on);
    compact pool the NMS selection works in.  0 (default) = automatic.  A small pool costs extra passes over the head
    tensors when very many candidates tie; the records do not depend on it. */
 int32_t ln_ctx_set_nms_pool_entries(ln_ctx* ctx, int64_t entries);
+/* Measurement aid (no counterpart in the reference): while on, ln_conv2d_bias_act_q brackets its convolution kernel with
+   CUDA events on the ctx stream; ln_ctx_last_kernel_ms returns the duration of the most recent one. */
+int32_t ln_ctx_set_kernel_timing(ln_ctx* ctx, int32_t on);
+int32_t ln_ctx_last_kernel_ms(ln_ctx* ctx, float* ms);
 /* Number of kernels this library has launched on the ctx since creation. */
 int64_t ln_ctx_launch_count(ln_ctx* ctx);
 

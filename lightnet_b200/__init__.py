@@ -56,6 +56,8 @@ SYMBOLS = {
     "ln_ctx_stream": (C.c_void_p, [_VP]),
     "ln_ctx_set_exact_epilogue": (C.c_int32, [_VP, C.c_int32]),
     "ln_ctx_set_nms_pool_entries": (C.c_int32, [_VP, C.c_int64]),
+    "ln_ctx_set_kernel_timing": (C.c_int32, [_VP, C.c_int32]),
+    "ln_ctx_last_kernel_ms": (C.c_int32, [_VP, C.POINTER(C.c_float)]),
     "ln_ctx_launch_count": (C.c_int64, [_VP]),
     "ln_tensor_upload_f32": (C.c_int32, [_VP, _I64P, _VP, _PP]),
     "ln_tensor_zeros_f32": (C.c_int32, [_VP, _I64P, _PP]),
@@ -227,6 +229,14 @@ class B200Backend:
 
     def set_exact_epilogue(self, on: bool):
         self._check(self.lib.ln_ctx_set_exact_epilogue(self.ctx, int(on)))
+
+    def set_kernel_timing(self, on: bool):
+        self._check(self.lib.ln_ctx_set_kernel_timing(self.ctx, int(on)))
+
+    def last_kernel_ms(self) -> float:
+        ms = C.c_float()
+        self._check(self.lib.ln_ctx_last_kernel_ms(self.ctx, C.byref(ms)))
+        return float(ms.value)
 
     def set_nms_pool_entries(self, entries: int):
         """Candidates per image the NMS selection pool holds (0 = automatic); results do not depend on it."""

@@ -812,7 +812,9 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
             ln_conv_umma_plan plan;
             plan.mb = mb;
             rc = ln_conv_umma_plan_build(ctx, &plan, g);
+            if (rc == LN_OK && ctx->time_kernels) cudaEventRecord(ctx->ev_k0, ctx->stream);
             if (rc == LN_OK) rc = ln_conv_umma_launch(ctx, &plan);
+            if (rc == LN_OK && ctx->time_kernels) { cudaEventRecord(ctx->ev_k1, ctx->stream); ctx->ev_pending = true; }
             if (rc == LN_OK) rc = ln_check_status(ctx, "ln_conv2d_bias_act_q");
             ln_conv_umma_plan_release(ctx, &plan);
         } else {

@@ -161,6 +161,26 @@ int32_t ln_ctx_set_exact_epilogue(ln_ctx* ctx, int32_t on) {
 
 int64_t ln_ctx_launch_count(ln_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+int32_t ln_ctx_set_kernel_timing(ln_ctx* ctx, int32_t on) {
+    if (!ctx) return LN_ERR_ARG;
+    cudaSetDevice(ctx->device);
+    if (on && !ctx->ev_k0) {
+        LN_CUDA(ctx, cudaEventCreate(&ctx->ev_k0));
+        LN_CUDA(ctx, cudaEventCreate(&ctx->ev_k1));
+    }
+    ctx->time_kernels = on != 0;
+    ctx->ev_pending = false;
+    return LN_OK;
+}
+
+int32_t ln_ctx_last_kernel_ms(ln_ctx* ctx, float* ms) {
+    if (!ctx || !ms) return ln_fail(ctx, LN_ERR_ARG, "ln_ctx_last_kernel_ms: NULL argument");
+    if (!ctx->ev_pending) return ln_fail(ctx, LN_ERR_ARG, "ln_ctx_last_kernel_ms: no kernel has been timed since timing was switched on");
+    LN_CUDA(ctx, cudaEventSynchronize(ctx->ev_k1));
+    LN_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_k0, ctx->ev_k1));
+    return LN_OK;
+}
+
 int32_t ln_tensor_upload_f32(ln_ctx* ctx, const int64_t shape[4], const float* host, ln_tensor** out) {
     if (!ctx || !shape || !host || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_tensor_upload_f32: NULL argument");
     cudaSetDevice(ctx->device);
