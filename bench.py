@@ -47,6 +47,24 @@ SWEEP_LAYERS = [(256, 52, 52, 512, 3, 1, 1), (512, 52, 52, 256, 1, 1, 0), (128, 
 STRESS_THR, STRESS_NMS, STRESS_TOPK = 0.001, 0.65, 300
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the 109 tensor-core convolution launches of one step,
+# per image, from an ncu capture of `bench.py --batch 16 --steps 1 --warmup 3 --no-cpu-baseline` (profiles/): 2.437 GB read +
+# 0.411 GB written for 16 images.  At batch 16 much of a layer's output is consumed from L2 and overwritten in the next step
+# before it is ever written back; at batch 64 less is, so scaling this figure by the batch is a lower bound.
+CONV_DRAM_BYTES_PER_IMAGE_B16 = (2436655360 + 410987776) / 16.0
+
+
+def conv_bytes_per_image(layers):
+    """Algorithmic bytes of the tensor-core convolutions: every input and output tensor once (int8; f32 for the heads)."""
+    total = 0
+    for i, l in enumerate(layers):
+        if l["kind"] != "conv" or i == 0:
+            continue
+        head = i + 1 < len(layers) and layers[i + 1]["kind"] == "yolo"
+        total += l["in_w"] * l["in_h"] * l["in_c"] + l["out_w"] * l["out_h"] * l["out_c"] * (4 if head else 1)
+    return total
+
+
 def conv_ops_per_image(layers):
     return sum(2 * l["out_w"] * l["out_h"] * l["out_c"] * l["in_c"] * l["size"] ** 2 for l in layers if l["kind"] == "conv")
 
@@ -456,7 +474,10 @@ def main():
             "gpu_launches": int(launches),
             "phases_ms": {"layers": fwd_ms, "decode_nms": nms_ms},
             "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel (%s implicit GEMM, all layers but the first)" % wl["precision"], "achieved": achieved,
-                         "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak": peak, "unit": "TOP/s", "frac": achieved / peak,
+                         "traffic": CONV_DRAM_BYTES_PER_IMAGE_B16 * B if args.workload == "yolov4-608-int8" else None,
+                         "traffic_basis": "bytes per step over all launches of the kernel: DRAM read + write measured with ncu at batch 16 (178 MB per image), scaled by the batch; a lower bound at batch 64, where less of a layer stays in L2",
+                         "algorithmic_bytes": conv_bytes_per_image(layers) * B,
                          "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf), "launches_per_step": umma_launches,
                          "ms_per_step": umma_ms},
             "kernel_classes_ms": {k: v[0] for k, v in per_op.items()},
