@@ -115,6 +115,7 @@ SYMBOLS = {
     "ln_net_last_times": (C.c_int32, [_VP, _VP]),
     "ln_net_set_profile": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_set_fusion": (C.c_int32, [_VP, C.c_int32]),
+    "ln_net_set_host_pipeline": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_set_cuda_graph": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_profile": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
 }
@@ -514,6 +515,10 @@ class GpuExecutableNetwork:
 
     def set_cuda_graph(self, on: bool):
         self.backend._check(self.lib.ln_net_set_cuda_graph(self.h, int(on)))
+
+    def set_host_pipeline(self, on: bool):
+        """detect() on host buffers uploads and runs the batch in two overlapping halves (default on)."""
+        self.backend._check(self.lib.ln_net_set_host_pipeline(self.h, int(on)))
 
     def set_fusion(self, on: bool):
         self.backend._check(self.lib.ln_net_set_fusion(self.h, int(on)))

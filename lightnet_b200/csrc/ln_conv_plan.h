@@ -29,6 +29,9 @@ struct ln_conv_umma_params {
     int act, out_kind;
     float inv_sy;
     const float2* mb;  // [fpad] {x_scale * w_scale[f], bias[f]}
+    // [fpad] {mult, bias - 1.5 * 2^23 * mult}: lets the fast epilogue apply scale and bias directly to the float whose bits are
+    // 0x4B400000 + accumulator (= 1.5 * 2^23 + accumulator); null when accumulators can exceed 2^22
+    const float2* mb_folded;
     void* out;
     long long out_pixel_stride;  // bytes between pixels of an 8-bit NHWC output
     // fused shortcut (null = none): out = quant((code * s_c + residual_code * s_res) * inv_sy2), code = the convolution's own int8 output
@@ -52,7 +55,8 @@ struct ln_conv_umma_plan {
     // device storage the plan owns when it packs pixel groups: the block-diagonal weight matrix and its {mult, bias} pairs
     void* aux_w = nullptr;
     float2* aux_mb = nullptr;
-    size_t aux_w_bytes = 0, aux_mb_bytes = 0;
+    float2* aux_mbf = nullptr;  // the folded table of mb_folded
+    size_t aux_w_bytes = 0, aux_mb_bytes = 0, aux_mbf_bytes = 0;
     size_t smem = 0;
     int grid = 0;
     int kind = LN_KIND_I8;

@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             uint32_t phase = 0, aphase = 0;
             int t = 0;
             bool ok = true;
-            long long w_tempty = 0, w_full = 0;
+            long long w_tempty = 0, w_full = 0, t_issue = 0, t_commit = 0;
             long long* pw1 = p.debug ? &w_tempty : nullptr;
             long long* pw2 = p.debug ? &w_full : nullptr;
             const long long t_start = kRoleTiming ? clock64() : 0;
@@ -360,18 +360,21 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                 }
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                    const long long ti0 = kRoleTiming && p.debug ? clock64() : 0;
                     tc_fence_after();
                     const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
                     const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + a_bytes, bk);
                     for (int k = 0; k < bk / 32; ++k)  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
                         tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
+                    const long long ti1 = kRoleTiming && p.debug ? clock64() : 0;
                     tc_commit(empty_bar(stage));  // arrives when the MMAs above have finished reading this stage
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
+                    if (kRoleTiming && p.debug) { t_issue += ti1 - ti0; t_commit += clock64() - ti1; }
                 }
                 if (!ok) break;
                 tc_commit(tfull_bar(buf));
             }
-            if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; }
+            if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; p.debug[25] = t_issue; p.debug[26] = t_commit; }
         }
     } else {
         // ------------------------------------------------------------------ epilogue
@@ -420,7 +423,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                 if (fast) {
                     // ---- fast path: 32 valid filters, int8 out.  The {mult, bias} pairs (two per 16-byte load) are fetched
                     // while the TMEM load is in flight, so the arithmetic below runs from registers only.
-                    const float4* mb4 = reinterpret_cast<const float4*>(p.mb + f0 + c0);
+                    const bool folded = !EXACT && p.mb_folded != nullptr;
+                    const float4* mb4 = reinterpret_cast<const float4*>((folded ? p.mb_folded : p.mb) + f0 + c0);
                     float4 m[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) m[j] = ldg_f4_pinned(mb4 + j);
@@ -439,7 +443,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     // converts exactly in two FMA-pipe instructions; otherwise the conversion unit (or, for the
                     // transcendental epilogues that need that unit for ex2/rcp, an exact ALU sequence).
                     float x[32];
-                    if (p.small_acc) {
+                    if (folded) {
+                        // the bias already carries -1.5 * 2^23 * mult: the FMA below removes the offset and applies scale and bias at once
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = __int_as_float(0x4B400000 + (int)acc[j]);
+                    } else if (p.small_acc) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) x[j] = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[j]), -12582912.0f);
                     } else if (kTranscendental) {
@@ -625,6 +633,11 @@ __global__ void pack_group_weights_kernel(const uint8_t* __restrict__ w, int cpa
     if ((i & 31) == 0) mb2[row] = j < pack ? mb[f] : make_float2(0.0f, 0.0f);
 }
 
+__global__ void fold_mb_kernel(const float2* __restrict__ mb, int n, float2* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = make_float2(mb[i].x, __fmaf_rn(-12582912.0f, mb[i].x, mb[i].y));
+}
+
 int ilog2(int v) {
     int l = 0;
     while ((1 << l) < v) ++l;
@@ -662,6 +675,8 @@ static void choose_box(int OW, int OH, int N, bool wide, int* TW, int* TH, int* 
 void ln_conv_umma_plan_release(ln_ctx* ctx, ln_conv_umma_plan* plan) {
     if (plan->aux_w) ln_pool_free(ctx, plan->aux_w, plan->aux_w_bytes);
     if (plan->aux_mb) ln_pool_free(ctx, plan->aux_mb, plan->aux_mb_bytes);
+    if (plan->aux_mbf) ln_pool_free(ctx, plan->aux_mbf, plan->aux_mbf_bytes);
+    plan->aux_mbf = nullptr;
     plan->aux_w = nullptr;
     plan->aux_mb = nullptr;
 }
@@ -761,6 +776,15 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.status = ctx->d_status;
     p.debug = ctx->debug_cycles;
     p.mb = mb;
+    p.mb_folded = nullptr;
+    if (g.kind == LN_KIND_I8 && g.small_acc && g.out_kind == LN_OUT_Q) {
+        plan->aux_mbf_bytes = (size_t)g.fpad * sizeof(float2);
+        plan->aux_mbf = (float2*)ln_pool_alloc(ctx, plan->aux_mbf_bytes);
+        if (!plan->aux_mbf) return LN_ERR_CUDA;
+        fold_mb_kernel<<<(g.fpad + 127) / 128, 128, 0, ctx->stream>>>(mb, g.fpad, plan->aux_mbf);
+        LN_LAUNCHED(ctx);
+        p.mb_folded = plan->aux_mbf;
+    }
 
     const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)bn * bk;  // all weights of one filter tile
     // weights stay in shared memory when there is a single filter tile and they leave room for at least four activation stages

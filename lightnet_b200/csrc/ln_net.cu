@@ -239,6 +239,13 @@ struct ln_net {
     std::vector<std::pair<void*, size_t>> buffers;
     std::vector<QView> views;
     ln_tensor* input_dev = nullptr;    // staging for host inputs
+    // Host-input pipeline of the 8-bit path: two half-batch networks with the same weights and scales; the upload of the
+    // second half overlaps the layers of the first (copy engine + its own stream), each half decodes its own images.
+    std::string cfg_text;
+    bool host_pipeline = true;
+    ln_net* pipe[2] = {nullptr, nullptr};
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t copy_ev[2] = {nullptr, nullptr};
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     float times_ms[2] = {0, 0};
     // CUDA graph of the 8-bit plan (one graph = the whole batch: every micro-batch, every layer)
@@ -904,6 +911,47 @@ int fill_heads(ln_net* net, std::vector<ln_yolo_head>& hs) {
     return LN_OK;
 }
 
+void release_pipe(ln_net* net) {
+    for (auto& c : net->pipe) {
+        if (c) ln_net_destroy(c);
+        c = nullptr;
+    }
+}
+
+// Builds (once) the two half-batch networks of the host-input pipeline from this network's cfg, weights and scales.
+int ensure_pipe(ln_net* net) {
+    ln_ctx* ctx = net->ctx;
+    if (net->pipe[0] && net->pipe[1]) return LN_OK;
+    release_pipe(net);
+    std::vector<float> blob;
+    for (auto& L : net->layers) {
+        if (L.kind != K_CONV) continue;
+        blob.insert(blob.end(), L.biases.begin(), L.biases.end());
+        if (L.bn) {
+            blob.insert(blob.end(), L.scales.begin(), L.scales.end());
+            blob.insert(blob.end(), L.mean.begin(), L.mean.end());
+            blob.insert(blob.end(), L.var.begin(), L.var.end());
+        }
+        blob.insert(blob.end(), L.weights.begin(), L.weights.end());
+    }
+    for (int h = 0; h < 2; ++h) {
+        int rc = ln_net_create(ctx, net->cfg_text.c_str(), net->batch / 2, net->precision, &net->pipe[h]);
+        if (rc == LN_OK) {
+            net->pipe[h]->host_pipeline = false;
+            net->pipe[h]->fuse_shortcut = net->fuse_shortcut;
+            net->pipe[h]->use_graph = net->use_graph;
+            rc = ln_net_load_weights(net->pipe[h], blob.data(), (int64_t)blob.size());
+        }
+        if (rc == LN_OK) rc = ln_net_set_scales(net->pipe[h], net->scale.data(), (int)net->scale.size());
+        if (rc) { release_pipe(net); return rc; }
+    }
+    if (!net->copy_stream) {
+        LN_CUDA(ctx, cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+        for (auto& e : net->copy_ev) LN_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    return LN_OK;
+}
+
 int stage_input(ln_net* net, const float* host) {
     ln_ctx* ctx = net->ctx;
     cudaSetDevice(ctx->device);
@@ -926,6 +974,7 @@ int32_t ln_net_create(ln_ctx* ctx, const char* cfg_text, int32_t batch, int32_t 
     net->ctx = ctx;
     net->precision = precision;
     try {
+        net->cfg_text = cfg_text;
         build_layers(net.get(), cfg_text, batch);
     } catch (const ParseError& e) {
         return ln_fail(ctx, LN_ERR_PARSE, "%s", e.msg.c_str());
@@ -947,6 +996,9 @@ int32_t ln_net_destroy(ln_net* net) {
     release_outputs(net);
     release_heads(net);
     ln_tensor_release(net->input_dev);
+    release_pipe(net);
+    if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+    for (auto& e : net->copy_ev) if (e) cudaEventDestroy(e);
     for (auto& L : net->layers) {
         ln_tensor_release(L.w_f32);
         ln_tensor_release(L.b_f32);
@@ -982,6 +1034,7 @@ int32_t ln_net_load_weights(ln_net* net, const float* blob, int64_t count) {
     if (count != ln_net_weight_count(net)) return ln_fail(ctx, LN_ERR_SHAPE, "weight blob has %lld values, the network needs %lld", (long long)count, (long long)ln_net_weight_count(net));
     cudaSetDevice(ctx->device);
     release_plan(net);
+    release_pipe(net);
     const float* w = blob;
     for (auto& L : net->layers) {
         if (L.kind != K_CONV) continue;
@@ -1073,6 +1126,7 @@ int32_t ln_net_set_scales(ln_net* net, const float* scales, int32_t count) {
     net->scale.assign(scales, scales + count);
     net->scales_set = true;
     release_plan(net);
+    release_pipe(net);
     return LN_OK;
 }
 
@@ -1158,9 +1212,46 @@ int32_t ln_net_detect_device(ln_net* net, const ln_tensor* input, const int32_t*
 int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
                       ln_detection* records_host, int32_t* counts_host) {
     if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_detect: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    if (net->precision != LN_F32 && net->host_pipeline && net->batch >= 8 && net->batch % 2 == 0 && net->weights_loaded && net->scales_set &&
+        image_w && image_h && opts && records_host && counts_host && opts->max_per_image >= 1) {
+        int rc = ensure_pipe(net);
+        if (rc) return rc;
+        cudaSetDevice(ctx->device);
+        const int half = net->batch / 2;
+        const size_t in_half = (size_t)half * net->channels * net->height * net->width;
+        for (int h = 0; h < 2; ++h) {
+            ln_net* c = net->pipe[h];
+            if (!c->input_dev) {
+                c->input_dev = ln_tensor_new(ctx, LN_F32, half, net->channels, net->height, net->width);
+                if (!c->input_dev) return LN_ERR_CUDA;
+            }
+            // every earlier call has synchronised the compute stream before it returned: nothing still reads these buffers
+            LN_CUDA(ctx, cudaMemcpyAsync(c->input_dev->ptr, input_host + (size_t)h * in_half, in_half * 4, cudaMemcpyHostToDevice, net->copy_stream));
+            LN_CUDA(ctx, cudaEventRecord(net->copy_ev[h], net->copy_stream));
+        }
+        net->times_ms[0] = net->times_ms[1] = 0.0f;
+        for (int h = 0; h < 2; ++h) {
+            ln_net* c = net->pipe[h];
+            LN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, net->copy_ev[h], 0));
+            rc = ln_net_detect_device(c, c->input_dev, image_w + h * half, image_h + h * half, opts,
+                                      records_host + (size_t)h * half * opts->max_per_image, counts_host + h * half);
+            if (rc) return rc;
+            net->times_ms[0] += c->times_ms[0];
+            net->times_ms[1] += c->times_ms[1];
+        }
+        return LN_OK;
+    }
     int rc = stage_input(net, input_host);
     if (rc) return rc;
     return ln_net_detect_device(net, net->input_dev, image_w, image_h, opts, records_host, counts_host);
+}
+
+int32_t ln_net_set_host_pipeline(ln_net* net, int32_t on) {
+    if (!net) return LN_ERR_ARG;
+    net->host_pipeline = on != 0;
+    if (!net->host_pipeline) release_pipe(net);
+    return LN_OK;
 }
 
 int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on) {

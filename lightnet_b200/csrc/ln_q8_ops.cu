@@ -367,9 +367,10 @@ __device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
-// The usual first layer: 3x3 convolution of a 3-channel f32 NCHW image, int8.  One thread per output pixel: the
-// 27 input values are quantised once into 7 packed words held in registers, then every filter costs 7 dp4a against
-// weights read (broadcast) from shared memory, and each group of 16 filters leaves as one 16-byte store.
+// The usual first layer: 3x3 convolution of a 3-channel f32 NCHW image, int8.  One thread per pair of adjacent output
+// pixels: the 27 input values of each are quantised once into 7 packed words held in registers, then every filter costs
+// 7 dp4a per pixel against weights read (broadcast) from shared memory once for both, and each group of 16 filters
+// leaves as one 16-byte store per pixel.
 template <int ACT, bool EXACT>
 __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
                                                                 const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
@@ -390,54 +391,86 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
     }
     for (int i = threadIdx.x; i < F16 * 16; i += blockDim.x) s_mb[i] = i < F ? mb[i] : make_float2(0.0f, 0.0f);
     __syncthreads();
-    const int64_t total = (int64_t)N * OH * OW;
-    for (int64_t pix = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; pix < total; pix += (int64_t)gridDim.x * blockDim.x) {
-        const int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
-        const int64_t n = pix / ((int64_t)OW * OH);
-        uint32_t patch[7] = {0, 0, 0, 0, 0, 0, 0};
+    // one thread per pair of horizontally adjacent output pixels: every weight word read from shared memory serves both
+    const int OWP = (OW + 1) / 2;
+    const int64_t total = (int64_t)N * OH * OWP;
+    for (int64_t pp = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; pp < total; pp += (int64_t)gridDim.x * blockDim.x) {
+        const int ox0 = (int)(pp % OWP) * 2, oy = (int)((pp / OWP) % OH);
+        const int64_t n = pp / ((int64_t)OWP * OH);
+        const bool second = ox0 + 1 < OW;
+        // taps outside the image contribute nothing: every load goes to a clamped (valid) address and the code is masked, so the
+        // loads carry no branches
+        uint32_t patch[2][7] = {{0, 0, 0, 0, 0, 0, 0}, {0, 0, 0, 0, 0, 0, 0}};
+        const float* xn = x + n * 3 * (int64_t)H * W;
+        int rowoff[3];
+        bool rowok[3];
 #pragma unroll
-        for (int t = 0; t < 27; ++t) {
-            const int c = t % 3, ky = (t / 3) / 3, kx = (t / 3) % 3;
-            const int iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
-            uint32_t code = 0;
-            if (iy >= 0 && iy < H && ix >= 0 && ix < W) code = quant_i8_magic(__ldg(x + ((n * 3 + c) * H + iy) * W + ix), inv_sx) & 0xFFu;
-            patch[t >> 2] |= code << (8 * (t & 3));
+        for (int k = 0; k < 3; ++k) {
+            const int iy = oy * stride + k - pad;
+            rowok[k] = iy >= 0 && iy < H;
+            rowoff[k] = min(max(iy, 0), H - 1) * W;
         }
-        for (int fg = 0; fg < F16; ++fg) {
-            uint32_t packed[4];
-            const __half2 inv_h = __float2half2_rn(inv_sy);
+#pragma unroll
+        for (int px = 0; px < 2; ++px) {
+            int coloff[3];
+            bool colok[3];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const int ix = (ox0 + px) * stride + k - pad;
+                colok[k] = ix >= 0 && ix < W;
+                coloff[k] = min(max(ix, 0), W - 1);
+            }
+#pragma unroll
+            for (int t = 0; t < 27; ++t) {
+                const int c = t % 3, ky = (t / 3) / 3, kx = (t / 3) % 3;
+                const uint32_t q = quant_i8_magic(__ldg(xn + (int64_t)c * H * W + rowoff[ky] + coloff[kx]), inv_sx) & 0xFFu;
+                patch[px][t >> 2] |= (rowok[ky] && colok[kx] ? q : 0u) << (8 * (t & 3));
+            }
+        }
+        const uint4* wp = s_w4;      // 16 filters x 2 words of 16 bytes per group: constant offsets inside the group
+        const float2* mp = s_mb;
+        uint8_t* op = out + (((int64_t)n * OH + oy) * OW + ox0) * out_pixel_stride;
+        const __half2 inv_h = __float2half2_rn(inv_sy);
+        for (int fg = 0; fg < F16; ++fg, wp += 32, mp += 16, op += 16) {
+            uint32_t packed[2][4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                float v[4];
+                float v[2][4];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    const int f = fg * 16 + q * 4 + b;
-                    const uint4 w0 = s_w4[f * 2], w1 = s_w4[f * 2 + 1];
-                    int acc = __dp4a((int)patch[0], (int)w0.x, 0);
-                    acc = __dp4a((int)patch[1], (int)w0.y, acc);
-                    acc = __dp4a((int)patch[2], (int)w0.z, acc);
-                    acc = __dp4a((int)patch[3], (int)w0.w, acc);
-                    acc = __dp4a((int)patch[4], (int)w1.x, acc);
-                    acc = __dp4a((int)patch[5], (int)w1.y, acc);
-                    acc = __dp4a((int)patch[6], (int)w1.z, acc);
-                    const float2 m = s_mb[f];
-                    // |acc| <= 27*127*127 < 2^22: adding it to the bits of 1.5*2^23 converts exactly
-                    const float xf = __fadd_rn(__int_as_float(0x4B400000 + acc), -12582912.0f);
-                    v[b] = __fmaf_rn(xf, m.x, m.y);  // filters beyond F have m = {0, 0}: their code is act(0) and is masked below
-                }
-                if (EXACT) {
-                    uint32_t u[4];
+                    const uint4 w0 = wp[(q * 4 + b) * 2], w1 = wp[(q * 4 + b) * 2 + 1];
+                    const float2 m = mp[q * 4 + b];
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) u[b] = fg * 16 + q * 4 + b < F ? quant_i8_magic(ln_epilogue_act<true>(ACT, v[b]), inv_sy) : 0u;
-                    packed[q] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
-                } else {
-                    uint32_t w = ln_h2_pack(ln_h2_act_quant<ACT>(v[0], v[1], inv_h), ln_h2_act_quant<ACT>(v[2], v[3], inv_h));
-                    const int valid = F - (fg * 16 + q * 4);  // keep only the codes of real filters
-                    if (valid < 4) w = valid <= 0 ? 0u : (w & (0xFFFFFFFFu >> (8 * (4 - valid))));
-                    packed[q] = w;
+                    for (int px = 0; px < 2; ++px) {
+                        int acc = __dp4a((int)patch[px][0], (int)w0.x, 0);
+                        acc = __dp4a((int)patch[px][1], (int)w0.y, acc);
+                        acc = __dp4a((int)patch[px][2], (int)w0.z, acc);
+                        acc = __dp4a((int)patch[px][3], (int)w0.w, acc);
+                        acc = __dp4a((int)patch[px][4], (int)w1.x, acc);
+                        acc = __dp4a((int)patch[px][5], (int)w1.y, acc);
+                        acc = __dp4a((int)patch[px][6], (int)w1.z, acc);
+                        // |acc| <= 27*127*127 < 2^22: adding it to the bits of 1.5*2^23 converts exactly
+                        const float xf = __fadd_rn(__int_as_float(0x4B400000 + acc), -12582912.0f);
+                        v[px][b] = __fmaf_rn(xf, m.x, m.y);  // filters beyond F have m = {0, 0}: their code is act(0) and is masked below
+                    }
+                }
+#pragma unroll
+                for (int px = 0; px < 2; ++px) {
+                    if (EXACT) {
+                        uint32_t u[4];
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) u[b] = fg * 16 + q * 4 + b < F ? quant_i8_magic(ln_epilogue_act<true>(ACT, v[px][b]), inv_sy) : 0u;
+                        packed[px][q] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
+                    } else {
+                        uint32_t w = ln_h2_pack(ln_h2_act_quant<ACT>(v[px][0], v[px][1], inv_h), ln_h2_act_quant<ACT>(v[px][2], v[px][3], inv_h));
+                        const int valid = F - (fg * 16 + q * 4);  // keep only the codes of real filters
+                        if (valid < 4) w = valid <= 0 ? 0u : (w & (0xFFFFFFFFu >> (8 * (4 - valid))));
+                        packed[px][q] = w;
+                    }
                 }
             }
-            *reinterpret_cast<uint4*>(out + pix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4*>(op) = make_uint4(packed[0][0], packed[0][1], packed[0][2], packed[0][3]);
+            if (second) *reinterpret_cast<uint4*>(op + out_pixel_stride) = make_uint4(packed[1][0], packed[1][1], packed[1][2], packed[1][3]);
         }
     }
 }
@@ -546,7 +579,8 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
     const bool exact = ctx->exact_epilogue;
     if (k == 3 && C == 3 && (kind == LN_KIND_I8 || F16 * 16 * 28 * 4 <= 40 * 1024)) {
         const size_t smem3 = (size_t)F16 * 16 * (kind == LN_KIND_I8 ? 32 : 28 * 4) + (size_t)F16 * 16 * sizeof(float2);
-        const int grid3 = grid_for(ctx, (int64_t)N * OH * OW);
+        // the int8 kernel takes two output pixels per thread, the FP8 one a single pixel
+        const int grid3 = grid_for(ctx, kind == LN_KIND_I8 ? (int64_t)N * OH * ((OW + 1) / 2) : (int64_t)N * OH * OW);
 #define LN_STEM3(A, E)                                                                                                                             \
     do {                                                                                                                                           \
         if (kind == LN_KIND_I8)                                                                                                                    \

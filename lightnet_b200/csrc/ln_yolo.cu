@@ -86,6 +86,9 @@ struct ImgState {
     int direct;      // the pool being filled is small enough to be the band itself
     int pool_count;  // keys in the pool
     int sampled;     // the histogram in progress is an estimate from a sample of the slots
+    // band selection inside a pool starts at the first digit on which the pool's keys differ (all earlier digits = start_prefix)
+    int start_level, fresh;
+    unsigned long long start_prefix;
 };
 
 __device__ __forceinline__ int level_shift(int l) { return l < 5 ? 52 - 12 * l : 0; }
@@ -297,7 +300,8 @@ __global__ void __launch_bounds__(256) yolo_head_hist_kernel(const __grid_consta
 // out with one reservation per few hundred keys.
 __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_constant__ YoloParams p, const ImgState* __restrict__ states,
                                                              unsigned long long* __restrict__ band, int* __restrict__ band_fill,
-                                                             unsigned long long* __restrict__ pool, int* __restrict__ pool_fill) {
+                                                             unsigned long long* __restrict__ pool, int* __restrict__ pool_fill,
+                                                             unsigned long long* __restrict__ key_and_or) {
     const int img = blockIdx.y;
     const ImgState st = states[img];
     if (st.phase != PHASE_FILL) return;
@@ -337,9 +341,19 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
     __syncthreads();
     const int n_listed = s_n;
     if (n_listed == 0) return;
+    unsigned long long t_and = ~0ull, t_or = 0ull;  // over the keys this thread emits
     auto emit = [&](unsigned long long key) {
         const int slot = atomicAdd(&s_cnt[warp], 1);  // stays below kWarpBuf, see the flush conditions
         s_buf[warp * kWarpBuf + slot] = key;
+        t_and &= key;
+        t_or |= key;
+    };
+    auto publish_and_or = [&]() {
+        for (int o = 16; o > 0; o >>= 1) {
+            t_and &= __shfl_xor_sync(0xffffffffu, t_and, o);
+            t_or |= __shfl_xor_sync(0xffffffffu, t_or, o);
+        }
+        if (lane == 0 && t_or != 0ull) { atomicAnd(&key_and_or[2 * img], t_and); atomicOr(&key_and_or[2 * img + 1], t_or); }
     };
     auto flush_if = [&](int limit, bool last) {
         // the warp writes its buffered keys out when the next step could overflow the buffer, and at the end
@@ -386,6 +400,7 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
             }
             flush_if(kWarpBuf - 256, c0 + 8 >= p.classes);  // a step adds at most 8 x 32 keys
         }
+        publish_and_or();
         return;
     }
     // few listed slots: all threads share the (class, listed slot) pairs
@@ -411,6 +426,7 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
         }
         flush_if(kWarpBuf - 32, base + 256 >= items);  // a step adds at most 32 keys
     }
+    publish_and_or();
 }
 
 // Loads the histogram of one image top bin first into shared memory (and zeroes it in global memory);
@@ -502,13 +518,16 @@ __global__ void __launch_bounds__(256) yolo_pool_select_kernel(const __grid_cons
 // keys than its destination holds (possible only after a sampled histogram) is thrown away and the image starts over
 // with the full histogram.
 __global__ void yolo_after_fill_kernel(ImgState* __restrict__ states, int* __restrict__ band_fill, int* __restrict__ pool_fill, int batch,
-                                       int band_max, int pool_max, int hist_stride, int* __restrict__ flags) {
+                                       int band_max, int pool_max, int hist_stride, int* __restrict__ flags,
+                                       unsigned long long* __restrict__ key_and_or) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= batch || states[i].phase != PHASE_FILL) return;
     int* fill = states[i].direct ? band_fill + i : pool_fill + i;
     const int n = *fill;
     if (n > (states[i].direct ? band_max : pool_max)) {
         *fill = 0;
+        key_and_or[2 * i] = ~0ull;
+        key_and_or[2 * i + 1] = 0ull;
         states[i].phase = PHASE_POOL;
         states[i].sampled = 0;
         states[i].level = 0;
@@ -516,13 +535,29 @@ __global__ void yolo_after_fill_kernel(ImgState* __restrict__ states, int* __res
         return;
     }
     states[i].sampled = hist_stride > 1 ? 1 : 0;  // for the next pool of this image
+    const unsigned long long k_and = key_and_or[2 * i], k_or = key_and_or[2 * i + 1];
+    key_and_or[2 * i] = ~0ull;
+    key_and_or[2 * i + 1] = 0ull;
     if (states[i].direct) {
         states[i].band_count = n;
         states[i].phase = PHASE_BAND;
     } else {
+        // digits on which the AND and the OR of the pool's keys agree are shared by all of them: the selection starts below them
+        int level = 0;
+        unsigned long long prefix = 0ull;
+        const unsigned long long diff = k_and ^ k_or;
+        while (n > 0 && level < kLevels - 1) {
+            const int sh = level_shift(level), bt = level_bits(level);
+            const unsigned long long m = ((1ull << bt) - 1ull) << sh;
+            if (diff & m) break;
+            prefix = (prefix << bt) | ((k_and & m) >> sh);
+            ++level;
+        }
         states[i].pool_count = n;
         states[i].phase = PHASE_SELECT;
-        states[i].level = 0;
+        states[i].level = states[i].start_level = level;
+        states[i].prefix = states[i].start_prefix = prefix;
+        states[i].fresh = 1;
     }
 }
 
@@ -608,10 +643,10 @@ __global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant_
     key_and_or[2 * img] = ~0ull;
     key_and_or[2 * img + 1] = 0ull;
     // ---- one thread decides (a few hundred steps at most)
-    if (st.level == 0) {
+    if (st.fresh) {  // first pass of this band: level and prefix are the pool's starting point
         st.cap = band_cap(p, st);
         st.above = 0;
-        st.prefix = 0;
+        st.fresh = 0;
     }
     const unsigned cap_left = (unsigned)(st.cap - st.above);
     const int shift = level_shift(st.level), bits = level_bits(st.level);
@@ -624,9 +659,10 @@ __global__ void __launch_bounds__(256) yolo_select_kernel(const __grid_constant_
     }
     if (owner < 0) {
         // everything that is left of the pool (under this prefix) fits into the band
-        st.lo = st.level == 0 ? st.pool_lo : (st.prefix << (shift + bits));
+        const bool whole_pool = st.level == st.start_level;  // nothing was cut off above this level: the rest of the pool is the band
+        st.lo = whole_pool ? st.pool_lo : (st.prefix << (shift + bits));
         st.band_count = st.above + (int)cum;
-        st.exhausted = st.level == 0 ? 1 : 0;
+        st.exhausted = whole_pool ? 1 : 0;
         st.phase = PHASE_BAND;
         states[img] = st;
         return;
@@ -817,7 +853,12 @@ __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant
                 st.prefix = 0;
                 st.above = 0;
                 atomicAdd(&flags[FLAG_NEED_POOL], 1);
-            } else st.phase = PHASE_SELECT;
+            } else {
+                st.phase = PHASE_SELECT;
+                st.level = st.start_level;
+                st.prefix = st.start_prefix;
+                st.fresh = 1;
+            }
         }
         states[img] = st;
     }
@@ -830,6 +871,7 @@ __global__ void yolo_init_states_kernel(ImgState* states, unsigned long long* ke
     s.hi = ~0ull; s.lo = 0; s.prefix = 0; s.pool_lo = 0;
     s.level = 0; s.phase = PHASE_POOL; s.cap = 0; s.above = 0; s.band_count = 0; s.kept = 0; s.exhausted = 0;
     s.img_w = img_w[i]; s.img_h = img_h[i]; s.last_gain = -1; s.direct = 0; s.pool_count = 0; s.sampled = hist_stride > 1 ? 1 : 0;
+    s.start_level = 0; s.fresh = 1; s.start_prefix = 0;
     states[i] = s;
     key_and_or[2 * i] = ~0ull;
     key_and_or[2 * i + 1] = 0ull;
@@ -1031,9 +1073,9 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
                 tock(0); tick();
                 yolo_pool_select_kernel<<<B, 256, 0, ctx->stream>>>(p, states, hist, flags);
                 tock(1); tick();
-                yolo_head_fill_kernel<<<scan_grid, 256, 0, ctx->stream>>>(p, states, band, band_fill, pool, pool_fill);
+                yolo_head_fill_kernel<<<scan_grid, 256, 0, ctx->stream>>>(p, states, band, band_fill, pool, pool_fill, key_and_or);
                 tock(2);
-                yolo_after_fill_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, band_fill, pool_fill, B, p.band_max, p.pool_max, p.hist_stride, flags);
+                yolo_after_fill_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, band_fill, pool_fill, B, p.band_max, p.pool_max, p.hist_stride, flags, key_and_or);
                 ctx->launches += 4;
                 n_full += 2;
             }

@@ -767,3 +767,25 @@ def test_sharded_detector_pads_short_shards(be):
     det = sharding.ShardedDetector(lambda im: net.detect(im, 640, 480, 0.2, 0.45, True, 0, 512), capacity=4)
     got = det.detect(x[:3])
     assert len(got) == 3 and all(np.array_equal(a, b) for a, b in zip(got, full[:3]))
+
+
+def test_host_pipeline_gives_the_same_detections(be):
+    """detect() on host buffers runs the batch as two overlapping half-batch networks; device-resident input runs it whole.
+    Both must give the records of the pipeline-off run, image for image."""
+    batch = 8
+    o = orc.Net(MINI_CFG, batch)
+    blob = synth.he_weights(o.layers(), 51, bn_identity=False)
+    x = synth.uniform_images(batch, o.channels, o.height, o.width, 52)
+    net = ln.GpuExecutableNetwork(be, MINI_CFG, batch, ln.LN_Q8)
+    net.load_weights(blob)
+    net.calibrate(x)
+    iw = [640, 320, 500, 640, 200, 333, 640, 100]
+    ih = [480, 240, 500, 360, 300, 333, 480, 200]
+    piped = net.detect(x, iw, ih, 0.2, 0.45, True, 0, 256)
+    piped2 = net.detect(x, iw, ih, 0.2, 0.45, True, 0, 256)      # second call replays the halves' graphs
+    net.set_host_pipeline(False)
+    whole = net.detect(x, iw, ih, 0.2, 0.45, True, 0, 256)
+    assert sum(len(d) for d in whole) > 50
+    for b in range(batch):
+        assert np.array_equal(piped[b], whole[b]), b
+        assert np.array_equal(piped2[b], whole[b]), b
