@@ -74,6 +74,9 @@ struct ln_conv_geom {
     int act = 0, out_kind = 0;
     float inv_sy = 1.0f;
     bool small_acc = false;  // 127 * max over filters of sum|w code| < 2^22
+    // x is the 2x2 space-to-depth image of the 32-channel input ([H/2][W/2][4 * 32], sub-pixel (y & 1) * 2 + (x & 1) major):
+    // the 3x3 stride-2 pad-1 convolution described here is then run as a 2x2 stride-1 one over 128-byte rows
+    bool s2d_input = false;
     void* out = nullptr;
     long long out_pixel_stride = 0;
     // fused linear shortcut that follows the convolution (see ln_conv_umma_params)
@@ -109,7 +112,7 @@ int ln_conv_simt_launch(ln_ctx* ctx, const ln_conv_geom& g, const void* w_oihw, 
 // First layer: f32 NCHW image in, quantise on the fly, 8-bit NHWC out (C <= 4).
 int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx, int N, int C, int H, int W, const void* w_oihw,
                         const float2* mb, int F, int k, int stride, int pad, int OH, int OW, int act, float inv_sy, void* out,
-                        long long out_pixel_stride);
+                        long long out_pixel_stride, int s2d_out = 0);
 
 // Reads the device status word; returns LN_OK or LN_ERR_TIMEOUT (and clears the word).
 int ln_check_status(ln_ctx* ctx, const char* where);

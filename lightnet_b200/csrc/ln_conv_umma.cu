@@ -633,6 +633,20 @@ __global__ void pack_group_weights_kernel(const uint8_t* __restrict__ w, int cpa
     if ((i & 31) == 0) mb2[row] = j < pack ? mb[f] : make_float2(0.0f, 0.0f);
 }
 
+// Weights of a 3x3 stride-2 pad-1 convolution over 32 channels, rearranged for its 2x2 stride-1 form over the 2x2
+// space-to-depth image: w2[f][ty][tx][(qy * 2 + qx) * 32 + c] = w[f][2 ty + qy - 1][2 tx + qx - 1][c], zero where that tap does
+// not exist (input row 2 (oy + ty - 1) + qy is row 2 oy + r - 1 of the original with r = 2 ty + qy - 1).
+__global__ void pack_s2d_weights_kernel(const uint8_t* __restrict__ w, int fpad, uint8_t* __restrict__ w2) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 4 bytes of w2: [fpad][2][2][128]
+    if (i >= fpad * 4 * 32) return;
+    const int f = i / 128, rem = i - f * 128, tap = rem >> 5, b = (rem & 31) * 4;
+    const int ty = tap >> 1, tx = tap & 1, q = b >> 5, c = b & 31;
+    const int r = 2 * ty + (q >> 1) - 1, sx = 2 * tx + (q & 1) - 1;
+    uint32_t v = 0;
+    if (r >= 0 && sx >= 0) v = *reinterpret_cast<const uint32_t*>(w + (((size_t)f * 3 + r) * 3 + sx) * 32 + c);
+    *reinterpret_cast<uint32_t*>(w2 + (size_t)i * 4) = v;
+}
+
 __global__ void fold_mb_kernel(const float2* __restrict__ mb, int n, float2* __restrict__ out) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = make_float2(mb[i].x, __fmaf_rn(-12582912.0f, mb[i].x, mb[i].y));
@@ -690,6 +704,20 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     // LN_CONV_DISABLE=pack,halo switches the two layout modes off (for A/B measurements)
     const char* disable = getenv("LN_CONV_DISABLE");
     const bool allow_pack = !(disable && strstr(disable, "pack")), allow_halo = !(disable && strstr(disable, "halo"));
+    // Space-to-depth input (see ln_conv_geom::s2d_input): 4 taps of 128-byte rows instead of 9 taps of 32-byte rows.
+    if (g.s2d_input) {
+        if (!(g.k == 3 && g.stride == 2 && g.pad == 1 && g.cpad == 32 && g.H % 2 == 0 && g.W % 2 == 0 && g.x_pixel_stride == 32 && g.res == nullptr))
+            return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: a space-to-depth input needs 3x3 stride 2 pad 1 over 32 channels and even sizes");
+        plan->aux_w_bytes = (size_t)g.fpad * 4 * 128;
+        plan->aux_w = ln_pool_alloc(ctx, plan->aux_w_bytes);
+        if (!plan->aux_w) return LN_ERR_CUDA;
+        pack_s2d_weights_kernel<<<(g.fpad * 128 + 255) / 256, 256, 0, ctx->stream>>>((const uint8_t*)g.w, g.fpad, (uint8_t*)plan->aux_w);
+        LN_LAUNCHED(ctx);
+        g.w = plan->aux_w;
+        g.k = 2; g.stride = 1; g.pad = 1;
+        g.cpad = 128; g.C = 128; g.x_pixel_stride = 128;
+        g.H /= 2; g.W /= 2;
+    }
     // Pixel-group packing.  The TMA unit spends about as long on a 32- or 64-byte row as on a 128-byte one, and a 1x1
     // convolution over a dense NHWC tensor is a plain GEMM over pixels: read `pack` = 128 / C consecutive pixels as one
     // 128-byte row and multiply by block-diagonal weights (pack x F virtual filters).  The tensor core does `pack` times the

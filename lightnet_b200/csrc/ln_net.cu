@@ -250,7 +250,7 @@ struct ln_net {
     float times_ms[2] = {0, 0};
     // CUDA graph of the 8-bit plan (one graph = the whole batch: every micro-batch, every layer)
     bool fuse_shortcut = true;  // a linear [shortcut] whose input is a convolution nobody else reads runs in that convolution's epilogue
-    std::vector<char> fused_into_next;  // per layer: its output is not materialised (8-bit plan)
+    std::vector<char> fused_into_next;  // per layer (8-bit plan): 1 = runs in the next layer's shortcut epilogue, no output; 2 = output kept in space-to-depth layout
     bool use_graph = true;
     cudaGraphExec_t graph_exec = nullptr;
     const void* graph_input = nullptr;
@@ -574,6 +574,22 @@ int build_plan(ln_net* net, int mb) {
             net->fused_into_next[i] = 1;
         }
     }
+    // 2c. the first layer writes the 2x2 space-to-depth image of its 32 channels when its only reader is a 3x3 stride-2 convolution:
+    // that convolution then reads 4 taps of 128-byte rows instead of 9 taps of 32-byte rows (value 2 = "kept in another layout")
+    if (net->fuse_shortcut && NL > 1) {
+        const NLayer& A = net->layers[0];
+        const NLayer& B = net->layers[1];
+        int readers0 = 0;
+        for (int i = 1; i < NL; ++i) {
+            if (i == 1 && net->layers[i].kind != K_ROUTE) readers0++;
+            if (net->layers[i].kind == K_ROUTE || net->layers[i].kind == K_SHORTCUT)
+                for (int s : net->layers[i].sources) readers0 += s == 0;
+        }
+        if (A.kind == K_CONV && A.in.c == 3 && A.size == 3 && A.filters == 32 && A.groups == 1 && A.out.w % 2 == 0 && A.out.h % 2 == 0 && !feeds_head(net, 0) &&
+            B.kind == K_CONV && B.size == 3 && B.stride_x == 2 && B.stride_y == 2 && B.padding == 1 && B.groups == 1 && B.dilation == 1 && readers0 == 1 &&
+            !net->fused_into_next[1] && !feeds_head(net, 1))
+            net->fused_into_next[0] = 2;
+    }
     // 3. buffers and views
     net->views.assign(NL, QView());
     std::vector<int> buffer_of(NL, -1);
@@ -658,13 +674,14 @@ int build_plan(ln_net* net, int mb) {
                 g.inv_sy = head ? 1.0f : 1.0f / sy;
                 g.small_acc = kind == LN_KIND_I8 && 127.0f * L.wq->max_l1 < 4194304.0f;
                 if (head) { g.out = net->heads[st.head_index]->ptr; g.out_pixel_stride = 0; }
-                else if (net->fused_into_next[i]) {
+                else if (net->fused_into_next[i] == 1) {
                     const int sl = i + 1, src = net->layers[sl].sources[0];
                     g.out = net->views[sl].ptr; g.out_pixel_stride = net->views[sl].cstride;
                     g.res = net->views[src].ptr; g.res_pixel_stride = net->views[src].cstride;
                     g.s_c = sy; g.s_res = net->scale[src + 1]; g.inv_sy2 = 1.0f / net->scale[sl + 1];
                 }
                 else { g.out = net->views[i].ptr; g.out_pixel_stride = net->views[i].cstride; }
+                if (i == 1 && net->fused_into_next[0] == 2) g.s2d_input = true;
                 if (i == 0) {
                     if (L.in.c > 4) {  // generic first layer: quantise the image, then a normal convolution
                         QStep q;
@@ -691,7 +708,7 @@ int build_plan(ln_net* net, int mb) {
                     rc = ln_conv_umma_plan_build(ctx, &st.umma, g);
                     if (rc) return rc;
                 } else st.op = 1;
-                if (st.op != 0 && net->fused_into_next[i]) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: a fused shortcut needs the tensor-core convolution", i);
+                if (st.op != 0 && net->fused_into_next[i] == 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: a fused shortcut needs the tensor-core convolution", i);
                 net->steps.push_back(st);
                 break;
             }
@@ -757,7 +774,7 @@ int build_plan(ln_net* net, int mb) {
                 break;
             }
             case K_SHORTCUT: {
-                if (net->fused_into_next[i - 1]) break;  // done in the epilogue of the convolution before it
+                if (net->fused_into_next[i - 1] == 1) break;  // done in the epilogue of the convolution before it
                 st.op = 6;
                 const int s = L.sources[0];
                 st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride; st.sa = sx;
@@ -811,7 +828,7 @@ int run_plan(ln_net* net, const float* input_dev_f32) {
                 }
                 case 2:
                     rc = ln_conv_stem_launch(ctx, kind, input_dev_f32 + b0 * in_image, st.inv_sy, mb, L.in.c, L.in.h, L.in.w, L.wq->w_oihw, st.mb, L.filters, L.size,
-                                             L.stride_x, L.padding, L.out.h, L.out.w, L.act, st.geom.inv_sy, st.geom.out, st.geom.out_pixel_stride);
+                                             L.stride_x, L.padding, L.out.h, L.out.w, L.act, st.geom.inv_sy, st.geom.out, st.geom.out_pixel_stride, net->fused_into_next[0] == 2 ? 1 : 0);
                     break;
                 case 3: rc = ln_q_maxpool_launch(ctx, kind, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, st.OH, st.OW, st.pool_size, L.stride_x, L.stride_y, st.pool_pad); break;
                 case 4: rc = ln_q_upsample_launch(ctx, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, L.up_stride); break;
@@ -1178,7 +1195,7 @@ int32_t ln_net_layer_output(ln_net* net, int32_t layer, ln_tensor** out) {
         *out = net->heads[k];
         return LN_OK;
     }
-    if (net->fused_into_next[layer]) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer %d is fused into the shortcut after it and has no output of its own (ln_net_set_fusion(0) keeps it)", layer);
+    if (net->fused_into_next[layer]) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer %d is fused into the layer after it and has no output of its own in the standard layout (ln_net_set_fusion(0) keeps it)", layer);
     const QView& v = net->views[layer];
     // a copy, so that the handle stays valid after the plan is rebuilt
     ln_tensor* t = ln_tensor_new(ctx, net->precision, net->batch, v.c, v.h, v.w);

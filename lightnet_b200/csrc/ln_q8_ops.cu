@@ -375,7 +375,7 @@ template <int ACT, bool EXACT>
 __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
                                                                 const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
                                                                 int pad, int OH, int OW, float inv_sy, uint8_t* __restrict__ out,
-                                                                int64_t out_pixel_stride) {
+                                                                int64_t out_pixel_stride, int s2d) {
     extern __shared__ uint4 s_w4[];  // [F16*16][2]: 8 words per filter, 7 used; byte t of a filter = tap (t/3), channel (t%3)
     const int F16 = (F + 15) / 16;
     float2* s_mb = reinterpret_cast<float2*>(s_w4 + F16 * 16 * 2);
@@ -429,7 +429,10 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
         }
         const uint4* wp = s_w4;      // 16 filters x 2 words of 16 bytes per group: constant offsets inside the group
         const float2* mp = s_mb;
-        uint8_t* op = out + (((int64_t)n * OH + oy) * OW + ox0) * out_pixel_stride;
+        // s2d: the 32 channels of pixel (y, x) go to sub-pixel (y & 1) * 2 + (x & 1) of the 128-byte pixel (y / 2, x / 2); the pair
+        // of this thread (x even, x + 1) lands in consecutive 32-byte slots either way
+        uint8_t* op = s2d ? out + ((((int64_t)n * (OH >> 1) + (oy >> 1)) * (OW >> 1) + (ox0 >> 1)) * 4 + (oy & 1) * 2) * out_pixel_stride
+                          : out + (((int64_t)n * OH + oy) * OW + ox0) * out_pixel_stride;
         const __half2 inv_h = __float2half2_rn(inv_sy);
         for (int fg = 0; fg < F16; ++fg, wp += 32, mp += 16, op += 16) {
             uint32_t packed[2][4];
@@ -481,7 +484,7 @@ template <int ACT, bool EXACT>
 __global__ void __launch_bounds__(256) conv_stem_k3c3_f8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
                                                                 const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
                                                                 int pad, int OH, int OW, float inv_sy, uint8_t* __restrict__ out,
-                                                                int64_t out_pixel_stride) {
+                                                                int64_t out_pixel_stride, int s2d) {
     extern __shared__ uint4 s_w4[];  // [F16*16][7] float4: 28 floats per filter, 27 used; float t of a filter = tap (t/3), channel (t%3)
     const int F16 = (F + 15) / 16;
     float* s_w = reinterpret_cast<float*>(s_w4);
@@ -530,7 +533,8 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_f8_kernel(const float* __r
                 }
                 packed[q] = word;
             }
-            *reinterpret_cast<uint4*>(out + pix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            const int64_t opix = s2d ? ((((int64_t)n * (OH >> 1) + (oy >> 1)) * (OW >> 1) + (ox >> 1)) * 4 + (oy & 1) * 2 + (ox & 1)) : pix;
+            *reinterpret_cast<uint4*>(out + opix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
     }
 }
@@ -568,7 +572,9 @@ int ln_conv_simt_launch(ln_ctx* ctx, const ln_conv_geom& g, const void* w_unused
 
 int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx, int N, int C, int H, int W, const void* w_oihw,
                         const float2* mb, int F, int k, int stride, int pad, int OH, int OW, int act, float inv_sy, void* out,
-                        long long out_pixel_stride) {
+                        long long out_pixel_stride, int s2d_out) {
+    if (s2d_out && !(k == 3 && C == 3 && F == 32 && out_pixel_stride == 32 && OH % 2 == 0 && OW % 2 == 0))
+        return ln_fail(ctx, LN_ERR_UNSUPPORTED, "first-layer convolution: the space-to-depth output needs 3x3 over 3 channels, 32 filters and even output sizes");
     const int taps = k * k * C, words = (taps + 3) / 4;
     if (words > kStemMaxWords) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "first-layer convolution: k*k*C = %d exceeds %d", taps, kStemMaxWords * 4);
     const int F16 = (F + 15) / 16;
@@ -585,10 +591,10 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
     do {                                                                                                                                           \
         if (kind == LN_KIND_I8)                                                                                                                    \
             conv_stem_k3c3_i8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, \
-                                                                                   OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride);              \
+                                                                                   OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);     \
         else                                                                                                                                       \
             conv_stem_k3c3_f8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, \
-                                                                                   OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride);              \
+                                                                                   OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);     \
     } while (0)
         switch (act) {
             case LN_ACT_LINEAR: if (exact) LN_STEM3(LN_ACT_LINEAR, true); else LN_STEM3(LN_ACT_LINEAR, false); break;
