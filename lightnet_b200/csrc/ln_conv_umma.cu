@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     for (int j = 0; j < 16; ++j) m[j] = ldg_f4_pinned(mb4 + j);
                     uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
                     if (p.res != nullptr && valid) {  // residual codes of the fused shortcut, fetched while TMEM is read
-                        const uint4* rp = (const uint4*)((const uint8_t*)p.res + pix * p.res_pixel_stride + f0 + c0);
+                        const uint4* rp = (const uint4*)((const uint8_t*)p.res + opix * p.res_pixel_stride + fo);
                         r0 = __ldg(rp);
                         r1 = __ldg(rp + 1);
                     }
@@ -633,6 +633,24 @@ __global__ void pack_group_weights_kernel(const uint8_t* __restrict__ w, int cpa
     if ((i & 31) == 0) mb2[row] = j < pack ? mb[f] : make_float2(0.0f, 0.0f);
 }
 
+// The same for a 3x3 stride-1 pad-1 convolution: a 128-byte row is `pack` consecutive pixels of one image row, the output row the
+// same `pack` pixels.  In units of pixel groups the taps are again 3x3 with pad 1; tap (r, s') of output pixel j_out reads input
+// pixel j_in of group X + s' - 1, which is column offset s = pack (s' - 1) + j_in - j_out + 1 of the original 3x3 (zero weight
+// when that is outside 0..2).  w is [fpad][3][3][cpad], w2 [fpad2][3][3][128].
+__global__ void pack_group_weights_k3_kernel(const uint8_t* __restrict__ w, int cpad, int F, int pack, int fpad2, uint8_t* __restrict__ w2,
+                                             const float2* __restrict__ mb, float2* __restrict__ mb2) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 4 bytes of w2
+    if (i >= fpad2 * 9 * 32) return;
+    const int row = i / 288, rem = i - row * 288, tap = rem >> 5, b = (rem & 31) * 4;
+    const int r = tap / 3, sp = tap - r * 3;
+    const int j_out = row / F, f = row - j_out * F, j_in = b / cpad, c = b - j_in * cpad;
+    const int s = pack * (sp - 1) + j_in - j_out + 1;
+    uint32_t v = 0;
+    if (j_out < pack && s >= 0 && s <= 2) v = *reinterpret_cast<const uint32_t*>(w + (((size_t)f * 3 + r) * 3 + s) * cpad + c);
+    *reinterpret_cast<uint32_t*>(w2 + (size_t)i * 4) = v;
+    if (rem == 0) mb2[row] = j_out < pack ? mb[f] : make_float2(0.0f, 0.0f);
+}
+
 // Weights of a 3x3 stride-2 pad-1 convolution over 32 channels, rearranged for its 2x2 stride-1 form over the 2x2
 // space-to-depth image: w2[f][ty][tx][(qy * 2 + qx) * 32 + c] = w[f][2 ty + qy - 1][2 tx + qx - 1][c], zero where that tap does
 // not exist (input row 2 (oy + ty - 1) + qy is row 2 oy + r - 1 of the original with r = 2 ty + qy - 1).
@@ -743,6 +761,29 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
             mb = plan->aux_mb;
         }
     }
+    // Pixel groups for 3x3 stride-1 layers with few channels: `pack` consecutive pixels of an image row per 128-byte row on both
+    // sides, nine taps in units of groups (see pack_group_weights_k3_kernel).  The tensor core multiplies mostly zeros -- `pack`
+    // times the arithmetic -- but it is idle at these sizes, and the loads become `pack` times fewer 128-byte rows.
+    {
+        const int pk = g.cpad < 128 ? 128 / g.cpad : 1;
+        if (allow_pack && pack == 1 && pk > 1 && !g.s2d_input && g.k == 3 && g.stride == 1 && g.pad == 1 && g.x_pixel_stride == g.cpad && g.W % pk == 0 &&
+            g.OW == g.W && g.OH == g.H && g.out_kind == LN_OUT_Q && g.F % 32 == 0 && pk * g.F <= 256 && (((uintptr_t)g.x) & 127) == 0) {
+            const int F2 = pk * g.F, bn2 = ln_conv_choose_bn(F2), fpad2 = (int)ln_round_up(F2, bn2);
+            plan->aux_w_bytes = (size_t)fpad2 * 9 * 128;
+            plan->aux_mb_bytes = (size_t)fpad2 * sizeof(float2);
+            plan->aux_w = ln_pool_alloc(ctx, plan->aux_w_bytes);
+            plan->aux_mb = (float2*)ln_pool_alloc(ctx, plan->aux_mb_bytes);
+            if (!plan->aux_w || !plan->aux_mb) return LN_ERR_CUDA;
+            pack_group_weights_k3_kernel<<<(fpad2 * 288 + 255) / 256, 256, 0, ctx->stream>>>((const uint8_t*)g.w, g.cpad, g.F, pk, fpad2, (uint8_t*)plan->aux_w,
+                                                                                           plan->mb, plan->aux_mb);
+            LN_LAUNCHED(ctx);
+            pack = pk;
+            g.w = plan->aux_w; g.fpad = fpad2; g.F = F2;
+            g.cpad = 128; g.C = 128; g.x_pixel_stride = 128;
+            g.W /= pk; g.OW /= pk;
+            mb = plan->aux_mb;
+        }
+    }
     if (!ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H))
         return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: unsupported geometry (cpad %d k %d stride %d)", g.cpad, g.k, g.stride);
     if (((uintptr_t)g.x & 15) || (g.x_pixel_stride & 15) || ((uintptr_t)g.w & 15))
@@ -769,7 +810,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     // image; the mode is used when that shape wastes at most 15 % of the rows, and only for layers of at most 64 channels:
     // measured, it gains 10 % there and loses with 128 and more (the larger boxes complete later than per-tap boxes do).
     const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u;
-    if (allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
+    if (allow_halo && g.k == 3 && g.stride == 1 && g.out_kind != LN_OUT_F32 && g_in.cpad <= 64 && !g_in.s2d_input) {
         int best_tw = 0, best_th = 0;
         int64_t best_tiles = -1;
         for (int lw = 3; lw <= 7; ++lw) {
