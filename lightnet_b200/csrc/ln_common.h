@@ -37,6 +37,9 @@ struct ln_ctx {
     long long* debug_cycles = nullptr;  // when set (LN_DEBUG_CYCLES=1), the tensor-core convolution records role timings of CTA 0
     std::set<const void*> configured_kernels;  // kernels whose dynamic shared memory limit has been raised
     // ln_ctx_set_kernel_timing: the operator-level convolution brackets its main kernel with these events
+    // pinned host staging for result read-backs (grown on demand by the entry points that may allocate)
+    void* h_stage = nullptr;
+    size_t h_stage_bytes = 0;
     bool time_kernels = false;
     cudaEvent_t ev_k0 = nullptr, ev_k1 = nullptr;
     bool ev_pending = false;

@@ -810,7 +810,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     // image; the mode is used when that shape wastes at most 15 % of the rows, and only for layers of at most 64 channels:
     // measured, it gains 10 % there and loses with 128 and more (the larger boxes complete later than per-tap boxes do).
     const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u;
-    if (allow_halo && g.k == 3 && g.stride == 1 && g.out_kind != LN_OUT_F32 && g_in.cpad <= 64 && !g_in.s2d_input) {
+    if (allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
         int best_tw = 0, best_th = 0;
         int64_t best_tiles = -1;
         for (int lw = 3; lw <= 7; ++lw) {

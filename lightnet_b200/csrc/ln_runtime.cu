@@ -135,6 +135,7 @@ int32_t ln_ctx_destroy(ln_ctx* ctx) {
     for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return LN_OK;

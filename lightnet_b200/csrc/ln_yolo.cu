@@ -1018,7 +1018,7 @@ int check_options(ln_ctx* ctx, YoloParams* p, const ln_detect_options* opts, con
 
 // The whole decode + NMS call over working memory that the caller provides (s.total bytes at `scratch`, 256-byte aligned).
 int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned char* scratch, const int32_t* image_w, const int32_t* image_h,
-                   ln_detection* records_host, int32_t* counts_host, const char* who) {
+                   ln_detection* records_host, int32_t* counts_host, const char* who, void* pinned_stage = nullptr) {
     const int B = p.batch;
     unsigned char* q = scratch;
     ImgState* states = (ImgState*)q; q += s.sz_states;
@@ -1113,9 +1113,19 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
     yolo_counts_kernel<<<(B + 127) / 128, 128, 0, ctx->stream>>>(states, counts, B, p.max_per_image);
     ctx->launches++;
     LN_Y(cudaGetLastError());
-    LN_Y(cudaMemcpyAsync(counts_host, counts, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    LN_Y(cudaMemcpyAsync(records_host, records, (size_t)B * p.max_per_image * sizeof(ln_detection), cudaMemcpyDeviceToHost, ctx->stream));
-    LN_Y(cudaStreamSynchronize(ctx->stream));
+    const size_t rec_bytes = (size_t)B * p.max_per_image * sizeof(ln_detection);
+    if (pinned_stage) {
+        // through pinned memory: the copy runs at link speed instead of being staged page by page by the driver
+        LN_Y(cudaMemcpyAsync(pinned_stage, records, rec_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        LN_Y(cudaMemcpyAsync((unsigned char*)pinned_stage + rec_bytes, counts, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        LN_Y(cudaStreamSynchronize(ctx->stream));
+        memcpy(records_host, pinned_stage, rec_bytes);
+        memcpy(counts_host, (unsigned char*)pinned_stage + rec_bytes, (size_t)B * 4);
+    } else {
+        LN_Y(cudaMemcpyAsync(counts_host, counts, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        LN_Y(cudaMemcpyAsync(records_host, records, rec_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        LN_Y(cudaStreamSynchronize(ctx->stream));
+    }
     if (dbg) fprintf(stderr, "[ln_yolo] whole call %.3f ms, of which the read-back of counts and records %.3f ms\n", now() - t_begin, now() - t_loop);
 #undef LN_Y
     return LN_OK;
@@ -1140,7 +1150,15 @@ int32_t ln_yolo_decode_nms(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_hea
     cudaSetDevice(ctx->device);
     unsigned char* scratch = (unsigned char*)ln_pool_alloc(ctx, s.total);
     if (!scratch) return LN_ERR_CUDA;
-    rc = run_decode_nms(ctx, p, s, scratch, image_w, image_h, records_host, counts_host, who);
+    const size_t stage_bytes = (size_t)p.batch * p.max_per_image * sizeof(ln_detection) + (size_t)p.batch * 4;
+    if (ctx->h_stage_bytes < stage_bytes) {
+        if (ctx->h_stage) cudaFreeHost(ctx->h_stage);
+        ctx->h_stage = nullptr;
+        ctx->h_stage_bytes = 0;
+        if (cudaMallocHost(&ctx->h_stage, stage_bytes) == cudaSuccess) ctx->h_stage_bytes = stage_bytes;
+        else { ctx->h_stage = nullptr; cudaGetLastError(); }  // no pinned memory to be had: read back directly
+    }
+    rc = run_decode_nms(ctx, p, s, scratch, image_w, image_h, records_host, counts_host, who, ctx->h_stage);
     ln_pool_free(ctx, scratch, s.total);
     return rc;
 }
