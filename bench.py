@@ -450,6 +450,17 @@ def main():
     for _ in range(args.warmup):   # the host-input path has its own plans and graphs to warm
         net.detect(x_np, *det_args)
     ms_e2e = timed(lambda: net.detect(x_np, *det_args), args.steps)
+    # the same call fed with 8-bit camera-sized images (640 x 480, letterboxed on the device): what a caller that does not
+    # pre-process on the host pays end to end
+    rng8 = np.random.default_rng(200 + rank)
+    images8 = [rng8.integers(0, 256, (480, 640, 3), dtype=np.uint8) for _ in range(B)]
+    flat8, off8, w8, h8 = ln.pack_u8_images(images8)
+    flat8_pinned = torch.from_numpy(flat8).pin_memory()
+    packed8 = (flat8_pinned.numpy(), off8, w8, h8)
+    u8_call = lambda: net.detect_u8(None, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE, packed=packed8)
+    for _ in range(args.warmup):
+        u8_call()
+    ms_u8 = timed(u8_call, args.steps)
     clocks = sampler.summary()
 
     # roofline of the dominant kernel (tensor-core convolution), from a profiled forward
@@ -473,6 +484,8 @@ def main():
                        "l2": "inputs larger than L2 (%.0f MB f32 batch)" % (x_np.nbytes / 1e6), "parallelism": "batch-sharded, no collective"},
             "e2e": {"value": B * world * args.steps / (ms_e2e * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(x_np.nbytes),
                     "d2h_bytes_per_step": int(B * MAX_PER_IMAGE * 28 + B * 4), "api": "ln_net_detect (host f32 NCHW batch -> detections; the two halves of the batch are uploaded and run as a two-stage pipeline)"},
+            "e2e_u8": {"value": B * world * args.steps / (ms_u8 * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(flat8.nbytes),
+                       "api": "ln_net_detect_u8 (host 8-bit 640x480 RGB images -> device letterbox -> detections)"},
             "gpu_launches": int(launches),
             "phases_ms": {"layers": fwd_ms, "decode_nms": nms_ms},
             "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel (%s implicit GEMM, all layers but the first)" % wl["precision"], "achieved": achieved,

@@ -226,6 +226,16 @@ int32_t ln_yolo_decode_only(ln_ctx* ctx, const ln_yolo_head* heads, int32_t n_he
                             int32_t net_h, int32_t image_w, int32_t image_h, float confidence_threshold, int32_t letterbox,
                             ln_detection* records_host, int64_t capacity, int64_t* count);
 
+/* ---- image pre-processing: the step in front of the network ---------------------------- */
+/* PlanarRgbImage::{from_interleaved_rgb_u8, letterbox, resize, resize_linear_exact} (lightnet-runtime/src/image.rs:57, 203,
+   95, 157) for a batch: `count` interleaved 8-bit RGB images of sizes widths[i] x heights[i], image i starting at
+   pixels_host + offsets[i], become one f32 [count, 3, dst_h, dst_w] tensor.  Bit-identical to the reference's CPU code. */
+#define LN_PRE_LETTERBOX 0    /* Darknet float resize to fit inside, 0.5 padding, offsets (dst - new) / 2 */
+#define LN_PRE_RESIZE 1       /* Darknet float resize to exactly dst_w x dst_h (align-corners bilinear) */
+#define LN_PRE_RESIZE_EXACT 2 /* OpenCV INTER_LINEAR_EXACT on the bytes, then byte / 255 */
+int32_t ln_image_preprocess_u8(ln_ctx* ctx, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths,
+                               const int32_t* heights, int32_t count, int32_t mode, int32_t dst_w, int32_t dst_h, ln_tensor** out);
+
 /* ---- whole network: GpuExecutableNetwork<B> ------------------------------------------ */
 /* GpuExecutableNetwork::new (runtime/gpu_state.rs:8) from cfg text; `batch` > 0 overrides [net] batch
    (Network::with_batch, model.rs:3256).  precision: LN_F32 (trait-faithful f32 NCHW path), LN_Q8 or LN_F8. */
@@ -263,6 +273,10 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
                       const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host);
 int32_t ln_net_detect_device(ln_net* net, const ln_tensor* input, const int32_t* image_w, const int32_t* image_h,
                              const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host);
+/* ln_image_preprocess_u8 (to the network's input size) followed by ln_net_detect_device; the records are scaled to each
+   image's own size (widths / heights), as `lightnet-rs detect-image` does (lightnet-cli/src/main.rs: load, letterbox, detect). */
+int32_t ln_net_detect_u8(ln_net* net, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
+                         int32_t mode, const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host);
 /* Device time in ms of the most recent ln_net_forward* / ln_net_detect* call, by phase
    (0 = layers, 1 = decode+NMS), measured with CUDA events on the ctx stream. */
 int32_t ln_net_last_times(const ln_net* net, float times_ms[2]);

@@ -23,6 +23,24 @@ ACTIVATIONS = {"linear": 0, "logistic": 1, "leaky": 2, "mish": 3, "swish": 4, "r
 STATUS = {0: "ok", 1: "shape", 2: "cuda", 3: "timeout", 4: "unsupported", 5: "argument", 6: "parse"}
 
 
+LN_PRE_LETTERBOX, LN_PRE_RESIZE, LN_PRE_RESIZE_EXACT = 0, 1, 2
+
+
+def pack_u8_images(images):
+    """Concatenates interleaved u8 RGB images into one byte buffer; returns (bytes, offsets int64, widths int32, heights int32)."""
+    images = [np.ascontiguousarray(im, np.uint8) for im in images]
+    for im in images:
+        if im.ndim != 3 or im.shape[2] != 3:
+            raise ValueError("expected [height, width, 3] uint8 images")
+    sizes = [im.size for im in images]
+    offsets = np.zeros(len(images), np.int64)
+    offsets[1:] = np.cumsum(sizes[:-1])
+    flat = np.concatenate([im.ravel() for im in images]) if images else np.zeros(0, np.uint8)
+    widths = np.array([im.shape[1] for im in images], np.int32)
+    heights = np.array([im.shape[0] for im in images], np.int32)
+    return flat, offsets, widths, heights
+
+
 class BackendError(RuntimeError):
     """Non-zero status from the C ABI (maps to `Result::Err(Self::Error)` of the reference traits)."""
 
@@ -56,6 +74,8 @@ SYMBOLS = {
     "ln_ctx_stream": (C.c_void_p, [_VP]),
     "ln_ctx_set_exact_epilogue": (C.c_int32, [_VP, C.c_int32]),
     "ln_ctx_set_nms_pool_entries": (C.c_int32, [_VP, C.c_int64]),
+    "ln_image_preprocess_u8": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _VP]),
+    "ln_net_detect_u8": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_int32, _VP, _VP, _VP]),
     "ln_ctx_set_kernel_timing": (C.c_int32, [_VP, C.c_int32]),
     "ln_ctx_last_kernel_ms": (C.c_int32, [_VP, C.POINTER(C.c_float)]),
     "ln_ctx_launch_count": (C.c_int64, [_VP]),
@@ -238,6 +258,13 @@ class B200Backend:
         ms = C.c_float()
         self._check(self.lib.ln_ctx_last_kernel_ms(self.ctx, C.byref(ms)))
         return float(ms.value)
+
+    # ---- image pre-processing (PlanarRgbImage::letterbox / resize / resize_linear_exact) ---------------
+    def preprocess_u8(self, images, dst_w, dst_h, mode=LN_PRE_LETTERBOX):
+        """images: list of uint8 arrays [h, w, 3] (interleaved RGB, any sizes) -> f32 Tensor [n, 3, dst_h, dst_w]."""
+        flat, offsets, widths, heights = pack_u8_images(images)
+        return self._out(self.lib.ln_image_preprocess_u8, _ptr(flat), _ptr(offsets), _ptr(widths), _ptr(heights), len(images), mode,
+                         dst_w, dst_h)
 
     def set_nms_pool_entries(self, entries: int):
         """Candidates per image the NMS selection pool holds (0 = automatic); results do not depend on it."""
@@ -512,6 +539,18 @@ class GpuExecutableNetwork:
                       max_per_image=1024):
         return self._detect(self.lib.ln_net_detect_device, t.h, image_w, image_h, confidence_threshold, nms_threshold, letterbox,
                             top_k, max_per_image)
+
+    def detect_u8(self, images, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0, max_per_image=1024,
+                  mode=LN_PRE_LETTERBOX, packed=None):
+        """Pre-processing on the device + detect for a batch of uint8 [h, w, 3] images (or `packed` = pack_u8_images(images),
+        e.g. kept in pinned memory by a caller that reuses it); boxes come back in each image's own pixel coordinates."""
+        flat, offsets, widths, heights = packed if packed is not None else pack_u8_images(images)
+        opts = ln_detect_options(confidence_threshold, nms_threshold, int(letterbox), top_k, max_per_image)
+        rec = np.empty((self.batch, max_per_image, 7), np.float32)
+        cnt = np.zeros(self.batch, np.int32)
+        self.backend._check(self.lib.ln_net_detect_u8(self.h, _ptr(flat), _ptr(offsets), _ptr(widths), _ptr(heights), mode, C.byref(opts),
+                                                      _ptr(rec), _ptr(cnt)))
+        return [rec[b, :cnt[b]].copy() for b in range(self.batch)]
 
     def set_cuda_graph(self, on: bool):
         self.backend._check(self.lib.ln_net_set_cuda_graph(self.h, int(on)))

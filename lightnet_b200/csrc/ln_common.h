@@ -72,6 +72,8 @@ struct ln_conv_weights {
 };
 
 int ln_fail(ln_ctx* ctx, int code, const char* fmt, ...);
+int ln_image_preprocess_into(ln_ctx* ctx, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
+                             int32_t count, int32_t mode, int32_t dst_w, int32_t dst_h, float* dst);
 void* ln_pool_alloc(ln_ctx* ctx, size_t bytes);
 void ln_pool_free(ln_ctx* ctx, void* p, size_t bytes);
 ln_tensor* ln_tensor_new(ln_ctx* ctx, int dtype, int64_t n, int64_t c, int64_t h, int64_t w);  // allocates storage

@@ -1264,6 +1264,21 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
     return ln_net_detect_device(net, net->input_dev, image_w, image_h, opts, records_host, counts_host);
 }
 
+int32_t ln_net_detect_u8(ln_net* net, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
+                         int32_t mode, const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host) {
+    if (!net || !pixels_host || !offsets || !widths || !heights) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_detect_u8: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    if (net->channels != 3) return ln_fail(ctx, LN_ERR_SHAPE, "ln_net_detect_u8: the network takes %d channels, RGB images have 3", net->channels);
+    cudaSetDevice(ctx->device);
+    if (!net->input_dev) {
+        net->input_dev = ln_tensor_new(ctx, LN_F32, net->batch, net->channels, net->height, net->width);
+        if (!net->input_dev) return LN_ERR_CUDA;
+    }
+    int rc = ln_image_preprocess_into(ctx, pixels_host, offsets, widths, heights, net->batch, mode, net->width, net->height, (float*)net->input_dev->ptr);
+    if (rc) return rc;
+    return ln_net_detect_device(net, net->input_dev, widths, heights, opts, records_host, counts_host);
+}
+
 int32_t ln_net_set_host_pipeline(ln_net* net, int32_t on) {
     if (!net) return LN_ERR_ARG;
     net->host_pipeline = on != 0;

@@ -1444,6 +1444,114 @@ void orc_conv_f8_acc(const uint8_t* x, int B, int C, int H, int W, const uint8_t
                 }
 }
 
+// ---------------------------------------------------------------------------
+// Image pre-processing (lightnet-runtime/src/image.rs): u8 interleaved RGB -> planar f32, Darknet's float resize,
+// OpenCV's INTER_LINEAR_EXACT resize, letterbox.  Same operations in the same order as the reference, f32 throughout.
+// ---------------------------------------------------------------------------
+
+// image.rs:57-89 from_interleaved_rgb_u8: planar[c][y][x] = byte / 255.0
+void orc_image_from_u8(const uint8_t* rgb, int w, int h, float* planar) {
+    const size_t plane = (size_t)w * h;
+    for (size_t i = 0; i < plane; ++i)
+        for (int c = 0; c < 3; ++c) planar[c * plane + i] = (float)rgb[i * 3 + c] / 255.0f;
+}
+
+// Rust's `x as usize` for a float: NaN and negatives become 0, values beyond the range saturate (here: to INT_MAX).
+static inline int f32_as_index(float v) {
+    if (!(v > 0.0f)) return 0;
+    if (v >= 2147483520.0f) return 2147483647;
+    return (int)v;
+}
+
+// image.rs:95-151 resize: align-corners bilinear, horizontal pass into an intermediate plane, then vertical.
+// (Resizing to a width or height of 1 from a larger source multiplies 0 by an infinite scale: the reference then produces
+// NaN pixels, and so does this restatement.)
+void orc_image_resize(const float* src, int sw, int sh, int channels, int w, int h, float* out) {
+    if (sw == w && sh == h) { std::memcpy(out, src, (size_t)sw * sh * channels * 4); return; }
+    const float w_scale = ((float)sw - 1.0f) / ((float)w - 1.0f);
+    const float h_scale = ((float)sh - 1.0f) / ((float)h - 1.0f);
+    std::vector<float> part((size_t)w * sh * channels);
+    for (int ch = 0; ch < channels; ++ch) {
+        for (int y = 0; y < sh; ++y) {
+            const float* row = src + ((size_t)ch * sh + y) * sw;
+            float* dst = part.data() + ((size_t)ch * sh + y) * w;
+            for (int c = 0; c < w; ++c) {
+                if (c == w - 1 || sw == 1) dst[c] = row[sw - 1];
+                else {
+                    const float sx = (float)c * w_scale;
+                    const int ix = f32_as_index(sx);
+                    const float dx = sx - (float)ix;
+                    dst[c] = (1.0f - dx) * row[ix] + dx * row[ix + 1];
+                }
+            }
+        }
+        for (int y = 0; y < h; ++y) {
+            const float sy = sh == 1 ? 0.0f : (float)y * h_scale;
+            const int iy = f32_as_index(sy);
+            const float dy = sy - (float)iy;
+            const float* row0 = part.data() + ((size_t)ch * sh + iy) * w;
+            float* dst = out + ((size_t)ch * h + y) * w;
+            for (int x = 0; x < w; ++x) dst[x] = (1.0f - dy) * row0[x];
+            if (y == h - 1 || sh == 1) continue;
+            const float* row1 = part.data() + ((size_t)ch * sh + iy + 1) * w;
+            for (int x = 0; x < w; ++x) dst[x] += dy * row1[x];
+        }
+    }
+}
+
+// image.rs:307-327 exact_coeffs: OpenCV INTER_LINEAR_EXACT taps (x0, x1, c0, c1), c0 + c1 == 256.
+static void exact_coeffs(int src, int dst, std::vector<int>& x0s, std::vector<int>& x1s, std::vector<uint32_t>& c0s, std::vector<uint32_t>& c1s) {
+    x0s.resize(dst); x1s.resize(dst); c0s.resize(dst); c1s.resize(dst);
+    for (int d = 0; d < dst; ++d) {
+        const double fsx = ((double)d + 0.5) * (double)src / (double)dst - 0.5;
+        double x0 = std::floor(fsx);
+        double fx = fsx - x0;
+        if (x0 < 0.0) { x0 = 0.0; fx = 0.0; }
+        if (x0 >= (double)src - 1.0) { x0 = (double)src - 1.0; fx = 0.0; }
+        const int i0 = (int)x0;
+        const uint32_t c1 = (uint32_t)std::floor(fx * 256.0 + 0.5);
+        x0s[d] = i0; x1s[d] = std::min(i0 + 1, src - 1); c0s[d] = 256 - c1; c1s[d] = c1;
+    }
+}
+
+// image.rs:157-190 resize_linear_exact on the u8 source: horizontal pass in 1/256, vertical in 1/65536, rounded.
+void orc_image_resize_exact_u8(const uint8_t* src, int sw, int sh, int w, int h, uint8_t* out) {
+    if (sw == w && sh == h) { std::memcpy(out, src, (size_t)sw * sh * 3); return; }
+    std::vector<int> x0, x1, y0, y1;
+    std::vector<uint32_t> cx0, cx1, cy0, cy1;
+    exact_coeffs(sw, w, x0, x1, cx0, cx1);
+    exact_coeffs(sh, h, y0, y1, cy0, cy1);
+    std::vector<uint32_t> tmp((size_t)sh * w * 3);
+    for (int y = 0; y < sh; ++y)
+        for (int x = 0; x < w; ++x)
+            for (int ch = 0; ch < 3; ++ch)
+                tmp[((size_t)y * w + x) * 3 + ch] = (uint32_t)src[((size_t)y * sw + x0[x]) * 3 + ch] * cx0[x] + (uint32_t)src[((size_t)y * sw + x1[x]) * 3 + ch] * cx1[x];
+    for (int y = 0; y < h; ++y)
+        for (int i = 0; i < w * 3; ++i) {
+            const uint32_t v = tmp[(size_t)y0[y] * w * 3 + i] * cy0[y] + tmp[(size_t)y1[y] * w * 3 + i] * cy1[y];
+            out[(size_t)y * w * 3 + i] = (uint8_t)((v + 32768u) >> 16);
+        }
+}
+
+// image.rs:329-341 fit_inside
+void orc_image_fit_inside(int sw, int sh, int dw, int dh, int* nw, int* nh) {
+    if (((float)dw / (float)sw) < ((float)dh / (float)sh)) { *nw = std::max(dw, 1); *nh = std::max((int)((long long)sh * dw / sw), 1); }
+    else { *nw = std::max((int)((long long)sw * dh / sh), 1); *nh = std::max(dh, 1); }
+}
+
+// image.rs:203-229 letterbox: float resize to fit, 0.5 padding, integer offsets (dst - new) / 2.
+void orc_image_letterbox(const float* src, int sw, int sh, int channels, int w, int h, float* out) {
+    int nw, nh;
+    orc_image_fit_inside(sw, sh, w, h, &nw, &nh);
+    std::vector<float> resized((size_t)nw * nh * channels);
+    orc_image_resize(src, sw, sh, channels, nw, nh, resized.data());
+    for (size_t i = 0; i < (size_t)w * h * channels; ++i) out[i] = 0.5f;
+    const int xo = (w - nw) / 2, yo = (h - nh) / 2;
+    for (int ch = 0; ch < channels; ++ch)
+        for (int y = 0; y < nh; ++y)
+            std::memcpy(out + ((size_t)ch * h + y + yo) * w + xo, resized.data() + ((size_t)ch * nh + y) * nw, (size_t)nw * 4);
+}
+
 // Single f32 conv layer in the reference loop order (folded weights + bias), NCHW.
 void orc_conv_f32(const float* x, int B, int C, int H, int W, const float* w, const float* bias, int F, int k, int sx, int sy,
                   int pad, int groups, int act, float* y) {

@@ -70,6 +70,11 @@ def lib():
                                       C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_int]
         L.orc_nms_records.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_int]
         L.orc_conv_q8_acc.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
+        L.orc_image_from_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.orc_image_resize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.orc_image_resize_exact_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.orc_image_letterbox.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.orc_image_fit_inside.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         L.orc_f8_epilogue.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
         L.orc_conv_f8_acc.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p, C.c_void_p]
         L.orc_q8_epilogue.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float,
@@ -397,6 +402,47 @@ def f32_to_e4m3_fast(v):
 def e4m3_table():
     """Value of every E4M3 code (NaN codes as nan)."""
     return np.array([e4m3_to_f32(c) for c in range(256)], np.float32)
+
+
+def image_from_u8(rgb):
+    """u8 [H, W, 3] interleaved -> f32 [3, H, W] (PlanarRgbImage::from_interleaved_rgb_u8)."""
+    rgb = np.ascontiguousarray(rgb, np.uint8)
+    h, w, _ = rgb.shape
+    out = np.zeros((3, h, w), np.float32)
+    lib().orc_image_from_u8(_p(rgb), w, h, _p(out))
+    return out
+
+
+def image_resize(planar, w, h):
+    """Darknet float resize of f32 [C, H, W] (PlanarRgbImage::resize)."""
+    planar = np.ascontiguousarray(planar, np.float32)
+    c, sh, sw = planar.shape
+    out = np.zeros((c, h, w), np.float32)
+    lib().orc_image_resize(_p(planar), sw, sh, c, w, h, _p(out))
+    return out
+
+
+def image_resize_exact_u8(rgb, w, h):
+    """OpenCV INTER_LINEAR_EXACT on u8 [H, W, 3] (PlanarRgbImage::resize_linear_exact)."""
+    rgb = np.ascontiguousarray(rgb, np.uint8)
+    sh, sw, _ = rgb.shape
+    out = np.zeros((h, w, 3), np.uint8)
+    lib().orc_image_resize_exact_u8(_p(rgb), sw, sh, w, h, _p(out))
+    return out
+
+
+def image_letterbox(planar, w, h):
+    planar = np.ascontiguousarray(planar, np.float32)
+    c, sh, sw = planar.shape
+    out = np.zeros((c, h, w), np.float32)
+    lib().orc_image_letterbox(_p(planar), sw, sh, c, w, h, _p(out))
+    return out
+
+
+def image_fit_inside(sw, sh, dw, dh):
+    nw, nh = C.c_int(), C.c_int()
+    lib().orc_image_fit_inside(sw, sh, dw, dh, C.byref(nw), C.byref(nh))
+    return nw.value, nh.value
 
 
 def set_threads(n):

@@ -347,3 +347,51 @@ def test_q8_conv_accumulators_match_numpy():
                 patch = xp[:, :, ky:ky + stride * oh:stride, kx:kx + stride * ow:stride]
                 ref += np.einsum("bchw,fc->bfhw", patch, w[:, :, ky, kx].astype(np.int64))
         assert np.array_equal(acc, ref)
+
+
+# ---------------------------------------------------------------------------------------- image pre-processing
+# Known answers of lightnet-runtime/src/image.rs:362-441 (fixtures repackaged by tests/golden/make_resize_fixtures.py).
+
+def _resize_fixtures():
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "resize_fixtures.npz"))
+
+
+def test_image_from_u8_kat():
+    # converts_interleaved_rgb_to_planar (image.rs:415-420)
+    out = orc.image_from_u8(np.array([[[255, 128, 0]]], np.uint8))
+    assert out.ravel().tolist() == [1.0, np.float32(128.0) / np.float32(255.0), 0.0]
+
+
+def test_image_resize_linear_exact_matches_opencv_bytes():
+    # resize_linear_exact_matches_opencv_bytes (image.rs:365-378): byte for byte
+    fx = _resize_fixtures()
+    for i in range(3):
+        for w, h in ((40, 28), (130, 100)):
+            got = orc.image_resize_exact_u8(fx["src%d" % i], w, h)
+            assert np.array_equal(got, fx["exact%d_%dx%d" % (i, w, h)]), (i, w, h)
+
+
+def test_image_resize_matches_darknet_float_resize():
+    # resize_matches_darknet_float_resize (image.rs:383-402): max |diff| <= 1e-6
+    fx = _resize_fixtures()
+    for i in range(3):
+        src = orc.image_from_u8(fx["src%d" % i])
+        for w, h in ((40, 28), (50, 60)):
+            got = orc.image_resize(src, w, h)
+            assert np.abs(got - fx["float%d_%dx%d" % (i, w, h)]).max() <= 1e-6, (i, w, h)
+
+
+def test_image_letterbox_kats():
+    fx = _resize_fixtures()
+    src = orc.image_from_u8(fx["src0"])
+    # letterbox_uses_half_gray_and_integer_offsets (image.rs:404-413): 96x72 into 50x60 -> 50x37 at y offset 11
+    assert orc.image_fit_inside(96, 72, 50, 60) == (50, 37)
+    boxed, resized = orc.image_letterbox(src, 50, 60), orc.image_resize(src, 50, 37)
+    assert boxed[0, 0, 0] == 0.5 and boxed[2, 10, 49] == 0.5 and boxed[2, 48, 0] == 0.5
+    assert boxed[1, 11, 7] == resized[1, 0, 7] and boxed[1, 47, 7] == resized[1, 36, 7]
+    # resizes_image_bilinearly / letterboxes_image_with_gray_padding (image.rs:422-441)
+    two = orc.image_from_u8(np.array([[[0, 0, 0], [255, 0, 0]]], np.uint8))
+    assert abs(orc.image_resize(two, 3, 1)[0, 0, 1] - 0.5) < 0.01
+    red = orc.image_from_u8(np.array([[[255, 0, 0], [255, 0, 0]]], np.uint8))
+    lb = orc.image_letterbox(red, 2, 2)
+    assert lb.shape == (3, 2, 2) and abs(lb.ravel()[0] - 1.0) < 0.01 and abs(lb.ravel()[2] - 0.5) < 0.01
