@@ -37,14 +37,14 @@ def test_float_resize_and_letterbox_bit_identical_to_the_oracle(be):
     rng = np.random.default_rng(1)
     images = [fx["src0"], fx["src1"], rng.integers(0, 256, (33, 57, 3), dtype=np.uint8), rng.integers(0, 256, (1, 9, 3), dtype=np.uint8),
               rng.integers(0, 256, (50, 1, 3), dtype=np.uint8), rng.integers(0, 256, (64, 48, 3), dtype=np.uint8)]
-    # (a destination height of 1 from a taller source makes the reference multiply 0 by an infinite scale: NaN pixels, not tested)
+    # (a fitted height of 1 from a taller source makes the reference multiply 0 by an infinite scale: NaN pixels on both sides)
     for w, h in ((50, 60), (40, 28), (64, 48), (1, 9), (7, 128)):
         got = be.download_f32(be.preprocess_u8(images, w, h, ln.LN_PRE_RESIZE))
         box = be.download_f32(be.preprocess_u8(images, w, h, ln.LN_PRE_LETTERBOX))
         for i, im in enumerate(images):
             planar = orc.image_from_u8(im)
-            assert np.array_equal(got[i], orc.image_resize(planar, w, h)), ("resize", i, w, h)
-            assert np.array_equal(box[i], orc.image_letterbox(planar, w, h)), ("letterbox", i, w, h)
+            assert np.array_equal(got[i], orc.image_resize(planar, w, h), equal_nan=True), ("resize", i, w, h)
+            assert np.array_equal(box[i], orc.image_letterbox(planar, w, h), equal_nan=True), ("letterbox", i, w, h)
     # the reference's float fixtures, within its own tolerance
     got = be.download_f32(be.preprocess_u8([fx["src2"]], 50, 60, ln.LN_PRE_RESIZE))
     assert np.abs(got[0] - fx["float2_50x60"]).max() <= 1e-6
