@@ -40,6 +40,7 @@ WORKLOADS = {
     "yolov7-640-fp8": dict(model="yolov7", size=640, batch=32, precision="fp8",
                            metric="images/sec YOLOv7-640 FP8 E4M3 (conv stack + yolo decode + NMS)"),
     "nms-stress": dict(model=None, size=640, batch=256, precision="f32", metric="decode + NMS GB/s (25200 candidates x 80 classes per image)"),
+    "preprocess": dict(model=None, size=608, batch=64, precision="f32", metric="images/sec letterbox pre-processing (640x480 8-bit RGB -> 608x608 f32 NCHW)"),
     "conv-sweep": dict(model=None, size=0, batch=16, precision="int8+fp8", metric="TOP/s single-layer implicit-GEMM convolution (bias + leaky epilogue)"),
 }
 # (channels, height, width, filters, kernel, stride, pad) of the single-layer sweep
@@ -184,6 +185,20 @@ def run_reference(args, rank):
     if args.workload == "conv-sweep":
         print(json.dumps({"impl": "reference", "unavailable": "the reference has no int8 / FP8 convolution; the sweep has no CPU arm"}))
         return
+    if args.workload == "preprocess":
+        from oracle import oracle_api as orc
+        rng = np.random.default_rng(300)
+        ims = [rng.integers(0, 256, (480, 640, 3), dtype=np.uint8) for _ in range(8)]
+        t0 = time.perf_counter()
+        for im in ims:
+            orc.image_letterbox(orc.image_from_u8(im), 608, 608)
+        v = 8.0 / (time.perf_counter() - t0)
+        print(json.dumps({"impl": "reference", "metric": WORKLOADS["preprocess"]["metric"], "value": v, "unit": "images/s", "n_gpus": args.gpus, "steps": 1,
+                          "warmup": 0, "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                          "data": "synthetic", "config": {"workload": "letterbox of random 640x480 8-bit RGB images to 608x608 f32 NCHW"},
+                          "cpu_baseline": {"value": v, "unit": "images/s", "cores": 1, "kind": "port", "sample": "8 images, one thread"},
+                          "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
     for _ in range(steps):
         if wl["model"] is None:
             dt, note = cpu_stress_sample(1)
@@ -311,6 +326,54 @@ def run_conv_sweep(args, be, rank, world, local_rank):
                          "frac": best["tops"] / peak, "traffic": None, "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf)}}))
 
 
+def run_preprocess(args, be, rank, world, local_rank):
+    """ln_image_preprocess_u8 on a batch of synthetic 640x480 8-bit images in pinned host memory (the upload is inside the call);
+    CPU arm: the oracle's restatement of PlanarRgbImage::from_interleaved_rgb_u8 + letterbox on one image, one thread."""
+    import torch
+
+    import lightnet_b200 as ln
+
+    B = args.batch
+    rng = np.random.default_rng(300 + rank)
+    images = [rng.integers(0, 256, (480, 640, 3), dtype=np.uint8) for _ in range(B)]
+    flat, off, w, h = ln.pack_u8_images(images)
+    flat = torch.from_numpy(flat).pin_memory().numpy()
+    stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", local_rank))
+    timed = make_timer(stream, world)
+    size = WORKLOADS["preprocess"]["size"]
+
+    def call():
+        return be._out(be.lib.ln_image_preprocess_u8, ln._ptr(flat), ln._ptr(off), ln._ptr(w), ln._ptr(h), B, ln.LN_PRE_LETTERBOX, size, size)
+
+    for _ in range(max(args.warmup, 3)):
+        call()
+    launches0 = be.launch_count
+    ms = timed(call, args.steps)
+    launches = be.launch_count - launches0
+    out_bytes = B * 3 * size * size * 4
+    _, hbm_gbs, basis = measured_peaks()
+    if rank == 0:
+        line = {"metric": WORKLOADS["preprocess"]["metric"], "value": B * world * args.steps / (ms * 1e-3), "unit": "images/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "letterbox of %d random 640x480 8-bit RGB images to %dx%d f32 NCHW" % (B, size, size), "batch_per_gpu": B,
+                           "l2": "output larger than L2 (%.0f MB)" % (out_bytes / 1e6)},
+                "e2e": {"value": B * world * args.steps / (ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(flat.nbytes), "d2h_bytes_per_step": 0,
+                        "api": "ln_image_preprocess_u8 (the timed call takes host pixels: value and e2e are the same measurement)"},
+                "gpu_launches": int(launches),
+                "roofline": {"bound": "hbm", "kernel": "image_float_resize_kernel + the upload of the pixels", "achieved": (flat.nbytes + out_bytes) * args.steps / (ms * 1e-3) / 1e9,
+                             "peak": hbm_gbs, "unit": "GB/s", "frac": (flat.nbytes + out_bytes) * args.steps / (ms * 1e-3) / 1e9 / hbm_gbs, "traffic": None,
+                             "peak_basis": "%s copy bandwidth; the call is bound by the 59 MB upload over PCIe, not by HBM" % basis}}
+        if not args.no_cpu_baseline:
+            from oracle import oracle_api as orc
+            t0 = time.perf_counter()
+            for im in images[:8]:
+                orc.image_letterbox(orc.image_from_u8(im), size, size)
+            dt = (time.perf_counter() - t0) / 8
+            line["cpu_baseline"] = {"value": 1.0 / dt, "unit": "images/s", "cores": 1, "kind": "port", "sample": "8 of the %d images, one thread (the reference's resize is serial)" % B}
+        print(json.dumps(line))
+
+
 def run_nms_stress(args, be, rank, world, local_rank):
     """decode + NMS alone on synthetic heads (resident in HBM for `value`; uploaded from pinned host memory inside the timed
     region for `e2e`).  The heads of 256 images are 2.19 GB, far larger than L2."""
@@ -410,7 +473,7 @@ def main():
     B = args.batch
     be = ln.B200Backend(local_rank)
     if wl["model"] is None:
-        (run_conv_sweep if args.workload == "conv-sweep" else run_nms_stress)(args, be, rank, world, local_rank)
+        {"conv-sweep": run_conv_sweep, "preprocess": run_preprocess}.get(args.workload, run_nms_stress)(args, be, rank, world, local_rank)
         if world > 1:
             dist.destroy_process_group()
         return

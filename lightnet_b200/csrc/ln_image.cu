@@ -17,51 +17,63 @@ struct ImageMeta {
     int xo, yo;        // where the resized image sits in the destination
 };
 
-__device__ __forceinline__ float src_value(const uint8_t* img, int sw, int y, int x, int c) {
-    return __fdiv_rn((float)img[((size_t)y * sw + x) * 3 + c], 255.0f);
+// byte / 255.0f for every byte value, filled once per block (an IEEE division per source tap would dominate the kernel)
+__device__ __forceinline__ void fill_unit_table(float* table) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) table[i] = __fdiv_rn((float)i, 255.0f);
+    __syncthreads();
+}
+
+__device__ __forceinline__ float src_value(const float* table, const uint8_t* img, int sw, int y, int x, int c) {
+    return table[img[((size_t)y * sw + x) * 3 + c]];
 }
 
 // image.rs:108-127: one value of the horizontally resized plane
-__device__ __forceinline__ float horizontal(const uint8_t* img, int sw, int nw, float w_scale, int y, int col, int c) {
-    if (col == nw - 1 || sw == 1) return src_value(img, sw, y, sw - 1, c);
+__device__ __forceinline__ float horizontal(const float* table, const uint8_t* img, int sw, int nw, float w_scale, int y, int col, int c) {
+    if (col == nw - 1 || sw == 1) return src_value(table, img, sw, y, sw - 1, c);
     const float sx = __fmul_rn((float)col, w_scale);
     const int ix = (int)sx;  // NaN -> 0, like the reference's saturating cast
     const float dx = __fsub_rn(sx, (float)ix);
     // the indices are clamped for memory safety only: for every size the reference accepts they are in range already
     const int i0 = min(max(ix, 0), sw - 1), i1 = min(i0 + 1, sw - 1);
-    return __fadd_rn(__fmul_rn(__fsub_rn(1.0f, dx), src_value(img, sw, y, i0, c)), __fmul_rn(dx, src_value(img, sw, y, i1, c)));
+    return __fadd_rn(__fmul_rn(__fsub_rn(1.0f, dx), src_value(table, img, sw, y, i0, c)), __fmul_rn(dx, src_value(table, img, sw, y, i1, c)));
 }
 
-// Darknet float resize (modes letterbox and resize): one thread per destination pixel, three channels.
+constexpr int kPixelsPerThread = 8;  // destination pixels per thread (amortises the table fill and the per-image scales)
+
+// Darknet float resize (modes letterbox and resize): a thread takes kPixelsPerThread destination pixels, three channels each.
 __global__ void __launch_bounds__(256) image_float_resize_kernel(const uint8_t* __restrict__ pixels, const ImageMeta* __restrict__ meta, int W, int H,
                                                                  float* __restrict__ out) {
+    __shared__ float table[256];
+    fill_unit_table(table);
     const int n = blockIdx.y;
     const ImageMeta m = meta[n];
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint8_t* img = pixels + m.offset;
+    const float w_scale = __fdiv_rn(__fsub_rn((float)m.sw, 1.0f), __fsub_rn((float)m.nw, 1.0f));
+    const float h_scale = __fdiv_rn(__fsub_rn((float)m.sh, 1.0f), __fsub_rn((float)m.nh, 1.0f));
+    for (int k = 0; k < kPixelsPerThread; ++k) {
+    const int p = (blockIdx.x * kPixelsPerThread + k) * blockDim.x + threadIdx.x;
     if (p >= W * H) return;
     const int y = p / W, x = p - y * W;
     float* o = out + (size_t)n * 3 * W * H + p;
     const int ry = y - m.yo, rx = x - m.xo;
     if (ry < 0 || ry >= m.nh || rx < 0 || rx >= m.nw) {
         o[0] = 0.5f; o[(size_t)W * H] = 0.5f; o[(size_t)2 * W * H] = 0.5f;  // letterbox padding (image.rs:216)
-        return;
+        continue;
     }
-    const uint8_t* img = pixels + m.offset;
     if (m.sw == m.nw && m.sh == m.nh) {  // resize returns the source unchanged (image.rs:102-104)
-        for (int c = 0; c < 3; ++c) o[(size_t)c * W * H] = src_value(img, m.sw, ry, rx, c);
-        return;
+        for (int c = 0; c < 3; ++c) o[(size_t)c * W * H] = src_value(table, img, m.sw, ry, rx, c);
+        continue;
     }
-    const float w_scale = __fdiv_rn(__fsub_rn((float)m.sw, 1.0f), __fsub_rn((float)m.nw, 1.0f));
-    const float h_scale = __fdiv_rn(__fsub_rn((float)m.sh, 1.0f), __fsub_rn((float)m.nh, 1.0f));
     const float sy = m.sh == 1 ? 0.0f : __fmul_rn((float)ry, h_scale);
     const int iy = (int)sy;
     const float dy = __fsub_rn(sy, (float)iy);
     const bool last_row = ry == m.nh - 1 || m.sh == 1;
     const int y0 = min(max(iy, 0), m.sh - 1), y1 = min(y0 + 1, m.sh - 1);  // clamped for memory safety only
     for (int c = 0; c < 3; ++c) {
-        float v = __fmul_rn(__fsub_rn(1.0f, dy), horizontal(img, m.sw, m.nw, w_scale, y0, rx, c));
-        if (!last_row) v = __fadd_rn(v, __fmul_rn(dy, horizontal(img, m.sw, m.nw, w_scale, y1, rx, c)));
+        float v = __fmul_rn(__fsub_rn(1.0f, dy), horizontal(table, img, m.sw, m.nw, w_scale, y0, rx, c));
+        if (!last_row) v = __fadd_rn(v, __fmul_rn(dy, horizontal(table, img, m.sw, m.nw, w_scale, y1, rx, c)));
         o[(size_t)c * W * H] = v;
+    }
     }
 }
 
@@ -81,16 +93,19 @@ __device__ __forceinline__ void exact_tap(int d, int src, int dst, int* x0, int*
 // OpenCV INTER_LINEAR_EXACT on the bytes (image.rs:157-190), then byte / 255: one thread per destination pixel.
 __global__ void __launch_bounds__(256) image_exact_resize_kernel(const uint8_t* __restrict__ pixels, const ImageMeta* __restrict__ meta, int W, int H,
                                                                  float* __restrict__ out) {
+    __shared__ float table[256];
+    fill_unit_table(table);
     const int n = blockIdx.y;
     const ImageMeta m = meta[n];
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint8_t* img = pixels + m.offset;
+    for (int k = 0; k < kPixelsPerThread; ++k) {
+    const int p = (blockIdx.x * kPixelsPerThread + k) * blockDim.x + threadIdx.x;
     if (p >= W * H) return;
     const int y = p / W, x = p - y * W;
     float* o = out + (size_t)n * 3 * W * H + p;
-    const uint8_t* img = pixels + m.offset;
     if (m.sw == W && m.sh == H) {
-        for (int c = 0; c < 3; ++c) o[(size_t)c * W * H] = src_value(img, m.sw, y, x, c);
-        return;
+        for (int c = 0; c < 3; ++c) o[(size_t)c * W * H] = src_value(table, img, m.sw, y, x, c);
+        continue;
     }
     int x0, x1, y0, y1;
     unsigned cx0, cx1, cy0, cy1;
@@ -100,7 +115,8 @@ __global__ void __launch_bounds__(256) image_exact_resize_kernel(const uint8_t* 
         const unsigned t0 = (unsigned)img[((size_t)y0 * m.sw + x0) * 3 + c] * cx0 + (unsigned)img[((size_t)y0 * m.sw + x1) * 3 + c] * cx1;
         const unsigned t1 = (unsigned)img[((size_t)y1 * m.sw + x0) * 3 + c] * cx0 + (unsigned)img[((size_t)y1 * m.sw + x1) * 3 + c] * cx1;
         const unsigned v = (t0 * cy0 + t1 * cy1 + 32768u) >> 16;
-        o[(size_t)c * W * H] = __fdiv_rn((float)(uint8_t)v, 255.0f);
+        o[(size_t)c * W * H] = table[v & 0xFFu];
+    }
     }
 }
 
@@ -147,7 +163,7 @@ int ln_image_preprocess_into(ln_ctx* ctx, const uint8_t* pixels_host, const int6
     cudaError_t e = cudaMemcpyAsync(dev, meta.data(), count * sizeof(ImageMeta), cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(dev + meta_bytes, pixels_host, (size_t)total, cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess) {
-        const dim3 grid((unsigned)(((int64_t)dst_w * dst_h + 255) / 256), (unsigned)count);
+        const dim3 grid((unsigned)(((int64_t)dst_w * dst_h + 256 * kPixelsPerThread - 1) / (256 * kPixelsPerThread)), (unsigned)count);
         if (mode == LN_PRE_RESIZE_EXACT) image_exact_resize_kernel<<<grid, 256, 0, ctx->stream>>>(dev + meta_bytes, (const ImageMeta*)dev, dst_w, dst_h, dst);
         else image_float_resize_kernel<<<grid, 256, 0, ctx->stream>>>(dev + meta_bytes, (const ImageMeta*)dev, dst_w, dst_h, dst);
         ctx->launches++;
