@@ -807,12 +807,18 @@ __global__ void __launch_bounds__(1024, 1) yolo_nms_kernel(const __grid_constant
             const int lane = threadIdx.x;
             unsigned removed = lane < 16 ? ~alive_words[lane] : 0xFFFFFFFFu;
             int kept_now = kept_before;
+            // the mask row of candidate i + 1 is fetched while candidate i is decided: the loop is a chain of dependent steps and
+            // the shared-memory latency would otherwise sit on it
+            unsigned row = lane < 16 ? mask[lane] : 0u;
             for (int i = 0; i < m && kept_now < p.k_eff; ++i) {
+                const unsigned next = (lane < 16 && i + 1 < m) ? mask[(i + 1) * 16 + lane] : 0u;
                 const unsigned r = __shfl_sync(0xffffffffu, removed, i >> 5);
-                if ((r >> (i & 31)) & 1u) continue;
-                if (lane < 16) removed |= mask[i * 16 + lane];
-                if (lane == 0) cpos[i] = kept_now;
-                ++kept_now;
+                if (!((r >> (i & 31)) & 1u)) {
+                    removed |= row;
+                    if (lane == 0) cpos[i] = kept_now;
+                    ++kept_now;
+                }
+                row = next;
             }
             if (lane == 0) s_kept = kept_now;
         }
