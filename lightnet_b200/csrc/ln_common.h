@@ -72,6 +72,9 @@ struct ln_conv_weights {
 };
 
 int ln_fail(ln_ctx* ctx, int code, const char* fmt, ...);
+int ln_image_preprocess_enqueue(ln_ctx* ctx, cudaStream_t stream, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths,
+                                const int32_t* heights, int32_t count, int32_t mode, int32_t dst_w, int32_t dst_h, float* dst, void** staging,
+                                size_t* staging_bytes);
 int ln_image_preprocess_into(ln_ctx* ctx, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
                              int32_t count, int32_t mode, int32_t dst_w, int32_t dst_h, float* dst);
 void* ln_pool_alloc(ln_ctx* ctx, size_t bytes);

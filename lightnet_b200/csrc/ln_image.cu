@@ -135,42 +135,63 @@ void fit_inside(int sw, int sh, int dw, int dh, int* nw, int* nh) {
 
 }  // namespace
 
-// Shared by the entry point below and by ln_net_detect_u8: fills `dst` (f32 [count, 3, dst_h, dst_w] on the device).
-int ln_image_preprocess_into(ln_ctx* ctx, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
-                             int32_t count, int32_t mode, int32_t dst_w, int32_t dst_h, float* dst) {
+// Enqueues upload + resize of `count` images on `stream` without synchronising.  The staging memory (metadata + pixels) comes
+// from the ctx pool and is handed back through *staging / *staging_bytes: the caller frees it once the stream has passed this work.
+int ln_image_preprocess_enqueue(ln_ctx* ctx, cudaStream_t stream, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths,
+                                const int32_t* heights, int32_t count, int32_t mode, int32_t dst_w, int32_t dst_h, float* dst, void** staging,
+                                size_t* staging_bytes) {
+    *staging = nullptr;
+    *staging_bytes = 0;
     if (mode < LN_PRE_LETTERBOX || mode > LN_PRE_RESIZE_EXACT) return ln_fail(ctx, LN_ERR_ARG, "image pre-processing: unknown mode %d", mode);
     if (dst_w < 1 || dst_h < 1) return ln_fail(ctx, LN_ERR_ARG, "resize dimensions must be non-zero");
     std::vector<ImageMeta> meta((size_t)count);
-    int64_t total = 0;
+    int64_t first = -1, last = 0;  // byte range of the pixel buffer these images occupy
     for (int i = 0; i < count; ++i) {
         if (widths[i] < 1 || heights[i] < 1) return ln_fail(ctx, LN_ERR_ARG, "source image dimensions must be non-zero");
         if (offsets[i] < 0) return ln_fail(ctx, LN_ERR_ARG, "image pre-processing: negative offset for image %d", i);
+        const int64_t end = offsets[i] + (int64_t)widths[i] * heights[i] * 3;
+        if (first < 0 || offsets[i] < first) first = offsets[i];
+        if (end > last) last = end;
+    }
+    for (int i = 0; i < count; ++i) {
         ImageMeta& m = meta[i];
-        m.offset = offsets[i]; m.sw = widths[i]; m.sh = heights[i];
+        m.offset = offsets[i] - first; m.sw = widths[i]; m.sh = heights[i];
         if (mode == LN_PRE_LETTERBOX) {
             fit_inside(m.sw, m.sh, dst_w, dst_h, &m.nw, &m.nh);
             m.xo = (dst_w - m.nw) / 2; m.yo = (dst_h - m.nh) / 2;
         } else { m.nw = dst_w; m.nh = dst_h; m.xo = 0; m.yo = 0; }
-        const int64_t end = offsets[i] + (int64_t)m.sw * m.sh * 3;
-        if (end > total) total = end;
     }
+    const int64_t total = last - first;
     cudaSetDevice(ctx->device);
     const size_t meta_bytes = (size_t)ln_round_up((int64_t)(count * sizeof(ImageMeta)), 256);
     const size_t bytes = meta_bytes + (size_t)total;
     unsigned char* dev = (unsigned char*)ln_pool_alloc(ctx, bytes);
     if (!dev) return LN_ERR_CUDA;
-    // the metadata travels through pinned memory of its own only if it outlives this call; it does not: synchronise before returning
-    cudaError_t e = cudaMemcpyAsync(dev, meta.data(), count * sizeof(ImageMeta), cudaMemcpyHostToDevice, ctx->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(dev + meta_bytes, pixels_host, (size_t)total, cudaMemcpyHostToDevice, ctx->stream);
+    *staging = dev;
+    *staging_bytes = bytes;
+    // `meta` is pageable host memory: this copy is complete (staged by the driver) when the call returns
+    cudaError_t e = cudaMemcpyAsync(dev, meta.data(), count * sizeof(ImageMeta), cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dev + meta_bytes, pixels_host + first, (size_t)total, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess) {
         const dim3 grid((unsigned)(((int64_t)dst_w * dst_h + 256 * kPixelsPerThread - 1) / (256 * kPixelsPerThread)), (unsigned)count);
-        if (mode == LN_PRE_RESIZE_EXACT) image_exact_resize_kernel<<<grid, 256, 0, ctx->stream>>>(dev + meta_bytes, (const ImageMeta*)dev, dst_w, dst_h, dst);
-        else image_float_resize_kernel<<<grid, 256, 0, ctx->stream>>>(dev + meta_bytes, (const ImageMeta*)dev, dst_w, dst_h, dst);
+        if (mode == LN_PRE_RESIZE_EXACT) image_exact_resize_kernel<<<grid, 256, 0, stream>>>(dev + meta_bytes, (const ImageMeta*)dev, dst_w, dst_h, dst);
+        else image_float_resize_kernel<<<grid, 256, 0, stream>>>(dev + meta_bytes, (const ImageMeta*)dev, dst_w, dst_h, dst);
         ctx->launches++;
         e = cudaGetLastError();
     }
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // `meta` and the caller's pixels may go away after this
-    ln_pool_free(ctx, dev, bytes);
+    if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "image pre-processing: %s", cudaGetErrorString(e));
+    return LN_OK;
+}
+
+// Shared by the entry point below and by ln_net_detect_u8: fills `dst` (f32 [count, 3, dst_h, dst_w] on the device) and waits for it.
+int ln_image_preprocess_into(ln_ctx* ctx, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
+                             int32_t count, int32_t mode, int32_t dst_w, int32_t dst_h, float* dst) {
+    void* staging = nullptr;
+    size_t staging_bytes = 0;
+    int rc = ln_image_preprocess_enqueue(ctx, ctx->stream, pixels_host, offsets, widths, heights, count, mode, dst_w, dst_h, dst, &staging, &staging_bytes);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);  // the caller's pixels may go away after this
+    if (staging) ln_pool_free(ctx, staging, staging_bytes);
+    if (rc) return rc;
     if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "image pre-processing: %s", cudaGetErrorString(e));
     return LN_OK;
 }

@@ -1274,6 +1274,8 @@ int32_t ln_net_detect_u8(ln_net* net, const uint8_t* pixels_host, const int64_t*
         net->input_dev = ln_tensor_new(ctx, LN_F32, net->batch, net->channels, net->height, net->width);
         if (!net->input_dev) return LN_ERR_CUDA;
     }
+    // (the two-half pipeline of ln_net_detect does not pay here: the 8-bit upload is a quarter of the f32 one, and two half-batch
+    // networks with two decode + NMS calls cost more than overlapping it saves -- measured 4212 against 4630 images/s)
     int rc = ln_image_preprocess_into(ctx, pixels_host, offsets, widths, heights, net->batch, mode, net->width, net->height, (float*)net->input_dev->ptr);
     if (rc) return rc;
     return ln_net_detect_device(net, net->input_dev, widths, heights, opts, records_host, counts_host);

@@ -789,3 +789,66 @@ def test_host_pipeline_gives_the_same_detections(be):
     for b in range(batch):
         assert np.array_equal(piped[b], whole[b]), b
         assert np.array_equal(piped2[b], whole[b]), b
+
+
+# ---------------------------------------------------------------------------------------- the benchmark networks themselves
+
+def test_yolov4_608_q8_bit_exact_full_network(be):
+    """BASELINE config 3 at its real size (YOLOv4, 608x608, 162 layers) on one image: with the exact epilogue the int8 heads are
+    bit-identical to the oracle's integer forward, and so are the detections.  Exercises every layout mode the planner picks
+    for this network (space-to-depth second layer, pixel groups, resident weights, fused shortcuts, SPP cascade, zero-copy routes)."""
+    cfg = zoo.yolov4_cfg(batch=1)
+    o = orc.Net(cfg, 1)
+    blob = synth.he_weights(o.layers(), 0)
+    o.set_weights(blob)
+    x = synth.uniform_images(1, 3, 608, 608, 71)
+    net = ln.GpuExecutableNetwork(be, cfg, 1, ln.LN_Q8)
+    net.load_weights(blob)
+    net.calibrate(x)
+    o.set_scales(net.scales())
+    o.forward_q8(x)
+    be.set_exact_epilogue(True)
+    try:
+        net.forward(x)
+        yolo = [i for i, l in enumerate(o.layers()) if l["kind"] == "yolo"]
+        assert len(yolo) == 3
+        for k, layer in enumerate(yolo):
+            got, ref = be.download_f32(net.head(k)), o.head_q8(layer)
+            assert np.array_equal(got, ref), layer
+        # the heads saturate with random weights (about 10^6 candidates per image): the oracle's quadratic NMS is run on the
+        # candidates that can reach the first 64 survivors, as in the stress-size test
+        specs = zoo.head_specs(cfg)
+        dev = [dict(raw=net.head(k), classes=s["classes"], anchors=s["anchors"], scale_x_y=s["scale_x_y"], new_coords=s["new_coords"])
+               for k, s in enumerate(specs)]
+        got = be.yolo_decode_nms(dev, 608, 608, 608, 608, 0.25, 0.45, True, 0, 64)[0]
+        recs = be.yolo_decode_only(dev, 0, 608, 608, 608, 608, 0.25, True)
+        top = recs[recs[:, 1] >= got[-1, 1]]
+        if top.shape[0] <= 40000:
+            ref = orc.nms_records(top, 0.45, top_k=64, skip_pass1=True)
+            assert np.array_equal(got, ref[:64])
+    finally:
+        be.set_exact_epilogue(False)
+
+
+def test_yolov7_320_f8_tracks_the_oracle(be):
+    """BASELINE config 4's network (YOLOv7, FP8 E4M3) at 320x320, one image: the heads stay within 10 % of the head's range of the
+    oracle's FP8 forward (double accumulation there, f32 tensor-core accumulation here; 105 layers of E4M3 rounding)."""
+    cfg = zoo.yolov7_cfg(320, 320, batch=1)
+    o = orc.Net(cfg, 1)
+    blob = synth.he_weights(o.layers(), 0)
+    o.set_weights(blob)
+    x = synth.uniform_images(1, 3, 320, 320, 72)
+    net = ln.GpuExecutableNetwork(be, cfg, 1, ln.LN_F8)
+    net.load_weights(blob)
+    net.calibrate(x)
+    o.set_scales(net.scales())
+    o.forward_f8(x)
+    be.set_exact_epilogue(True)
+    try:
+        net.forward(x)
+        yolo = [i for i, l in enumerate(o.layers()) if l["kind"] == "yolo"]
+        for k, layer in enumerate(yolo):
+            got, ref = be.download_f32(net.head(k)), o.head_f8(layer)
+            assert np.abs(got - ref).max() <= 0.1 * np.abs(ref).max(), (layer, float(np.abs(got - ref).max() / np.abs(ref).max()))
+    finally:
+        be.set_exact_epilogue(False)

@@ -58,21 +58,25 @@ def test_preprocess_errors(be):
         be.preprocess_u8([im], 8, 8, 7)
 
 
-def test_detect_u8_equals_detect_on_the_oracles_letterbox(be):
-    """ln_net_detect_u8 = device letterbox + detect: same records as detect() fed with the oracle's letterboxed f32 batch."""
+@pytest.mark.parametrize("batch", [4, 8])
+def test_detect_u8_equals_detect_on_the_oracles_letterbox(be, batch):
+    """ln_net_detect_u8 = device letterbox + detect: same records as detect() fed with the oracle's letterboxed f32 batch.
+    (detect() itself is run with its host pipeline off, so the reference side is the plain whole-batch path at both sizes.)"""
     from test_gpu_parity import MINI_CFG
-    batch = 4
     o = orc.Net(MINI_CFG, batch)
     blob = synth.he_weights(o.layers(), 61, bn_identity=False)
     rng = np.random.default_rng(62)
-    sizes = [(48, 64), (100, 75), (31, 200), (64, 64)]   # (h, w)
+    sizes = [(48, 64), (100, 75), (31, 200), (64, 64), (90, 90), (17, 33), (240, 320), (64, 48)][:batch]   # (h, w)
     images = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for h, w in sizes]
     x = np.stack([orc.image_letterbox(orc.image_from_u8(im), o.width, o.height) for im in images])
     net = ln.GpuExecutableNetwork(be, MINI_CFG, batch, ln.LN_Q8)
     net.load_weights(blob)
     net.calibrate(x)
+    net.set_host_pipeline(False)
     ref = net.detect(x, [w for _, w in sizes], [h for h, _ in sizes], 0.2, 0.45, True, 0, 256)
-    got = net.detect_u8(images, 0.2, 0.45, True, 0, 256)
+    net.set_host_pipeline(True)
     assert sum(len(r) for r in ref) > 20
-    for b in range(batch):
-        assert np.array_equal(got[b], ref[b]), b
+    for _ in range(2):
+        got = net.detect_u8(images, 0.2, 0.45, True, 0, 256)
+        for b in range(batch):
+            assert np.array_equal(got[b], ref[b]), b
