@@ -288,9 +288,9 @@ int32_t ln_net_last_times(const ln_net* net, float times_ms[2]);
    convolution (same arithmetic on the same int8 codes, so results do not change); 0 = keep every layer separate. */
 int32_t ln_net_set_fusion(ln_net* net, int32_t on);
 int32_t ln_net_set_profile(ln_net* net, int32_t on);
-/* Host-input pipeline (default on; 8-bit precisions, even batch >= 8): ln_net_detect uploads the two halves of the batch on a
-   copy stream and runs them through two half-batch networks with the same weights and scales, so the upload of the second
-   half overlaps the layers of the first.  Detections are the same as with the pipeline off.  No counterpart in the reference. */
+/* Host-input pipeline (default on; 8-bit precisions, even batch >= 8): ln_net_detect uploads the batch in two parts (a quarter,
+   then three quarters) on a copy stream and runs them through two networks of those batch sizes with the same weights and
+   scales, so the upload of the second part overlaps the layers of the first.  Detections are the same as with the pipeline off.  No counterpart in the reference. */
 int32_t ln_net_set_host_pipeline(ln_net* net, int32_t on);
 /* 8-bit forwards replay one captured CUDA graph of the whole batch (default on); 0 = launch kernel by kernel. */
 int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on);
