@@ -1,7 +1,7 @@
 """Regenerates tests/golden/*_shapes.csv from the reference's own geometry tables.
 
 Run where the reference checkout is mounted:
-    python tests/golden/make_shape_tables.py /root/reference
+    python tests/golden/make_shape_tables.py /path/to/reference
 The reference keeps, for its real-GPU parity tests, tables of every conv / maxpool
 geometry found in its 101 cfg files together with the output extents its shape rules
 give (src/lightnet-cuda-oxide/tests/data/{conv,maxpool}_shapes.csv).  Only the numeric
@@ -28,4 +28,4 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1])

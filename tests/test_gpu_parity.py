@@ -99,7 +99,7 @@ def test_error_conventions(be):
 # ---------------------------------------------------------------------------------------- int8 convolution
 
 def quantized_conv_case(rng, n, c, h, w, f, k):
-    """Inputs of BASELINE config 2: weights N(0, 0.02) per-output-channel symmetric, activations leaky(N(0,1)) per tensor."""
+    """Inputs of the single-layer sweep of the benchmark: weights N(0, 0.02) per-output-channel symmetric, activations leaky(N(0,1)) per tensor."""
     wt = rng.normal(0, 0.02, (f, c, k, k)).astype(np.float32)
     act = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
     act = np.where(act > 0, act, np.float32(0.1) * act).astype(np.float32)
@@ -108,7 +108,7 @@ def quantized_conv_case(rng, n, c, h, w, f, k):
     return wt, act, bias, float(sx)
 
 
-Q8_CASES = [  # (n, c, h, w, f, k, stride, pad): BASELINE config-2 layer shapes at a batch the CPU oracle finishes quickly, plus edge shapes
+Q8_CASES = [  # (n, c, h, w, f, k, stride, pad): the benchmark's single-layer sweep shapes at a batch the CPU oracle finishes quickly, plus edge shapes
     (1, 256, 52, 52, 512, 3, 1, 1),
     (2, 512, 52, 52, 256, 1, 1, 0),
     (1, 128, 104, 104, 256, 3, 2, 1),
@@ -203,7 +203,7 @@ def test_q8_glue_matches_oracle(be):
 # ---------------------------------------------------------------------------------------- decode + NMS
 
 def synth_heads(rng, batch, grids, classes, obj_mu=-4.0):
-    """Head tensors with the distributions of BASELINE config 5 (xy N(0,1), wh N(0,0.5), obj/class N(-4,2))."""
+    """Head tensors with the distributions of the decode + NMS stress workload (xy N(0,1), wh N(0,0.5), obj/class N(-4,2))."""
     heads = []
     for g in grids:
         t = np.empty((batch, 3, 5 + classes, g, g), np.float32)
@@ -260,7 +260,7 @@ def test_decode_nms_records_identical(be, thr, nms, top_k, maxper):
 
 
 def test_decode_nms_stress_full_size(be):
-    """BASELINE config 5 at its full per-image size (25200 candidates x 80 classes, threshold 0.001, IoU 0.65, top-k 300).
+    """The decode + NMS stress workload at its full per-image size (25200 candidates x 80 classes, threshold 0.001, IoU 0.65, top-k 300).
     The oracle's quadratic apply_nms cannot take the ~10^6 candidates of an image, but the first 300 survivors depend only on
     candidates scoring at least as high as the last of them: those (taken from the bit-exact decode, in emission order) go
     through the oracle's NMS and must give the same 300 records."""
@@ -539,7 +539,7 @@ def test_mini_network_f32(be):
 
 
 def test_yolov3_tiny_f32_config1(be):
-    """BASELINE config 1: yolov3-tiny 416, batch 1, He-normal weights, identity BN, uniform input."""
+    """The CPU-runnable benchmark case: yolov3-tiny 416, batch 1, He-normal weights, identity BN, uniform input."""
     cfg = zoo.yolov3_tiny_cfg()
     o = orc.Net(cfg, 1)
     blob = synth.he_weights(o.layers(), 0)
@@ -626,7 +626,7 @@ def test_yolov3_tiny_q8_bit_exact(be):
     be.set_exact_epilogue(False)
 
 
-# ---------------------------------------------------------------------------------------- FP8 E4M3 (BASELINE config 4's arithmetic)
+# ---------------------------------------------------------------------------------------- FP8 E4M3 (the arithmetic of the YOLOv7 benchmark)
 
 F8_CASES = [  # (n, c, h, w, f, k, stride, pad)
     (1, 256, 26, 26, 512, 3, 1, 1),
@@ -794,7 +794,7 @@ def test_host_pipeline_gives_the_same_detections(be):
 # ---------------------------------------------------------------------------------------- the benchmark networks themselves
 
 def test_yolov4_608_q8_bit_exact_full_network(be):
-    """BASELINE config 3 at its real size (YOLOv4, 608x608, 162 layers) on one image: with the exact epilogue the int8 heads are
+    """The headline benchmark network at its real size (YOLOv4, 608x608, 162 layers) on one image: with the exact epilogue the int8 heads are
     bit-identical to the oracle's integer forward, and so are the detections.  Exercises every layout mode the planner picks
     for this network (space-to-depth second layer, pixel groups, resident weights, fused shortcuts, SPP cascade, zero-copy routes)."""
     cfg = zoo.yolov4_cfg(batch=1)
@@ -831,7 +831,7 @@ def test_yolov4_608_q8_bit_exact_full_network(be):
 
 
 def test_yolov7_320_f8_tracks_the_oracle(be):
-    """BASELINE config 4's network (YOLOv7, FP8 E4M3) at 320x320, one image: the heads stay within 10 % of the head's range of the
+    """The FP8 benchmark network (YOLOv7, FP8 E4M3) at 320x320, one image: the heads stay within 10 % of the head's range of the
     oracle's FP8 forward (double accumulation there, f32 tensor-core accumulation here; 105 layers of E4M3 rounding)."""
     cfg = zoo.yolov7_cfg(320, 320, batch=1)
     o = orc.Net(cfg, 1)

@@ -7,7 +7,8 @@ import pytest
 from lightnet_b200 import zoo
 from oracle import oracle_api as orc
 
-REF_CFG = "/root/reference/cfg"
+# cfg directory of a reference checkout, when one is mounted (LIGHTNET_REFERENCE names the checkout)
+REF_CFG = os.path.join(os.environ.get("LIGHTNET_REFERENCE", os.path.join(os.sep, "root", "reference")), "cfg")
 
 
 def _macs(net):
