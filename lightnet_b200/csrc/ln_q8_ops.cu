@@ -478,8 +478,9 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
     }
 }
 
-// The same first layer in FP8 E4M3: the 27 input values are rounded to E4M3 once and kept as floats (products of two
-// E4M3 values are exact in f32), every filter costs 27 FMAs against decoded weights read (broadcast) from shared memory.
+// The same first layer in FP8 E4M3, one thread per pair of adjacent output pixels: the 27 input values of each are rounded
+// to E4M3 once and kept as floats (products of two E4M3 values are exact in f32), every filter costs 27 FMAs per pixel
+// against decoded weights read (broadcast) from shared memory once for both.
 template <int ACT, bool EXACT>
 __global__ void __launch_bounds__(256) conv_stem_k3c3_f8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
                                                                 const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
@@ -496,45 +497,75 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_f8_kernel(const float* __r
     for (int i = threadIdx.x; i < F16 * 16; i += blockDim.x) s_mb[i] = i < F ? mb[i] : make_float2(0.0f, 0.0f);
     __syncthreads();
     const float4* s_wv = reinterpret_cast<const float4*>(s_w);
-    const int64_t total = (int64_t)N * OH * OW;
-    for (int64_t pix = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; pix < total; pix += (int64_t)gridDim.x * blockDim.x) {
-        const int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
-        const int64_t n = pix / ((int64_t)OW * OH);
-        float patch[28];
-        patch[27] = 0.0f;
+    const int OWP = (OW + 1) / 2;
+    const int64_t total = (int64_t)N * OH * OWP;
+    for (int64_t pp = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; pp < total; pp += (int64_t)gridDim.x * blockDim.x) {
+        const int ox0 = (int)(pp % OWP) * 2, oy = (int)((pp / OWP) % OH);
+        const int64_t n = pp / ((int64_t)OWP * OH);
+        const bool second = ox0 + 1 < OW;
+        // taps outside the image contribute nothing: every load goes to a clamped (valid) address and the value is masked
+        float patch[2][28];
+        patch[0][27] = patch[1][27] = 0.0f;
+        const float* xn = x + n * 3 * (int64_t)H * W;
+        int rowoff[3];
+        bool rowok[3];
 #pragma unroll
-        for (int t = 0; t < 27; ++t) {
-            const int c = t % 3, ky = (t / 3) / 3, kx = (t / 3) % 3;
-            const int iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
-            float v = 0.0f;
-            if (iy >= 0 && iy < H && ix >= 0 && ix < W) v = e4m3_to_float(float_to_e4m3(__fmul_rn(__ldg(x + ((n * 3 + c) * H + iy) * W + ix), inv_sx)));
-            patch[t] = v;
+        for (int k = 0; k < 3; ++k) {
+            const int iy = oy * stride + k - pad;
+            rowok[k] = iy >= 0 && iy < H;
+            rowoff[k] = min(max(iy, 0), H - 1) * W;
         }
-        for (int fg = 0; fg < F16; ++fg) {
-            uint32_t packed[4];
+#pragma unroll
+        for (int px = 0; px < 2; ++px) {
+            int coloff[3];
+            bool colok[3];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const int ix = (ox0 + px) * stride + k - pad;
+                colok[k] = ix >= 0 && ix < W;
+                coloff[k] = min(max(ix, 0), W - 1);
+            }
+#pragma unroll
+            for (int t = 0; t < 27; ++t) {
+                const int c = t % 3, ky = (t / 3) / 3, kx = (t / 3) % 3;
+                const float v = e4m3_to_float(float_to_e4m3(__fmul_rn(__ldg(xn + (int64_t)c * H * W + rowoff[ky] + coloff[kx]), inv_sx)));
+                patch[px][t] = rowok[ky] && colok[kx] ? v : 0.0f;
+            }
+        }
+        uint8_t* op = s2d ? out + ((((int64_t)n * (OH >> 1) + (oy >> 1)) * (OW >> 1) + (ox0 >> 1)) * 4 + (oy & 1) * 2) * out_pixel_stride
+                          : out + (((int64_t)n * OH + oy) * OW + ox0) * out_pixel_stride;
+        for (int fg = 0; fg < F16; ++fg, op += 16) {
+            uint32_t packed[2][4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                uint32_t word = 0;
+                uint32_t word[2] = {0, 0};
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                     const int f = fg * 16 + q * 4 + b;
-                    float acc = 0.0f;
+                    float acc[2] = {0.0f, 0.0f};
 #pragma unroll
                     for (int j = 0; j < 7; ++j) {
                         const float4 w = s_wv[f * 7 + j];
-                        acc = __fmaf_rn(patch[4 * j], w.x, acc);
-                        acc = __fmaf_rn(patch[4 * j + 1], w.y, acc);
-                        acc = __fmaf_rn(patch[4 * j + 2], w.z, acc);
-                        acc = __fmaf_rn(patch[4 * j + 3], w.w, acc);
+#pragma unroll
+                        for (int px = 0; px < 2; ++px) {
+                            acc[px] = __fmaf_rn(patch[px][4 * j], w.x, acc[px]);
+                            acc[px] = __fmaf_rn(patch[px][4 * j + 1], w.y, acc[px]);
+                            acc[px] = __fmaf_rn(patch[px][4 * j + 2], w.z, acc[px]);
+                            acc[px] = __fmaf_rn(patch[px][4 * j + 3], w.w, acc[px]);
+                        }
                     }
                     const float2 m = s_mb[f];
-                    const float a = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(acc, m.x, m.y));
-                    if (f < F) word |= (uint32_t)float_to_e4m3(__fmul_rn(a, inv_sy)) << (8 * b);
+#pragma unroll
+                    for (int px = 0; px < 2; ++px) {
+                        const float a = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(acc[px], m.x, m.y));
+                        if (f < F) word[px] |= (uint32_t)float_to_e4m3(__fmul_rn(a, inv_sy)) << (8 * b);
+                    }
                 }
-                packed[q] = word;
+                packed[0][q] = word[0];
+                packed[1][q] = word[1];
             }
-            const int64_t opix = s2d ? ((((int64_t)n * (OH >> 1) + (oy >> 1)) * (OW >> 1) + (ox >> 1)) * 4 + (oy & 1) * 2 + (ox & 1)) : pix;
-            *reinterpret_cast<uint4*>(out + opix * out_pixel_stride + fg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4*>(op) = make_uint4(packed[0][0], packed[0][1], packed[0][2], packed[0][3]);
+            if (second) *reinterpret_cast<uint4*>(op + out_pixel_stride) = make_uint4(packed[1][0], packed[1][1], packed[1][2], packed[1][3]);
         }
     }
 }
@@ -585,8 +616,8 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
     const bool exact = ctx->exact_epilogue;
     if (k == 3 && C == 3 && (kind == LN_KIND_I8 || F16 * 16 * 28 * 4 <= 40 * 1024)) {
         const size_t smem3 = (size_t)F16 * 16 * (kind == LN_KIND_I8 ? 32 : 28 * 4) + (size_t)F16 * 16 * sizeof(float2);
-        // the int8 kernel takes two output pixels per thread, the FP8 one a single pixel
-        const int grid3 = grid_for(ctx, kind == LN_KIND_I8 ? (int64_t)N * OH * ((OW + 1) / 2) : (int64_t)N * OH * OW);
+        // both kernels take two horizontally adjacent output pixels per thread
+        const int grid3 = grid_for(ctx, (int64_t)N * OH * ((OW + 1) / 2));
 #define LN_STEM3(A, E)                                                                                                                             \
     do {                                                                                                                                           \
         if (kind == LN_KIND_I8)                                                                                                                    \
