@@ -546,7 +546,7 @@ def main():
                        "batch_per_gpu": B, "micro_batch": args.micro_batch, "max_detections_per_image": MAX_PER_IMAGE,
                        "l2": "inputs larger than L2 (%.0f MB f32 batch)" % (x_np.nbytes / 1e6), "parallelism": "batch-sharded, no collective"},
             "e2e": {"value": B * world * args.steps / (ms_e2e * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(x_np.nbytes),
-                    "d2h_bytes_per_step": int(B * MAX_PER_IMAGE * 28 + B * 4), "api": "ln_net_detect (host f32 NCHW batch -> detections; the batch is uploaded and run in two parts, 16 + 48 images, as a two-stage pipeline)"},
+                    "d2h_bytes_per_step": int(B * MAX_PER_IMAGE * 28 + B * 4), "api": "ln_net_detect (host f32 NCHW batch -> detections; the batch is uploaded and run in two parts, %d + %d images, as a two-stage pipeline)" % ((B // 4, B - B // 4) if B >= 16 else (B // 2, B - B // 2))},
             "e2e_u8": {"value": B * world * args.steps / (ms_u8 * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(flat8.nbytes),
                        "api": "ln_net_detect_u8 (host 8-bit 640x480 RGB images -> device letterbox -> detections)"},
             "gpu_launches": int(launches),
