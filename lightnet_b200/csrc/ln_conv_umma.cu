@@ -500,31 +500,36 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     if (kRoleTiming && p.debug) { dbg_math += tq2 - tq1; dbg_st += clock64() - tq2; }
                     continue;
                 }
+                // ---- general path: f32 / raw-accumulator outputs (NCHW), FP8, and int8 chunks with fewer than 32 real filters.
+                // The {mult, bias} pairs come two per 16-byte load (the table is padded to a multiple of 32 filters).
+                const int nf = p.F - (f0 + c0);  // real filters from this chunk's first column on (32 or more: all of the chunk)
                 tmem_ld_wait();
-                if (!valid || f0 + c0 >= p.fpad_used) continue;
+                if (!valid || nf <= 0) continue;
                 if (p.out_kind == LN_OUT_ACC) {
-                    int32_t* o = (int32_t*)p.out;  // NCHW, raw accumulator bits (int32 or f32)
+                    // NCHW, raw accumulator bits (int32 or f32): consecutive lanes are consecutive pixels of a row, one plane per filter
+                    const int64_t plane = (int64_t)p.OH * p.OW;
+                    int32_t* o = (int32_t*)p.out + ((int64_t)n * p.F + (f0 + c0)) * plane + (int64_t)oh * p.OW + ow;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int f = f0 + c0 + j;
-                        if (f < p.F) o[(((int64_t)n * p.F + f) * p.OH + oh) * p.OW + ow] = (int32_t)acc[j];
-                    }
+                    for (int j = 0; j < 32; ++j, o += plane)
+                        if (j < nf) *o = (int32_t)acc[j];
                     continue;
                 }
                 float a[32];
+                const float4* mb4 = reinterpret_cast<const float4*>(p.mb + f0 + c0);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float2 mb = __ldg(&p.mb[f0 + c0 + j]);
-                    const float x = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[j]) : __uint_as_float(acc[j]);
-                    a[j] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x, mb.x, mb.y));
+                for (int j = 0; j < 16; ++j) {
+                    const float4 mj = __ldg(mb4 + j);
+                    const float x0 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
+                    const float x1 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
+                    a[2 * j] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x0, mj.x, mj.y));
+                    a[2 * j + 1] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x1, mj.z, mj.w));
                 }
                 if (p.out_kind == LN_OUT_F32) {
-                    float* o = (float*)p.out;  // NCHW
+                    const int64_t plane = (int64_t)p.OH * p.OW;
+                    float* o = (float*)p.out + ((int64_t)n * p.F + (f0 + c0)) * plane + (int64_t)oh * p.OW + ow;  // NCHW
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int f = f0 + c0 + j;
-                        if (f < p.F) o[(((int64_t)n * p.F + f) * p.OH + oh) * p.OW + ow] = a[j];
-                    }
+                    for (int j = 0; j < 32; ++j, o += plane)
+                        if (j < nf) *o = a[j];
                 } else {
                     uint32_t packed[8];
                     if (KIND == LN_KIND_I8) {
@@ -533,8 +538,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                             uint32_t v = 0;
 #pragma unroll
                             for (int b = 0; b < 4; ++b) {
-                                const int f = f0 + c0 + 4 * j + b;
-                                const int q = f < p.F ? ln_quant_i8(a[4 * j + b], p.inv_sy) : 0;
+                                const int q = 4 * j + b < nf ? ln_quant_i8(a[4 * j + b], p.inv_sy) : 0;
                                 v |= ((uint32_t)q & 0xFFu) << (8 * b);
                             }
                             packed[j] = v;
@@ -542,15 +546,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            float v0 = a[4 * j] * p.inv_sy, v1 = a[4 * j + 1] * p.inv_sy, v2 = a[4 * j + 2] * p.inv_sy, v3 = a[4 * j + 3] * p.inv_sy;
-                            const int f = f0 + c0 + 4 * j;
-                            if (f >= p.F) v0 = 0.0f;
-                            if (f + 1 >= p.F) v1 = 0.0f;
-                            if (f + 2 >= p.F) v2 = 0.0f;
-                            if (f + 3 >= p.F) v3 = 0.0f;
-                            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v0, v1), __NV_SATFINITE, __NV_E4M3);
-                            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v2, v3), __NV_SATFINITE, __NV_E4M3);
-                            packed[j] = lo | (hi << 16);
+                            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a[4 * j] * p.inv_sy, a[4 * j + 1] * p.inv_sy), __NV_SATFINITE, __NV_E4M3);
+                            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(a[4 * j + 2] * p.inv_sy, a[4 * j + 3] * p.inv_sy), __NV_SATFINITE, __NV_E4M3);
+                            uint32_t w = lo | (hi << 16);
+                            const int left = nf - 4 * j;  // codes of filters that do not exist are zero
+                            if (left < 4) w = left <= 0 ? 0u : (w & (0xFFFFFFFFu >> (8 * (4 - left))));
+                            packed[j] = w;
                         }
                     }
                     uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
