@@ -723,6 +723,9 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     // LN_CONV_DISABLE=pack,halo switches the two layout modes off (for A/B measurements)
     const char* disable = getenv("LN_CONV_DISABLE");
     const bool allow_pack = !(disable && strstr(disable, "pack")), allow_halo = !(disable && strstr(disable, "halo"));
+    const bool allow_resident = !(disable && strstr(disable, "resident"));
+    const char* rms = getenv("LN_CONV_RESIDENT_MIN_STAGES");
+    const uint32_t res_min_stages = rms && atoi(rms) >= 2 ? (uint32_t)atoi(rms) : 4u;
     // Space-to-depth input (see ln_conv_geom::s2d_input): 4 taps of 128-byte rows instead of 9 taps of 32-byte rows.
     if (g.s2d_input) {
         if (!(g.k == 3 && g.stride == 2 && g.pad == 1 && g.cpad == 32 && g.H % 2 == 0 && g.W % 2 == 0 && g.x_pixel_stride == 32 && g.res == nullptr))
@@ -878,7 +881,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         p.stages = stages;
         plan->smem = (size_t)a_stages * box + (p.b_resident ? b_total : (size_t)stages * b_bytes) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     } else {
-    p.b_resident = (p.tiles_f == 1 && b_total + 4u * 128u * bk <= smem_budget) ? 1 : 0;
+    p.b_resident = (allow_resident && p.tiles_f == 1 && b_total + res_min_stages * 128u * bk <= smem_budget) ? 1 : 0;
     const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + bn) * bk;
     int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u) - (p.b_resident ? b_total : 0u)) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
