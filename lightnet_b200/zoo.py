@@ -149,7 +149,7 @@ def yolov7_cfg(width=640, height=640, batch=1, classes=80) -> str:
 
 
 def head_specs(cfg_text: str):
-    """[yolo] parameters of a cfg as the decode API takes them: list of dicts {classes, anchors [(w,h)..], scale_x_y,
+    """[yolo] / [gaussian_yolo] parameters of a cfg as the decode API takes them: list of dicts {classes, anchors [(w,h)..], scale_x_y,
     new_coords} in layer order."""
     specs = []
     cur = None
@@ -158,7 +158,7 @@ def head_specs(cfg_text: str):
         if not line:
             continue
         if line.startswith("["):
-            cur = {} if line.strip("[]").strip().lower() == "yolo" else None
+            cur = {} if line.strip("[]").strip().lower() in ("yolo", "gaussian_yolo") else None
             if cur is not None:
                 specs.append(cur)
             continue

@@ -346,10 +346,13 @@ static std::unique_ptr<Net> build_net(const std::string& cfg, int batch_override
             L.out = cur;
             if (L.up_reverse) { L.out.w = cur.w / L.up_stride; L.out.h = cur.h / L.up_stride; }
             else { L.out.w = cur.w * L.up_stride; L.out.h = cur.h * L.up_stride; }
-        } else if (s.name == "yolo") {
+        } else if (s.name == "yolo" || s.name == "gaussian_yolo") {
+            // model.rs:4271-4344 and :4513-4543: at inference [gaussian_yolo] is the same identity layer with the same spec, decoded
+            // by the same function (detect.rs:78, :135); its num is max(len(mask), num)
             L.kind = K_YOLO;
             L.mask = parse_list<int>(s, "mask");
             L.num = s.usz("num", L.mask.empty() ? 1 : (int)L.mask.size());
+            if (s.name == "gaussian_yolo" && L.num < (int)L.mask.size()) L.num = (int)L.mask.size();
             if (L.mask.empty()) for (int k = 0; k < L.num; ++k) L.mask.push_back(k);
             L.classes = s.usz("classes", 20);
             L.anchors = parse_list<float>(s, "anchors");

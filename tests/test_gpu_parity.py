@@ -791,6 +791,26 @@ def test_host_pipeline_gives_the_same_detections(be):
         assert np.array_equal(piped2[b], whole[b]), b
 
 
+def test_gaussian_yolo_head_is_decoded_like_a_yolo_head(be):
+    """[gaussian_yolo] is the same identity layer and the same decode as [yolo] at inference (model.rs:4513-4543,
+    exec_forward.rs:908-912, detect.rs:78): a network whose heads carry that name gives the records of the [yolo] one."""
+    batch = 2
+    gcfg = MINI_CFG.replace("[yolo]", "[Gaussian_yolo]")
+    assert gcfg != MINI_CFG
+    o = orc.Net(MINI_CFG, batch)
+    blob = synth.he_weights(o.layers(), 53, bn_identity=False)
+    x = synth.uniform_images(batch, o.channels, o.height, o.width, 54)
+    out = []
+    for cfg in (MINI_CFG, gcfg):
+        net = ln.GpuExecutableNetwork(be, cfg, batch, ln.LN_Q8)
+        net.load_weights(blob)
+        net.calibrate(x)
+        out.append(net.detect(x, [640, 320], [480, 240], 0.2, 0.45, True, 0, 256))
+    assert sum(len(d) for d in out[0]) > 10
+    for b in range(batch):
+        assert np.array_equal(out[0][b], out[1][b]), b
+
+
 # ---------------------------------------------------------------------------------------- the benchmark networks themselves
 
 def test_yolov4_608_q8_bit_exact_full_network(be):

@@ -207,6 +207,19 @@ def test_cfg_parse_rules():
         orc.Net("width=4\n")
 
 
+def test_gaussian_yolo_section_is_a_yolo_head():
+    # model.rs:4513-4543: [gaussian_yolo] builds the same YoloSpec, with num = max(len(mask), num); exec_forward.rs:908-912: identity at
+    # inference; detect.rs:78, :135: decoded by the same function as [yolo]
+    body = "mask = 0,1\nanchors = 10,14, 23,27, 37,58\nclasses=3\nscale_x_y=1.05\n"
+    cfg = "[net]\nwidth=8\nheight=8\nchannels=3\n[convolutional]\nfilters=16\nsize=1\nactivation=linear\n[%s]\n" + body
+    a, b = orc.Net(cfg % "yolo", 1), orc.Net(cfg % "Gaussian_yolo", 1)
+    assert a.layers() == b.layers()
+    assert b.layers()[1]["kind"] == "yolo"
+    from lightnet_b200 import zoo
+    assert zoo.head_specs(cfg % "yolo") == zoo.head_specs(cfg % "Gaussian_yolo")
+    assert zoo.head_specs(cfg % "yolo")[0]["anchors"] == [(10.0, 14.0), (23.0, 27.0)]
+
+
 # --- lightnet-cuda-oxide/src/fp8.rs:200-309 (E4M3 grid, round trip, saturation, NaN, ties to even)
 def test_fp8_e4m3_codec_kats():
     grid = [(0x00, 0.0), (0x01, 2.0 ** -9), (0x07, 7 * 2.0 ** -9), (0x08, 2.0 ** -6), (0x38, 1.0), (0x39, 1.125), (0x3C, 1.5),
