@@ -290,7 +290,9 @@ int32_t ln_net_set_fusion(ln_net* net, int32_t on);
 int32_t ln_net_set_profile(ln_net* net, int32_t on);
 /* Host-input pipeline (default on; 8-bit precisions, even batch >= 8): ln_net_detect uploads the batch in two parts (a quarter,
    then three quarters) on a copy stream and runs them through two networks of those batch sizes with the same weights and
-   scales, so the upload of the second part overlaps the layers of the first.  Detections are the same as with the pipeline off.  No counterpart in the reference. */
+   scales, so the upload of the second part overlaps the layers of the first; both write their image ranges of one set of head
+   tensors, and one decode + NMS runs over the whole batch.  Detections are the same as with the pipeline off.  No counterpart
+   in the reference. */
 int32_t ln_net_set_host_pipeline(ln_net* net, int32_t on);
 /* 8-bit forwards replay one captured CUDA graph of the whole batch (default on); 0 = launch kernel by kernel. */
 int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on);

@@ -81,6 +81,7 @@ void* ln_pool_alloc(ln_ctx* ctx, size_t bytes);
 void ln_pool_free(ln_ctx* ctx, void* p, size_t bytes);
 ln_tensor* ln_tensor_new(ln_ctx* ctx, int dtype, int64_t n, int64_t c, int64_t h, int64_t w);  // allocates storage
 ln_tensor* ln_tensor_view_q(ln_tensor* parent, int64_t channel_offset, int64_t channels);      // channel slice of an NHWC tensor
+ln_tensor* ln_tensor_view_batch(ln_tensor* parent, int64_t start, int64_t count);               // image range of an f32 NCHW tensor
 inline int64_t ln_round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 #define LN_CUDA(ctx, call)                                                                                   \

@@ -245,6 +245,8 @@ struct ln_net {
     std::string cfg_text;
     bool host_pipeline = true;
     ln_net* pipe[2] = {nullptr, nullptr};
+    std::vector<ln_tensor*> pipe_heads;  // whole-batch head tensors the two part networks write their image ranges of
+    std::vector<ln_tensor*> ext_heads;   // part network: its views into the owner's pipe_heads (used instead of own head storage)
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t copy_ev[2] = {nullptr, nullptr};
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
@@ -647,9 +649,15 @@ int build_plan(ln_net* net, int mb) {
     }
     // 4. heads
     release_heads(net);
-    for (int hl : net->head_layers) {
-        const NLayer& L = net->layers[hl];
-        ln_tensor* t = ln_tensor_new(ctx, LN_F32, net->batch, L.out.c, L.out.h, L.out.w);
+    for (size_t k = 0; k < net->head_layers.size(); ++k) {
+        const NLayer& L = net->layers[net->head_layers[k]];
+        ln_tensor* t;
+        if (net->ext_heads.size() == net->head_layers.size()) {  // a part network of the host-input pipeline writes into its owner's heads
+            t = net->ext_heads[k];
+            ln_tensor_retain(t);
+        } else {
+            t = ln_tensor_new(ctx, LN_F32, net->batch, L.out.c, L.out.h, L.out.w);
+        }
         if (!t) return LN_ERR_CUDA;
         net->heads.push_back(t);
     }
@@ -915,14 +923,15 @@ int forward_any(ln_net* net, const ln_tensor* input) {
     return LN_OK;
 }
 
-int fill_heads(ln_net* net, std::vector<ln_yolo_head>& hs) {
-    if (net->heads.size() != net->head_layers.size()) return ln_fail(net->ctx, LN_ERR_ARG, "no head output: run a forward first");
+int fill_heads(ln_net* net, std::vector<ln_yolo_head>& hs, const std::vector<ln_tensor*>* tensors = nullptr) {
+    const std::vector<ln_tensor*>& heads = tensors ? *tensors : net->heads;
+    if (heads.size() != net->head_layers.size()) return ln_fail(net->ctx, LN_ERR_ARG, "no head output: run a forward first");
     hs.resize(net->head_layers.size());
     for (size_t k = 0; k < hs.size(); ++k) {
         const NLayer& L = net->layers[net->head_layers[k]];
         ln_yolo_head& h = hs[k];
         memset(&h, 0, sizeof h);
-        h.raw = net->heads[k];
+        h.raw = heads[k];
         h.classes = L.classes;
         h.n_anchor = (int)L.mask.size();
         for (size_t m = 0; m < L.mask.size(); ++m) { h.anchors[2 * m] = L.anchors[2 * L.mask[m]]; h.anchors[2 * m + 1] = L.anchors[2 * L.mask[m] + 1]; }
@@ -936,7 +945,11 @@ int fill_heads(ln_net* net, std::vector<ln_yolo_head>& hs) {
 // (YOLOv4-608 on a B200): a short first part gets its upload out of the way quickly and its layers cover the upload of the long
 // second part, which then runs at nearly whole-batch efficiency.  A quarter / three quarters split minimises the sum.
 int pipe_batch(const ln_net* net, int part) {
-    const int first = net->batch >= 16 ? net->batch / 4 : net->batch / 2;
+    int first = net->batch >= 16 ? net->batch / 4 : net->batch / 2;
+    if (const char* e = getenv("LN_PIPE_FIRST")) {  // tuning aid: images in the first part
+        const int v = atoi(e);
+        if (v >= 1 && v < net->batch) first = v;
+    }
     return part == 0 ? first : net->batch - first;
 }
 
@@ -945,6 +958,8 @@ void release_pipe(ln_net* net) {
         if (c) ln_net_destroy(c);
         c = nullptr;
     }
+    for (auto*& t : net->pipe_heads) { ln_tensor_release(t); t = nullptr; }
+    net->pipe_heads.clear();
 }
 
 // Builds (once) the two part-batch networks of the host-input pipeline from this network's cfg, weights and scales.
@@ -963,9 +978,16 @@ int ensure_pipe(ln_net* net) {
         }
         blob.insert(blob.end(), L.weights.begin(), L.weights.end());
     }
+    for (int hl : net->head_layers) {
+        const NLayer& L = net->layers[hl];
+        ln_tensor* t = ln_tensor_new(ctx, LN_F32, net->batch, L.out.c, L.out.h, L.out.w);
+        if (!t) { release_pipe(net); return LN_ERR_CUDA; }
+        net->pipe_heads.push_back(t);
+    }
     for (int h = 0; h < 2; ++h) {
         int rc = ln_net_create(ctx, net->cfg_text.c_str(), pipe_batch(net, h), net->precision, &net->pipe[h]);
         if (rc == LN_OK) {
+            for (ln_tensor* t : net->pipe_heads) net->pipe[h]->ext_heads.push_back(ln_tensor_view_batch(t, h == 0 ? 0 : pipe_batch(net, 0), pipe_batch(net, h)));
             net->pipe[h]->host_pipeline = false;
             net->pipe[h]->fuse_shortcut = net->fuse_shortcut;
             net->pipe[h]->use_graph = net->use_graph;
@@ -1024,6 +1046,7 @@ int32_t ln_net_destroy(ln_net* net) {
     release_plan(net);
     release_outputs(net);
     release_heads(net);
+    for (auto*& t : net->ext_heads) { ln_tensor_release(t); t = nullptr; }
     ln_tensor_release(net->input_dev);
     release_pipe(net);
     if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
@@ -1260,16 +1283,26 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
                                          net->copy_stream));
             LN_CUDA(ctx, cudaEventRecord(net->copy_ev[h], net->copy_stream));
         }
-        net->times_ms[0] = net->times_ms[1] = 0.0f;
+        // both parts' layers (the second waits for its upload), each writing its image range of the shared heads, then one
+        // decode + NMS over the whole batch
         for (int h = 0; h < 2; ++h) {
             ln_net* c = net->pipe[h];
             LN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, net->copy_ev[h], 0));
-            rc = ln_net_detect_device(c, c->input_dev, image_w + start[h], image_h + start[h], opts,
-                                      records_host + (size_t)start[h] * opts->max_per_image, counts_host + start[h]);
+            rc = forward_any(c, c->input_dev);
             if (rc) return rc;
-            net->times_ms[0] += c->times_ms[0];
-            net->times_ms[1] += c->times_ms[1];
         }
+        std::vector<ln_yolo_head> hs;
+        rc = fill_heads(net, hs, &net->pipe_heads);
+        if (rc) return rc;
+        rc = ln_yolo_decode_nms(ctx, hs.data(), (int)hs.size(), net->width, net->height, image_w, image_h, opts, records_host, counts_host);
+        if (rc) return rc;
+        LN_CUDA(ctx, cudaEventRecord(net->ev[2], ctx->stream));
+        LN_CUDA(ctx, cudaEventSynchronize(net->ev[2]));
+        float part[2] = {0.0f, 0.0f}, nms = 0.0f;
+        for (int h = 0; h < 2; ++h) cudaEventElapsedTime(&part[h], net->pipe[h]->ev[0], net->pipe[h]->ev[1]);
+        cudaEventElapsedTime(&nms, net->pipe[1]->ev[1], net->ev[2]);
+        net->times_ms[0] = part[0] + part[1];
+        net->times_ms[1] = nms;
         return LN_OK;
     }
     int rc = stage_input(net, input_host);

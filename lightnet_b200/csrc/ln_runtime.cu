@@ -87,6 +87,19 @@ ln_tensor* ln_tensor_view_q(ln_tensor* parent, int64_t channel_offset, int64_t c
     return t;
 }
 
+// Images [start, start + count) of an f32 NCHW tensor (a contiguous range of the parent's storage).
+ln_tensor* ln_tensor_view_batch(ln_tensor* parent, int64_t start, int64_t count) {
+    ln_tensor* t = new ln_tensor(*parent);
+    t->refcount = 1;
+    t->base = nullptr;
+    t->bytes = 0;
+    t->parent = parent;
+    parent->refcount++;
+    t->n = count;
+    t->ptr = (char*)parent->ptr + (size_t)start * parent->c * parent->h * parent->w * 4;
+    return t;
+}
+
 extern "C" {
 
 int32_t ln_ctx_create(int32_t device, ln_ctx** out) {
