@@ -133,6 +133,10 @@ int32_t ln_ctx_create(int32_t device, ln_ctx** out) {
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
     if (e != cudaSuccess || !fn) { delete ctx; return ln_fail(nullptr, LN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"); }
     ctx->encode_tiled = (ln_encode_tiled_fn)fn;
+    if (const char* e = getenv("LN_NMS_POOL_ENTRIES")) {  // tuning aid: same as ln_ctx_set_nms_pool_entries
+        const long long v = atoll(e);
+        if (v > 0 && v <= (1ll << 30)) ctx->nms_pool_entries = (int)v;
+    }
     if (getenv("LN_DEBUG_CYCLES")) {
         if (cudaMallocManaged(&ctx->debug_cycles, 32 * sizeof(long long)) != cudaSuccess) ctx->debug_cycles = nullptr;
         else memset(ctx->debug_cycles, 0, 32 * sizeof(long long));
