@@ -487,7 +487,9 @@ __global__ void __launch_bounds__(256) yolo_pool_select_kernel(const __grid_cons
         count = st.above + cum * scale;
     } else {
         const long long incl = st.above + (cum + s_h[nb - 1 - b]) * scale;
-        const long long fits = st.sampled ? incl + incl / 2 : incl;
+        long long fits = st.sampled ? incl + incl / 2 : incl;
+        const long long all = (long long)p.total_ca * p.classes;  // an image has no more candidates than this, whatever the estimate says
+        if (fits > all) fits = all;
         if (fits <= p.pool_max || (!st.sampled && st.level == kLevels - 1)) {
             st.pool_lo = base + ((unsigned long long)b << shift);
             count = incl;
