@@ -172,6 +172,38 @@ __global__ void maxpool_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint
     }
 }
 
+// The SPP case: stride 1, output the size of the input, window SIZE x SIZE around the pixel.  Every window meets the image, so
+// taps outside are replaced by the nearest pixel inside (which the window holds already): no branches, SIZE independent
+// 16-byte loads in flight per row.
+template <int KIND, int SIZE>
+__global__ void __launch_bounds__(256) maxpool_same_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N,
+                                                            int C16, int H, int W, int off) {
+    const int64_t total = N * H * W * C16;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % C16);
+        const int64_t pix = i / C16;
+        const int ox = (int)(pix % W), oy = (int)((pix / W) % H);
+        const int64_t n = pix / ((int64_t)W * H);
+        const uint8_t* xn = x + n * H * W * xs + cg * 16;
+        int col[SIZE];
+#pragma unroll
+        for (int k = 0; k < SIZE; ++k) col[k] = min(max(ox + k - off, 0), W - 1);
+        uint4 m;
+#pragma unroll
+        for (int ky = 0; ky < SIZE; ++ky) {
+            const int iy = min(max(oy + ky - off, 0), H - 1);
+            const uint8_t* row = xn + (int64_t)iy * W * xs;
+            uint4 v[SIZE];
+#pragma unroll
+            for (int kx = 0; kx < SIZE; ++kx) v[kx] = *reinterpret_cast<const uint4*>(row + col[kx] * xs);
+            if (ky == 0) m = v[0];
+#pragma unroll
+            for (int kx = 0; kx < SIZE; ++kx) m = max16<KIND>(m, v[kx]);
+        }
+        *reinterpret_cast<uint4*>(y + pix * ys + cg * 16) = m;
+    }
+}
+
 // nearest up-sample, NHWC (runtime/layer_ops.rs:2208-2256, scale folded into the tensor scale)
 __global__ void upsample_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N, int C16, int H, int W,
                                   int s) {
@@ -656,6 +688,13 @@ int ln_q_maxpool_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* 
                         int size, int sx, int sy, int padding) {
     const int C16 = (int)(ln_round_up(C, 16) / 16);
     const int64_t total = N * OH * OW * C16;
+    const int off = padding / 2;
+    if (size == 5 && sx == 1 && sy == 1 && OH == H && OW == W && off >= 0 && off <= 4) {
+        if (kind == LN_KIND_I8) maxpool_same_q_kernel<LN_KIND_I8, 5><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off);
+        else maxpool_same_q_kernel<LN_KIND_F8, 5><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off);
+        LN_LAUNCHED(ctx);
+        return LN_OK;
+    }
     if (kind == LN_KIND_I8)
         maxpool_q_kernel<LN_KIND_I8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, OH, OW, size, sx, sy, padding);
     else
