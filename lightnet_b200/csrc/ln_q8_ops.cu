@@ -172,35 +172,37 @@ __global__ void maxpool_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint
     }
 }
 
-// The SPP case: stride 1, output the size of the input, window SIZE x SIZE around the pixel.  Every window meets the image, so
-// taps outside are replaced by the nearest pixel inside (which the window holds already): no branches, SIZE independent
-// 16-byte loads in flight per row.
-template <int KIND, int SIZE>
-__global__ void __launch_bounds__(256) maxpool_same_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N,
-                                                            int C16, int H, int W, int off) {
-    const int64_t total = N * H * W * C16;
+// The SPP case: 5x5 window, stride 1, output the size of the input.  Every window meets the image, so taps outside are
+// replaced by the nearest pixel inside (which the window holds already): no branches.  One thread walks down a column
+// segment of one (image, x, 16 channels) keeping the horizontal 5-tap maxima of the last five rows: 5 loads per output
+// instead of 25.
+template <int KIND>
+__global__ void __launch_bounds__(256) maxpool5_same_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N,
+                                                             int C16, int H, int W, int off, int seg_rows) {
+    const int64_t total = N * W * C16;
+    const int oy0 = blockIdx.y * seg_rows, oy1 = min(oy0 + seg_rows, H);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int cg = (int)(i % C16);
-        const int64_t pix = i / C16;
-        const int ox = (int)(pix % W), oy = (int)((pix / W) % H);
-        const int64_t n = pix / ((int64_t)W * H);
+        const int ox = (int)((i / C16) % W);
+        const int64_t n = i / ((int64_t)C16 * W);
         const uint8_t* xn = x + n * H * W * xs + cg * 16;
-        int col[SIZE];
+        uint8_t* yn = y + n * H * W * ys + cg * 16;
+        int64_t col[5];
 #pragma unroll
-        for (int k = 0; k < SIZE; ++k) col[k] = min(max(ox + k - off, 0), W - 1);
-        uint4 m;
+        for (int k = 0; k < 5; ++k) col[k] = (int64_t)min(max(ox + k - off, 0), W - 1) * xs;
+        auto row_max = [&](int iy) {
+            const uint8_t* row = xn + (int64_t)min(max(iy, 0), H - 1) * W * xs;
+            uint4 v[5];
 #pragma unroll
-        for (int ky = 0; ky < SIZE; ++ky) {
-            const int iy = min(max(oy + ky - off, 0), H - 1);
-            const uint8_t* row = xn + (int64_t)iy * W * xs;
-            uint4 v[SIZE];
-#pragma unroll
-            for (int kx = 0; kx < SIZE; ++kx) v[kx] = *reinterpret_cast<const uint4*>(row + col[kx] * xs);
-            if (ky == 0) m = v[0];
-#pragma unroll
-            for (int kx = 0; kx < SIZE; ++kx) m = max16<KIND>(m, v[kx]);
+            for (int k = 0; k < 5; ++k) v[k] = *reinterpret_cast<const uint4*>(row + col[k]);
+            return max16<KIND>(max16<KIND>(max16<KIND>(v[0], v[1]), max16<KIND>(v[2], v[3])), v[4]);
+        };
+        uint4 r0 = row_max(oy0 - off), r1 = row_max(oy0 - off + 1), r2 = row_max(oy0 - off + 2), r3 = row_max(oy0 - off + 3);
+        for (int oy = oy0; oy < oy1; ++oy) {
+            const uint4 r4 = row_max(oy - off + 4);
+            *reinterpret_cast<uint4*>(yn + ((int64_t)oy * W + ox) * ys) = max16<KIND>(max16<KIND>(max16<KIND>(r0, r1), max16<KIND>(r2, r3)), r4);
+            r0 = r1; r1 = r2; r2 = r3; r3 = r4;
         }
-        *reinterpret_cast<uint4*>(y + pix * ys + cg * 16) = m;
     }
 }
 
@@ -690,8 +692,14 @@ int ln_q_maxpool_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* 
     const int64_t total = N * OH * OW * C16;
     const int off = padding / 2;
     if (size == 5 && sx == 1 && sy == 1 && OH == H && OW == W && off >= 0 && off <= 4) {
-        if (kind == LN_KIND_I8) maxpool_same_q_kernel<LN_KIND_I8, 5><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off);
-        else maxpool_same_q_kernel<LN_KIND_F8, 5><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off);
+        // columns are split into row segments until there are about two blocks per SM (a segment re-reads four rows)
+        const int64_t cols = N * W * C16;
+        int segs = (int)((2ll * ctx->sm_count * kThreads + cols - 1) / cols);
+        segs = segs < 1 ? 1 : (segs > (H + 3) / 4 ? (H + 3) / 4 : segs);
+        const int seg_rows = (H + segs - 1) / segs;
+        const dim3 grid((unsigned)grid_for(ctx, cols), (unsigned)((H + seg_rows - 1) / seg_rows));
+        if (kind == LN_KIND_I8) maxpool5_same_q_kernel<LN_KIND_I8><<<grid, kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off, seg_rows);
+        else maxpool5_same_q_kernel<LN_KIND_F8><<<grid, kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off, seg_rows);
         LN_LAUNCHED(ctx);
         return LN_OK;
     }
