@@ -206,6 +206,25 @@ __global__ void __launch_bounds__(256) maxpool5_same_q_kernel(const uint8_t* __r
     }
 }
 
+// The down-sampling case: 2x2 window, stride 2, window origin at (2 oy, 2 ox).  The first tap is always inside the image; a
+// second tap beyond the last row / column (odd sizes) is replaced by the first: four independent loads, no branches.
+template <int KIND>
+__global__ void __launch_bounds__(256) maxpool2_s2_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N,
+                                                           int C16, int H, int W, int OH, int OW) {
+    const int64_t total = N * OH * OW * C16;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % C16);
+        const int64_t pix = i / C16;
+        const int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
+        const int64_t n = pix / ((int64_t)OW * OH);
+        const int x0 = 2 * ox, x1 = min(x0 + 1, W - 1), y0 = 2 * oy, y1 = min(y0 + 1, H - 1);
+        const uint8_t* xn = x + n * H * W * xs + cg * 16;
+        const uint4 a = *reinterpret_cast<const uint4*>(xn + ((int64_t)y0 * W + x0) * xs), b = *reinterpret_cast<const uint4*>(xn + ((int64_t)y0 * W + x1) * xs);
+        const uint4 c = *reinterpret_cast<const uint4*>(xn + ((int64_t)y1 * W + x0) * xs), d = *reinterpret_cast<const uint4*>(xn + ((int64_t)y1 * W + x1) * xs);
+        *reinterpret_cast<uint4*>(y + pix * ys + cg * 16) = max16<KIND>(max16<KIND>(a, b), max16<KIND>(c, d));
+    }
+}
+
 // nearest up-sample, NHWC (runtime/layer_ops.rs:2208-2256, scale folded into the tensor scale)
 __global__ void upsample_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N, int C16, int H, int W,
                                   int s) {
@@ -700,6 +719,12 @@ int ln_q_maxpool_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* 
         const dim3 grid((unsigned)grid_for(ctx, cols), (unsigned)((H + seg_rows - 1) / seg_rows));
         if (kind == LN_KIND_I8) maxpool5_same_q_kernel<LN_KIND_I8><<<grid, kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off, seg_rows);
         else maxpool5_same_q_kernel<LN_KIND_F8><<<grid, kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, off, seg_rows);
+        LN_LAUNCHED(ctx);
+        return LN_OK;
+    }
+    if (size == 2 && sx == 2 && sy == 2 && off == 0 && 2 * (OH - 1) < H && 2 * (OW - 1) < W) {
+        if (kind == LN_KIND_I8) maxpool2_s2_q_kernel<LN_KIND_I8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, OH, OW);
+        else maxpool2_s2_q_kernel<LN_KIND_F8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C16, H, W, OH, OW);
         LN_LAUNCHED(ctx);
         return LN_OK;
     }
