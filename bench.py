@@ -183,7 +183,7 @@ def run_reference(args, rank):
     steps = max(1, min(args.steps, 2))
     total, note = 0.0, ""
     if args.workload == "conv-sweep":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference has no int8 / FP8 convolution; the sweep has no CPU arm"}))
+        emit_line(({"impl": "reference", "unavailable": "the reference has no int8 / FP8 convolution; the sweep has no CPU arm"}))
         return
     if args.workload == "preprocess":
         from oracle import oracle_api as orc
@@ -193,7 +193,7 @@ def run_reference(args, rank):
         for im in ims:
             orc.image_letterbox(orc.image_from_u8(im), 608, 608)
         v = 8.0 / (time.perf_counter() - t0)
-        print(json.dumps({"impl": "reference", "metric": WORKLOADS["preprocess"]["metric"], "value": v, "unit": "images/s", "n_gpus": args.gpus, "steps": 1,
+        emit_line(({"impl": "reference", "metric": WORKLOADS["preprocess"]["metric"], "value": v, "unit": "images/s", "n_gpus": args.gpus, "steps": 1,
                           "warmup": 0, "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
                           "data": "synthetic", "config": {"workload": "letterbox of random 640x480 8-bit RGB images to 608x608 f32 NCHW"},
                           "cpu_baseline": {"value": v, "unit": "images/s", "cores": 1, "kind": "port", "sample": "8 images, one thread"},
@@ -210,7 +210,7 @@ def run_reference(args, rank):
         v, unit, cores = stress_bytes(1) / dt / 1e9, "GB/s", 1
     else:
         v, unit = 1.0 / dt, "images/s"
-    print(json.dumps({"impl": "reference", "metric": wl["metric"], "value": v, "unit": unit, "n_gpus": args.gpus, "steps": steps,
+    emit_line(({"impl": "reference", "metric": wl["metric"], "value": v, "unit": unit, "n_gpus": args.gpus, "steps": steps,
                       "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                       "dtype": "f32", "data": "synthetic",
                       "config": {"workload": workload_text(args.workload), "batch_per_gpu": args.batch},
@@ -315,7 +315,7 @@ def run_conv_sweep(args, be, rank, world, local_rank):
     launches = be.launch_count - launches0
     if rank == 0:
         best = max(rows, key=lambda r: r["tops"])
-        print(json.dumps({
+        emit_line(({
             "metric": WORKLOADS["conv-sweep"]["metric"], "value": best["tops"], "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8+fp8", "data": "synthetic",
@@ -371,7 +371,7 @@ def run_preprocess(args, be, rank, world, local_rank):
                 orc.image_letterbox(orc.image_from_u8(im), size, size)
             dt = (time.perf_counter() - t0) / 8
             line["cpu_baseline"] = {"value": 1.0 / dt, "unit": "images/s", "cores": 1, "kind": "port", "sample": "8 of the %d images, one thread (the reference's resize is serial)" % B}
-        print(json.dumps(line))
+        emit_line((line))
 
 
 def run_nms_stress(args, be, rank, world, local_rank):
@@ -429,7 +429,26 @@ def run_nms_stress(args, be, rank, world, local_rank):
         if world == 1 and not args.no_cpu_baseline:
             dt, note = cpu_stress_sample(1)
             line["cpu_baseline"] = {"value": stress_bytes(1) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port", "sample": note}
-        print(json.dumps(line))
+        emit_line((line))
+
+
+_RESULT_OUT = None
+
+
+def claim_stdout():
+    """Keeps the process's real stdout for the one JSON line and points file descriptor 1 at stderr, so that whatever a
+    library prints on stdout (NCCL's version banner under torchrun) cannot land beside the line."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit_line(obj):
+    out = _RESULT_OUT or sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
 
 
 def main():
@@ -449,6 +468,7 @@ def main():
     ap.add_argument("--width", type=int, default=0)
     ap.add_argument("--height", type=int, default=0)
     args = ap.parse_args()
+    claim_stdout()
     wl = WORKLOADS[args.workload]
     args.batch = args.batch or wl["batch"]
     args.width = args.width or wl["size"]
@@ -564,7 +584,7 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(B, wl["model"], wl["size"])
-        print(json.dumps(line))
+        emit_line((line))
     if world > 1:
         dist.destroy_process_group()
 
