@@ -432,6 +432,27 @@ def run_nms_stress(args, be, rank, world, local_rank):
         emit_line((line))
 
 
+def bind_to_gpu_cpus(device_index):
+    """One rank per GPU: run this process (and so first-touch its pinned upload buffers) on the host cores next to its GPU,
+    as the driver reports them (read-only NVML query; only this process's own CPU affinity changes).  Best effort."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:  # the CUDA index need not be the NVML index: go through the PCI address
+            import torch
+            pr = torch.cuda.get_device_properties(device_index)
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(("%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)).encode())
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus = near & os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception as e:  # no NVML, a restricted container, ...: keep the affinity as it is
+        print("cpu binding skipped: %s" % e, file=sys.stderr)
+
+
 _RESULT_OUT = None
 
 
@@ -489,6 +510,7 @@ def main():
 
     torch.cuda.set_device(local_rank)
     if world > 1:
+        bind_to_gpu_cpus(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     B = args.batch
     be = ln.B200Backend(local_rank)
