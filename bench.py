@@ -48,11 +48,33 @@ SWEEP_LAYERS = [(256, 52, 52, 512, 3, 1, 1), (512, 52, 52, 256, 1, 1, 0), (128, 
 STRESS_THR, STRESS_NMS, STRESS_TOPK = 0.001, 0.65, 300
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the 109 tensor-core convolution launches of one step,
-# per image, from an ncu capture of `bench.py --batch 16 --steps 1 --warmup 3 --no-cpu-baseline` (profiles/): 2.437 GB read +
-# 0.411 GB written for 16 images.  At batch 16 much of a layer's output is consumed from L2 and overwritten in the next step
-# before it is ever written back; at batch 64 less is, so scaling this figure by the batch is a lower bound.
-CONV_DRAM_BYTES_PER_IMAGE_B16 = (2436655360 + 410987776) / 16.0
+# ncu summaries under profiles/ that hold the tensor-pipe counters of a layer class, keyed by (kernel size, stride, in_c, out_c)
+LAYER_CLASS_PROFILES = {
+    (3, 1, 128, 128): "profiles/conv_umma_3x3_c128_k128_int8_n64.md",
+    (1, 1, 64, 64): "profiles/conv_umma_1x1_c64_k64_mish_int8_n16.md",
+    (3, 1, 256, 512): "profiles/conv_umma_3x3_c256_k512_int8_n128.md",
+    (3, 1, 3, 32): "profiles/conv_stem_k3c3_i8_608_n16.md",
+}
+
+
+def layer_classes(layers, per_layer_ms, batch, top=10):
+    """Per layer class (kernel, stride, channels -> filters): launches, total ms, TOP/s over the class, and the ncu summary that
+    holds its tensor-pipe counters where one is committed.  Sorted by time, the `top` slowest classes."""
+    acc = {}
+    for l, ms in zip(layers, per_layer_ms):
+        if l["kind"] != "conv" or ms <= 0:
+            continue
+        key = (l["size"], l["stride_x"], l["in_c"], l["out_c"])
+        ops = 2.0 * l["out_w"] * l["out_h"] * l["out_c"] * l["in_c"] * l["size"] ** 2 * batch
+        a = acc.setdefault(key, [0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += ms
+        a[2] += ops
+    rows = []
+    for key, (n, ms, ops) in sorted(acc.items(), key=lambda kv: -kv[1][1])[:top]:
+        rows.append({"layer": "%dx%d s%d C%d->K%d" % (key[0], key[0], key[1], key[2], key[3]), "launches": n, "ms": round(ms, 4),
+                     "tops": round(ops / ms / 1e9, 1), "profile": LAYER_CLASS_PROFILES.get(key)})
+    return rows
 
 
 def conv_bytes_per_image(layers):
@@ -64,6 +86,11 @@ def conv_bytes_per_image(layers):
         head = i + 1 < len(layers) and layers[i + 1]["kind"] == "yolo"
         total += l["in_w"] * l["in_h"] * l["in_c"] + l["out_w"] * l["out_h"] * l["out_c"] * (4 if head else 1)
     return total
+
+
+def head_bytes(layers, batch):
+    """Algorithmic bytes of decode + NMS: every f32 head value once."""
+    return sum(4 * batch * layers[i - 1]["out_w"] * layers[i - 1]["out_h"] * layers[i - 1]["out_c"] for i, l in enumerate(layers) if l["kind"] == "yolo")
 
 
 def conv_ops_per_image(layers):
@@ -115,15 +142,18 @@ def measured_peaks():
     return 1400.0, 6650.0, "fallback"
 
 
-def cpu_reference_sample(batch, threads, model="yolov4", size=608):
+def cpu_reference_sample(batch, threads, model="yolov4", size=608, with_unbounded_estimate=True):
     """Times the reference's CPU path (oracle restatement: f32 direct convolution with unfolded batch norm, libm
-    activations, decode, the two apply_nms passes) on ONE image of the workload and returns (seconds per image, note).
+    activations, decode, confidence sort, apply_nms) on ONE image of the workload.  Returns a dict of seconds.
 
-    The conv stack of the image is timed in full.  decode + NMS is timed on a sample: apply_nms
-    (lightnet-train/src/detect.rs:1449-1484) visits every pair of candidates, and this workload (random weights,
-    saturated heads) yields about 10^6 candidates per image, i.e. minutes of single-threaded pair visits.  The sample
-    keeps every 4th row and every 4th column of each head (1/16 of the cells, hence of the candidates); its time is
-    multiplied by 16^2, the growth of the pair count."""
+    Everything in `measured_s` is timed in full on that image, doing the work the GPU arm does: the whole conv stack,
+    the decode of every head, and the sorted-list apply_nms pass (lightnet-train/src/detect.rs:1449-1484) stopped once
+    MAX_PER_IMAGE rows are kept -- exact for those records, and the GPU arm's own stopping rule.  Like the device path it
+    leaves out the thr = 1.0 pre-pass of detect.rs:127-128.
+
+    `unbounded_nms_estimate_s` is NOT part of any reported rate: the reference itself runs apply_nms to the end over all
+    ~10^6 candidates of such an image (random weights saturate the heads), a pair loop of minutes to hours; it is timed on
+    1/16 of the grid cells and scaled by 16^2, and reported separately, flagged as an extrapolation."""
     from lightnet_b200 import synth, zoo
     from oracle import oracle_api as orc
 
@@ -136,41 +166,49 @@ def cpu_reference_sample(batch, threads, model="yolov4", size=608):
     o.forward_f32(x)
     t_conv = time.perf_counter() - t0
     specs = zoo.head_specs(cfg)
-    heads, sub = [], []
     yolo_layers = [i for i, l in enumerate(o.layers()) if l["kind"] == "yolo"]
-    for li, sp in zip(yolo_layers, specs):
-        h = o.layer_output_f32(li)[0]                      # [255, g, g]
-        hs = np.ascontiguousarray(h[:, ::4, ::4])
-        heads.append(hs)
-        sub.append(dict(gw=hs.shape[2], gh=hs.shape[1], classes=sp["classes"], anchors=sp["anchors"], scale_x_y=sp["scale_x_y"],
-                        new_coords=sp["new_coords"]))
+    heads = [np.ascontiguousarray(o.layer_output_f32(li)[0]) for li in yolo_layers]
+    full = [dict(sp, gw=h.shape[2], gh=h.shape[1]) for sp, h in zip(specs, heads)]
     t0 = time.perf_counter()
-    d = orc.decode_nms(heads, sub, size, size, size, size, CONF_THR, NMS_THR, letterbox=True)
-    t_nms_sample = time.perf_counter() - t0
-    t_nms = t_nms_sample * 256.0
-    note = ("1 image of the batch of %d: f32 conv stack in full (%.1f s on %d threads, OpenMP over (image, filter)); decode + NMS timed on "
-            "1/16 of the grid cells (%.2f s, %d boxes kept) and scaled by 16^2 = %.0f s, apply_nms being quadratic in the candidate count"
-            % (batch, t_conv, threads, t_nms_sample, len(d), t_nms))
-    return t_conv + t_nms, note
+    cands = orc.decode_only(heads, full, size, size, size, size, CONF_THR, letterbox=True)
+    t_decode = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    kept = orc.nms_records_first_k(cands, NMS_THR, MAX_PER_IMAGE)
+    t_nms = time.perf_counter() - t0
+    out = {"conv_s": t_conv, "decode_s": t_decode, "nms_s": t_nms, "measured_s": t_conv + t_decode + t_nms, "candidates": int(len(cands)),
+           "kept": int(len(kept)), "threads": threads}
+    if with_unbounded_estimate:
+        sub_heads = [np.ascontiguousarray(h[:, ::4, ::4]) for h in heads]
+        sub = [dict(sp, gw=h.shape[2], gh=h.shape[1]) for sp, h in zip(specs, sub_heads)]
+        t0 = time.perf_counter()
+        orc.decode_nms(sub_heads, sub, size, size, size, size, CONF_THR, NMS_THR, letterbox=True)
+        out["unbounded_nms_estimate_s"] = (time.perf_counter() - t0) * 256.0
+    out["note"] = ("1 image of the batch of %d, all measured: f32 conv stack %.1f s on %d threads (OpenMP over (image, filter)), decode of %d candidates %.2f s, "
+                   "confidence sort + apply_nms stopped at %d kept rows %.2f s (one thread, like the reference); no thr=1.0 pre-pass, as on the device"
+                   % (batch, t_conv, threads, len(cands), t_decode, MAX_PER_IMAGE, t_nms))
+    return out
 
 
 def cpu_stress_sample(threads):
     """decode + NMS of the reference (oracle restatement, one thread: the reference's decode and apply_nms are serial) on
-    ONE image of the stress workload, on 1/16 of its grid cells; returns (seconds per image, note).  Time is scaled by 16^2
-    because apply_nms visits every pair of candidates."""
+    ONE full image of the stress workload, all measured: decode of every candidate, confidence sort, and the sorted-list
+    apply_nms pass stopped at top-k kept rows (exact for those records; the device path's stopping rule); no thr = 1.0
+    pre-pass, as on the device.  Returns (seconds per image, note)."""
     from lightnet_b200 import synth
     from oracle import oracle_api as orc
 
-    heads = [np.ascontiguousarray(h[0][:, ::4, ::4]) for h in synth.stress_heads(1)]
+    heads = [np.ascontiguousarray(h[0]) for h in synth.stress_heads(1)]
     specs = synth.stress_head_specs()
     for sp, h in zip(specs, heads):
         sp["gw"], sp["gh"] = h.shape[2], h.shape[1]
     t0 = time.perf_counter()
-    d = orc.decode_nms(heads, specs, 640, 640, 640, 640, STRESS_THR, STRESS_NMS, letterbox=True, top_k=STRESS_TOPK)
+    cands = orc.decode_only(heads, specs, 640, 640, 640, 640, STRESS_THR, letterbox=True)
+    t_dec = time.perf_counter() - t0
+    kept = orc.nms_records_first_k(cands, STRESS_NMS, STRESS_TOPK)
     dt = time.perf_counter() - t0
-    note = ("1 image of 256, 1/16 of the grid cells (%.2f s, %d boxes kept), scaled by 16^2 for the quadratic pair loop of apply_nms"
-            % (dt, len(d)))
-    return dt * 256.0, note
+    note = ("1 image of 256 in full, all measured, one thread: decode of %d candidates %.2f s, confidence sort + apply_nms stopped at %d kept rows %.2f s"
+            % (len(cands), t_dec, len(kept), dt - t_dec))
+    return dt, note
 
 
 def run_reference(args, rank):
@@ -199,23 +237,34 @@ def run_reference(args, rank):
                           "cpu_baseline": {"value": v, "unit": "images/s", "cores": 1, "kind": "port", "sample": "8 images, one thread"},
                           "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
+    parts, unbounded = None, None
     for _ in range(steps):
         if wl["model"] is None:
             dt, note = cpu_stress_sample(1)
         else:
-            dt, note = cpu_reference_sample(args.batch, cores, wl["model"], wl["size"])
+            parts = cpu_reference_sample(args.batch, cores, wl["model"], wl["size"], with_unbounded_estimate=unbounded is None)
+            unbounded = parts.get("unbounded_nms_estimate_s", unbounded)
+            dt, note = parts["measured_s"], parts["note"]
         total += dt
     dt = total / steps
     if wl["model"] is None:
         v, unit, cores = stress_bytes(1) / dt / 1e9, "GB/s", 1
     else:
         v, unit = 1.0 / dt, "images/s"
-    emit_line(({"impl": "reference", "metric": wl["metric"], "value": v, "unit": unit, "n_gpus": args.gpus, "steps": steps,
-                      "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                      "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": workload_text(args.workload), "batch_per_gpu": args.batch},
-                      "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": note},
-                      "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+    line = {"impl": "reference", "metric": wl["metric"], "value": v, "unit": unit, "n_gpus": args.gpus, "steps": steps,
+            "warmup": 0, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_text(args.workload), "batch_per_gpu": args.batch,
+                       "step": "one image of the batch per step (a bounded sample); steps capped at 2"},
+            "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": note},
+            "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    line["extrapolated"] = False
+    if wl["model"] is not None:
+        line["measured_s"] = {k: parts[k] for k in ("conv_s", "decode_s", "nms_s", "measured_s")}
+        line["conv_stack_images_per_s"] = 1.0 / parts["conv_s"]
+        line["extrapolated_s"] = {"unbounded_nms_estimate_s": unbounded,
+                                  "note": "not in value: what apply_nms run to the end (the reference's own behaviour) would add, from 1/16 of the cells x 16^2"}
+    emit_line(line)
 
 
 def workload_text(name):
@@ -234,8 +283,9 @@ def stress_bytes(batch):
 
 def cpu_baseline(batch, model="yolov4", size=608):
     cores = os.cpu_count() or 1
-    dt, note = cpu_reference_sample(batch, cores, model, size)
-    return {"value": 1.0 / dt, "unit": "images/s", "cores": cores, "kind": "port", "sample": note}
+    parts = cpu_reference_sample(batch, cores, model, size, with_unbounded_estimate=False)
+    return {"value": 1.0 / parts["measured_s"], "unit": "images/s", "cores": cores, "kind": "port", "sample": parts["note"],
+            "measured_s": {k: parts[k] for k in ("conv_s", "decode_s", "nms_s", "measured_s")}, "extrapolated": False}
 
 
 def make_timer(stream, world):
@@ -595,12 +645,16 @@ def main():
             "phases_ms": {"layers": fwd_ms, "decode_nms": nms_ms},
             "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel (%s implicit GEMM, all layers but the first)" % wl["precision"], "achieved": achieved,
                          "peak": peak, "unit": "TOP/s", "frac": achieved / peak,
-                         "traffic": CONV_DRAM_BYTES_PER_IMAGE_B16 * B if args.workload == "yolov4-608-int8" else None,
-                         "traffic_basis": "bytes per step over all launches of the kernel: DRAM read + write measured with ncu at batch 16 (178 MB per image), scaled by the batch; a lower bound at batch 64, where less of a layer stays in L2",
+                         "traffic": None,
+                         "traffic_basis": "not measured at this batch: an ncu capture of all launches of a 64-image step is beyond the size a capture may have; per-launch DRAM bytes of single layers are in the profiles/ summaries named under layer_classes",
                          "algorithmic_bytes": conv_bytes_per_image(layers) * B,
                          "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf), "launches_per_step": umma_launches,
                          "ms_per_step": umma_ms},
             "kernel_classes_ms": {k: v[0] for k, v in per_op.items()},
+            "layer_classes": layer_classes(layers, per_layer, B),
+            "nms_gbs": {"value": head_bytes(layers, B) / (nms_ms * 1e-3) / 1e9 if nms_ms > 0 else None, "unit": "GB/s",
+                        "basis": "f32 head tensors read once (%d bytes) / phases_ms.decode_nms" % head_bytes(layers, B),
+                        "frac_of_hbm": head_bytes(layers, B) / (nms_ms * 1e-3) / 1e9 / hbm_gbs if nms_ms > 0 else None},
             "clocks": clocks,
             "detections_first_image": int(len(dets[0])) if dets is not None else None,
         }

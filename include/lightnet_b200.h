@@ -257,7 +257,8 @@ int32_t ln_net_calibrate(ln_net* net, const float* input_host);
 /* scales[num_layers+1]: [0] network input, [1+i] output of layer i. */
 int32_t ln_net_get_scales(const ln_net* net, float* scales, int32_t count);
 int32_t ln_net_set_scales(ln_net* net, const float* scales, int32_t count);
-/* Layers of the batch run `micro_batch` images at a time so that activations stay in L2 (0 = whole batch). */
+/* Layers of the batch run `micro_batch` images at a time so that activations stay in L2 (0 = whole batch).  The two part
+   networks of the host-input pipeline (ln_net_set_host_pipeline) always run their part whole. */
 int32_t ln_net_set_micro_batch(ln_net* net, int32_t micro_batch);
 /* forward_compact (runtime/gpu_forward_compact.rs:8): host f32 NCHW input -> heads resident on the device. */
 int32_t ln_net_forward(ln_net* net, const float* input_host);
@@ -297,6 +298,19 @@ int32_t ln_net_set_host_pipeline(ln_net* net, int32_t on);
 /* 8-bit forwards replay one captured CUDA graph of the whole batch (default on); 0 = launch kernel by kernel. */
 int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on);
 int32_t ln_net_profile(const ln_net* net, float* per_layer_ms, int32_t num_layers, float per_op_ms[8], int32_t per_op_launches[8]);
+
+
+/* ---- debug aids (no counterpart in the reference) ------------------------------------------- */
+/* Largest distance, in units of the 32-bit confidence key, between the approximate (hardware ex2 / rcp) score the head passes
+   classify candidates with and the exact one, over a sweep of n_obj objectness logits in [obj_lo, obj_hi] times n_x class
+   logits in [x_lo, x_hi].  The passes trust the approximation only beyond 256 units from a decision boundary. */
+int32_t ln_debug_score_key_error(ln_ctx* ctx, float obj_lo, float obj_hi, float x_lo, float x_hi, int32_t n_obj, int32_t n_x,
+                                 uint32_t* worst);
+/* Role-timing counters (clock cycles) that CTA 0 of the most recent tensor-core convolution recorded: [0..1] producer total /
+   waiting, [2..5] MMA issuer total / waiting for an accumulator / waiting for operands / tiles, [6..] epilogue warps.  Only with
+   a library built with -DLN_CONV_ROLE_TIMING and LN_DEBUG_CYCLES=1 in the environment at ln_ctx_create; LN_ERR_UNSUPPORTED
+   otherwise. */
+int32_t ln_ctx_debug_cycles(ln_ctx* ctx, int64_t cycles[32]);
 
 #ifdef __cplusplus
 }

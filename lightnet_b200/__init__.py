@@ -138,6 +138,8 @@ SYMBOLS = {
     "ln_net_set_host_pipeline": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_set_cuda_graph": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_profile": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
+    "ln_debug_score_key_error": (C.c_int32, [_VP, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32, C.POINTER(C.c_uint32)]),
+    "ln_ctx_debug_cycles": (C.c_int32, [_VP, _I64P]),
 }
 
 
@@ -272,12 +274,15 @@ class B200Backend:
 
     def debug_score_key_error(self, obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x):
         """Largest distance, in confidence-key units, between the approximate and the exact candidate score over a sweep."""
-        fn = self.lib.ln_debug_score_key_error
-        fn.restype = C.c_int32
-        fn.argtypes = [_VP, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32, C.POINTER(C.c_uint32)]
         worst = C.c_uint32()
-        self._check(fn(self.ctx, obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x, C.byref(worst)))
+        self._check(self.lib.ln_debug_score_key_error(self.ctx, obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x, C.byref(worst)))
         return int(worst.value)
+
+    def debug_cycles(self):
+        """The 32 role-timing counters of the last tensor-core convolution (needs a -DLN_CONV_ROLE_TIMING build and LN_DEBUG_CYCLES=1)."""
+        out = (C.c_int64 * 32)()
+        self._check(self.lib.ln_ctx_debug_cycles(self.ctx, out))
+        return list(out)
 
     # ---- F32TensorOpsBackend ------------------------------------------------------------------
     def upload_f32(self, shape, host):

@@ -29,8 +29,10 @@ struct ln_ctx {
     int nms_pool_entries = 0;  // capacity of one NMS candidate pool, 0 = automatic
     int64_t launches = 0;
     int sm_count = 0;
-    std::multimap<size_t, void*> free_blocks;  // size-keyed pool; reuse is stream ordered
-    size_t pool_bytes = 0;
+    std::multimap<size_t, void*> free_blocks;  // size-keyed cache of freed blocks; reuse is stream ordered
+    std::map<void*, size_t> live_blocks;       // true size of every block handed out
+    size_t pool_bytes = 0;                     // bytes held from the device: live + cached
+    size_t cached_bytes = 0;
     int* d_status = nullptr;  // device status word written by kernels whose bounded waits give up
     int* h_status = nullptr;  // pinned mirror
     ln_encode_tiled_fn encode_tiled = nullptr;

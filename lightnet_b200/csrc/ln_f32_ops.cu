@@ -160,9 +160,10 @@ __global__ void bn_fold_kernel(const float* gamma, const float* mean, const floa
                                float* bias_out, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    float s = gamma[i] / sqrtf(var[i] + eps);
+    // single IEEE operations in the order of weights_io.rs:32-92 (no fused multiply-add), so the result has the host fold's bits
+    float s = __fdiv_rn(gamma[i], __fsqrt_rn(__fadd_rn(var[i], eps)));
     scale[i] = s;
-    bias_out[i] = bias[i] - mean[i] * s;
+    bias_out[i] = __fsub_rn(bias[i], __fmul_rn(mean[i], s));
 }
 
 int grid_for(ln_ctx* ctx, int64_t n) {

@@ -1338,6 +1338,8 @@ int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on) {
     if (!net) return LN_ERR_ARG;
     net->use_graph = on != 0;
     if (!net->use_graph) release_graph(net);
+    for (ln_net* c : net->pipe)  // the part networks of the host-input pipeline follow their owner
+        if (c) ln_net_set_cuda_graph(c, on);
     return LN_OK;
 }
 
@@ -1345,6 +1347,7 @@ int32_t ln_net_set_fusion(ln_net* net, int32_t on) {
     if (!net) return LN_ERR_ARG;
     net->fuse_shortcut = on != 0;
     release_plan(net);
+    release_pipe(net);  // the part networks of the host-input pipeline are rebuilt with the new setting on the next host-input call
     return LN_OK;
 }
 

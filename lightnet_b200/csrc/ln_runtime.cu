@@ -17,20 +17,33 @@ int ln_fail(ln_ctx* ctx, int code, const char* fmt, ...) {
     return code;
 }
 
+// Device-memory pool of a ctx.  Freed blocks are cached by size:
+// a request takes the smallest cached block that holds it, provided that block is at most twice the request (so a caller
+// whose sizes vary from call to call -- image staging, NMS working memory -- does not force a fresh cudaMalloc, a device-wide
+// synchronisation, for every distinct size).  The true size of every live block is remembered, so callers may pass the
+// size they asked for when they free.  The cache is trimmed when it exceeds the larger of 2 GiB and the live bytes.
+static void pool_drop_cached(ln_ctx* ctx, std::multimap<size_t, void*>::iterator it) {
+    cudaFree(it->second);
+    ctx->cached_bytes -= it->first;
+    ctx->pool_bytes -= it->first;
+    ctx->free_blocks.erase(it);
+}
+
 void* ln_pool_alloc(ln_ctx* ctx, size_t bytes) {
     bytes = (size_t)ln_round_up((int64_t)(bytes ? bytes : 1), 512);
-    auto it = ctx->free_blocks.find(bytes);
-    if (it != ctx->free_blocks.end()) {
+    auto it = ctx->free_blocks.lower_bound(bytes);
+    if (it != ctx->free_blocks.end() && it->first <= 2 * bytes) {
         void* p = it->second;
+        ctx->cached_bytes -= it->first;
+        ctx->live_blocks[p] = it->first;
         ctx->free_blocks.erase(it);
         return p;
     }
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, bytes);
     if (e != cudaSuccess) {
-        // release cached blocks once and retry
-        for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
-        ctx->free_blocks.clear();
+        // release every cached block once and retry
+        while (!ctx->free_blocks.empty()) pool_drop_cached(ctx, ctx->free_blocks.begin());
         (void)cudaGetLastError();
         e = cudaMalloc(&p, bytes);
         if (e != cudaSuccess) {
@@ -40,13 +53,21 @@ void* ln_pool_alloc(ln_ctx* ctx, size_t bytes) {
         }
     }
     ctx->pool_bytes += bytes;
+    ctx->live_blocks[p] = bytes;
     return p;
 }
 
 void ln_pool_free(ln_ctx* ctx, void* p, size_t bytes) {
     if (!p) return;
-    bytes = (size_t)ln_round_up((int64_t)(bytes ? bytes : 1), 512);
-    ctx->free_blocks.emplace(bytes, p);
+    auto live = ctx->live_blocks.find(p);
+    const size_t real = live != ctx->live_blocks.end() ? live->second : (size_t)ln_round_up((int64_t)(bytes ? bytes : 1), 512);
+    if (live != ctx->live_blocks.end()) ctx->live_blocks.erase(live);
+    ctx->free_blocks.emplace(real, p);
+    ctx->cached_bytes += real;
+    // trim: largest blocks first (cudaFree waits for the device, so nothing in flight still uses them)
+    const size_t live_bytes = ctx->pool_bytes - ctx->cached_bytes;
+    const size_t cap = live_bytes > ((size_t)2 << 30) ? live_bytes : ((size_t)2 << 30);
+    while (ctx->cached_bytes > cap && !ctx->free_blocks.empty()) pool_drop_cached(ctx, std::prev(ctx->free_blocks.end()));
 }
 
 static size_t storage_bytes(int dtype, int64_t n, int64_t c, int64_t h, int64_t w, int64_t* cstride) {
@@ -168,8 +189,15 @@ int32_t ln_sync(ln_ctx* ctx) {
 
 void* ln_ctx_stream(ln_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
-// Debug aid (LN_DEBUG_CYCLES=1): role timings of CTA 0 of the last tensor-core convolution; NULL when off.
-const long long* ln_ctx_debug_cycles(ln_ctx* ctx) { return ctx ? ctx->debug_cycles : nullptr; }
+// Debug aid (LN_DEBUG_CYCLES=1 in the environment when the ctx is created, library built with -DLN_CONV_ROLE_TIMING): the 32
+// role-timing counters CTA 0 of the last tensor-core convolution wrote.  LN_ERR_UNSUPPORTED when the counters are off.
+int32_t ln_ctx_debug_cycles(ln_ctx* ctx, int64_t cycles[32]) {
+    if (!ctx || !cycles) return ln_fail(ctx, LN_ERR_ARG, "ln_ctx_debug_cycles: NULL argument");
+    if (!ctx->debug_cycles) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_ctx_debug_cycles: role timing is off (set LN_DEBUG_CYCLES=1 before ln_ctx_create)");
+    LN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int i = 0; i < 32; ++i) cycles[i] = (int64_t)ctx->debug_cycles[i];
+    return LN_OK;
+}
 
 int32_t ln_ctx_set_exact_epilogue(ln_ctx* ctx, int32_t on) {
     if (!ctx) return LN_ERR_ARG;

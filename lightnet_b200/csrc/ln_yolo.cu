@@ -1013,7 +1013,9 @@ void scratch_layout(YoloParams* p, int pool_entries, Scratch* s) {
 
 int check_options(ln_ctx* ctx, YoloParams* p, const ln_detect_options* opts, const int32_t* image_w, const int32_t* image_h, int band_max, const char* who) {
     p->thr = opts->confidence_threshold;
-    p->nms_thr = opts->nms_threshold;
+    // apply_nms returns at once for a threshold <= 0 (detect.rs:1449-1452): nothing is suppressed.  The kernels test
+    // `iou > nms_thr`, which no IoU passes when the threshold is +infinity.
+    p->nms_thr = opts->nms_threshold > 0.0f ? opts->nms_threshold : INFINITY;
     p->letterbox = opts->letterbox;
     p->max_per_image = opts->max_per_image;
     p->k_eff = opts->top_k > 0 && opts->top_k < opts->max_per_image ? opts->top_k : opts->max_per_image;

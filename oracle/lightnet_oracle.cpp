@@ -1384,6 +1384,105 @@ int orc_nms_records(float* recs, int n, float nms_thr, int top_k, int skip_pass1
     return (int)d.size();
 }
 
+// The sorted-list pass of decode_network_detections (stable sort by confidence, then apply_nms) stopped as soon as
+// `k` rows have been kept.  On a confidence-sorted list apply_nms always keeps row i and drops later rows, so the rows
+// kept up to any point are final: the result is the first k records of the full pass, at the cost of k row scans
+// instead of one per survivor.  This is the work the device path does when it is given max_per_image = k; the
+// thr = 1.0 pre-pass on the unsorted list (detect.rs:127-128) is not part of it.
+int orc_nms_records_first_k(float* recs, int n, float nms_thr, int k) {
+    std::vector<Det> d(n);
+    for (int i = 0; i < n; ++i) {
+        const float* r = recs + 7 * i;
+        d[i] = Det{(int)r[0], r[1], r[2], r[3], r[4], r[5], r[6]};
+    }
+    sort_conf_desc(d);
+    std::vector<char> sup((size_t)n, 0);
+    std::vector<Det> kept;
+    for (int i = 0; i < n && (int)kept.size() < k; ++i) {
+        if (sup[i]) continue;
+        if (nms_thr > 0.0f)
+            for (int j = i + 1; j < n; ++j) {
+                if (sup[j] || d[i].class_id != d[j].class_id) continue;
+                // sorted: conf[i] >= conf[j], so row i is the one kept (detect.rs:1463-1467)
+                if (bbox_iou(d[i], d[j]) > nms_thr) sup[j] = 1;
+            }
+        kept.push_back(d[i]);
+    }
+    for (size_t i = 0; i < kept.size(); ++i) {
+        float* r = recs + 7 * i;
+        const Det& e = kept[i];
+        r[0] = (float)e.class_id; r[1] = e.conf; r[2] = e.obj; r[3] = e.x; r[4] = e.y; r[5] = e.w; r[6] = e.h;
+    }
+    return (int)kept.size();
+}
+
+// The same NMS sequence run class by class.  apply_nms never pairs records of different classes
+// (detect.rs:1461), so a stable partition by class followed by the per-class passes keeps exactly the
+// records the whole-list passes keep; the final order of the reference is confidence descending with
+// ties in emission order (two stable sorts, detect.rs:107 and :242), which is rebuilt here from the
+// emission index.  Costs the sum of the squared class sizes instead of the squared total.
+int orc_nms_records_by_class(float* recs, int n, float nms_thr, int top_k, int skip_pass1) {
+    struct Tagged { Det d; int idx; };
+    std::map<int, std::vector<Tagged>> by_class;
+    for (int i = 0; i < n; ++i) {
+        const float* r = recs + 7 * i;
+        by_class[(int)r[0]].push_back(Tagged{Det{(int)r[0], r[1], r[2], r[3], r[4], r[5], r[6]}, i});
+    }
+    std::vector<Tagged> kept;
+    for (auto& kv : by_class) {
+        std::vector<Tagged>& v = kv.second;
+        // the passes of apply_nms restricted to one class; `order` is compacted and permuted together with the
+        // records so that every survivor can be traced back to its emission index
+        std::vector<Det> d(v.size());
+        for (size_t i = 0; i < v.size(); ++i) d[i] = v[i].d;
+        std::vector<int> order(v.size());
+        for (size_t i = 0; i < v.size(); ++i) order[i] = (int)i;
+        auto run_pass = [&](float thr) {
+            if (thr <= 0.0f) return;
+            const size_t m = d.size();
+            std::vector<char> sup(m, 0);
+            for (size_t i = 0; i < m; ++i) {
+                if (sup[i]) continue;
+                for (size_t j = i + 1; j < m; ++j) {
+                    if (sup[j]) continue;
+                    size_t keep, drop;
+                    if (d[i].conf >= d[j].conf) { keep = i; drop = j; } else { keep = j; drop = i; }
+                    if (bbox_iou(d[keep], d[drop]) > thr) sup[drop] = 1;
+                }
+            }
+            size_t k = 0;
+            for (size_t i = 0; i < m; ++i) if (!sup[i]) { d[k] = d[i]; order[k] = order[i]; ++k; }
+            d.resize(k); order.resize(k);
+        };
+        auto sort_desc = [&]() {
+            auto key = [](float f) { int32_t b; std::memcpy(&b, &f, 4); return b < 0 ? (int32_t)(b ^ 0x7fffffff) : b; };
+            std::vector<size_t> perm(d.size());
+            for (size_t i = 0; i < perm.size(); ++i) perm[i] = i;
+            std::stable_sort(perm.begin(), perm.end(), [&](size_t a, size_t b) { return key(d[a].conf) > key(d[b].conf); });
+            std::vector<Det> d2(d.size());
+            std::vector<int> o2(d.size());
+            for (size_t i = 0; i < perm.size(); ++i) { d2[i] = d[perm[i]]; o2[i] = order[perm[i]]; }
+            d.swap(d2); order.swap(o2);
+        };
+        if (!skip_pass1) run_pass(1.0f);
+        sort_desc();
+        run_pass(nms_thr);
+        for (size_t i = 0; i < d.size(); ++i) kept.push_back(Tagged{d[i], v[order[i]].idx});
+    }
+    auto key = [](float f) { int32_t b; std::memcpy(&b, &f, 4); return b < 0 ? (int32_t)(b ^ 0x7fffffff) : b; };
+    std::sort(kept.begin(), kept.end(), [&](const Tagged& a, const Tagged& b) {
+        const int32_t ka = key(a.d.conf), kb = key(b.d.conf);
+        return ka != kb ? ka > kb : a.idx < b.idx;
+    });
+    if (top_k > 0 && (int)kept.size() > top_k) kept.resize(top_k);
+    for (size_t i = 0; i < kept.size(); ++i) {
+        float* r = recs + 7 * i;
+        const Det& d = kept[i].d;
+        r[0] = (float)d.class_id; r[1] = d.conf; r[2] = d.obj; r[3] = d.x; r[4] = d.y; r[5] = d.w; r[6] = d.h;
+    }
+    return (int)kept.size();
+}
+
 // Single-layer int8 conv: NCHW int8 in, [F][C][k][k] int8 weights, NCHW int32 accumulators out.
 void orc_conv_q8_acc(const int8_t* x, int B, int C, int H, int W, const int8_t* wq, int F, int k, int sx, int sy, int pad,
                      int32_t* acc) {

@@ -69,6 +69,8 @@ def lib():
         L.orc_decode_only.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                       C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_int]
         L.orc_nms_records.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_int]
+        L.orc_nms_records_by_class.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_int]
+        L.orc_nms_records_first_k.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int]
         L.orc_conv_q8_acc.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
         L.orc_image_from_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         L.orc_image_resize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
@@ -283,9 +285,19 @@ def decode_only(heads, specs, net_w, net_h, img_w, img_h, thr, letterbox=False, 
     return out[:n].copy()
 
 
-def nms_records(recs, nms, top_k=0, skip_pass1=False):
+def nms_records(recs, nms, top_k=0, skip_pass1=False, by_class=False):
+    """The NMS sequence of decode_network_detections on records in emission order.  by_class=True runs it class by
+    class (classes never interact in apply_nms): same result, cost quadratic in the class sizes instead of the total."""
     r = np.ascontiguousarray(recs, np.float32).copy()
-    n = lib().orc_nms_records(_p(r), r.shape[0], nms, top_k, int(skip_pass1))
+    fn = lib().orc_nms_records_by_class if by_class else lib().orc_nms_records
+    n = fn(_p(r), r.shape[0], nms, top_k, int(skip_pass1))
+    return r[:n].copy()
+
+
+def nms_records_first_k(recs, nms, k):
+    """First k records of the sorted-list NMS pass (no thr = 1.0 pre-pass), stopping once k rows are kept."""
+    r = np.ascontiguousarray(recs, np.float32).copy()
+    n = lib().orc_nms_records_first_k(_p(r), r.shape[0], nms, k)
     return r[:n].copy()
 
 
@@ -346,16 +358,18 @@ def f32_to_e4m3_array(v):
     return np.array([f32_to_e4m3_fast(t) for t in v.ravel()], np.uint8).reshape(v.shape)
 
 
-def conv_f32(x, w, bias, stride=1, pad=0, groups=1, act="linear"):
+def conv_f32(x, w, bias, stride=1, pad=0, groups=1, act="linear", stride_y=None):
+    """`stride` is the stride in x; stride_y defaults to it (the reference's geometry case sx2_sy1 has two)."""
     x = np.ascontiguousarray(x, np.float32)
     w = np.ascontiguousarray(w, np.float32)
     bias = np.ascontiguousarray(bias, np.float32)
     B, Cc, H, W = x.shape
     F, _, k, _ = w.shape
-    OH = (H + 2 * pad - k) // stride + 1
+    sy = stride if stride_y is None else stride_y
+    OH = (H + 2 * pad - k) // sy + 1
     OW = (W + 2 * pad - k) // stride + 1
     y = np.zeros((B, F, OH, OW), np.float32)
-    lib().orc_conv_f32(_p(x), B, Cc, H, W, _p(w), _p(bias), F, k, stride, stride, pad, groups, ACT[act], _p(y))
+    lib().orc_conv_f32(_p(x), B, Cc, H, W, _p(w), _p(bias), F, k, stride, sy, pad, groups, ACT[act], _p(y))
     return y
 
 
