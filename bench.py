@@ -68,7 +68,7 @@ def layer_classes(layers, per_layer_ms, batch, top=10):
         ops = 2.0 * l["out_w"] * l["out_h"] * l["out_c"] * l["in_c"] * l["size"] ** 2 * batch
         a = acc.setdefault(key, [0, 0.0, 0.0])
         a[0] += 1
-        a[1] += ms
+        a[1] += float(ms)
         a[2] += ops
     rows = []
     for key, (n, ms, ops) in sorted(acc.items(), key=lambda kv: -kv[1][1])[:top]:

@@ -15,7 +15,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "liblightnet_b200.so")
+# the in-tree library; LIGHTNET_B200_LIB names another build of it (e.g. one compiled with extra -D switches for an A/B run)
+LIB_PATH = os.environ.get("LIGHTNET_B200_LIB") or os.path.join(_HERE, "liblightnet_b200.so")
 
 LN_F32, LN_Q8, LN_I32, LN_F8 = 0, 1, 2, 3
 LN_OUT_Q, LN_OUT_F32, LN_OUT_ACC = 0, 1, 2

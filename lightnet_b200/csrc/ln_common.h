@@ -218,6 +218,34 @@ __device__ __forceinline__ uint32_t ln_h2_act_quant(float v0, float v1, __half2 
     t = __hadd2(t, __float2half2_rn(1536.0f));  // ulp is 1 in [1024, 2048): the low mantissa bits are rne(t)
     return *reinterpret_cast<uint32_t*>(&t);
 }
+// The same with the two pre-activations already in units of the output scale (t = v / s; the caller folds 1 / s into its
+// per-filter multiplier and bias, so no multiply by 1 / s is left here).  `k` holds s * log2(e) in both halves: t * k is the
+// exponent argument of the transcendental activations; `inv_s` is used by the logistic only.  Activations that are bounded
+// below by a small multiple of s (mish >= -0.31, swish >= -0.28, relu, logistic) need no lower clamp as long as
+// s >= 0.31 / 127, which the caller checks.
+template <int ACT>
+__device__ __forceinline__ uint32_t ln_h2_code(float t0, float t1, __half2 k, __half2 inv_s) {
+    uint32_t tb;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(tb) : "f"(t1), "f"(t0));  // first source -> upper half
+    const __half2 t = *reinterpret_cast<const __half2*>(&tb);
+    const __half2 lo = __float2half2_rn(-127.0f);
+    __half2 y;
+    if (ACT == LN_ACT_LEAKY) y = __hmax2(__hmax2(t, __hmul2(t, __float2half2_rn(0.1f))), lo);
+    else if (ACT == LN_ACT_RELU) y = __hmax2(t, __float2half2_rn(0.0f));
+    else if (ACT == LN_ACT_MISH) {
+        // t * w / (w + 2), w = e^v (e^v + 2), the ratio evaluated at min(v, 5)
+        const __half2 e = ln_h2_ex2(__hmin2(__hmul2(t, k), __float2half2_rn(5.0f * 1.44269504f)));
+        const __half2 w = __hmul2(e, __hadd2(e, __float2half2_rn(2.0f)));
+        y = __hmul2(t, __hmul2(w, ln_h2_rcp(__hadd2(w, __float2half2_rn(2.0f)))));
+    } else if (ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC) {
+        // 1 / (1 + e^-v) with v clamped to >= -10
+        const __half2 e = ln_h2_ex2(__hmin2(__hmul2(t, __hneg2(k)), __float2half2_rn(10.0f * 1.44269504f)));
+        const __half2 sg = ln_h2_rcp(__hadd2(e, __float2half2_rn(1.0f)));
+        y = ACT == LN_ACT_SWISH ? __hmul2(t, sg) : __hmul2(sg, inv_s);
+    } else y = __hmax2(t, lo);
+    y = __hadd2(__hmin2(y, __float2half2_rn(127.0f)), __float2half2_rn(1536.0f));  // ulp is 1 in [1024, 2048): the low mantissa bits are rne(y)
+    return *reinterpret_cast<uint32_t*>(&y);
+}
 // {a.lo, a.hi, b.lo, b.hi} code bytes of two ln_h2_act_quant results -> one packed word
 __device__ __forceinline__ uint32_t ln_h2_pack(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x6420); }
 

@@ -18,6 +18,7 @@ struct ln_conv_umma_params {
     CUtensorMap tmA[4];  // activations; stride-2 convolutions use one map per input parity class
     CUtensorMap tmB;     // weights as a [fpad][k*k*cpad] matrix
     int bk, bn, stages, nbuf;
+    int subs;  // an accumulator tile is handed to the epilogue as `subs` units of bn / subs columns
     int b_resident;  // the weights of the (single) filter tile stay in shared memory for the whole kernel
     int small_acc;  // every accumulator is known to stay below 2^22 in magnitude
     int R, S, stride, pad;
@@ -29,9 +30,12 @@ struct ln_conv_umma_params {
     int act, out_kind;
     float inv_sy;
     const float2* mb;  // [fpad] {x_scale * w_scale[f], bias[f]}
-    // [fpad] {mult, bias - 1.5 * 2^23 * mult}: lets the fast epilogue apply scale and bias directly to the float whose bits are
-    // 0x4B400000 + accumulator (= 1.5 * 2^23 + accumulator); null when accumulators can exceed 2^22
+    // [fpad / 2] float4 {m 2i, m 2i+1, b 2i, b 2i+1}, m = mult / s_y, b = bias / s_y - 1.5 * 2^23 * m: lets the fast epilogue take
+    // the pre-activation, in units of the output scale, straight from the float whose bits are 0x4B400000 + accumulator
+    // (= 1.5 * 2^23 + accumulator); null when accumulators can exceed 2^22
     const float2* mb_folded;
+    float sy_log2e;  // output scale * log2(e): exponent argument per code unit (folded fast epilogue)
+    int tab_bytes;   // bytes of the {multiplier, bias} table the epilogue warps copy to shared memory (all filter tiles)
     void* out;
     long long out_pixel_stride;  // bytes between pixels of an 8-bit NHWC output
     // fused shortcut (null = none): out = quant((code * s_c + residual_code * s_res) * inv_sy2), code = the convolution's own int8 output

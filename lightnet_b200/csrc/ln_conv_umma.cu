@@ -11,8 +11,9 @@
 // matching weight slab.  Stride-2 convolutions use one tensor map per input parity class so that the
 // strided gather is again a dense box.  Every CTA fetches its own operands.
 //
-// Roles (448 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..13 = epilogue (three warps per
-// TMEM lane quadrant, each group of four warps taking every third tile, so every scheduler has three warps to hide latency with).
+// Roles (576 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..17 = epilogue (four warps per
+// TMEM lane quadrant, each group of four warps taking every fourth tile, so every scheduler has four warps to hide latency with;
+// the per-filter {multiplier, bias} table lives in shared memory so that the epilogue fits in 112 registers).
 // The accumulator is double buffered in TMEM so the epilogue of tile t overlaps the main loop of t+1.
 // Every mbarrier wait is bounded: when it gives up it raises a status word the host reads, and all
 // roles leave their loops, TMEM is released and the kernel returns.
@@ -26,7 +27,10 @@
 namespace {
 
 constexpr int kMaxStages = 8;
-constexpr int kEpilogueGroups = 3;   // groups of four epilogue warps (one warp per TMEM lane quadrant); group g takes the tiles t with t % groups == g
+#ifndef LN_EPILOGUE_GROUPS
+#define LN_EPILOGUE_GROUPS 4
+#endif
+constexpr int kEpilogueGroups = LN_EPILOGUE_GROUPS;   // groups of four epilogue warps (one warp per TMEM lane quadrant); group g takes the tiles t with t % groups == g
 constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
 constexpr int kThreads = 32 * (2 + kEpilogueWarps);  // producer warp, MMA warp, epilogue warps
 constexpr int kMaxAccBufs = 8;       // accumulator tiles in TMEM: 512 columns / BN, at most 8
@@ -128,6 +132,15 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
 }
+// the same for 16 columns
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
 // n / d for n * d < 2^40 with the precomputed multiplier ceil(2^40 / d): one wide multiply and a shift
 __device__ __forceinline__ int fast_div(int n, unsigned long long magic) { return (int)(((unsigned long long)(unsigned)n * magic) >> 40); }
 
@@ -137,7 +150,21 @@ __device__ __forceinline__ float4 ldg_f4_pinned(const float4* p) {
     asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
     return v;
 }
+// 16-byte read from shared memory (the table it reads is written once, before the epilogue warps' barrier)
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+    float4 v;
+    asm("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// the same, naming the 16 registers an earlier load fills, so that no use of them can be scheduled before the wait
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
+                   "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
 
 
 // int32 -> f32 (round to nearest even) on the FMA/ALU pipes only: the conversion unit shares its issue port with
@@ -160,6 +187,16 @@ __device__ __forceinline__ float s8_to_float(uint32_t w, int b) {
 }
 __device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// d = a * b + c on two binary32 values with one instruction (packed f32x2 arithmetic of sm_100)
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    unsigned long long a, b, c, d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(b0), "f"(b1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(c0), "f"(c1));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
 }
 
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are BK bytes wide and swizzled
@@ -204,6 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     volatile int* abort_flag = (volatile int*)(tmem_slot + 2);
     auto afull_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 4 + s); };
     auto aempty_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 4 + kMaxStages + s); };
+    const uint32_t tab_base = bar_base + 512u;  // the {multiplier, bias} pairs of all filter tiles, after the barrier block
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t tmem_cols = 512u;  // the CTA owns the SM: take all of TMEM and keep 512/BN (at most 8) accumulator tiles in flight
@@ -216,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         }
         for (int b = 0; b < nbuf; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 4);  // the four warps of the group that drained the buffer
+            mbar_init(tempty_bar(b), 4 * p.subs);  // the four warps of each group that drained one of the tile's column units
         }
         mbar_init(bres_bar, 1);
         for (int s = 0; s < kMaxStages; ++s) {
@@ -379,22 +417,38 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     } else {
         // ------------------------------------------------------------------ epilogue
         const int quad = warp & 3;          // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
-        // Which of the warps of the quadrant: group g takes the tiles with t % groups == g.  Never more groups than accumulator
-        // buffers: a group that starts waiting for tile t has finished tile t - groups, so every earlier tile's accumulation is
-        // complete, in particular the previous use of this buffer (tile t - nbuf <= t - groups); a parity wait needs that.
+        // Which of the warps of the quadrant.  The work of the epilogue is cut into units: an accumulator tile is `subs` units of
+        // bn / subs columns each (subs > 1 when TMEM holds fewer tiles than there are groups, so that all groups stay busy), and
+        // group g takes the units u with u % groups == g, u counting (tile, sub) pairs in order.  Never more groups than
+        // nbuf * subs: a group that starts waiting for a unit of tile t has finished its unit `groups` earlier, a unit of tile
+        // t - ceil(groups / subs) or later; tiles are committed in order, so the previous use of this buffer (tile t - nbuf) has
+        // been accumulated in full, which a parity wait needs.
         const int group = (warp - 2) >> 2;
-        const int groups = nbuf < kEpilogueGroups ? nbuf : kEpilogueGroups;
+        const int subs = p.subs, sub_cols = bn / subs;
+        const int groups = nbuf * subs < kEpilogueGroups ? nbuf * subs : kEpilogueGroups;
         const int row = quad * 32 + lane;
         const int pw = row & (p.TW - 1), ph = (row >> p.log_tw) & (p.TH - 1), pn = row >> (p.log_tw + p.log_th);
         constexpr bool kTranscendental = ACT == LN_ACT_MISH || ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC;
+        const bool folded = !EXACT && p.mb_folded != nullptr;
+        {
+            // the epilogue warps bring the table in while the producer and the MMA issuer fill the pipeline
+            const uint4* src = reinterpret_cast<const uint4*>(folded ? p.mb_folded : p.mb);
+            for (int i = (int)threadIdx.x - 64; i < p.tab_bytes / 16; i += 32 * kEpilogueWarps) {
+                const uint4 v = __ldg(src + i);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tab_base + 16u * (uint32_t)i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        }
         int t = 0;
         bool ok = true;
         long long w_tfull = 0, dbg_ld = 0, dbg_math = 0, dbg_st = 0;
         long long* pwe = p.debug ? &w_tfull : nullptr;
         const long long t_start = kRoleTiming ? clock64() : 0;
-        int turn = 0;  // t % groups
-        for (int tile = blockIdx.x; ok && group < groups && tile < p.num_tiles; tile += gridDim.x, ++t, turn = turn + 1 == groups ? 0 : turn + 1) {
-            if (turn != group) continue;  // another group of epilogue warps takes this tile
+        int turn = 0;  // unit counter modulo groups
+        for (int tile = blockIdx.x; ok && group < groups && tile < p.num_tiles; tile += gridDim.x, ++t)
+        for (int sub = 0; ok && sub < subs; ++sub, turn = turn + 1 == groups ? 0 : turn + 1) {
+            if (turn != group) continue;  // another group of epilogue warps takes this unit
+            const int c_begin = sub * sub_cols, c_end = c_begin + sub_cols;
             const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
             const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
             const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
@@ -406,7 +460,72 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * bn);
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
-            for (int c0 = 0; c0 < bn; c0 += 32) {
+            if (folded) {
+                // Fast mode, int8 out, accumulators below 2^22, filters a multiple of 32 (every chunk is full).  The accumulators
+                // come 16 columns at a time into two register sets: while one set is turned into codes the load of the next is
+                // in flight, so the TMEM latency is paid once per tile, not once per chunk.
+                // Adding an accumulator to the bits of 1.5 * 2^23 gives the float 1.5 * 2^23 + accumulator; the table holds
+                // {mult 2i, mult 2i+1, bias 2i, bias 2i+1} divided by the output scale, the bias carrying -1.5 * 2^23 * mult, so
+                // one packed FMA yields two pre-activations in code units; activation and rounding run in packed binary16.
+                const __half2 kh = __float2half2_rn(p.sy_log2e), inv_h = __float2half2_rn(p.inv_sy);
+                uint32_t a0[16], a1[16];
+                auto codes16 = [&](const uint32_t (&a)[16], uint32_t mt, uint32_t (&out)[4]) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 ma = lds_f4(mt + 32u * j), mc = lds_f4(mt + 32u * j + 16u);
+                        float t0, t1, t2, t3;
+                        ffma2(t0, t1, __int_as_float(0x4B400000 + (int)a[4 * j]), __int_as_float(0x4B400000 + (int)a[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
+                        ffma2(t2, t3, __int_as_float(0x4B400000 + (int)a[4 * j + 2]), __int_as_float(0x4B400000 + (int)a[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
+                        out[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
+                    }
+                };
+                tmem_ld_32x16(taddr0 + (uint32_t)c_begin, a0);
+                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+                    int64_t opix = pix;
+                    int fo = f0 + c0;
+                    if (p.pack > 1) {
+                        int j = 0;
+                        while (fo >= p.f_real) { fo -= p.f_real; ++j; }
+                        opix = pix * p.pack + j;
+                    }
+                    uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
+                    if (p.res != nullptr && valid) {  // residual codes of the fused shortcut
+                        const uint4* rp = (const uint4*)((const uint8_t*)p.res + opix * p.res_pixel_stride + fo);
+                        r0 = __ldg(rp);
+                        r1 = __ldg(rp + 1);
+                    }
+                    const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);
+                    uint32_t lo[4], hi[4];
+                    tmem_ld_wait16(a0);
+                    tmem_ld_32x16(taddr0 + (uint32_t)c0 + 16u, a1);
+                    codes16(a0, mtab, lo);
+                    tmem_ld_wait16(a1);
+                    if (c0 + 32 < c_end) tmem_ld_32x16(taddr0 + (uint32_t)c0 + 32u, a0);
+                    codes16(a1, mtab + 128u, hi);
+                    uint32_t packed[8] = {lo[0], lo[1], lo[2], lo[3], hi[0], hi[1], hi[2], hi[3]};
+                    if (p.res != nullptr) {
+                        // fused shortcut, the arithmetic of the stand-alone shortcut kernel applied to the codes just produced
+                        const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            uint32_t u[4];
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                float v = __fmul_rn(s8_to_float(packed[j], b), p.s_c);
+                                v = __fmaf_rn(s8_to_float(rw[j], b), p.s_res, v);
+                                u[b] = quant_i8_magic(v, p.inv_sy2);
+                            }
+                            packed[j] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
+                        }
+                    }
+                    if (valid) {
+                        uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
+                        o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
+                }
+            } else
+            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                 uint32_t acc[32];
                 const long long tq0 = kRoleTiming && p.debug ? clock64() : 0;
                 tmem_ld_32x32(taddr0 + (uint32_t)c0, acc);
@@ -423,11 +542,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                 if (fast) {
                     // ---- fast path: 32 valid filters, int8 out.  The {mult, bias} pairs (two per 16-byte load) are fetched
                     // while the TMEM load is in flight, so the arithmetic below runs from registers only.
-                    const bool folded = !EXACT && p.mb_folded != nullptr;
-                    const float4* mb4 = reinterpret_cast<const float4*>((folded ? p.mb_folded : p.mb) + f0 + c0);
-                    float4 m[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) m[j] = ldg_f4_pinned(mb4 + j);
+                    const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);
                     uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
                     if (p.res != nullptr && valid) {  // residual codes of the fused shortcut, fetched while TMEM is read
                         const uint4* rp = (const uint4*)((const uint8_t*)p.res + opix * p.res_pixel_stride + fo);
@@ -439,43 +554,28 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     if (kRoleTiming && p.debug) dbg_ld += tq1 - tq0;
                     if (!valid) continue;
                     uint32_t packed[8];
-                    // int32 -> f32.  When every accumulator is known to stay below 2^22, adding it to the bits of 1.5*2^23
-                    // converts exactly in two FMA-pipe instructions; otherwise the conversion unit (or, for the
-                    // transcendental epilogues that need that unit for ex2/rcp, an exact ALU sequence).
-                    float x[32];
-                    if (folded) {
-                        // the bias already carries -1.5 * 2^23 * mult: the FMA below removes the offset and applies scale and bias at once
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) x[j] = __int_as_float(0x4B400000 + (int)acc[j]);
-                    } else if (p.small_acc) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) x[j] = __fadd_rn(__int_as_float(0x4B400000 + (int)acc[j]), -12582912.0f);
-                    } else if (kTranscendental) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) x[j] = i2f_alu((int)acc[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) x[j] = __int2float_rn((int)acc[j]);
-                    }
-                    if (EXACT) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            x[2 * j] = ln_epilogue_act<true>(ACT, __fmaf_rn(x[2 * j], m[j].x, m[j].y));
-                            x[2 * j + 1] = ln_epilogue_act<true>(ACT, __fmaf_rn(x[2 * j + 1], m[j].z, m[j].w));
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            packed[j] = pack4_low_bytes(quant_i8_magic(x[4 * j], p.inv_sy), quant_i8_magic(x[4 * j + 1], p.inv_sy),
-                                                        quant_i8_magic(x[4 * j + 2], p.inv_sy), quant_i8_magic(x[4 * j + 3], p.inv_sy));
-                    } else {
-                        // fast mode: the f32 scale-and-bias stays exact, activation and requantisation run two at a time in binary16
+                    // Four values at a time, each loop body fetching its own two table entries from shared memory, so that few
+                    // values are live at once (the kernel has to fit in 96 registers).
+                    {
+                        // int32 -> f32: below 2^22 through the bits of 1.5 * 2^23 (two FMA-pipe instructions, exact); otherwise the
+                        // conversion unit, or, for the transcendental epilogues that need that unit for ex2 / rcp, an exact ALU sequence
+                        const bool small = p.small_acc != 0;
                         const __half2 inv_h = __float2half2_rn(p.inv_sy);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const uint32_t q01 = ln_h2_act_quant<ACT>(__fmaf_rn(x[4 * j], m[2 * j].x, m[2 * j].y), __fmaf_rn(x[4 * j + 1], m[2 * j].z, m[2 * j].w), inv_h);
-                            const uint32_t q23 = ln_h2_act_quant<ACT>(__fmaf_rn(x[4 * j + 2], m[2 * j + 1].x, m[2 * j + 1].y),
-                                                                      __fmaf_rn(x[4 * j + 3], m[2 * j + 1].z, m[2 * j + 1].w), inv_h);
-                            packed[j] = ln_h2_pack(q01, q23);
+                            const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
+                            float x[4];
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const int a = (int)acc[4 * j + b];
+                                x[b] = small ? __fadd_rn(__int_as_float(0x4B400000 + a), -12582912.0f) : (kTranscendental ? i2f_alu(a) : __int2float_rn(a));
+                            }
+                            const float v0 = __fmaf_rn(x[0], ma.x, ma.y), v1 = __fmaf_rn(x[1], ma.z, ma.w), v2 = __fmaf_rn(x[2], mc.x, mc.y), v3 = __fmaf_rn(x[3], mc.z, mc.w);
+                            if (EXACT)
+                                packed[j] = pack4_low_bytes(quant_i8_magic(ln_epilogue_act<true>(ACT, v0), p.inv_sy), quant_i8_magic(ln_epilogue_act<true>(ACT, v1), p.inv_sy),
+                                                            quant_i8_magic(ln_epilogue_act<true>(ACT, v2), p.inv_sy), quant_i8_magic(ln_epilogue_act<true>(ACT, v3), p.inv_sy));
+                            else
+                                packed[j] = ln_h2_pack(ln_h2_act_quant<ACT>(v0, v1, inv_h), ln_h2_act_quant<ACT>(v2, v3, inv_h));
                         }
                     }
                     if (p.res != nullptr) {
@@ -515,10 +615,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     continue;
                 }
                 float a[32];
-                const float4* mb4 = reinterpret_cast<const float4*>(p.mb + f0 + c0);
+                const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);  // (never the folded table: that one needs int8 output and full chunks)
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float4 mj = __ldg(mb4 + j);
+                    const float4 mj = lds_f4(mtab + 16u * j);
                     const float x0 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
                     const float x1 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
                     a[2 * j] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x0, mj.x, mj.y));
@@ -563,7 +663,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(buf));
         }
-        if (p.debug && blockIdx.x == 0 && lane == 0) {
+        if (p.debug && blockIdx.x == 0 && lane == 0 && warp - 2 < 8) {  // (the counter block has room for eight epilogue warps)
             p.debug[6 + 2 * (warp - 2)] = clock64() - t_start;
             p.debug[7 + 2 * (warp - 2)] = w_tfull;
             if (warp == 2) { p.debug[22] = dbg_ld; p.debug[23] = dbg_math; p.debug[24] = dbg_st; }
@@ -586,6 +686,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
 }
 
 constexpr int kMaxDynamicSmem = 227 * 1024;
+constexpr uint32_t kMaxTableBytes = 32u * 1024u;  // {multiplier, bias} pairs of at most 4096 filters
 
 template <int KIND, bool EXACT>
 cudaError_t launch_act(ln_ctx* ctx, const ln_conv_umma_params& p, int grid, size_t smem, cudaStream_t stream) {
@@ -666,9 +767,16 @@ __global__ void pack_s2d_weights_kernel(const uint8_t* __restrict__ w, int fpad,
     *reinterpret_cast<uint32_t*>(w2 + (size_t)i * 4) = v;
 }
 
-__global__ void fold_mb_kernel(const float2* __restrict__ mb, int n, float2* __restrict__ out) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = make_float2(mb[i].x, __fmaf_rn(-12582912.0f, mb[i].x, mb[i].y));
+// Table of the folded fast epilogue, one float4 per pair of filters: {m0, m1, b0, b1} with m = mult / s_y and
+// b = bias / s_y - 1.5 * 2^23 * m, so that fma(float with the bits 0x4B400000 + accumulator, m, b) is the pre-activation in
+// units of the output scale.
+__global__ void fold_mb_kernel(const float2* __restrict__ mb, int n, float inv_sy, float2* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;  // pair index
+    if (2 * i >= n) return;
+    const float m0 = __fmul_rn(mb[2 * i].x, inv_sy), m1 = __fmul_rn(mb[2 * i + 1].x, inv_sy);
+    const float b0 = __fmaf_rn(-12582912.0f, m0, __fmul_rn(mb[2 * i].y, inv_sy)), b1 = __fmaf_rn(-12582912.0f, m1, __fmul_rn(mb[2 * i + 1].y, inv_sy));
+    out[2 * i] = make_float2(m0, m1);
+    out[2 * i + 1] = make_float2(b0, b1);
 }
 
 int ilog2(int v) {
@@ -803,6 +911,8 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.OW = g.OW; p.OH = g.OH; p.N = g.N; p.F = g.F;
     p.fpad_used = (int)ln_round_up(g.F, 32);
     p.nbuf = 512 / bn > kMaxAccBufs ? kMaxAccBufs : 512 / bn;
+    p.subs = p.nbuf >= kEpilogueGroups ? 1 : (kEpilogueGroups + p.nbuf - 1) / p.nbuf;  // column units per tile: keeps every epilogue group busy
+    while (p.subs > 1 && (bn % (32 * p.subs)) != 0) --p.subs;
     p.small_acc = g.small_acc ? 1 : 0;
     p.pack = pack; p.f_real = g_in.F;
     choose_box(g.OW, g.OH, g.N, g.out_kind != LN_OUT_Q, &p.TW, &p.TH, &p.TN);
@@ -813,7 +923,11 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     // is a multiple of 8 -- so a tile and channel block costs 3 loads instead of 9.  The tile has to be TW x TH pixels of one
     // image; the mode is used when that shape wastes at most 15 % of the rows, and only for layers of at most 64 channels:
     // measured, it gains 10 % there and loses with 128 and more (the larger boxes complete later than per-tap boxes do).
-    const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u;
+    // {multiplier, bias} pairs of every filter tile, kept in shared memory behind the barrier block
+    const uint32_t tab_bytes = (uint32_t)(ln_round_up(g.F, bn) * sizeof(float2));
+    if (tab_bytes > kMaxTableBytes) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d filters exceed the %u the epilogue table holds", g.F, kMaxTableBytes / 8u);
+    p.tab_bytes = (int)tab_bytes;
+    const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u - tab_bytes;
     if (allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
         int best_tw = 0, best_th = 0;
         int64_t best_tiles = -1;
@@ -850,11 +964,13 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.debug = ctx->debug_cycles;
     p.mb = mb;
     p.mb_folded = nullptr;
-    if (g.kind == LN_KIND_I8 && g.small_acc && g.out_kind == LN_OUT_Q) {
+    p.sy_log2e = 1.44269504f / g.inv_sy;
+    // (the folded epilogue drops the lower clamp of the activations that are bounded below: needs 0.31 / s_y <= 127)
+    if (g.kind == LN_KIND_I8 && g.small_acc && g.out_kind == LN_OUT_Q && g.inv_sy <= 400.0f && g.F % 32 == 0) {
         plan->aux_mbf_bytes = (size_t)g.fpad * sizeof(float2);
         plan->aux_mbf = (float2*)ln_pool_alloc(ctx, plan->aux_mbf_bytes);
         if (!plan->aux_mbf) return LN_ERR_CUDA;
-        fold_mb_kernel<<<(g.fpad + 127) / 128, 128, 0, ctx->stream>>>(mb, g.fpad, plan->aux_mbf);
+        fold_mb_kernel<<<(g.fpad / 2 + 127) / 128, 128, 0, ctx->stream>>>(mb, g.fpad, g.inv_sy, plan->aux_mbf);
         LN_LAUNCHED(ctx);
         p.mb_folded = plan->aux_mbf;
     }
@@ -883,12 +999,13 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     } else {
     p.b_resident = (allow_resident && p.tiles_f == 1 && b_total + res_min_stages * 128u * bk <= smem_budget) ? 1 : 0;
     const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + bn) * bk;
-    int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u) - (p.b_resident ? b_total : 0u)) / stage_bytes);
+    int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u)) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
     p.stages = stages;
     plan->smem = (size_t)stages * stage_bytes + (p.b_resident ? b_total : 0u) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     }
+    plan->smem += tab_bytes;
     plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     plan->kind = g.kind;
 

@@ -714,7 +714,7 @@ int build_plan(ln_net* net, int mb) {
                 } else {
                     g.x = net->views[i - 1].ptr; g.x_pixel_stride = net->views[i - 1].cstride;
                 }
-                if (g.x_pixel_stride >= g.cpad && ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H)) {
+                if (g.x_pixel_stride >= g.cpad && g.F <= 4096 && ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H)) {
                     st.op = 0;
                     st.umma.mb = st.mb;
                     rc = ln_conv_umma_plan_build(ctx, &st.umma, g);

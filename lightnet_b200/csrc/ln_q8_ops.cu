@@ -951,7 +951,7 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
     g.small_acc = kind == LN_KIND_I8 && 127.0f * weights->max_l1 < 4194304.0f;
     g.out = y->ptr; g.out_pixel_stride = y->cstride;
     if (rc == LN_OK) {
-        if (x->cstride >= weights->cpad && ln_conv_umma_supported(weights->cpad, kernel_size, stride_x, stride_y, dilation, groups, input_width, input_height)) {
+        if (x->cstride >= weights->cpad && filters <= 4096 && ln_conv_umma_supported(weights->cpad, kernel_size, stride_x, stride_y, dilation, groups, input_width, input_height)) {
             ln_conv_umma_plan plan;
             plan.mb = mb;
             rc = ln_conv_umma_plan_build(ctx, &plan, g);
