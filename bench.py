@@ -42,6 +42,7 @@ WORKLOADS = {
     "nms-stress": dict(model=None, size=640, batch=256, precision="f32", metric="decode + NMS GB/s (25200 candidates x 80 classes per image)"),
     "preprocess": dict(model=None, size=608, batch=64, precision="f32", metric="images/sec letterbox pre-processing (640x480 8-bit RGB -> 608x608 f32 NCHW)"),
     "conv-sweep": dict(model=None, size=0, batch=16, precision="int8+fp8", metric="TOP/s single-layer implicit-GEMM convolution (bias + leaky epilogue)"),
+    "mma-peak": dict(model=None, size=0, batch=1, precision="int8", metric="TOP/s of a tcgen05.mma-only loop (M=128, N=256, operands resident in shared memory)"),
 }
 # (channels, height, width, filters, kernel, stride, pad) of the single-layer sweep
 SWEEP_LAYERS = [(256, 52, 52, 512, 3, 1, 1), (512, 52, 52, 256, 1, 1, 0), (128, 104, 104, 256, 3, 2, 1)]
@@ -220,8 +221,8 @@ def run_reference(args, rank):
     wl = WORKLOADS[args.workload]
     steps = max(1, min(args.steps, 2))
     total, note = 0.0, ""
-    if args.workload == "conv-sweep":
-        emit_line(({"impl": "reference", "unavailable": "the reference has no int8 / FP8 convolution; the sweep has no CPU arm"}))
+    if args.workload in ("conv-sweep", "mma-peak"):
+        emit_line(({"impl": "reference", "unavailable": "the reference has no int8 / FP8 convolution; this workload has no CPU arm"}))
         return
     if args.workload == "preprocess":
         from oracle import oracle_api as orc
@@ -374,6 +375,31 @@ def run_conv_sweep(args, be, rank, world, local_rank):
             "layers": rows, "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel", "achieved": best["tops"], "peak": peak, "unit": "TOP/s",
                          "frac": best["tops"] / peak, "traffic": None, "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf)}}))
+
+
+def run_mma_peak(args, be, rank, world, local_rank):
+    """The tensor-pipe denominators: tcgen05.mma issued back to back on every SM with nothing else in the way (ln_debug_mma_peak),
+    for the three operand types, timed with CUDA events inside the library."""
+    import lightnet_b200 as ln
+
+    iters = 8192
+    launches0 = be.launch_count
+    vals = {name: max(be.mma_peak(dt, iters) for _ in range(max(args.steps, 3))) for name, dt in (("int8", ln.LN_Q8), ("fp8", ln.LN_F8), ("f16", ln.LN_F16))}
+    bf16_tf, _, basis = measured_peaks()
+    if rank == 0:
+        emit_line({"metric": WORKLOADS["mma-peak"]["metric"], "value": vals["int8"], "unit": "TOP/s", "n_gpus": world, "steps": max(args.steps, 3), "warmup": 1,
+                   "ms_per_step": 2.0 * 128 * 256 * 32 * 4 * iters * be_sm_count(be) / (vals["int8"] * 1e12) * 1e3, "higher_is_better": True, "scaling": "weak",
+                   "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                   "config": {"workload": "tcgen05.mma kind::i8 / f8f6f4 / f16, %d x 4 instructions per SM, best of %d launches" % (iters, max(args.steps, 3)),
+                              "l2": "no memory traffic: operands stay in shared memory"},
+                   "peaks_tops": vals, "gpu_launches": int(be.launch_count - launches0),
+                   "roofline": {"bound": "tensor", "kernel": "mma_peak_kernel", "achieved": vals["int8"], "peak": 2.0 * bf16_tf, "unit": "TOP/s",
+                                "frac": vals["int8"] / (2.0 * bf16_tf), "traffic": None, "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf)}})
+
+
+def be_sm_count(be):
+    import torch
+    return torch.cuda.get_device_properties(be.device).multi_processor_count
 
 
 def run_preprocess(args, be, rank, world, local_rank):
@@ -565,7 +591,7 @@ def main():
     B = args.batch
     be = ln.B200Backend(local_rank)
     if wl["model"] is None:
-        {"conv-sweep": run_conv_sweep, "preprocess": run_preprocess}.get(args.workload, run_nms_stress)(args, be, rank, world, local_rank)
+        {"conv-sweep": run_conv_sweep, "preprocess": run_preprocess, "mma-peak": run_mma_peak}.get(args.workload, run_nms_stress)(args, be, rank, world, local_rank)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -627,6 +653,7 @@ def main():
     ops_img = conv_ops_per_image(layers) - 2 * layers[0]["out_w"] * layers[0]["out_h"] * layers[0]["out_c"] * layers[0]["in_c"] * layers[0]["size"] ** 2
     bf16_tf, hbm_gbs, basis = measured_peaks()
     peak = 2.0 * bf16_tf  # dense int8 / FP8 tensor throughput is twice bf16 on this part
+    mma_peak = max(be.mma_peak(prec, 4096) for _ in range(3))  # the same denominator measured: a tcgen05.mma-only loop on every SM
     achieved = ops_img * B / (umma_ms * 1e-3) / 1e12 if umma_ms > 0 else 0.0
 
     if rank == 0:
@@ -649,6 +676,8 @@ def main():
                          "traffic_basis": "not measured at this batch: an ncu capture of all launches of a 64-image step is beyond the size a capture may have; per-launch DRAM bytes of single layers are in the profiles/ summaries named under layer_classes",
                          "algorithmic_bytes": conv_bytes_per_image(layers) * B,
                          "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf), "launches_per_step": umma_launches,
+                         "peak_mma_loop": mma_peak, "frac_of_mma_loop": achieved / mma_peak if mma_peak > 0 else None,
+                         "peak_mma_loop_basis": "tcgen05.mma-only loop of this library on this GPU (ln_debug_mma_peak), burst clocks",
                          "ms_per_step": umma_ms},
             "kernel_classes_ms": {k: v[0] for k, v in per_op.items()},
             "layer_classes": layer_classes(layers, per_layer, B),

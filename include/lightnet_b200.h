@@ -49,7 +49,7 @@ enum ln_status {
 /* F32ActivationKind (lightnet-cuda/src/lib.rs:23-55), hot-path subset. */
 enum ln_activation { LN_ACT_LINEAR = 0, LN_ACT_LOGISTIC = 1, LN_ACT_LEAKY = 2, LN_ACT_MISH = 3, LN_ACT_SWISH = 4, LN_ACT_RELU = 5 };
 
-enum ln_dtype { LN_F32 = 0, LN_Q8 = 1, LN_I32 = 2, LN_F8 = 3 };
+enum ln_dtype { LN_F32 = 0, LN_Q8 = 1, LN_I32 = 2, LN_F8 = 3, LN_F16 = 4 };
 
 /* What a reduced-precision convolution writes. */
 enum ln_conv_out {
@@ -117,6 +117,9 @@ int32_t ln_maxpool_f32(ln_ctx* ctx, const ln_tensor* x, const int64_t output_sha
 int32_t ln_upsample_f32(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels,
                         int64_t input_height, int64_t input_width, int64_t stride, float scale, int32_t reverse,
                         ln_tensor** out);
+/* channel_scale_f32 (lib.rs:485): out[i] = x[i] * scale[(i / channel_stride) % channels] */
+int32_t ln_channel_scale_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* scale, int64_t channels, int64_t channel_stride,
+                             ln_tensor** out);
 /* batchnorm_fold_f32 (lib.rs:6208): returns (scale, bias') */
 int32_t ln_batchnorm_fold_f32(ln_ctx* ctx, const ln_tensor* gamma, const ln_tensor* mean, const ln_tensor* variance,
                               const ln_tensor* bias, float eps, ln_tensor** scale_out, ln_tensor** bias_out);
@@ -166,6 +169,39 @@ int32_t ln_route_concat_q(ln_ctx* ctx, const ln_tensor* const* inputs, int32_t n
                           int64_t channel_stride, ln_tensor** out);
 int32_t ln_shortcut_add_act_q(ln_ctx* ctx, const ln_tensor* a, const ln_tensor* b, int32_t activation, float y_scale,
                               ln_tensor** out);
+
+/* ---- binary16 storage: trait F16TensorOpsBackend (lib.rs:6295-6629) ------------------------ */
+/* The twin that forward_compact_f16 (lightnet-runtime/src/runtime/gpu_f16.rs:21) drives, method for method.  TensorF16 is an
+   ln_tensor of dtype LN_F16 (storage backend-defined: NHWC, channels padded to 32); values are rounded once to binary16 (nearest
+   even, overflow stays infinite); convolutions run tcgen05.mma kind::f16 with binary32 accumulation.
+   upload_f16 (lib.rs:6300), download_f16 (:6302, widened to f32 NCHW), widen_f16 (:6304), narrow_f32 (:6308). */
+int32_t ln_tensor_upload_f16(ln_ctx* ctx, const int64_t shape[4], const float* host, ln_tensor** out);
+int32_t ln_tensor_download_f16(ln_ctx* ctx, const ln_tensor* t, float* host, int64_t count);
+int32_t ln_tensor_widen_f16(ln_ctx* ctx, const ln_tensor* t, ln_tensor** out_f32);
+int32_t ln_tensor_narrow_f16(ln_ctx* ctx, const ln_tensor* t_f32, ln_tensor** out_f16);
+/* conv_weights_f16 (lib.rs:6311): f32 [filters, per_filter] BN-folded weights -> the backend's GEMM operand.  Released with
+   ln_conv_weights_release. */
+int32_t ln_conv_weights_f16(ln_ctx* ctx, const ln_tensor* weights_f32, int64_t filters, int64_t per_filter, ln_conv_weights** out);
+/* conv2d_bias_act_f16 (lib.rs:6342): f16(activation(conv(x, weights) + bias)), bias f32 [filters].  groups = 1, dilation = 1 and
+   stride_x = stride_y in {1, 2} run on the tensor cores; every other geometry runs a CUDA-core kernel with the same arithmetic.
+   (`weights` is not const: the operand layout is built by the first call that names the geometry.) */
+int32_t ln_conv2d_bias_act_f16(ln_ctx* ctx, const ln_tensor* x, ln_conv_weights* weights, const ln_tensor* bias,
+                               const int64_t output_shape[4], int64_t channels, int64_t input_height, int64_t input_width,
+                               int64_t filters, int64_t size, int64_t stride_x, int64_t stride_y, int64_t dilation, int64_t padding,
+                               int64_t groups, int32_t activation, ln_tensor** out);
+/* maxpool_f16 (lib.rs:6384), upsample_f16 (:6405; reverse != 0 sums stride x stride blocks), route_concat_f16 (:6417),
+   shortcut_fit_f16 (:6494), shortcut_add_act_f16 (:6502), channel_affine_act_f16 (:6619; scale may be NULL). */
+int32_t ln_maxpool_f16(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height,
+                       int64_t input_width, int64_t size, int64_t stride_x, int64_t stride_y, int64_t padding, ln_tensor** out);
+int32_t ln_upsample_f16(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height,
+                        int64_t input_width, int64_t stride, float scale, int32_t reverse, ln_tensor** out);
+int32_t ln_route_concat_f16(ln_ctx* ctx, const ln_tensor* const* inputs, int32_t n_inputs, const int64_t* input_channel_offsets,
+                            const int64_t* input_channels, const int64_t* input_total_channels, const int64_t output_shape[4],
+                            int64_t channel_stride, ln_tensor** out);
+int32_t ln_shortcut_fit_f16(ln_ctx* ctx, const ln_tensor* x, int64_t batch, const int64_t output_shape[4], ln_tensor** out);
+int32_t ln_shortcut_add_act_f16(ln_ctx* ctx, const ln_tensor* a, const ln_tensor* b, int32_t activation, ln_tensor** out);
+int32_t ln_channel_affine_act_f16(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* scale, const ln_tensor* bias, int64_t channels,
+                                  int64_t channel_stride, int32_t activation, ln_tensor** out);
 
 /* ---- [yolo] decode + NMS on the device ---------------------------------------------- */
 /* Optional device path for decode_network_detections (lightnet-train/src/detect.rs:113-244): the Rust shim
@@ -238,13 +274,14 @@ int32_t ln_image_preprocess_u8(ln_ctx* ctx, const uint8_t* pixels_host, const in
 
 /* ---- whole network: GpuExecutableNetwork<B> ------------------------------------------ */
 /* GpuExecutableNetwork::new (runtime/gpu_state.rs:8) from cfg text; `batch` > 0 overrides [net] batch
-   (Network::with_batch, model.rs:3256).  precision: LN_F32 (trait-faithful f32 NCHW path), LN_Q8 or LN_F8. */
+   (Network::with_batch, model.rs:3256).  precision: LN_F32 (trait-faithful f32 NCHW path), LN_F16 (the operator sequence of
+   forward_compact_f16 over the binary16 twin), LN_Q8 or LN_F8. */
 int32_t ln_net_create(ln_ctx* ctx, const char* cfg_text, int32_t batch, int32_t precision, ln_net** out);
 int32_t ln_net_destroy(ln_net* net);
 int32_t ln_net_num_layers(const ln_net* net);
-/* info[16]: kind(0 conv,1 maxpool,2 route,3 shortcut,4 upsample,5 yolo), in w,h,c,b, out w,h,c,b,
-   filters,size,stride_x,stride_y,padding,batch_normalize,activation */
-int32_t ln_net_layer_info(const ln_net* net, int32_t layer, int32_t info[16]);
+/* info[20]: kind(0 conv,1 maxpool,2 route,3 shortcut,4 upsample,5 yolo), in w,h,c,b, out w,h,c,b,
+   filters,size,stride_x,stride_y,padding,batch_normalize,activation,groups,dilation, two reserved (0) */
+int32_t ln_net_layer_info(const ln_net* net, int32_t layer, int32_t info[20]);
 int64_t ln_net_weight_count(const ln_net* net);
 /* load_weights_file payload (runtime/weights_io.rs:227-235): per conv biases, [scales, mean, variance], weights. */
 int32_t ln_net_load_weights(ln_net* net, const float* blob, int64_t count);
@@ -306,6 +343,10 @@ int32_t ln_net_profile(const ln_net* net, float* per_layer_ms, int32_t num_layer
    logits in [x_lo, x_hi].  The passes trust the approximation only beyond 256 units from a decision boundary. */
 int32_t ln_debug_score_key_error(ln_ctx* ctx, float obj_lo, float obj_hi, float x_lo, float x_hi, int32_t n_obj, int32_t n_x,
                                  uint32_t* worst);
+/* Sustained tensor-core rate of this GPU, in TOP/s (TFLOP/s for binary16): every SM issues `iters` x 4 tcgen05.mma instructions
+   (M = 128, N = 256, 32 bytes of K each) on operands resident in shared memory, timed with CUDA events on the ctx stream.  The
+   measured denominator of the convolution's roofline.  dtype: LN_Q8, LN_F8 or LN_F16. */
+int32_t ln_debug_mma_peak(ln_ctx* ctx, int32_t dtype, int32_t iters, float* tops);
 /* Role-timing counters (clock cycles) that CTA 0 of the most recent tensor-core convolution recorded: [0..1] producer total /
    waiting, [2..5] MMA issuer total / waiting for an accumulator / waiting for operands / tiles, [6..] epilogue warps.  Only with
    a library built with -DLN_CONV_ROLE_TIMING and LN_DEBUG_CYCLES=1 in the environment at ln_ctx_create; LN_ERR_UNSUPPORTED

@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # the in-tree library; LIGHTNET_B200_LIB names another build of it (e.g. one compiled with extra -D switches for an A/B run)
 LIB_PATH = os.environ.get("LIGHTNET_B200_LIB") or os.path.join(_HERE, "liblightnet_b200.so")
 
-LN_F32, LN_Q8, LN_I32, LN_F8 = 0, 1, 2, 3
+LN_F32, LN_Q8, LN_I32, LN_F8, LN_F16 = 0, 1, 2, 3, 4
 LN_OUT_Q, LN_OUT_F32, LN_OUT_ACC = 0, 1, 2
 ACTIVATIONS = {"linear": 0, "logistic": 1, "leaky": 2, "mish": 3, "swish": 4, "relu": 5}
 STATUS = {0: "ok", 1: "shape", 2: "cuda", 3: "timeout", 4: "unsupported", 5: "argument", 6: "parse"}
@@ -139,8 +139,22 @@ SYMBOLS = {
     "ln_net_set_host_pipeline": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_set_cuda_graph": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_profile": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
+    "ln_channel_scale_f32": (C.c_int32, [_VP, _VP, _VP, C.c_int64, C.c_int64, _PP]),
+    "ln_tensor_upload_f16": (C.c_int32, [_VP, _I64P, _VP, _PP]),
+    "ln_tensor_download_f16": (C.c_int32, [_VP, _VP, _VP, C.c_int64]),
+    "ln_tensor_widen_f16": (C.c_int32, [_VP, _VP, _PP]),
+    "ln_tensor_narrow_f16": (C.c_int32, [_VP, _VP, _PP]),
+    "ln_conv_weights_f16": (C.c_int32, [_VP, _VP, C.c_int64, C.c_int64, _PP]),
+    "ln_conv2d_bias_act_f16": (C.c_int32, [_VP, _VP, _VP, _VP, _I64P] + [C.c_int64] * 10 + [C.c_int32, _PP]),
+    "ln_maxpool_f16": (C.c_int32, [_VP, _VP, _I64P] + [C.c_int64] * 7 + [_PP]),
+    "ln_upsample_f16": (C.c_int32, [_VP, _VP, _I64P] + [C.c_int64] * 4 + [C.c_float, C.c_int32, _PP]),
+    "ln_route_concat_f16": (C.c_int32, [_VP, _PP, C.c_int32, _I64P, _I64P, _I64P, _I64P, C.c_int64, _PP]),
+    "ln_shortcut_fit_f16": (C.c_int32, [_VP, _VP, C.c_int64, _I64P, _PP]),
+    "ln_shortcut_add_act_f16": (C.c_int32, [_VP, _VP, _VP, C.c_int32, _PP]),
+    "ln_channel_affine_act_f16": (C.c_int32, [_VP, _VP, _VP, _VP, C.c_int64, C.c_int64, C.c_int32, _PP]),
     "ln_debug_score_key_error": (C.c_int32, [_VP, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32, C.POINTER(C.c_uint32)]),
     "ln_ctx_debug_cycles": (C.c_int32, [_VP, _I64P]),
+    "ln_debug_mma_peak": (C.c_int32, [_VP, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
 }
 
 
@@ -279,6 +293,12 @@ class B200Backend:
         self._check(self.lib.ln_debug_score_key_error(self.ctx, obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x, C.byref(worst)))
         return int(worst.value)
 
+    def mma_peak(self, dtype=LN_Q8, iters=4096):
+        """Measured tensor-core rate (TOP/s) of a tcgen05.mma-only loop on every SM."""
+        t = C.c_float()
+        self._check(self.lib.ln_debug_mma_peak(self.ctx, dtype, iters, C.byref(t)))
+        return float(t.value)
+
     def debug_cycles(self):
         """The 32 role-timing counters of the last tensor-core convolution (needs a -DLN_CONV_ROLE_TIMING build and LN_DEBUG_CYCLES=1)."""
         out = (C.c_int64 * 32)()
@@ -346,6 +366,54 @@ class B200Backend:
         s, b = C.c_void_p(), C.c_void_p()
         self._check(self.lib.ln_batchnorm_fold_f32(self.ctx, gamma.h, mean.h, variance.h, bias.h, float(eps), C.byref(s), C.byref(b)))
         return Tensor(self, s), Tensor(self, b)
+
+    def channel_scale_f32(self, x, scale, channels, channel_stride):
+        return self._out(self.lib.ln_channel_scale_f32, x.h, scale.h, channels, channel_stride)
+
+    # ---- F16TensorOpsBackend (binary16 storage) ---------------------------------------------------
+    def upload_f16(self, shape, host):
+        host = np.ascontiguousarray(host, np.float32)
+        return self._out(self.lib.ln_tensor_upload_f16, _shape4(shape), _ptr(host))
+
+    def download_f16(self, t):
+        out = np.empty(t.shape, np.float32)
+        self._check(self.lib.ln_tensor_download_f16(self.ctx, t.h, _ptr(out), out.size))
+        return out
+
+    def widen_f16(self, t):
+        return self._out(self.lib.ln_tensor_widen_f16, t.h)
+
+    def narrow_f32_f16(self, t):
+        """narrow_f32 of the binary16 trait: an f32 device tensor rounded to binary16 storage."""
+        return self._out(self.lib.ln_tensor_narrow_f16, t.h)
+
+    def conv_weights_f16(self, weights, filters, per_filter):
+        h = C.c_void_p()
+        self._check(self.lib.ln_conv_weights_f16(self.ctx, weights.h, filters, per_filter, C.byref(h)))
+        return ConvWeights(self, h)
+
+    def conv2d_bias_act_f16(self, x, weights, bias, output_shape, channels, input_height, input_width, filters, size, stride_x, stride_y,
+                            dilation, padding, groups, activation):
+        return self._out(self.lib.ln_conv2d_bias_act_f16, x.h, weights.h, bias.h, _shape4(output_shape), channels, input_height, input_width,
+                         filters, size, stride_x, stride_y, dilation, padding, groups, _act(activation))
+
+    def maxpool_f16(self, x, output_shape, channels, input_height, input_width, size, stride_x, stride_y, padding):
+        return self._out(self.lib.ln_maxpool_f16, x.h, _shape4(output_shape), channels, input_height, input_width, size, stride_x, stride_y, padding)
+
+    def upsample_f16(self, x, output_shape, channels, input_height, input_width, stride, scale, reverse):
+        return self._out(self.lib.ln_upsample_f16, x.h, _shape4(output_shape), channels, input_height, input_width, stride, float(scale), int(bool(reverse)))
+
+    def route_concat_f16(self, inputs, input_channel_offsets, input_channels, input_total_channels, output_shape, channel_stride):
+        return self._route(self.lib.ln_route_concat_f16, inputs, input_channel_offsets, input_channels, input_total_channels, output_shape, channel_stride)
+
+    def shortcut_fit_f16(self, x, batch, output_shape):
+        return self._out(self.lib.ln_shortcut_fit_f16, x.h, batch, _shape4(output_shape))
+
+    def shortcut_add_act_f16(self, a, b, activation):
+        return self._out(self.lib.ln_shortcut_add_act_f16, a.h, b.h, _act(activation))
+
+    def channel_affine_act_f16(self, x, scale, bias, channels, channel_stride, activation):
+        return self._out(self.lib.ln_channel_affine_act_f16, x.h, scale.h if scale is not None else None, bias.h, channels, channel_stride, _act(activation))
 
     # ---- 8-bit twins (int8 / FP8 E4M3) ---------------------------------------------------------
     def upload_q(self, shape, host, scale, dtype=LN_Q8):
@@ -465,11 +533,11 @@ class GpuExecutableNetwork:
             self.h = None
 
     def layer_info(self, i):
-        v = np.zeros(16, np.int32)
+        v = np.zeros(20, np.int32)
         if self.lib.ln_net_layer_info(self.h, i, _ptr(v)):
             raise IndexError(i)
         keys = ["kind", "in_w", "in_h", "in_c", "in_b", "out_w", "out_h", "out_c", "out_b", "filters", "size", "stride_x", "stride_y",
-                "padding", "bn", "act"]
+                "padding", "bn", "act", "groups", "dilation"]
         d = dict(zip(keys, (int(x) for x in v)))
         d["kind"] = self.KINDS[d["kind"]]
         return d

@@ -56,7 +56,7 @@ struct ln_tensor {
     void* base = nullptr;                // pool block (nullptr for a view onto `parent`)
     size_t bytes = 0;
     ln_tensor* parent = nullptr;         // keeps the owner of a view alive
-    int64_t cstride = 0;                 // 8-bit NHWC tensors: bytes between consecutive pixels
+    int64_t cstride = 0;                 // 8-bit and binary16 NHWC tensors: bytes between consecutive pixels
     float scale = 1.0f;                  // 8-bit tensors: value = code * scale
     int64_t count() const { return n * c * h * w; }
 };
@@ -71,6 +71,9 @@ struct ln_conv_weights {
     std::vector<float> h_wscale;    // host copy
     float max_l1 = 0.0f;            // max over filters of the sum of |code| (bounds the int8 accumulators)
     void* w_oihw = nullptr;         // [filters][channels][k][k] codes in the reference's weight order (SIMT path)
+    // binary16 weights (dtype LN_F16): the f32 source is kept and packed by the first convolution that names kernel size and channels
+    ln_tensor* src_f32 = nullptr;
+    int64_t per_filter = 0;
 };
 
 int ln_fail(ln_ctx* ctx, int code, const char* fmt, ...);

@@ -4,7 +4,9 @@
 
 #include "ln_common.h"
 
-enum { LN_KIND_I8 = 0, LN_KIND_F8 = 1 };
+// operand type of the tensor-core convolution: int8 (int32 accumulate), FP8 E4M3 or binary16 (f32 accumulate).  The kernel and its
+// planner count channels in BYTES per pixel (cpad, x_pixel_stride); binary16 callers pass two bytes per channel.
+enum { LN_KIND_I8 = 0, LN_KIND_F8 = 1, LN_KIND_F16 = 2 };
 
 // status word values written by kernels whose bounded waits gave up
 enum {
@@ -36,6 +38,7 @@ struct ln_conv_umma_params {
     const float2* mb_folded;
     float sy_log2e;  // output scale * log2(e): exponent argument per code unit (folded fast epilogue)
     int tab_bytes;   // bytes of the {multiplier, bias} table the epilogue warps copy to shared memory (all filter tiles)
+    int out_esize;   // bytes per element of an LN_OUT_Q output (1, or 2 for binary16)
     void* out;
     long long out_pixel_stride;  // bytes between pixels of an 8-bit NHWC output
     // fused shortcut (null = none): out = quant((code * s_c + residual_code * s_res) * inv_sy2), code = the convolution's own int8 output
@@ -74,6 +77,9 @@ struct ln_conv_geom {
     int N = 0, H = 0, W = 0, C = 0, cpad = 0;
     const void* w = nullptr;      // [fpad][k][k][cpad]
     int F = 0, fpad = 0, k = 1, stride = 1, pad = 0;
+    // grouped convolution (CUDA-core kernels only): filter f reads the C / groups channels of group f / (F / groups); the weights
+    // are [fpad][k][k][w_cpad] with C / groups real channels per row (w_cpad = 0 means cpad, the ungrouped layout)
+    int groups = 1, w_cpad = 0;
     int OH = 0, OW = 0;
     int act = 0, out_kind = 0;
     float inv_sy = 1.0f;

@@ -111,10 +111,16 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
             "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
             : "memory");
-    } else {
+    } else if (KIND == LN_KIND_F8) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
             : "memory");
     }
@@ -132,24 +138,9 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
 }
-// the same for 16 columns
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
 // n / d for n * d < 2^40 with the precomputed multiplier ceil(2^40 / d): one wide multiply and a shift
 __device__ __forceinline__ int fast_div(int n, unsigned long long magic) { return (int)(((unsigned long long)(unsigned)n * magic) >> 40); }
 
-// 16-byte read-only load that the compiler may not sink into the arithmetic that uses it
-__device__ __forceinline__ float4 ldg_f4_pinned(const float4* p) {
-    float4 v;
-    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-}
 // 16-byte read from shared memory (the table it reads is written once, before the epilogue warps' barrier)
 __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
     float4 v;
@@ -157,14 +148,6 @@ __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
     return v;
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// the same, naming the 16 registers an earlier load fills, so that no use of them can be scheduled before the wait
-__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
-                   "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-                 :
-                 : "memory");
-}
 
 
 // int32 -> f32 (round to nearest even) on the FMA/ALU pipes only: the conversion unit shares its issue port with
@@ -345,6 +328,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
+            // instruction descriptor: accumulator type (bits 4-5: 1 = f32, 2 = s32), A and B types (bits 7-9, 10-12: 0 = E4M3 / binary16
+            // depending on the kind, 1 = signed 8-bit), N / 8 and M / 16; both operands K-major
             const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((uint32_t)(bn >> 3) << 17) |
                                    ((128u >> 4) << 24);
             int stage = 0, astage = 0;
@@ -460,71 +445,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * bn);
             const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
-            if (folded) {
-                // Fast mode, int8 out, accumulators below 2^22, filters a multiple of 32 (every chunk is full).  The accumulators
-                // come 16 columns at a time into two register sets: while one set is turned into codes the load of the next is
-                // in flight, so the TMEM latency is paid once per tile, not once per chunk.
-                // Adding an accumulator to the bits of 1.5 * 2^23 gives the float 1.5 * 2^23 + accumulator; the table holds
-                // {mult 2i, mult 2i+1, bias 2i, bias 2i+1} divided by the output scale, the bias carrying -1.5 * 2^23 * mult, so
-                // one packed FMA yields two pre-activations in code units; activation and rounding run in packed binary16.
-                const __half2 kh = __float2half2_rn(p.sy_log2e), inv_h = __float2half2_rn(p.inv_sy);
-                uint32_t a0[16], a1[16];
-                auto codes16 = [&](const uint32_t (&a)[16], uint32_t mt, uint32_t (&out)[4]) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float4 ma = lds_f4(mt + 32u * j), mc = lds_f4(mt + 32u * j + 16u);
-                        float t0, t1, t2, t3;
-                        ffma2(t0, t1, __int_as_float(0x4B400000 + (int)a[4 * j]), __int_as_float(0x4B400000 + (int)a[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
-                        ffma2(t2, t3, __int_as_float(0x4B400000 + (int)a[4 * j + 2]), __int_as_float(0x4B400000 + (int)a[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
-                        out[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
-                    }
-                };
-                tmem_ld_32x16(taddr0 + (uint32_t)c_begin, a0);
-                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-                    int64_t opix = pix;
-                    int fo = f0 + c0;
-                    if (p.pack > 1) {
-                        int j = 0;
-                        while (fo >= p.f_real) { fo -= p.f_real; ++j; }
-                        opix = pix * p.pack + j;
-                    }
-                    uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
-                    if (p.res != nullptr && valid) {  // residual codes of the fused shortcut
-                        const uint4* rp = (const uint4*)((const uint8_t*)p.res + opix * p.res_pixel_stride + fo);
-                        r0 = __ldg(rp);
-                        r1 = __ldg(rp + 1);
-                    }
-                    const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);
-                    uint32_t lo[4], hi[4];
-                    tmem_ld_wait16(a0);
-                    tmem_ld_32x16(taddr0 + (uint32_t)c0 + 16u, a1);
-                    codes16(a0, mtab, lo);
-                    tmem_ld_wait16(a1);
-                    if (c0 + 32 < c_end) tmem_ld_32x16(taddr0 + (uint32_t)c0 + 32u, a0);
-                    codes16(a1, mtab + 128u, hi);
-                    uint32_t packed[8] = {lo[0], lo[1], lo[2], lo[3], hi[0], hi[1], hi[2], hi[3]};
-                    if (p.res != nullptr) {
-                        // fused shortcut, the arithmetic of the stand-alone shortcut kernel applied to the codes just produced
-                        const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            uint32_t u[4];
-#pragma unroll
-                            for (int b = 0; b < 4; ++b) {
-                                float v = __fmul_rn(s8_to_float(packed[j], b), p.s_c);
-                                v = __fmaf_rn(s8_to_float(rw[j], b), p.s_res, v);
-                                u[b] = quant_i8_magic(v, p.inv_sy2);
-                            }
-                            packed[j] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
-                        }
-                    }
-                    if (valid) {
-                        uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
-                        o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    }
-                }
-            } else
             for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                 uint32_t acc[32];
                 const long long tq0 = kRoleTiming && p.debug ? clock64() : 0;
@@ -556,7 +476,21 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     uint32_t packed[8];
                     // Four values at a time, each loop body fetching its own two table entries from shared memory, so that few
                     // values are live at once (the kernel has to fit in 96 registers).
-                    {
+                    if (folded) {
+                        // Fast mode, accumulators below 2^22.  Adding an accumulator to the bits of 1.5 * 2^23 gives the float
+                        // 1.5 * 2^23 + accumulator; the table holds {mult 2i, mult 2i+1, bias 2i, bias 2i+1} divided by the output scale,
+                        // the bias carrying -1.5 * 2^23 * mult, so one packed FMA yields two pre-activations in code units;
+                        // activation and rounding run in packed binary16.
+                        const __half2 kh = __float2half2_rn(p.sy_log2e), inv_h = __float2half2_rn(p.inv_sy);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
+                            float t0, t1, t2, t3;
+                            ffma2(t0, t1, __int_as_float(0x4B400000 + (int)acc[4 * j]), __int_as_float(0x4B400000 + (int)acc[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
+                            ffma2(t2, t3, __int_as_float(0x4B400000 + (int)acc[4 * j + 2]), __int_as_float(0x4B400000 + (int)acc[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
+                            packed[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
+                        }
+                    } else {
                         // int32 -> f32: below 2^22 through the bits of 1.5 * 2^23 (two FMA-pipe instructions, exact); otherwise the
                         // conversion unit, or, for the transcendental epilogues that need that unit for ex2 / rcp, an exact ALU sequence
                         const bool small = p.small_acc != 0;
@@ -631,6 +565,19 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
                     for (int j = 0; j < 32; ++j, o += plane)
                         if (j < nf) *o = a[j];
                 } else {
+                    if (KIND == LN_KIND_F16) {
+                        // binary16 NHWC: 32 filters = 64 bytes per pixel, rounded to nearest even, infinities kept
+                        uint32_t hw[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const __half2 h = __floats2half2_rn(2 * j < nf ? a[2 * j] : 0.0f, 2 * j + 1 < nf ? a[2 * j + 1] : 0.0f);
+                            hw[j] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + 2 * fo);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) o[j] = make_uint4(hw[4 * j], hw[4 * j + 1], hw[4 * j + 2], hw[4 * j + 3]);
+                        continue;
+                    }
                     uint32_t packed[8];
                     if (KIND == LN_KIND_I8) {
 #pragma unroll
@@ -682,6 +629,55 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+// Tensor-pipe peak probe: one CTA per SM, one thread issuing tcgen05.mma (M = 128, N = 256, 32 bytes of K per instruction)
+// back to back on operand tiles that stay in shared memory, no loads, no epilogue.  What it measures is the rate the tensor
+// cores sustain when nothing else limits them: the denominator of the convolution's roofline.
+template <int KIND>
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_base = base, b_base = base + 128u * 128u, bar = b_base + 256u * 128u;
+    uint8_t* g = smem_raw + (base - smem_u32(smem_raw));
+    for (int i = threadIdx.x; i < (128 + 256) * 128 / 16; i += blockDim.x) reinterpret_cast<uint4*>(g)[i] = make_uint4(0u, 0u, 0u, 0u);
+    volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(g + (128 + 256) * 128 + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(g + (128 + 256) * 128 + 32);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zeroed tiles are read through the async proxy
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *slot;
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+        const uint64_t a_desc = make_smem_desc(a_base, 128), b_desc = make_smem_desc(b_base, 128);
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int it = 0; ok && it < iters; ++it) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) tc_mma<KIND>(tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((it | k) != 0));
+            if ((it & 63) == 63 || it + 1 == iters) {  // keep the queue bounded: wait for every 256th instruction
+                tc_commit(bar);
+                ok = mbar_wait(bar, phase, abort_flag, status, LN_STATUS_MMA_TIMEOUT);
+                phase ^= 1u;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
     }
 }
 
@@ -956,6 +952,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.magic_f = magic(p.tiles_f); p.magic_w = magic(p.tiles_w); p.magic_h = magic(p.tiles_h);
     if ((long long)p.num_tiles * p.num_tiles >= (1ll << 40)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d tiles", p.num_tiles);
     p.act = g.act; p.inv_sy = g.inv_sy; p.out_kind = g.out_kind;
+    p.out_esize = g.kind == LN_KIND_F16 ? 2 : 1;
     p.out = g.out; p.out_pixel_stride = g.out_pixel_stride;
     p.res = g.res; p.res_pixel_stride = g.res_pixel_stride; p.s_c = g.s_c; p.s_res = g.s_res; p.inv_sy2 = g.inv_sy2;
     if (g.res && (g.out_kind != LN_OUT_Q || g.kind != LN_KIND_I8 || g.F % 32 != 0 || (((uintptr_t)g.res) & 15) || (g.res_pixel_stride & 15)))
@@ -1047,12 +1044,49 @@ int ln_conv_umma_make_mb(ln_ctx* ctx, const float* wscale_dev, const float* bias
     return LN_OK;
 }
 
+extern "C" int32_t ln_debug_mma_peak(ln_ctx* ctx, int32_t dtype, int32_t iters, float* tops) {
+    if (!ctx || !tops || iters < 1 || iters > (1 << 20)) return ln_fail(ctx, LN_ERR_ARG, "ln_debug_mma_peak: bad argument");
+    if (dtype != LN_Q8 && dtype != LN_F8 && dtype != LN_F16) return ln_fail(ctx, LN_ERR_ARG, "ln_debug_mma_peak: dtype must be LN_Q8, LN_F8 or LN_F16");
+    cudaSetDevice(ctx->device);
+    const size_t smem = (128 + 256) * 128 + 1024 + 64;
+    auto launch = [&](int n) {
+        if (dtype == LN_Q8) mma_peak_kernel<LN_KIND_I8><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, ctx->d_status);
+        else if (dtype == LN_F8) mma_peak_kernel<LN_KIND_F8><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, ctx->d_status);
+        else mma_peak_kernel<LN_KIND_F16><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, ctx->d_status);
+        ctx->launches++;
+    };
+    LN_CUDA(ctx, cudaFuncSetAttribute(mma_peak_kernel<LN_KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LN_CUDA(ctx, cudaFuncSetAttribute(mma_peak_kernel<LN_KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LN_CUDA(ctx, cudaFuncSetAttribute(mma_peak_kernel<LN_KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaEvent_t e0, e1;
+    LN_CUDA(ctx, cudaEventCreate(&e0));
+    LN_CUDA(ctx, cudaEventCreate(&e1));
+    launch(iters < 64 ? iters : 64);  // warm-up
+    cudaEventRecord(e0, ctx->stream);
+    launch(iters);
+    cudaEventRecord(e1, ctx->stream);
+    cudaError_t e = cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "ln_debug_mma_peak: %s", cudaGetErrorString(e));
+    int rc = ln_check_status(ctx, "ln_debug_mma_peak");
+    if (rc) return rc;
+    // one instruction is 128 x 256 x (32 bytes of K) multiply-adds: 32 per row pair for the 8-bit types, 16 for binary16
+    const double k_elems = dtype == LN_F16 ? 16.0 : 32.0;
+    *tops = (float)(2.0 * 128.0 * 256.0 * k_elems * 4.0 * (double)iters * ctx->sm_count / (ms * 1e-3) / 1e12);
+    return LN_OK;
+}
+
 int ln_conv_umma_launch(ln_ctx* ctx, const ln_conv_umma_plan* plan) {
     cudaError_t e;
     const bool exact = ctx->exact_epilogue;
     if (plan->kind == LN_KIND_I8)
         e = exact ? launch_act<LN_KIND_I8, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
                   : launch_act<LN_KIND_I8, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
+    else if (plan->kind == LN_KIND_F16)  // activations with the hardware ex2 / rcp (2 ulp of binary32, far below one binary16 rounding)
+        e = launch_act<LN_KIND_F16, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
     else
         e = exact ? launch_act<LN_KIND_F8, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
                   : launch_act<LN_KIND_F8, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);

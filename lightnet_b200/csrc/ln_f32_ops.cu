@@ -81,6 +81,12 @@ __global__ void bias_act_f32_kernel(const float* __restrict__ x, const float* __
     }
 }
 
+__global__ void channel_scale_f32_kernel(const float* __restrict__ x, const float* __restrict__ scale, float* __restrict__ y, int64_t n, int64_t channels,
+                                         int64_t channel_stride) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = __fmul_rn(x[i], scale[(i / channel_stride) % channels]);
+}
+
 __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y, int64_t n) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) y[i] = a[i] + b[i];
 }
@@ -246,6 +252,22 @@ int32_t ln_bias_activation_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor*
                                int32_t activation, ln_tensor** out) {
     if (!bias) return ln_fail(ctx, LN_ERR_ARG, "ln_bias_activation_f32: bias is NULL");
     return bias_act_impl(ctx, x, bias, channels, channel_stride, activation, out, "ln_bias_activation_f32");
+}
+
+int32_t ln_channel_scale_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* scale, int64_t channels, int64_t channel_stride, ln_tensor** out) {
+    if (!ctx || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_channel_scale_f32: NULL argument");
+    if (!is_f32(x) || !is_f32(scale)) return ln_fail(ctx, LN_ERR_ARG, "ln_channel_scale_f32: f32 tensors required");
+    if (channels < 1 || channel_stride < 1 || scale->count() != channels)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_channel_scale_f32: scale has %lld elements for %lld channels", (long long)scale->count(), (long long)channels);
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, LN_F32, x->n, x->c, x->h, x->w);
+    if (!y) return LN_ERR_CUDA;
+    channel_scale_f32_kernel<<<grid_for(ctx, x->count()), kThreads, 0, ctx->stream>>>((const float*)x->ptr, (const float*)scale->ptr, (float*)y->ptr, x->count(), channels, channel_stride);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ln_tensor_release(y); return ln_fail(ctx, LN_ERR_CUDA, "channel_scale launch: %s", cudaGetErrorString(e)); }
+    *out = y;
+    return LN_OK;
 }
 
 int32_t ln_shortcut_add_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* y, ln_tensor** out) {

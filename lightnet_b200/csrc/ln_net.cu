@@ -494,6 +494,88 @@ int forward_f32(ln_net* net, const ln_tensor* input, unsigned* amax_dev) {
     return LN_OK;
 }
 
+// ---- binary16 forward: the operator sequence of forward_compact_f16 (gpu_f16.rs:21-957) over the F16 twin ------------------
+// Every convolution, the ones in front of the heads included, runs conv2d_bias_act_f16 on cached conv_weights_f16
+// (gpu_f16.rs:164-224); shortcuts fit mismatched sources and add them one by one, the layer's activation going to the last
+// add (:440-490); a [yolo] layer hands the previous output on, widened to f32 as download_f16 does for the decoder (:898-925).
+int forward_f16(ln_net* net, const ln_tensor* input) {
+    ln_ctx* ctx = net->ctx;
+    release_outputs(net);
+    release_heads(net);
+    const int NL = (int)net->layers.size();
+    net->out.assign(NL, nullptr);
+    ln_tensor* in16 = nullptr;
+    int rc = ln_tensor_narrow_f16(ctx, input, &in16);  // upload_f16: the f32 input rounded to binary16 on the device
+    if (rc) return rc;
+    for (int i = 0; i < NL && rc == LN_OK; ++i) {
+        NLayer& L = net->layers[i];
+        const ln_tensor* x = i == 0 ? in16 : net->out[i - 1];
+        const int64_t oshape[4] = {L.out.b, L.out.c, L.out.h, L.out.w};
+        ln_tensor* y = nullptr;
+        switch (L.kind) {
+            case K_CONV:
+                rc = ln_conv2d_bias_act_f16(ctx, x, L.wq, L.b_f32, oshape, L.in.c, L.in.h, L.in.w, L.filters, L.size, L.stride_x, L.stride_y, L.dilation, L.padding,
+                                            L.groups, L.act, &y);
+                break;
+            case K_MAXPOOL:
+                rc = ln_maxpool_f16(ctx, x, oshape, L.in.c, L.in.h, L.in.w, L.size, L.stride_x, L.stride_y, L.padding, &y);
+                break;
+            case K_ROUTE: {
+                std::vector<const ln_tensor*> ins;
+                std::vector<int64_t> offs, chans, totals;
+                for (int src : L.sources) {
+                    const ln_tensor* t = net->out[src];
+                    const int64_t chunk = t->c / L.route_groups;
+                    ins.push_back(t);
+                    offs.push_back(chunk * L.route_group_id);
+                    chans.push_back(chunk);
+                    totals.push_back(t->c);
+                }
+                rc = ln_route_concat_f16(ctx, ins.data(), (int)ins.size(), offs.data(), chans.data(), totals.data(), oshape, (int64_t)L.out.h * L.out.w, &y);
+                break;
+            }
+            case K_SHORTCUT: {
+                ln_tensor* acc = const_cast<ln_tensor*>(x);
+                ln_tensor_retain(acc);
+                for (size_t k = 0; k < L.sources.size() && rc == LN_OK; ++k) {
+                    const ln_tensor* s = net->out[L.sources[k]];
+                    ln_tensor* fitted = nullptr;
+                    if (s->n != acc->n) { rc = ln_fail(ctx, LN_ERR_SHAPE, "shortcut layer #%d mixes incompatible batch shapes", i); break; }
+                    if (s->c != acc->c || s->h != acc->h || s->w != acc->w) {
+                        rc = ln_shortcut_fit_f16(ctx, s, L.out.b, oshape, &fitted);
+                        if (rc) break;
+                        s = fitted;
+                    }
+                    ln_tensor* sum = nullptr;
+                    rc = ln_shortcut_add_act_f16(ctx, acc, s, k + 1 == L.sources.size() ? L.act : LN_ACT_LINEAR, &sum);
+                    ln_tensor_release(fitted);
+                    if (rc) break;
+                    ln_tensor_release(acc);
+                    acc = sum;
+                }
+                if (rc == LN_OK) y = acc;
+                else ln_tensor_release(acc);
+                break;
+            }
+            case K_UPSAMPLE:
+                rc = ln_upsample_f16(ctx, x, oshape, L.in.c, L.in.h, L.in.w, L.up_stride, L.up_scale, L.up_reverse ? 1 : 0, &y);
+                break;
+            case K_YOLO: {
+                y = const_cast<ln_tensor*>(x);
+                ln_tensor_retain(y);
+                ln_tensor* head = nullptr;
+                rc = ln_tensor_widen_f16(ctx, x, &head);
+                if (rc == LN_OK) net->heads.push_back(head);
+                break;
+            }
+        }
+        if (rc == LN_OK) net->out[i] = y;
+        else ln_tensor_release(y);
+    }
+    ln_tensor_release(in16);
+    return rc;
+}
+
 // ---- per-tensor scales from the calibration amax (tensors joined by route / maxpool / upsample share one)
 void scales_from_amax(ln_net* net, const std::vector<float>& amax, float qmax) {
     const int T = (int)net->layers.size() + 1;
@@ -526,8 +608,9 @@ int build_plan(ln_net* net, int mb) {
     // 1. support checks
     for (int i = 0; i < NL; ++i) {
         const NLayer& L = net->layers[i];
-        if (L.kind == K_CONV && (L.groups != 1 || L.dilation != 1 || L.stride_x != L.stride_y))
-            return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit convolution needs groups=1, dilation=1, stride_x=stride_y", i);
+        if (L.kind == K_CONV && (L.dilation != 1 || L.stride_x != L.stride_y))
+            return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit convolution needs dilation=1, stride_x=stride_y", i);
+        if (L.kind == K_CONV && L.groups != 1 && i == 0) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #0: the first layer cannot be a grouped convolution in the 8-bit plan");
         if (L.kind == K_UPSAMPLE && (L.up_reverse || L.up_scale != 1.0f)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit up-sample needs scale=1, forward", i);
         if (L.kind == K_SHORTCUT) {
             if (L.sources.size() != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit shortcut takes exactly one source", i);
@@ -714,7 +797,9 @@ int build_plan(ln_net* net, int mb) {
                 } else {
                     g.x = net->views[i - 1].ptr; g.x_pixel_stride = net->views[i - 1].cstride;
                 }
-                if (g.x_pixel_stride >= g.cpad && g.F <= 4096 && ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H)) {
+                g.groups = L.groups;
+                if (L.groups > 1) { g.cpad = (int)ln_round_up(L.in.c, 32); g.w_cpad = (int)L.wq->cpad; }  // grouped / depthwise: CUDA-core kernels
+                if (L.groups == 1 && g.x_pixel_stride >= g.cpad && g.F <= 4096 && ln_conv_umma_supported(g.cpad, g.k, g.stride, g.stride, 1, 1, g.W, g.H)) {
                     st.op = 0;
                     st.umma.mb = st.mb;
                     rc = ln_conv_umma_plan_build(ctx, &st.umma, g);
@@ -879,6 +964,7 @@ int forward_any(ln_net* net, const ln_tensor* input) {
     LN_CUDA(ctx, cudaEventRecord(net->ev[0], ctx->stream));
     int rc;
     if (net->precision == LN_F32) rc = forward_f32(net, input, nullptr);
+    else if (net->precision == LN_F16) rc = forward_f16(net, input);
     else {
         int mb = net->micro_batch > 0 && net->micro_batch < net->batch ? net->micro_batch : net->batch;
         if (net->batch % mb != 0) return ln_fail(ctx, LN_ERR_ARG, "micro batch %d does not divide batch %d", mb, net->batch);
@@ -1020,7 +1106,8 @@ extern "C" {
 
 int32_t ln_net_create(ln_ctx* ctx, const char* cfg_text, int32_t batch, int32_t precision, ln_net** out) {
     if (!ctx || !cfg_text || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_net_create: NULL argument");
-    if (precision != LN_F32 && precision != LN_Q8 && precision != LN_F8) return ln_fail(ctx, LN_ERR_ARG, "ln_net_create: precision must be LN_F32, LN_Q8 or LN_F8");
+    if (precision != LN_F32 && precision != LN_F16 && precision != LN_Q8 && precision != LN_F8)
+        return ln_fail(ctx, LN_ERR_ARG, "ln_net_create: precision must be LN_F32, LN_F16, LN_Q8 or LN_F8");
     std::unique_ptr<ln_net> net(new ln_net());
     net->ctx = ctx;
     net->precision = precision;
@@ -1064,10 +1151,11 @@ int32_t ln_net_destroy(ln_net* net) {
 
 int32_t ln_net_num_layers(const ln_net* net) { return net ? (int)net->layers.size() : 0; }
 
-int32_t ln_net_layer_info(const ln_net* net, int32_t layer, int32_t info[16]) {
+int32_t ln_net_layer_info(const ln_net* net, int32_t layer, int32_t info[20]) {
     if (!net || !info || layer < 0 || layer >= (int)net->layers.size()) return LN_ERR_ARG;
     const NLayer& L = net->layers[layer];
-    int v[16] = {L.kind, L.in.w, L.in.h, L.in.c, L.in.b, L.out.w, L.out.h, L.out.c, L.out.b, L.filters, L.size, L.stride_x, L.stride_y, L.padding, L.bn ? 1 : 0, L.act};
+    int v[20] = {L.kind, L.in.w, L.in.h, L.in.c, L.in.b, L.out.w, L.out.h, L.out.c, L.out.b, L.filters, L.size, L.stride_x, L.stride_y, L.padding, L.bn ? 1 : 0, L.act,
+                 L.groups, L.dilation, 0, 0};
     memcpy(info, v, sizeof v);
     return LN_OK;
 }
@@ -1112,9 +1200,10 @@ int32_t ln_net_load_weights(ln_net* net, const float* blob, int64_t count) {
         int rc = ln_tensor_upload_f32(ctx, wshape, fw.data(), &L.w_f32);
         if (rc == LN_OK) rc = ln_tensor_upload_f32(ctx, bshape, fb.data(), &L.b_f32);
         if (rc == LN_OK) rc = ln_sync(ctx);  // the host vectors die at the end of this scope
-        if (rc == LN_OK && net->precision != LN_F32) {
-            if (L.groups != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "8-bit convolution needs groups=1");
-            rc = ln_conv_weights_q(ctx, L.w_f32, L.filters, L.in.c, L.size, net->precision, &L.wq);
+        if (rc == LN_OK && net->precision == LN_F16)
+            rc = ln_conv_weights_f16(ctx, L.w_f32, L.filters, (int64_t)(L.in.c / L.groups) * L.size * L.size, &L.wq);
+        else if (rc == LN_OK && net->precision != LN_F32) {
+            rc = ln_conv_weights_q(ctx, L.w_f32, L.filters, L.in.c / L.groups, L.size, net->precision, &L.wq);  // [filters][C / groups][k][k]
         }
         if (rc) return rc;
     }
@@ -1214,7 +1303,7 @@ int32_t ln_net_head(ln_net* net, int32_t head_index, ln_tensor** out) {
 int32_t ln_net_layer_output(ln_net* net, int32_t layer, ln_tensor** out) {
     if (!net || !out || layer < 0 || layer >= (int)net->layers.size()) return LN_ERR_ARG;
     ln_ctx* ctx = net->ctx;
-    if (net->precision == LN_F32) {
+    if (net->precision == LN_F32 || net->precision == LN_F16) {
         if ((int)net->out.size() <= layer || !net->out[layer]) return ln_fail(ctx, LN_ERR_ARG, "layer %d has no output (run a forward first)", layer);
         ln_tensor_retain(net->out[layer]);
         *out = net->out[layer];
@@ -1265,7 +1354,7 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
                       ln_detection* records_host, int32_t* counts_host) {
     if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_detect: NULL argument");
     ln_ctx* ctx = net->ctx;
-    if (net->precision != LN_F32 && net->host_pipeline && net->batch >= 8 && net->batch % 2 == 0 && net->weights_loaded && net->scales_set &&
+    if ((net->precision == LN_Q8 || net->precision == LN_F8) && net->host_pipeline && net->batch >= 8 && net->batch % 2 == 0 && net->weights_loaded && net->scales_set &&
         image_w && image_h && opts && records_host && counts_host && opts->max_per_image >= 1) {
         int rc = ensure_pipe(net);
         if (rc) return rc;

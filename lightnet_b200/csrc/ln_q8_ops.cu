@@ -300,21 +300,32 @@ __global__ void conv_simt_kernel(ln_conv_geom g, const float2* __restrict__ mb) 
         int64_t n = pix / ((int64_t)g.OW * g.OH);
         int iacc = 0;
         float facc = 0.0f;
+        // a group's channels: all of them (padded, where the pad bytes of both operands are zero) when there is one group
+        const int w_cpad = g.w_cpad ? g.w_cpad : g.cpad;
+        const int cpg = g.groups > 1 ? g.C / g.groups : g.cpad, cbase = g.groups > 1 ? (f / (g.F / g.groups)) * cpg : 0;
+        const bool words = (cpg & 3) == 0 && (cbase & 3) == 0;
         for (int ky = 0; ky < g.k; ++ky) {
             int iy = oy * g.stride + ky - g.pad;
             if (iy < 0 || iy >= g.H) continue;
             for (int kx = 0; kx < g.k; ++kx) {
                 int ix = ox * g.stride + kx - g.pad;
                 if (ix < 0 || ix >= g.W) continue;
-                const uint8_t* xp = x + ((n * g.H + iy) * g.W + ix) * g.x_pixel_stride;
-                const uint8_t* wp = w + (((int64_t)f * g.k + ky) * g.k + kx) * g.cpad;
-                for (int c = 0; c < g.cpad; c += 4) {
-                    uint32_t xv = *reinterpret_cast<const uint32_t*>(xp + c), wv = *reinterpret_cast<const uint32_t*>(wp + c);
-                    if (KIND == LN_KIND_I8) iacc = __dp4a((int)xv, (int)wv, iacc);
-                    else {
+                const uint8_t* xp = x + ((n * g.H + iy) * g.W + ix) * g.x_pixel_stride + cbase;
+                const uint8_t* wp = w + (((int64_t)f * g.k + ky) * g.k + kx) * w_cpad;
+                if (words) {
+                    for (int c = 0; c < cpg; c += 4) {
+                        uint32_t xv = *reinterpret_cast<const uint32_t*>(xp + c), wv = *reinterpret_cast<const uint32_t*>(wp + c);
+                        if (KIND == LN_KIND_I8) iacc = __dp4a((int)xv, (int)wv, iacc);
+                        else {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            facc = fmaf(e4m3_to_float((uint8_t)(xv >> (8 * j))), e4m3_to_float((uint8_t)(wv >> (8 * j))), facc);
+                            for (int j = 0; j < 4; ++j)
+                                facc = fmaf(e4m3_to_float((uint8_t)(xv >> (8 * j))), e4m3_to_float((uint8_t)(wv >> (8 * j))), facc);
+                        }
+                    }
+                } else {
+                    for (int c = 0; c < cpg; ++c) {
+                        if (KIND == LN_KIND_I8) iacc += (int)(int8_t)xp[c] * (int)(int8_t)wp[c];
+                        else facc = fmaf(e4m3_to_float(xp[c]), e4m3_to_float(wp[c]), facc);
                     }
                 }
             }
@@ -328,6 +339,66 @@ __global__ void conv_simt_kernel(ln_conv_geom g, const float2* __restrict__ mb) 
         float a = ln_epilogue_act<EXACT>(g.act, __fmaf_rn(KIND == LN_KIND_I8 ? __int2float_rn(iacc) : facc, m.x, m.y));
         if (g.out_kind == LN_OUT_F32) ((float*)g.out)[(((int64_t)n * g.F + f) * g.OH + oy) * g.OW + ox] = a;
         else ((uint8_t*)g.out)[pix * g.out_pixel_stride + f] = quantize_code<KIND>(a, g.inv_sy);
+    }
+}
+
+// Depthwise convolution (groups = channels = filters; lightnet-cuda-oxide/src/kernels/conv_direct.rs:19 with one channel per
+// group): HBM-bound byte work.  One thread per (output pixel, 16 channels): every tap is one 16-byte load of the input and one
+// 16-byte load of the weights, which are staged in shared memory tap-major ([k*k][C]) once per block; the 16 outputs leave as
+// one 16-byte store.
+template <int KIND, bool EXACT>
+__global__ void __launch_bounds__(256) conv_dw_q_kernel(ln_conv_geom g, const float2* __restrict__ mb) {
+    extern __shared__ uint8_t s_dw[];  // [k*k][C16*16]
+    const int kk = g.k * g.k, C16 = (g.C + 15) / 16, w_cpad = g.w_cpad ? g.w_cpad : g.cpad;
+    const uint8_t* w = (const uint8_t*)g.w;
+    for (int i = threadIdx.x; i < kk * C16 * 16; i += blockDim.x) {
+        const int tap = i / (C16 * 16), c = i - tap * (C16 * 16);
+        s_dw[i] = c < g.C ? w[((int64_t)c * kk + tap) * w_cpad] : 0;
+    }
+    __syncthreads();
+    const uint8_t* x = (const uint8_t*)g.x;
+    const int64_t total = (int64_t)g.N * g.OH * g.OW * C16;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % C16);
+        const int64_t pix = i / C16;
+        const int ox = (int)(pix % g.OW), oy = (int)((pix / g.OW) % g.OH);
+        const int64_t n = pix / ((int64_t)g.OW * g.OH);
+        int iacc[16];
+        float facc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { iacc[j] = 0; facc[j] = 0.0f; }
+        for (int ky = 0; ky < g.k; ++ky) {
+            const int iy = oy * g.stride + ky - g.pad;
+            if (iy < 0 || iy >= g.H) continue;
+            for (int kx = 0; kx < g.k; ++kx) {
+                const int ix = ox * g.stride + kx - g.pad;
+                if (ix < 0 || ix >= g.W) continue;
+                const uint4 xv = *reinterpret_cast<const uint4*>(x + ((n * g.H + iy) * g.W + ix) * g.x_pixel_stride + cg * 16);
+                const uint4 wv = *reinterpret_cast<const uint4*>(s_dw + (ky * g.k + kx) * C16 * 16 + cg * 16);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint8_t xb = (uint8_t)(xw[j >> 2] >> (8 * (j & 3))), wb = (uint8_t)(ww[j >> 2] >> (8 * (j & 3)));
+                    if (KIND == LN_KIND_I8) iacc[j] += (int)(int8_t)xb * (int)(int8_t)wb;
+                    else facc[j] = fmaf(e4m3_to_float(xb), e4m3_to_float(wb), facc[j]);
+                }
+            }
+        }
+        uint32_t packed[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int f = cg * 16 + j;
+            if (f >= g.F) continue;
+            if (g.out_kind == LN_OUT_ACC) {
+                ((int32_t*)g.out)[(((int64_t)n * g.F + f) * g.OH + oy) * g.OW + ox] = KIND == LN_KIND_I8 ? iacc[j] : __float_as_int(facc[j]);
+                continue;
+            }
+            const float2 m = mb[f];
+            const float a = ln_epilogue_act<EXACT>(g.act, __fmaf_rn(KIND == LN_KIND_I8 ? __int2float_rn(iacc[j]) : facc[j], m.x, m.y));
+            if (g.out_kind == LN_OUT_F32) ((float*)g.out)[(((int64_t)n * g.F + f) * g.OH + oy) * g.OW + ox] = a;
+            else packed[j >> 2] |= (uint32_t)quantize_code<KIND>(a, g.inv_sy) << (8 * (j & 3));
+        }
+        if (g.out_kind == LN_OUT_Q) *reinterpret_cast<uint4*>((uint8_t*)g.out + pix * g.out_pixel_stride + cg * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
 }
 
@@ -641,8 +712,23 @@ int ln_check_status(ln_ctx* ctx, const char* where) {
 int ln_conv_simt_launch(ln_ctx* ctx, const ln_conv_geom& g, const void* w_unused, const float2* mb) {
     (void)w_unused;
     const int64_t total = (int64_t)g.N * g.OH * g.OW * g.F;
-    const int grid = grid_for(ctx, total);
     const bool exact = ctx->exact_epilogue;
+    // depthwise: the vectorised kernel (16 channels per thread, weights tap-major in shared memory)
+    const size_t dw_smem = (size_t)g.k * g.k * ((g.C + 15) / 16) * 16;
+    if (g.groups > 1 && g.groups == g.C && g.F == g.C && dw_smem <= 48 * 1024 && (g.x_pixel_stride & 15) == 0 && (((uintptr_t)g.x) & 15) == 0 &&
+        (g.out_kind != LN_OUT_Q || ((g.out_pixel_stride & 15) == 0 && (((uintptr_t)g.out) & 15) == 0))) {
+        const int dgrid = grid_for(ctx, (int64_t)g.N * g.OH * g.OW * ((g.C + 15) / 16));
+        if (g.kind == LN_KIND_I8) {
+            if (exact) conv_dw_q_kernel<LN_KIND_I8, true><<<dgrid, kThreads, dw_smem, ctx->stream>>>(g, mb);
+            else conv_dw_q_kernel<LN_KIND_I8, false><<<dgrid, kThreads, dw_smem, ctx->stream>>>(g, mb);
+        } else {
+            if (exact) conv_dw_q_kernel<LN_KIND_F8, true><<<dgrid, kThreads, dw_smem, ctx->stream>>>(g, mb);
+            else conv_dw_q_kernel<LN_KIND_F8, false><<<dgrid, kThreads, dw_smem, ctx->stream>>>(g, mb);
+        }
+        LN_LAUNCHED(ctx);
+        return LN_OK;
+    }
+    const int grid = grid_for(ctx, total);
     if (g.kind == LN_KIND_I8) {
         if (exact) conv_simt_kernel<LN_KIND_I8, true><<<grid, kThreads, 0, ctx->stream>>>(g, mb);
         else conv_simt_kernel<LN_KIND_I8, false><<<grid, kThreads, 0, ctx->stream>>>(g, mb);
@@ -906,6 +992,7 @@ int32_t ln_conv_weights_release(ln_conv_weights* w) {
     if (w->w) ln_pool_free(ctx, w->w, (size_t)(w->fpad * w->k * w->k * w->cpad));
     if (w->w_oihw) ln_pool_free(ctx, w->w_oihw, (size_t)(w->filters * w->channels * w->k * w->k));
     if (w->wscale) ln_pool_free(ctx, w->wscale, (size_t)w->fpad * 8);
+    ln_tensor_release(w->src_f32);
     delete w;
     return LN_OK;
 }
@@ -918,9 +1005,10 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
     if (!is_q(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: 8-bit input required");
     if (x->dtype != weights->dtype) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: input and weights have different 8-bit types");
     if (bias->dtype != LN_F32 || bias->count() != filters) return ln_fail(ctx, LN_ERR_SHAPE, "ln_conv2d_bias_act_q: bias must be f32 [filters]");
-    if (groups != 1 || dilation != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_conv2d_bias_act_q: groups and dilation must be 1");
+    if (dilation != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_conv2d_bias_act_q: dilation must be 1");
+    if (groups < 1 || channels % groups || filters % groups) return ln_fail(ctx, LN_ERR_SHAPE, "ln_conv2d_bias_act_q: groups do not divide channels / filters");
     if (stride_x != stride_y || stride_x < 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_conv2d_bias_act_q: stride_x must equal stride_y");
-    if (x->c != channels || x->h != input_height || x->w != input_width || weights->channels != channels || weights->filters != filters || weights->k != kernel_size)
+    if (x->c != channels || x->h != input_height || x->w != input_width || weights->channels != channels / groups || weights->filters != filters || weights->k != kernel_size)
         return ln_fail(ctx, LN_ERR_SHAPE, "ln_conv2d_bias_act_q: geometry does not match the tensors");
     if (activation < LN_ACT_LINEAR || activation > LN_ACT_RELU) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_conv2d_bias_act_q: activation %d is not on the detector path", activation);
     if (out_kind < LN_OUT_Q || out_kind > LN_OUT_ACC) return ln_fail(ctx, LN_ERR_ARG, "ln_conv2d_bias_act_q: bad out_kind");
@@ -950,8 +1038,10 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
     g.inv_sy = out_kind == LN_OUT_Q ? 1.0f / y_scale : 1.0f;
     g.small_acc = kind == LN_KIND_I8 && 127.0f * weights->max_l1 < 4194304.0f;
     g.out = y->ptr; g.out_pixel_stride = y->cstride;
+    g.groups = (int)groups;
+    if (groups > 1) { g.cpad = (int)ln_round_up(channels, 32); g.w_cpad = (int)weights->cpad; }
     if (rc == LN_OK) {
-        if (x->cstride >= weights->cpad && filters <= 4096 && ln_conv_umma_supported(weights->cpad, kernel_size, stride_x, stride_y, dilation, groups, input_width, input_height)) {
+        if (groups == 1 && x->cstride >= weights->cpad && filters <= 4096 && ln_conv_umma_supported(weights->cpad, kernel_size, stride_x, stride_y, dilation, groups, input_width, input_height)) {
             ln_conv_umma_plan plan;
             plan.mb = mb;
             rc = ln_conv_umma_plan_build(ctx, &plan, g);

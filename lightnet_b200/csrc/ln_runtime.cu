@@ -75,6 +75,10 @@ static size_t storage_bytes(int dtype, int64_t n, int64_t c, int64_t h, int64_t 
         *cstride = ln_round_up(c, 32);
         return (size_t)(n * h * w * *cstride);
     }
+    if (dtype == LN_F16) {  // NHWC binary16, channels padded to 32: a pixel is a multiple of 64 bytes
+        *cstride = 2 * ln_round_up(c, 32);
+        return (size_t)(n * h * w * *cstride);
+    }
     *cstride = 0;
     return (size_t)(n * c * h * w) * 4;
 }

@@ -14,7 +14,7 @@ def he_weights(layers, seed: int = 0, bn_identity: bool = True) -> np.ndarray:
     for l in layers:
         if l["kind"] != "conv":
             continue
-        f, c, k = l["filters"], l["in_c"], l["size"]
+        f, c, k = l["filters"], l["in_c"] // l.get("groups", 1), l["size"]   # channels each filter reads
         fan_in = c * k * k
         if bn_identity or not l["bn"]:
             parts.append(np.zeros(f, np.float32) if bn_identity else rng.normal(0, 0.1, f).astype(np.float32))

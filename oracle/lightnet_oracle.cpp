@@ -735,18 +735,21 @@ static bool feeds_head(const Net& net, int i) {
 
 // int32 accumulators of one int8 conv; NCHW in, NCHW out.  Integer arithmetic is
 // order independent, so any loop order is exact.
+// `groups`: filter f reads the C / groups channels of group f / (F / groups), as forward_layers.rs:646-679 does
+// (input channel g * cpg + ic, weight [f][ic][ky][kx]).
 static void conv_q8_acc(const int8_t* x, int B, int C, int H, int W, const int8_t* wq, int F, int k, int sx, int sy,
-                        int pad, int OH, int OW, int32_t* acc) {
+                        int pad, int OH, int OW, int32_t* acc, int groups = 1) {
+    const int cpg = C / groups, fpg = F / groups;
 #pragma omp parallel for collapse(2) schedule(dynamic)
     for (int b = 0; b < B; ++b)
         for (int f = 0; f < F; ++f) {
             int32_t* out = acc + ((size_t)b * F + f) * OH * OW;
             std::fill(out, out + (size_t)OH * OW, 0);
-            for (int ic = 0; ic < C; ++ic) {
-                const int8_t* xp = x + ((size_t)b * C + ic) * H * W;
+            for (int ic = 0; ic < cpg; ++ic) {
+                const int8_t* xp = x + ((size_t)b * C + (f / fpg) * cpg + ic) * H * W;
                 for (int ky = 0; ky < k; ++ky)
                     for (int kx = 0; kx < k; ++kx) {
-                        int32_t wv = wq[(((size_t)f * C + ic) * k + ky) * k + kx];
+                        int32_t wv = wq[(((size_t)f * cpg + ic) * k + ky) * k + kx];
                         if (wv == 0) continue;
                         for (int oy = 0; oy < OH; ++oy) {
                             int yy = oy * sy + ky - pad;
@@ -781,10 +784,10 @@ static void forward_q8(Net& net, const float* input) {
         TensorI8 y(L.out);
         switch (L.kind) {
             case K_CONV: {
-                if (L.groups != 1 || L.dilation != 1) throw std::runtime_error("int8 conv supports groups=1 dilation=1");
+                if (L.dilation != 1) throw std::runtime_error("int8 conv supports dilation=1");
                 std::vector<int32_t> acc(L.out.count());
                 conv_q8_acc(x.d.data(), x.s.b, x.s.c, x.s.h, x.s.w, L.wq.data(), L.filters, L.size, L.stride_x, L.stride_y,
-                            L.padding, L.out.h, L.out.w, acc.data());
+                            L.padding, L.out.h, L.out.w, acc.data(), std::max(L.groups, 1));
                 bool head = feeds_head(net, i);
                 if (head) net.head_q8[i] = Tensor(L.out);
                 float inv = 1.0f / sy;
@@ -1133,8 +1136,8 @@ int orc_net_layer_info(void* h, int i, int* info) {
     Net* n = (Net*)h;
     if (i < 0 || i >= (int)n->layers.size()) return -1;
     const Layer& L = n->layers[i];
-    int v[16] = {L.kind, L.in.w, L.in.h, L.in.c, L.in.b, L.out.w, L.out.h, L.out.c, L.out.b,
-                 L.filters, L.size, L.stride_x, L.stride_y, L.padding, L.bn ? 1 : 0, (int)L.act};
+    int v[20] = {L.kind, L.in.w, L.in.h, L.in.c, L.in.b, L.out.w, L.out.h, L.out.c, L.out.b,
+                 L.filters, L.size, L.stride_x, L.stride_y, L.padding, L.bn ? 1 : 0, (int)L.act, std::max(L.groups, 1), std::max(L.dilation, 1), 0, 0};
     std::memcpy(info, v, sizeof v);
     return 0;
 }
@@ -1484,6 +1487,12 @@ int orc_nms_records_by_class(float* recs, int n, float nms_thr, int top_k, int s
 }
 
 // Single-layer int8 conv: NCHW int8 in, [F][C][k][k] int8 weights, NCHW int32 accumulators out.
+void orc_conv_q8_acc_grouped(const int8_t* x, int B, int C, int H, int W, const int8_t* wq, int F, int k, int sx, int sy, int pad, int groups,
+                             int32_t* acc) {
+    int OH = conv_dim(H, pad, k, sy), OW = conv_dim(W, pad, k, sx);
+    conv_q8_acc(x, B, C, H, W, wq, F, k, sx, sy, pad, OH, OW, acc, groups);
+}
+
 void orc_conv_q8_acc(const int8_t* x, int B, int C, int H, int W, const int8_t* wq, int F, int k, int sx, int sy, int pad,
                      int32_t* acc) {
     int OH = conv_dim(H, pad, k, sy), OW = conv_dim(W, pad, k, sx);

@@ -72,6 +72,7 @@ def lib():
         L.orc_nms_records_by_class.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_int]
         L.orc_nms_records_first_k.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_int]
         L.orc_conv_q8_acc.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
+        L.orc_conv_q8_acc_grouped.argtypes = [C.c_void_p] + [C.c_int] * 4 + [C.c_void_p] + [C.c_int] * 6 + [C.c_void_p]
         L.orc_image_from_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         L.orc_image_resize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.orc_image_resize_exact_u8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
@@ -131,11 +132,11 @@ class Net:
             self.h = None
 
     def layer_info(self, i):
-        v = np.zeros(16, np.int32)
+        v = np.zeros(20, np.int32)
         if lib().orc_net_layer_info(self.h, i, _p(v)):
             raise IndexError(i)
         keys = ["kind", "in_w", "in_h", "in_c", "in_b", "out_w", "out_h", "out_c", "out_b", "filters", "size", "stride_x",
-                "stride_y", "padding", "bn", "act"]
+                "stride_y", "padding", "bn", "act", "groups", "dilation"]
         d = dict(zip(keys, (int(x) for x in v)))
         d["kind"] = KIND[d["kind"]]
         src = np.zeros(16, np.int32)
@@ -301,17 +302,17 @@ def nms_records_first_k(recs, nms, k):
     return r[:n].copy()
 
 
-def conv_q8_acc(x, wq, stride=1, pad=0):
-    """x int8 NCHW, wq int8 [F,C,k,k] -> int32 NCHW accumulators."""
+def conv_q8_acc(x, wq, stride=1, pad=0, groups=1):
+    """x int8 NCHW, wq int8 [F, C/groups, k, k] -> int32 NCHW accumulators."""
     x = np.ascontiguousarray(x, np.int8)
     wq = np.ascontiguousarray(wq, np.int8)
     B, Cc, H, W = x.shape
-    F, C2, k, _ = wq.shape
-    assert C2 == Cc
+    F, cpg, k, _ = wq.shape
+    assert cpg * groups == Cc and F % groups == 0
     OH = (H + 2 * pad - k) // stride + 1
     OW = (W + 2 * pad - k) // stride + 1
     acc = np.zeros((B, F, OH, OW), np.int32)
-    lib().orc_conv_q8_acc(_p(x), B, Cc, H, W, _p(wq), F, k, stride, stride, pad, _p(acc))
+    lib().orc_conv_q8_acc_grouped(_p(x), B, Cc, H, W, _p(wq), F, k, stride, stride, pad, groups, _p(acc))
     return acc
 
 

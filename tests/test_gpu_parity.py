@@ -167,6 +167,53 @@ def test_q8_conv_accumulators_bit_exact(be, case):
         assert d.max() <= 1 and (d > 0).mean() < 0.05, (act_name, d.max(), (d > 0).mean())
 
 
+GROUPED_CASES = [  # (n, c, h, w, f, k, stride, pad, groups): depthwise and grouped shapes of the kind efficientnet / csresnext cfgs use
+    (2, 32, 28, 28, 32, 3, 1, 1, 32),     # depthwise 3x3 (lightnet-cuda-oxide/tests/data/conv_shapes_summary.md: groups = channels)
+    (1, 96, 30, 26, 96, 3, 2, 1, 96),     # depthwise, stride 2
+    (2, 144, 14, 14, 144, 5, 1, 2, 144),  # depthwise 5x5
+    (1, 40, 9, 11, 40, 3, 1, 1, 40),      # depthwise, channels not a multiple of 16
+    (2, 64, 20, 20, 128, 3, 1, 1, 32),    # grouped: 2 channels, 4 filters per group
+    (1, 128, 19, 19, 128, 3, 1, 1, 32),   # grouped: 4 channels per group (csresnext)
+    (2, 24, 12, 12, 36, 1, 1, 0, 3),      # grouped 1x1
+]
+
+
+@pytest.mark.parametrize("case", GROUPED_CASES)
+def test_q8_grouped_conv_bit_exact(be, case):
+    """Grouped / depthwise int8 convolutions (CUDA-core kernels): int32 accumulators and exact-epilogue codes equal to the oracle's,
+    fast-epilogue codes within one."""
+    n, c, h, w, f, k, s, p, groups = case
+    rng = np.random.default_rng(hash(case) & 0xFFFF)
+    wt = rng.normal(0, 0.1, (f, c // groups, k, k)).astype(np.float32)
+    act = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    bias = rng.normal(0, 0.05, f).astype(np.float32)
+    sx = float(np.float32(np.abs(act).max() / 127.0))
+    oh, ow = conv_out(h, w, k, s, p)
+    tw = be.upload_f32(wt.shape, wt)
+    wq = be.conv_weights_q(tw, f, c // groups, k, ln.LN_Q8)
+    tx = be.upload_q((n, c, h, w), act, sx, ln.LN_Q8)
+    tb = be.upload_f32((1, f, 1, 1), bias)
+    xq, _ = be.download_q(tx)
+    ws = (np.abs(wt.reshape(f, -1)).max(1) / np.float32(127.0)).astype(np.float32)
+    wq_ref = np.clip(np.rint(wt / ws[:, None, None, None]), -127, 127).astype(np.int8)
+    acc_ref = orc.conv_q8_acc(xq, wq_ref, s, p, groups=groups)
+    acc = be.download_i32(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, groups, "linear", 1.0, ln.LN_OUT_ACC))
+    assert np.array_equal(acc, acc_ref)
+    mult = (np.float32(sx) * ws).astype(np.float32)
+    for act_name in ("leaky", "swish"):
+        a_ref, _ = orc.q8_epilogue(acc_ref, mult, bias, act_name, 1.0)
+        sy = np.float32(max(np.abs(a_ref).max(), 1e-6) / 127.0)
+        a_ref, q_ref = orc.q8_epilogue(acc_ref, mult, bias, act_name, float(np.float32(1.0) / sy))
+        be.set_exact_epilogue(True)
+        q, _ = be.download_q(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, groups, act_name, float(sy), ln.LN_OUT_Q))
+        assert np.array_equal(q, q_ref), act_name
+        head = be.download_f32(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, groups, act_name, 1.0, ln.LN_OUT_F32))
+        assert np.array_equal(head, a_ref), act_name
+        be.set_exact_epilogue(False)
+        q, _ = be.download_q(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, groups, act_name, float(sy), ln.LN_OUT_Q))
+        assert np.abs(q.astype(np.int32) - q_ref.astype(np.int32)).max() <= 1, act_name
+
+
 def test_q8_glue_matches_oracle(be):
     rng = np.random.default_rng(4)
     codes = rng.integers(-127, 128, (3, 64, 19, 19), dtype=np.int8)
@@ -599,6 +646,70 @@ def test_mini_network_q8_bit_exact(be):
     for b in range(4):
         ref = o.detect("q8", b, 640, 480, 0.2, 0.45, True, det_exp=True)
         assert np.array_equal(dets[b], ref[:512])
+    be.set_exact_epilogue(False)
+
+
+SEPARABLE_CFG = """
+[net]
+batch=2
+width=48
+height=40
+channels=3
+[convolutional]
+batch_normalize=1
+filters=32
+size=3
+stride=2
+pad=1
+activation=swish
+[convolutional]
+batch_normalize=1
+filters=32
+size=3
+stride=1
+pad=1
+groups=32
+activation=swish
+[convolutional]
+batch_normalize=1
+filters=64
+size=1
+stride=1
+pad=1
+activation=linear
+[convolutional]
+batch_normalize=1
+filters=64
+size=3
+stride=2
+pad=1
+groups=16
+activation=leaky
+[convolutional]
+filters=24
+size=1
+stride=1
+pad=1
+activation=linear
+[yolo]
+mask=0,1,2
+anchors=4,6, 8,10, 12,16
+classes=3
+num=3
+"""
+
+
+def test_separable_network_q8_bit_exact(be):
+    """A network with a depthwise and a grouped convolution in the 8-bit plan: every layer equal to the oracle's integer forward."""
+    o, net, x = check_q8_network(be, SEPARABLE_CFG, 2, 27)
+    for i, l in enumerate(o.layers()):
+        if l["kind"] == "yolo":
+            continue
+        if i + 1 < o.num_layers and o.layer_info(i + 1)["kind"] == "yolo":
+            assert np.array_equal(be.download_f32(net.layer_output(i)), o.head_q8(i)), i
+            continue
+        got, _ = be.download_q(net.layer_output(i))
+        assert np.array_equal(got, o.layer_output_q8(i)), (i, l["kind"])
     be.set_exact_epilogue(False)
 
 

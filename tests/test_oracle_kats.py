@@ -371,6 +371,18 @@ def test_conv_against_torch_on_reference_geometries():
         assert np.all(np.abs(y - ref) <= 1e-3 + 1e-3 * np.abs(ref))
 
 
+def test_q8_grouped_conv_accumulators_match_torch():
+    """Grouped / depthwise integer accumulators against torch's int64 convolution (forward_layers.rs:646-679 channel rule)."""
+    import torch
+
+    rng = np.random.default_rng(6)
+    for (c, f, k, stride, pad, groups) in [(8, 12, 3, 1, 1, 4), (8, 8, 3, 2, 1, 8), (6, 9, 1, 1, 0, 3)]:
+        x = rng.integers(-127, 128, (2, c, 7, 9), dtype=np.int8)
+        w = rng.integers(-127, 128, (f, c // groups, k, k), dtype=np.int8)
+        ref = torch.nn.functional.conv2d(torch.from_numpy(x.astype(np.int64)), torch.from_numpy(w.astype(np.int64)), stride=stride, padding=pad, groups=groups).numpy()
+        assert np.array_equal(orc.conv_q8_acc(x, w, stride, pad, groups=groups), ref)
+
+
 def test_q8_conv_accumulators_match_numpy():
     rng = np.random.default_rng(5)
     x = rng.integers(-127, 128, (2, 8, 7, 9), dtype=np.int8)
