@@ -120,6 +120,14 @@ int32_t ln_upsample_f32(ln_ctx* ctx, const ln_tensor* x, const int64_t output_sh
 /* channel_scale_f32 (lib.rs:485): out[i] = x[i] * scale[(i / channel_stride) % channels] */
 int32_t ln_channel_scale_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* scale, int64_t channels, int64_t channel_stride,
                              ln_tensor** out);
+/* region_forward_f32 (lib.rs:5090; host_ops.rs:73-116): the [region] head's forward.  x is [batch, anchors * entries, h, w]; the result
+   holds the same values in spatial-major order [batch, h * w, anchors, entries] with the objectness (entry 4) through the logistic and,
+   when softmax_classes != 0, a softmax over entries 5 .. 5 + classes. */
+int32_t ln_region_forward_f32(ln_ctx* ctx, const ln_tensor* x, int64_t anchors, int64_t entries, int64_t classes, int32_t softmax_classes,
+                              ln_tensor** out);
+/* yolo_activate_f32 (lib.rs:4951): classic [yolo] head activation in place order: logistic on every entry but w / h (none with
+   new_coords), then x, y become v * scale_xy - 0.5 * (scale_xy - 1). */
+int32_t ln_yolo_activate_f32(ln_ctx* ctx, const ln_tensor* x, int64_t classes, float scale_xy, int32_t new_coords, ln_tensor** out);
 /* batchnorm_fold_f32 (lib.rs:6208): returns (scale, bias') */
 int32_t ln_batchnorm_fold_f32(ln_ctx* ctx, const ln_tensor* gamma, const ln_tensor* mean, const ln_tensor* variance,
                               const ln_tensor* bias, float eps, ln_tensor** scale_out, ln_tensor** bias_out);
@@ -158,8 +166,9 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
                              int64_t padding, int64_t groups, int32_t activation, float y_scale, int32_t out_kind,
                              ln_tensor** out);
 /* maxpool_f16 (lib.rs:6384), upsample_f16 (lib.rs:6405), route_concat_f16 (lib.rs:6417),
-   shortcut_add_act_f16 (lib.rs:6502) analogues.  Max-pool, up-sample and route keep the input scale
-   (route inputs must share one scale); shortcut requantises act(a*sa + b*sb) with y_scale. */
+   shortcut_add_act_f16 (lib.rs:6502) analogues.  Max-pool, up-sample and route keep the codes (route inputs must share one
+   scale; a forward up-sample multiplies the tensor scale by `scale`); a reverse up-sample stores the mean code of each
+   stride x stride block and carries scale * stride^2 in the tensor scale; shortcut requantises act(a*sa + b*sb) with y_scale. */
 int32_t ln_maxpool_q(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height,
                      int64_t input_width, int64_t size, int64_t stride_x, int64_t stride_y, int64_t padding, ln_tensor** out);
 int32_t ln_upsample_q(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shape[4], int64_t channels, int64_t input_height,
@@ -169,6 +178,8 @@ int32_t ln_route_concat_q(ln_ctx* ctx, const ln_tensor* const* inputs, int32_t n
                           int64_t channel_stride, ln_tensor** out);
 int32_t ln_shortcut_add_act_q(ln_ctx* ctx, const ln_tensor* a, const ln_tensor* b, int32_t activation, float y_scale,
                               ln_tensor** out);
+/* shortcut_fit_f16 (lib.rs:6494) analogue: flat per-sample crop / zero-pad of a mismatched shortcut source, on the codes (the scale is kept). */
+int32_t ln_shortcut_fit_q(ln_ctx* ctx, const ln_tensor* x, int64_t batch, const int64_t output_shape[4], ln_tensor** out);
 
 /* ---- binary16 storage: trait F16TensorOpsBackend (lib.rs:6295-6629) ------------------------ */
 /* The twin that forward_compact_f16 (lightnet-runtime/src/runtime/gpu_f16.rs:21) drives, method for method.  TensorF16 is an

@@ -111,6 +111,7 @@ SYMBOLS = {
     "ln_upsample_q": (C.c_int32, [_VP, _VP, _I64P] + [C.c_int64] * 4 + [C.c_float, C.c_int32, _PP]),
     "ln_route_concat_q": (C.c_int32, [_VP, _PP, C.c_int32, _I64P, _I64P, _I64P, _I64P, C.c_int64, _PP]),
     "ln_shortcut_add_act_q": (C.c_int32, [_VP, _VP, _VP, C.c_int32, C.c_float, _PP]),
+    "ln_shortcut_fit_q": (C.c_int32, [_VP, _VP, C.c_int64, _I64P, _PP]),
     "ln_yolo_decode_nms": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_int32, _VP, _VP, _VP, _VP, _VP]),
     "ln_yolo_decode_nms_noalloc": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_int32, _VP, _VP, _VP, _VP, _VP]),
     "ln_yolo_decode_only": (C.c_int32, [_VP, _VP, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
@@ -140,6 +141,8 @@ SYMBOLS = {
     "ln_net_set_cuda_graph": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_profile": (C.c_int32, [_VP, _VP, C.c_int32, _VP, _VP]),
     "ln_channel_scale_f32": (C.c_int32, [_VP, _VP, _VP, C.c_int64, C.c_int64, _PP]),
+    "ln_region_forward_f32": (C.c_int32, [_VP, _VP, C.c_int64, C.c_int64, C.c_int64, C.c_int32, _PP]),
+    "ln_yolo_activate_f32": (C.c_int32, [_VP, _VP, C.c_int64, C.c_float, C.c_int32, _PP]),
     "ln_tensor_upload_f16": (C.c_int32, [_VP, _I64P, _VP, _PP]),
     "ln_tensor_download_f16": (C.c_int32, [_VP, _VP, _VP, C.c_int64]),
     "ln_tensor_widen_f16": (C.c_int32, [_VP, _VP, _PP]),
@@ -370,6 +373,12 @@ class B200Backend:
     def channel_scale_f32(self, x, scale, channels, channel_stride):
         return self._out(self.lib.ln_channel_scale_f32, x.h, scale.h, channels, channel_stride)
 
+    def region_forward_f32(self, x, anchors, entries, classes, softmax_classes):
+        return self._out(self.lib.ln_region_forward_f32, x.h, anchors, entries, classes, int(bool(softmax_classes)))
+
+    def yolo_activate_f32(self, x, classes, scale_xy, new_coords):
+        return self._out(self.lib.ln_yolo_activate_f32, x.h, classes, float(scale_xy), int(bool(new_coords)))
+
     # ---- F16TensorOpsBackend (binary16 storage) ---------------------------------------------------
     def upload_f16(self, shape, host):
         host = np.ascontiguousarray(host, np.float32)
@@ -464,6 +473,9 @@ class B200Backend:
     def route_concat_q(self, inputs, input_channel_offsets, input_channels, input_total_channels, output_shape, channel_stride):
         return self._route(self.lib.ln_route_concat_q, inputs, input_channel_offsets, input_channels, input_total_channels,
                            output_shape, channel_stride)
+
+    def shortcut_fit_q(self, x, batch, output_shape):
+        return self._out(self.lib.ln_shortcut_fit_q, x.h, batch, _shape4(output_shape))
 
     def shortcut_add_act_q(self, a, b, activation, y_scale):
         return self._out(self.lib.ln_shortcut_add_act_q, a.h, b.h, _act(activation), float(y_scale))

@@ -87,6 +87,47 @@ __global__ void channel_scale_f32_kernel(const float* __restrict__ x, const floa
         y[i] = __fmul_rn(x[i], scale[(i / channel_stride) % channels]);
 }
 
+// [region] forward (lightnet-cuda/src/host_ops.rs:73-116): channel-major NCHW entries -> spatial-major [batch, spatial, anchor, entry],
+// logistic objectness (entry 4), optional softmax over the class entries.  One thread per (batch, cell, anchor).
+__global__ void region_forward_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t batch, int spatial, int anchors, int entries, int classes,
+                                          int softmax_classes) {
+    const int64_t total = batch * spatial * anchors;
+    const int64_t channels = (int64_t)anchors * entries;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int a = (int)(i % anchors);
+        const int64_t s = (i / anchors) % spatial, b = i / ((int64_t)anchors * spatial);
+        float* out = y + (b * spatial + s) * channels + (int64_t)a * entries;
+        const float* in = x + (b * channels + (int64_t)a * entries) * spatial + s;
+        for (int e = 0; e < entries; ++e) out[e] = in[(int64_t)e * spatial];
+        out[4] = 1.0f / (1.0f + expf(-out[4]));
+        if (softmax_classes) {
+            float mx = -INFINITY;
+            for (int c = 0; c < classes; ++c) mx = fmaxf(mx, out[5 + c]);
+            float sum = 0.0f;
+            for (int c = 0; c < classes; ++c) {
+                const float v = expf(out[5 + c] - mx);
+                out[5 + c] = v;
+                sum += v;
+            }
+            if (sum > 0.0f)
+                for (int c = 0; c < classes; ++c) out[5 + c] = out[5 + c] / sum;
+        }
+    }
+}
+
+// Classic [yolo] head activation on anchor-major NCHW entries (lightnet-cuda/src/lib.rs:4951-4966): logistic on every entry but w / h
+// (none when new_coords), then x, y scaled: v * scale_xy - 0.5 * (scale_xy - 1).
+__global__ void yolo_activate_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n, int64_t plane, int entries, float scale_xy,
+                                         int new_coords) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int entry = (int)((i / plane) % entries);
+        float v = x[i];
+        if (!new_coords && entry != 2 && entry != 3) v = 1.0f / (1.0f + expf(-v));
+        if (entry < 2) v = __fsub_rn(__fmul_rn(v, scale_xy), __fmul_rn(0.5f, __fsub_rn(scale_xy, 1.0f)));
+        y[i] = v;
+    }
+}
+
 __global__ void add_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y, int64_t n) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) y[i] = a[i] + b[i];
 }
@@ -266,6 +307,38 @@ int32_t ln_channel_scale_f32(ln_ctx* ctx, const ln_tensor* x, const ln_tensor* s
     ctx->launches++;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { ln_tensor_release(y); return ln_fail(ctx, LN_ERR_CUDA, "channel_scale launch: %s", cudaGetErrorString(e)); }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_region_forward_f32(ln_ctx* ctx, const ln_tensor* x, int64_t anchors, int64_t entries, int64_t classes, int32_t softmax_classes, ln_tensor** out) {
+    if (!ctx || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_region_forward_f32: NULL argument");
+    if (!is_f32(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_region_forward_f32: f32 tensor required");
+    if (anchors < 1 || classes < 0 || entries < classes + 5 || x->c != anchors * entries)
+        return ln_fail(ctx, LN_ERR_SHAPE, "ln_region_forward_f32: %lld channels do not hold %lld anchors of %lld entries (>= classes + 5)", (long long)x->c, (long long)anchors, (long long)entries);
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, LN_F32, x->n, x->c, x->h, x->w);  // same element count; the layout is [batch, spatial, anchor, entry]
+    if (!y) return LN_ERR_CUDA;
+    region_forward_f32_kernel<<<grid_for(ctx, x->n * x->h * x->w * anchors), kThreads, 0, ctx->stream>>>((const float*)x->ptr, (float*)y->ptr, x->n, (int)(x->h * x->w), (int)anchors,
+                                                                                                         (int)entries, (int)classes, softmax_classes);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ln_tensor_release(y); return ln_fail(ctx, LN_ERR_CUDA, "region_forward launch: %s", cudaGetErrorString(e)); }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_yolo_activate_f32(ln_ctx* ctx, const ln_tensor* x, int64_t classes, float scale_xy, int32_t new_coords, ln_tensor** out) {
+    if (!ctx || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_yolo_activate_f32: NULL argument");
+    if (!is_f32(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_yolo_activate_f32: f32 tensor required");
+    if (classes < 0 || x->c % (classes + 5)) return ln_fail(ctx, LN_ERR_SHAPE, "YOLO head tensor length mismatch: %lld channels are not a multiple of %lld entries", (long long)x->c, (long long)(classes + 5));
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, LN_F32, x->n, x->c, x->h, x->w);
+    if (!y) return LN_ERR_CUDA;
+    yolo_activate_f32_kernel<<<grid_for(ctx, x->count()), kThreads, 0, ctx->stream>>>((const float*)x->ptr, (float*)y->ptr, x->count(), x->h * x->w, (int)(classes + 5), scale_xy, new_coords);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ln_tensor_release(y); return ln_fail(ctx, LN_ERR_CUDA, "yolo_activate launch: %s", cudaGetErrorString(e)); }
     *out = y;
     return LN_OK;
 }

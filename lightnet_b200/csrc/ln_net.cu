@@ -22,6 +22,8 @@ int ln_q_maxpool_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* 
                         int size, int sx, int sy, int padding);
 int ln_q_upsample_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int stride);
 int ln_q_copy_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys, int64_t pixels, int C);
+int ln_q_upsample_requant_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int stride, int reverse, float r);
+int ln_q_shortcut_fit_launch(ln_ctx* ctx, const void* x, int64_t xs, int sc, int sh, int sw, void* y, int64_t ys, int64_t N, int C, int H, int W);
 int ln_q_shortcut_launch(ln_ctx* ctx, int kind, const void* a, int64_t as, float sa, const void* b, int64_t bs, float sb, void* y, int64_t ys,
                          int64_t pixels, int C, int act, float inv_sy);
 int ln_q_quantize_launch(ln_ctx* ctx, int kind, const float* x, void* y, int64_t N, int C, int H, int W, int64_t cstride, float inv_s);
@@ -65,7 +67,8 @@ struct NLayer {
 
 struct QStep {
     int layer = -1;
-    int op = 0;  // 0 umma conv, 1 simt conv, 2 stem conv, 3 maxpool, 4 upsample, 5 copy, 6 shortcut, 7 quantize input
+    int op = 0;  // 0 umma conv, 1 simt conv, 2 stem conv, 3 maxpool, 4 upsample, 5 copy, 6 shortcut, 7 quantize input, 8 shortcut fit, 9 requantising up-sample
+    int sc = 0, sh = 0, sw = 0;  // shortcut fit: shape of the source
     ln_conv_umma_plan umma;
     ln_conv_geom geom;
     float2* mb = nullptr;
@@ -585,7 +588,8 @@ void scales_from_amax(ln_net* net, const std::vector<float>& amax, float qmax) {
     auto join = [&](int a, int b) { a = find(a); b = find(b); if (a != b) parent[std::max(a, b)] = std::min(a, b); };
     for (int i = 0; i < T - 1; ++i) {
         const NLayer& L = net->layers[i];
-        if (L.kind == K_MAXPOOL || L.kind == K_UPSAMPLE || L.kind == K_YOLO) join(i + 1, i);
+        // tensors whose codes are copied share a scale; an up-sample that scales or sums (reverse) requantises instead
+        if (L.kind == K_MAXPOOL || L.kind == K_YOLO || (L.kind == K_UPSAMPLE && !L.up_reverse && L.up_scale == 1.0f)) join(i + 1, i);
         if (L.kind == K_ROUTE) for (int s : L.sources) join(i + 1, s + 1);
     }
     std::vector<float> gmax(T, 0.0f);
@@ -611,12 +615,8 @@ int build_plan(ln_net* net, int mb) {
         if (L.kind == K_CONV && (L.dilation != 1 || L.stride_x != L.stride_y))
             return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit convolution needs dilation=1, stride_x=stride_y", i);
         if (L.kind == K_CONV && L.groups != 1 && i == 0) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #0: the first layer cannot be a grouped convolution in the 8-bit plan");
-        if (L.kind == K_UPSAMPLE && (L.up_reverse || L.up_scale != 1.0f)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit up-sample needs scale=1, forward", i);
-        if (L.kind == K_SHORTCUT) {
-            if (L.sources.size() != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit shortcut takes exactly one source", i);
-            const Shape4& s = net->layers[L.sources[0]].out;
-            if (s.w != L.out.w || s.h != L.out.h || s.c != L.out.c) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit shortcut needs same-shape sources", i);
-        }
+        if (L.kind == K_UPSAMPLE && !(L.up_scale > 0.0f)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit up-sample needs a positive scale", i);
+        if (L.kind == K_SHORTCUT && L.sources.size() != 1) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: 8-bit shortcut takes exactly one source", i);
         if (L.kind == K_YOLO && (i == 0 || !feeds_head(net, i - 1))) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: [yolo] must follow a convolution", i);
         if (L.kind == K_ROUTE && L.route_groups > 1 && (L.sources.size() != 1)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d: grouped route with several sources", i);
         if (L.kind != K_CONV && L.kind != K_YOLO && i > 0 && feeds_head(net, i - 1)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "layer #%d reads a head convolution's f32 output", i);
@@ -658,6 +658,7 @@ int build_plan(ln_net* net, int mb) {
             const NLayer& C = net->layers[i];
             const NLayer& S = net->layers[i + 1];
             if (C.kind != K_CONV || S.kind != K_SHORTCUT || S.act != LN_ACT_LINEAR || S.sources.size() != 1) continue;
+            { const Shape4& ss = net->layers[S.sources[0]].out; if (ss.w != S.out.w || ss.h != S.out.h || ss.c != S.out.c) continue; }  // a fitted source is not fused
             if (readers[i] != 1 || S.sources[0] == i || C.filters % 32 != 0 || feeds_head(net, i)) continue;
             if (!ln_conv_umma_supported(ln_round_up(C.in.c, 32), C.size, C.stride_x, C.stride_y, C.dilation, C.groups, C.in.w, C.in.h)) continue;
             net->fused_into_next[i] = 1;
@@ -835,10 +836,12 @@ int build_plan(ln_net* net, int mb) {
                 break;
             }
             case K_UPSAMPLE: {
-                st.op = 4;
+                const bool copy = !L.up_reverse && L.up_scale == 1.0f;
+                st.op = copy ? 4 : 9;
                 st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride;
                 st.y = net->views[i].ptr; st.ys = net->views[i].cstride;
                 st.C = L.in.c; st.H = L.in.h; st.W = L.in.w;
+                st.inv_sy = (sx * L.up_scale) / sy;  // requantisation factor of the scaling / reverse form
                 net->steps.push_back(st);
                 break;
             }
@@ -876,6 +879,20 @@ int build_plan(ln_net* net, int mb) {
                 const int s = L.sources[0];
                 st.x = net->views[i - 1].ptr; st.xs = net->views[i - 1].cstride; st.sa = sx;
                 st.x2 = net->views[s].ptr; st.xs2 = net->views[s].cstride; st.sb = net->scale[s + 1];
+                const Shape4& ss = net->layers[s].out;
+                if (ss.w != L.out.w || ss.h != L.out.h || ss.c != L.out.c) {
+                    // a source of another shape is cropped / zero-padded flat per sample into a buffer of this layer's shape first
+                    QStep f;
+                    f.layer = i; f.op = 8;
+                    const int64_t cs = ln_round_up(L.out.c, 32);
+                    const int b = alloc_buffer((int64_t)mb * L.out.h * L.out.w * cs);
+                    if (b < 0) return LN_ERR_CUDA;
+                    f.x = st.x2; f.xs = st.xs2; f.sc = ss.c; f.sh = ss.h; f.sw = ss.w;
+                    f.y = (uint8_t*)net->buffers[b].first; f.ys = cs;
+                    f.C = L.out.c; f.H = L.out.h; f.W = L.out.w;
+                    net->steps.push_back(f);
+                    st.x2 = f.y; st.xs2 = cs;
+                }
                 st.y = net->views[i].ptr; st.ys = net->views[i].cstride; st.inv_sy = 1.0f / sy;
                 st.C = L.out.c; st.H = L.out.h; st.W = L.out.w;
                 net->steps.push_back(st);
@@ -931,6 +948,8 @@ int run_plan(ln_net* net, const float* input_dev_f32) {
                 case 4: rc = ln_q_upsample_launch(ctx, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, L.up_stride); break;
                 case 5: rc = ln_q_copy_launch(ctx, st.x, st.xs, st.y, st.ys, (int64_t)mb * st.H * st.W, st.C); break;
                 case 6: rc = ln_q_shortcut_launch(ctx, kind, st.x, st.xs, st.sa, st.x2, st.xs2, st.sb, st.y, st.ys, (int64_t)mb * st.H * st.W, st.C, L.act, st.inv_sy); break;
+                case 8: rc = ln_q_shortcut_fit_launch(ctx, st.x, st.xs, st.sc, st.sh, st.sw, st.y, st.ys, mb, st.C, st.H, st.W); break;
+                case 9: rc = ln_q_upsample_requant_launch(ctx, kind, st.x, st.xs, st.y, st.ys, mb, st.C, st.H, st.W, L.up_stride, L.up_reverse ? 1 : 0, st.inv_sy); break;
                 case 7: rc = ln_q_quantize_launch(ctx, kind, input_dev_f32 + b0 * in_image, st.y, mb, st.C, st.H, st.W, st.ys, st.inv_sy); break;
             }
             if (rc) return rc;

@@ -240,6 +240,52 @@ __global__ void upsample_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uin
     }
 }
 
+// Up-sample that requantises (runtime/layer_ops.rs:2208-2256 on codes): nearest with a scale, or reverse = scale times the sum of each
+// stride x stride block ((dy, dx) order; the sum of int8 codes is exact), written as quantise(value * r), r = s_in * scale / s_out.
+template <int KIND>
+__global__ void upsample_requant_q_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t N, int C, int H, int W,
+                                          int OH, int OW, int s, int reverse, float r) {
+    const int64_t total = N * OH * OW * C;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C);
+        const int64_t pix = i / C;
+        const int ox = (int)(pix % OW), oy = (int)((pix / OW) % OH);
+        const int64_t n = pix / ((int64_t)OW * OH);
+        float v;
+        if (reverse) {
+            int isum = 0;
+            float fsum = 0.0f;
+            for (int dy = 0; dy < s; ++dy)
+                for (int dx = 0; dx < s; ++dx) {
+                    const int iy = oy * s + dy, ix = ox * s + dx;
+                    if (iy >= H || ix >= W) continue;
+                    const uint8_t code = x[((n * H + iy) * W + ix) * xs + c];
+                    if (KIND == LN_KIND_I8) isum += (int)(int8_t)code;
+                    else fsum = __fadd_rn(fsum, e4m3_to_float(code));
+                }
+            v = KIND == LN_KIND_I8 ? __int2float_rn(isum) : fsum;
+        } else v = code_to_float<KIND>(x[((n * H + oy / s) * W + ox / s) * xs + c]);
+        y[pix * ys + c] = quantize_code<KIND>(v, r);
+    }
+}
+
+// shortcut_fit on codes (lightnet-cuda/src/lib.rs:4041 / :6494): element i of a sample, in NCHW order, is element i of the source sample,
+// zero beyond the source's length
+__global__ void shortcut_fit_q_kernel(const uint8_t* __restrict__ x, int64_t xs, int sc, int sh, int sw, uint8_t* __restrict__ y, int64_t ys, int64_t N, int C,
+                                      int H, int W) {
+    const int64_t total = N * C * H * W, src_len = (int64_t)sc * sh * sw;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t flat = i % ((int64_t)C * H * W), n = i / ((int64_t)C * H * W);
+        const int w = (int)(flat % W), h = (int)((flat / W) % H), c = (int)(flat / ((int64_t)W * H));
+        uint8_t v = 0;
+        if (flat < src_len) {
+            const int sx = (int)(flat % sw), sy = (int)((flat / sw) % sh), scc = (int)(flat / ((int64_t)sw * sh));
+            v = x[((n * sh + sy) * sw + sx) * xs + scc];
+        }
+        y[((n * H + h) * W + w) * ys + c] = v;
+    }
+}
+
 // channel-slice copy between NHWC views (route); 16-byte and byte variants
 __global__ void copy_q16_kernel(const uint8_t* __restrict__ x, int64_t xs, uint8_t* __restrict__ y, int64_t ys, int64_t pixels, int C16) {
     const int64_t total = pixels * C16;
@@ -822,6 +868,24 @@ int ln_q_maxpool_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* 
     return LN_OK;
 }
 
+int ln_q_upsample_requant_launch(ln_ctx* ctx, int kind, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int stride, int reverse,
+                                 float r) {
+    const int OH = reverse ? H / stride : H * stride, OW = reverse ? W / stride : W * stride;
+    const int64_t total = N * OH * OW * C;
+    if (kind == LN_KIND_I8)
+        upsample_requant_q_kernel<LN_KIND_I8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C, H, W, OH, OW, stride, reverse, r);
+    else
+        upsample_requant_q_kernel<LN_KIND_F8><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, (uint8_t*)y, ys, N, C, H, W, OH, OW, stride, reverse, r);
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
+int ln_q_shortcut_fit_launch(ln_ctx* ctx, const void* x, int64_t xs, int sc, int sh, int sw, void* y, int64_t ys, int64_t N, int C, int H, int W) {
+    shortcut_fit_q_kernel<<<grid_for(ctx, N * C * H * W), kThreads, 0, ctx->stream>>>((const uint8_t*)x, xs, sc, sh, sw, (uint8_t*)y, ys, N, C, H, W);
+    LN_LAUNCHED(ctx);
+    return LN_OK;
+}
+
 int ln_q_upsample_launch(ln_ctx* ctx, const void* x, int64_t xs, void* y, int64_t ys, int64_t N, int C, int H, int W, int stride) {
     const int C16 = (int)(ln_round_up(C, 16) / 16);
     const int64_t total = N * H * stride * W * stride * C16;
@@ -1086,16 +1150,40 @@ int32_t ln_upsample_q(ln_ctx* ctx, const ln_tensor* x, const int64_t output_shap
     if (!ctx || !output_shape || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_upsample_q: NULL argument");
     if (!is_q(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_upsample_q: 8-bit tensor required");
     if (stride < 1) return ln_fail(ctx, LN_ERR_SHAPE, "ln_upsample_q: upsample stride cannot be zero");
-    if (reverse) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_upsample_q: reverse up-sampling is only available in f32");
     if (!(scale > 0.0f)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_upsample_q: scale must be positive");
     if (x->c != channels || x->h != input_height || x->w != input_width) return ln_fail(ctx, LN_ERR_SHAPE, "ln_upsample_q: geometry does not match the input tensor");
-    if (output_shape[0] != x->n || output_shape[1] != channels || output_shape[2] != input_height * stride || output_shape[3] != input_width * stride)
+    const int64_t oh = reverse ? input_height / stride : input_height * stride, ow = reverse ? input_width / stride : input_width * stride;
+    if (output_shape[0] != x->n || output_shape[1] != channels || output_shape[2] != oh || output_shape[3] != ow || oh < 1 || ow < 1)
         return ln_fail(ctx, LN_ERR_SHAPE, "ln_upsample_q: output_shape does not match");
     cudaSetDevice(ctx->device);
-    ln_tensor* y = ln_tensor_new(ctx, x->dtype, x->n, channels, input_height * stride, input_width * stride);
+    ln_tensor* y = ln_tensor_new(ctx, x->dtype, x->n, channels, oh, ow);
     if (!y) return LN_ERR_CUDA;
-    y->scale = x->scale * scale;  // out = scale * in: the codes are unchanged, the tensor scale carries the factor
-    int rc = ln_q_upsample_launch(ctx, x->ptr, x->cstride, y->ptr, y->cstride, x->n, (int)channels, (int)input_height, (int)input_width, (int)stride);
+    int rc;
+    if (reverse) {
+        // out = scale * (sum of a stride x stride block): the code is the block's mean, the tensor scale carries scale * stride^2
+        if (y->cstride != y->c) cudaMemsetAsync(y->ptr, 0, y->bytes, ctx->stream);
+        y->scale = x->scale * scale * (float)(stride * stride);
+        rc = ln_q_upsample_requant_launch(ctx, kind_of(x->dtype), x->ptr, x->cstride, y->ptr, y->cstride, x->n, (int)channels, (int)input_height, (int)input_width, (int)stride, 1,
+                                          1.0f / (float)(stride * stride));
+    } else {
+        y->scale = x->scale * scale;  // out = scale * in: the codes are unchanged, the tensor scale carries the factor
+        rc = ln_q_upsample_launch(ctx, x->ptr, x->cstride, y->ptr, y->cstride, x->n, (int)channels, (int)input_height, (int)input_width, (int)stride);
+    }
+    if (rc) { ln_tensor_release(y); return rc; }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_shortcut_fit_q(ln_ctx* ctx, const ln_tensor* x, int64_t batch, const int64_t output_shape[4], ln_tensor** out) {
+    if (!ctx || !output_shape || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_shortcut_fit_q: NULL argument");
+    if (!is_q(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_shortcut_fit_q: 8-bit tensor required");
+    if (batch != x->n || output_shape[0] != batch) return ln_fail(ctx, LN_ERR_SHAPE, "ln_shortcut_fit_q: batch mismatch");
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, x->dtype, output_shape[0], output_shape[1], output_shape[2], output_shape[3]);
+    if (!y) return LN_ERR_SHAPE;
+    y->scale = x->scale;
+    if (y->cstride != y->c) cudaMemsetAsync(y->ptr, 0, y->bytes, ctx->stream);
+    int rc = ln_q_shortcut_fit_launch(ctx, x->ptr, x->cstride, (int)x->c, (int)x->h, (int)x->w, y->ptr, y->cstride, y->n, (int)y->c, (int)y->h, (int)y->w);
     if (rc) { ln_tensor_release(y); return rc; }
     *out = y;
     return LN_OK;

@@ -716,7 +716,8 @@ static void calibrate(Net& net, float qmax = 127.0f) {
     UF uf(T);
     for (int i = 0; i < (int)net.layers.size(); ++i) {
         const Layer& L = net.layers[i];
-        if (L.kind == K_MAXPOOL || L.kind == K_UPSAMPLE || L.kind == K_YOLO) uf.join(i + 1, i);
+        // tensors whose codes are copied share a scale; an up-sample that scales or sums (reverse) requantises instead
+        if (L.kind == K_MAXPOOL || L.kind == K_YOLO || (L.kind == K_UPSAMPLE && !L.up_reverse && L.up_scale == 1.0f)) uf.join(i + 1, i);
         if (L.kind == K_ROUTE) for (int s : L.sources) uf.join(i + 1, s + 1);
     }
     std::vector<float> gmax(T, 0.0f);
@@ -826,22 +827,51 @@ static void forward_q8(Net& net, const float* input) {
             case K_ROUTE: route_any(L, net.out_q8, y); break;
             case K_SHORTCUT: {
                 float inv = 1.0f / sy;
-                for (int src : L.sources)
-                    if (net.out_q8[src].s.count() != y.s.count()) throw std::runtime_error("int8 shortcut needs same-shape sources");
+                // a source of another shape is cropped / zero-padded flat per sample (lib.rs:4041 shortcut_fit, layer_ops.rs:2110-2145):
+                // element p of a sample takes the source's element p while the source has one
+                const size_t os = y.s.count() / y.s.b;
                 for (size_t p = 0; p < y.d.size(); ++p) {
+                    const size_t b = p / os, q = p % os;
                     float v = (float)x.d[p] * sx;
-                    for (int src : L.sources) v = std::fma((float)net.out_q8[src].d[p], net.scale[src + 1], v);
+                    for (int src : L.sources) {
+                        const TensorI8& sT = net.out_q8[src];
+                        if (sT.s.b != y.s.b) throw std::runtime_error("shortcut mixes incompatible batch shapes");
+                        const size_t ss = sT.s.count() / sT.s.b;
+                        v = std::fma(q < ss ? (float)sT.d[b * ss + q] : 0.0f, net.scale[src + 1], v);
+                    }
                     y.d[p] = quant_i8(det_activate(L.act, v), inv);
                 }
                 break;
             }
             case K_UPSAMPLE: {
-                if (L.up_reverse || L.up_scale != 1.0f) throw std::runtime_error("int8 upsample supports scale=1, forward only");
+                const int st = L.up_stride;
+                if (!L.up_reverse && L.up_scale == 1.0f) {  // codes copied, scale shared
+                    for (int b = 0; b < y.s.b; ++b)
+                        for (int c = 0; c < y.s.c; ++c)
+                            for (int yy = 0; yy < y.s.h; ++yy)
+                                for (int xx = 0; xx < y.s.w; ++xx)
+                                    y.d[y.off(b, c, yy, xx)] = x.d[x.off(b, c, yy / st, xx / st)];
+                    break;
+                }
+                // layer_ops.rs:2208-2256 on codes: out = scale * in (nearest) or scale * sum of the stride x stride block (reverse; the
+                // integer sum is exact, taken in (dy, dx) order), requantised with r = s_in * scale / s_out
+                const float r = (sx * L.up_scale) / sy;
                 for (int b = 0; b < y.s.b; ++b)
                     for (int c = 0; c < y.s.c; ++c)
                         for (int yy = 0; yy < y.s.h; ++yy)
-                            for (int xx = 0; xx < y.s.w; ++xx)
-                                y.d[y.off(b, c, yy, xx)] = x.d[x.off(b, c, yy / L.up_stride, xx / L.up_stride)];
+                            for (int xx = 0; xx < y.s.w; ++xx) {
+                                float v;
+                                if (L.up_reverse) {
+                                    int sum = 0;
+                                    for (int dy = 0; dy < st; ++dy)
+                                        for (int dx = 0; dx < st; ++dx) {
+                                            const int iy = yy * st + dy, ix = xx * st + dx;
+                                            if (iy < x.s.h && ix < x.s.w) sum += x.d[x.off(b, c, iy, ix)];
+                                        }
+                                    v = (float)sum;
+                                } else v = (float)x.d[x.off(b, c, yy / st, xx / st)];
+                                y.d[y.off(b, c, yy, xx)] = quant_i8(v, r);
+                            }
                 break;
             }
             case K_YOLO: {

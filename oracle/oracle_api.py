@@ -302,6 +302,45 @@ def nms_records_first_k(recs, nms, k):
     return r[:n].copy()
 
 
+def region_forward(x, anchors, entries, classes, softmax_classes):
+    """lightnet-cuda/src/host_ops.rs:73-116 region_forward, loop for loop (small cases): [B, A*E, H, W] -> [B, H*W, A, E] flat."""
+    x = np.asarray(x, np.float32)
+    B, Cc, H, W = x.shape
+    assert Cc == anchors * entries and entries >= classes + 5
+    spatial = H * W
+    flat = x.reshape(B, Cc, spatial)
+    out = np.zeros((B, spatial, anchors, entries), np.float32)
+    for b in range(B):
+        for s in range(spatial):
+            for a in range(anchors):
+                row = flat[b, a * entries:(a + 1) * entries, s].copy()
+                row[4] = np.float32(1.0) / (np.float32(1.0) + np.exp(-row[4], dtype=np.float32))
+                if softmax_classes:
+                    cls = row[5:5 + classes]
+                    mx = np.float32(-np.inf) if classes == 0 else cls.max()
+                    e = np.exp(cls - mx, dtype=np.float32)
+                    total = np.float32(0)
+                    for v in e:
+                        total = np.float32(total + v)
+                    row[5:5 + classes] = e / total if total > 0 else e
+                out[b, s, a] = row
+    return out
+
+
+def yolo_activate(x, classes, scale_xy, new_coords):
+    """lightnet-cuda/src/lib.rs:4951-4966 yolo_activate_f32 default body."""
+    x = np.asarray(x, np.float32)
+    B, Cc, H, W = x.shape
+    entries = classes + 5
+    out = x.copy().reshape(B, Cc // entries, entries, H * W)
+    if not new_coords:
+        keep = [e for e in range(entries) if e not in (2, 3)]
+        out[:, :, keep] = np.float32(1.0) / (np.float32(1.0) + np.exp(-out[:, :, keep], dtype=np.float32))
+    s = np.float32(scale_xy)
+    out[:, :, :2] = out[:, :, :2] * s - np.float32(0.5) * (s - np.float32(1.0))
+    return out.reshape(x.shape)
+
+
 def conv_q8_acc(x, wq, stride=1, pad=0, groups=1):
     """x int8 NCHW, wq int8 [F, C/groups, k, k] -> int32 NCHW accumulators."""
     x = np.ascontiguousarray(x, np.int8)

@@ -115,3 +115,25 @@ def test_widen_and_narrow_between_f32_and_8_bit(be):
         be.narrow_f32(t, 0.0, ln.LN_Q8)
     with pytest.raises(ln.BackendError):
         be.widen_q(t)
+
+
+def test_region_forward_and_yolo_activate(be):
+    """The two classic head activations of the f32 trait: [region] forward (lightnet-cuda/src/lib.rs:5090, host_ops.rs:73-116) and
+    yolo_activate_f32 (lib.rs:4951), against numpy restatements of the reference's host loops (libm exp on both sides: 2 ulp)."""
+    rng = np.random.default_rng(12)
+    anchors, classes = 5, 7
+    entries = classes + 5
+    x = rng.normal(0, 2, (2, anchors * entries, 6, 7)).astype(np.float32)
+    t = be.upload_f32(x.shape, x)
+    for softmax in (True, False):
+        got = be.download_f32(be.region_forward_f32(t, anchors, entries, classes, softmax)).reshape(2, 42, anchors, entries)
+        ref = orc.region_forward(x, anchors, entries, classes, softmax)
+        assert np.allclose(got, ref, rtol=3e-6, atol=1e-7)
+        assert np.array_equal(got[..., :4], ref[..., :4])          # the box entries are only moved
+        if softmax:
+            assert np.allclose(got[..., 5:].sum(-1), 1.0, atol=1e-5)
+    with pytest.raises(ln.BackendError):
+        be.region_forward_f32(t, anchors, entries + 1, classes, True)
+    for new_coords, s in ((False, 1.2), (True, 2.0)):
+        got = be.download_f32(be.yolo_activate_f32(t, classes, s, new_coords))
+        assert np.allclose(got, orc.yolo_activate(x, classes, s, new_coords), rtol=3e-6, atol=1e-7)
