@@ -52,9 +52,10 @@ STRESS_THR, STRESS_NMS, STRESS_TOPK = 0.001, 0.65, 300
 # ncu summaries under profiles/ that hold the tensor-pipe counters of a layer class, keyed by (kernel size, stride, in_c, out_c)
 LAYER_CLASS_PROFILES = {
     (3, 1, 128, 128): "profiles/conv_umma_3x3_c128_k128_int8_n64.md",
-    (1, 1, 64, 64): "profiles/conv_umma_1x1_c64_k64_mish_int8_n16.md",
+    (1, 1, 64, 64): "profiles/conv_umma_1x1_c64_k64_mish_int8_n16_global_table.md",
     (3, 1, 256, 512): "profiles/conv_umma_3x3_c256_k512_int8_n128.md",
     (3, 1, 3, 32): "profiles/conv_stem_k3c3_i8_608_n16.md",
+    (1, 1, 128, 128): "profiles/conv_umma_1x1_c128_k128_mish_int8_n64.md",
 }
 
 
