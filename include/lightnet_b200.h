@@ -358,6 +358,12 @@ int32_t ln_debug_score_key_error(ln_ctx* ctx, float obj_lo, float obj_hi, float 
    (M = 128, N = 256, 32 bytes of K each) on operands resident in shared memory, timed with CUDA events on the ctx stream.  The
    measured denominator of the convolution's roofline.  dtype: LN_Q8, LN_F8 or LN_F16. */
 int32_t ln_debug_mma_peak(ln_ctx* ctx, int32_t dtype, int32_t iters, float* tops);
+/* The same loop with another instruction shape: N = n filters per instruction (a multiple of 32 up to 256) and, with pair != 0,
+   clusters of two CTAs issuing M = 256 instructions for both SMs (tcgen05.mma.cta_group::2).  Shows what a filter tile narrower
+   than 256 costs at the issue port.  Bits 1 and 2 of `pair` select variants of the loop: 2 = a tcgen05.commit after every
+   four instructions (as a pipelined main loop releases its stages), 4 = the operands rotate through four tile sets, 8 = two
+   warps issue, each into its own accumulator. */
+int32_t ln_debug_mma_peak_shape(ln_ctx* ctx, int32_t dtype, int32_t n, int32_t pair, int32_t iters, float* tops);
 /* Role-timing counters (clock cycles) that CTA 0 of the most recent tensor-core convolution recorded: [0..1] producer total /
    waiting, [2..5] MMA issuer total / waiting for an accumulator / waiting for operands / tiles, [6..] epilogue warps.  Only with
    a library built with -DLN_CONV_ROLE_TIMING and LN_DEBUG_CYCLES=1 in the environment at ln_ctx_create; LN_ERR_UNSUPPORTED

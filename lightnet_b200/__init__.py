@@ -158,6 +158,7 @@ SYMBOLS = {
     "ln_debug_score_key_error": (C.c_int32, [_VP, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32, C.POINTER(C.c_uint32)]),
     "ln_ctx_debug_cycles": (C.c_int32, [_VP, _I64P]),
     "ln_debug_mma_peak": (C.c_int32, [_VP, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
+    "ln_debug_mma_peak_shape": (C.c_int32, [_VP, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
 }
 
 
@@ -296,10 +297,13 @@ class B200Backend:
         self._check(self.lib.ln_debug_score_key_error(self.ctx, obj_lo, obj_hi, x_lo, x_hi, n_obj, n_x, C.byref(worst)))
         return int(worst.value)
 
-    def mma_peak(self, dtype=LN_Q8, iters=4096):
-        """Measured tensor-core rate (TOP/s) of a tcgen05.mma-only loop on every SM."""
+    def mma_peak(self, dtype=LN_Q8, iters=4096, n=256, pair=False):
+        """Measured tensor-core rate (TOP/s) of a tcgen05.mma-only loop on every SM: M = 128 (256 over a CTA pair), N = n."""
         t = C.c_float()
-        self._check(self.lib.ln_debug_mma_peak(self.ctx, dtype, iters, C.byref(t)))
+        if n == 256 and not pair:
+            self._check(self.lib.ln_debug_mma_peak(self.ctx, dtype, iters, C.byref(t)))
+        else:
+            self._check(self.lib.ln_debug_mma_peak_shape(self.ctx, dtype, n, 1 if pair else 0, iters, C.byref(t)))
         return float(t.value)
 
     def debug_cycles(self):

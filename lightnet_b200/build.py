@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "liblightnet_b200.so")
 SOURCES = ["ln_runtime.cu", "ln_f32_ops.cu", "ln_q8_ops.cu", "ln_f16_ops.cu", "ln_conv_umma.cu", "ln_yolo.cu", "ln_image.cu", "ln_net.cu"]
-HEADERS = ["ln_common.h", "ln_conv_plan.h", os.path.join("..", "..", "include", "lightnet_b200.h")]
+HEADERS = ["ln_common.h", "ln_conv_plan.h", "ln_conv_layout.inc", os.path.join("..", "..", "include", "lightnet_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-ffp-contract=off,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr",

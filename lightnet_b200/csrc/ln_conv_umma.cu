@@ -19,6 +19,7 @@
 // roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda_fp8.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -32,7 +33,8 @@ constexpr int kMaxStages = 8;
 #endif
 constexpr int kEpilogueGroups = LN_EPILOGUE_GROUPS;   // groups of four epilogue warps (one warp per TMEM lane quadrant); group g takes the tiles t with t % groups == g
 constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
-constexpr int kThreads = 32 * (2 + kEpilogueWarps);  // producer warp, MMA warp, epilogue warps
+constexpr int kRoleWarps = 4;  // producer and MMA issuer of pipeline 0 (warps 0, 1) and of pipeline 1 (warps 2, 3)
+constexpr int kThreads = 32 * (kRoleWarps + kEpilogueWarps);
 constexpr int kMaxAccBufs = 8;       // accumulator tiles in TMEM: 512 columns / BN, at most 8
 constexpr uint32_t kWaitLimit = 1u << 20;
 // Role timing of CTA 0 (clock reads in the hot loops) is compiled in only with -DLN_CONV_ROLE_TIMING.
@@ -95,6 +97,69 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
                  "l"(map), "r"(bar), "r"(c0), "r"(c1)
                  : "memory");
+}
+
+// CTA-pair forms (clusters of two CTAs, tcgen05 with cta_group::2).  The two CTAs of a pair each load their own operand tiles
+// into their own shared memory, but every load signals the barrier of the pair's first CTA, whose MMA thread issues the
+// instructions for both.  None of these loads is a multicast: every CTA fetches what it needs itself.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the address, in the shared::cluster window, of the first CTA's copy of a shared-memory variable of this CTA
+__device__ __forceinline__ uint32_t map_to_leader(uint32_t addr) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+        "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(leader_bar), "r"(c0), "r"(c1)
+                 : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once all MMAs issued so far have finished
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3)
+                 : "memory");
+}
+// M = 256 over the pair: rows 0..127 of A and of the accumulator live in the first CTA, 128..255 in the second; each CTA holds
+// half of the N rows of B at the same shared-memory offset.
+template <int KIND>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t z = 0u;  // no output lane disabled
+    if (KIND == LN_KIND_I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+            : "memory");
+    } else if (KIND == LN_KIND_F8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+            : "memory");
+    }
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -195,41 +260,419 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int bk) {
     return d;
 }
 
-template <int KIND, int ACT, bool EXACT>
+// tile of CTA `rank` of a pair in work unit `unit`: pixel tile 2 * (unit / tiles_f) + rank of filter tile unit % tiles_f
+__device__ __forceinline__ int pair_tile(int unit, int rank, unsigned long long magic_f, int tiles_f) {
+    const int pp = fast_div(unit, magic_f), tf = unit - pp * tiles_f;
+    return (2 * pp + rank) * tiles_f + tf;
+}
+
+#define LN_FIRST_UNIT (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x)
+#define LN_UNIT_STEP (PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x)
+
+    // Pipelines: issuing one tcgen05.mma costs its thread about 100 cycles whatever the instruction's size, so one issuing
+    // thread keeps the tensor pipe busy only with N = 256 instructions.  With two pipelines (pipes = 2) the CTA's tiles alternate
+    // between two producer / issuer pairs, each with its own half of the stage ring and its own accumulator buffers (tile t uses
+    // buffer t % nbuf, nbuf is even); the two instruction streams overlap in the tensor pipe.  The epilogue takes the tiles in
+    // order, as before.
+// The roles are inlined into the kernel: as functions of their own they would read the parameters through a pointer instead of
+// as constant-bank operands, which costs the single-thread loops 20 to 50 % (measured).
+template <bool PAIR>
+__device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p) {
+#include "ln_conv_layout.inc"
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && pipe < pipes) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        long long w_empty = 0;
+        long long* pw = p.debug ? &w_empty : nullptr;
+        const long long t_start = kRoleTiming ? clock64() : 0;
+        if (b_res && pipe == 0 && LN_FIRST_UNIT < p.num_units) {
+            if (rank == 0) mbar_arrive_expect_tx(bres_bar, (PAIR ? 2u : 1u) * (uint32_t)kblocks * b_bytes);
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
+                if (PAIR) tma_load_2d_pair(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, (int)rank * b_rows, lead_base + (bres_bar - bar_base));
+                else tma_load_2d(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, 0, bres_bar);
+            }
+        }
+        int astage = 0;
+        uint32_t aphase = 0;
+        for (int unit = LN_FIRST_UNIT + pipe * LN_UNIT_STEP; ok && unit < p.num_units; unit += pipes * LN_UNIT_STEP) {
+            const int tile = PAIR ? pair_tile(unit, (int)rank, p.magic_f, p.tiles_f) : unit;
+            const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
+            const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
+            const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
+            const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn + (int)rank * b_rows;
+            if (halo) {
+                // per channel block: box s, then (unless the weights are resident) the weight tiles of the taps that read it
+                for (int c0 = 0; ok && c0 < p.cpad; c0 += bk)
+                    for (int s = 0; ok && s < 3; ++s) {
+                        if (!(ok = mbar_wait(aempty_bar(astage), aphase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
+                        mbar_arrive_expect_tx(afull_bar(astage), box_bytes);
+                        tma_load_4d(ring_base + (uint32_t)astage * box_bytes, &p.tmA[0], c0, ow0 - p.pad + s, oh0 - p.pad, n0, afull_bar(astage));
+                        if (++astage == p.a_stages) { astage = 0; aphase ^= 1u; }
+                        if (b_res) continue;
+                        for (int r = 0; r < 3; ++r) {
+                            if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
+                            mbar_arrive_expect_tx(full_bar(stage), b_bytes);
+                            tma_load_2d(bring_base + (uint32_t)stage * b_bytes, &p.tmB, (r * 3 + s) * p.cpad + c0, f0, full_bar(stage));
+                            if (++stage == stages) { stage = 0; phase ^= 1u; }
+                        }
+                    }
+                continue;
+            }
+            // taps and channel blocks in nested loops: no division on this single thread's critical path
+            int wcol = 0;  // first column of the k-block in the weight matrix: tap * cpad + c0
+            for (int r = 0; ok && r < p.R; ++r) {
+                for (int s = 0; ok && s < p.S; ++s) {
+                    int ty = r - p.pad, tx = s - p.pad, map = 0;
+                    if (p.stride == 2) {
+                        const int py = ty & 1, px = tx & 1;  // parity class of the tap (two's complement & 1 is non-negative)
+                        ty = (ty - py) >> 1;
+                        tx = (tx - px) >> 1;
+                        map = py * 2 + px;
+                    }
+                    for (int c0 = 0; c0 < p.cpad; c0 += bk, wcol += bk) {
+                        if (!(ok = mbar_wait(empty_bar(s0 + stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
+                        const uint32_t sa = ring_base + (uint32_t)(s0 + stage) * stage_bytes;
+                        if (PAIR) {
+                            // the first CTA's barrier counts the bytes of both CTAs; the other CTA's loads may land before it is
+                            // armed (the transaction count goes negative for a moment), never in an earlier phase: this stage
+                            // was released by MMAs that had seen that phase complete
+                            const uint32_t lead_full = lead_base + (full_bar(s0 + stage) - bar_base);
+                            if (rank == 0) mbar_arrive_expect_tx(full_bar(s0 + stage), 2u * stage_bytes);
+                            tma_load_4d_pair(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, lead_full);
+                            if (!b_res) tma_load_2d_pair(sa + a_bytes, &p.tmB, wcol, f0, lead_full);
+                        } else {
+                            mbar_arrive_expect_tx(full_bar(s0 + stage), stage_bytes);
+                            tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(s0 + stage));
+                            if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, wcol, f0, full_bar(s0 + stage));
+                        }
+                        if (++stage == spp) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+        }
+        if (kRoleTiming && p.debug && blockIdx.x == 0 && pipe == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
+    }
+}
+
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
+#include "ln_conv_layout.inc"
+    const uint32_t tmem_base = *tmem_slot;
+    // ------------------------------------------------------------------ MMA issuer (of a pair: the first CTA's)
+    if (lane == 0 && rank == 0 && pipe < pipes) {
+        // instruction descriptor: accumulator type (bits 4-5: 1 = f32, 2 = s32), A and B types (bits 7-9, 10-12: 0 = E4M3 / binary16
+        // depending on the kind, 1 = signed 8-bit), N / 8 and M / 16; both operands K-major
+        const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((uint32_t)(bn >> 3) << 17) |
+                               (((PAIR ? 256u : 128u) >> 4) << 24);
+        int stage = 0, astage = 0;
+        uint32_t phase = 0, aphase = 0;
+        int t = pipe;  // the CTA's tile counter: pipeline i takes the tiles t = i, i + pipes, ...
+        bool ok = true;
+        long long w_tempty = 0, w_full = 0, t_issue = 0, t_commit = 0;
+        long long* pw1 = p.debug ? &w_tempty : nullptr;
+        long long* pw2 = p.debug ? &w_full : nullptr;
+        const long long t_start = kRoleTiming ? clock64() : 0;
+        if (b_res && LN_FIRST_UNIT < p.num_units) ok = mbar_wait(bres_bar, 0u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT);
+        for (int unit = LN_FIRST_UNIT + pipe * LN_UNIT_STEP; ok && unit < p.num_units; unit += pipes * LN_UNIT_STEP, t += pipes) {
+            const int buf = t % nbuf;
+            const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
+            if (!(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw1))) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
+            if (halo) {
+                uint32_t accumulate = 0;
+                for (int cb = 0; ok && cb < p.cblocks; ++cb)
+                    for (int s = 0; ok && s < 3; ++s) {
+                        if (!(ok = mbar_wait(afull_bar(astage), aphase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                        tc_fence_after();
+                        const uint32_t sa = ring_base + (uint32_t)astage * box_bytes;
+                        for (int r = 0; r < 3; ++r) {
+                            uint32_t sb;
+                            if (b_res) sb = bres_base + (uint32_t)((r * 3 + s) * p.cblocks + cb) * b_bytes;
+                            else {
+                                if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                                tc_fence_after();
+                                sb = bring_base + (uint32_t)stage * b_bytes;
+                            }
+                            // the box from its row r on: 128 consecutive rows of bk bytes, aligned to the 8-row swizzle pattern
+                            const uint64_t a_desc = make_smem_desc(sa + (uint32_t)(r * p.TW * bk), bk), b_desc = make_smem_desc(sb, bk);
+                            for (int k = 0; k < bk / 32; ++k) {
+                                tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accumulate);
+                                accumulate = 1u;
+                            }
+                            if (!b_res) {
+                                tc_commit(empty_bar(stage));
+                                if (++stage == stages) { stage = 0; phase ^= 1u; }
+                            }
+                        }
+                        if (!ok) break;
+                        tc_commit(aempty_bar(astage));  // arrives when the MMAs above have finished reading the box
+                        if (++astage == p.a_stages) { astage = 0; aphase ^= 1u; }
+                    }
+                if (!ok) break;
+                tc_commit(tfull_bar(buf));
+                continue;
+            }
+            for (int kb = 0; kb < kblocks; ++kb) {
+                if (!(ok = mbar_wait(full_bar(s0 + stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                const long long ti0 = kRoleTiming && p.debug ? clock64() : 0;
+                tc_fence_after();
+                const uint32_t sa = ring_base + (uint32_t)(s0 + stage) * stage_bytes;
+                const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + a_bytes, bk);
+                for (int k = 0; k < bk / 32; ++k) {  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
+                    if (PAIR) tc_mma_pair<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
+                    else tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
+                }
+                const long long ti1 = kRoleTiming && p.debug ? clock64() : 0;
+                // arrives (in both CTAs of a pair) when the MMAs above have finished reading this stage
+                if (PAIR) tc_commit_pair(empty_bar(s0 + stage));
+                else tc_commit(empty_bar(s0 + stage));
+                if (++stage == spp) { stage = 0; phase ^= 1u; }
+                if (kRoleTiming && p.debug) { t_issue += ti1 - ti0; t_commit += clock64() - ti1; }
+            }
+            if (!ok) break;
+            if (PAIR) tc_commit_pair(tfull_bar(buf));
+            else tc_commit(tfull_bar(buf));
+        }
+        if (kRoleTiming && p.debug && blockIdx.x == 0 && pipe == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; p.debug[25] = t_issue; p.debug[26] = t_commit; }
+    }
+}
+
+template <int KIND, int ACT, bool EXACT, bool PAIR>
+__device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p) {
+#include "ln_conv_layout.inc"
+    const uint32_t tmem_base = *tmem_slot;
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;          // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
+    // Which of the warps of the quadrant.  The work of the epilogue is cut into units: an accumulator tile is `subs` units of
+    // bn / subs columns each (subs > 1 when TMEM holds fewer tiles than there are groups, so that all groups stay busy), and
+    // group g takes the units u with u % groups == g, u counting (tile, sub) pairs in order.  Never more groups than
+    // nbuf * subs: a group that starts waiting for a unit of tile t has finished its unit `groups` earlier, a unit of tile
+    // t - ceil(groups / subs) or later; tiles are committed in order, so the previous use of this buffer (tile t - nbuf) has
+    // been accumulated in full, which a parity wait needs.
+    const int group = (warp - kRoleWarps) >> 2;
+    const int subs = p.subs, sub_cols = bn / subs;
+    const int groups = nbuf * subs < kEpilogueGroups ? nbuf * subs : kEpilogueGroups;
+    const int row = quad * 32 + lane;
+    const int pw = row & (p.TW - 1), ph = (row >> p.log_tw) & (p.TH - 1), pn = row >> (p.log_tw + p.log_th);
+    constexpr bool kTranscendental = ACT == LN_ACT_MISH || ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC;
+    const bool folded = !EXACT && p.mb_folded != nullptr;
+    {
+        // the epilogue warps bring the table in while the producer and the MMA issuer fill the pipeline
+        const uint4* src = reinterpret_cast<const uint4*>(folded ? p.mb_folded : p.mb);
+        for (int i = (int)threadIdx.x - 32 * kRoleWarps; i < p.tab_bytes / 16; i += 32 * kEpilogueWarps) {
+            const uint4 v = __ldg(src + i);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tab_base + 16u * (uint32_t)i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+    }
+    int t = 0;
+    bool ok = true;
+    long long w_tfull = 0, dbg_ld = 0, dbg_math = 0, dbg_st = 0;
+    long long* pwe = p.debug ? &w_tfull : nullptr;
+    const long long t_start = kRoleTiming ? clock64() : 0;
+    int turn = 0;  // unit counter modulo groups
+    for (int unit = LN_FIRST_UNIT; ok && group < groups && unit < p.num_units; unit += LN_UNIT_STEP, ++t)
+    for (int sub = 0; ok && sub < subs; ++sub, turn = turn + 1 == groups ? 0 : turn + 1) {
+        if (turn != group) continue;  // another group of epilogue warps takes this unit
+        const int tile = PAIR ? pair_tile(unit, (int)rank, p.magic_f, p.tiles_f) : unit;
+        const int c_begin = sub * sub_cols, c_end = c_begin + sub_cols;
+        const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
+        const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
+        const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
+        const int ow = tw * p.TW + pw, oh = th * p.TH + ph, n = tn * p.TN + pn, f0 = tf * bn;
+        const bool valid = ow < p.OW && oh < p.OH && n < p.N;
+        const int buf = t % nbuf;
+        const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
+        if (!(ok = mbar_wait<false>(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT, pwe))) break;
+        tc_fence_after();
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * bn);
+        const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+            uint32_t acc[32];
+            const long long tq0 = kRoleTiming && p.debug ? clock64() : 0;
+            tmem_ld_32x32(taddr0 + (uint32_t)c0, acc);
+            const bool fast = KIND == LN_KIND_I8 && p.out_kind == LN_OUT_Q && f0 + c0 + 32 <= p.F;
+            // where this chunk goes: with pixel-group packing the columns [j * f_real, (j + 1) * f_real) are the filters of the
+            // j-th pixel of the row's group (f_real is a multiple of 32 then, so a chunk never straddles two pixels)
+            int64_t opix = pix;
+            int fo = f0 + c0;
+            if (p.pack > 1) {
+                int j = 0;
+                while (fo >= p.f_real) { fo -= p.f_real; ++j; }
+                opix = pix * p.pack + j;
+            }
+            if (fast) {
+                // ---- fast path: 32 valid filters, int8 out.  The {mult, bias} pairs (two per 16-byte load) are fetched
+                // while the TMEM load is in flight, so the arithmetic below runs from registers only.
+                const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);
+                uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
+                if (p.res != nullptr && valid) {  // residual codes of the fused shortcut, fetched while TMEM is read
+                    const uint4* rp = (const uint4*)((const uint8_t*)p.res + opix * p.res_pixel_stride + fo);
+                    r0 = __ldg(rp);
+                    r1 = __ldg(rp + 1);
+                }
+                tmem_ld_wait();
+                const long long tq1 = kRoleTiming && p.debug ? clock64() : 0;
+                if (kRoleTiming && p.debug) dbg_ld += tq1 - tq0;
+                if (!valid) continue;
+                uint32_t packed[8];
+                // Four values at a time, each loop body fetching its own two table entries from shared memory, so that few
+                // values are live at once (the kernel has to fit in 96 registers).
+                if (folded) {
+                    // Fast mode, accumulators below 2^22.  Adding an accumulator to the bits of 1.5 * 2^23 gives the float
+                    // 1.5 * 2^23 + accumulator; the table holds {mult 2i, mult 2i+1, bias 2i, bias 2i+1} divided by the output scale,
+                    // the bias carrying -1.5 * 2^23 * mult, so one packed FMA yields two pre-activations in code units;
+                    // activation and rounding run in packed binary16.
+                    const __half2 kh = __float2half2_rn(p.sy_log2e), inv_h = __float2half2_rn(p.inv_sy);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
+                        float t0, t1, t2, t3;
+                        ffma2(t0, t1, __int_as_float(0x4B400000 + (int)acc[4 * j]), __int_as_float(0x4B400000 + (int)acc[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
+                        ffma2(t2, t3, __int_as_float(0x4B400000 + (int)acc[4 * j + 2]), __int_as_float(0x4B400000 + (int)acc[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
+                        packed[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
+                    }
+                } else {
+                    // int32 -> f32: below 2^22 through the bits of 1.5 * 2^23 (two FMA-pipe instructions, exact); otherwise the
+                    // conversion unit, or, for the transcendental epilogues that need that unit for ex2 / rcp, an exact ALU sequence
+                    const bool small = p.small_acc != 0;
+                    const __half2 inv_h = __float2half2_rn(p.inv_sy);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
+                        float x[4];
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            const int a = (int)acc[4 * j + b];
+                            x[b] = small ? __fadd_rn(__int_as_float(0x4B400000 + a), -12582912.0f) : (kTranscendental ? i2f_alu(a) : __int2float_rn(a));
+                        }
+                        const float v0 = __fmaf_rn(x[0], ma.x, ma.y), v1 = __fmaf_rn(x[1], ma.z, ma.w), v2 = __fmaf_rn(x[2], mc.x, mc.y), v3 = __fmaf_rn(x[3], mc.z, mc.w);
+                        if (EXACT)
+                            packed[j] = pack4_low_bytes(quant_i8_magic(ln_epilogue_act<true>(ACT, v0), p.inv_sy), quant_i8_magic(ln_epilogue_act<true>(ACT, v1), p.inv_sy),
+                                                        quant_i8_magic(ln_epilogue_act<true>(ACT, v2), p.inv_sy), quant_i8_magic(ln_epilogue_act<true>(ACT, v3), p.inv_sy));
+                        else
+                            packed[j] = ln_h2_pack(ln_h2_act_quant<ACT>(v0, v1, inv_h), ln_h2_act_quant<ACT>(v2, v3, inv_h));
+                    }
+                }
+                if (p.res != nullptr) {
+                    // fused shortcut, the arithmetic of the stand-alone shortcut kernel applied to the codes just produced
+                    const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t u[4];
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            float v = __fmul_rn(s8_to_float(packed[j], b), p.s_c);
+                            v = __fmaf_rn(s8_to_float(rw[j], b), p.s_res, v);
+                            u[b] = quant_i8_magic(v, p.inv_sy2);
+                        }
+                        packed[j] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
+                    }
+                }
+                const long long tq2 = kRoleTiming && p.debug ? clock64() : 0;
+                uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
+                o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                if (kRoleTiming && p.debug) { dbg_math += tq2 - tq1; dbg_st += clock64() - tq2; }
+                continue;
+            }
+            // ---- general path: f32 / raw-accumulator outputs (NCHW), FP8, and int8 chunks with fewer than 32 real filters.
+            // The {mult, bias} pairs come two per 16-byte load (the table is padded to a multiple of 32 filters).
+            const int nf = p.F - (f0 + c0);  // real filters from this chunk's first column on (32 or more: all of the chunk)
+            tmem_ld_wait();
+            if (!valid || nf <= 0) continue;
+            if (p.out_kind == LN_OUT_ACC) {
+                // NCHW, raw accumulator bits (int32 or f32): consecutive lanes are consecutive pixels of a row, one plane per filter
+                const int64_t plane = (int64_t)p.OH * p.OW;
+                int32_t* o = (int32_t*)p.out + ((int64_t)n * p.F + (f0 + c0)) * plane + (int64_t)oh * p.OW + ow;
+#pragma unroll
+                for (int j = 0; j < 32; ++j, o += plane)
+                    if (j < nf) *o = (int32_t)acc[j];
+                continue;
+            }
+            float a[32];
+            const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);  // (never the folded table: that one needs int8 output and full chunks)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float4 mj = lds_f4(mtab + 16u * j);
+                const float x0 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
+                const float x1 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
+                a[2 * j] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x0, mj.x, mj.y));
+                a[2 * j + 1] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x1, mj.z, mj.w));
+            }
+            if (p.out_kind == LN_OUT_F32) {
+                const int64_t plane = (int64_t)p.OH * p.OW;
+                float* o = (float*)p.out + ((int64_t)n * p.F + (f0 + c0)) * plane + (int64_t)oh * p.OW + ow;  // NCHW
+#pragma unroll
+                for (int j = 0; j < 32; ++j, o += plane)
+                    if (j < nf) *o = a[j];
+            } else {
+                if (KIND == LN_KIND_F16) {
+                    // binary16 NHWC: 32 filters = 64 bytes per pixel, rounded to nearest even, infinities kept
+                    uint32_t hw[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const __half2 h = __floats2half2_rn(2 * j < nf ? a[2 * j] : 0.0f, 2 * j + 1 < nf ? a[2 * j + 1] : 0.0f);
+                        hw[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + 2 * fo);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) o[j] = make_uint4(hw[4 * j], hw[4 * j + 1], hw[4 * j + 2], hw[4 * j + 3]);
+                    continue;
+                }
+                uint32_t packed[8];
+                if (KIND == LN_KIND_I8) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t v = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            const int q = 4 * j + b < nf ? ln_quant_i8(a[4 * j + b], p.inv_sy) : 0;
+                            v |= ((uint32_t)q & 0xFFu) << (8 * b);
+                        }
+                        packed[j] = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a[4 * j] * p.inv_sy, a[4 * j + 1] * p.inv_sy), __NV_SATFINITE, __NV_E4M3);
+                        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(a[4 * j + 2] * p.inv_sy, a[4 * j + 3] * p.inv_sy), __NV_SATFINITE, __NV_E4M3);
+                        uint32_t w = lo | (hi << 16);
+                        const int left = nf - 4 * j;  // codes of filters that do not exist are zero
+                        if (left < 4) w = left <= 0 ? 0u : (w & (0xFFFFFFFFu >> (8 * (4 - left))));
+                        packed[j] = w;
+                    }
+                }
+                uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
+                o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(lead_base + (tempty_bar(buf) - bar_base));  // the MMA issuer waits for both CTAs
+            else mbar_arrive(tempty_bar(buf));
+        }
+    }
+    if (p.debug && blockIdx.x == 0 && lane == 0 && warp - kRoleWarps < 8) {  // (the counter block has room for eight epilogue warps)
+        p.debug[6 + 2 * (warp - kRoleWarps)] = clock64() - t_start;
+        p.debug[7 + 2 * (warp - kRoleWarps)] = w_tfull;
+        if (warp == kRoleWarps) { p.debug[22] = dbg_ld; p.debug[23] = dbg_math; p.debug[24] = dbg_st; }
+    }
+}
+
+// PAIR: the kernel runs as clusters of two CTAs (on the two SMs of a TPC) and one tcgen05.mma.cta_group::2 instruction, issued by
+// the first CTA, multiplies the 2 x 128 pixels of both by the filter tile, each CTA holding half of the filter rows: twice the
+// arithmetic per issued instruction, half the weight bytes per SM in shared memory (more stages), and per SM only half of B to
+// read from shared memory per instruction.  Work unit of a pair: two consecutive pixel tiles x one filter tile.
+template <int KIND, int ACT, bool EXACT, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_constant__ ln_conv_umma_params p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int bk = p.bk, bn = p.bn, stages = p.stages;
-    // Weight-stationary mode (one filter tile, all of its weights fit): the B operand of every k-block is loaded once and
-    // stays in shared memory; the ring then carries activations only.  TMA cost is per row, so this removes a third of the
-    // load work of the layers with few channels.
-    const bool b_res = p.b_resident != 0;
-    const uint32_t a_bytes = 128u * bk, b_bytes = (uint32_t)bn * bk, stage_bytes = b_res ? a_bytes : a_bytes + b_bytes;
-    const uint32_t bres_base = smem_base;  // resident weights first (kblocks * b_bytes), then the ring
-    const uint32_t ring_base = smem_base + (b_res ? (uint32_t)(p.R * p.S * p.cblocks) * b_bytes : 0u);
-    // Row-shifted-box mode (3x3, stride 1): the activation ring holds a_stages sets of three boxes, the weight tiles follow in
-    // a ring of their own (none when they are resident).
-    const bool halo = p.halo != 0;
-    const uint32_t box_bytes = (uint32_t)p.box_bytes;
-    const uint32_t bring_base = ring_base + (uint32_t)p.a_stages * box_bytes;
-    const uint32_t bar_base = halo ? bring_base + (b_res ? 0u : (uint32_t)stages * b_bytes) : ring_base + (uint32_t)stages * stage_bytes;
-    // barrier block: full[8] empty[8] tfull[8] tempty[8] | resident weights | tmem slot | abort flag | afull[8] aempty[8]
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
-    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + b); };
-    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxStages + kMaxAccBufs + b); };
-    uint8_t* generic_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(generic_base + (bar_base - smem_base) + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 1));
-    const uint32_t bres_bar = bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs);
-    volatile int* abort_flag = (volatile int*)(tmem_slot + 2);
-    auto afull_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 4 + s); };
-    auto aempty_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxAccBufs + 4 + kMaxStages + s); };
-    const uint32_t tab_base = bar_base + 512u;  // the {multiplier, bias} pairs of all filter tiles, after the barrier block
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tmem_cols = 512u;  // the CTA owns the SM: take all of TMEM and keep 512/BN (at most 8) accumulator tiles in flight
-    const int nbuf = p.nbuf;
-
+#include "ln_conv_layout.inc"
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(full_bar(s), 1);
@@ -237,7 +680,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         }
         for (int b = 0; b < nbuf; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 4 * p.subs);  // the four warps of each group that drained one of the tile's column units
+            mbar_init(tempty_bar(b), (PAIR ? 8 : 4) * p.subs);  // the four warps of each group (of both CTAs of a pair) that drained one of the tile's column units
         }
         mbar_init(bres_bar, 1);
         for (int s = 0; s < kMaxStages; ++s) {
@@ -248,378 +691,37 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
-                     "r"(tmem_cols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {  // the same warp of both CTAs, same slot offset
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                         "r"(tmem_cols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                         "r"(tmem_cols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // the other CTA's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int kblocks = p.R * p.S * p.cblocks;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            long long w_empty = 0;
-            long long* pw = p.debug ? &w_empty : nullptr;
-            const long long t_start = kRoleTiming ? clock64() : 0;
-            if (b_res && (int)blockIdx.x < p.num_tiles) {
-                mbar_arrive_expect_tx(bres_bar, (uint32_t)kblocks * b_bytes);
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
-                    tma_load_2d(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, 0, bres_bar);
-                }
-            }
-            int astage = 0;
-            uint32_t aphase = 0;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
-                const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
-                const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
-                const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn;
-                if (halo) {
-                    // per channel block: box s, then (unless the weights are resident) the weight tiles of the taps that read it
-                    for (int c0 = 0; ok && c0 < p.cpad; c0 += bk)
-                        for (int s = 0; ok && s < 3; ++s) {
-                            if (!(ok = mbar_wait(aempty_bar(astage), aphase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
-                            mbar_arrive_expect_tx(afull_bar(astage), box_bytes);
-                            tma_load_4d(ring_base + (uint32_t)astage * box_bytes, &p.tmA[0], c0, ow0 - p.pad + s, oh0 - p.pad, n0, afull_bar(astage));
-                            if (++astage == p.a_stages) { astage = 0; aphase ^= 1u; }
-                            if (b_res) continue;
-                            for (int r = 0; r < 3; ++r) {
-                                if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
-                                mbar_arrive_expect_tx(full_bar(stage), b_bytes);
-                                tma_load_2d(bring_base + (uint32_t)stage * b_bytes, &p.tmB, (r * 3 + s) * p.cpad + c0, f0, full_bar(stage));
-                                if (++stage == stages) { stage = 0; phase ^= 1u; }
-                            }
-                        }
-                    continue;
-                }
-                // taps and channel blocks in nested loops: no division on this single thread's critical path
-                int wcol = 0;  // first column of the k-block in the weight matrix: tap * cpad + c0
-                for (int r = 0; ok && r < p.R; ++r) {
-                    for (int s = 0; ok && s < p.S; ++s) {
-                        int ty = r - p.pad, tx = s - p.pad, map = 0;
-                        if (p.stride == 2) {
-                            const int py = ty & 1, px = tx & 1;  // parity class of the tap (two's complement & 1 is non-negative)
-                            ty = (ty - py) >> 1;
-                            tx = (tx - px) >> 1;
-                            map = py * 2 + px;
-                        }
-                        for (int c0 = 0; c0 < p.cpad; c0 += bk, wcol += bk) {
-                            if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
-                            const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
-                            mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
-                            tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(stage));
-                            if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, wcol, f0, full_bar(stage));
-                            if (++stage == stages) { stage = 0; phase ^= 1u; }
-                        }
-                    }
-                }
-            }
-            if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            // instruction descriptor: accumulator type (bits 4-5: 1 = f32, 2 = s32), A and B types (bits 7-9, 10-12: 0 = E4M3 / binary16
-            // depending on the kind, 1 = signed 8-bit), N / 8 and M / 16; both operands K-major
-            const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((uint32_t)(bn >> 3) << 17) |
-                                   ((128u >> 4) << 24);
-            int stage = 0, astage = 0;
-            uint32_t phase = 0, aphase = 0;
-            int t = 0;
-            bool ok = true;
-            long long w_tempty = 0, w_full = 0, t_issue = 0, t_commit = 0;
-            long long* pw1 = p.debug ? &w_tempty : nullptr;
-            long long* pw2 = p.debug ? &w_full : nullptr;
-            const long long t_start = kRoleTiming ? clock64() : 0;
-            if (b_res && (int)blockIdx.x < p.num_tiles) ok = mbar_wait(bres_bar, 0u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT);
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
-                const int buf = t % nbuf;
-                const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
-                if (!(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw1))) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
-                if (halo) {
-                    uint32_t accumulate = 0;
-                    for (int cb = 0; ok && cb < p.cblocks; ++cb)
-                        for (int s = 0; ok && s < 3; ++s) {
-                            if (!(ok = mbar_wait(afull_bar(astage), aphase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
-                            tc_fence_after();
-                            const uint32_t sa = ring_base + (uint32_t)astage * box_bytes;
-                            for (int r = 0; r < 3; ++r) {
-                                uint32_t sb;
-                                if (b_res) sb = bres_base + (uint32_t)((r * 3 + s) * p.cblocks + cb) * b_bytes;
-                                else {
-                                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
-                                    tc_fence_after();
-                                    sb = bring_base + (uint32_t)stage * b_bytes;
-                                }
-                                // the box from its row r on: 128 consecutive rows of bk bytes, aligned to the 8-row swizzle pattern
-                                const uint64_t a_desc = make_smem_desc(sa + (uint32_t)(r * p.TW * bk), bk), b_desc = make_smem_desc(sb, bk);
-                                for (int k = 0; k < bk / 32; ++k) {
-                                    tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accumulate);
-                                    accumulate = 1u;
-                                }
-                                if (!b_res) {
-                                    tc_commit(empty_bar(stage));
-                                    if (++stage == stages) { stage = 0; phase ^= 1u; }
-                                }
-                            }
-                            if (!ok) break;
-                            tc_commit(aempty_bar(astage));  // arrives when the MMAs above have finished reading the box
-                            if (++astage == p.a_stages) { astage = 0; aphase ^= 1u; }
-                        }
-                    if (!ok) break;
-                    tc_commit(tfull_bar(buf));
-                    continue;
-                }
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
-                    const long long ti0 = kRoleTiming && p.debug ? clock64() : 0;
-                    tc_fence_after();
-                    const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
-                    const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + a_bytes, bk);
-                    for (int k = 0; k < bk / 32; ++k)  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
-                        tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
-                    const long long ti1 = kRoleTiming && p.debug ? clock64() : 0;
-                    tc_commit(empty_bar(stage));  // arrives when the MMAs above have finished reading this stage
-                    if (++stage == stages) { stage = 0; phase ^= 1u; }
-                    if (kRoleTiming && p.debug) { t_issue += ti1 - ti0; t_commit += clock64() - ti1; }
-                }
-                if (!ok) break;
-                tc_commit(tfull_bar(buf));
-            }
-            if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; p.debug[25] = t_issue; p.debug[26] = t_commit; }
-        }
+    if (warp < kRoleWarps) {
+        if ((warp & 1) == 0) conv_producer_role<PAIR>(p);
+        else conv_mma_role<KIND, PAIR>(p);
     } else {
-        // ------------------------------------------------------------------ epilogue
-        const int quad = warp & 3;          // TMEM lanes 32*quad .. 32*quad+31 are the ones this warp may read
-        // Which of the warps of the quadrant.  The work of the epilogue is cut into units: an accumulator tile is `subs` units of
-        // bn / subs columns each (subs > 1 when TMEM holds fewer tiles than there are groups, so that all groups stay busy), and
-        // group g takes the units u with u % groups == g, u counting (tile, sub) pairs in order.  Never more groups than
-        // nbuf * subs: a group that starts waiting for a unit of tile t has finished its unit `groups` earlier, a unit of tile
-        // t - ceil(groups / subs) or later; tiles are committed in order, so the previous use of this buffer (tile t - nbuf) has
-        // been accumulated in full, which a parity wait needs.
-        const int group = (warp - 2) >> 2;
-        const int subs = p.subs, sub_cols = bn / subs;
-        const int groups = nbuf * subs < kEpilogueGroups ? nbuf * subs : kEpilogueGroups;
-        const int row = quad * 32 + lane;
-        const int pw = row & (p.TW - 1), ph = (row >> p.log_tw) & (p.TH - 1), pn = row >> (p.log_tw + p.log_th);
-        constexpr bool kTranscendental = ACT == LN_ACT_MISH || ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC;
-        const bool folded = !EXACT && p.mb_folded != nullptr;
-        {
-            // the epilogue warps bring the table in while the producer and the MMA issuer fill the pipeline
-            const uint4* src = reinterpret_cast<const uint4*>(folded ? p.mb_folded : p.mb);
-            for (int i = (int)threadIdx.x - 64; i < p.tab_bytes / 16; i += 32 * kEpilogueWarps) {
-                const uint4 v = __ldg(src + i);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tab_base + 16u * (uint32_t)i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
-        }
-        int t = 0;
-        bool ok = true;
-        long long w_tfull = 0, dbg_ld = 0, dbg_math = 0, dbg_st = 0;
-        long long* pwe = p.debug ? &w_tfull : nullptr;
-        const long long t_start = kRoleTiming ? clock64() : 0;
-        int turn = 0;  // unit counter modulo groups
-        for (int tile = blockIdx.x; ok && group < groups && tile < p.num_tiles; tile += gridDim.x, ++t)
-        for (int sub = 0; ok && sub < subs; ++sub, turn = turn + 1 == groups ? 0 : turn + 1) {
-            if (turn != group) continue;  // another group of epilogue warps takes this unit
-            const int c_begin = sub * sub_cols, c_end = c_begin + sub_cols;
-            const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
-            const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
-            const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
-            const int ow = tw * p.TW + pw, oh = th * p.TH + ph, n = tn * p.TN + pn, f0 = tf * bn;
-            const bool valid = ow < p.OW && oh < p.OH && n < p.N;
-            const int buf = t % nbuf;
-            const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
-            if (!(ok = mbar_wait<false>(tfull_bar(buf), acc_phase, abort_flag, p.status, LN_STATUS_EPILOGUE_TIMEOUT, pwe))) break;
-            tc_fence_after();
-            const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * bn);
-            const int64_t pix = ((int64_t)n * p.OH + oh) * p.OW + ow;
-            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-                uint32_t acc[32];
-                const long long tq0 = kRoleTiming && p.debug ? clock64() : 0;
-                tmem_ld_32x32(taddr0 + (uint32_t)c0, acc);
-                const bool fast = KIND == LN_KIND_I8 && p.out_kind == LN_OUT_Q && f0 + c0 + 32 <= p.F;
-                // where this chunk goes: with pixel-group packing the columns [j * f_real, (j + 1) * f_real) are the filters of the
-                // j-th pixel of the row's group (f_real is a multiple of 32 then, so a chunk never straddles two pixels)
-                int64_t opix = pix;
-                int fo = f0 + c0;
-                if (p.pack > 1) {
-                    int j = 0;
-                    while (fo >= p.f_real) { fo -= p.f_real; ++j; }
-                    opix = pix * p.pack + j;
-                }
-                if (fast) {
-                    // ---- fast path: 32 valid filters, int8 out.  The {mult, bias} pairs (two per 16-byte load) are fetched
-                    // while the TMEM load is in flight, so the arithmetic below runs from registers only.
-                    const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);
-                    uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
-                    if (p.res != nullptr && valid) {  // residual codes of the fused shortcut, fetched while TMEM is read
-                        const uint4* rp = (const uint4*)((const uint8_t*)p.res + opix * p.res_pixel_stride + fo);
-                        r0 = __ldg(rp);
-                        r1 = __ldg(rp + 1);
-                    }
-                    tmem_ld_wait();
-                    const long long tq1 = kRoleTiming && p.debug ? clock64() : 0;
-                    if (kRoleTiming && p.debug) dbg_ld += tq1 - tq0;
-                    if (!valid) continue;
-                    uint32_t packed[8];
-                    // Four values at a time, each loop body fetching its own two table entries from shared memory, so that few
-                    // values are live at once (the kernel has to fit in 96 registers).
-                    if (folded) {
-                        // Fast mode, accumulators below 2^22.  Adding an accumulator to the bits of 1.5 * 2^23 gives the float
-                        // 1.5 * 2^23 + accumulator; the table holds {mult 2i, mult 2i+1, bias 2i, bias 2i+1} divided by the output scale,
-                        // the bias carrying -1.5 * 2^23 * mult, so one packed FMA yields two pre-activations in code units;
-                        // activation and rounding run in packed binary16.
-                        const __half2 kh = __float2half2_rn(p.sy_log2e), inv_h = __float2half2_rn(p.inv_sy);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
-                            float t0, t1, t2, t3;
-                            ffma2(t0, t1, __int_as_float(0x4B400000 + (int)acc[4 * j]), __int_as_float(0x4B400000 + (int)acc[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
-                            ffma2(t2, t3, __int_as_float(0x4B400000 + (int)acc[4 * j + 2]), __int_as_float(0x4B400000 + (int)acc[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
-                            packed[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
-                        }
-                    } else {
-                        // int32 -> f32: below 2^22 through the bits of 1.5 * 2^23 (two FMA-pipe instructions, exact); otherwise the
-                        // conversion unit, or, for the transcendental epilogues that need that unit for ex2 / rcp, an exact ALU sequence
-                        const bool small = p.small_acc != 0;
-                        const __half2 inv_h = __float2half2_rn(p.inv_sy);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
-                            float x[4];
-#pragma unroll
-                            for (int b = 0; b < 4; ++b) {
-                                const int a = (int)acc[4 * j + b];
-                                x[b] = small ? __fadd_rn(__int_as_float(0x4B400000 + a), -12582912.0f) : (kTranscendental ? i2f_alu(a) : __int2float_rn(a));
-                            }
-                            const float v0 = __fmaf_rn(x[0], ma.x, ma.y), v1 = __fmaf_rn(x[1], ma.z, ma.w), v2 = __fmaf_rn(x[2], mc.x, mc.y), v3 = __fmaf_rn(x[3], mc.z, mc.w);
-                            if (EXACT)
-                                packed[j] = pack4_low_bytes(quant_i8_magic(ln_epilogue_act<true>(ACT, v0), p.inv_sy), quant_i8_magic(ln_epilogue_act<true>(ACT, v1), p.inv_sy),
-                                                            quant_i8_magic(ln_epilogue_act<true>(ACT, v2), p.inv_sy), quant_i8_magic(ln_epilogue_act<true>(ACT, v3), p.inv_sy));
-                            else
-                                packed[j] = ln_h2_pack(ln_h2_act_quant<ACT>(v0, v1, inv_h), ln_h2_act_quant<ACT>(v2, v3, inv_h));
-                        }
-                    }
-                    if (p.res != nullptr) {
-                        // fused shortcut, the arithmetic of the stand-alone shortcut kernel applied to the codes just produced
-                        const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            uint32_t u[4];
-#pragma unroll
-                            for (int b = 0; b < 4; ++b) {
-                                float v = __fmul_rn(s8_to_float(packed[j], b), p.s_c);
-                                v = __fmaf_rn(s8_to_float(rw[j], b), p.s_res, v);
-                                u[b] = quant_i8_magic(v, p.inv_sy2);
-                            }
-                            packed[j] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
-                        }
-                    }
-                    const long long tq2 = kRoleTiming && p.debug ? clock64() : 0;
-                    uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
-                    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    if (kRoleTiming && p.debug) { dbg_math += tq2 - tq1; dbg_st += clock64() - tq2; }
-                    continue;
-                }
-                // ---- general path: f32 / raw-accumulator outputs (NCHW), FP8, and int8 chunks with fewer than 32 real filters.
-                // The {mult, bias} pairs come two per 16-byte load (the table is padded to a multiple of 32 filters).
-                const int nf = p.F - (f0 + c0);  // real filters from this chunk's first column on (32 or more: all of the chunk)
-                tmem_ld_wait();
-                if (!valid || nf <= 0) continue;
-                if (p.out_kind == LN_OUT_ACC) {
-                    // NCHW, raw accumulator bits (int32 or f32): consecutive lanes are consecutive pixels of a row, one plane per filter
-                    const int64_t plane = (int64_t)p.OH * p.OW;
-                    int32_t* o = (int32_t*)p.out + ((int64_t)n * p.F + (f0 + c0)) * plane + (int64_t)oh * p.OW + ow;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j, o += plane)
-                        if (j < nf) *o = (int32_t)acc[j];
-                    continue;
-                }
-                float a[32];
-                const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);  // (never the folded table: that one needs int8 output and full chunks)
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float4 mj = lds_f4(mtab + 16u * j);
-                    const float x0 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
-                    const float x1 = KIND == LN_KIND_I8 ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
-                    a[2 * j] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x0, mj.x, mj.y));
-                    a[2 * j + 1] = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(x1, mj.z, mj.w));
-                }
-                if (p.out_kind == LN_OUT_F32) {
-                    const int64_t plane = (int64_t)p.OH * p.OW;
-                    float* o = (float*)p.out + ((int64_t)n * p.F + (f0 + c0)) * plane + (int64_t)oh * p.OW + ow;  // NCHW
-#pragma unroll
-                    for (int j = 0; j < 32; ++j, o += plane)
-                        if (j < nf) *o = a[j];
-                } else {
-                    if (KIND == LN_KIND_F16) {
-                        // binary16 NHWC: 32 filters = 64 bytes per pixel, rounded to nearest even, infinities kept
-                        uint32_t hw[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const __half2 h = __floats2half2_rn(2 * j < nf ? a[2 * j] : 0.0f, 2 * j + 1 < nf ? a[2 * j + 1] : 0.0f);
-                            hw[j] = *reinterpret_cast<const uint32_t*>(&h);
-                        }
-                        uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + 2 * fo);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) o[j] = make_uint4(hw[4 * j], hw[4 * j + 1], hw[4 * j + 2], hw[4 * j + 3]);
-                        continue;
-                    }
-                    uint32_t packed[8];
-                    if (KIND == LN_KIND_I8) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            uint32_t v = 0;
-#pragma unroll
-                            for (int b = 0; b < 4; ++b) {
-                                const int q = 4 * j + b < nf ? ln_quant_i8(a[4 * j + b], p.inv_sy) : 0;
-                                v |= ((uint32_t)q & 0xFFu) << (8 * b);
-                            }
-                            packed[j] = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a[4 * j] * p.inv_sy, a[4 * j + 1] * p.inv_sy), __NV_SATFINITE, __NV_E4M3);
-                            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(a[4 * j + 2] * p.inv_sy, a[4 * j + 3] * p.inv_sy), __NV_SATFINITE, __NV_E4M3);
-                            uint32_t w = lo | (hi << 16);
-                            const int left = nf - 4 * j;  // codes of filters that do not exist are zero
-                            if (left < 4) w = left <= 0 ? 0u : (w & (0xFFFFFFFFu >> (8 * (4 - left))));
-                            packed[j] = w;
-                        }
-                    }
-                    uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
-                    o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(buf));
-        }
-        if (p.debug && blockIdx.x == 0 && lane == 0 && warp - 2 < 8) {  // (the counter block has room for eight epilogue warps)
-            p.debug[6 + 2 * (warp - 2)] = clock64() - t_start;
-            p.debug[7 + 2 * (warp - 2)] = w_tfull;
-            if (warp == 2) { p.debug[22] = dbg_ld; p.debug[23] = dbg_math; p.debug[24] = dbg_st; }
-        }
+        conv_epilogue_role<KIND, ACT, EXACT, PAIR>(p);
     }
 
     // ---------------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
+    // neither CTA of a pair leaves (or frees TMEM) while the other may still signal its barriers or run MMAs into its TMEM
+    if (PAIR) cluster_sync_all();
     if (*abort_flag && warp == 0 && lane == 0) {
         // a wait was abandoned: give copies that may still be in flight time to land before the CTA's
         // shared memory is handed to another CTA
@@ -628,46 +730,74 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
-// Tensor-pipe peak probe: one CTA per SM, one thread issuing tcgen05.mma (M = 128, N = 256, 32 bytes of K per instruction)
+#undef LN_FIRST_UNIT
+#undef LN_UNIT_STEP
+
+// Tensor-pipe peak probe: one CTA per SM, one thread issuing tcgen05.mma (M = 128, N = n, 32 bytes of K per instruction)
 // back to back on operand tiles that stay in shared memory, no loads, no epilogue.  What it measures is the rate the tensor
-// cores sustain when nothing else limits them: the denominator of the convolution's roofline.
-template <int KIND>
-__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status) {
+// cores sustain when nothing else limits them: the denominator of the convolution's roofline.  PAIR: clusters of two CTAs,
+// the first one issuing M = 256 instructions for both (tcgen05.mma.cta_group::2).
+template <int KIND, bool PAIR>
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int n, int variant, int* status) {
+    // variant bit 0: a tcgen05.commit (to a barrier nobody waits for) after every four instructions, as a pipelined main loop
+    // releases its stages; bit 1: the operands rotate through four tile sets instead of staying on one
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t a_base = base, b_base = base + 128u * 128u, bar = b_base + 256u * 128u;
+    constexpr uint32_t kSet = (128u + 256u) * 128u;  // one A tile + one B tile
+    const uint32_t sets = (variant & 2) ? 4u : 1u;
+    // variant bit 2: a second warp issues the same stream into its own accumulator (its own barriers, 16 bytes further on)
+    const uint32_t issuer = threadIdx.x >> 5;  // warp 0, and warp 1 when two warps issue
+    const uint32_t bar = base + sets * kSet + 16u * issuer, bar2 = bar + 8u;
     uint8_t* g = smem_raw + (base - smem_u32(smem_raw));
-    for (int i = threadIdx.x; i < (128 + 256) * 128 / 16; i += blockDim.x) reinterpret_cast<uint4*>(g)[i] = make_uint4(0u, 0u, 0u, 0u);
-    volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(g + (128 + 256) * 128 + 16);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(g + (128 + 256) * 128 + 32);
+    for (uint32_t i = threadIdx.x; i < sets * kSet / 16u; i += blockDim.x) reinterpret_cast<uint4*>(g)[i] = make_uint4(0u, 0u, 0u, 0u);
+    volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(g + sets * kSet + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(g + sets * kSet + 48);
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
     if (threadIdx.x == 0) {
-        mbar_init(bar, 1);
+        for (uint32_t i = 0; i < 4u; ++i) mbar_init(base + sets * kSet + 8u * i, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zeroed tiles are read through the async proxy
     if (threadIdx.x < 32) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)slot)), "r"(256u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)slot)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)slot)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();
     tc_fence_after();
-    const uint32_t tmem = *slot;
-    if (threadIdx.x == 0) {
-        const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
-        const uint64_t a_desc = make_smem_desc(a_base, 128), b_desc = make_smem_desc(b_base, 128);
+    const uint32_t tmem_all = *slot, tmem = tmem_all + 256u * issuer;
+    if ((threadIdx.x == 0 || ((variant & 4) && threadIdx.x == 32)) && rank == 0) {
+        const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | (((uint32_t)n >> 3) << 17) |
+                               (((PAIR ? 256u : 128u) >> 4) << 24);
         uint32_t phase = 0;
         bool ok = true;
         for (int it = 0; ok && it < iters; ++it) {
+            const uint32_t set = (uint32_t)it & (sets - 1u);
+            const uint64_t a_desc = make_smem_desc(base + set * kSet, 128), b_desc = make_smem_desc(base + set * kSet + 128u * 128u, 128);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) tc_mma<KIND>(tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((it | k) != 0));
+            for (int k = 0; k < 4; ++k) {
+                if (PAIR) tc_mma_pair<KIND>(tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((it | k) != 0));
+                else tc_mma<KIND>(tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((it | k) != 0));
+            }
+            if (variant & 1) {
+                if (PAIR) tc_commit_pair(bar2);
+                else tc_commit(bar2);
+            }
             if ((it & 63) == 63 || it + 1 == iters) {  // keep the queue bounded: wait for every 256th instruction
-                tc_commit(bar);
+                if (PAIR) tc_commit_pair(bar);
+                else tc_commit(bar);
                 ok = mbar_wait(bar, phase, abort_flag, status, LN_STATUS_MMA_TIMEOUT);
                 phase ^= 1u;
             }
@@ -675,24 +805,41 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();
     if (threadIdx.x < 32) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_all), "r"(512u) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_all), "r"(512u) : "memory");
     }
 }
 
 constexpr int kMaxDynamicSmem = 227 * 1024;
 constexpr uint32_t kMaxTableBytes = 32u * 1024u;  // {multiplier, bias} pairs of at most 4096 filters
 
-template <int KIND, bool EXACT>
+template <int KIND, bool EXACT, bool PAIR>
 cudaError_t launch_act(ln_ctx* ctx, const ln_conv_umma_params& p, int grid, size_t smem, cudaStream_t stream) {
 #define LN_LAUNCH_ACT(A)                                                                                             \
     case A: {                                                                                                        \
-        auto k = conv_umma_kernel<KIND, A, EXACT>;                                                                     \
+        auto k = conv_umma_kernel<KIND, A, EXACT, PAIR>;                                                               \
         if (!ctx->configured_kernels.count((const void*)k)) { /* once per kernel per context */                      \
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);   \
             if (e != cudaSuccess) return e;                                                                          \
             ctx->configured_kernels.insert((const void*)k);                                                          \
+        }                                                                                                            \
+        if (PAIR) { /* clusters of two CTAs: the pair shares one tcgen05.mma.cta_group::2 stream */                  \
+            cudaLaunchConfig_t cfg = {};                                                                             \
+            cfg.gridDim = dim3((unsigned)grid);                                                                      \
+            cfg.blockDim = dim3(kThreads);                                                                           \
+            cfg.dynamicSmemBytes = smem;                                                                             \
+            cfg.stream = stream;                                                                                     \
+            cudaLaunchAttribute attr[1];                                                                             \
+            attr[0].id = cudaLaunchAttributeClusterDimension;                                                        \
+            attr[0].val.clusterDim.x = 2;                                                                            \
+            attr[0].val.clusterDim.y = 1;                                                                            \
+            attr[0].val.clusterDim.z = 1;                                                                            \
+            cfg.attrs = attr;                                                                                        \
+            cfg.numAttrs = 1;                                                                                        \
+            return cudaLaunchKernelEx(&cfg, k, p);                                                                   \
         }                                                                                                            \
         k<<<grid, kThreads, smem, stream>>>(p);                                                                           \
         return cudaGetLastError();                                                                                   \
@@ -898,7 +1045,11 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         return ln_fail(ctx, LN_ERR_ARG, "tensor-core convolution: operands must be 16-byte aligned with 16-byte pixel strides");
     if (g.out_kind == LN_OUT_Q && ((((uintptr_t)g.out) & 15) || (g.out_pixel_stride & 15)))
         return ln_fail(ctx, LN_ERR_ARG, "tensor-core convolution: 8-bit output must be 16-byte aligned");
-    const int bk = g.cpad % 128 == 0 ? 128 : (g.cpad % 64 == 0 ? 64 : 32);
+    int bk = g.cpad % 128 == 0 ? 128 : (g.cpad % 64 == 0 ? 64 : 32);
+    if (const char* e = getenv("LN_CONV_BK")) {  // (A/B measurements: a smaller channel block, 64 or 32 bytes)
+        const int v = atoi(e);
+        if ((v == 64 || v == 32) && v < bk) bk = v;
+    }
     const int bn = ln_conv_choose_bn(g.F);  // filter tile: least padding, ties to the larger tile
     if (g.fpad % bn != 0) return ln_fail(ctx, LN_ERR_ARG, "tensor-core convolution: weights are padded to %d filters, tile needs a multiple of %d", g.fpad, bn);
     p.bk = bk; p.bn = bn;
@@ -907,6 +1058,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.OW = g.OW; p.OH = g.OH; p.N = g.N; p.F = g.F;
     p.fpad_used = (int)ln_round_up(g.F, 32);
     p.nbuf = 512 / bn > kMaxAccBufs ? kMaxAccBufs : 512 / bn;
+    p.pipes = 1;
     p.subs = p.nbuf >= kEpilogueGroups ? 1 : (kEpilogueGroups + p.nbuf - 1) / p.nbuf;  // column units per tile: keeps every epilogue group busy
     while (p.subs > 1 && (bn % (32 * p.subs)) != 0) --p.subs;
     p.small_acc = g.small_acc ? 1 : 0;
@@ -924,7 +1076,14 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     if (tab_bytes > kMaxTableBytes) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d filters exceed the %u the epilogue table holds", g.F, kMaxTableBytes / 8u);
     p.tab_bytes = (int)tab_bytes;
     const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u - tab_bytes;
-    if (allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
+    // CTA pairs (see conv_umma_kernel): LN_CONV_PAIR = 0 never, 2 wherever the kernel can, 1 / unset by the rule below.
+    const char* pair_env = getenv("LN_CONV_PAIR");
+    const int pair_mode = pair_env ? atoi(pair_env) : 0;
+    const int64_t pixel_tiles = (int64_t)((g.OW + p.TW - 1) / p.TW) * ((g.OH + p.TH - 1) / p.TH) * ((g.N + p.TN - 1) / p.TN);
+    const bool pair_possible = pixel_tiles >= 2 && ctx->sm_count >= 2;
+    const bool pair_rule = false;
+    p.pair = pair_possible && (pair_mode == 2 || (pair_mode == 1 && pair_rule)) ? 1 : 0;
+    if (!p.pair && allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
         int best_tw = 0, best_th = 0;
         int64_t best_tiles = -1;
         for (int lw = 3; lw <= 7; ++lw) {
@@ -948,6 +1107,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.tiles_n = (g.N + p.TN - 1) / p.TN;
     p.tiles_f = (int)(ln_round_up(g.F, bn) / bn);
     p.num_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_f;
+    p.num_units = p.pair ? ((p.tiles_w * p.tiles_h * p.tiles_n + 1) / 2) * p.tiles_f : p.num_tiles;
     auto magic = [](int d) { return ((1ull << 40) + (unsigned long long)d - 1) / (unsigned long long)d; };
     p.magic_f = magic(p.tiles_f); p.magic_w = magic(p.tiles_w); p.magic_h = magic(p.tiles_h);
     if ((long long)p.num_tiles * p.num_tiles >= (1ll << 40)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d tiles", p.num_tiles);
@@ -972,7 +1132,8 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         p.mb_folded = plan->aux_mbf;
     }
 
-    const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)bn * bk;  // all weights of one filter tile
+    const int b_rows = p.pair ? bn / 2 : bn;  // filter rows per CTA
+    const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)b_rows * bk;  // all weights of one filter tile (this CTA's part)
     // weights stay in shared memory when there is a single filter tile and they leave room for at least four activation stages
     if (p.halo) {
         const uint32_t box = (uint32_t)p.box_bytes, b_bytes = (uint32_t)bn * bk;
@@ -995,15 +1156,22 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         plan->smem = (size_t)a_stages * box + (p.b_resident ? b_total : (size_t)stages * b_bytes) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     } else {
     p.b_resident = (allow_resident && p.tiles_f == 1 && b_total + res_min_stages * 128u * bk <= smem_budget) ? 1 : 0;
-    const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + bn) * bk;
-    int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u)) / stage_bytes);
+    const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + b_rows) * bk;
+    int stages = (int)((((p.b_resident || p.pair) ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u)) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
+    // two producer / issuer pipelines when each gets at least two stages (LN_CONV_PIPES=1 switches them off, for A/B measurements)
+    const char* pipes_env = getenv("LN_CONV_PIPES");
+    if (!p.pair && stages >= 4 && !(pipes_env && atoi(pipes_env) == 1)) {
+        p.pipes = 2;
+        stages &= ~1;
+    }
     p.stages = stages;
     plan->smem = (size_t)stages * stage_bytes + (p.b_resident ? b_total : 0u) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     }
     plan->smem += tab_bytes;
-    plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
+    if (p.pair) plan->grid = 2 * (p.num_units < ctx->sm_count / 2 ? p.num_units : ctx->sm_count / 2);
+    else plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     plan->kind = g.kind;
 
     const CUtensorMapSwizzle swz = bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
@@ -1028,13 +1196,17 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     {
         cuuint64_t dims[2] = {(cuuint64_t)g.k * g.k * g.cpad, (cuuint64_t)g.fpad};
         cuuint64_t strides[1] = {(cuuint64_t)g.k * g.k * g.cpad};
-        cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)bn};
+        cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)b_rows};
         cuuint32_t estr[2] = {1, 1};
         CUresult r = ctx->encode_tiled(&p.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)g.w, dims, strides, box, estr,
                                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return ln_fail(ctx, LN_ERR_CUDA, "cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
     }
+    if (getenv("LN_DEBUG_PLAN"))
+        fprintf(stderr, "plan: bk %d bn %d stages %d nbuf %d subs %d b_res %d halo %d a_stages %d box %d TW %d TH %d TN %d tiles %d f %d grid %d smem %zu tab %d kind %d small %d folded %d pack %d%s\n",
+                p.bk, p.bn, p.stages, p.nbuf, p.subs, p.b_resident, p.halo, p.a_stages, p.box_bytes, p.TW, p.TH, p.TN, p.num_tiles, p.tiles_f, plan->grid,
+                plan->smem, p.tab_bytes, plan->kind, p.small_acc, p.mb_folded != nullptr, p.pack, (p.pair ? " pair" : (p.pipes == 2 ? " 2 pipelines" : "")));
     return LN_OK;
 }
 
@@ -1044,52 +1216,93 @@ int ln_conv_umma_make_mb(ln_ctx* ctx, const float* wscale_dev, const float* bias
     return LN_OK;
 }
 
-extern "C" int32_t ln_debug_mma_peak(ln_ctx* ctx, int32_t dtype, int32_t iters, float* tops) {
-    if (!ctx || !tops || iters < 1 || iters > (1 << 20)) return ln_fail(ctx, LN_ERR_ARG, "ln_debug_mma_peak: bad argument");
-    if (dtype != LN_Q8 && dtype != LN_F8 && dtype != LN_F16) return ln_fail(ctx, LN_ERR_ARG, "ln_debug_mma_peak: dtype must be LN_Q8, LN_F8 or LN_F16");
+static int32_t mma_peak_run(ln_ctx* ctx, int32_t dtype, int32_t n, int32_t pair_and_variant, int32_t iters, float* tops, const char* who) {
+    const int pair = pair_and_variant & 1, variant = (pair_and_variant >> 1) & 7;
+    if (!ctx || !tops || iters < 1 || iters > (1 << 20)) return ln_fail(ctx, LN_ERR_ARG, "%s: bad argument", who);
+    if (dtype != LN_Q8 && dtype != LN_F8 && dtype != LN_F16) return ln_fail(ctx, LN_ERR_ARG, "%s: dtype must be LN_Q8, LN_F8 or LN_F16", who);
+    if (n < 32 || n > 256 || n % 32 != 0) return ln_fail(ctx, LN_ERR_ARG, "%s: N must be a multiple of 32 up to 256", who);
     cudaSetDevice(ctx->device);
-    const size_t smem = (128 + 256) * 128 + 1024 + 64;
-    auto launch = [&](int n) {
-        if (dtype == LN_Q8) mma_peak_kernel<LN_KIND_I8><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, ctx->d_status);
-        else if (dtype == LN_F8) mma_peak_kernel<LN_KIND_F8><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, ctx->d_status);
-        else mma_peak_kernel<LN_KIND_F16><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, ctx->d_status);
+    const size_t smem = (size_t)((variant & 2) ? 4 : 1) * (128 + 256) * 128 + 1024 + 64;
+    const int grid = pair ? 2 * (ctx->sm_count / 2) : ctx->sm_count;
+    auto launch = [&](int it) -> cudaError_t {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = pair ? 2 : 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
         ctx->launches++;
+#define LN_PEAK(K)                                                                                                           \
+    {                                                                                                                        \
+        cudaError_t e;                                                                                                       \
+        if (pair) {                                                                                                          \
+            e = cudaFuncSetAttribute(mma_peak_kernel<K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+            if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, mma_peak_kernel<K, true>, it, (int)n, variant, ctx->d_status);         \
+        } else {                                                                                                             \
+            e = cudaFuncSetAttribute(mma_peak_kernel<K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+            if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, mma_peak_kernel<K, false>, it, (int)n, variant, ctx->d_status);        \
+        }                                                                                                                    \
+        return e;                                                                                                            \
+    }
+        if (dtype == LN_Q8) LN_PEAK(LN_KIND_I8)
+        if (dtype == LN_F8) LN_PEAK(LN_KIND_F8)
+        LN_PEAK(LN_KIND_F16)
+#undef LN_PEAK
     };
-    LN_CUDA(ctx, cudaFuncSetAttribute(mma_peak_kernel<LN_KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    LN_CUDA(ctx, cudaFuncSetAttribute(mma_peak_kernel<LN_KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    LN_CUDA(ctx, cudaFuncSetAttribute(mma_peak_kernel<LN_KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaEvent_t e0, e1;
     LN_CUDA(ctx, cudaEventCreate(&e0));
     LN_CUDA(ctx, cudaEventCreate(&e1));
-    launch(iters < 64 ? iters : 64);  // warm-up
+    cudaError_t e = launch(iters < 64 ? iters : 64);  // warm-up
     cudaEventRecord(e0, ctx->stream);
-    launch(iters);
+    if (e == cudaSuccess) e = launch(iters);
     cudaEventRecord(e1, ctx->stream);
-    cudaError_t e = cudaEventSynchronize(e1);
+    if (e == cudaSuccess) e = cudaEventSynchronize(e1);
     float ms = 0.0f;
     if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
-    if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "ln_debug_mma_peak: %s", cudaGetErrorString(e));
-    int rc = ln_check_status(ctx, "ln_debug_mma_peak");
+    if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "%s: %s", who, cudaGetErrorString(e));
+    int rc = ln_check_status(ctx, who);
     if (rc) return rc;
-    // one instruction is 128 x 256 x (32 bytes of K) multiply-adds: 32 per row pair for the 8-bit types, 16 for binary16
+    // one instruction is M x N x (32 bytes of K) multiply-adds: 32 per row pair for the 8-bit types, 16 for binary16
     const double k_elems = dtype == LN_F16 ? 16.0 : 32.0;
-    *tops = (float)(2.0 * 128.0 * 256.0 * k_elems * 4.0 * (double)iters * ctx->sm_count / (ms * 1e-3) / 1e12);
+    const double issuers = (pair ? grid / 2 : grid) * ((variant & 4) ? 2.0 : 1.0), m = pair ? 256.0 : 128.0;
+    *tops = (float)(2.0 * m * (double)n * k_elems * 4.0 * (double)iters * issuers / (ms * 1e-3) / 1e12);
     return LN_OK;
+}
+
+extern "C" int32_t ln_debug_mma_peak(ln_ctx* ctx, int32_t dtype, int32_t iters, float* tops) {
+    return mma_peak_run(ctx, dtype, 256, 0, iters, tops, "ln_debug_mma_peak");
+}
+
+extern "C" int32_t ln_debug_mma_peak_shape(ln_ctx* ctx, int32_t dtype, int32_t n, int32_t pair, int32_t iters, float* tops) {
+    return mma_peak_run(ctx, dtype, n, pair, iters, tops, "ln_debug_mma_peak_shape");
 }
 
 int ln_conv_umma_launch(ln_ctx* ctx, const ln_conv_umma_plan* plan) {
     cudaError_t e;
     const bool exact = ctx->exact_epilogue;
-    if (plan->kind == LN_KIND_I8)
-        e = exact ? launch_act<LN_KIND_I8, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
-                  : launch_act<LN_KIND_I8, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
-    else if (plan->kind == LN_KIND_F16)  // activations with the hardware ex2 / rcp (2 ulp of binary32, far below one binary16 rounding)
-        e = launch_act<LN_KIND_F16, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
-    else
-        e = exact ? launch_act<LN_KIND_F8, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
-                  : launch_act<LN_KIND_F8, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
+    const bool pair = plan->p.pair != 0;
+    if (plan->kind == LN_KIND_I8) {
+        if (pair) e = exact ? launch_act<LN_KIND_I8, true, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
+                            : launch_act<LN_KIND_I8, false, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
+        else e = exact ? launch_act<LN_KIND_I8, true, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
+                       : launch_act<LN_KIND_I8, false, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
+    } else if (plan->kind == LN_KIND_F16) {  // activations with the hardware ex2 / rcp (2 ulp of binary32, far below one binary16 rounding)
+        e = pair ? launch_act<LN_KIND_F16, false, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
+                 : launch_act<LN_KIND_F16, false, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
+    } else {
+        if (pair) e = exact ? launch_act<LN_KIND_F8, true, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
+                            : launch_act<LN_KIND_F8, false, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
+        else e = exact ? launch_act<LN_KIND_F8, true, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
+                       : launch_act<LN_KIND_F8, false, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
+    }
     ctx->launches++;
     if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "tensor-core convolution launch: %s", cudaGetErrorString(e));
     return LN_OK;
