@@ -28,9 +28,7 @@ struct ln_conv_umma_params {
     int OW, OH, N, F, fpad_used;
     int TW, TH, TN, log_tw, log_th;
     int tiles_w, tiles_h, tiles_n, tiles_f, num_tiles;
-    // CTA pairs (pair = 1): the kernel runs as clusters of two CTAs; a work unit is two consecutive pixel tiles x one filter tile,
-    // each CTA loading its own pixels and half of the filter rows.  num_units = work units (= num_tiles without pairs).
-    int pair, num_units;
+    int num_units;  // work units of the persistent loop (= num_tiles)
     // pipelines (1 or 2): producer / MMA-issuer pairs that take the CTA's tiles alternately, each with stages / pipes stages
     int pipes;
     unsigned long long magic_f, magic_w, magic_h;  // ceil(2^40 / tiles_*) for division-free tile decoding

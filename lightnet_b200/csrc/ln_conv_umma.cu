@@ -33,8 +33,9 @@ constexpr int kMaxStages = 8;
 #endif
 constexpr int kEpilogueGroups = LN_EPILOGUE_GROUPS;   // groups of four epilogue warps (one warp per TMEM lane quadrant); group g takes the tiles t with t % groups == g
 constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
-constexpr int kRoleWarps = 4;  // producer and MMA issuer of pipeline 0 (warps 0, 1) and of pipeline 1 (warps 2, 3)
-constexpr int kThreads = 32 * (kRoleWarps + kEpilogueWarps);
+// A kernel with PIPES producer / issuer pipelines has 2 * PIPES role warps (producer and MMA issuer of pipeline i are warps 2 i and
+// 2 i + 1) followed by the epilogue warps; an epilogue warp's TMEM lane quadrant is its warp index modulo 4 either way.
+constexpr int conv_threads(int pipes) { return 32 * (2 * pipes + kEpilogueWarps); }
 constexpr int kMaxAccBufs = 8;       // accumulator tiles in TMEM: 512 columns / BN, at most 8
 constexpr uint32_t kWaitLimit = 1u << 20;
 // Role timing of CTA 0 (clock reads in the hot loops) is compiled in only with -DLN_CONV_ROLE_TIMING.
@@ -99,37 +100,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  : "memory");
 }
 
-// CTA-pair forms (clusters of two CTAs, tcgen05 with cta_group::2).  The two CTAs of a pair each load their own operand tiles
-// into their own shared memory, but every load signals the barrier of the pair's first CTA, whose MMA thread issues the
-// instructions for both.  None of these loads is a multicast: every CTA fetches what it needs itself.
+// CTA-pair forms (clusters of two CTAs, tcgen05 with cta_group::2), used by the tensor-pipe probe only: measured, an M = 256
+// instruction over a pair takes as long as an M = 128 one on each SM, so pairs buy the convolution nothing.
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-// the address, in the shared::cluster window, of the first CTA's copy of a shared-memory variable of this CTA
-__device__ __forceinline__ uint32_t map_to_leader(uint32_t addr) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(addr));
-    return r;
-}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t leader_bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
-        "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
-    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-                 "l"(map), "r"(leader_bar), "r"(c0), "r"(c1)
-                 : "memory");
 }
 // arrives on the barrier at this shared-memory offset in both CTAs of the pair once all MMAs issued so far have finished
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
@@ -260,14 +240,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int bk) {
     return d;
 }
 
-// tile of CTA `rank` of a pair in work unit `unit`: pixel tile 2 * (unit / tiles_f) + rank of filter tile unit % tiles_f
-__device__ __forceinline__ int pair_tile(int unit, int rank, unsigned long long magic_f, int tiles_f) {
-    const int pp = fast_div(unit, magic_f), tf = unit - pp * tiles_f;
-    return (2 * pp + rank) * tiles_f + tf;
-}
 
-#define LN_FIRST_UNIT (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x)
-#define LN_UNIT_STEP (PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x)
+// (block index and grid size are read where they are used, not once at the top of the kernel: two values fewer to keep alive
+// across the roles' loops; hoisting them cost the layers with many channels 12 %)
+#define LN_FIRST_UNIT ((int)blockIdx.x)
+#define LN_UNIT_STEP ((int)gridDim.x)
 
     // Pipelines: issuing one tcgen05.mma costs its thread about 100 cycles whatever the instruction's size, so one issuing
     // thread keeps the tensor pipe busy only with N = 256 instructions.  With two pipelines (pipes = 2) the CTA's tiles alternate
@@ -276,7 +253,7 @@ __device__ __forceinline__ int pair_tile(int unit, int rank, unsigned long long 
     // order, as before.
 // The roles are inlined into the kernel: as functions of their own they would read the parameters through a pointer instead of
 // as constant-bank operands, which costs the single-thread loops 20 to 50 % (measured).
-template <bool PAIR>
+template <int PIPES>
 __device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p) {
 #include "ln_conv_layout.inc"
     // ------------------------------------------------------------------ TMA producer
@@ -288,21 +265,20 @@ __device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p)
         long long* pw = p.debug ? &w_empty : nullptr;
         const long long t_start = kRoleTiming ? clock64() : 0;
         if (b_res && pipe == 0 && LN_FIRST_UNIT < p.num_units) {
-            if (rank == 0) mbar_arrive_expect_tx(bres_bar, (PAIR ? 2u : 1u) * (uint32_t)kblocks * b_bytes);
+            mbar_arrive_expect_tx(bres_bar, (uint32_t)kblocks * b_bytes);
             for (int kb = 0; kb < kblocks; ++kb) {
                 const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
-                if (PAIR) tma_load_2d_pair(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, (int)rank * b_rows, lead_base + (bres_bar - bar_base));
-                else tma_load_2d(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, 0, bres_bar);
+                tma_load_2d(bres_base + (uint32_t)kb * b_bytes, &p.tmB, tap * p.cpad + c0, 0, bres_bar);
             }
         }
         int astage = 0;
         uint32_t aphase = 0;
         for (int unit = LN_FIRST_UNIT + pipe * LN_UNIT_STEP; ok && unit < p.num_units; unit += pipes * LN_UNIT_STEP) {
-            const int tile = PAIR ? pair_tile(unit, (int)rank, p.magic_f, p.tiles_f) : unit;
+            const int tile = unit;
             const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
             const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
             const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
-            const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn + (int)rank * b_rows;
+            const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn;
             if (halo) {
                 // per channel block: box s, then (unless the weights are resident) the weight tiles of the taps that read it
                 for (int c0 = 0; ok && c0 < p.cpad; c0 += bk)
@@ -335,19 +311,9 @@ __device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p)
                     for (int c0 = 0; c0 < p.cpad; c0 += bk, wcol += bk) {
                         if (!(ok = mbar_wait(empty_bar(s0 + stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
                         const uint32_t sa = ring_base + (uint32_t)(s0 + stage) * stage_bytes;
-                        if (PAIR) {
-                            // the first CTA's barrier counts the bytes of both CTAs; the other CTA's loads may land before it is
-                            // armed (the transaction count goes negative for a moment), never in an earlier phase: this stage
-                            // was released by MMAs that had seen that phase complete
-                            const uint32_t lead_full = lead_base + (full_bar(s0 + stage) - bar_base);
-                            if (rank == 0) mbar_arrive_expect_tx(full_bar(s0 + stage), 2u * stage_bytes);
-                            tma_load_4d_pair(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, lead_full);
-                            if (!b_res) tma_load_2d_pair(sa + a_bytes, &p.tmB, wcol, f0, lead_full);
-                        } else {
-                            mbar_arrive_expect_tx(full_bar(s0 + stage), stage_bytes);
-                            tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(s0 + stage));
-                            if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, wcol, f0, full_bar(s0 + stage));
-                        }
+                        mbar_arrive_expect_tx(full_bar(s0 + stage), stage_bytes);
+                        tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(s0 + stage));
+                        if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, wcol, f0, full_bar(s0 + stage));
                         if (++stage == spp) { stage = 0; phase ^= 1u; }
                     }
                 }
@@ -357,16 +323,16 @@ __device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p)
     }
 }
 
-template <int KIND, bool PAIR>
+template <int KIND, int PIPES>
 __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
 #include "ln_conv_layout.inc"
     const uint32_t tmem_base = *tmem_slot;
-    // ------------------------------------------------------------------ MMA issuer (of a pair: the first CTA's)
-    if (lane == 0 && rank == 0 && pipe < pipes) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && pipe < pipes) {
         // instruction descriptor: accumulator type (bits 4-5: 1 = f32, 2 = s32), A and B types (bits 7-9, 10-12: 0 = E4M3 / binary16
         // depending on the kind, 1 = signed 8-bit), N / 8 and M / 16; both operands K-major
         const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((uint32_t)(bn >> 3) << 17) |
-                               (((PAIR ? 256u : 128u) >> 4) << 24);
+                               ((128u >> 4) << 24);
         int stage = 0, astage = 0;
         uint32_t phase = 0, aphase = 0;
         int t = pipe;  // the CTA's tile counter: pipeline i takes the tiles t = i, i + pipes, ...
@@ -423,25 +389,21 @@ __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
                 const uint32_t sa = ring_base + (uint32_t)(s0 + stage) * stage_bytes;
                 const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + a_bytes, bk);
                 for (int k = 0; k < bk / 32; ++k) {  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
-                    if (PAIR) tc_mma_pair<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
-                    else tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
+                    tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
                 }
                 const long long ti1 = kRoleTiming && p.debug ? clock64() : 0;
-                // arrives (in both CTAs of a pair) when the MMAs above have finished reading this stage
-                if (PAIR) tc_commit_pair(empty_bar(s0 + stage));
-                else tc_commit(empty_bar(s0 + stage));
+                tc_commit(empty_bar(s0 + stage));  // arrives when the MMAs above have finished reading this stage
                 if (++stage == spp) { stage = 0; phase ^= 1u; }
                 if (kRoleTiming && p.debug) { t_issue += ti1 - ti0; t_commit += clock64() - ti1; }
             }
             if (!ok) break;
-            if (PAIR) tc_commit_pair(tfull_bar(buf));
-            else tc_commit(tfull_bar(buf));
+            tc_commit(tfull_bar(buf));
         }
         if (kRoleTiming && p.debug && blockIdx.x == 0 && pipe == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; p.debug[25] = t_issue; p.debug[26] = t_commit; }
     }
 }
 
-template <int KIND, int ACT, bool EXACT, bool PAIR>
+template <int KIND, int ACT, bool EXACT, int PIPES>
 __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p) {
 #include "ln_conv_layout.inc"
     const uint32_t tmem_base = *tmem_slot;
@@ -453,7 +415,7 @@ __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p)
     // nbuf * subs: a group that starts waiting for a unit of tile t has finished its unit `groups` earlier, a unit of tile
     // t - ceil(groups / subs) or later; tiles are committed in order, so the previous use of this buffer (tile t - nbuf) has
     // been accumulated in full, which a parity wait needs.
-    const int group = (warp - kRoleWarps) >> 2;
+    const int group = (warp - 2 * PIPES) >> 2;
     const int subs = p.subs, sub_cols = bn / subs;
     const int groups = nbuf * subs < kEpilogueGroups ? nbuf * subs : kEpilogueGroups;
     const int row = quad * 32 + lane;
@@ -463,7 +425,7 @@ __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p)
     {
         // the epilogue warps bring the table in while the producer and the MMA issuer fill the pipeline
         const uint4* src = reinterpret_cast<const uint4*>(folded ? p.mb_folded : p.mb);
-        for (int i = (int)threadIdx.x - 32 * kRoleWarps; i < p.tab_bytes / 16; i += 32 * kEpilogueWarps) {
+        for (int i = (int)threadIdx.x - 64 * PIPES; i < p.tab_bytes / 16; i += 32 * kEpilogueWarps) {
             const uint4 v = __ldg(src + i);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tab_base + 16u * (uint32_t)i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
         }
@@ -478,7 +440,7 @@ __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p)
     for (int unit = LN_FIRST_UNIT; ok && group < groups && unit < p.num_units; unit += LN_UNIT_STEP, ++t)
     for (int sub = 0; ok && sub < subs; ++sub, turn = turn + 1 == groups ? 0 : turn + 1) {
         if (turn != group) continue;  // another group of epilogue warps takes this unit
-        const int tile = PAIR ? pair_tile(unit, (int)rank, p.magic_f, p.tiles_f) : unit;
+        const int tile = unit;
         const int c_begin = sub * sub_cols, c_end = c_begin + sub_cols;
         const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
         const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
@@ -654,24 +616,19 @@ __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p)
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-            if (PAIR) mbar_arrive_cluster(lead_base + (tempty_bar(buf) - bar_base));  // the MMA issuer waits for both CTAs
-            else mbar_arrive(tempty_bar(buf));
-        }
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
     }
-    if (p.debug && blockIdx.x == 0 && lane == 0 && warp - kRoleWarps < 8) {  // (the counter block has room for eight epilogue warps)
-        p.debug[6 + 2 * (warp - kRoleWarps)] = clock64() - t_start;
-        p.debug[7 + 2 * (warp - kRoleWarps)] = w_tfull;
-        if (warp == kRoleWarps) { p.debug[22] = dbg_ld; p.debug[23] = dbg_math; p.debug[24] = dbg_st; }
+    if (p.debug && blockIdx.x == 0 && lane == 0 && warp - 2 * PIPES < 8) {  // (the counter block has room for eight epilogue warps)
+        p.debug[6 + 2 * (warp - 2 * PIPES)] = clock64() - t_start;
+        p.debug[7 + 2 * (warp - 2 * PIPES)] = w_tfull;
+        if (warp == 2 * PIPES) { p.debug[22] = dbg_ld; p.debug[23] = dbg_math; p.debug[24] = dbg_st; }
     }
 }
 
-// PAIR: the kernel runs as clusters of two CTAs (on the two SMs of a TPC) and one tcgen05.mma.cta_group::2 instruction, issued by
-// the first CTA, multiplies the 2 x 128 pixels of both by the filter tile, each CTA holding half of the filter rows: twice the
-// arithmetic per issued instruction, half the weight bytes per SM in shared memory (more stages), and per SM only half of B to
-// read from shared memory per instruction.  Work unit of a pair: two consecutive pixel tiles x one filter tile.
-template <int KIND, int ACT, bool EXACT, bool PAIR>
-__global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_constant__ ln_conv_umma_params p) {
+// PIPES (1 or 2): the number of producer / issuer pipelines, a compile-time constant so that the single-pipeline kernel carries
+// none of the other's index arithmetic in its single-thread loops.
+template <int KIND, int ACT, bool EXACT, int PIPES>
+__global__ void __launch_bounds__(conv_threads(PIPES), 1) conv_umma_kernel(const __grid_constant__ ln_conv_umma_params p) {
 #include "ln_conv_layout.inc"
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -680,7 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         }
         for (int b = 0; b < nbuf; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), (PAIR ? 8 : 4) * p.subs);  // the four warps of each group (of both CTAs of a pair) that drained one of the tile's column units
+            mbar_init(tempty_bar(b), 4 * p.subs);  // the four warps of each group that drained one of the tile's column units
         }
         mbar_init(bres_bar, 1);
         for (int s = 0; s < kMaxStages; ++s) {
@@ -691,37 +648,27 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        if (PAIR) {  // the same warp of both CTAs, same slot offset
-            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
-                         "r"(tmem_cols)
-                         : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-        } else {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
-                         "r"(tmem_cols)
-                         : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        }
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                     "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
-    if (PAIR) cluster_sync_all();  // the other CTA's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
 
-    if (warp < kRoleWarps) {
-        if ((warp & 1) == 0) conv_producer_role<PAIR>(p);
-        else conv_mma_role<KIND, PAIR>(p);
+    if (warp < 2 * PIPES) {
+        if ((warp & 1) == 0) conv_producer_role<PIPES>(p);
+        else conv_mma_role<KIND, PIPES>(p);
     } else {
-        conv_epilogue_role<KIND, ACT, EXACT, PAIR>(p);
+        conv_epilogue_role<KIND, ACT, EXACT, PIPES>(p);
     }
 
     // ---------------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    // neither CTA of a pair leaves (or frees TMEM) while the other may still signal its barriers or run MMAs into its TMEM
-    if (PAIR) cluster_sync_all();
     if (*abort_flag && warp == 0 && lane == 0) {
         // a wait was abandoned: give copies that may still be in flight time to land before the CTA's
         // shared memory is handed to another CTA
@@ -730,8 +677,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_umma_kernel(const __grid_con
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
-        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
@@ -816,32 +762,17 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int n, int 
 constexpr int kMaxDynamicSmem = 227 * 1024;
 constexpr uint32_t kMaxTableBytes = 32u * 1024u;  // {multiplier, bias} pairs of at most 4096 filters
 
-template <int KIND, bool EXACT, bool PAIR>
+template <int KIND, bool EXACT, int PIPES>
 cudaError_t launch_act(ln_ctx* ctx, const ln_conv_umma_params& p, int grid, size_t smem, cudaStream_t stream) {
 #define LN_LAUNCH_ACT(A)                                                                                             \
     case A: {                                                                                                        \
-        auto k = conv_umma_kernel<KIND, A, EXACT, PAIR>;                                                               \
+        auto k = conv_umma_kernel<KIND, A, EXACT, PIPES>;                                                              \
         if (!ctx->configured_kernels.count((const void*)k)) { /* once per kernel per context */                      \
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);   \
             if (e != cudaSuccess) return e;                                                                          \
             ctx->configured_kernels.insert((const void*)k);                                                          \
         }                                                                                                            \
-        if (PAIR) { /* clusters of two CTAs: the pair shares one tcgen05.mma.cta_group::2 stream */                  \
-            cudaLaunchConfig_t cfg = {};                                                                             \
-            cfg.gridDim = dim3((unsigned)grid);                                                                      \
-            cfg.blockDim = dim3(kThreads);                                                                           \
-            cfg.dynamicSmemBytes = smem;                                                                             \
-            cfg.stream = stream;                                                                                     \
-            cudaLaunchAttribute attr[1];                                                                             \
-            attr[0].id = cudaLaunchAttributeClusterDimension;                                                        \
-            attr[0].val.clusterDim.x = 2;                                                                            \
-            attr[0].val.clusterDim.y = 1;                                                                            \
-            attr[0].val.clusterDim.z = 1;                                                                            \
-            cfg.attrs = attr;                                                                                        \
-            cfg.numAttrs = 1;                                                                                        \
-            return cudaLaunchKernelEx(&cfg, k, p);                                                                   \
-        }                                                                                                            \
-        k<<<grid, kThreads, smem, stream>>>(p);                                                                           \
+        k<<<grid, conv_threads(PIPES), smem, stream>>>(p);                                                                           \
         return cudaGetLastError();                                                                                   \
     }
     switch (p.act) {
@@ -1076,14 +1007,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     if (tab_bytes > kMaxTableBytes) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d filters exceed the %u the epilogue table holds", g.F, kMaxTableBytes / 8u);
     p.tab_bytes = (int)tab_bytes;
     const uint32_t smem_budget = (uint32_t)kMaxDynamicSmem - 1024u - 512u - tab_bytes;
-    // CTA pairs (see conv_umma_kernel): LN_CONV_PAIR = 0 never, 2 wherever the kernel can, 1 / unset by the rule below.
-    const char* pair_env = getenv("LN_CONV_PAIR");
-    const int pair_mode = pair_env ? atoi(pair_env) : 0;
-    const int64_t pixel_tiles = (int64_t)((g.OW + p.TW - 1) / p.TW) * ((g.OH + p.TH - 1) / p.TH) * ((g.N + p.TN - 1) / p.TN);
-    const bool pair_possible = pixel_tiles >= 2 && ctx->sm_count >= 2;
-    const bool pair_rule = false;
-    p.pair = pair_possible && (pair_mode == 2 || (pair_mode == 1 && pair_rule)) ? 1 : 0;
-    if (!p.pair && allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
+    if (allow_halo && g.k == 3 && g.stride == 1 && pack == 1 && g.out_kind != LN_OUT_F32 && g.cpad <= 64) {
         int best_tw = 0, best_th = 0;
         int64_t best_tiles = -1;
         for (int lw = 3; lw <= 7; ++lw) {
@@ -1107,7 +1031,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.tiles_n = (g.N + p.TN - 1) / p.TN;
     p.tiles_f = (int)(ln_round_up(g.F, bn) / bn);
     p.num_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_f;
-    p.num_units = p.pair ? ((p.tiles_w * p.tiles_h * p.tiles_n + 1) / 2) * p.tiles_f : p.num_tiles;
+    p.num_units = p.num_tiles;
     auto magic = [](int d) { return ((1ull << 40) + (unsigned long long)d - 1) / (unsigned long long)d; };
     p.magic_f = magic(p.tiles_f); p.magic_w = magic(p.tiles_w); p.magic_h = magic(p.tiles_h);
     if ((long long)p.num_tiles * p.num_tiles >= (1ll << 40)) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: %d tiles", p.num_tiles);
@@ -1132,7 +1056,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         p.mb_folded = plan->aux_mbf;
     }
 
-    const int b_rows = p.pair ? bn / 2 : bn;  // filter rows per CTA
+    const int b_rows = bn;
     const uint32_t b_total = (uint32_t)(g.k * g.k * (g.cpad / bk)) * (uint32_t)b_rows * bk;  // all weights of one filter tile (this CTA's part)
     // weights stay in shared memory when there is a single filter tile and they leave room for at least four activation stages
     if (p.halo) {
@@ -1157,12 +1081,18 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     } else {
     p.b_resident = (allow_resident && p.tiles_f == 1 && b_total + res_min_stages * 128u * bk <= smem_budget) ? 1 : 0;
     const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + b_rows) * bk;
-    int stages = (int)((((p.b_resident || p.pair) ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u)) / stage_bytes);
+    int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u)) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
-    // two producer / issuer pipelines when each gets at least two stages (LN_CONV_PIPES=1 switches them off, for A/B measurements)
+    // Two producer / issuer pipelines where one issuing thread cannot keep the tensor pipe busy: filter tiles of at most 128 (an
+    // instruction costs its thread about 100 cycles whatever N is, the tensor pipe 64 cycles at N = 128) with enough instructions
+    // per tile for that to matter, and at least two stages for each pipeline.  Measured on 3x3 C128 -> K128 at 76x76: 104 -> 84 us;
+    // 3x3 stride 2 C64 -> K128 at 304x304: 88 -> 61 us; with 256-filter tiles the two stages per pipeline that fit lose 6 %.
+    // LN_CONV_PIPES = 1 / 2 forces one / two (for A/B measurements).
     const char* pipes_env = getenv("LN_CONV_PIPES");
-    if (!p.pair && stages >= 4 && !(pipes_env && atoi(pipes_env) == 1)) {
+    const int pipes_forced = pipes_env ? atoi(pipes_env) : 0;
+    const bool pipes_rule = bn <= 128 && g.k * g.k * (g.cpad / 32) >= 16;
+    if (stages >= 4 && pipes_forced != 1 && (pipes_rule || pipes_forced == 2)) {
         p.pipes = 2;
         stages &= ~1;
     }
@@ -1170,8 +1100,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     plan->smem = (size_t)stages * stage_bytes + (p.b_resident ? b_total : 0u) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     }
     plan->smem += tab_bytes;
-    if (p.pair) plan->grid = 2 * (p.num_units < ctx->sm_count / 2 ? p.num_units : ctx->sm_count / 2);
-    else plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
+    plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     plan->kind = g.kind;
 
     const CUtensorMapSwizzle swz = bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
@@ -1206,7 +1135,7 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     if (getenv("LN_DEBUG_PLAN"))
         fprintf(stderr, "plan: bk %d bn %d stages %d nbuf %d subs %d b_res %d halo %d a_stages %d box %d TW %d TH %d TN %d tiles %d f %d grid %d smem %zu tab %d kind %d small %d folded %d pack %d%s\n",
                 p.bk, p.bn, p.stages, p.nbuf, p.subs, p.b_resident, p.halo, p.a_stages, p.box_bytes, p.TW, p.TH, p.TN, p.num_tiles, p.tiles_f, plan->grid,
-                plan->smem, p.tab_bytes, plan->kind, p.small_acc, p.mb_folded != nullptr, p.pack, (p.pair ? " pair" : (p.pipes == 2 ? " 2 pipelines" : "")));
+                plan->smem, p.tab_bytes, plan->kind, p.small_acc, p.mb_folded != nullptr, p.pack, (p.pipes == 2 ? " 2 pipelines" : ""));
     return LN_OK;
 }
 
@@ -1288,21 +1217,12 @@ extern "C" int32_t ln_debug_mma_peak_shape(ln_ctx* ctx, int32_t dtype, int32_t n
 int ln_conv_umma_launch(ln_ctx* ctx, const ln_conv_umma_plan* plan) {
     cudaError_t e;
     const bool exact = ctx->exact_epilogue;
-    const bool pair = plan->p.pair != 0;
-    if (plan->kind == LN_KIND_I8) {
-        if (pair) e = exact ? launch_act<LN_KIND_I8, true, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
-                            : launch_act<LN_KIND_I8, false, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
-        else e = exact ? launch_act<LN_KIND_I8, true, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
-                       : launch_act<LN_KIND_I8, false, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
-    } else if (plan->kind == LN_KIND_F16) {  // activations with the hardware ex2 / rcp (2 ulp of binary32, far below one binary16 rounding)
-        e = pair ? launch_act<LN_KIND_F16, false, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
-                 : launch_act<LN_KIND_F16, false, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
-    } else {
-        if (pair) e = exact ? launch_act<LN_KIND_F8, true, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
-                            : launch_act<LN_KIND_F8, false, true>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
-        else e = exact ? launch_act<LN_KIND_F8, true, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream)
-                       : launch_act<LN_KIND_F8, false, false>(ctx, plan->p, plan->grid, plan->smem, ctx->stream);
-    }
+    const bool two = plan->p.pipes == 2;
+#define LN_LAUNCH_KIND(K, X) (two ? launch_act<K, X, 2>(ctx, plan->p, plan->grid, plan->smem, ctx->stream) : launch_act<K, X, 1>(ctx, plan->p, plan->grid, plan->smem, ctx->stream))
+    if (plan->kind == LN_KIND_I8) e = exact ? LN_LAUNCH_KIND(LN_KIND_I8, true) : LN_LAUNCH_KIND(LN_KIND_I8, false);
+    else if (plan->kind == LN_KIND_F16) e = LN_LAUNCH_KIND(LN_KIND_F16, false);  // activations with the hardware ex2 / rcp (2 ulp of binary32, far below one binary16 rounding)
+    else e = exact ? LN_LAUNCH_KIND(LN_KIND_F8, true) : LN_LAUNCH_KIND(LN_KIND_F8, false);
+#undef LN_LAUNCH_KIND
     ctx->launches++;
     if (e != cudaSuccess) return ln_fail(ctx, LN_ERR_CUDA, "tensor-core convolution launch: %s", cudaGetErrorString(e));
     return LN_OK;
