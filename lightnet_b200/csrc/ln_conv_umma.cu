@@ -246,25 +246,27 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int bk) {
 #define LN_FIRST_UNIT ((int)blockIdx.x)
 #define LN_UNIT_STEP ((int)gridDim.x)
 
-    // Pipelines: issuing one tcgen05.mma costs its thread about 100 cycles whatever the instruction's size, so one issuing
-    // thread keeps the tensor pipe busy only with N = 256 instructions.  With two pipelines (pipes = 2) the CTA's tiles alternate
-    // between two producer / issuer pairs, each with its own half of the stage ring and its own accumulator buffers (tile t uses
-    // buffer t % nbuf, nbuf is even); the two instruction streams overlap in the tensor pipe.  The epilogue takes the tiles in
-    // order, as before.
+// Pipelines: issuing one tcgen05.mma costs its thread about 100 cycles whatever the instruction's size (the tensor pipe needs 64
+// for N = 128, 136 for N = 256), and the waits and commits around every k-block cost the thread as much again, so one issuing
+// thread leaves the tensor pipe idle half of the time or more.  With two pipelines (PIPES = 2) the CTA takes its tiles two at
+// a time: a stage holds the activation tiles of both and the weight tile they share (consecutive tiles of a CTA have the same
+// filter tile: the grid is a multiple of tiles_f), one producer fills it, and two issuing threads (warps 1 and 2) each multiply
+// their own activation tile by the shared weights into their own accumulator buffer (tile t uses buffer t % nbuf, nbuf is
+// even).  The two instruction streams overlap in the tensor pipe.  The epilogue takes the tiles in order, as before.
 // The roles are inlined into the kernel: as functions of their own they would read the parameters through a pointer instead of
 // as constant-bank operands, which costs the single-thread loops 20 to 50 % (measured).
 template <int PIPES>
 __device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p) {
 #include "ln_conv_layout.inc"
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && pipe < pipes) {
+    if (lane == 0) {
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
         long long w_empty = 0;
         long long* pw = p.debug ? &w_empty : nullptr;
         const long long t_start = kRoleTiming ? clock64() : 0;
-        if (b_res && pipe == 0 && LN_FIRST_UNIT < p.num_units) {
+        if (b_res && LN_FIRST_UNIT < p.num_units) {
             mbar_arrive_expect_tx(bres_bar, (uint32_t)kblocks * b_bytes);
             for (int kb = 0; kb < kblocks; ++kb) {
                 const int tap = kb / p.cblocks, c0 = (kb - tap * p.cblocks) * bk;
@@ -273,12 +275,21 @@ __device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p)
         }
         int astage = 0;
         uint32_t aphase = 0;
-        for (int unit = LN_FIRST_UNIT + pipe * LN_UNIT_STEP; ok && unit < p.num_units; unit += pipes * LN_UNIT_STEP) {
+        for (int unit = LN_FIRST_UNIT; ok && unit < p.num_units; unit += PIPES * LN_UNIT_STEP) {
             const int tile = unit;
             const int q1 = fast_div(tile, p.magic_f), tf = tile - q1 * p.tiles_f;
             const int q2 = fast_div(q1, p.magic_w), tw = q1 - q2 * p.tiles_w;
             const int tn = fast_div(q2, p.magic_h), th = q2 - tn * p.tiles_h;
             const int ow0 = tw * p.TW, oh0 = th * p.TH, n0 = tn * p.TN, f0 = tf * bn;
+            // two pipelines: the CTA's next tile as well (the same filter tile: the grid is a multiple of tiles_f), unless this was the last
+            const bool has1 = PIPES == 2 && unit + LN_UNIT_STEP < p.num_units;
+            int ow1 = 0, oh1 = 0, n1 = 0;
+            if (has1) {
+                const int u1 = fast_div(unit + LN_UNIT_STEP, p.magic_f);
+                const int u2 = fast_div(u1, p.magic_w), uw = u1 - u2 * p.tiles_w;
+                const int un = fast_div(u2, p.magic_h), uh = u2 - un * p.tiles_h;
+                ow1 = uw * p.TW; oh1 = uh * p.TH; n1 = un * p.TN;
+            }
             if (halo) {
                 // per channel block: box s, then (unless the weights are resident) the weight tiles of the taps that read it
                 for (int c0 = 0; ok && c0 < p.cpad; c0 += bk)
@@ -309,17 +320,19 @@ __device__ __forceinline__ void conv_producer_role(const ln_conv_umma_params& p)
                         map = py * 2 + px;
                     }
                     for (int c0 = 0; c0 < p.cpad; c0 += bk, wcol += bk) {
-                        if (!(ok = mbar_wait(empty_bar(s0 + stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
-                        const uint32_t sa = ring_base + (uint32_t)(s0 + stage) * stage_bytes;
-                        mbar_arrive_expect_tx(full_bar(s0 + stage), stage_bytes);
-                        tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(s0 + stage));
-                        if (!b_res) tma_load_2d(sa + a_bytes, &p.tmB, wcol, f0, full_bar(s0 + stage));
-                        if (++stage == spp) { stage = 0; phase ^= 1u; }
+                        if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, LN_STATUS_PRODUCER_TIMEOUT, pw))) break;
+                        const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
+                        // a stage: the activation tile (both pipelines' tiles when there are two), then the weight tile they share
+                        mbar_arrive_expect_tx(full_bar(stage), PIPES == 2 && !has1 ? stage_bytes - a_bytes : stage_bytes);
+                        tma_load_4d(sa, &p.tmA[map], c0, ow0 + tx, oh0 + ty, n0, full_bar(stage));
+                        if (has1) tma_load_4d(sa + a_bytes, &p.tmA[map], c0, ow1 + tx, oh1 + ty, n1, full_bar(stage));
+                        if (!b_res) tma_load_2d(sa + PIPES * a_bytes, &p.tmB, wcol, f0, full_bar(stage));
+                        if (++stage == stages) { stage = 0; phase ^= 1u; }
                     }
                 }
             }
         }
-        if (kRoleTiming && p.debug && blockIdx.x == 0 && pipe == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
+        if (kRoleTiming && p.debug && blockIdx.x == 0) { p.debug[0] = clock64() - t_start; p.debug[1] = w_empty; }
     }
 }
 
@@ -328,7 +341,7 @@ __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
 #include "ln_conv_layout.inc"
     const uint32_t tmem_base = *tmem_slot;
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && pipe < pipes) {
+    if (lane == 0) {
         // instruction descriptor: accumulator type (bits 4-5: 1 = f32, 2 = s32), A and B types (bits 7-9, 10-12: 0 = E4M3 / binary16
         // depending on the kind, 1 = signed 8-bit), N / 8 and M / 16; both operands K-major
         const uint32_t idesc = (KIND == LN_KIND_I8 ? ((2u << 4) | (1u << 7) | (1u << 10)) : (1u << 4)) | ((uint32_t)(bn >> 3) << 17) |
@@ -342,10 +355,13 @@ __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
         long long* pw2 = p.debug ? &w_full : nullptr;
         const long long t_start = kRoleTiming ? clock64() : 0;
         if (b_res && LN_FIRST_UNIT < p.num_units) ok = mbar_wait(bres_bar, 0u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT);
-        for (int unit = LN_FIRST_UNIT + pipe * LN_UNIT_STEP; ok && unit < p.num_units; unit += pipes * LN_UNIT_STEP, t += pipes) {
+        for (int unit = LN_FIRST_UNIT; ok && unit < p.num_units; unit += PIPES * LN_UNIT_STEP, t += PIPES) {
+            // (two pipelines: this issuer's tile is the pair's first or second; a last pair may lack the second, whose issuer then
+            // only hands the stages back)
+            const bool has = PIPES == 1 || unit + pipe * LN_UNIT_STEP < p.num_units;
             const int buf = t % nbuf;
             const uint32_t acc_phase = (uint32_t)(t / nbuf) & 1u;
-            if (!(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw1))) break;
+            if (has && !(ok = mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw1))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
             if (halo) {
@@ -383,21 +399,27 @@ __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
                 continue;
             }
             for (int kb = 0; kb < kblocks; ++kb) {
-                if (!(ok = mbar_wait(full_bar(s0 + stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
+                if (PIPES == 2 && !has) {
+                    mbar_arrive(empty_bar(stage));
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                    continue;
+                }
                 const long long ti0 = kRoleTiming && p.debug ? clock64() : 0;
                 tc_fence_after();
-                const uint32_t sa = ring_base + (uint32_t)(s0 + stage) * stage_bytes;
-                const uint64_t a_desc = make_smem_desc(sa, bk), b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + a_bytes, bk);
+                const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
+                const uint64_t a_desc = make_smem_desc(sa + (uint32_t)pipe * a_bytes, bk),
+                               b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + PIPES * a_bytes, bk);
                 for (int k = 0; k < bk / 32; ++k) {  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
                     tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
                 }
                 const long long ti1 = kRoleTiming && p.debug ? clock64() : 0;
-                tc_commit(empty_bar(s0 + stage));  // arrives when the MMAs above have finished reading this stage
-                if (++stage == spp) { stage = 0; phase ^= 1u; }
+                tc_commit(empty_bar(stage));  // arrives when the MMAs above have finished reading this stage
+                if (++stage == stages) { stage = 0; phase ^= 1u; }
                 if (kRoleTiming && p.debug) { t_issue += ti1 - ti0; t_commit += clock64() - ti1; }
             }
             if (!ok) break;
-            tc_commit(tfull_bar(buf));
+            if (has) tc_commit(tfull_bar(buf));
         }
         if (kRoleTiming && p.debug && blockIdx.x == 0 && pipe == 0) { p.debug[2] = clock64() - t_start; p.debug[3] = w_tempty; p.debug[4] = w_full; p.debug[5] = t; p.debug[25] = t_issue; p.debug[26] = t_commit; }
     }
@@ -633,7 +655,7 @@ __global__ void __launch_bounds__(conv_threads(PIPES), 1) conv_umma_kernel(const
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(empty_bar(s), PIPES);  // every issuer hands the stage back
         }
         for (int b = 0; b < nbuf; ++b) {
             mbar_init(tfull_bar(b), 1);
@@ -660,8 +682,8 @@ __global__ void __launch_bounds__(conv_threads(PIPES), 1) conv_umma_kernel(const
 
 
     if (warp < 2 * PIPES) {
-        if ((warp & 1) == 0) conv_producer_role<PIPES>(p);
-        else conv_mma_role<KIND, PIPES>(p);
+        if (warp == 0) conv_producer_role<PIPES>(p);
+        else if (warp <= PIPES) conv_mma_role<KIND, PIPES>(p);
     } else {
         conv_epilogue_role<KIND, ACT, EXACT, PIPES>(p);
     }
@@ -1080,27 +1102,35 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         plan->smem = (size_t)a_stages * box + (p.b_resident ? b_total : (size_t)stages * b_bytes) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     } else {
     p.b_resident = (allow_resident && p.tiles_f == 1 && b_total + res_min_stages * 128u * bk <= smem_budget) ? 1 : 0;
-    const uint32_t stage_bytes = p.b_resident ? 128u * bk : (uint32_t)(128 + b_rows) * bk;
-    int stages = (int)(((p.b_resident ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u)) / stage_bytes);
-    if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
-    // Two producer / issuer pipelines where one issuing thread cannot keep the tensor pipe busy: filter tiles of at most 128 (an
-    // instruction costs its thread about 100 cycles whatever N is, the tensor pipe 64 cycles at N = 128) with enough instructions
-    // per tile for that to matter, and at least two stages for each pipeline.  Measured on 3x3 C128 -> K128 at 76x76: 104 -> 84 us;
-    // 3x3 stride 2 C64 -> K128 at 304x304: 88 -> 61 us; with 256-filter tiles the two stages per pipeline that fit lose 6 %.
-    // LN_CONV_PIPES = 1 / 2 forces one / two (for A/B measurements).
+    const uint32_t ring_budget = (p.b_resident ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u);
+    // Two pipelines (see the kernel) where one issuing thread cannot keep the tensor pipe busy and two double stages fit; the
+    // tiles of a pair must share their filter tile, so the grid has to be a multiple of tiles_f.
+    // LN_CONV_PIPES = 1 / 2 forces one / two wherever possible (for A/B measurements).
     const char* pipes_env = getenv("LN_CONV_PIPES");
     const int pipes_forced = pipes_env ? atoi(pipes_env) : 0;
+    const uint32_t stage2_bytes = 256u * bk + (p.b_resident ? 0u : (uint32_t)bn * bk);
+    int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
+    // Measured (us, one -> two issuers): 3x3 C128 -> K128 at 76x76 x64 106 -> 83; 3x3 stride 2 C64 -> K128 at 304x304 x16 88 -> 65;
+    // 3x3 C256 -> K512 at 38x38 x64 94 -> 92; 1x1 C512 -> K256 27 -> 35; the packed 3x3 C32 -> K64 (256 virtual filters) 111 -> 129:
+    // filter tiles of 256 keep one issuer (their instructions are long enough, and three 64 KB stages are too few).
     const bool pipes_rule = bn <= 128 && g.k * g.k * (g.cpad / 32) >= 16;
-    if (stages >= 4 && pipes_forced != 1 && (pipes_rule || pipes_forced == 2)) {
-        p.pipes = 2;
-        stages &= ~1;
+    if (ring_budget / stage2_bytes >= 2 && p.num_tiles >= 2 * grid && pipes_forced != 1 && (pipes_rule || pipes_forced == 2)) {
+        const int grid2 = grid - grid % p.tiles_f;
+        if (grid2 > 0 && grid2 * 20 >= grid * 19) {  // (giving up more than 5 % of the SMs for the alignment is not worth it)
+            p.pipes = 2;
+            grid = grid2;
+        }
     }
+    const uint32_t stage_bytes = p.pipes == 2 ? stage2_bytes : (p.b_resident ? 128u * bk : (uint32_t)(128 + b_rows) * bk);
+    int stages = (int)(ring_budget / stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "tensor-core convolution: stage of %u bytes does not fit", stage_bytes);
     p.stages = stages;
+    plan->grid = grid;
     plan->smem = (size_t)stages * stage_bytes + (p.b_resident ? b_total : 0u) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     }
     plan->smem += tab_bytes;
-    plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
+    if (p.halo) plan->grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     plan->kind = g.kind;
 
     const CUtensorMapSwizzle swz = bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
