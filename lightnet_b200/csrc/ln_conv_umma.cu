@@ -11,9 +11,10 @@
 // matching weight slab.  Stride-2 convolutions use one tensor map per input parity class so that the
 // strided gather is again a dense box.  Every CTA fetches its own operands.
 //
-// Roles (576 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..17 = epilogue (four warps per
-// TMEM lane quadrant, each group of four warps taking every fourth tile, so every scheduler has four warps to hide latency with;
-// the per-filter {multiplier, bias} table lives in shared memory so that the epilogue fits in 112 registers).
+// Roles: warp 0 = TMA producer, warp 1 (and warp 2 in the two-issuer form, see "Pipelines" below) = MMA issuer, warp 1 owns TMEM;
+// then sixteen epilogue warps (four per TMEM lane quadrant, each group of four warps taking every fourth unit of work, so every
+// scheduler has four warps to hide latency with; the per-filter {multiplier, bias} table lives in shared memory so that the
+// epilogue fits in 96 registers).  576 threads with one issuer, 640 with two.
 // The accumulator is double buffered in TMEM so the epilogue of tile t overlaps the main loop of t+1.
 // Every mbarrier wait is bounded: when it gives up it raises a status word the host reads, and all
 // roles leave their loops, TMEM is released and the kernel returns.

@@ -167,6 +167,45 @@ def test_q8_conv_accumulators_bit_exact(be, case):
         assert d.max() <= 1 and (d > 0).mean() < 0.05, (act_name, d.max(), (d > 0).mean())
 
 
+TWO_ISSUER_CASES = [  # every CTA gets two or three tiles, so both the paired and the lone last tile of the two-issuer kernel are run
+    (8, 128, 76, 76, 128, 3, 1, 1),    # resident weights, 361 tiles: the planner's own choice of two issuers
+    (8, 128, 76, 76, 256, 3, 1, 1),    # 256-filter tile, weight tiles shared through the ring (forced)
+    (8, 64, 152, 152, 128, 3, 2, 1),   # stride 2: four parity maps, 64-byte rows
+    (9, 256, 38, 38, 512, 1, 1, 0),    # two filter tiles: the tiles of a pair must share theirs (grid rounded to a multiple of two)
+]
+
+
+@pytest.mark.parametrize("case", TWO_ISSUER_CASES)
+def test_q8_conv_two_issuers_bit_exact(be, case, monkeypatch):
+    """The kernel form with two MMA-issuing threads (LN_CONV_PIPES=2 forces it wherever it fits) gives the accumulators and the
+    exact-epilogue codes of the oracle, like the one-issuer form."""
+    monkeypatch.setenv("LN_CONV_PIPES", "2")
+    n, c, h, w, f, k, s, p = case
+    rng = np.random.default_rng(hash(case) & 0xFFFF)
+    wt, act, bias, sx = quantized_conv_case(rng, n, c, h, w, f, k)
+    oh, ow = conv_out(h, w, k, s, p)
+    tw = be.upload_f32(wt.shape, wt)
+    wq = be.conv_weights_q(tw, f, c, k, ln.LN_Q8)
+    tx = be.upload_q((n, c, h, w), act, sx, ln.LN_Q8)
+    tb = be.upload_f32((1, f, 1, 1), bias)
+    xq, _ = be.download_q(tx)
+    ws = (np.abs(wt.reshape(f, -1)).max(1) / np.float32(127.0)).astype(np.float32)
+    wq_ref = np.clip(np.rint(wt / ws[:, None, None, None]), -127, 127).astype(np.int8)
+    acc_ref = orc.conv_q8_acc(xq, wq_ref, s, p)
+    acc = be.download_i32(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, "linear", 1.0, ln.LN_OUT_ACC))
+    assert np.array_equal(acc, acc_ref)
+    mult = (np.float32(sx) * ws).astype(np.float32)
+    a_ref, _ = orc.q8_epilogue(acc_ref, mult, bias, "mish", 1.0)
+    sy = np.float32(max(np.abs(a_ref).max(), 1e-6) / 127.0)
+    _, q_ref = orc.q8_epilogue(acc_ref, mult, bias, "mish", float(np.float32(1.0) / sy))
+    be.set_exact_epilogue(True)
+    try:
+        q, _ = be.download_q(be.conv2d_bias_act_q(tx, wq, tb, (n, f, oh, ow), c, h, w, f, k, s, s, 1, p, 1, "mish", float(sy), ln.LN_OUT_Q))
+    finally:
+        be.set_exact_epilogue(False)
+    assert np.array_equal(q, q_ref)
+
+
 GROUPED_CASES = [  # (n, c, h, w, f, k, stride, pad, groups): depthwise and grouped shapes of the kind efficientnet / csresnext cfgs use
     (2, 32, 28, 28, 32, 3, 1, 1, 32),     # depthwise 3x3 (lightnet-cuda-oxide/tests/data/conv_shapes_summary.md: groups = channels)
     (1, 96, 30, 26, 96, 3, 2, 1, 96),     # depthwise, stride 2
