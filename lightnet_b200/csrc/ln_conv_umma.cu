@@ -349,6 +349,8 @@ __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
                                ((128u >> 4) << 24);
         int stage = 0, astage = 0;
         uint32_t phase = 0, aphase = 0;
+        const uint64_t desc_base = make_smem_desc(0u, bk);
+        const uint32_t a_off = (uint32_t)pipe * a_bytes;  // this issuer's activation tile inside a stage
         int t = pipe;  // the CTA's tile counter: pipeline i takes the tiles t = i, i + pipes, ...
         bool ok = true;
         long long w_tempty = 0, w_full = 0, t_issue = 0, t_commit = 0;
@@ -370,22 +372,19 @@ __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
                 for (int cb = 0; ok && cb < p.cblocks; ++cb)
                     for (int s = 0; ok && s < 3; ++s) {
                         if (!(ok = mbar_wait(afull_bar(astage), aphase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
-                        tc_fence_after();
                         const uint32_t sa = ring_base + (uint32_t)astage * box_bytes;
                         for (int r = 0; r < 3; ++r) {
                             uint32_t sb;
                             if (b_res) sb = bres_base + (uint32_t)((r * 3 + s) * p.cblocks + cb) * b_bytes;
                             else {
                                 if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, LN_STATUS_MMA_TIMEOUT, pw2))) break;
-                                tc_fence_after();
                                 sb = bring_base + (uint32_t)stage * b_bytes;
                             }
                             // the box from its row r on: 128 consecutive rows of bk bytes, aligned to the 8-row swizzle pattern
-                            const uint64_t a_desc = make_smem_desc(sa + (uint32_t)(r * p.TW * bk), bk), b_desc = make_smem_desc(sb, bk);
-                            for (int k = 0; k < bk / 32; ++k) {
-                                tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accumulate);
-                                accumulate = 1u;
-                            }
+                            const uint64_t a_desc = desc_base + ((sa + (uint32_t)(r * p.TW * bk)) >> 4), b_desc = desc_base + (sb >> 4);
+                            tc_mma<KIND>(d_tmem, a_desc, b_desc, idesc, accumulate);
+                            if (bk == 64) tc_mma<KIND>(d_tmem, a_desc + 2u, b_desc + 2u, idesc, 1u);  // (this mode runs with 32 or 64 bytes per row)
+                            accumulate = 1u;
                             if (!b_res) {
                                 tc_commit(empty_bar(stage));
                                 if (++stage == stages) { stage = 0; phase ^= 1u; }
@@ -407,12 +406,23 @@ __device__ __forceinline__ void conv_mma_role(const ln_conv_umma_params& p) {
                     continue;
                 }
                 const long long ti0 = kRoleTiming && p.debug ? clock64() : 0;
-                tc_fence_after();
+                // (no tcgen05 fence here: the operands were written by the TMA unit and its completion on the barrier just waited for
+                // makes them visible to the tensor core; the fence after the accumulator wait above orders the MMAs behind the
+                // epilogue's TMEM reads)
+                // descriptors: the constant part plus the operand's address in units of 16 bytes (shared-memory addresses stay below
+                // 2^18, so the sum never carries out of the 14-bit field); one instruction consumes 32 bytes of K = +2 units
                 const uint32_t sa = ring_base + (uint32_t)stage * stage_bytes;
-                const uint64_t a_desc = make_smem_desc(sa + (uint32_t)pipe * a_bytes, bk),
-                               b_desc = make_smem_desc(b_res ? bres_base + (uint32_t)kb * b_bytes : sa + PIPES * a_bytes, bk);
-                for (int k = 0; k < bk / 32; ++k) {  // one instruction consumes 32 bytes of K; +2 in units of 16 bytes
-                    tc_mma<KIND>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (uint32_t)((kb | k) != 0));
+                const uint64_t a_desc = desc_base + ((sa + a_off) >> 4),
+                               b_desc = desc_base + ((b_res ? bres_base + (uint32_t)kb * b_bytes : sa + PIPES * a_bytes) >> 4);
+                const uint32_t acc0 = (uint32_t)(kb != 0);
+                if (bk == 128) {
+                    tc_mma<KIND>(d_tmem, a_desc, b_desc, idesc, acc0);
+                    tc_mma<KIND>(d_tmem, a_desc + 2u, b_desc + 2u, idesc, 1u);
+                    tc_mma<KIND>(d_tmem, a_desc + 4u, b_desc + 4u, idesc, 1u);
+                    tc_mma<KIND>(d_tmem, a_desc + 6u, b_desc + 6u, idesc, 1u);
+                } else {
+                    tc_mma<KIND>(d_tmem, a_desc, b_desc, idesc, acc0);
+                    if (bk == 64) tc_mma<KIND>(d_tmem, a_desc + 2u, b_desc + 2u, idesc, 1u);
                 }
                 const long long ti1 = kRoleTiming && p.debug ? clock64() : 0;
                 tc_commit(empty_bar(stage));  // arrives when the MMAs above have finished reading this stage
