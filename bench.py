@@ -631,7 +631,35 @@ def main():
     fwd_ms, nms_ms = net.last_times_ms()
     for _ in range(args.warmup):   # the host-input path has its own plans and graphs to warm
         net.detect(x_np, *det_args)
-    ms_e2e = timed(lambda: net.detect(x_np, *det_args), args.steps)
+    ms_sync = timed(lambda: net.detect(x_np, *det_args), args.steps)
+    # A stream of batches through ln_net_submit / ln_net_collect: the upload of batch i + 1 (from its own pinned buffer) runs
+    # while batch i goes through the layers.  Every step's upload and every step's read-back are inside the timed region.
+    x2_host = torch.from_numpy(synth.uniform_images(B, 3, args.height, args.width, 300 + rank)).pin_memory()
+    xs = (x_np, x2_host.numpy())
+
+    def stream_of_batches(steps):
+        net.submit(xs[0])
+        for i in range(steps):
+            if i + 1 < steps:
+                net.submit(xs[(i + 1) & 1])
+            net.collect(*det_args)
+
+    stream_of_batches(max(args.warmup, 2))
+    ms_e2e = timed(lambda: stream_of_batches(args.steps), 1)
+    # what the PCIe link gives this rank while all ranks copy at once: one plain pinned -> device copy of the batch per step
+    tstream = torch.cuda.Stream(device=torch.device("cuda", local_rank))
+    with torch.cuda.stream(tstream):
+        scratch_dev = torch.empty(x_host.shape, dtype=torch.float32, device=torch.device("cuda", local_rank))
+        scratch_dev.copy_(x_host, non_blocking=True)
+    tstream.synchronize()
+    timed_copy = make_timer(tstream, world)
+
+    def plain_copy():
+        with torch.cuda.stream(tstream):
+            scratch_dev.copy_(x_host, non_blocking=True)
+
+    ms_copy = timed_copy(plain_copy, args.steps)
+    del scratch_dev
     # the same call fed with 8-bit camera-sized images (640 x 480, letterboxed on the device): what a caller that does not
     # pre-process on the host pays end to end
     rng8 = np.random.default_rng(200 + rank)
@@ -666,7 +694,12 @@ def main():
                        "batch_per_gpu": B, "micro_batch": args.micro_batch, "max_detections_per_image": MAX_PER_IMAGE,
                        "l2": "inputs larger than L2 (%.0f MB f32 batch)" % (x_np.nbytes / 1e6), "parallelism": "batch-sharded, no collective"},
             "e2e": {"value": B * world * args.steps / (ms_e2e * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(x_np.nbytes),
-                    "d2h_bytes_per_step": int(B * MAX_PER_IMAGE * 28 + B * 4), "api": "ln_net_detect (host f32 NCHW batch -> detections; the batch is uploaded and run in two parts, %d + %d images, as a two-stage pipeline)" % ((B // 4, B - B // 4) if B >= 16 else (B // 2, B - B // 2))},
+                    "d2h_bytes_per_step": int(B * MAX_PER_IMAGE * 28 + B * 4),
+                    "api": "ln_net_submit + ln_net_collect on a stream of host f32 NCHW batches (two pinned buffers, the upload of the next batch overlaps the layers of the current one; %d uploads and %d read-backs inside the timed region)" % (args.steps, args.steps)},
+            "h2d": {"gbs_per_rank": x_np.nbytes * args.steps / (ms_copy * 1e-3) / 1e9, "ms_per_batch": ms_copy / args.steps,
+                    "basis": "a plain cudaMemcpyAsync of the pinned f32 batch on every rank at once, slowest rank"},
+            "e2e_sync": {"value": B * world * args.steps / (ms_sync * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(x_np.nbytes),
+                         "api": "ln_net_detect, one synchronous call per batch (the batch is uploaded and run in two parts, %d + %d images, as a two-stage pipeline)" % ((B // 4, B - B // 4) if B >= 16 else (B // 2, B - B // 2))},
             "e2e_u8": {"value": B * world * args.steps / (ms_u8 * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(flat8.nbytes),
                        "api": "ln_net_detect_u8 (host 8-bit 640x480 RGB images -> device letterbox -> detections)"},
             "gpu_launches": int(launches),

@@ -322,6 +322,16 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
                       const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host);
 int32_t ln_net_detect_device(ln_net* net, const ln_tensor* input, const int32_t* image_w, const int32_t* image_h,
                              const ln_detect_options* opts, ln_detection* records_host, int32_t* counts_host);
+/* The same work as ln_net_detect split in two calls so that a caller with a stream of batches overlaps the upload of the next
+   batch with the layers of the current one (what a serving loop over GpuExecutableNetwork::forward_compact,
+   lightnet-runtime/src/runtime/gpu_forward_compact.rs:8, does with a second input tensor).  ln_net_submit enqueues the
+   host-to-device copy of one f32 NCHW batch on the network's copy stream and returns at once; at most two batches may be in
+   flight, and `input_host` must stay unchanged until the matching ln_net_collect returns (pinned memory for a copy that really
+   is asynchronous).  ln_net_collect runs the oldest submitted batch (layers, decode, NMS) and returns its records like
+   ln_net_detect.  LN_ERR_ARG when a third batch is submitted or nothing is left to collect. */
+int32_t ln_net_submit(ln_net* net, const float* input_host);
+int32_t ln_net_collect(ln_net* net, const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
+                       ln_detection* records_host, int32_t* counts_host);
 /* ln_image_preprocess_u8 (to the network's input size) followed by ln_net_detect_device; the records are scaled to each
    image's own size (widths / heights), as `lightnet-rs detect-image` does (lightnet-cli/src/main.rs: load, letterbox, detect). */
 int32_t ln_net_detect_u8(ln_net* net, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,

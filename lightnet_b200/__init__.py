@@ -134,6 +134,8 @@ SYMBOLS = {
     "ln_net_layer_output": (C.c_int32, [_VP, C.c_int32, _PP]),
     "ln_net_detect": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_detect_device": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
+    "ln_net_submit": (C.c_int32, [_VP, _VP]),
+    "ln_net_collect": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_last_times": (C.c_int32, [_VP, _VP]),
     "ln_net_set_profile": (C.c_int32, [_VP, C.c_int32]),
     "ln_net_set_fusion": (C.c_int32, [_VP, C.c_int32]),
@@ -624,6 +626,29 @@ class GpuExecutableNetwork:
         x = np.ascontiguousarray(x, np.float32)
         return self._detect(self.lib.ln_net_detect, _ptr(x), image_w, image_h, confidence_threshold, nms_threshold, letterbox,
                             top_k, max_per_image)
+
+    def submit(self, x):
+        """Enqueues the upload of one host batch (f32 NCHW, C-contiguous; keep it alive and unchanged until the matching collect
+        returns; pinned memory makes the copy asynchronous).  At most two batches may be in flight."""
+        if not (isinstance(x, np.ndarray) and x.dtype == np.float32 and x.flags["C_CONTIGUOUS"]):
+            raise ValueError("submit needs a C-contiguous float32 array (it is read after this call returns)")
+        self._in_flight = getattr(self, "_in_flight", [])
+        self.backend._check(self.lib.ln_net_submit(self.h, _ptr(x)))
+        self._in_flight.append(x)
+
+    def collect(self, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0, max_per_image=1024):
+        """Runs the oldest submitted batch and returns its detections, like detect()."""
+        iw = np.ascontiguousarray(np.broadcast_to(np.asarray(image_w, np.int32), (self.batch,)))
+        ih = np.ascontiguousarray(np.broadcast_to(np.asarray(image_h, np.int32), (self.batch,)))
+        opts = ln_detect_options(confidence_threshold, nms_threshold, int(letterbox), top_k, max_per_image)
+        rec = np.zeros((self.batch, max_per_image, 7), np.float32)
+        cnt = np.zeros(self.batch, np.int32)
+        try:
+            self.backend._check(self.lib.ln_net_collect(self.h, _ptr(iw), _ptr(ih), C.byref(opts), _ptr(rec), _ptr(cnt)))
+        finally:
+            if getattr(self, "_in_flight", None):
+                self._in_flight.pop(0)
+        return [rec[b, :cnt[b]].copy() for b in range(self.batch)]
 
     def detect_device(self, t: Tensor, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0,
                       max_per_image=1024):

@@ -1014,7 +1014,11 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         const int v = atoi(e);
         if ((v == 64 || v == 32) && v < bk) bk = v;
     }
-    const int bn = ln_conv_choose_bn(g.F);  // filter tile: least padding, ties to the larger tile
+    int bn = ln_conv_choose_bn(g.F);  // filter tile: least padding, ties to the larger tile
+    if (const char* e = getenv("LN_CONV_BN")) {  // (A/B measurements: a smaller filter tile)
+        const int v = atoi(e);
+        if ((v == 128 || v == 64) && v < bn && g.fpad % v == 0) bn = v;
+    }
     if (g.fpad % bn != 0) return ln_fail(ctx, LN_ERR_ARG, "tensor-core convolution: weights are padded to %d filters, tile needs a multiple of %d", g.fpad, bn);
     p.bk = bk; p.bn = bn;
     p.R = g.k; p.S = g.k; p.stride = g.stride; p.pad = g.pad;

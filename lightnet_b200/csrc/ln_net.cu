@@ -252,6 +252,10 @@ struct ln_net {
     std::vector<ln_tensor*> ext_heads;   // part network: its views into the owner's pipe_heads (used instead of own head storage)
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t copy_ev[2] = {nullptr, nullptr};
+    // ln_net_submit / ln_net_collect: two input slots; `submitted` counts uploads enqueued, `collected` batches run
+    ln_tensor* slot_dev[2] = {nullptr, nullptr};
+    cudaEvent_t slot_ev[2] = {nullptr, nullptr};
+    long long submitted = 0, collected = 0;
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     float times_ms[2] = {0, 0};
     // CUDA graph of the 8-bit plan (one graph = the whole batch: every micro-batch, every layer)
@@ -1154,6 +1158,8 @@ int32_t ln_net_destroy(ln_net* net) {
     release_heads(net);
     for (auto*& t : net->ext_heads) { ln_tensor_release(t); t = nullptr; }
     ln_tensor_release(net->input_dev);
+    for (auto& t : net->slot_dev) if (t) ln_tensor_release(t);
+    for (auto& e : net->slot_ev) if (e) cudaEventDestroy(e);
     release_pipe(net);
     if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
     for (auto& e : net->copy_ev) if (e) cudaEventDestroy(e);
@@ -1416,6 +1422,40 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
     int rc = stage_input(net, input_host);
     if (rc) return rc;
     return ln_net_detect_device(net, net->input_dev, image_w, image_h, opts, records_host, counts_host);
+}
+
+int32_t ln_net_submit(ln_net* net, const float* input_host) {
+    if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_submit: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    if (net->submitted - net->collected >= 2) return ln_fail(ctx, LN_ERR_ARG, "ln_net_submit: two batches are in flight already; collect one first");
+    cudaSetDevice(ctx->device);
+    if (!net->copy_stream) {
+        LN_CUDA(ctx, cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+        for (auto& e : net->copy_ev) LN_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    const int slot = (int)(net->submitted & 1);
+    if (!net->slot_dev[slot]) {
+        net->slot_dev[slot] = ln_tensor_new(ctx, LN_F32, net->batch, net->channels, net->height, net->width);
+        if (!net->slot_dev[slot]) return LN_ERR_CUDA;
+        LN_CUDA(ctx, cudaEventCreateWithFlags(&net->slot_ev[slot], cudaEventDisableTiming));
+    }
+    // the slot's previous batch was collected (its forward has been synchronised), so nothing reads the buffer any more
+    LN_CUDA(ctx, cudaMemcpyAsync(net->slot_dev[slot]->ptr, input_host, (size_t)net->slot_dev[slot]->count() * 4, cudaMemcpyHostToDevice, net->copy_stream));
+    LN_CUDA(ctx, cudaEventRecord(net->slot_ev[slot], net->copy_stream));
+    net->submitted++;
+    return LN_OK;
+}
+
+int32_t ln_net_collect(ln_net* net, const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts, ln_detection* records_host,
+                       int32_t* counts_host) {
+    if (!net) return ln_fail(nullptr, LN_ERR_ARG, "ln_net_collect: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    if (net->submitted == net->collected) return ln_fail(ctx, LN_ERR_ARG, "ln_net_collect: no batch has been submitted");
+    cudaSetDevice(ctx->device);
+    const int slot = (int)(net->collected & 1);
+    net->collected++;  // (the slot is free again whatever happens below: every path out of ln_net_detect_device has synchronised or failed)
+    LN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, net->slot_ev[slot], 0));
+    return ln_net_detect_device(net, net->slot_dev[slot], image_w, image_h, opts, records_host, counts_host);
 }
 
 int32_t ln_net_detect_u8(ln_net* net, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,

@@ -1034,6 +1034,38 @@ def test_host_pipeline_gives_the_same_detections(be):
         assert np.array_equal(piped2[b], whole[b]), b
 
 
+def test_submit_collect_gives_the_detections_of_detect(be):
+    """A stream of batches through submit / collect (two in flight) returns, batch for batch, what detect() returns; a third
+    submit and a collect with nothing in flight are refused."""
+    batch = 4
+    o = orc.Net(MINI_CFG, batch)
+    blob = synth.he_weights(o.layers(), 61, bn_identity=False)
+    xs = [synth.uniform_images(batch, o.channels, o.height, o.width, 70 + i) for i in range(4)]
+    net = ln.GpuExecutableNetwork(be, MINI_CFG, batch, ln.LN_Q8)
+    net.load_weights(blob)
+    net.calibrate(xs[0])
+    args = (640, 480, 0.2, 0.45, True, 0, 256)
+    want = [net.detect(x, *args) for x in xs]
+    assert sum(len(d) for w in want for d in w) > 50
+    got = []
+    net.submit(xs[0])
+    for i in range(len(xs)):
+        if i + 1 < len(xs):
+            net.submit(xs[i + 1])
+        got.append(net.collect(*args))
+    for w, g in zip(want, got):
+        for b in range(batch):
+            assert np.array_equal(w[b], g[b])
+    with pytest.raises(ln.BackendError):
+        net.collect(*args)
+    net.submit(xs[0])
+    net.submit(xs[1])
+    with pytest.raises(ln.BackendError):
+        net.submit(xs[2])
+    assert np.array_equal(net.collect(*args)[0], want[0][0])
+    assert np.array_equal(net.collect(*args)[0], want[1][0])
+
+
 def test_gaussian_yolo_head_is_decoded_like_a_yolo_head(be):
     """[gaussian_yolo] is the same identity layer and the same decode as [yolo] at inference (model.rs:4513-4543,
     exec_forward.rs:908-912, detect.rs:78): a network whose heads carry that name gives the records of the [yolo] one."""
