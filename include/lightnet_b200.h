@@ -228,6 +228,12 @@ typedef struct ln_yolo_head {
     float anchors[2 * 8];  /* (w,h) per masked anchor, already selected through `mask` (detection_geometry.rs:100) */
     float scale_x_y;
     int32_t new_coords;
+    /* 0 = [yolo] / [gaussian_yolo] (the fields above); 1 = an activated [yolox] head (classes + 5 channels: cxcywh logits,
+       objectness, classes; box by decode_yolox_box, lightnet-layers/src/modern_yolo/cpu.rs:461, score objectness * class);
+       2 = a [ppyoloe] / [yolonas] head after ln_modern_yolo_predecode_f32 (final box, objectness, classes; score
+       max(class, objectness * class), lightnet-train/src/detect.rs:1158-1162).  Kinds 1 and 2 take n_anchor = 1, ignore
+       anchors / scale_x_y / new_coords, and expect the probabilities ln_modern_yolo_forward_f32 produces (in [0, 1]). */
+    int32_t kind;
 } ln_yolo_head;
 
 typedef struct ln_detection { /* Detection (detect.rs:21-27): bbox centre/size in image pixels */
@@ -357,6 +363,17 @@ int32_t ln_net_set_host_pipeline(ln_net* net, int32_t on);
 int32_t ln_net_set_cuda_graph(ln_net* net, int32_t on);
 int32_t ln_net_profile(const ln_net* net, float* per_layer_ms, int32_t num_layers, float per_op_ms[8], int32_t per_op_launches[8]);
 
+
+/* ---- modern anchor-free heads ------------------------------------------------------------- */
+/* modern_yolo_forward_f32 (lightnet-cuda/src/lib.rs:4884): the shared [yolox] / [ppyoloe] / [yolonas] output activation in NCHW:
+   every entry sanitised (non-finite -> 0), the trailing 1 + classes planes through a sigmoid of the logit clamped to [-30, 30]. */
+int32_t ln_modern_yolo_forward_f32(ln_ctx* ctx, const ln_tensor* x, int64_t classes, ln_tensor** out);
+/* modern_yolo_predecode_f32 (lib.rs:4936; kernel lightnet-cuda-oxide/src/kernels/dense_loss.rs:788): device box decode of an
+   activated [ppyoloe] / [yolonas] head (kind 1 or 2, the trait's numbering) of coords = 4 * (reg_max + 1) box entries:
+   returns [batch, 5 + classes, H, W] holding the final centre-size box, then the objectness and class planes.  Hand the
+   result to ln_yolo_decode_nms as a head of kind 2 (decode_modern_detections, lightnet-train/src/detect.rs:1035, through
+   decode_network_detections). */
+int32_t ln_modern_yolo_predecode_f32(ln_ctx* ctx, const ln_tensor* x, int64_t classes, int64_t coords, int32_t kind, ln_tensor** out);
 
 /* ---- debug aids (no counterpart in the reference) ------------------------------------------- */
 /* Largest distance, in units of the 32-bit confidence key, between the approximate (hardware ex2 / rcp) score the head passes

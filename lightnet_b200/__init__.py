@@ -53,7 +53,7 @@ class BackendError(RuntimeError):
 
 class ln_yolo_head(C.Structure):
     _fields_ = [("raw", C.c_void_p), ("classes", C.c_int32), ("n_anchor", C.c_int32), ("anchors", C.c_float * 16),
-                ("scale_x_y", C.c_float), ("new_coords", C.c_int32)]
+                ("scale_x_y", C.c_float), ("new_coords", C.c_int32), ("kind", C.c_int32)]
 
 
 class ln_detect_options(C.Structure):
@@ -159,6 +159,8 @@ SYMBOLS = {
     "ln_channel_affine_act_f16": (C.c_int32, [_VP, _VP, _VP, _VP, C.c_int64, C.c_int64, C.c_int32, _PP]),
     "ln_debug_score_key_error": (C.c_int32, [_VP, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32, C.POINTER(C.c_uint32)]),
     "ln_ctx_debug_cycles": (C.c_int32, [_VP, _I64P]),
+    "ln_modern_yolo_forward_f32": (C.c_int32, [_VP, _VP, C.c_int64, _VP]),
+    "ln_modern_yolo_predecode_f32": (C.c_int32, [_VP, _VP, C.c_int64, C.c_int64, C.c_int32, _VP]),
     "ln_debug_mma_peak": (C.c_int32, [_VP, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
     "ln_debug_mma_peak_shape": (C.c_int32, [_VP, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_float)]),
 }
@@ -385,6 +387,14 @@ class B200Backend:
     def yolo_activate_f32(self, x, classes, scale_xy, new_coords):
         return self._out(self.lib.ln_yolo_activate_f32, x.h, classes, float(scale_xy), int(bool(new_coords)))
 
+    def modern_yolo_forward_f32(self, x, classes):
+        """The output activation of [yolox] / [ppyoloe] / [yolonas] heads (lightnet-cuda/src/lib.rs:4884)."""
+        return self._out(self.lib.ln_modern_yolo_forward_f32, x.h, int(classes))
+
+    def modern_yolo_predecode_f32(self, x, classes, coords, kind):
+        """Device box decode of an activated distribution head (lib.rs:4936): [B, coords + 1 + classes, H, W] -> [B, 5 + classes, H, W]."""
+        return self._out(self.lib.ln_modern_yolo_predecode_f32, x.h, int(classes), int(coords), int(kind))
+
     # ---- F16TensorOpsBackend (binary16 storage) ---------------------------------------------------
     def upload_f16(self, shape, host):
         host = np.ascontiguousarray(host, np.float32)
@@ -499,6 +509,7 @@ class B200Backend:
                 arr[k].anchors[i] = v
             arr[k].scale_x_y = h.get("scale_x_y", 1.0)
             arr[k].new_coords = int(h.get("new_coords", 0))
+            arr[k].kind = int(h.get("kind", 0))  # 1 = activated [yolox] head, 2 = predecoded distribution head (one dummy anchor)
         return arr
 
     def yolo_decode_nms(self, heads, net_w, net_h, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45,

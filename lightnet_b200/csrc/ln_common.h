@@ -108,6 +108,9 @@ inline int64_t ln_round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 #ifdef __CUDACC__
 // exp built only from IEEE-754 binary32 operations (fma where written): a CPU evaluating the same
 // sequence gets the same bits.  Accuracy: a few ulp.
+// f32::is_finite ? v : 0 (finite_or_zero of lightnet-layers/src/modern_yolo/cpu.rs:199)
+__device__ __forceinline__ float ln_finite_or_zero(float v) { return (__float_as_uint(v) & 0x7F800000u) == 0x7F800000u ? 0.0f : v; }
+
 __device__ __forceinline__ float ln_det_expf(float x) {
     x = fminf(fmaxf(x, -87.0f), 88.0f);
     float n = rintf(__fmul_rn(x, 1.44269502e+00f));

@@ -115,6 +115,53 @@ __global__ void region_forward_f32_kernel(const float* __restrict__ x, float* __
     }
 }
 
+// modern_yolo_forward_f32 (lightnet-cuda/src/lib.rs:4884-4915): every entry sanitised, the trailing 1 + classes planes through a
+// sigmoid of the logit clamped to [-30, 30].
+__global__ void modern_activate_f32_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, long long spatial, int channels, int class_begin) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)((i / spatial) % channels);
+        float v = ln_finite_or_zero(x[i]);
+        if (c >= class_begin) v = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-fminf(fmaxf(v, -30.0f), 30.0f))));
+        y[i] = v;
+    }
+}
+
+// modern_yolo_predecode (lightnet-cuda-oxide/src/kernels/dense_loss.rs:788-812): one thread per cell; the softmax expectation of
+// each side's bins (modern_yolo/cpu.rs:283-308), corners to a sanitised centre-size box (cpu.rs:340-387), then the objectness
+// and class planes copied behind it.
+__global__ void modern_predecode_f32_kernel(const float* __restrict__ x, float* __restrict__ y, long long cells, int w, int h, int classes, int coords) {
+    const long long s = (long long)w * h;
+    const int bins = coords / 4 > 2 ? coords / 4 : 2, cin = coords + 1 + classes, cout = 5 + classes;
+    for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < cells; g += (long long)gridDim.x * blockDim.x) {
+        const long long b = g / s, loc = g - b * s;
+        const float* px = x + b * cin * s + loc;
+        float side[4];
+        for (int sd = 0; sd < 4; ++sd) {
+            float mx = -INFINITY;
+            for (int k = 0; k < bins; ++k) mx = fmaxf(mx, ln_finite_or_zero(px[(long long)(sd * bins + k) * s]));
+            float denom = 0.0f, expected = 0.0f;
+            for (int k = 0; k < bins; ++k) {
+                const float e = expf(fminf(fmaxf(__fsub_rn(ln_finite_or_zero(px[(long long)(sd * bins + k) * s]), mx), -60.0f), 60.0f));
+                denom = __fadd_rn(denom, e);
+                expected = __fadd_rn(expected, __fmul_rn((float)k, e));
+            }
+            side[sd] = __fdiv_rn(expected, fmaxf(denom, 1e-8f));
+        }
+        const int row = (int)(loc / w), col = (int)(loc - (long long)row * w);
+        const float cx = (float)col + 0.5f, cy = (float)row + 0.5f;
+        float left = ln_finite_or_zero(__fdiv_rn(__fsub_rn(cx, side[0]), (float)w)), top = ln_finite_or_zero(__fdiv_rn(__fsub_rn(cy, side[1]), (float)h));
+        float right = ln_finite_or_zero(__fdiv_rn(__fadd_rn(cx, side[2]), (float)w)), bottom = ln_finite_or_zero(__fdiv_rn(__fadd_rn(cy, side[3]), (float)h));
+        if (right < left) { const float t = left; left = right; right = t; }
+        if (bottom < top) { const float t = top; top = bottom; bottom = t; }
+        float* py = y + b * cout * s + loc;
+        py[0] = ln_finite_or_zero(__fmul_rn(0.5f, __fadd_rn(left, right)));
+        py[s] = ln_finite_or_zero(__fmul_rn(0.5f, __fadd_rn(top, bottom)));
+        py[2 * s] = fmaxf(ln_finite_or_zero(fmaxf(__fsub_rn(right, left), 1e-6f)), 1e-6f);
+        py[3 * s] = fmaxf(ln_finite_or_zero(fmaxf(__fsub_rn(bottom, top), 1e-6f)), 1e-6f);
+        for (int e = 0; e < classes + 1; ++e) py[(long long)(4 + e) * s] = px[(long long)(coords + e) * s];
+    }
+}
+
 // Classic [yolo] head activation on anchor-major NCHW entries (lightnet-cuda/src/lib.rs:4951-4966): logistic on every entry but w / h
 // (none when new_coords), then x, y scaled: v * scale_xy - 0.5 * (scale_xy - 1).
 __global__ void yolo_activate_f32_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t n, int64_t plane, int entries, float scale_xy,
@@ -339,6 +386,40 @@ int32_t ln_yolo_activate_f32(ln_ctx* ctx, const ln_tensor* x, int64_t classes, f
     ctx->launches++;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { ln_tensor_release(y); return ln_fail(ctx, LN_ERR_CUDA, "yolo_activate launch: %s", cudaGetErrorString(e)); }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_modern_yolo_forward_f32(ln_ctx* ctx, const ln_tensor* x, int64_t classes, ln_tensor** out) {
+    if (!ctx || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_modern_yolo_forward_f32: NULL argument");
+    if (!is_f32(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_modern_yolo_forward_f32: f32 tensor required");
+    if (classes < 0) return ln_fail(ctx, LN_ERR_ARG, "ln_modern_yolo_forward_f32: negative class count");
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, LN_F32, x->n, x->c, x->h, x->w);
+    if (!y) return LN_ERR_CUDA;
+    const long long class_begin = x->c - (classes + 1) > 0 ? x->c - (classes + 1) : 0;  // saturating_sub, lib.rs:4898
+    modern_activate_f32_kernel<<<grid_for(ctx, x->count()), kThreads, 0, ctx->stream>>>((const float*)x->ptr, (float*)y->ptr, x->count(), x->h * x->w, (int)x->c, (int)class_begin);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ln_tensor_release(y); return ln_fail(ctx, LN_ERR_CUDA, "modern_yolo_forward launch: %s", cudaGetErrorString(e)); }
+    *out = y;
+    return LN_OK;
+}
+
+int32_t ln_modern_yolo_predecode_f32(ln_ctx* ctx, const ln_tensor* x, int64_t classes, int64_t coords, int32_t kind, ln_tensor** out) {
+    if (!ctx || !out) return ln_fail(ctx, LN_ERR_ARG, "ln_modern_yolo_predecode_f32: NULL argument");
+    if (!is_f32(x)) return ln_fail(ctx, LN_ERR_ARG, "ln_modern_yolo_predecode_f32: f32 tensor required");
+    if (kind != 1 && kind != 2) return ln_fail(ctx, LN_ERR_UNSUPPORTED, "ln_modern_yolo_predecode_f32: kind %d is not a distribution head (1 = ppyoloe, 2 = yolonas)", kind);
+    if (classes < 1 || coords < 8 || coords % 4) return ln_fail(ctx, LN_ERR_ARG, "ln_modern_yolo_predecode_f32: %lld classes, %lld box entries", (long long)classes, (long long)coords);
+    if (x->c != coords + 1 + classes) return ln_fail(ctx, LN_ERR_SHAPE, "distribution head tensor length mismatch: %lld channels, expected %lld", (long long)x->c, (long long)(coords + 1 + classes));
+    cudaSetDevice(ctx->device);
+    ln_tensor* y = ln_tensor_new(ctx, LN_F32, x->n, 5 + classes, x->h, x->w);
+    if (!y) return LN_ERR_CUDA;
+    const long long cells = x->n * x->h * x->w;
+    modern_predecode_f32_kernel<<<grid_for(ctx, cells), kThreads, 0, ctx->stream>>>((const float*)x->ptr, (float*)y->ptr, cells, (int)x->w, (int)x->h, (int)classes, (int)coords);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { ln_tensor_release(y); return ln_fail(ctx, LN_ERR_CUDA, "modern_yolo_predecode launch: %s", cudaGetErrorString(e)); }
     *out = y;
     return LN_OK;
 }

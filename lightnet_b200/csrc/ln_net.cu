@@ -57,6 +57,8 @@ struct NLayer {
     std::vector<float> anchors;
     float scale_x_y = 1.0f;
     bool new_coords = false;
+    // anchor-free heads ([yolox] = 1, [ppyoloe] = 2, [yolonas] = 3; 0 = [yolo]): box entries per cell (model.rs:1086-1091)
+    int modern = 0, modern_coords = 4;
     // host parameters (lightnet-layers/src/params.rs:7-26)
     std::vector<float> biases, scales, mean, var, weights;
     // device parameters
@@ -235,6 +237,7 @@ struct ln_net {
     std::vector<ln_tensor*> out;       // f32 path: every layer output; 8-bit path: views (whole-batch runs only)
     std::vector<int> head_layers;      // indices of [yolo] layers
     std::vector<ln_tensor*> heads;     // f32 [batch, A*(5+classes), gh, gw]
+    std::vector<ln_tensor*> modern_heads;  // per head: the activated (and box-decoded) tensor of an anchor-free head, else null
     // 8-bit plan
     bool plan_valid = false;
     int plan_mb = 0;
@@ -374,6 +377,25 @@ void build_layers(ln_net* net, const std::string& cfg, int batch_override) {
             if (L.mask.size() > 8) throw ParseError{"more than 8 anchors per head"};
             L.out = cur;
             net->head_layers.push_back(li);
+        } else if (s.name == "yolox" || s.name == "ppyoloe" || s.name == "yolonas") {  // model.rs:4835-4842, :8818-8852 parse_modern_yolo_spec
+            // an anchor-free head: its forward is the output activation (lib.rs:4884); the distribution heads are then decoded to
+            // final boxes on the device (lib.rs:4936), so the head tensor has 5 + classes channels for every kind
+            L.kind = K_YOLO;
+            L.modern = s.name == "yolox" ? 1 : (s.name == "ppyoloe" ? 2 : 3);
+            L.classes = get_usize(s, "classes", 20);
+            if (L.classes == 0) throw ParseError{"[yolox] at line " + std::to_string(s.line) + ": classes must be > 0"};
+            if (get_usize(s, "max", 200) == 0) throw ParseError{"[yolox] at line " + std::to_string(s.line) + ": max must be > 0"};
+            const int reg_max = (int)get_usize(s, "reg_max", 16);
+            L.modern_coords = L.modern == 1 ? 4 : 4 * ((reg_max < 1 ? 1 : (reg_max > 64 ? 64 : reg_max)) + 1);
+            if (cur.c != L.modern_coords + 1 + L.classes)
+                throw ParseError{"[" + s.name + "] at line " + std::to_string(s.line) + ": the layer before it has " + std::to_string(cur.c) + " channels, the head needs " +
+                                 std::to_string(L.modern_coords + 1 + L.classes)};
+            L.mask = {0};
+            L.num = 1;
+            L.anchors = {1.0f, 1.0f};
+            L.out = cur;
+            L.out.c = 5 + L.classes;
+            net->head_layers.push_back(li);
         } else {
             throw ParseError{"layer [" + s.name + "] at line " + std::to_string(s.line) + " is not on the detector path"};
         }
@@ -393,6 +415,8 @@ void release_outputs(ln_net* net) {
 void release_heads(ln_net* net) {
     for (auto*& t : net->heads) { ln_tensor_release(t); t = nullptr; }
     net->heads.clear();
+    for (auto*& t : net->modern_heads) { if (t) ln_tensor_release(t); t = nullptr; }
+    net->modern_heads.clear();
 }
 void release_graph(ln_net* net) {
     if (net->graph_exec) { cudaGraphExecDestroy(net->graph_exec); net->graph_exec = nullptr; }
@@ -744,7 +768,7 @@ int build_plan(ln_net* net, int mb) {
             t = net->ext_heads[k];
             ln_tensor_retain(t);
         } else {
-            t = ln_tensor_new(ctx, LN_F32, net->batch, L.out.c, L.out.h, L.out.w);
+            t = ln_tensor_new(ctx, LN_F32, net->batch, L.modern ? L.modern_coords + 1 + L.classes : L.out.c, L.out.h, L.out.w);  // what the convolution writes
         }
         if (!t) return LN_ERR_CUDA;
         net->heads.push_back(t);
@@ -1028,6 +1052,25 @@ int forward_any(ln_net* net, const ln_tensor* input) {
         if (rc == LN_OK) rc = ln_check_status(ctx, "ln_net_forward");
     }
     if (rc) return rc;
+    // anchor-free heads: the head layer's own forward, on the raw f32 tensor the convolution before it wrote: the output activation
+    // (lib.rs:4884), then for the distribution heads the device box decode (lib.rs:4936)
+    for (size_t k = 0; k < net->head_layers.size() && k < net->heads.size(); ++k) {
+        const NLayer& L = net->layers[net->head_layers[k]];
+        if (!L.modern) continue;
+        if (net->modern_heads.size() != net->head_layers.size()) net->modern_heads.assign(net->head_layers.size(), nullptr);
+        if (net->modern_heads[k]) { ln_tensor_release(net->modern_heads[k]); net->modern_heads[k] = nullptr; }
+        ln_tensor* act = nullptr;
+        rc = ln_modern_yolo_forward_f32(ctx, net->heads[k], L.classes, &act);
+        if (rc) return rc;
+        if (L.modern == 1) net->modern_heads[k] = act;
+        else {
+            ln_tensor* boxes = nullptr;
+            rc = ln_modern_yolo_predecode_f32(ctx, act, L.classes, L.modern_coords, L.modern - 1, &boxes);
+            ln_tensor_release(act);
+            if (rc) return rc;
+            net->modern_heads[k] = boxes;
+        }
+    }
     LN_CUDA(ctx, cudaEventRecord(net->ev[1], ctx->stream));
     return LN_OK;
 }
@@ -1041,6 +1084,11 @@ int fill_heads(ln_net* net, std::vector<ln_yolo_head>& hs, const std::vector<ln_
         ln_yolo_head& h = hs[k];
         memset(&h, 0, sizeof h);
         h.raw = heads[k];
+        if (L.modern) {
+            if (tensors || k >= net->modern_heads.size() || !net->modern_heads[k]) return ln_fail(net->ctx, LN_ERR_UNSUPPORTED, "anchor-free heads are not run through the host-input pipeline");
+            h.raw = net->modern_heads[k];
+            h.kind = L.modern == 1 ? 1 : 2;
+        }
         h.classes = L.classes;
         h.n_anchor = (int)L.mask.size();
         for (size_t m = 0; m < L.mask.size(); ++m) { h.anchors[2 * m] = L.anchors[2 * L.mask[m]]; h.anchors[2 * m + 1] = L.anchors[2 * L.mask[m] + 1]; }
@@ -1320,8 +1368,9 @@ int32_t ln_net_num_heads(const ln_net* net) { return net ? (int)net->head_layers
 int32_t ln_net_head(ln_net* net, int32_t head_index, ln_tensor** out) {
     if (!net || !out) return LN_ERR_ARG;
     if (head_index < 0 || head_index >= (int)net->heads.size()) return ln_fail(net->ctx, LN_ERR_ARG, "head %d is not available (run a forward first)", head_index);
-    ln_tensor_retain(net->heads[head_index]);
-    *out = net->heads[head_index];
+    ln_tensor* t = head_index < (int)net->modern_heads.size() && net->modern_heads[head_index] ? net->modern_heads[head_index] : net->heads[head_index];
+    ln_tensor_retain(t);
+    *out = t;
     return LN_OK;
 }
 
@@ -1379,7 +1428,9 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
                       ln_detection* records_host, int32_t* counts_host) {
     if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_detect: NULL argument");
     ln_ctx* ctx = net->ctx;
-    if ((net->precision == LN_Q8 || net->precision == LN_F8) && net->host_pipeline && net->batch >= 8 && net->batch % 2 == 0 && net->weights_loaded && net->scales_set &&
+    bool any_modern = false;
+    for (int hl : net->head_layers) any_modern = any_modern || net->layers[hl].modern != 0;
+    if (!any_modern && (net->precision == LN_Q8 || net->precision == LN_F8) && net->host_pipeline && net->batch >= 8 && net->batch % 2 == 0 && net->weights_loaded && net->scales_set &&
         image_w && image_h && opts && records_host && counts_host && opts->max_per_image >= 1) {
         int rc = ensure_pipe(net);
         if (rc) return rc;

@@ -59,6 +59,9 @@ enum { FLAG_SELECT_PENDING = 0, FLAG_ACTIVE = 1, FLAG_POOL_PENDING = 2, FLAG_NEE
 struct HeadDev {
     const float* raw;  // [batch][n_anchor*(5+classes)][gh*gw]
     int gw, gh, classes, n_anchor, new_coords;
+    // 0 = [yolo]; 1 = activated [yolox] head; 2 = predecoded distribution head ([ppyoloe] / [yolonas]).  Kinds 1 and 2 hold
+    // probabilities already (new_coords = 1: values are used as they are) and have one box per cell.
+    int kind;
     float scale_x_y;
     float anchors[16];
     int ca_base;  // number of (anchor, cell) slots in earlier heads
@@ -95,6 +98,9 @@ __device__ __forceinline__ int level_shift(int l) { return l < 5 ? 52 - 12 * l :
 __device__ __forceinline__ int level_bits(int l) { return l < 5 ? 12 : 4; }
 
 __device__ __forceinline__ float head_act(float raw, int new_coords) { return new_coords ? raw : ln_det_sigmoid(raw); }
+// The objectness factor of a score.  The distribution heads gate on max(class, objectness * class) (detect.rs:1158-1162), which
+// is the class score itself for an objectness in [0, 1]: their factor is 1 (a product with 1 is exact).
+__device__ __forceinline__ float score_obj(const HeadDev& h, float raw_obj) { return h.kind == 2 ? 1.0f : head_act(raw_obj, h.new_coords); }
 
 __device__ __forceinline__ unsigned conf_key(float c) {
     unsigned b = __float_as_uint(c);
@@ -116,16 +122,26 @@ __device__ __forceinline__ Box decode_box(const HeadDev& h, const float* img, in
     const float tw = img[(size_t)(a * epa + 2) * stride + idx], th = img[(size_t)(a * epa + 3) * stride + idx];
     const float s = h.scale_x_y, nw = (float)net_w, nh = (float)net_h, iw = (float)img_w, ih = (float)img_h;
     const float half = __fmul_rn(0.5f, __fsub_rn(s, 1.0f));
-    float bx = __fdiv_rn(__fsub_rn(__fadd_rn((float)col, __fmul_rn(s, head_act(tx, h.new_coords))), half), (float)h.gw);
-    float by = __fdiv_rn(__fsub_rn(__fadd_rn((float)row, __fmul_rn(s, head_act(ty, h.new_coords))), half), (float)h.gh);
-    float bw, bh;
+    float bx, by, bw, bh;
     const float aw = h.anchors[2 * a], ah = h.anchors[2 * a + 1];
+    if (h.kind == 2) {  // final centre-size box of modern_yolo_predecode (dense_loss.rs:788)
+        bx = tx; by = ty; bw = tw; bh = th;
+    } else if (h.kind == 1) {  // decode_yolox_box (lightnet-layers/src/modern_yolo/cpu.rs:461-475), sanitised like cpu.rs:212-217
+        const float cw = fminf(fmaxf(ln_finite_or_zero(tw), -10.0f), 10.0f), ch = fminf(fmaxf(ln_finite_or_zero(th), -10.0f), 10.0f);
+        bx = ln_finite_or_zero(__fdiv_rn(__fadd_rn((float)col, ln_finite_or_zero(tx)), (float)h.gw));
+        by = ln_finite_or_zero(__fdiv_rn(__fadd_rn((float)row, ln_finite_or_zero(ty)), (float)h.gh));
+        bw = fmaxf(ln_finite_or_zero(__fdiv_rn(ln_det_expf(cw), (float)h.gw)), 1e-6f);
+        bh = fmaxf(ln_finite_or_zero(__fdiv_rn(ln_det_expf(ch), (float)h.gh)), 1e-6f);
+    } else {
+    bx = __fdiv_rn(__fsub_rn(__fadd_rn((float)col, __fmul_rn(s, head_act(tx, h.new_coords))), half), (float)h.gw);
+    by = __fdiv_rn(__fsub_rn(__fadd_rn((float)row, __fmul_rn(s, head_act(ty, h.new_coords))), half), (float)h.gh);
     if (h.new_coords) {
         bw = __fdiv_rn(__fmul_rn(__fmul_rn(__fmul_rn(tw, tw), 4.0f), aw), nw);
         bh = __fdiv_rn(__fmul_rn(__fmul_rn(__fmul_rn(th, th), 4.0f), ah), nh);
     } else {
         bw = __fdiv_rn(__fmul_rn(ln_det_expf(tw), aw), nw);
         bh = __fdiv_rn(__fmul_rn(ln_det_expf(th), ah), nh);
+    }
     }
     float new_w, new_h;
     if (letterbox) {
@@ -248,7 +264,7 @@ __global__ void __launch_bounds__(256) yolo_head_hist_kernel(const __grid_consta
         const int epa = h.classes + 5, local = ca - h.ca_base;
         const int a = local / stride, idx = local - a * stride;
         const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
-        const float obj = head_act(__ldg(img_raw + (size_t)(a * epa + 4) * stride + idx), new_coords);
+        const float obj = score_obj(h, __ldg(img_raw + (size_t)(a * epa + 4) * stride + idx));
         const float* __restrict__ cls_raw = img_raw + (size_t)(a * epa + 5) * stride + idx;
         const bool fast = approx_ok && !new_coords;
         if (obj > p.thr) {
@@ -329,7 +345,7 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
         const int epa = h.classes + 5, local = ca - h.ca_base;
         const int a = local / stride, idx = local - a * stride;
         const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
-        const float obj = head_act(__ldg(img_raw + (size_t)(a * epa + 4) * stride + idx), new_coords);
+        const float obj = score_obj(h, __ldg(img_raw + (size_t)(a * epa + 4) * stride + idx));
         if (obj > p.thr && (new_coords || conf_key(obj) >= r.rlo_ck)) {
             const int slot = atomicAdd(&s_n, 1);
             s_ptr[slot] = img_raw + (size_t)(a * epa + 5) * stride + idx;
@@ -915,7 +931,7 @@ __global__ void yolo_decode_count_kernel(const __grid_constant__ YoloParams p, i
     const int stride = h.gw * h.gh, epa = h.classes + 5;
     const int local = ca - h.ca_base, a = local / stride, idx = local - a * stride;
     const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
-    const float obj = head_act(img_raw[(size_t)(a * epa + 4) * stride + idx], h.new_coords);
+    const float obj = score_obj(h, img_raw[(size_t)(a * epa + 4) * stride + idx]);
     int n = 0;
     if (obj > p.thr)
         for (int c = 0; c < h.classes; ++c)
@@ -930,7 +946,8 @@ __global__ void yolo_decode_write_kernel(const __grid_constant__ YoloParams p, i
     const int stride = h.gw * h.gh, epa = h.classes + 5;
     const int local = ca - h.ca_base, a = local / stride, idx = local - a * stride;
     const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
-    const float obj = head_act(img_raw[(size_t)(a * epa + 4) * stride + idx], h.new_coords);
+    const float obj = score_obj(h, img_raw[(size_t)(a * epa + 4) * stride + idx]);
+    const float obj_reported = head_act(img_raw[(size_t)(a * epa + 4) * stride + idx], h.new_coords);
     if (!(obj > p.thr)) return;
     long long o = offsets[ca];
     Box b;
@@ -941,7 +958,7 @@ __global__ void yolo_decode_write_kernel(const __grid_constant__ YoloParams p, i
         if (!have) { b = decode_box(h, img_raw, a, idx, p.net_w, p.net_h, img_w, img_h, p.letterbox); have = true; }
         if (o < capacity) {
             ln_detection d;
-            d.class_id = (float)c; d.confidence = conf; d.objectness = obj; d.x = b.x; d.y = b.y; d.w = b.w; d.h = b.h;
+            d.class_id = (float)c; d.confidence = conf; d.objectness = obj_reported; d.x = b.x; d.y = b.y; d.w = b.w; d.h = b.h;
             out[o] = d;
         }
         ++o;
@@ -962,7 +979,11 @@ int fill_params(ln_ctx* ctx, YoloParams* p, const ln_yolo_head* heads, int32_t n
         if (k > 0 && (s.raw->n != heads[0].raw->n || s.classes != heads[0].classes)) return ln_fail(ctx, LN_ERR_SHAPE, "%s: heads disagree on batch or class count", who);
         HeadDev& h = p->heads[k];
         h.raw = (const float*)s.raw->ptr;
-        h.gw = (int)s.raw->w; h.gh = (int)s.raw->h; h.classes = s.classes; h.n_anchor = s.n_anchor; h.new_coords = s.new_coords;
+        if (s.kind < 0 || s.kind > 2) return ln_fail(ctx, LN_ERR_ARG, "%s: head %d has kind %d (0 = yolo, 1 = yolox, 2 = predecoded distribution head)", who, k, s.kind);
+        if (s.kind != 0 && s.n_anchor != 1) return ln_fail(ctx, LN_ERR_ARG, "%s: head %d is anchor-free and takes n_anchor = 1", who, k);
+        h.gw = (int)s.raw->w; h.gh = (int)s.raw->h; h.classes = s.classes; h.n_anchor = s.n_anchor;
+        h.kind = s.kind;
+        h.new_coords = s.kind != 0 ? 1 : s.new_coords;  // the modern heads hold probabilities already
         h.scale_x_y = s.scale_x_y;
         for (int i = 0; i < 2 * s.n_anchor; ++i) h.anchors[i] = s.anchors[i];
         h.ca_base = ca;

@@ -1016,13 +1016,68 @@ struct HeadSpec {
     const float* anchors_wh;  // n_anchor pairs, already selected through mask
     float scale_x_y;
     int new_coords;
+    // 0 = [yolo] / [gaussian_yolo]; 1 = activated [yolox] head (classes + 5 channels, cxcywh logits); 2 = a distribution head
+    // ([ppyoloe], [yolonas]) after modern_yolo_predecode: final centre-size box, objectness, classes
+    int kind = 0;
 };
+
+static inline float finite_or_zero(float v) { return std::isfinite(v) ? v : 0.0f; }
+static inline float clamp01(float v) { return std::min(std::max(v, 0.0f), 1.0f); }
+
+// lightnet-train/src/detect.rs:1035-1125 decode_modern_detections (the candidates of one image's head, before its NMS), with
+// lightnet-layers/src/modern_yolo/cpu.rs:461-475 decode_yolox_box, :493-527 modern_objectness / modern_class_score and
+// detect.rs:1414-1447 correct_bbox.  The emission order is (cell, class), as the reference's loops run.
+static void decode_modern_head(const float* data, const HeadSpec& hs, int net_w, int net_h, int img_w, int img_h, float thr,
+                               bool letterbox, bool det_exp, std::vector<Det>& out) {
+    const int stride = hs.gw * hs.gh;
+    const float iw = (float)img_w, ih = (float)img_h, nw = (float)net_w, nh = (float)net_h;
+    float new_w, new_h;
+    if (letterbox) {
+        if (nw / iw < nh / ih) { new_w = nw; new_h = ih * nw / iw; }
+        else { new_w = iw * nh / ih; new_h = nh; }
+    } else { new_w = nw; new_h = nh; }
+    const float delta_w = nw - new_w, delta_h = nh - new_h, ratio_w = new_w / nw, ratio_h = new_h / nh;
+    for (int idx = 0; idx < stride; ++idx) {
+        const int row = idx / hs.gw, col = idx % hs.gw;
+        const float obj = clamp01(finite_or_zero(data[(size_t)4 * stride + idx]));
+        bool have = false;
+        float bx = 0, by = 0, bw = 0, bh = 0;
+        for (int c = 0; c < hs.classes; ++c) {
+            const float cls = clamp01(finite_or_zero(data[(size_t)(5 + c) * stride + idx]));
+            // the distribution heads gate on the class score, not on the product (detect.rs:1158-1162)
+            const float score = hs.kind == 2 ? std::max(cls, obj * cls) : obj * cls;
+            if (score <= thr) continue;
+            if (!have) {
+                have = true;
+                if (hs.kind == 2) {
+                    bx = data[idx]; by = data[(size_t)stride + idx]; bw = data[(size_t)2 * stride + idx]; bh = data[(size_t)3 * stride + idx];
+                } else {
+                    const float tw = std::min(std::max(finite_or_zero(data[(size_t)2 * stride + idx]), -10.0f), 10.0f);
+                    const float th = std::min(std::max(finite_or_zero(data[(size_t)3 * stride + idx]), -10.0f), 10.0f);
+                    bx = ((float)col + finite_or_zero(data[idx])) / (float)hs.gw;
+                    by = ((float)row + finite_or_zero(data[(size_t)stride + idx])) / (float)hs.gh;
+                    bw = (det_exp ? det_expf(tw) : std::exp(tw)) / (float)hs.gw;
+                    bh = (det_exp ? det_expf(th) : std::exp(th)) / (float)hs.gh;
+                    bx = finite_or_zero(bx); by = finite_or_zero(by);                                      // sanitize (cpu.rs:212-217)
+                    bw = std::max(finite_or_zero(bw), 1e-6f); bh = std::max(finite_or_zero(bh), 1e-6f);
+                }
+                bx = (bx - delta_w / 2.0f / nw) / ratio_w;
+                by = (by - delta_h / 2.0f / nh) / ratio_h;
+                bw /= ratio_w;
+                bh /= ratio_h;
+                bx *= iw; by *= ih; bw *= iw; bh *= ih;
+            }
+            out.push_back(Det{c, score, obj, bx, by, bw, bh});
+        }
+    }
+}
 
 // lightnet-train/src/detect.rs:934-1016 decode_yolo_head, :1288-1322 decode_bbox,
 // :1414-1447 correct_bbox.  `data` is one image's head, channel-major
 // [anchor*(5+classes)+entry][gh*gw].  det_exp selects det_expf instead of libm.
 static void decode_head(const float* data, const HeadSpec& hs, int net_w, int net_h, int img_w, int img_h, float thr,
                         bool letterbox, bool det_exp, std::vector<Det>& out) {
+    if (hs.kind != 0) { decode_modern_head(data, hs, net_w, net_h, img_w, img_h, thr, letterbox, det_exp, out); return; }
     const int stride = hs.gw * hs.gh, epa = hs.classes + 5;
     const bool nc = hs.new_coords != 0;
     const float iw = (float)img_w, ih = (float)img_h, nw = (float)net_w, nh = (float)net_h;
@@ -1349,6 +1404,56 @@ int orc_net_detect(void* h, int source, int b, int img_w, int img_h, float thr, 
     ORC_CATCH(-1)
 }
 
+// lightnet-cuda/src/lib.rs:4884-4915 modern_yolo_forward_f32 (= modern_yolo/cpu.rs:268-281 activate_modern_output): every entry
+// sanitised, the trailing 1 + classes planes through a sigmoid of the logit clamped to [-30, 30].  In place, NCHW.
+int orc_modern_activate(float* x, int batch, int channels, int spatial, int classes) {
+    const int class_begin = std::max(channels - (classes + 1), 0);
+    for (int b = 0; b < batch; ++b)
+        for (int c = 0; c < channels; ++c)
+            for (int i = 0; i < spatial; ++i) {
+                float& v = x[((size_t)b * channels + c) * spatial + i];
+                if (!std::isfinite(v)) v = 0.0f;
+                if (c >= class_begin) v = 1.0f / (1.0f + std::exp(-std::min(std::max(v, -30.0f), 30.0f)));
+            }
+    return 0;
+}
+
+// lightnet-cuda-oxide/src/kernels/dense_loss.rs:788-812 modern_yolo_predecode with modern_yolo/cpu.rs:283-308 dfl_expectation,
+// :340-362 box_from_corners, :364-387 decode_dfl_box: an activated [ppyoloe] / [yolonas] head [batch, coords + 1 + classes, h, w]
+// -> [batch, 5 + classes, h, w]: the final centre-size box, then the objectness and class planes copied.
+int orc_modern_predecode(const float* act, float* out, int batch, int w, int h, int classes, int coords) {
+    const int s = w * h, bins = std::max(coords / 4, 2), cin = coords + 1 + classes, cout = 5 + classes;
+    const float eps = 1e-8f;
+    for (int b = 0; b < batch; ++b)
+        for (int loc = 0; loc < s; ++loc) {
+            const float* x = act + (size_t)b * cin * s + loc;
+            float side[4];
+            for (int sd = 0; sd < 4; ++sd) {
+                float mx = -INFINITY;
+                for (int k = 0; k < bins; ++k) mx = std::max(mx, finite_or_zero(x[(size_t)(sd * bins + k) * s]));
+                float denom = 0.0f, expected = 0.0f;
+                for (int k = 0; k < bins; ++k) {
+                    const float e = std::exp(std::min(std::max(finite_or_zero(x[(size_t)(sd * bins + k) * s]) - mx, -60.0f), 60.0f));
+                    denom += e;
+                    expected += (float)k * e;
+                }
+                side[sd] = expected / std::max(denom, eps);
+            }
+            const int row = loc / w, col = loc % w;
+            const float cx = (float)col + 0.5f, cy = (float)row + 0.5f;
+            float left = finite_or_zero((cx - side[0]) / (float)w), top = finite_or_zero((cy - side[1]) / (float)h);
+            float right = finite_or_zero((cx + side[2]) / (float)w), bottom = finite_or_zero((cy + side[3]) / (float)h);
+            if (right < left) std::swap(left, right);
+            if (bottom < top) std::swap(top, bottom);
+            float bx = finite_or_zero(0.5f * (left + right)), by = finite_or_zero(0.5f * (top + bottom));
+            float bw = std::max(finite_or_zero(std::max(right - left, 1e-6f)), 1e-6f), bh = std::max(finite_or_zero(std::max(bottom - top, 1e-6f)), 1e-6f);
+            float* o = out + (size_t)b * cout * s + loc;
+            o[0] = bx; o[(size_t)s] = by; o[(size_t)2 * s] = bw; o[(size_t)3 * s] = bh;
+            for (int e = 0; e < classes + 1; ++e) o[(size_t)(4 + e) * s] = x[(size_t)(coords + e) * s];
+        }
+    return 0;
+}
+
 // Standalone decode+NMS of one image given raw head tensors.
 // meta per head (8 floats): gw, gh, classes, n_anchor, scale_x_y, new_coords, then
 // anchors are passed in `anchors` as consecutive (w,h) pairs per head.
@@ -1362,7 +1467,7 @@ int orc_decode_nms(int n_heads, const float* const* heads, const float* meta, co
     for (int k = 0; k < n_heads; ++k) {
         const float* m = meta + 8 * k;
         specs[k].gw = (int)m[0]; specs[k].gh = (int)m[1]; specs[k].classes = (int)m[2]; specs[k].n_anchor = (int)m[3];
-        specs[k].scale_x_y = m[4]; specs[k].new_coords = (int)m[5];
+        specs[k].scale_x_y = m[4]; specs[k].new_coords = (int)m[5]; specs[k].kind = (int)m[6];
         specs[k].anchors_wh = a;
         a += 2 * specs[k].n_anchor;
     }
@@ -1385,7 +1490,7 @@ int orc_decode_only(int n_heads, const float* const* heads, const float* meta, c
         const float* m = meta + 8 * k;
         HeadSpec hs;
         hs.gw = (int)m[0]; hs.gh = (int)m[1]; hs.classes = (int)m[2]; hs.n_anchor = (int)m[3];
-        hs.scale_x_y = m[4]; hs.new_coords = (int)m[5]; hs.anchors_wh = a;
+        hs.scale_x_y = m[4]; hs.new_coords = (int)m[5]; hs.kind = (int)m[6]; hs.anchors_wh = a;
         a += 2 * hs.n_anchor;
         decode_head(heads[k], hs, net_w, net_h, img_w, img_h, thr, letterbox != 0, det_exp != 0, d);
     }

@@ -251,13 +251,14 @@ class Net:
 
 def _head_args(heads, specs):
     """heads: list of float32 arrays (one image each, [A*(5+cls), gh, gw]); specs: list of dicts
-    {gw, gh, classes, anchors:[(w,h),...], scale_x_y, new_coords}."""
+    {gw, gh, classes, anchors:[(w,h),...], scale_x_y, new_coords, kind}; kind 1 = an activated [yolox] head, 2 = a distribution
+    head after modern_predecode (both take one dummy anchor)."""
     arrs = [np.ascontiguousarray(h, np.float32) for h in heads]
     ptrs = (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
     meta = np.zeros((len(specs), 8), np.float32)
     anchors = []
     for k, s in enumerate(specs):
-        meta[k, :6] = [s["gw"], s["gh"], s["classes"], len(s["anchors"]), s.get("scale_x_y", 1.0), s.get("new_coords", 0)]
+        meta[k, :7] = [s["gw"], s["gh"], s["classes"], len(s["anchors"]), s.get("scale_x_y", 1.0), s.get("new_coords", 0), s.get("kind", 0)]
         for a in s["anchors"]:
             anchors += [a[0], a[1]]
     return arrs, ptrs, meta, np.asarray(anchors, np.float32)
@@ -284,6 +285,28 @@ def decode_only(heads, specs, net_w, net_h, img_w, img_h, thr, letterbox=False, 
     if n > max_out:
         raise OracleError("decode_only: %d candidates exceed max_out" % n)
     return out[:n].copy()
+
+
+def modern_activate(x, classes):
+    """modern_yolo_forward_f32 (lightnet-cuda/src/lib.rs:4884): NCHW head -> sanitised, objectness and classes through a sigmoid."""
+    y = np.ascontiguousarray(x, np.float32).copy()
+    b, c, h, w = y.shape
+    L = lib()
+    L.orc_modern_activate.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
+    L.orc_modern_activate(_p(y), b, c, h * w, classes)
+    return y
+
+
+def modern_predecode(act, classes, coords):
+    """modern_yolo_predecode (lightnet-cuda-oxide/src/kernels/dense_loss.rs:788): [B, coords + 1 + classes, H, W] -> [B, 5 + classes, H, W]."""
+    a = np.ascontiguousarray(act, np.float32)
+    b, c, h, w = a.shape
+    assert c == coords + 1 + classes
+    out = np.zeros((b, 5 + classes, h, w), np.float32)
+    L = lib()
+    L.orc_modern_predecode.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+    L.orc_modern_predecode(_p(a), _p(out), b, w, h, classes, coords)
+    return out
 
 
 def nms_records(recs, nms, top_k=0, skip_pass1=False, by_class=False):

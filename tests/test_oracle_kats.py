@@ -445,3 +445,61 @@ def test_image_letterbox_kats():
     red = orc.image_from_u8(np.array([[[255, 0, 0], [255, 0, 0]]], np.uint8))
     lb = orc.image_letterbox(red, 2, 2)
     assert lb.shape == (3, 2, 2) and abs(lb.ravel()[0] - 1.0) < 0.01 and abs(lb.ravel()[2] - 0.5) < 0.01
+
+
+# ---- modern anchor-free heads: the reference's own vectors (lightnet-train/src/detect.rs:2422-2600) -------------------------
+def _yolox_spec():
+    return [dict(gw=4, gh=4, classes=2, anchors=[(1, 1)], kind=1)]
+
+
+def test_modern_yolox_decodes_a_confident_box():
+    # detect.rs:2423-2470 yolox_decodes_a_confident_box: the vector is passed to the decoder as it stands (the decoder clamps
+    # objectness and class entries to [0, 1])
+    data = np.zeros((7, 4, 4), np.float32)
+    data[0, 2, 1] = 1.0
+    data[1, 2, 1] = 2.0
+    data[2, 2, 1] = np.log(np.float32(4.0))
+    data[3, 2, 1] = np.log(np.float32(4.0))
+    data[4, 2, 1] = 10.0
+    data[5, 2, 1] = 10.0
+    for det_exp in (False, True):
+        d = orc.decode_nms([data], _yolox_spec(), 16, 16, 16, 16, 0.3, 0.45, False, det_exp=det_exp)
+        assert d.shape[0] == 1
+        assert d[0, 0] == 0 and d[0, 1] > 0.99
+        assert np.allclose(d[0, 3:7], [8.0, 16.0, 16.0, 16.0], atol=1e-3)
+
+
+def test_modern_threshold_filters_and_nms_deduplicates():
+    # detect.rs:2472-2512 the_confidence_threshold_filters_and_nms_deduplicates
+    data = np.zeros((7, 4, 4), np.float32)
+    for loc in (0, 1):
+        data[2, 0, loc] = np.log(np.float32(4.0))
+        data[3, 0, loc] = np.log(np.float32(4.0))
+        data[4, 0, loc] = 0.99
+        data[6, 0, loc] = 0.98
+    d = orc.decode_nms([data], _yolox_spec(), 16, 16, 16, 16, 0.9, 0.45, False)
+    assert d.shape[0] == 1 and d[0, 0] == 1
+    assert orc.decode_nms([data], _yolox_spec(), 16, 16, 16, 16, 0.995, 0.45, False).shape[0] == 0
+
+
+def test_modern_distribution_head_decodes_through_the_dfl_expectation():
+    # detect.rs:2557-2600 the_distribution_heads_decode_through_the_dfl_expectation: 4x4 grid, one class, reg_max = 3
+    bins, coords, classes = 4, 16, 1
+    data = np.zeros((1, coords + 1 + classes, 4, 4), np.float32)
+    row, col = 2, 1
+    for side in range(4):
+        data[0, side * bins + 2, row, col] = 40.0
+    data[0, coords, row, col] = 40.0
+    data[0, coords + 1, row, col] = 40.0
+    pre = orc.modern_predecode(data, classes, coords)
+    assert pre.shape == (1, 5 + classes, 4, 4)
+    spec = [dict(gw=4, gh=4, classes=1, anchors=[(1, 1)], kind=2)]
+    d = orc.decode_nms([pre[0]], spec, 16, 16, 16, 16, 0.3, 0.45, False)
+    assert d.shape[0] == 1
+    assert np.allclose(d[0, 3:6], [6.0, 10.0, 16.0], atol=1e-2)
+    # the activation of the head's forward (lib.rs:4884) leaves the same detection: sigmoid(40) rounds to 1, and the other
+    # cells' class score sigmoid(0) = 0.5 stays under a threshold of 0.6
+    act = orc.modern_activate(data, classes)
+    assert act[0, coords, row, col] == 1.0 and act[0, coords, 0, 0] == 0.5 and act[0, 2, row, col] == 40.0
+    d2 = orc.decode_nms([orc.modern_predecode(act, classes, coords)[0]], spec, 16, 16, 16, 16, 0.6, 0.45, False)
+    assert d2.shape[0] == 1 and np.allclose(d2[0, 3:6], [6.0, 10.0, 16.0], atol=1e-2)
