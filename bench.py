@@ -616,7 +616,10 @@ def main():
     x_np = x_host.numpy()
     x_dev = be.upload_f32(x_np.shape, x_np)
     stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", local_rank))
-    det_args = (args.width, args.height, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE)
+    # the records come back into page-locked host buffers (by DMA, no staging copy), reused from step to step
+    rec_pinned = torch.empty((B, MAX_PER_IMAGE, 7), dtype=torch.float32).pin_memory()
+    cnt_pinned = torch.zeros((B,), dtype=torch.int32).pin_memory()
+    det_args = (args.width, args.height, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE, (rec_pinned.numpy(), cnt_pinned.numpy()))
 
     timed = make_timer(stream, world)
 
@@ -667,7 +670,7 @@ def main():
     flat8, off8, w8, h8 = ln.pack_u8_images(images8)
     flat8_pinned = torch.from_numpy(flat8).pin_memory()
     packed8 = (flat8_pinned.numpy(), off8, w8, h8)
-    u8_call = lambda: net.detect_u8(None, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE, packed=packed8)
+    u8_call = lambda: net.detect_u8(None, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE, packed=packed8, out=det_args[-1])
     for _ in range(args.warmup):
         u8_call()
     ms_u8 = timed(u8_call, args.steps)

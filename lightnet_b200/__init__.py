@@ -622,21 +622,31 @@ class GpuExecutableNetwork:
         self.backend._check(self.lib.ln_net_layer_output(self.h, i, C.byref(h)))
         return Tensor(self.backend, h)
 
-    def _detect(self, fn, src, image_w, image_h, confidence_threshold, nms_threshold, letterbox, top_k, max_per_image):
+    def _out_buffers(self, max_per_image, out):
+        """(records [batch, max_per_image, 7] f32, counts [batch] i32): fresh arrays, or the caller's own (`out`, e.g. page-locked ones
+        that the records then reach by DMA; the returned per-image arrays are views into them, valid until the buffers are reused)."""
+        if out is None:
+            return np.empty((self.batch, max_per_image, 7), np.float32), np.zeros(self.batch, np.int32), True
+        rec, cnt = out
+        if rec.shape != (self.batch, max_per_image, 7) or rec.dtype != np.float32 or not rec.flags["C_CONTIGUOUS"] or \
+                cnt.shape != (self.batch,) or cnt.dtype != np.int32:
+            raise ValueError("out must be (float32 [batch, max_per_image, 7], int32 [batch]) C-contiguous arrays")
+        return rec, cnt, False
+
+    def _detect(self, fn, src, image_w, image_h, confidence_threshold, nms_threshold, letterbox, top_k, max_per_image, out=None):
         iw = np.ascontiguousarray(np.broadcast_to(np.asarray(image_w, np.int32), (self.batch,)))
         ih = np.ascontiguousarray(np.broadcast_to(np.asarray(image_h, np.int32), (self.batch,)))
         opts = ln_detect_options(confidence_threshold, nms_threshold, int(letterbox), top_k, max_per_image)
-        rec = np.zeros((self.batch, max_per_image, 7), np.float32)
-        cnt = np.zeros(self.batch, np.int32)
+        rec, cnt, own = self._out_buffers(max_per_image, out)
         self.backend._check(fn(self.h, src, _ptr(iw), _ptr(ih), C.byref(opts), _ptr(rec), _ptr(cnt)))
-        return [rec[b, :cnt[b]].copy() for b in range(self.batch)]
+        return [rec[b, :cnt[b]].copy() if own else rec[b, :cnt[b]] for b in range(self.batch)]
 
     def detect(self, x, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0,
-               max_per_image=1024):
+               max_per_image=1024, out=None):
         """forward + device decode + NMS for a host batch (what `lightnet-rs detect-image` does per image)."""
         x = np.ascontiguousarray(x, np.float32)
         return self._detect(self.lib.ln_net_detect, _ptr(x), image_w, image_h, confidence_threshold, nms_threshold, letterbox,
-                            top_k, max_per_image)
+                            top_k, max_per_image, out)
 
     def submit(self, x):
         """Enqueues the upload of one host batch (f32 NCHW, C-contiguous; keep it alive and unchanged until the matching collect
@@ -647,36 +657,35 @@ class GpuExecutableNetwork:
         self.backend._check(self.lib.ln_net_submit(self.h, _ptr(x)))
         self._in_flight.append(x)
 
-    def collect(self, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0, max_per_image=1024):
+    def collect(self, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0, max_per_image=1024,
+                out=None):
         """Runs the oldest submitted batch and returns its detections, like detect()."""
         iw = np.ascontiguousarray(np.broadcast_to(np.asarray(image_w, np.int32), (self.batch,)))
         ih = np.ascontiguousarray(np.broadcast_to(np.asarray(image_h, np.int32), (self.batch,)))
         opts = ln_detect_options(confidence_threshold, nms_threshold, int(letterbox), top_k, max_per_image)
-        rec = np.zeros((self.batch, max_per_image, 7), np.float32)
-        cnt = np.zeros(self.batch, np.int32)
+        rec, cnt, own = self._out_buffers(max_per_image, out)
         try:
             self.backend._check(self.lib.ln_net_collect(self.h, _ptr(iw), _ptr(ih), C.byref(opts), _ptr(rec), _ptr(cnt)))
         finally:
             if getattr(self, "_in_flight", None):
                 self._in_flight.pop(0)
-        return [rec[b, :cnt[b]].copy() for b in range(self.batch)]
+        return [rec[b, :cnt[b]].copy() if own else rec[b, :cnt[b]] for b in range(self.batch)]
 
     def detect_device(self, t: Tensor, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0,
-                      max_per_image=1024):
+                      max_per_image=1024, out=None):
         return self._detect(self.lib.ln_net_detect_device, t.h, image_w, image_h, confidence_threshold, nms_threshold, letterbox,
-                            top_k, max_per_image)
+                            top_k, max_per_image, out)
 
     def detect_u8(self, images, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0, max_per_image=1024,
-                  mode=LN_PRE_LETTERBOX, packed=None):
+                  mode=LN_PRE_LETTERBOX, packed=None, out=None):
         """Pre-processing on the device + detect for a batch of uint8 [h, w, 3] images (or `packed` = pack_u8_images(images),
         e.g. kept in pinned memory by a caller that reuses it); boxes come back in each image's own pixel coordinates."""
         flat, offsets, widths, heights = packed if packed is not None else pack_u8_images(images)
         opts = ln_detect_options(confidence_threshold, nms_threshold, int(letterbox), top_k, max_per_image)
-        rec = np.empty((self.batch, max_per_image, 7), np.float32)
-        cnt = np.zeros(self.batch, np.int32)
+        rec, cnt, own = self._out_buffers(max_per_image, out)
         self.backend._check(self.lib.ln_net_detect_u8(self.h, _ptr(flat), _ptr(offsets), _ptr(widths), _ptr(heights), mode, C.byref(opts),
                                                       _ptr(rec), _ptr(cnt)))
-        return [rec[b, :cnt[b]].copy() for b in range(self.batch)]
+        return [rec[b, :cnt[b]].copy() if own else rec[b, :cnt[b]] for b in range(self.batch)]
 
     def set_cuda_graph(self, on: bool):
         self.backend._check(self.lib.ln_net_set_cuda_graph(self.h, int(on)))

@@ -1145,6 +1145,14 @@ int run_decode_nms(ln_ctx* ctx, const YoloParams& p, const Scratch& s, unsigned 
     ctx->launches++;
     LN_Y(cudaGetLastError());
     const size_t rec_bytes = (size_t)B * p.max_per_image * sizeof(ln_detection);
+    // a caller that passes page-locked buffers gets its records by DMA, without the staging copy below
+    if (pinned_stage) {
+        cudaPointerAttributes pa_r, pa_c;
+        if (cudaPointerGetAttributes(&pa_r, records_host) == cudaSuccess && cudaPointerGetAttributes(&pa_c, counts_host) == cudaSuccess &&
+            pa_r.type == cudaMemoryTypeHost && pa_c.type == cudaMemoryTypeHost)
+            pinned_stage = nullptr;
+        (void)cudaGetLastError();  // (an unregistered pointer is not an error here)
+    }
     if (pinned_stage) {
         // through pinned memory: the copy runs at link speed instead of being staged page by page by the driver
         LN_Y(cudaMemcpyAsync(pinned_stage, records, rec_bytes, cudaMemcpyDeviceToHost, ctx->stream));
