@@ -56,6 +56,11 @@ LAYER_CLASS_PROFILES = {
     (3, 1, 256, 512): "profiles/conv_umma_3x3_c256_k512_int8_n128.md",
     (3, 1, 3, 32): "profiles/conv_stem_k3c3_i8_608_n16.md",
     (1, 1, 128, 128): "profiles/conv_umma_1x1_c128_k128_mish_int8_n64.md",
+    (3, 1, 32, 64): "profiles/conv_umma_layer_classes_int8.md",
+    (3, 1, 256, 256): "profiles/conv_umma_layer_classes_int8.md",
+    (1, 1, 128, 64): "profiles/conv_umma_layer_classes_int8.md",
+    (3, 1, 512, 1024): "profiles/conv_umma_layer_classes_int8.md",
+    (1, 1, 256, 256): "profiles/conv_umma_layer_classes_int8.md",
 }
 
 
@@ -710,7 +715,7 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel (%s implicit GEMM, all layers but the first)" % wl["precision"], "achieved": achieved,
                          "peak": peak, "unit": "TOP/s", "frac": achieved / peak,
                          "traffic": None,
-                         "traffic_basis": "not measured at this batch: an ncu capture of all launches of a 64-image step is beyond the size a capture may have; per-launch DRAM bytes of single layers are in the profiles/ summaries named under layer_classes",
+                         "traffic_basis": "not measured at this batch: an ncu capture of all launches of a 64-image step is beyond the size a capture may have; per-launch DRAM bytes of eleven layer classes are in profiles/conv_umma_layer_classes_int8.md: reads equal the algorithmic input bytes in every class (taps and filter tiles re-read L2, not DRAM), writes stay below the output bytes while an output fits in L2",
                          "algorithmic_bytes": conv_bytes_per_image(layers) * B,
                          "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf), "launches_per_step": umma_launches,
                          "peak_mma_loop": mma_peak, "frac_of_mma_loop": achieved / mma_peak if mma_peak > 0 else None,
