@@ -648,6 +648,173 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
     }
 }
 
+// The int8 first layer on the warp-level tensor-core instruction (mma.sync m16n8k32, s8 x s8 -> s32): K = 27 taps padded to 32 is
+// one instruction deep, so there is no pipeline to build -- what the layer costs is quantising the 27 inputs of a pixel and the
+// epilogue of its F outputs.  A warp takes 64 output pixels (two horizontally adjacent ones per thread, as the CUDA-core kernel
+// does): every thread quantises its two patches into a [64 pixels][32 bytes] tile of shared memory, ldmatrix hands the tile to
+// the tensor core 16 pixels at a time, and a thread receives, for two pixels of the 16, the accumulators of filters 8 j + 2 q
+// and 8 j + 2 q + 1 (q = lane % 4): adjacent filters of one pixel, which is what the packed-binary16 epilogue wants, with the
+// {multiplier, bias} of its eight filters in registers for the whole kernel.  Codes go back through the same tile (a pixel's
+// row holds its patch before and its F codes after), so every thread stores the 16-byte pieces of its own two pixels.
+// F is a multiple of 8, at most 32.  Bit-exact accumulators; the epilogue is the one of conv_umma_kernel (exact or fast).
+template <int ACT, bool EXACT>
+__global__ void __launch_bounds__(256) conv_stem_mma_i8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
+                                                               const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
+                                                               int pad, int OH, int OW, float inv_sy, uint8_t* __restrict__ out,
+                                                               int64_t out_pixel_stride, int s2d) {
+    __shared__ __align__(16) uint32_t s_w[32 * 8];          // [filter][8 words]: byte t of a filter = tap (t / 3), channel (t % 3)
+    __shared__ __align__(16) uint8_t s_tile[8][64 * 32];    // per warp
+    for (int i = threadIdx.x; i < 32 * 8; i += blockDim.x) {
+        const int f = i >> 3, wd = i & 7;
+        uint32_t v = 0;
+        for (int j = 0; j < 4; ++j) {
+            const int t = wd * 4 + j;
+            if (f < F && t < 27) v |= (uint32_t)w_oihw[((int64_t)f * 3 + (t % 3)) * 9 + (t / 3)] << (8 * j);
+        }
+        s_w[i] = v;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q = lane & 3, r8 = lane >> 2;
+    const int groups = F >> 3;  // filter groups of 8
+    // B fragments (32 x 8, "col": filter r8 of the group, K words q and q + 4) and the epilogue constants of this thread's filters
+    uint32_t bfrag[4][2];
+    float cm[4][2], cb[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int fb = 8 * j + r8;
+        bfrag[j][0] = j < groups ? s_w[fb * 8 + q] : 0u;
+        bfrag[j][1] = j < groups ? s_w[fb * 8 + q + 4] : 0u;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int f = 8 * j + 2 * q + e;
+            const float2 m = f < F ? mb[f] : make_float2(0.0f, 0.0f);
+            if (EXACT) { cm[j][e] = m.x; cb[j][e] = m.y; }
+            else {  // folded: fma(float with the bits 0x4B400000 + acc, m / s_y, b / s_y - 1.5 * 2^23 * m / s_y) is the pre-activation in code units
+                cm[j][e] = __fmul_rn(m.x, inv_sy);
+                cb[j][e] = __fmaf_rn(-12582912.0f, cm[j][e], __fmul_rn(m.y, inv_sy));
+            }
+        }
+    }
+    uint8_t* tile = s_tile[warp];
+    const uint32_t tile_s = (uint32_t)__cvta_generic_to_shared(tile);
+    const __half2 kh = __float2half2_rn(1.44269504f / inv_sy), inv_h = __float2half2_rn(inv_sy);
+    const int OWP = (OW + 1) / 2;
+    const int total = N * OH * OWP;  // pixel pairs (the launcher checks that this fits 31 bits)
+    const int warps_total = (int)gridDim.x * (int)(blockDim.x >> 5);
+    for (int wbase = ((int)blockIdx.x * (int)(blockDim.x >> 5) + warp) * 32; wbase < total; wbase += warps_total * 32) {
+        const int pp = wbase + lane;
+        const bool have = pp < total;
+        const unsigned ppc = (unsigned)(have ? pp : total - 1);
+        const unsigned rowi = ppc / (unsigned)OWP;  // n * OH + oy
+        const int ox0 = (int)(ppc - rowi * (unsigned)OWP) * 2;
+        const int n = (int)(rowi / (unsigned)OH), oy = (int)(rowi - (unsigned)n * (unsigned)OH);
+        const bool second = ox0 + 1 < OW;
+        // ---- quantise the inputs of the two patches once (they share 3 - stride of their three columns), as one word of three
+        // channel codes per input pixel; taps outside the image contribute nothing: clamped loads, masked words
+        const float* xn = x + (int64_t)n * 3 * H * W;
+        const int plane = H * W;
+        uint32_t trip[3][5];
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+            const int iy = oy * stride + ky - pad;
+            const bool rok = iy >= 0 && iy < H;
+            const int roff = min(max(iy, 0), H - 1) * W;
+#pragma unroll
+            for (int j = 0; j < 5; ++j) {
+                if (j < 3 + stride) {  // (stride is 1 or 2)
+                    const int ix = ox0 * stride + j - pad;
+                    const float* px = xn + roff + min(max(ix, 0), W - 1);
+                    const uint32_t c0 = quant_i8_magic(__ldg(px), inv_sx) & 0xFFu, c1 = quant_i8_magic(__ldg(px + plane), inv_sx) & 0xFFu,
+                                   c2 = quant_i8_magic(__ldg(px + 2 * plane), inv_sx) & 0xFFu;
+                    trip[ky][j] = rok && ix >= 0 && ix < W ? (c0 | (c1 << 8) | (c2 << 16)) : 0u;
+                } else trip[ky][j] = 0u;
+            }
+        }
+        // the patch is the byte stream of nine such triples (tap major); word w takes bytes 4 w .. 4 w + 3 of it
+#pragma unroll
+        for (int px = 0; px < 2; ++px) {
+            uint32_t t9[10];
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap) t9[tap] = stride == 1 ? trip[tap / 3][tap % 3 + px] : trip[tap / 3][tap % 3 + 2 * px];
+            t9[9] = 0u;
+            uint32_t patch[8];
+            patch[7] = 0u;
+#pragma unroll
+            for (int wd = 0; wd < 7; ++wd) {
+                const int b0 = 4 * wd, ta = b0 / 3, off = b0 % 3;  // first byte of the word is byte `off` of triple `ta`
+                // bytes off .. 2 of triple ta, then the first 1 + off bytes of triple ta + 1 (a triple's fourth byte is 0, and so is triple 9)
+                patch[wd] = off == 0 ? __byte_perm(t9[ta], t9[ta + 1], 0x4210) : (off == 1 ? __byte_perm(t9[ta], t9[ta + 1], 0x5421) : __byte_perm(t9[ta], t9[ta + 1], 0x6542));
+            }
+            // (the two 16-byte halves of a row are swapped in rows 4..7 mod 8: rows r and r + 4 then sit in different banks)
+            const int rr = 2 * lane + px, sw = (rr >> 2) & 1;
+            uint4* row = reinterpret_cast<uint4*>(tile + rr * 32);
+            row[sw] = make_uint4(patch[0], patch[1], patch[2], patch[3]);
+            row[sw ^ 1] = make_uint4(patch[4], patch[5], patch[6], patch[7]);
+        }
+        __syncwarp();
+        // ---- 16 pixels at a time through the tensor core, then the epilogue of this thread's 2 x 8 values of the group
+#pragma unroll 1
+        for (int g = 0; g < 4; ++g) {
+            uint32_t a0, a1, a2, a3;
+            // ldmatrix x4: lanes 0-7 address rows 0-7 (bytes 0-15), 8-15 rows 8-15 (bytes 0-15), 16-23 rows 0-7 (bytes 16-31), 24-31 rows 8-15 (bytes 16-31)
+            const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
+            const uint32_t addr = tile_s + (uint32_t)((16 * g + lrow) * 32 + (((lane >> 4) ^ (lrow >> 2)) & 1) * 16);
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(addr));
+            __syncwarp();  // every lane has its fragment: the rows of this group may now take the codes
+            int acc[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
+                if (j < groups)
+                    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                                 : "+r"(acc[j][0]), "+r"(acc[j][1]), "+r"(acc[j][2]), "+r"(acc[j][3])
+                                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bfrag[j][0]), "r"(bfrag[j][1]));
+            }
+            // this thread: pixel rows r8 and r8 + 8 of the group, filters 8 j + 2 q, 8 j + 2 q + 1
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                uint8_t* orow = tile + (16 * g + r8 + 8 * hrow) * 32;
+                const int osw = ((r8 >> 2) & 1) << 4;  // (16 g and 8 hrow do not change bit 2 of the row)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (j >= groups) continue;
+                    const int a_lo = acc[j][2 * hrow], a_hi = acc[j][2 * hrow + 1];
+                    uint32_t two;  // the two code bytes, filter 8 j + 2 q in the low one
+                    if (EXACT) {
+                        // |acc| <= 27 * 127 * 127 < 2^22: adding it to the bits of 1.5 * 2^23 converts exactly
+                        const float v0 = __fmaf_rn(__fadd_rn(__int_as_float(0x4B400000 + a_lo), -12582912.0f), cm[j][0], cb[j][0]);
+                        const float v1 = __fmaf_rn(__fadd_rn(__int_as_float(0x4B400000 + a_hi), -12582912.0f), cm[j][1], cb[j][1]);
+                        const uint32_t u0 = quant_i8_magic(ln_epilogue_act<true>(ACT, v0), inv_sy), u1 = quant_i8_magic(ln_epilogue_act<true>(ACT, v1), inv_sy);
+                        two = (u0 & 0xFFu) | ((u1 & 0xFFu) << 8);
+                    } else {
+                        const float t0 = __fmaf_rn(__int_as_float(0x4B400000 + a_lo), cm[j][0], cb[j][0]);
+                        const float t1 = __fmaf_rn(__int_as_float(0x4B400000 + a_hi), cm[j][1], cb[j][1]);
+                        const uint32_t c2 = ln_h2_code<ACT>(t0, t1, kh, inv_h);  // code bytes in the low byte of each half
+                        two = __byte_perm(c2, 0u, 0x4420);
+                    }
+                    *reinterpret_cast<uint16_t*>(orow + ((8 * j + 2 * q) ^ osw)) = (uint16_t)two;
+                }
+            }
+        }
+        __syncwarp();
+        // ---- every thread stores the codes of its own two pixels
+        if (have) {
+            uint8_t* op = s2d ? out + ((((int64_t)n * (OH >> 1) + (oy >> 1)) * (OW >> 1) + (ox0 >> 1)) * 4 + (oy & 1) * 2) * out_pixel_stride
+                              : out + (((int64_t)n * OH + oy) * OW + ox0) * out_pixel_stride;
+            const uint4* r0 = reinterpret_cast<const uint4*>(tile + (2 * lane) * 32);
+            const uint4* r1 = reinterpret_cast<const uint4*>(tile + (2 * lane + 1) * 32);
+            const int sw0 = ((2 * lane) >> 2) & 1;  // rows 2 lane and 2 lane + 1 share their bit 2
+            for (int fg = 0; fg * 16 < F; ++fg) {
+                uint4 v0 = r0[fg ^ sw0], v1 = r1[fg ^ sw0];
+                if (F - fg * 16 < 16) { v0.z = v0.w = 0u; v1.z = v1.w = 0u; }  // eight real filters in this half: the rest of the 16 bytes is padding
+                *reinterpret_cast<uint4*>(op + fg * 16) = v0;
+                if (second) *reinterpret_cast<uint4*>(op + out_pixel_stride + fg * 16) = v1;
+            }
+        }
+        __syncwarp();
+    }
+}
+
 // The same first layer in FP8 E4M3, one thread per pair of adjacent output pixels: the 27 input values of each are rounded
 // to E4M3 once and kept as floats (products of two E4M3 values are exact in f32), every filter costs 27 FMAs per pixel
 // against decoded weights read (broadcast) from shared memory once for both.
@@ -812,6 +979,29 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
             conv_stem_k3c3_f8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, \
                                                                                    OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);     \
     } while (0)
+        // int8 with 8, 16, 24 or 32 filters: the tensor-core form (LN_STEM_MMA=0 keeps the CUDA-core kernel, for A/B measurements)
+        const char* stem_env = getenv("LN_STEM_MMA");
+        // (its fast epilogue drops the lower clamp of the activations that are bounded below: needs 0.31 / s_y <= 127)
+        if (kind == LN_KIND_I8 && F % 8 == 0 && F <= 32 && F >= 8 && (stride == 1 || stride == 2) && (int64_t)N * OH * ((OW + 1) / 2) < (1ll << 30) &&
+            (exact || inv_sy <= 400.0f) && !(stem_env && atoi(stem_env) == 0)) {
+            const int64_t warps = ((int64_t)N * OH * ((OW + 1) / 2) + 31) / 32;
+            int64_t blocks = (warps + 7) / 8;
+            const int64_t cap = (int64_t)ctx->sm_count * 8;
+            if (blocks > cap) blocks = cap;
+#define LN_STEM_MMA(A, E) conv_stem_mma_i8_kernel<A, E><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out)
+            switch (act) {
+                case LN_ACT_LINEAR: if (exact) LN_STEM_MMA(LN_ACT_LINEAR, true); else LN_STEM_MMA(LN_ACT_LINEAR, false); break;
+                case LN_ACT_LEAKY: if (exact) LN_STEM_MMA(LN_ACT_LEAKY, true); else LN_STEM_MMA(LN_ACT_LEAKY, false); break;
+                case LN_ACT_RELU: if (exact) LN_STEM_MMA(LN_ACT_RELU, true); else LN_STEM_MMA(LN_ACT_RELU, false); break;
+                case LN_ACT_MISH: if (exact) LN_STEM_MMA(LN_ACT_MISH, true); else LN_STEM_MMA(LN_ACT_MISH, false); break;
+                case LN_ACT_SWISH: if (exact) LN_STEM_MMA(LN_ACT_SWISH, true); else LN_STEM_MMA(LN_ACT_SWISH, false); break;
+                case LN_ACT_LOGISTIC: if (exact) LN_STEM_MMA(LN_ACT_LOGISTIC, true); else LN_STEM_MMA(LN_ACT_LOGISTIC, false); break;
+                default: return ln_fail(ctx, LN_ERR_UNSUPPORTED, "first-layer convolution: activation %d", act);
+            }
+#undef LN_STEM_MMA
+            LN_LAUNCHED(ctx);
+            return LN_OK;
+        }
         switch (act) {
             case LN_ACT_LINEAR: if (exact) LN_STEM3(LN_ACT_LINEAR, true); else LN_STEM3(LN_ACT_LINEAR, false); break;
             case LN_ACT_LEAKY: if (exact) LN_STEM3(LN_ACT_LEAKY, true); else LN_STEM3(LN_ACT_LEAKY, false); break;
