@@ -648,7 +648,7 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
     }
 }
 
-// The int8 first layer on the warp-level tensor-core instruction (mma.sync m16n8k32, s8 x s8 -> s32): K = 27 taps padded to 32 is
+// The first layer on the warp-level tensor-core instruction (mma.sync m16n8k32, s8 x s8 -> s32): K = 27 taps padded to 32 is
 // one instruction deep, so there is no pipeline to build -- what the layer costs is quantising the 27 inputs of a pixel and the
 // epilogue of its F outputs.  A warp takes 64 output pixels (two horizontally adjacent ones per thread, as the CUDA-core kernel
 // does): every thread quantises its two patches into a [64 pixels][32 bytes] tile of shared memory, ldmatrix hands the tile to
@@ -657,8 +657,10 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
 // {multiplier, bias} of its eight filters in registers for the whole kernel.  Codes go back through the same tile (a pixel's
 // row holds its patch before and its F codes after), so every thread stores the 16-byte pieces of its own two pixels.
 // F is a multiple of 8, at most 32.  Bit-exact accumulators; the epilogue is the one of conv_umma_kernel (exact or fast).
-template <int ACT, bool EXACT>
-__global__ void __launch_bounds__(256) conv_stem_mma_i8_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
+// KIND = LN_KIND_F8: the same with E4M3 codes and f32 accumulation (mma.sync ... f32.e4m3.e4m3.f32); the epilogue is the general one
+// (activation in f32, exact or with the hardware exponential, E4M3 code of a / s_y).
+template <int KIND, int ACT, bool EXACT>
+__global__ void __launch_bounds__(256) conv_stem_mma_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
                                                                const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
                                                                int pad, int OH, int OW, float inv_sy, uint8_t* __restrict__ out,
                                                                int64_t out_pixel_stride, int s2d) {
@@ -688,7 +690,7 @@ __global__ void __launch_bounds__(256) conv_stem_mma_i8_kernel(const float* __re
         for (int e = 0; e < 2; ++e) {
             const int f = 8 * j + 2 * q + e;
             const float2 m = f < F ? mb[f] : make_float2(0.0f, 0.0f);
-            if (EXACT) { cm[j][e] = m.x; cb[j][e] = m.y; }
+            if (EXACT || KIND != LN_KIND_I8) { cm[j][e] = m.x; cb[j][e] = m.y; }
             else {  // folded: fma(float with the bits 0x4B400000 + acc, m / s_y, b / s_y - 1.5 * 2^23 * m / s_y) is the pre-activation in code units
                 cm[j][e] = __fmul_rn(m.x, inv_sy);
                 cb[j][e] = __fmaf_rn(-12582912.0f, cm[j][e], __fmul_rn(m.y, inv_sy));
@@ -724,8 +726,16 @@ __global__ void __launch_bounds__(256) conv_stem_mma_i8_kernel(const float* __re
                 if (j < 3 + stride) {  // (stride is 1 or 2)
                     const int ix = ox0 * stride + j - pad;
                     const float* px = xn + roff + min(max(ix, 0), W - 1);
-                    const uint32_t c0 = quant_i8_magic(__ldg(px), inv_sx) & 0xFFu, c1 = quant_i8_magic(__ldg(px + plane), inv_sx) & 0xFFu,
-                                   c2 = quant_i8_magic(__ldg(px + 2 * plane), inv_sx) & 0xFFu;
+                    uint32_t c0, c1, c2;
+                    if (KIND == LN_KIND_I8) {
+                        c0 = quant_i8_magic(__ldg(px), inv_sx) & 0xFFu;
+                        c1 = quant_i8_magic(__ldg(px + plane), inv_sx) & 0xFFu;
+                        c2 = quant_i8_magic(__ldg(px + 2 * plane), inv_sx) & 0xFFu;
+                    } else {
+                        c0 = float_to_e4m3(__fmul_rn(__ldg(px), inv_sx));
+                        c1 = float_to_e4m3(__fmul_rn(__ldg(px + plane), inv_sx));
+                        c2 = float_to_e4m3(__fmul_rn(__ldg(px + 2 * plane), inv_sx));
+                    }
                     trip[ky][j] = rok && ix >= 0 && ix < W ? (c0 | (c1 << 8) | (c2 << 16)) : 0u;
                 } else trip[ky][j] = 0u;
             }
@@ -761,14 +771,20 @@ __global__ void __launch_bounds__(256) conv_stem_mma_i8_kernel(const float* __re
             const uint32_t addr = tile_s + (uint32_t)((16 * g + lrow) * 32 + (((lane >> 4) ^ (lrow >> 2)) & 1) * 16);
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(addr));
             __syncwarp();  // every lane has its fragment: the rows of this group may now take the codes
-            int acc[4][4];
+            int acc[4][4];  // int32 accumulators, or the bits of f32 ones
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
-                if (j < groups)
-                    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                                 : "+r"(acc[j][0]), "+r"(acc[j][1]), "+r"(acc[j][2]), "+r"(acc[j][3])
-                                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bfrag[j][0]), "r"(bfrag[j][1]));
+                if (j < groups) {
+                    if (KIND == LN_KIND_I8)
+                        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                                     : "+r"(acc[j][0]), "+r"(acc[j][1]), "+r"(acc[j][2]), "+r"(acc[j][3])
+                                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bfrag[j][0]), "r"(bfrag[j][1]));
+                    else
+                        asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                                     : "+r"(acc[j][0]), "+r"(acc[j][1]), "+r"(acc[j][2]), "+r"(acc[j][3])
+                                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bfrag[j][0]), "r"(bfrag[j][1]));
+                }
             }
             // this thread: pixel rows r8 and r8 + 8 of the group, filters 8 j + 2 q, 8 j + 2 q + 1
 #pragma unroll
@@ -780,7 +796,11 @@ __global__ void __launch_bounds__(256) conv_stem_mma_i8_kernel(const float* __re
                     if (j >= groups) continue;
                     const int a_lo = acc[j][2 * hrow], a_hi = acc[j][2 * hrow + 1];
                     uint32_t two;  // the two code bytes, filter 8 j + 2 q in the low one
-                    if (EXACT) {
+                    if (KIND != LN_KIND_I8) {
+                        const float v0 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(__int_as_float(a_lo), cm[j][0], cb[j][0]));
+                        const float v1 = ln_epilogue_act<EXACT>(ACT, __fmaf_rn(__int_as_float(a_hi), cm[j][1], cb[j][1]));
+                        two = (uint32_t)float_to_e4m3(__fmul_rn(v0, inv_sy)) | ((uint32_t)float_to_e4m3(__fmul_rn(v1, inv_sy)) << 8);
+                    } else if (EXACT) {
                         // |acc| <= 27 * 127 * 127 < 2^22: adding it to the bits of 1.5 * 2^23 converts exactly
                         const float v0 = __fmaf_rn(__fadd_rn(__int_as_float(0x4B400000 + a_lo), -12582912.0f), cm[j][0], cb[j][0]);
                         const float v1 = __fmaf_rn(__fadd_rn(__int_as_float(0x4B400000 + a_hi), -12582912.0f), cm[j][1], cb[j][1]);
@@ -979,16 +999,24 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
             conv_stem_k3c3_f8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, \
                                                                                    OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);     \
     } while (0)
-        // int8 with 8, 16, 24 or 32 filters: the tensor-core form (LN_STEM_MMA=0 keeps the CUDA-core kernel, for A/B measurements)
+        // 8, 16, 24 or 32 filters: the tensor-core form (LN_STEM_MMA=0 keeps the CUDA-core kernels, for A/B measurements)
         const char* stem_env = getenv("LN_STEM_MMA");
         // (its fast epilogue drops the lower clamp of the activations that are bounded below: needs 0.31 / s_y <= 127)
-        if (kind == LN_KIND_I8 && F % 8 == 0 && F <= 32 && F >= 8 && (stride == 1 || stride == 2) && (int64_t)N * OH * ((OW + 1) / 2) < (1ll << 30) &&
-            (exact || inv_sy <= 400.0f) && !(stem_env && atoi(stem_env) == 0)) {
+        if (F % 8 == 0 && F <= 32 && F >= 8 && (stride == 1 || stride == 2) && (int64_t)N * OH * ((OW + 1) / 2) < (1ll << 30) &&
+            (kind != LN_KIND_I8 || exact || inv_sy <= 400.0f) && !(stem_env && atoi(stem_env) == 0)) {
             const int64_t warps = ((int64_t)N * OH * ((OW + 1) / 2) + 31) / 32;
             int64_t blocks = (warps + 7) / 8;
             const int64_t cap = (int64_t)ctx->sm_count * 8;
             if (blocks > cap) blocks = cap;
-#define LN_STEM_MMA(A, E) conv_stem_mma_i8_kernel<A, E><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out)
+#define LN_STEM_MMA(A, E)                                                                                                                          \
+    do {                                                                                                                                           \
+        if (kind == LN_KIND_I8)                                                                                                                    \
+            conv_stem_mma_kernel<LN_KIND_I8, A, E><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
+                                                                                        OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);  \
+        else                                                                                                                                       \
+            conv_stem_mma_kernel<LN_KIND_F8, A, E><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
+                                                                                        OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);  \
+    } while (0)
             switch (act) {
                 case LN_ACT_LINEAR: if (exact) LN_STEM_MMA(LN_ACT_LINEAR, true); else LN_STEM_MMA(LN_ACT_LINEAR, false); break;
                 case LN_ACT_LEAKY: if (exact) LN_STEM_MMA(LN_ACT_LEAKY, true); else LN_STEM_MMA(LN_ACT_LEAKY, false); break;
