@@ -656,10 +656,10 @@ __global__ void __launch_bounds__(256) conv_stem_k3c3_i8_kernel(const float* __r
 // and 8 j + 2 q + 1 (q = lane % 4): adjacent filters of one pixel, which is what the packed-binary16 epilogue wants, with the
 // {multiplier, bias} of its eight filters in registers for the whole kernel.  Codes go back through the same tile (a pixel's
 // row holds its patch before and its F codes after), so every thread stores the 16-byte pieces of its own two pixels.
-// F is a multiple of 8, at most 32.  Bit-exact accumulators; the epilogue is the one of conv_umma_kernel (exact or fast).
+// F = 8 * GROUPS (16 or 32 are instantiated).  Bit-exact accumulators; the epilogue is the one of conv_umma_kernel (exact or fast).
 // KIND = LN_KIND_F8: the same with E4M3 codes and f32 accumulation (mma.sync ... f32.e4m3.e4m3.f32); the epilogue is the general one
 // (activation in f32, exact or with the hardware exponential, E4M3 code of a / s_y).
-template <int KIND, int ACT, bool EXACT>
+template <int KIND, int ACT, bool EXACT, int GROUPS>
 __global__ void __launch_bounds__(256) conv_stem_mma_kernel(const float* __restrict__ x, float inv_sx, int N, int H, int W,
                                                                const uint8_t* __restrict__ w_oihw, const float2* __restrict__ mb, int F, int stride,
                                                                int pad, int OH, int OW, float inv_sy, uint8_t* __restrict__ out,
@@ -677,7 +677,7 @@ __global__ void __launch_bounds__(256) conv_stem_mma_kernel(const float* __restr
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q = lane & 3, r8 = lane >> 2;
-    const int groups = F >> 3;  // filter groups of 8
+    constexpr int groups = GROUPS;  // filter groups of 8 (F = 8 * GROUPS)
     // B fragments (32 x 8, "col": filter r8 of the group, K words q and q + 4) and the epilogue constants of this thread's filters
     uint32_t bfrag[4][2];
     float cm[4][2], cb[4][2];
@@ -999,10 +999,10 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
             conv_stem_k3c3_f8_kernel<A, E><<<grid3, kThreads, smem3, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, \
                                                                                    OH, OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);     \
     } while (0)
-        // 8, 16, 24 or 32 filters: the tensor-core form (LN_STEM_MMA=0 keeps the CUDA-core kernels, for A/B measurements)
+        // 16 or 32 filters: the tensor-core form (LN_STEM_MMA=0 keeps the CUDA-core kernels, for A/B measurements)
         const char* stem_env = getenv("LN_STEM_MMA");
         // (its fast epilogue drops the lower clamp of the activations that are bounded below: needs 0.31 / s_y <= 127)
-        if (F % 8 == 0 && F <= 32 && F >= 8 && (stride == 1 || stride == 2) && (int64_t)N * OH * ((OW + 1) / 2) < (1ll << 30) &&
+        if ((F == 32 || F == 16) && (stride == 1 || stride == 2) && (int64_t)N * OH * ((OW + 1) / 2) < (1ll << 30) &&
             (kind != LN_KIND_I8 || exact || inv_sy <= 400.0f) && !(stem_env && atoi(stem_env) == 0)) {
             const int64_t warps = ((int64_t)N * OH * ((OW + 1) / 2) + 31) / 32;
             int64_t blocks = (warps + 7) / 8;
@@ -1010,12 +1010,18 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
             if (blocks > cap) blocks = cap;
 #define LN_STEM_MMA(A, E)                                                                                                                          \
     do {                                                                                                                                           \
-        if (kind == LN_KIND_I8)                                                                                                                    \
-            conv_stem_mma_kernel<LN_KIND_I8, A, E><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
-                                                                                        OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);  \
+        if (kind == LN_KIND_I8 && F == 32)                                                                                                         \
+            conv_stem_mma_kernel<LN_KIND_I8, A, E, 4><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
+                                                                                           OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out); \
+        else if (kind == LN_KIND_I8)                                                                                                               \
+            conv_stem_mma_kernel<LN_KIND_I8, A, E, 2><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
+                                                                                           OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out); \
+        else if (F == 32)                                                                                                                          \
+            conv_stem_mma_kernel<LN_KIND_F8, A, E, 4><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
+                                                                                           OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out); \
         else                                                                                                                                       \
-            conv_stem_mma_kernel<LN_KIND_F8, A, E><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
-                                                                                        OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out);  \
+            conv_stem_mma_kernel<LN_KIND_F8, A, E, 2><<<(int)blocks, 256, 0, ctx->stream>>>(x_nchw, inv_sx, N, H, W, (const uint8_t*)w_oihw, mb, F, stride, pad, OH, \
+                                                                                           OW, inv_sy, (uint8_t*)out, out_pixel_stride, s2d_out); \
     } while (0)
             switch (act) {
                 case LN_ACT_LINEAR: if (exact) LN_STEM_MMA(LN_ACT_LINEAR, true); else LN_STEM_MMA(LN_ACT_LINEAR, false); break;
