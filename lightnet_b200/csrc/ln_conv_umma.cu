@@ -845,12 +845,13 @@ __global__ void pack_group_weights_kernel(const uint8_t* __restrict__ w, int cpa
 // The same for a 3x3 stride-1 pad-1 convolution: a 128-byte row is `pack` consecutive pixels of one image row, the output row the
 // same `pack` pixels.  In units of pixel groups the taps are again 3x3 with pad 1; tap (r, s') of output pixel j_out reads input
 // pixel j_in of group X + s' - 1, which is column offset s = pack (s' - 1) + j_in - j_out + 1 of the original 3x3 (zero weight
-// when that is outside 0..2).  w is [fpad][3][3][cpad], w2 [fpad2][3][3][128].
+// when that is outside 0..2).  w is [fpad][3][3][cpad], w2 [fpad2][3][3][pack * cpad].
 __global__ void pack_group_weights_k3_kernel(const uint8_t* __restrict__ w, int cpad, int F, int pack, int fpad2, uint8_t* __restrict__ w2,
                                              const float2* __restrict__ mb, float2* __restrict__ mb2) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 4 bytes of w2
-    if (i >= fpad2 * 9 * 32) return;
-    const int row = i / 288, rem = i - row * 288, tap = rem >> 5, b = (rem & 31) * 4;
+    const int rw = pack * cpad / 4;                      // words of one row of `pack` pixels (32 for a 128-byte row)
+    if (i >= fpad2 * 9 * rw) return;
+    const int row = i / (9 * rw), rem = i - row * 9 * rw, tap = rem / rw, b = (rem - tap * rw) * 4;
     const int r = tap / 3, sp = tap - r * 3;
     const int j_out = row / F, f = row - j_out * F, j_in = b / cpad, c = b - j_in * cpad;
     const int s = pack * (sp - 1) + j_in - j_out + 1;
@@ -984,21 +985,29 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     // sides, nine taps in units of groups (see pack_group_weights_k3_kernel).  The tensor core multiplies mostly zeros -- `pack`
     // times the arithmetic -- but it is idle at these sizes, and the loads become `pack` times fewer 128-byte rows.
     {
-        const int pk = g.cpad < 128 ? 128 / g.cpad : 1;
+        // two pixels per row at most: with 32 channels that is a 64-byte row and 2 x zeros for the tensor core instead of a 128-byte
+        // row and 4 x (3x3 C32 -> K64 at 304x304 x16: 113 -> 103 us, and the 128 virtual filters then run with two issuers)
+        int pk = g.cpad < 128 ? 128 / g.cpad : 1;
+        if (pk > 2) pk = 2;
+        if (const char* e = getenv("LN_CONV_PACK3_MAX")) {  // (A/B measurements: 4, 2 or 1 pixels per row)
+            const int v = atoi(e);
+            if (v >= 1 && v * g.cpad <= 128) pk = v;
+        }
+        const int rb = pk * g.cpad;  // bytes of one row of pk pixels
         if (allow_pack && pack == 1 && pk > 1 && !g.s2d_input && g.k == 3 && g.stride == 1 && g.pad == 1 && g.x_pixel_stride == g.cpad && g.W % pk == 0 &&
             g.OW == g.W && g.OH == g.H && g.out_kind == LN_OUT_Q && g.F % 32 == 0 && pk * g.F <= 256 && (((uintptr_t)g.x) & 127) == 0) {
             const int F2 = pk * g.F, bn2 = ln_conv_choose_bn(F2), fpad2 = (int)ln_round_up(F2, bn2);
-            plan->aux_w_bytes = (size_t)fpad2 * 9 * 128;
+            plan->aux_w_bytes = (size_t)fpad2 * 9 * rb;
             plan->aux_mb_bytes = (size_t)fpad2 * sizeof(float2);
             plan->aux_w = ln_pool_alloc(ctx, plan->aux_w_bytes);
             plan->aux_mb = (float2*)ln_pool_alloc(ctx, plan->aux_mb_bytes);
             if (!plan->aux_w || !plan->aux_mb) return LN_ERR_CUDA;
-            pack_group_weights_k3_kernel<<<(fpad2 * 288 + 255) / 256, 256, 0, ctx->stream>>>((const uint8_t*)g.w, g.cpad, g.F, pk, fpad2, (uint8_t*)plan->aux_w,
+            pack_group_weights_k3_kernel<<<(fpad2 * 9 * (rb / 4) + 255) / 256, 256, 0, ctx->stream>>>((const uint8_t*)g.w, g.cpad, g.F, pk, fpad2, (uint8_t*)plan->aux_w,
                                                                                            plan->mb, plan->aux_mb);
             LN_LAUNCHED(ctx);
             pack = pk;
             g.w = plan->aux_w; g.fpad = fpad2; g.F = F2;
-            g.cpad = 128; g.C = 128; g.x_pixel_stride = 128;
+            g.cpad = rb; g.C = rb; g.x_pixel_stride = rb;
             g.W /= pk; g.OW /= pk;
             mb = plan->aux_mb;
         }
