@@ -882,9 +882,20 @@ F8_CASES = [  # (n, c, h, w, f, k, stride, pad)
     (1, 64, 48, 80, 512, 3, 1, 1),     # row-shifted boxes, weight ring
 ]
 
+F8_TWO_ISSUER_CASES = [  # two or three tiles per CTA; run with the two-issuer kernel forced
+    (8, 128, 76, 76, 128, 3, 1, 1),
+    (9, 256, 38, 38, 512, 1, 1, 0),
+]
+
 # Accumulation-order tolerance of an f32 tensor-core accumulator against the oracle's double sum:
 # |acc - ref| <= F8_ACC_TOL * sum|x||w| per output (products of two E4M3 values are exact in f32).
 F8_ACC_TOL = 2.0 ** -13
+
+
+@pytest.mark.parametrize("case", F8_TWO_ISSUER_CASES)
+def test_f8_conv_two_issuers_matches_oracle(be, case, monkeypatch):
+    monkeypatch.setenv("LN_CONV_PIPES", "2")
+    test_f8_conv_matches_oracle(be, case)
 
 
 @pytest.mark.parametrize("case", F8_CASES)
