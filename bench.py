@@ -8,8 +8,11 @@
 A step is one pass over one batch of `--batch` synthetic images per GPU (uniform [0,1) f32, 608x608x3, larger than
 L2) through the network built from the generated yolov4 cfg with He-normal random weights: forward, device decode
 (threshold 0.25) and per-class NMS (IoU 0.45); the detections land in host memory.  `value` times that with the
-input batch already resident in HBM; `e2e` times the same call given HOST buffers (pinned), so the host->device copy
-of the batch and the device->host read of the detections are inside the timed region.  Batches are independent, so N
+input batch already resident in HBM; `e2e` times the same K batches given as HOST buffers (pinned) through
+`submit`/`collect`, which keep two batches in flight so the host->device copy of one batch runs under the layers of
+the previous one; every step's upload and the device->host read of its detections are inside the timed region.
+`e2e_sync` is the same through the one-call-per-batch `detect` (upload, layers and read-back in series), `e2e_u8` the
+one-call form with 8-bit pixels.  Batches are independent, so N
 GPUs each run their own batch with no collective on the path (weak scaling); timing is CUDA events on the launching
 stream, max over ranks.  One JSON line is printed by rank 0.
 """
