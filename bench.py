@@ -11,8 +11,8 @@ L2) through the network built from the generated yolov4 cfg with He-normal rando
 input batch already resident in HBM; `e2e` times the same K batches given as HOST buffers (pinned) through
 `submit`/`collect`, which keep two batches in flight so the host->device copy of one batch runs under the layers of
 the previous one; every step's upload and the device->host read of its detections are inside the timed region.
-`e2e_sync` is the same through the one-call-per-batch `detect` (upload, layers and read-back in series), `e2e_u8` the
-one-call form with 8-bit pixels.  Batches are independent, so N
+`e2e_sync` is the same through the one-call-per-batch `detect` (upload, layers and read-back in series), `e2e_u8` /
+`e2e_u8_sync` the two forms fed with 8-bit camera images (letterboxed on the device).  Batches are independent, so N
 GPUs each run their own batch with no collective on the path (weak scaling); timing is CUDA events on the launching
 stream, max over ranks.  One JSON line is printed by rank 0.
 """
@@ -681,7 +681,25 @@ def main():
     u8_call = lambda: net.detect_u8(None, CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE, packed=packed8, out=det_args[-1])
     for _ in range(args.warmup):
         u8_call()
-    ms_u8 = timed(u8_call, args.steps)
+    ms_u8_sync = timed(u8_call, args.steps)
+    # the stream of batches again, fed with the 8-bit images (two pinned pixel buffers; upload + letterbox of batch i + 1 run
+    # on the copy stream while batch i goes through the layers)
+    images8b = [rng8.integers(0, 256, (480, 640, 3), dtype=np.uint8) for _ in range(B)]
+    flat8b, off8b, w8b, h8b = ln.pack_u8_images(images8b)
+    flat8b_pinned = torch.from_numpy(flat8b).pin_memory()
+    packs8 = (packed8, (flat8b_pinned.numpy(), off8b, w8b, h8b))
+    u8_args = (CONF_THR, NMS_THR, True, 0, MAX_PER_IMAGE, det_args[-1])
+
+    def stream_of_u8_batches(steps):
+        net.submit_u8(None, packed=packs8[0])
+        for i in range(steps):
+            if i + 1 < steps:
+                net.submit_u8(None, packed=packs8[(i + 1) & 1])
+            pk = packs8[i & 1]
+            net.collect(pk[2], pk[3], *u8_args)
+
+    stream_of_u8_batches(max(args.warmup, 2))
+    ms_u8 = timed(lambda: stream_of_u8_batches(args.steps), 1)
     clocks = sampler.summary()
 
     # roofline of the dominant kernel (tensor-core convolution), from a profiled forward
@@ -712,7 +730,9 @@ def main():
             "e2e_sync": {"value": B * world * args.steps / (ms_sync * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(x_np.nbytes),
                          "api": "ln_net_detect, one synchronous call per batch (the batch is uploaded and run in two parts, %d + %d images, as a two-stage pipeline)" % ((B // 4, B - B // 4) if B >= 16 else (B // 2, B - B // 2))},
             "e2e_u8": {"value": B * world * args.steps / (ms_u8 * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(flat8.nbytes),
-                       "api": "ln_net_detect_u8 (host 8-bit 640x480 RGB images -> device letterbox -> detections)"},
+                       "api": "ln_net_submit_u8 + ln_net_collect on a stream of batches of host 8-bit 640x480 RGB images (device letterbox on the copy stream under the layers of the previous batch)"},
+            "e2e_u8_sync": {"value": B * world * args.steps / (ms_u8_sync * 1e-3), "unit": "images/s", "h2d_bytes_per_step": int(flat8.nbytes),
+                            "api": "ln_net_detect_u8, one synchronous call per batch (upload -> device letterbox -> detections)"},
             "gpu_launches": int(launches),
             "phases_ms": {"layers": fwd_ms, "decode_nms": nms_ms},
             "roofline": {"bound": "tensor", "kernel": "conv_umma_kernel (%s implicit GEMM, all layers but the first)" % wl["precision"], "achieved": achieved,

@@ -336,6 +336,11 @@ int32_t ln_net_detect_device(ln_net* net, const ln_tensor* input, const int32_t*
    is asynchronous).  ln_net_collect runs the oldest submitted batch (layers, decode, NMS) and returns its records like
    ln_net_detect.  LN_ERR_ARG when a third batch is submitted or nothing is left to collect. */
 int32_t ln_net_submit(ln_net* net, const float* input_host);
+/* ln_net_submit for a batch of 8-bit RGB images (the arguments of ln_image_preprocess_u8): the upload of the pixels and the
+   resize to the network's input run on the copy stream, under the layers of the batch submitted before.  `pixels_host` must stay
+   unchanged until the matching ln_net_collect returns; pass that call the images' own widths / heights as image_w / image_h. */
+int32_t ln_net_submit_u8(ln_net* net, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
+                         int32_t mode);
 int32_t ln_net_collect(ln_net* net, const int32_t* image_w, const int32_t* image_h, const ln_detect_options* opts,
                        ln_detection* records_host, int32_t* counts_host);
 /* ln_image_preprocess_u8 (to the network's input size) followed by ln_net_detect_device; the records are scaled to each

@@ -135,6 +135,7 @@ SYMBOLS = {
     "ln_net_detect": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_detect_device": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_submit": (C.c_int32, [_VP, _VP]),
+    "ln_net_submit_u8": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, C.c_int32]),
     "ln_net_collect": (C.c_int32, [_VP, _VP, _VP, _VP, _VP, _VP]),
     "ln_net_last_times": (C.c_int32, [_VP, _VP]),
     "ln_net_set_profile": (C.c_int32, [_VP, C.c_int32]),
@@ -656,6 +657,16 @@ class GpuExecutableNetwork:
         self._in_flight = getattr(self, "_in_flight", [])
         self.backend._check(self.lib.ln_net_submit(self.h, _ptr(x)))
         self._in_flight.append(x)
+
+    def submit_u8(self, images, mode=LN_PRE_LETTERBOX, packed=None):
+        """submit() for a batch of uint8 [h, w, 3] images (or `packed` = pack_u8_images(images), kept alive and unchanged until
+        the matching collect returns): upload and resize run under the layers of the batch submitted before.  Pass the images'
+        own widths / heights to collect()."""
+        packed = packed if packed is not None else pack_u8_images(images)
+        flat, offsets, widths, heights = packed
+        self._in_flight = getattr(self, "_in_flight", [])
+        self.backend._check(self.lib.ln_net_submit_u8(self.h, _ptr(flat), _ptr(offsets), _ptr(widths), _ptr(heights), mode))
+        self._in_flight.append(packed)
 
     def collect(self, image_w, image_h, confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, top_k=0, max_per_image=1024,
                 out=None):

@@ -258,6 +258,8 @@ struct ln_net {
     // ln_net_submit / ln_net_collect: two input slots; `submitted` counts uploads enqueued, `collected` batches run
     ln_tensor* slot_dev[2] = {nullptr, nullptr};
     cudaEvent_t slot_ev[2] = {nullptr, nullptr};
+    void* slot_staging[2] = {nullptr, nullptr};  // 8-bit pixels + metadata of ln_net_submit_u8, back to the pool at collect
+    size_t slot_staging_bytes[2] = {0, 0};
     long long submitted = 0, collected = 0;
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     float times_ms[2] = {0, 0};
@@ -1206,6 +1208,9 @@ int32_t ln_net_destroy(ln_net* net) {
     release_heads(net);
     for (auto*& t : net->ext_heads) { ln_tensor_release(t); t = nullptr; }
     ln_tensor_release(net->input_dev);
+    if (net->copy_stream) cudaStreamSynchronize(net->copy_stream);  // a submitted batch that was never collected
+    for (int i = 0; i < 2; ++i)
+        if (net->slot_staging[i]) ln_pool_free(net->ctx, net->slot_staging[i], net->slot_staging_bytes[i]);
     for (auto& t : net->slot_dev) if (t) ln_tensor_release(t);
     for (auto& e : net->slot_ev) if (e) cudaEventDestroy(e);
     release_pipe(net);
@@ -1475,10 +1480,10 @@ int32_t ln_net_detect(ln_net* net, const float* input_host, const int32_t* image
     return ln_net_detect_device(net, net->input_dev, image_w, image_h, opts, records_host, counts_host);
 }
 
-int32_t ln_net_submit(ln_net* net, const float* input_host) {
-    if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_submit: NULL argument");
+// Common part of the two submit calls: the copy stream, the slot of the next batch and its device tensor.
+static int submit_slot(ln_net* net, const char* who, int* slot_out) {
     ln_ctx* ctx = net->ctx;
-    if (net->submitted - net->collected >= 2) return ln_fail(ctx, LN_ERR_ARG, "ln_net_submit: two batches are in flight already; collect one first");
+    if (net->submitted - net->collected >= 2) return ln_fail(ctx, LN_ERR_ARG, "%s: two batches are in flight already; collect one first", who);
     cudaSetDevice(ctx->device);
     if (!net->copy_stream) {
         LN_CUDA(ctx, cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
@@ -1490,8 +1495,46 @@ int32_t ln_net_submit(ln_net* net, const float* input_host) {
         if (!net->slot_dev[slot]) return LN_ERR_CUDA;
         LN_CUDA(ctx, cudaEventCreateWithFlags(&net->slot_ev[slot], cudaEventDisableTiming));
     }
+    *slot_out = slot;
+    return LN_OK;
+}
+
+int32_t ln_net_submit(ln_net* net, const float* input_host) {
+    if (!net || !input_host) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_submit: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    int slot = 0;
+    int rc = submit_slot(net, "ln_net_submit", &slot);
+    if (rc) return rc;
     // the slot's previous batch was collected (its forward has been synchronised), so nothing reads the buffer any more
     LN_CUDA(ctx, cudaMemcpyAsync(net->slot_dev[slot]->ptr, input_host, (size_t)net->slot_dev[slot]->count() * 4, cudaMemcpyHostToDevice, net->copy_stream));
+    LN_CUDA(ctx, cudaEventRecord(net->slot_ev[slot], net->copy_stream));
+    net->submitted++;
+    return LN_OK;
+}
+
+int32_t ln_net_submit_u8(ln_net* net, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,
+                         int32_t mode) {
+    if (!net || !pixels_host || !offsets || !widths || !heights) return ln_fail(net ? net->ctx : nullptr, LN_ERR_ARG, "ln_net_submit_u8: NULL argument");
+    ln_ctx* ctx = net->ctx;
+    if (net->channels != 3) return ln_fail(ctx, LN_ERR_SHAPE, "ln_net_submit_u8: the network takes %d channels, RGB images have 3", net->channels);
+    int slot = 0;
+    int rc = submit_slot(net, "ln_net_submit_u8", &slot);
+    if (rc) return rc;
+    // The staging block comes from the ctx pool, whose blocks may have been handed back in ctx-stream order: whatever that stream
+    // holds right now goes first (nothing, in a submit / collect loop: every collect ends synchronised).
+    LN_CUDA(ctx, cudaEventRecord(net->slot_ev[slot], ctx->stream));
+    LN_CUDA(ctx, cudaStreamWaitEvent(net->copy_stream, net->slot_ev[slot], 0));
+    // upload and resize both run on the copy stream, under the layers of the batch submitted before
+    rc = ln_image_preprocess_enqueue(ctx, net->copy_stream, pixels_host, offsets, widths, heights, net->batch, mode, net->width, net->height,
+                                     (float*)net->slot_dev[slot]->ptr, &net->slot_staging[slot], &net->slot_staging_bytes[slot]);
+    if (rc) {
+        if (net->slot_staging[slot]) {  // (something may have been enqueued before the failure)
+            cudaStreamSynchronize(net->copy_stream);
+            ln_pool_free(ctx, net->slot_staging[slot], net->slot_staging_bytes[slot]);
+            net->slot_staging[slot] = nullptr;
+        }
+        return rc;
+    }
     LN_CUDA(ctx, cudaEventRecord(net->slot_ev[slot], net->copy_stream));
     net->submitted++;
     return LN_OK;
@@ -1505,8 +1548,16 @@ int32_t ln_net_collect(ln_net* net, const int32_t* image_w, const int32_t* image
     cudaSetDevice(ctx->device);
     const int slot = (int)(net->collected & 1);
     net->collected++;  // (the slot is free again whatever happens below: every path out of ln_net_detect_device has synchronised or failed)
-    LN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, net->slot_ev[slot], 0));
-    return ln_net_detect_device(net, net->slot_dev[slot], image_w, image_h, opts, records_host, counts_host);
+    int rc = LN_OK;
+    cudaError_t e = cudaStreamWaitEvent(ctx->stream, net->slot_ev[slot], 0);
+    if (e != cudaSuccess) rc = ln_fail(ctx, LN_ERR_CUDA, "ln_net_collect: %s", cudaGetErrorString(e));
+    else rc = ln_net_detect_device(net, net->slot_dev[slot], image_w, image_h, opts, records_host, counts_host);
+    if (net->slot_staging[slot]) {
+        if (rc) cudaStreamSynchronize(net->copy_stream);  // an early failure may have left the resize in flight
+        ln_pool_free(ctx, net->slot_staging[slot], net->slot_staging_bytes[slot]);
+        net->slot_staging[slot] = nullptr;
+    }
+    return rc;
 }
 
 int32_t ln_net_detect_u8(ln_net* net, const uint8_t* pixels_host, const int64_t* offsets, const int32_t* widths, const int32_t* heights,

@@ -1077,6 +1077,48 @@ def test_submit_collect_gives_the_detections_of_detect(be):
     assert np.array_equal(net.collect(*args)[0], want[1][0])
 
 
+def test_submit_u8_collect_gives_the_detections_of_detect_u8(be):
+    """8-bit images of mixed sizes through submit_u8 / collect (upload and letterbox on the copy stream, two batches in flight)
+    give, batch for batch, the records of the one-call detect_u8; f32 and 8-bit batches may alternate in the two slots."""
+    batch = 4
+    o = orc.Net(MINI_CFG, batch)
+    blob = synth.he_weights(o.layers(), 62, bn_identity=False)
+    rng = np.random.default_rng(63)
+    sizes = [(48, 64), (96, 80), (33, 57), (120, 120)]
+    sets = [[rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for (h, w) in sizes[i:] + sizes[:i]] for i in range(4)]
+    net = ln.GpuExecutableNetwork(be, MINI_CFG, batch, ln.LN_Q8)
+    net.load_weights(blob)
+    net.calibrate(synth.uniform_images(batch, o.channels, o.height, o.width, 64))
+    opts = (0.2, 0.45, True, 0, 256)
+    want = [net.detect_u8(s, *opts) for s in sets]
+    assert sum(len(d) for w in want for d in w) > 50
+    packs = [ln.pack_u8_images(s) for s in sets]
+    got = []
+    net.submit_u8(None, packed=packs[0])
+    for i in range(len(sets)):
+        if i + 1 < len(sets):
+            net.submit_u8(None, packed=packs[i + 1])
+        got.append(net.collect(packs[i][2], packs[i][3], *opts))
+    for w, g in zip(want, got):
+        for b in range(batch):
+            assert np.array_equal(w[b], g[b])
+    # a float batch in one slot, an 8-bit one in the other
+    x = synth.uniform_images(batch, o.channels, o.height, o.width, 65)
+    want_f = net.detect(x, 640, 480, *opts)
+    net.submit(x)
+    net.submit_u8(sets[1])
+    got_f = net.collect(640, 480, *opts)
+    got_8 = net.collect(packs[1][2], packs[1][3], *opts)
+    for b in range(batch):
+        assert np.array_equal(want_f[b], got_f[b])
+        assert np.array_equal(want[1][b], got_8[b])
+    with pytest.raises(ln.BackendError):
+        net.submit_u8(sets[0], mode=7)
+    net.submit_u8(sets[2])  # the refused call left the slot usable
+    got_2 = net.collect(packs[2][2], packs[2][3], *opts)
+    assert all(np.array_equal(want[2][b], got_2[b]) for b in range(batch))
+
+
 def test_gaussian_yolo_head_is_decoded_like_a_yolo_head(be):
     """[gaussian_yolo] is the same identity layer and the same decode as [yolo] at inference (model.rs:4513-4543,
     exec_forward.rs:908-912, detect.rs:78): a network whose heads carry that name gives the records of the [yolo] one."""
