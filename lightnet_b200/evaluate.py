@@ -144,12 +144,14 @@ def normalise(records: np.ndarray, width: int, height: int) -> np.ndarray:
 
 class ValidationRun:
     """Batched `detector map` pass.  `detect_u8(images, ...)` is `GpuExecutableNetwork.detect_u8` of a network built for `batch`
-    images (or a `sharding.ShardedDetector` around it); images are interleaved 8-bit RGB arrays of any sizes."""
+    images (or a `sharding.ShardedDetector` around it); images are interleaved 8-bit RGB arrays of any sizes.  With `stream` =
+    that network (anything with its `submit_u8` / `collect`), the batches go through the two-slot stream instead: packing, upload
+    and resize of the next batch run while the current one is in the layers; the records are the same."""
 
-    def __init__(self, detect_u8: Callable[..., list], batch: int, classes: int):
+    def __init__(self, detect_u8: Callable[..., list], batch: int, classes: int, stream=None):
         if batch < 1 or classes < 1:
             raise ValueError("batch and classes must be positive")
-        self.detect_u8, self.batch, self.classes = detect_u8, batch, classes
+        self.detect_u8, self.batch, self.classes, self.stream = detect_u8, batch, classes, stream
 
     def detections(self, images: Sequence[np.ndarray], confidence_threshold=0.25, nms_threshold=0.45, letterbox=True, max_per_image=1024):
         """Per image, in order: normalised records.  A short last batch is filled by repeating its last image; the results of the
@@ -158,10 +160,28 @@ class ValidationRun:
             raise ValueError("invalid validation confidence/NMS threshold")  # evaluate.rs:337-345
         mode = LN_PRE_LETTERBOX if letterbox else LN_PRE_RESIZE_EXACT
         out = []
+        parts = []
         for start in range(0, len(images), self.batch):
             part = list(images[start:start + self.batch])
             real = len(part)
-            part += [part[-1]] * (self.batch - real)
+            parts.append((part + [part[-1]] * (self.batch - real), real))
+        if self.stream is not None and parts:
+            from . import pack_u8_images
+
+            def submit(k):
+                packed = pack_u8_images(parts[k][0])
+                self.stream.submit_u8(None, mode=mode, packed=packed)
+                return packed
+
+            current = submit(0)
+            for k, (part, real) in enumerate(parts):
+                following = submit(k + 1) if k + 1 < len(parts) else None
+                recs = self.stream.collect(current[2], current[3], confidence_threshold, nms_threshold, letterbox, 0, max_per_image)
+                for im, r in zip(part[:real], recs[:real]):
+                    out.append(normalise(r, im.shape[1], im.shape[0]))
+                current = following
+            return out
+        for part, real in parts:
             recs = self.detect_u8(part, confidence_threshold, nms_threshold, letterbox, 0, max_per_image, mode=mode)
             for im, r in zip(part[:real], recs[:real]):
                 out.append(normalise(r, im.shape[1], im.shape[0]))

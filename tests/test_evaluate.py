@@ -90,6 +90,39 @@ def test_validation_run_batches_pads_and_normalises():
         run.detections(images, confidence_threshold=1.5)
 
 
+class FakeStream:
+    """Stands in for the submit_u8 / collect pair of GpuExecutableNetwork on top of a FakeDetector: at most two batches in
+    flight, collected in order."""
+
+    def __init__(self, batch):
+        self.det, self.queue, self.most = FakeDetector(batch), [], 0
+
+    def submit_u8(self, images, mode=0, packed=None):
+        assert images is None and len(self.queue) < 2
+        flat, offsets, widths, heights = packed
+        self.queue.append(([flat[o:o + 3 * w * h].reshape(h, w, 3) for o, w, h in zip(offsets, widths, heights)], mode))
+        self.most = max(self.most, len(self.queue))
+
+    def collect(self, image_w, image_h, thr, nms, letterbox, top_k, max_per_image):
+        images, mode = self.queue.pop(0)
+        assert list(image_w) == [im.shape[1] for im in images] and list(image_h) == [im.shape[0] for im in images]
+        return self.det(images, thr, nms, letterbox, top_k, max_per_image, mode=mode)
+
+
+def test_validation_run_streamed_gives_the_same_report():
+    images = [np.full((10 + i, 20 + 2 * i, 3), 25 * (i + 1), np.uint8) for i in range(9)]
+    labels = [np.array([[0, 0.5, 0.5, 1.0, 1.0]], np.float32)] * 9
+    plain = ev.ValidationRun(FakeDetector(4), 4, 1)
+    fake = FakeStream(4)
+    streamed = ev.ValidationRun(None, 4, 1, stream=fake)
+    a = plain.detections(images, confidence_threshold=0.2, letterbox=False)
+    b = streamed.detections(images, confidence_threshold=0.2, letterbox=False)
+    assert len(a) == len(b) == 9 and all(np.array_equal(x, y) for x, y in zip(a, b))
+    assert fake.most == 2 and not fake.queue and [c[0] for c in fake.det.calls] == [4, 4, 4]
+    assert plain.evaluate(images, labels, confidence_threshold=0.2) == streamed.evaluate(images, labels, confidence_threshold=0.2)
+    assert streamed.detections([], confidence_threshold=0.2) == []
+
+
 def test_detect_server_protocol(tmp_path):
     # lightnet-cli/src/main.rs:558-661: a reply per line, errors as {"error": ...}, default threshold 0.25, normalised boxes
     paths = []
@@ -139,6 +172,10 @@ def test_batched_callers_over_a_real_network(tmp_path):
             run = ev.ValidationRun(net.detect_u8, batch, 80)
             dets.append(run.detections(images, confidence_threshold=0.2, letterbox=True, max_per_image=256))
             reports.append(run.evaluate(images, labels, confidence_threshold=0.2, letterbox=True, max_per_image=256))
+            if batch == 4:  # the same pass through the two-slot stream of the network
+                streamed = ev.ValidationRun(net.detect_u8, batch, 80, stream=net)
+                for a, b in zip(dets[-1], streamed.detections(images, confidence_threshold=0.2, letterbox=True, max_per_image=256)):
+                    assert np.array_equal(a, b)
         assert sum(len(d) for d in dets[0]) > 10
         for a, b in zip(*dets):
             assert np.array_equal(a, b)
