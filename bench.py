@@ -67,24 +67,48 @@ LAYER_CLASS_PROFILES = {
 }
 
 
-def layer_classes(layers, per_layer_ms, batch, top=10):
-    """Per layer class (kernel, stride, channels -> filters): launches, total ms, TOP/s over the class, and the ncu summary that
-    holds its tensor-pipe counters where one is committed.  Sorted by time, the `top` slowest classes."""
+def layer_bytes(layers, i, batch):
+    """Algorithmic bytes of convolution i: input, weights and output once at storage width (f32 output for a head), and the
+    residual read where the shortcut behind it runs in its epilogue."""
+    l = layers[i]
+    head = i + 1 < len(layers) and layers[i + 1]["kind"] == "yolo"
+    fused = i + 1 < len(layers) and layers[i + 1]["kind"] == "shortcut"
+    return (batch * l["in_w"] * l["in_h"] * l["in_c"] + l["out_c"] * l["in_c"] * l["size"] ** 2
+            + batch * l["out_w"] * l["out_h"] * l["out_c"] * (4 if head else 2 if fused else 1))
+
+
+def layer_classes(layers, per_layer_ms, batch, peak_tops, hbm_gbs, top=10):
+    """Per layer class (kernel, stride, channels -> filters): launches, total ms, TOP/s over the class, its arithmetic intensity
+    (operations per algorithmic byte), the roofline that intensity allows (peak x min(1, intensity / ridge), ridge = peak /
+    HBM bandwidth) with the fraction of it reached, and the ncu summary that holds its counters where one is committed.
+    Sorted by time, the `top` slowest classes; the second value is the whole stack against the sum of its layers' bounds."""
     acc = {}
-    for l, ms in zip(layers, per_layer_ms):
+    t_bound = t_all = 0.0
+    for i, (l, ms) in enumerate(zip(layers, per_layer_ms)):
         if l["kind"] != "conv" or ms <= 0:
             continue
         key = (l["size"], l["stride_x"], l["in_c"], l["out_c"])
         ops = 2.0 * l["out_w"] * l["out_h"] * l["out_c"] * l["in_c"] * l["size"] ** 2 * batch
-        a = acc.setdefault(key, [0, 0.0, 0.0])
+        nbytes = float(layer_bytes(layers, i, batch))
+        a = acc.setdefault(key, [0, 0.0, 0.0, 0.0])
         a[0] += 1
         a[1] += float(ms)
         a[2] += ops
+        a[3] += nbytes
+        if i > 0:  # (the first layer is not a launch of the tensor-core kernel)
+            t_bound += max(ops / (peak_tops * 1e12), nbytes / (hbm_gbs * 1e9)) * 1e3
+            t_all += float(ms)
+    ridge = peak_tops * 1e12 / (hbm_gbs * 1e9)
     rows = []
-    for key, (n, ms, ops) in sorted(acc.items(), key=lambda kv: -kv[1][1])[:top]:
+    for key, (n, ms, ops, nbytes) in sorted(acc.items(), key=lambda kv: -kv[1][1])[:top]:
+        ai = ops / nbytes
+        bound = peak_tops * min(1.0, ai / ridge)
         rows.append({"layer": "%dx%d s%d C%d->K%d" % (key[0], key[0], key[1], key[2], key[3]), "launches": n, "ms": round(ms, 4),
-                     "tops": round(ops / ms / 1e9, 1), "profile": LAYER_CLASS_PROFILES.get(key)})
-    return rows
+                     "tops": round(ops / ms / 1e9, 1), "ops_per_byte": round(ai, 1), "bound_tops": round(bound, 1),
+                     "frac_of_bound": round(ops / ms / 1e9 / bound, 3), "profile": LAYER_CLASS_PROFILES.get(key)})
+    return rows, {"ridge_ops_per_byte": round(ridge, 1), "bound_ms": round(t_bound, 4), "measured_ms": round(t_all, 4),
+                  "frac": round(t_bound / t_all, 4) if t_all > 0 else None,
+                  "basis": "sum over the tensor-core layers of max(operations / peak, algorithmic bytes / measured HBM bandwidth) against the sum of their measured times (profiled forward)"}
 
 
 def conv_bytes_per_image(layers):
@@ -394,14 +418,31 @@ def run_mma_peak(args, be, rank, world, local_rank):
     iters = 8192
     launches0 = be.launch_count
     vals = {name: max(be.mma_peak(dt, iters) for _ in range(max(args.steps, 3))) for name, dt in (("int8", ln.LN_Q8), ("fp8", ln.LN_F8), ("f16", ln.LN_F16))}
-    bf16_tf, _, basis = measured_peaks()
+    bf16_tf, hbm_file, basis = measured_peaks()
+    # the other denominator measured here as well: a large device-to-device copy (1 GiB read + 1 GiB written per pass, so far
+    # beyond L2), best of a few passes, CUDA events on the copying stream
+    import torch
+    dev = torch.device("cuda", local_rank)
+    src = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    dst = torch.empty_like(src)
+    best = 0.0
+    for i in range(8):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dst.copy_(src)
+        e1.record()
+        e1.synchronize()
+        if i >= 3:
+            best = max(best, 2.0 * src.numel() / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    del src, dst
     if rank == 0:
         emit_line({"metric": WORKLOADS["mma-peak"]["metric"], "value": vals["int8"], "unit": "TOP/s", "n_gpus": world, "steps": max(args.steps, 3), "warmup": 1,
                    "ms_per_step": 2.0 * 128 * 256 * 32 * 4 * iters * be_sm_count(be) / (vals["int8"] * 1e12) * 1e3, "higher_is_better": True, "scaling": "weak",
                    "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                    "config": {"workload": "tcgen05.mma kind::i8 / f8f6f4 / f16, %d x 4 instructions per SM, best of %d launches" % (iters, max(args.steps, 3)),
                               "l2": "no memory traffic: operands stay in shared memory"},
-                   "peaks_tops": vals, "gpu_launches": int(be.launch_count - launches0),
+                   "peaks_tops": vals, "copy_gbs": {"value": best, "basis": "device-to-device copy of 1 GiB (read + write bytes), best of 5 after 3 warm-ups", "measured_peaks_file": hbm_file},
+                   "gpu_launches": int(be.launch_count - launches0),
                    "roofline": {"bound": "tensor", "kernel": "mma_peak_kernel", "achieved": vals["int8"], "peak": 2.0 * bf16_tf, "unit": "TOP/s",
                                 "frac": vals["int8"] / (2.0 * bf16_tf), "traffic": None, "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf)}})
 
@@ -714,6 +755,7 @@ def main():
     mma_peak = max(be.mma_peak(prec, 4096) for _ in range(3))  # the same denominator measured: a tcgen05.mma-only loop on every SM
     achieved = ops_img * B / (umma_ms * 1e-3) / 1e12 if umma_ms > 0 else 0.0
 
+    classes, adjusted = layer_classes(layers, per_layer, B, peak, hbm_gbs)
     if rank == 0:
         line = {
             "metric": wl["metric"], "value": B * world * args.steps / (ms * 1e-3), "unit": "images/s", "n_gpus": world, "steps": args.steps,
@@ -743,9 +785,9 @@ def main():
                          "peak_basis": "2 x %s bf16 sustained (%.1f TFLOP/s)" % (basis, bf16_tf), "launches_per_step": umma_launches,
                          "peak_mma_loop": mma_peak, "frac_of_mma_loop": achieved / mma_peak if mma_peak > 0 else None,
                          "peak_mma_loop_basis": "tcgen05.mma-only loop of this library on this GPU (ln_debug_mma_peak), burst clocks",
-                         "ms_per_step": umma_ms},
+                         "ms_per_step": umma_ms, "intensity_adjusted": adjusted},
             "kernel_classes_ms": {k: v[0] for k, v in per_op.items()},
-            "layer_classes": layer_classes(layers, per_layer, B),
+            "layer_classes": classes,
             "nms_gbs": {"value": head_bytes(layers, B) / (nms_ms * 1e-3) / 1e9 if nms_ms > 0 else None, "unit": "GB/s",
                         "basis": "f32 head tensors read once (%d bytes) / phases_ms.decode_nms" % head_bytes(layers, B),
                         "frac_of_hbm": head_bytes(layers, B) / (nms_ms * 1e-3) / 1e9 / hbm_gbs if nms_ms > 0 else None},
