@@ -73,7 +73,7 @@ def layer_bytes(layers, i, batch):
     l = layers[i]
     head = i + 1 < len(layers) and layers[i + 1]["kind"] == "yolo"
     fused = i + 1 < len(layers) and layers[i + 1]["kind"] == "shortcut"
-    return (batch * l["in_w"] * l["in_h"] * l["in_c"] + l["out_c"] * l["in_c"] * l["size"] ** 2
+    return (batch * l["in_w"] * l["in_h"] * l["in_c"] * (4 if i == 0 else 1) + l["out_c"] * l["in_c"] * l["size"] ** 2  # (the first layer reads the f32 image)
             + batch * l["out_w"] * l["out_h"] * l["out_c"] * (4 if head else 2 if fused else 1))
 
 
