@@ -267,10 +267,17 @@ struct ln_net {
     bool fuse_shortcut = true;  // a linear [shortcut] whose input is a convolution nobody else reads runs in that convolution's epilogue
     std::vector<char> fused_into_next;  // per layer (8-bit plan): 1 = runs in the next layer's shortcut epilogue, no output; 2 = output kept in space-to-depth layout
     bool use_graph = true;
-    cudaGraphExec_t graph_exec = nullptr;
-    const void* graph_input = nullptr;
-    bool graph_exact = false;
-    int graph_warm = 0;  // eager runs seen with the current key; the graph is captured on the second
+    // One graph per (input pointer, epilogue mode): a caller that alternates between a few input tensors (the two slots of
+    // ln_net_submit) replays a graph for each.  A key runs eagerly the first time it is seen and is captured the second time, so a
+    // caller whose input pointer changes on every call pays no capture; the least recently used entry makes room.
+    struct GraphSlot {
+        const void* input = nullptr;
+        bool exact = false;
+        cudaGraphExec_t exec = nullptr;
+        unsigned long long used = 0;
+    };
+    GraphSlot graphs[4];
+    unsigned long long graph_clock = 0;
     // optional per-launch timing
     bool profile = false;
     std::vector<cudaEvent_t> prof_events;
@@ -421,9 +428,10 @@ void release_heads(ln_net* net) {
     net->modern_heads.clear();
 }
 void release_graph(ln_net* net) {
-    if (net->graph_exec) { cudaGraphExecDestroy(net->graph_exec); net->graph_exec = nullptr; }
-    net->graph_input = nullptr;
-    net->graph_warm = 0;
+    for (auto& g : net->graphs) {
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+        g = ln_net::GraphSlot();
+    }
 }
 
 void release_plan(ln_net* net) {
@@ -1025,18 +1033,23 @@ int forward_any(ln_net* net, const ln_tensor* input) {
         if (!net->use_graph || net->profile) rc = run_plan(net, (const float*)input->ptr);
         else {
             // launch-bound otherwise (about a thousand launches per batch): replay one captured graph
-            if (net->graph_input != input->ptr || net->graph_exact != ctx->exact_epilogue) {
-                release_graph(net);
-                net->graph_input = input->ptr;
-                net->graph_exact = ctx->exact_epilogue;
-            }
-            if (net->graph_exec) {
-                LN_CUDA(ctx, cudaGraphLaunch(net->graph_exec, ctx->stream));
+            ln_net::GraphSlot* slot = nullptr;
+            for (auto& g : net->graphs)
+                if (g.used && g.input == input->ptr && g.exact == ctx->exact_epilogue) slot = &g;
+            if (slot && slot->exec) {
+                LN_CUDA(ctx, cudaGraphLaunch(slot->exec, ctx->stream));
                 ctx->launches += (int64_t)net->steps.size() * (net->batch / mb);
                 rc = LN_OK;
-            } else if (net->graph_warm == 0) {
-                rc = run_plan(net, (const float*)input->ptr);  // first run is eager (kernel attributes get set here)
-                net->graph_warm = 1;
+            } else if (!slot) {
+                // first sight of this key: an eager run (kernel attributes get set here), and the key is remembered
+                slot = &net->graphs[0];
+                for (auto& g : net->graphs)
+                    if (g.used < slot->used) slot = &g;
+                if (slot->exec) cudaGraphExecDestroy(slot->exec);
+                *slot = ln_net::GraphSlot();
+                slot->input = input->ptr;
+                slot->exact = ctx->exact_epilogue;
+                rc = run_plan(net, (const float*)input->ptr);
             } else {
                 cudaGraph_t graph = nullptr;
                 LN_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
@@ -1044,12 +1057,13 @@ int forward_any(ln_net* net, const ln_tensor* input) {
                 cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
                 if (rc == LN_OK && e != cudaSuccess) rc = ln_fail(ctx, LN_ERR_CUDA, "graph capture: %s", cudaGetErrorString(e));
                 if (rc == LN_OK) {
-                    e = cudaGraphInstantiate(&net->graph_exec, graph, 0);
-                    if (e != cudaSuccess) rc = ln_fail(ctx, LN_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+                    e = cudaGraphInstantiate(&slot->exec, graph, 0);
+                    if (e != cudaSuccess) { slot->exec = nullptr; rc = ln_fail(ctx, LN_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
                 }
                 if (graph) cudaGraphDestroy(graph);
-                if (rc == LN_OK) LN_CUDA(ctx, cudaGraphLaunch(net->graph_exec, ctx->stream));
+                if (rc == LN_OK) LN_CUDA(ctx, cudaGraphLaunch(slot->exec, ctx->stream));
             }
+            slot->used = ++net->graph_clock;
         }
         if (rc == LN_OK) rc = ln_check_status(ctx, "ln_net_forward");
     }
