@@ -1119,6 +1119,29 @@ def test_submit_u8_collect_gives_the_detections_of_detect_u8(be):
     assert all(np.array_equal(want[2][b], got_2[b]) for b in range(batch))
 
 
+def test_graphs_per_input_tensor_replay_the_eager_results(be):
+    """The 8-bit forward keeps one CUDA graph per input pointer seen twice (four entries, least recently used out): six input
+    tensors visited in turn, three times over, give on every visit the detections of the eager run."""
+    batch = 2
+    o = orc.Net(MINI_CFG, batch)
+    blob = synth.he_weights(o.layers(), 66, bn_identity=False)
+    xs = [synth.uniform_images(batch, o.channels, o.height, o.width, 80 + i) for i in range(6)]
+    net = ln.GpuExecutableNetwork(be, MINI_CFG, batch, ln.LN_Q8)
+    net.load_weights(blob)
+    net.calibrate(xs[0])
+    args = (640, 480, 0.2, 0.45, True, 0, 256)
+    tensors = [be.upload_f32(x.shape, x) for x in xs]
+    net.set_cuda_graph(False)
+    want = [net.detect_device(t, *args) for t in tensors]
+    assert sum(len(d) for w in want for d in w) > 50
+    net.set_cuda_graph(True)
+    for order in (range(6), range(6), (0, 1, 0, 1, 0, 1, 2, 3, 2, 3), reversed(range(6)), (5, 5, 5, 0, 0, 0)):
+        for i in order:
+            got = net.detect_device(tensors[i], *args)
+            for b in range(batch):
+                assert np.array_equal(want[i][b], got[b]), i
+
+
 def test_gaussian_yolo_head_is_decoded_like_a_yolo_head(be):
     """[gaussian_yolo] is the same identity layer and the same decode as [yolo] at inference (model.rs:4513-4543,
     exec_forward.rs:908-912, detect.rs:78): a network whose heads carry that name gives the records of the [yolo] one."""
