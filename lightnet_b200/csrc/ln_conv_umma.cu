@@ -209,11 +209,6 @@ __device__ __forceinline__ uint32_t quant_i8_magic(float a, float inv_s) {
     t = fminf(fmaxf(t, -127.0f), 127.0f);  // NaN -> -127
     return __float_as_uint(__fadd_rn(t, 12582912.0f));
 }
-// signed byte `b` (0..3) of w as a float, FMA pipe only: (byte ^ 0x80) is byte + 128 as an unsigned number
-__device__ __forceinline__ float s8_to_float(uint32_t w, int b) {
-    const uint32_t u = (w >> (8 * b)) & 0xFFu;
-    return __fadd_rn(__uint_as_float(0x4B000000u | (u ^ 0x80u)), -8388736.0f);
-}
 __device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
@@ -226,6 +221,34 @@ __device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, 
     asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(c0), "f"(c1));
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+
+// d = a * b and d = a + b in the same packed form (each half rounds like the scalar instruction)
+__device__ __forceinline__ void fmul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    unsigned long long a, b, d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(b0), "f"(b1));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    unsigned long long a, b, d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(b0), "f"(b1));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+// The four signed bytes of w as floats: w ^ 0x80808080 holds byte + 128 as unsigned numbers, each placed under the exponent of
+// 2^23 by one byte permute; the subtraction of 2^23 + 128 is exact.
+__device__ __forceinline__ void s8x4_to_float(uint32_t w, float (&f)[4]) {
+    const uint32_t x = w ^ 0x80808080u;
+    float u[4];
+    u[0] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650));
+    u[1] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651));
+    u[2] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652));
+    u[3] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653));
+    fadd2(f[0], f[1], u[0], u[1], -8388736.0f, -8388736.0f);
+    fadd2(f[2], f[3], u[2], u[3], -8388736.0f, -8388736.0f);
 }
 
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are BK bytes wide and swizzled
@@ -556,14 +579,24 @@ __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p)
                 if (p.res != nullptr) {
                     // fused shortcut, the arithmetic of the stand-alone shortcut kernel applied to the codes just produced
                     const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+                    // (two values per instruction where the packed f32x2 forms exist: every product, sum and fma rounds exactly
+                    // like its scalar twin, so the codes are those of the stand-alone kernel)
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
+                        float c[4], r[4], v[4];
+                        s8x4_to_float(packed[j], c);
+                        s8x4_to_float(rw[j], r);
                         uint32_t u[4];
 #pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            float v = __fmul_rn(s8_to_float(packed[j], b), p.s_c);
-                            v = __fmaf_rn(s8_to_float(rw[j], b), p.s_res, v);
-                            u[b] = quant_i8_magic(v, p.inv_sy2);
+                        for (int b = 0; b < 4; b += 2) {
+                            fmul2(v[b], v[b + 1], c[b], c[b + 1], p.s_c, p.s_c);
+                            ffma2(v[b], v[b + 1], r[b], r[b + 1], p.s_res, p.s_res, v[b], v[b + 1]);
+                            fmul2(v[b], v[b + 1], v[b], v[b + 1], p.inv_sy2, p.inv_sy2);
+                            v[b] = fminf(fmaxf(v[b], -127.0f), 127.0f);  // NaN -> -127, as in quant_i8_magic
+                            v[b + 1] = fminf(fmaxf(v[b + 1], -127.0f), 127.0f);
+                            fadd2(v[b], v[b + 1], v[b], v[b + 1], 12582912.0f, 12582912.0f);
+                            u[b] = __float_as_uint(v[b]);
+                            u[b + 1] = __float_as_uint(v[b + 1]);
                         }
                         packed[j] = pack4_low_bytes(u[0], u[1], u[2], u[3]);
                     }
