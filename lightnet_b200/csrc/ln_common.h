@@ -70,6 +70,7 @@ struct ln_conv_weights {
     float* wscale = nullptr;        // [fpad] per-filter scale (device)
     std::vector<float> h_wscale;    // host copy
     float max_l1 = 0.0f;            // max over filters of the sum of |code| (bounds the int8 accumulators)
+    float max_scale = 0.0f;         // largest per-filter scale
     void* w_oihw = nullptr;         // [filters][channels][k][k] codes in the reference's weight order (SIMT path)
     // binary16 weights (dtype LN_F16): the f32 source is kept and packed by the first convolution that names kernel size and channels
     ln_tensor* src_f32 = nullptr;

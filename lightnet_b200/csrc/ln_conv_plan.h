@@ -23,6 +23,7 @@ struct ln_conv_umma_params {
     int subs;  // an accumulator tile is handed to the epilogue as `subs` units of bn / subs columns
     int b_resident;  // the weights of the (single) filter tile stay in shared memory for the whole kernel
     int small_acc;  // every accumulator is known to stay below 2^22 in magnitude
+    int acc_shift;  // fast int8 epilogue: low accumulator bits dropped so that what is left stays below 2^22 (0 = none)
     int R, S, stride, pad;
     int cblocks, cpad;
     int OW, OH, N, F, fpad_used;
@@ -87,6 +88,8 @@ struct ln_conv_geom {
     int act = 0, out_kind = 0;
     float inv_sy = 1.0f;
     bool small_acc = false;  // 127 * max over filters of sum|w code| < 2^22
+    // Larger accumulators in the fast epilogue: this many low bits are dropped first (see ln_acc_shift); 0 = none, -1 = not allowed
+    int acc_shift = 0;
     // x is the 2x2 space-to-depth image of the 32-channel input ([H/2][W/2][4 * 32], sub-pixel (y & 1) * 2 + (x & 1) major):
     // the 3x3 stride-2 pad-1 convolution described here is then run as a 2x2 stride-1 one over 128-byte rows
     bool s2d_input = false;
@@ -129,3 +132,18 @@ int ln_conv_stem_launch(ln_ctx* ctx, int kind, const float* x_nchw, float inv_sx
 
 // Reads the device status word; returns LN_OK or LN_ERR_TIMEOUT (and clears the word).
 int ln_check_status(ln_ctx* ctx, const char* where);
+
+// The fast int8 epilogue converts an accumulator to binary32 by adding it to the bits of 1.5 * 2^23, which needs |accumulator| < 2^22.
+// Where the bound 127 * max_l1 (max_l1 = largest sum of |weight code| of a filter) is larger, the low `shift` bits are dropped
+// first; that moves a pre-activation by at most 2^(shift - 1) accumulator units (the mean is put back into the bias), i.e.
+// 2^(shift - 1) * s_x * s_w / s_y output codes, which has to stay at or under 0.02 of a code for every filter.
+// Returns the shift (0 when none is needed) or -1 when no shift up to 8 bits meets both conditions.
+inline int ln_acc_shift(float max_l1, float x_scale, float max_w_scale, float inv_sy) {
+    const float bound = 127.0f * max_l1;
+    for (int sh = 0; sh <= 8; ++sh) {
+        if (bound >= 4194304.0f * (float)(1 << sh)) continue;
+        if (sh == 0) return 0;
+        return (float)(1 << (sh - 1)) * x_scale * max_w_scale * inv_sy <= 0.02f ? sh : -1;
+    }
+    return -1;
+}

@@ -545,14 +545,29 @@ __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p)
                     // 1.5 * 2^23 + accumulator; the table holds {mult 2i, mult 2i+1, bias 2i, bias 2i+1} divided by the output scale,
                     // the bias carrying -1.5 * 2^23 * mult, so one packed FMA yields two pre-activations in code units;
                     // activation and rounding run in packed binary16.
+                    // Accumulators that may reach 2^22 lose their low p.acc_shift bits first (the table carries the larger
+                    // multiplier and the mean of what is dropped); the planner allows that only where it moves a
+                    // pre-activation by no more than 0.02 of a code.
                     const __half2 kh = __float2half2_rn(p.sy_log2e), inv_h = __float2half2_rn(p.inv_sy);
+                    const int sh = p.acc_shift;
+                    if (sh == 0) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
-                        float t0, t1, t2, t3;
-                        ffma2(t0, t1, __int_as_float(0x4B400000 + (int)acc[4 * j]), __int_as_float(0x4B400000 + (int)acc[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
-                        ffma2(t2, t3, __int_as_float(0x4B400000 + (int)acc[4 * j + 2]), __int_as_float(0x4B400000 + (int)acc[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
-                        packed[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
+                            float t0, t1, t2, t3;
+                            ffma2(t0, t1, __int_as_float(0x4B400000 + (int)acc[4 * j]), __int_as_float(0x4B400000 + (int)acc[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
+                            ffma2(t2, t3, __int_as_float(0x4B400000 + (int)acc[4 * j + 2]), __int_as_float(0x4B400000 + (int)acc[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
+                            packed[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
+                            float t0, t1, t2, t3;
+                            ffma2(t0, t1, __int_as_float(0x4B400000 + ((int)acc[4 * j] >> sh)), __int_as_float(0x4B400000 + ((int)acc[4 * j + 1] >> sh)), ma.x, ma.y, ma.z, ma.w);
+                            ffma2(t2, t3, __int_as_float(0x4B400000 + ((int)acc[4 * j + 2] >> sh)), __int_as_float(0x4B400000 + ((int)acc[4 * j + 3] >> sh)), mc.x, mc.y, mc.z, mc.w);
+                            packed[j] = ln_h2_pack(ln_h2_code<ACT>(t0, t1, kh, inv_h), ln_h2_code<ACT>(t2, t3, kh, inv_h));
+                        }
                     }
                 } else {
                     // int32 -> f32: below 2^22 through the bits of 1.5 * 2^23 (two FMA-pipe instructions, exact); otherwise the
@@ -911,11 +926,16 @@ __global__ void pack_s2d_weights_kernel(const uint8_t* __restrict__ w, int fpad,
 // Table of the folded fast epilogue, one float4 per pair of filters: {m0, m1, b0, b1} with m = mult / s_y and
 // b = bias / s_y - 1.5 * 2^23 * m, so that fma(float with the bits 0x4B400000 + accumulator, m, b) is the pre-activation in
 // units of the output scale.
-__global__ void fold_mb_kernel(const float2* __restrict__ mb, int n, float inv_sy, float2* __restrict__ out) {
+__global__ void fold_mb_kernel(const float2* __restrict__ mb, int n, float inv_sy, int shift, float2* __restrict__ out) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;  // pair index
     if (2 * i >= n) return;
-    const float m0 = __fmul_rn(mb[2 * i].x, inv_sy), m1 = __fmul_rn(mb[2 * i + 1].x, inv_sy);
-    const float b0 = __fmaf_rn(-12582912.0f, m0, __fmul_rn(mb[2 * i].y, inv_sy)), b1 = __fmaf_rn(-12582912.0f, m1, __fmul_rn(mb[2 * i + 1].y, inv_sy));
+    // with `shift` low accumulator bits dropped (floor) the multiplier grows by 2^shift and the bias takes the mean of what was
+    // dropped, (2^shift - 1) / 2 accumulator units
+    const float up = (float)(1 << shift), mean = 0.5f * (float)((1 << shift) - 1);
+    const float u0 = __fmul_rn(mb[2 * i].x, inv_sy), u1 = __fmul_rn(mb[2 * i + 1].x, inv_sy);  // codes per accumulator unit
+    const float m0 = __fmul_rn(u0, up), m1 = __fmul_rn(u1, up);
+    const float c0 = __fmaf_rn(mean, u0, __fmul_rn(mb[2 * i].y, inv_sy)), c1 = __fmaf_rn(mean, u1, __fmul_rn(mb[2 * i + 1].y, inv_sy));
+    const float b0 = __fmaf_rn(-12582912.0f, m0, c0), b1 = __fmaf_rn(-12582912.0f, m1, c1);
     out[2 * i] = make_float2(m0, m1);
     out[2 * i + 1] = make_float2(b0, b1);
 }
@@ -1126,11 +1146,14 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     p.mb_folded = nullptr;
     p.sy_log2e = 1.44269504f / g.inv_sy;
     // (the folded epilogue drops the lower clamp of the activations that are bounded below: needs 0.31 / s_y <= 127)
-    if (g.kind == LN_KIND_I8 && g.small_acc && g.out_kind == LN_OUT_Q && g.inv_sy <= 400.0f && g.F % 32 == 0) {
+    const int acc_shift = g.small_acc ? 0 : g.acc_shift;  // (callers that do not set acc_shift leave it 0 with small_acc false: no fold)
+    p.acc_shift = 0;
+    if (g.kind == LN_KIND_I8 && (g.small_acc || acc_shift > 0) && g.out_kind == LN_OUT_Q && g.inv_sy <= 400.0f && g.F % 32 == 0) {
+        p.acc_shift = acc_shift;
         plan->aux_mbf_bytes = (size_t)g.fpad * sizeof(float2);
         plan->aux_mbf = (float2*)ln_pool_alloc(ctx, plan->aux_mbf_bytes);
         if (!plan->aux_mbf) return LN_ERR_CUDA;
-        fold_mb_kernel<<<(g.fpad / 2 + 127) / 128, 128, 0, ctx->stream>>>(mb, g.fpad, g.inv_sy, plan->aux_mbf);
+        fold_mb_kernel<<<(g.fpad / 2 + 127) / 128, 128, 0, ctx->stream>>>(mb, g.fpad, g.inv_sy, acc_shift, plan->aux_mbf);
         LN_LAUNCHED(ctx);
         p.mb_folded = plan->aux_mbf;
     }
@@ -1159,24 +1182,38 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
         plan->smem = (size_t)a_stages * box + (p.b_resident ? b_total : (size_t)stages * b_bytes) + 1024 /*alignment slack*/ + 512 /*barriers*/;
     } else {
     p.b_resident = (allow_resident && p.tiles_f == 1 && b_total + res_min_stages * 128u * bk <= smem_budget) ? 1 : 0;
-    const uint32_t ring_budget = (p.b_resident ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u);
+    uint32_t ring_budget = (p.b_resident ? smem_budget : 200u * 1024u - tab_bytes) - (p.b_resident ? b_total : 0u);
     // Two pipelines (see the kernel) where one issuing thread cannot keep the tensor pipe busy and two double stages fit; the
     // tiles of a pair must share their filter tile, so the grid has to be a multiple of tiles_f.
     // LN_CONV_PIPES = 1 / 2 forces one / two wherever possible (for A/B measurements).
     const char* pipes_env = getenv("LN_CONV_PIPES");
     const int pipes_forced = pipes_env ? atoi(pipes_env) : 0;
-    const uint32_t stage2_bytes = 256u * bk + (p.b_resident ? 0u : (uint32_t)bn * bk);
+    uint32_t stage2_bytes = 256u * bk + (p.b_resident ? 0u : (uint32_t)bn * bk);
     int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
     // Measured (us, one -> two issuers): 3x3 C128 -> K128 at 76x76 x64 106 -> 83; 3x3 stride 2 C64 -> K128 at 304x304 x16 88 -> 65;
     // 3x3 C256 -> K512 at 38x38 x64 94 -> 92; 1x1 C512 -> K256 27 -> 35; the packed 3x3 C32 -> K64 (256 virtual filters) 111 -> 129:
     // filter tiles of 256 keep one issuer (their instructions are long enough, and three 64 KB stages are too few).
     const bool pipes_rule = bn <= 128 && g.k * g.k * (g.cpad / 32) >= 16;
+    bool streamed_for_pipes = false;
+    // Two issuers drain a stage twice as fast, so the ring has to be deeper: where resident weights would leave fewer than four
+    // double stages and streaming them leaves four, stream them (3x3 C128 -> K128 at 76x76 x64: 77.8 -> 73.7 us).
+    if (p.b_resident && pipes_forced != 1 && (pipes_rule || pipes_forced == 2) && ring_budget / stage2_bytes < 4 &&
+        (200u * 1024u - tab_bytes) / (256u * bk + (uint32_t)bn * bk) >= 4) {
+        streamed_for_pipes = true;
+        p.b_resident = 0;
+        ring_budget = 200u * 1024u - tab_bytes;
+        stage2_bytes = 256u * bk + (uint32_t)bn * bk;
+    }
     if (ring_budget / stage2_bytes >= 2 && p.num_tiles >= 2 * grid && pipes_forced != 1 && (pipes_rule || pipes_forced == 2)) {
         const int grid2 = grid - grid % p.tiles_f;
         if (grid2 > 0 && grid2 * 20 >= grid * 19) {  // (giving up more than 5 % of the SMs for the alignment is not worth it)
             p.pipes = 2;
             grid = grid2;
         }
+    }
+    if (streamed_for_pipes && p.pipes != 2) {  // one issuer after all: back to the resident weights
+        p.b_resident = 1;
+        ring_budget = smem_budget - b_total;
     }
     const uint32_t stage_bytes = p.pipes == 2 ? stage2_bytes : (p.b_resident ? 128u * bk : (uint32_t)(128 + b_rows) * bk);
     int stages = (int)(ring_budget / stage_bytes);

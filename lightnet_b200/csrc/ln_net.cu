@@ -807,6 +807,7 @@ int build_plan(ln_net* net, int mb) {
                 g.out_kind = head ? LN_OUT_F32 : LN_OUT_Q;
                 g.inv_sy = head ? 1.0f : 1.0f / sy;
                 g.small_acc = kind == LN_KIND_I8 && 127.0f * L.wq->max_l1 < 4194304.0f;
+                g.acc_shift = kind == LN_KIND_I8 && !head ? ln_acc_shift(L.wq->max_l1, sx, L.wq->max_scale, g.inv_sy) : -1;
                 if (head) { g.out = net->heads[st.head_index]->ptr; g.out_pixel_stride = 0; }
                 else if (net->fused_into_next[i] == 1) {
                     const int sl = i + 1, src = net->layers[sl].sources[0];

@@ -1269,6 +1269,8 @@ int32_t ln_conv_weights_q(ln_ctx* ctx, const ln_tensor* weights_f32, int64_t fil
     w->max_l1 = 0.0f;
     for (int64_t f = 0; f < w->fpad; ++f) w->max_l1 = w->h_wscale[(size_t)(w->fpad + f)] > w->max_l1 ? w->h_wscale[(size_t)(w->fpad + f)] : w->max_l1;
     w->h_wscale.resize((size_t)w->fpad);
+    w->max_scale = 0.0f;
+    for (float v : w->h_wscale) w->max_scale = v > w->max_scale ? v : w->max_scale;
     if (e != cudaSuccess) { ln_conv_weights_release(w); return ln_fail(ctx, LN_ERR_CUDA, "weight packing: %s", cudaGetErrorString(e)); }
     *out = w;
     return LN_OK;
@@ -1325,6 +1327,7 @@ int32_t ln_conv2d_bias_act_q(ln_ctx* ctx, const ln_tensor* x, const ln_conv_weig
     g.OH = (int)oh; g.OW = (int)ow; g.act = activation; g.out_kind = out_kind;
     g.inv_sy = out_kind == LN_OUT_Q ? 1.0f / y_scale : 1.0f;
     g.small_acc = kind == LN_KIND_I8 && 127.0f * weights->max_l1 < 4194304.0f;
+    g.acc_shift = kind == LN_KIND_I8 && out_kind == LN_OUT_Q ? ln_acc_shift(weights->max_l1, x->scale, weights->max_scale, g.inv_sy) : -1;
     g.out = y->ptr; g.out_pixel_stride = y->cstride;
     g.groups = (int)groups;
     if (groups > 1) { g.cpad = (int)ln_round_up(channels, 32); g.w_cpad = (int)weights->cpad; }
