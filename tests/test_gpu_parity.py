@@ -125,6 +125,7 @@ Q8_CASES = [  # (n, c, h, w, f, k, stride, pad): the benchmark's single-layer sw
     (2, 128, 76, 76, 128, 3, 1, 1),    # 128-byte rows, resident weights of 147 KB
     (2, 64, 152, 152, 64, 3, 1, 1),    # row-shifted boxes, 64-byte rows, weights resident
     (1, 64, 80, 72, 512, 3, 1, 1),     # row-shifted boxes, weight tiles in their own ring
+    (1, 512, 19, 19, 256, 3, 1, 1),    # accumulators up to 2^25: the fast epilogue drops three low bits before its conversion
 ]
 
 
