@@ -253,6 +253,33 @@ __device__ __forceinline__ uint32_t ln_h2_code(float t0, float t1, __half2 k, __
     y = __hadd2(__hmin2(y, __float2half2_rn(127.0f)), __float2half2_rn(1536.0f));  // ulp is 1 in [1024, 2048): the low mantissa bits are rne(y)
     return *reinterpret_cast<uint32_t*>(&y);
 }
+// The activation alone for two pre-activations that are already in units of the output scale (see ln_h2_code): the value in
+// those units, unrounded and unclamped.  Used where the conversion that follows saturates by itself (FP8 output).
+template <int ACT>
+__device__ __forceinline__ __half2 ln_h2_value(float t0, float t1, __half2 k, __half2 inv_s) {
+    uint32_t tb;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(tb) : "f"(t1), "f"(t0));  // first source -> upper half
+    const __half2 t = *reinterpret_cast<const __half2*>(&tb);
+    if (ACT == LN_ACT_LEAKY) return __hmax2(t, __hmul2(t, __float2half2_rn(0.1f)));
+    if (ACT == LN_ACT_RELU) return __hmax2(t, __float2half2_rn(0.0f));
+    if (ACT == LN_ACT_MISH) {
+        const __half2 e = ln_h2_ex2(__hmin2(__hmul2(t, k), __float2half2_rn(5.0f * 1.44269504f)));
+        const __half2 w = __hmul2(e, __hadd2(e, __float2half2_rn(2.0f)));
+        return __hmul2(t, __hmul2(w, ln_h2_rcp(__hadd2(w, __float2half2_rn(2.0f)))));
+    }
+    if (ACT == LN_ACT_SWISH || ACT == LN_ACT_LOGISTIC) {
+        const __half2 e = ln_h2_ex2(__hmin2(__hmul2(t, __hneg2(k)), __float2half2_rn(10.0f * 1.44269504f)));
+        const __half2 sg = ln_h2_rcp(__hadd2(e, __float2half2_rn(1.0f)));
+        return ACT == LN_ACT_SWISH ? __hmul2(t, sg) : __hmul2(sg, inv_s);
+    }
+    return t;
+}
+// two binary16 values -> two E4M3 codes (round to nearest even, saturating to +-448), lower half in the lower byte
+__device__ __forceinline__ uint32_t ln_h2_to_e4m3x2(__half2 v) {
+    uint16_t d;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(d) : "r"(*reinterpret_cast<const uint32_t*>(&v)));
+    return (uint32_t)d;
+}
 // {a.lo, a.hi, b.lo, b.hi} code bytes of two ln_h2_act_quant results -> one packed word
 __device__ __forceinline__ uint32_t ln_h2_pack(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x6420); }
 

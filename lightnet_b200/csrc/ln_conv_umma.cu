@@ -623,6 +623,28 @@ __device__ __forceinline__ void conv_epilogue_role(const ln_conv_umma_params& p)
                 if (kRoleTiming && p.debug) { dbg_math += tq2 - tq1; dbg_st += clock64() - tq2; }
                 continue;
             }
+            if (KIND == LN_KIND_F8 && folded && p.out_kind == LN_OUT_Q) {
+                // ---- FP8 fast path (the planner folds only when every chunk has its 32 filters): pre-activations in units of the
+                // output scale by one packed fma on the binary32 accumulators, activation in packed binary16, two E4M3 codes
+                // per conversion
+                const uint32_t mtab = tab_base + 8u * (uint32_t)(f0 + c0);
+                tmem_ld_wait();
+                if (!valid) continue;
+                const __half2 kh = __float2half2_rn(p.sy_log2e), inv_h = __float2half2_rn(p.inv_sy);
+                uint32_t packed[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 ma = lds_f4(mtab + 32u * j), mc = lds_f4(mtab + 32u * j + 16u);
+                    float t0, t1, t2, t3;
+                    ffma2(t0, t1, __uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]), ma.x, ma.y, ma.z, ma.w);
+                    ffma2(t2, t3, __uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3]), mc.x, mc.y, mc.z, mc.w);
+                    packed[j] = ln_h2_to_e4m3x2(ln_h2_value<ACT>(t0, t1, kh, inv_h)) | (ln_h2_to_e4m3x2(ln_h2_value<ACT>(t2, t3, kh, inv_h)) << 16);
+                }
+                uint4* o = (uint4*)((uint8_t*)p.out + opix * p.out_pixel_stride + fo);
+                o[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                o[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                continue;
+            }
             // ---- general path: f32 / raw-accumulator outputs (NCHW), FP8, and int8 chunks with fewer than 32 real filters.
             // The {mult, bias} pairs come two per 16-byte load (the table is padded to a multiple of 32 filters).
             const int nf = p.F - (f0 + c0);  // real filters from this chunk's first column on (32 or more: all of the chunk)
@@ -931,11 +953,14 @@ __global__ void fold_mb_kernel(const float2* __restrict__ mb, int n, float inv_s
     if (2 * i >= n) return;
     // with `shift` low accumulator bits dropped (floor) the multiplier grows by 2^shift and the bias takes the mean of what was
     // dropped, (2^shift - 1) / 2 accumulator units
+    // (shift < 0: binary32 accumulators, FP8 layers -- nothing dropped and no 1.5 * 2^23 to take out)
+    const bool f32acc = shift < 0;
+    if (f32acc) shift = 0;
     const float up = (float)(1 << shift), mean = 0.5f * (float)((1 << shift) - 1);
     const float u0 = __fmul_rn(mb[2 * i].x, inv_sy), u1 = __fmul_rn(mb[2 * i + 1].x, inv_sy);  // codes per accumulator unit
     const float m0 = __fmul_rn(u0, up), m1 = __fmul_rn(u1, up);
     const float c0 = __fmaf_rn(mean, u0, __fmul_rn(mb[2 * i].y, inv_sy)), c1 = __fmaf_rn(mean, u1, __fmul_rn(mb[2 * i + 1].y, inv_sy));
-    const float b0 = __fmaf_rn(-12582912.0f, m0, c0), b1 = __fmaf_rn(-12582912.0f, m1, c1);
+    const float b0 = f32acc ? c0 : __fmaf_rn(-12582912.0f, m0, c0), b1 = f32acc ? c1 : __fmaf_rn(-12582912.0f, m1, c1);
     out[2 * i] = make_float2(m0, m1);
     out[2 * i + 1] = make_float2(b0, b1);
 }
@@ -1148,12 +1173,15 @@ int ln_conv_umma_plan_build(ln_ctx* ctx, ln_conv_umma_plan* plan, const ln_conv_
     // (the folded epilogue drops the lower clamp of the activations that are bounded below: needs 0.31 / s_y <= 127)
     const int acc_shift = g.small_acc ? 0 : g.acc_shift;  // (callers that do not set acc_shift leave it 0 with small_acc false: no fold)
     p.acc_shift = 0;
-    if (g.kind == LN_KIND_I8 && (g.small_acc || acc_shift > 0) && g.out_kind == LN_OUT_Q && g.inv_sy <= 400.0f && g.F % 32 == 0) {
+    // FP8 layers with 8-bit output and whole 32-filter chunks take the same packed binary16 epilogue (binary32 accumulators go
+    // straight into the fma; the conversion to E4M3 saturates by itself)
+    const bool fold_f8 = g.kind == LN_KIND_F8 && g.out_kind == LN_OUT_Q && g.F % 32 == 0 && !(getenv("LN_CONV_F8_FOLD") && atoi(getenv("LN_CONV_F8_FOLD")) == 0);
+    if (fold_f8 || (g.kind == LN_KIND_I8 && (g.small_acc || acc_shift > 0) && g.out_kind == LN_OUT_Q && g.inv_sy <= 400.0f && g.F % 32 == 0)) {
         p.acc_shift = acc_shift;
         plan->aux_mbf_bytes = (size_t)g.fpad * sizeof(float2);
         plan->aux_mbf = (float2*)ln_pool_alloc(ctx, plan->aux_mbf_bytes);
         if (!plan->aux_mbf) return LN_ERR_CUDA;
-        fold_mb_kernel<<<(g.fpad / 2 + 127) / 128, 128, 0, ctx->stream>>>(mb, g.fpad, g.inv_sy, acc_shift, plan->aux_mbf);
+        fold_mb_kernel<<<(g.fpad / 2 + 127) / 128, 128, 0, ctx->stream>>>(mb, g.fpad, g.inv_sy, fold_f8 ? -1 : acc_shift, plan->aux_mbf);
         LN_LAUNCHED(ctx);
         p.mb_folded = plan->aux_mbf;
     }
