@@ -203,6 +203,18 @@ __device__ __forceinline__ void approx_score_key(float obj, float x, unsigned& k
     khi = k + d;
 }
 
+// The same interval for either kind of head: heads with new_coords take the class value as it is, so their score is one
+// exact product and the interval a single key (NaN scores are left to the exact evaluation, which drops them).
+__device__ __forceinline__ bool score_key_interval(float obj, float x, int new_coords, bool approx_ok, unsigned& klo, unsigned& khi) {
+    if (new_coords) {
+        const float conf = __fmul_rn(obj, x);
+        klo = khi = conf_key(conf);
+        return approx_ok && conf == conf;
+    }
+    approx_score_key(obj, x, klo, khi);
+    return approx_ok && x == x;  // a NaN logit goes to the exact evaluation, whose clamps decide what it means
+}
+
 constexpr int kWarpBuf = 512;  // keys one warp of the fill pass buffers in shared memory before it reserves space in the pool
 
 // Range of keys one pass over the heads is interested in, [rlo, rhi] inclusive, from the state of the image.
@@ -266,7 +278,6 @@ __global__ void __launch_bounds__(256) yolo_head_hist_kernel(const __grid_consta
         const float* img_raw = h.raw + (size_t)img * h.n_anchor * epa * stride;
         const float obj = score_obj(h, __ldg(img_raw + (size_t)(a * epa + 4) * stride + idx));
         const float* __restrict__ cls_raw = img_raw + (size_t)(a * epa + 5) * stride + idx;
-        const bool fast = approx_ok && !new_coords;
         if (obj > p.thr) {
             // consecutive classes often fall into the same bin (always, when scores saturate): runs are counted in registers
             unsigned run_bin = kBins, run_len = 0;
@@ -280,8 +291,7 @@ __global__ void __launch_bounds__(256) yolo_head_hist_kernel(const __grid_consta
                 for (int j = 0; j < 8; ++j) {
                     const float x = xs[j];
                     unsigned klo, khi;
-                    approx_score_key(obj, x, klo, khi);
-                    const bool usable = fast && x == x;  // a NaN logit goes to the exact evaluation, whose clamps decide what it means
+                    const bool usable = score_key_interval(obj, x, new_coords, approx_ok, klo, khi);
                     const bool out = khi <= kthr || klo > r.rhi_ck || khi < r.rlo_ck;  // certainly not a candidate of interest
                     unsigned bin = klo >> 20;
                     const bool certain = level0 && klo > kthr && khi < r.rhi_ck && bin == (khi >> 20);  // the bin is all this pass needs
@@ -395,7 +405,6 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
         const int new_coords = s_ca[j] < 0 ? 1 : 0, stride = s_stride[j];
         const unsigned cell = (unsigned)s_ca[j] & 0x7FFFFFFFu;
         const float* __restrict__ cls_raw = s_ptr[j];
-        const bool fast = approx_ok && !new_coords;
         for (int c0 = 0; c0 < p.classes; c0 += 8) {
             if (have) {
                 float xs[8];
@@ -406,8 +415,7 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
                 for (int q = 0; q < 8; ++q) {
                     const float x = xs[q];
                     unsigned klo, khi;
-                    approx_score_key(obj, x, klo, khi);
-                    const bool out = fast && x == x && (khi <= kthr || khi < r.rlo_ck || klo > r.rhi_ck);
+                    const bool out = score_key_interval(obj, x, new_coords, approx_ok, klo, khi) && (khi <= kthr || khi < r.rlo_ck || klo > r.rhi_ck);
                     if (!out && c0 + q < p.classes) {
                         const unsigned long long key = exact_key_in_range(p, r, obj, x, new_coords, cell, (unsigned)(c0 + q));
                         if (key != 0ull) emit(key);
@@ -430,11 +438,8 @@ __global__ void __launch_bounds__(256) yolo_head_fill_kernel(const __grid_consta
             const unsigned cell = (unsigned)s_ca[j] & 0x7FFFFFFFu;
             const float x = __ldg(s_ptr[j] + (size_t)c * s_stride[j]);
             bool maybe = true;
-            if (approx_ok && !new_coords && x == x) {
-                unsigned klo, khi;
-                approx_score_key(obj, x, klo, khi);
-                maybe = !(khi <= kthr || khi < r.rlo_ck || klo > r.rhi_ck);
-            }
+            unsigned klo, khi;
+            if (score_key_interval(obj, x, new_coords, approx_ok, klo, khi)) maybe = !(khi <= kthr || khi < r.rlo_ck || klo > r.rhi_ck);
             if (maybe) {
                 const unsigned long long key = exact_key_in_range(p, r, obj, x, new_coords, cell, (unsigned)c);
                 if (key != 0ull) emit(key);
